@@ -1,0 +1,148 @@
+"""Trace replay on the GPU against the plain implementation: the same requests whole, with the
+last 32 tokens one by one, in portions of changing size, and mixed with other requests in a pool
+so small that pages are used again; in float32 and in bfloat16."""
+
+import json
+import os
+import subprocess
+import sys
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+import cuttings
+from plain_llama import TINY_WEIGHTS, tiny_configs
+
+pytestmark = pytest.mark.gpu
+ROOT = Path(__file__).resolve().parent.parent
+
+
+def requests_for(cfg_index: int) -> dict[str, list[int]]:
+    cfg = tiny_configs()[cfg_index]
+    lengths = [100, 37, 64, 5, 81, 128, 50] if cfg_index == 0 else [200, 1, 63, 100, 40, 256, 17]
+    return {f"r{i}": cuttings.random_tokens(n, cfg["vocab_size"], 100 * cfg_index + i)
+            for i, n in enumerate(lengths)}
+
+
+def replay(model_dir, dtype, steps, page_size, max_tokens=None):
+    from tokasaurus_b200.engine.trace import TraceReplayer
+
+    if max_tokens is None:
+        max_tokens = cuttings.max_live_tokens(steps)
+    rp = TraceReplayer(str(model_dir), dtype, max_tokens, page_size=page_size)
+    outs = []
+    for st in steps:
+        outs.append(rp.run_step(st))
+        rp.runner.cache.check()
+    assert not rp.runner.cache.requests, "every request was ended, so nothing may be held"
+    assert all(f == g.allocator.num_pages for f, g in zip(rp.runner.cache.num_free_pages(), rp.runner.cache.groups))
+    return cuttings.collect(steps, outs)
+
+
+def compare(got, want64, want32, dtype):
+    for rid, ref in want64.items():
+        tol = cuttings.tolerance(dtype, ref, want32[rid] if want32 else None)
+        err = np.abs(got[rid] - ref).max(axis=1)
+        bad = np.nonzero(err > tol)[0]
+        assert bad.size == 0, (f"{dtype}: request {rid}: first wrong token at position {bad[0]} "
+                               f"(error {err[bad[0]]:.3g}, tolerance {tol:.3g}); {bad.size} of {len(err)} wrong")
+        if dtype == "float32":
+            # same argmax wherever the plain implementation's top two are clearly apart
+            srt = np.sort(ref, axis=1)
+            clear = (srt[:, -1] - srt[:, -2]) > 4 * tol
+            assert np.array_equal(got[rid].argmax(1)[clear], ref.argmax(1)[clear])
+
+
+CUTS = {
+    "whole": cuttings.whole,
+    "prefix_then_single": cuttings.prefix_then_single,
+    "changing_portions": cuttings.changing_portions,
+    "mixed": cuttings.mixed,
+}
+
+
+@pytest.fixture(scope="module")
+def plain(tiny_model_dirs):
+    out = {}
+    for i, d in enumerate(tiny_model_dirs):
+        reqs = requests_for(i)
+        out[i] = (reqs, cuttings.plain_logits(d, reqs, torch.float64), cuttings.plain_logits(d, reqs, torch.float32))
+    return out
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("cut", list(CUTS))
+@pytest.mark.parametrize("cfg_index", [0, 1])
+def test_cuttings_match_plain(tiny_model_dirs, plain, cfg_index, cut, dtype):
+    reqs, p64, p32 = plain[cfg_index]
+    steps = CUTS[cut](reqs)
+    got = replay(tiny_model_dirs[cfg_index], dtype, steps, TINY_WEIGHTS[cfg_index]["page_size"])
+    compare(got, p64, p32, dtype)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_cuttings_agree_with_each_other(tiny_model_dirs, plain, dtype):
+    """The logits at a position do not depend on the cutting beyond rounding: compare the cuttings
+    with one another, which is a tighter test in bfloat16 than the comparison with the plain
+    implementation."""
+    reqs, p64, _ = plain[1]
+    base = replay(tiny_model_dirs[1], dtype, cuttings.whole(reqs), 8)
+    for name in ("prefix_then_single", "changing_portions", "mixed"):
+        got = replay(tiny_model_dirs[1], dtype, CUTS[name](reqs), 8)
+        for rid in reqs:
+            top = np.abs(p64[rid]).max()
+            tol = (2e-5 if dtype == "float32" else 2e-2) * top
+            err = np.abs(got[rid] - base[rid]).max(axis=1)
+            bad = np.nonzero(err > tol)[0]
+            assert bad.size == 0, f"{dtype} {name}: request {rid} first differs at position {bad[0]} ({err[bad[0]]:.3g})"
+
+
+def test_mixed_pool_is_reused(tiny_model_dirs):
+    """The mixed cutting must really hand pages out again."""
+    from tokasaurus_b200.engine.trace import TraceReplayer
+
+    reqs = requests_for(0)
+    steps = cuttings.mixed(reqs)
+    rp = TraceReplayer(str(tiny_model_dirs[0]), "float32", cuttings.max_live_tokens(steps), page_size=16)
+    seen: dict[int, set] = {}
+    for st in steps:
+        rp.run_step(dict(st, end=[]))
+        for rid, rc in rp.runner.cache.requests.items():
+            for p in rc.tables[0]:
+                seen.setdefault(p, set()).add(rid)
+        for rid in st["end"]:
+            rp.runner.cache.free(rid)
+            del rp.lengths[rid]
+    assert any(len(v) > 1 for v in seen.values()), "no page was used by two requests"
+
+
+def test_trace_run_program(tiny_model_dirs, tmp_path):
+    """bin/trace_run as a user calls it: JSON lines in, 'done <step>' lines and .f32 files out."""
+    reqs = {k: v for k, v in list(requests_for(0).items())[:5]}
+    steps = cuttings.mixed(reqs, seed=3)
+    text = "\n".join(json.dumps(s) for s in steps) + "\n"
+    out = tmp_path / "out"
+    proc = subprocess.run(
+        [sys.executable, str(ROOT / "bin" / "trace_run"), "--model", str(tiny_model_dirs[0]), "--dtype", "float32",
+         "--out", str(out), "--max-tokens", str(cuttings.max_live_tokens(steps))],
+        input=text, capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    assert proc.stdout.split("\n")[:-1] == [f"done {s['step']}" for s in steps]
+    vocab = tiny_configs()[0]["vocab_size"]
+    outs = []
+    for s in steps:
+        n = sum(len(e["want"]) for e in s["entries"])
+        f = out / f"{s['step']}.f32"
+        if n:
+            a = np.fromfile(f, dtype="<f4")
+            assert a.size == n * vocab
+            outs.append(a.reshape(n, vocab))
+        else:
+            assert not f.exists()
+            outs.append(None)
+    got = cuttings.collect(steps, outs)
+    p64 = cuttings.plain_logits(tiny_model_dirs[0], reqs, torch.float64)
+    p32 = cuttings.plain_logits(tiny_model_dirs[0], reqs, torch.float32)
+    compare(got, p64, p32, "float32")

@@ -1,0 +1,43 @@
+"""The step function, batch builder and cache manager together on the CPU, with the plain
+statements of the kernels (tests/kernel_refs.py) in the kernels' place.  This checks the
+bookkeeping (positions, block tables, wanted rows, page reuse), not the kernels: those are
+compared on the GPU."""
+
+import numpy as np
+import pytest
+import torch
+
+import cuttings
+import kernel_refs
+from plain_llama import TINY_WEIGHTS, tiny_configs
+
+
+@pytest.fixture()
+def cpu_kernels(monkeypatch):
+    kernel_refs.install_cpu_kernels(monkeypatch)
+
+
+def _replay(model_dir, steps, page_size):
+    from tokasaurus_b200.engine.trace import TraceReplayer
+
+    rp = TraceReplayer(str(model_dir), "float32", cuttings.max_live_tokens(steps), page_size=page_size, device="cpu")
+    outs = []
+    for st in steps:
+        outs.append(rp.run_step(st))
+        rp.runner.cache.check()
+    assert not rp.runner.cache.requests
+    return cuttings.collect(steps, outs)
+
+
+@pytest.mark.parametrize("cfg_index", [0, 1])
+@pytest.mark.parametrize("cut", ["whole", "changing_portions", "mixed"])
+def test_replay_on_cpu_matches_plain(cpu_kernels, tiny_model_dirs, cfg_index, cut):
+    cfg = tiny_configs()[cfg_index]
+    lengths = [40, 9, 33, 1, 24] if cfg_index == 0 else [37, 2, 17, 41, 8]
+    reqs = {f"r{i}": cuttings.random_tokens(n, cfg["vocab_size"], 7 * cfg_index + i) for i, n in enumerate(lengths)}
+    steps = getattr(cuttings, cut)(reqs)
+    got = _replay(tiny_model_dirs[cfg_index], steps, TINY_WEIGHTS[cfg_index]["page_size"])
+    want = cuttings.plain_logits(tiny_model_dirs[cfg_index], reqs, torch.float64)
+    for rid in reqs:
+        err = np.abs(got[rid] - want[rid]).max(axis=1)
+        assert err.max() < 1e-4 * max(1.0, np.abs(want[rid]).max()), (rid, int(err.argmax()), float(err.max()))

@@ -1,0 +1,252 @@
+// Memory-bound kernels of the forward pass: embedding gather, fused residual add + RMS norm,
+// rotary encoding fused with the write of keys and values into cache pages, SiLU-gated product,
+// row gather.  Each is written for both activation types (float and bfloat16); arithmetic is float.
+#include "common.cuh"
+
+using namespace tkb;
+
+// ------------------------------------------------------------------------------------------------
+// Embedding gather into the float32 residual stream.
+// A token id < 0 means "the token this request sampled last": it is read from last_token[slot].
+// Rows whose token_seq is < 0 are padding and become zero.
+template <typename T>
+__global__ void embed_gather_kernel(const T* __restrict__ table, const int* __restrict__ ids,
+                                    const int* __restrict__ token_seq, const int* __restrict__ seq_slot,
+                                    const int* __restrict__ last_token, float* __restrict__ x, int H, int V,
+                                    int* __restrict__ status) {
+  const int t = blockIdx.x;
+  const int s = token_seq[t];
+  int id = ids[t];
+  bool valid = s >= 0;
+  if (valid && id < 0) id = last_token[seq_slot[s]];
+  if (valid && (id < 0 || id >= V)) {
+    if (threadIdx.x == 0) atomicOr(status, TKB_STATUS_BAD_TOKEN_ID);
+    valid = false;
+  }
+  float* xr = x + (size_t)t * H;
+  if (!valid) {
+    for (int i = threadIdx.x; i < H; i += blockDim.x) xr[i] = 0.f;
+    return;
+  }
+  const T* row = table + (size_t)id * H;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) xr[i] = to_float(row[i]);
+}
+
+template <typename T>
+static int embed_gather_launch(const void* table, const int* ids, const int* token_seq, const int* seq_slot,
+                               const int* last_token, float* x, int n_tokens, int H, int V, int* status,
+                               cudaStream_t st) {
+  if (n_tokens <= 0) return 0;
+  int threads = H >= 1024 ? 256 : (H >= 256 ? 128 : 64);
+  embed_gather_kernel<T><<<n_tokens, threads, 0, st>>>((const T*)table, ids, token_seq, seq_slot, last_token, x, H,
+                                                       V, status);
+  return launch_status();
+}
+TKB_EXPORT int tkb_embed_gather_f32(const void* table, const int* ids, const int* token_seq, const int* seq_slot,
+                                    const int* last_token, float* x, int n_tokens, int H, int V, int* status,
+                                    void* st) {
+  return embed_gather_launch<float>(table, ids, token_seq, seq_slot, last_token, x, n_tokens, H, V, status,
+                                    (cudaStream_t)st);
+}
+TKB_EXPORT int tkb_embed_gather_bf16(const void* table, const int* ids, const int* token_seq, const int* seq_slot,
+                                     const int* last_token, float* x, int n_tokens, int H, int V, int* status,
+                                     void* st) {
+  return embed_gather_launch<__nv_bfloat16>(table, ids, token_seq, seq_slot, last_token, x, n_tokens, H, V, status,
+                                            (cudaStream_t)st);
+}
+
+// ------------------------------------------------------------------------------------------------
+// x += delta (if delta is given; x is float32 and is written back), then
+// out = (x * rsqrt(mean(x^2) + eps)) * w, rounded once to the activation type.
+// One block per row.
+template <typename T>
+__global__ void add_rmsnorm_kernel(float* __restrict__ x, const T* __restrict__ delta, const float* __restrict__ w,
+                                   T* __restrict__ out, float eps, int H) {
+  __shared__ float scratch[33];
+  const size_t base = (size_t)blockIdx.x * H;
+  float* xr = x + base;
+  float ss = 0.f;
+  if (delta != nullptr) {
+    const T* dr = delta + base;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+      float v = xr[i] + to_float(dr[i]);
+      xr[i] = v;
+      ss += v * v;
+    }
+  } else {
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+      float v = xr[i];
+      ss += v * v;
+    }
+  }
+  const float total = block_sum(ss, scratch);
+  const float rstd = rsqrtf(total / (float)H + eps);
+  T* orow = out + base;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) orow[i] = from_float<T>(xr[i] * rstd * w[i]);
+}
+
+template <typename T>
+static int add_rmsnorm_launch(float* x, const void* delta, const float* w, void* out, float eps, int rows, int H,
+                              cudaStream_t st) {
+  if (rows <= 0) return 0;
+  int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
+  add_rmsnorm_kernel<T><<<rows, threads, 0, st>>>(x, (const T*)delta, w, (T*)out, eps, H);
+  return launch_status();
+}
+TKB_EXPORT int tkb_add_rmsnorm_f32(float* x, const void* delta, const float* w, void* out, float eps, int rows,
+                                   int H, void* st) {
+  return add_rmsnorm_launch<float>(x, delta, w, out, eps, rows, H, (cudaStream_t)st);
+}
+TKB_EXPORT int tkb_add_rmsnorm_bf16(float* x, const void* delta, const float* w, void* out, float eps, int rows,
+                                    int H, void* st) {
+  return add_rmsnorm_launch<__nv_bfloat16>(x, delta, w, out, eps, rows, H, (cudaStream_t)st);
+}
+
+// ------------------------------------------------------------------------------------------------
+// Rotary position encoding of q and k (half-split pairing: element j pairs with j + rot/2), in
+// place on q, and the write of the rotated k and of v into the cache pages of the token's
+// request.  qkv row layout: [nh*hd | nkv*hd | nkv*hd].  Cache layout per layer: [page, kv head,
+// slot in page, hd].  The angle is the float32 product position * inv_freq[j]; cos and sin use
+// the accurate float routines (full range reduction), once per token and pair, shared by heads.
+// rot == 0 means no position encoding.  Tokens with token_seq < 0 are padding and are skipped.
+template <typename T>
+__global__ void rope_kv_write_kernel(T* __restrict__ qkv, const int* __restrict__ positions,
+                                     const int* __restrict__ token_seq, const int* __restrict__ page_indptr,
+                                     const int* __restrict__ page_ids, const float* __restrict__ inv_freq,
+                                     T* __restrict__ kcache, T* __restrict__ vcache, int nh, int nkv, int hd, int rot,
+                                     int page_size, int num_pages, int write_cache, int* __restrict__ status) {
+  extern __shared__ float cs[];  // cos[rot/2], sin[rot/2]
+  const int t = blockIdx.x;
+  const int s = token_seq[t];
+  if (s < 0) return;
+  const int pos = positions[t];
+  const int half = rot >> 1;
+  for (int j = threadIdx.x; j < half; j += blockDim.x) {
+    float ang = (float)pos * inv_freq[j];
+    float sn, c;
+    sincosf(ang, &sn, &c);
+    cs[j] = c;
+    cs[half + j] = sn;
+  }
+  __syncthreads();
+
+  T* row = qkv + (size_t)t * (size_t)(nh + 2 * nkv) * hd;
+  // q heads: rotate in place.
+  for (int idx = threadIdx.x; idx < nh * half; idx += blockDim.x) {
+    const int h = idx / half, j = idx - h * half;
+    T* p = row + h * hd;
+    const float x1 = to_float(p[j]), x2 = to_float(p[j + half]);
+    const float c = cs[j], sn = cs[half + j];
+    p[j] = from_float<T>(x1 * c - x2 * sn);
+    p[j + half] = from_float<T>(x2 * c + x1 * sn);
+  }
+  if (!write_cache) return;  // a layer call that reads another call's cache writes none of its own
+  const int page = page_ids[page_indptr[s] + pos / page_size];
+  if (page < 0 || page >= num_pages) {
+    if (threadIdx.x == 0) atomicOr(status, TKB_STATUS_BAD_PAGE);
+    return;
+  }
+  const int slot = pos % page_size;
+  const T* krow = row + nh * hd;
+  const T* vrow = krow + nkv * hd;
+  for (int idx = threadIdx.x; idx < nkv * hd; idx += blockDim.x) {
+    const int h = idx / hd, d = idx - h * hd;
+    const size_t dst = (((size_t)page * nkv + h) * page_size + slot) * hd + d;
+    float kv;
+    if (d < half) {
+      kv = to_float(krow[idx]) * cs[d] - to_float(krow[idx + half]) * cs[half + d];
+    } else if (d < rot) {
+      const int j = d - half;
+      kv = to_float(krow[idx]) * cs[j] + to_float(krow[idx - half]) * cs[half + j];
+    } else {
+      kv = to_float(krow[idx]);
+    }
+    kcache[dst] = from_float<T>(kv);
+    vcache[dst] = vrow[idx];
+  }
+}
+
+template <typename T>
+static int rope_kv_write_launch(void* qkv, const int* positions, const int* token_seq, const int* page_indptr,
+                                const int* page_ids, const float* inv_freq, void* kcache, void* vcache,
+                                int n_tokens, int nh, int nkv, int hd, int rot, int page_size, int num_pages,
+                                int write_cache, int* status, cudaStream_t st) {
+  if (n_tokens <= 0) return 0;
+  if (rot < 0 || rot > hd || (rot & 1)) return -2;
+  int work = nh * (rot / 2) > nkv * hd ? nh * (rot / 2) : nkv * hd;
+  int threads = work >= 512 ? 256 : (work >= 128 ? 128 : 64);
+  size_t smem = (size_t)(rot > 0 ? rot : 2) * sizeof(float);
+  rope_kv_write_kernel<T><<<n_tokens, threads, smem, st>>>((T*)qkv, positions, token_seq, page_indptr, page_ids,
+                                                           inv_freq, (T*)kcache, (T*)vcache, nh, nkv, hd, rot,
+                                                           page_size, num_pages, write_cache, status);
+  return launch_status();
+}
+TKB_EXPORT int tkb_rope_kv_write_f32(void* qkv, const int* positions, const int* token_seq, const int* page_indptr,
+                                     const int* page_ids, const float* inv_freq, void* kcache, void* vcache,
+                                     int n_tokens, int nh, int nkv, int hd, int rot, int page_size, int num_pages,
+                                     int write_cache, int* status, void* st) {
+  return rope_kv_write_launch<float>(qkv, positions, token_seq, page_indptr, page_ids, inv_freq, kcache, vcache,
+                                     n_tokens, nh, nkv, hd, rot, page_size, num_pages, write_cache, status,
+                                     (cudaStream_t)st);
+}
+TKB_EXPORT int tkb_rope_kv_write_bf16(void* qkv, const int* positions, const int* token_seq, const int* page_indptr,
+                                      const int* page_ids, const float* inv_freq, void* kcache, void* vcache,
+                                      int n_tokens, int nh, int nkv, int hd, int rot, int page_size, int num_pages,
+                                      int write_cache, int* status, void* st) {
+  return rope_kv_write_launch<__nv_bfloat16>(qkv, positions, token_seq, page_indptr, page_ids, inv_freq, kcache,
+                                             vcache, n_tokens, nh, nkv, hd, rot, page_size, num_pages, write_cache,
+                                             status, (cudaStream_t)st);
+}
+
+// ------------------------------------------------------------------------------------------------
+// out[t, i] = silu(gu[t, i]) * gu[t, I + i]  (gate columns first, then up columns).
+template <typename T>
+__global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, long long total, int I) {
+  for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+       idx += (long long)gridDim.x * blockDim.x) {
+    const long long t = idx / I;
+    const int i = (int)(idx - t * I);
+    const float g = to_float(gu[t * 2 * I + i]);
+    const float u = to_float(gu[t * 2 * I + I + i]);
+    const float sg = g / (1.f + expf(-g));
+    out[idx] = from_float<T>(sg * u);
+  }
+}
+template <typename T>
+static int silu_mul_launch(const void* gu, void* out, int rows, int I, cudaStream_t st) {
+  long long total = (long long)rows * I;
+  if (total <= 0) return 0;
+  long long blocks = (total + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  silu_mul_kernel<T><<<(int)blocks, 256, 0, st>>>((const T*)gu, (T*)out, total, I);
+  return launch_status();
+}
+TKB_EXPORT int tkb_silu_mul_f32(const void* gu, void* out, int rows, int I, void* st) {
+  return silu_mul_launch<float>(gu, out, rows, I, (cudaStream_t)st);
+}
+TKB_EXPORT int tkb_silu_mul_bf16(const void* gu, void* out, int rows, int I, void* st) {
+  return silu_mul_launch<__nv_bfloat16>(gu, out, rows, I, (cudaStream_t)st);
+}
+
+// ------------------------------------------------------------------------------------------------
+// dst[r, :] = src[rows[r], :], rows of row_bytes bytes (a multiple of 2).
+__global__ void gather_rows_kernel(const unsigned short* __restrict__ src, unsigned short* __restrict__ dst,
+                                   const int* __restrict__ rows, int row_halfwords) {
+  const int r = blockIdx.x;
+  const unsigned short* s = src + (size_t)rows[r] * row_halfwords;
+  unsigned short* d = dst + (size_t)r * row_halfwords;
+  if ((row_halfwords & 7) == 0 && ((((uintptr_t)src) | ((uintptr_t)dst)) & 15) == 0) {
+    const uint4* s4 = (const uint4*)s;
+    uint4* d4 = (uint4*)d;
+    for (int i = threadIdx.x; i < (row_halfwords >> 3); i += blockDim.x) d4[i] = s4[i];
+  } else {
+    for (int i = threadIdx.x; i < row_halfwords; i += blockDim.x) d[i] = s[i];
+  }
+}
+TKB_EXPORT int tkb_gather_rows(const void* src, void* dst, const int* rows, int n_rows, int row_bytes, void* st) {
+  if (n_rows <= 0) return 0;
+  if (row_bytes & 1) return -2;
+  gather_rows_kernel<<<n_rows, 128, 0, (cudaStream_t)st>>>((const unsigned short*)src, (unsigned short*)dst, rows,
+                                                          row_bytes / 2);
+  return launch_status();
+}

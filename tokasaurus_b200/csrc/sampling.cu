@@ -1,0 +1,243 @@
+// Next-token choice from float32 logits [R, V]: greedy argmax, or temperature sampling by the
+// Gumbel-max rule  argmax_i(logit_i / T + g_i),  g_i = -log(-log(u_i)),  which draws from
+// softmax(logits / T) without a pass to normalise.  The uniforms come from Philox4x32-10 keyed
+// by the row's stream key (made on the host from the sampling seed and the request) with the
+// counter (vocabulary index / 4, position of the sampled token): the draw does not depend on
+// the row's place in the batch or on what else is in it.
+// Also: the chosen token's log-probability under softmax(logits / T) (T = 1 for greedy rows),
+// the scatter of the chosen ids into the per-slot last-token table, and top-k log-probabilities.
+#include "common.cuh"
+#include <float.h>
+
+using namespace tkb;
+
+namespace {
+
+struct Philox {
+  static constexpr uint32_t M0 = 0xD2511F53u, M1 = 0xCD9E8D57u, W0 = 0x9E3779B9u, W1 = 0xBB67AE85u;
+  __device__ static uint4 run(uint4 c, uint2 k) {
+#pragma unroll
+    for (int r = 0; r < 10; r++) {
+      const uint32_t hi0 = __umulhi(M0, c.x), lo0 = M0 * c.x;
+      const uint32_t hi1 = __umulhi(M1, c.z), lo1 = M1 * c.z;
+      c = make_uint4(hi1 ^ c.y ^ k.x, lo1, hi0 ^ c.w ^ k.y, lo0);
+      k.x += W0;
+      k.y += W1;
+    }
+    return c;
+  }
+};
+
+__device__ __forceinline__ float uniform_open(uint32_t x) {
+  // (0, 1), exactly representable: 24 random bits plus one half.
+  return ((float)(x >> 8) + 0.5f) * (1.0f / 16777216.0f);
+}
+
+struct Best {
+  float v;
+  int i;
+};
+__device__ __forceinline__ Best better(Best a, Best b) {
+  // larger value wins; equal values: smaller index wins (the first maximum)
+  if (b.v > a.v || (b.v == a.v && b.i < a.i)) return b;
+  return a;
+}
+__device__ __forceinline__ Best warp_best(Best a) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    Best b;
+    b.v = __shfl_xor_sync(0xffffffffu, a.v, o);
+    b.i = __shfl_xor_sync(0xffffffffu, a.i, o);
+    a = better(a, b);
+  }
+  return a;
+}
+
+constexpr int SAMPLE_THREADS = 512;
+
+__global__ void __launch_bounds__(SAMPLE_THREADS)
+sample_kernel(const float* __restrict__ logits, const float* __restrict__ temperature,
+              const unsigned long long* __restrict__ stream_key, const int* __restrict__ sample_pos,
+              const int* __restrict__ row_slot, int* __restrict__ out_ids, float* __restrict__ out_logprob,
+              int* __restrict__ last_token, int V) {
+  __shared__ float s_v[SAMPLE_THREADS / 32];
+  __shared__ int s_i[SAMPLE_THREADS / 32];
+  __shared__ float s_m[SAMPLE_THREADS / 32];
+  __shared__ float s_l[SAMPLE_THREADS / 32];
+  __shared__ int s_choice;
+  __shared__ float s_lse;
+  const int r = blockIdx.x;
+  const float* lg = logits + (size_t)r * V;
+  const float T = temperature ? temperature[r] : 0.f;
+  const bool greedy = !(T > 0.f);
+  const float inv_t = greedy ? 1.f : 1.f / T;
+  const unsigned long long key = stream_key ? stream_key[r] : 0ull;
+  const uint2 k2 = make_uint2((uint32_t)key, (uint32_t)(key >> 32));
+  const uint32_t pos = sample_pos ? (uint32_t)sample_pos[r] : 0u;
+
+  Best best = {-FLT_MAX, 0x7fffffff};
+  float m = -FLT_MAX, l = 0.f;  // running max and sum of exp of logits * inv_t
+  const int ngroups = (V + 3) >> 2;
+  for (int g = threadIdx.x; g < ngroups; g += SAMPLE_THREADS) {
+    uint4 rnd = make_uint4(0, 0, 0, 0);
+    if (!greedy) rnd = Philox::run(make_uint4((uint32_t)g, pos, 0u, 0u), k2);
+    const uint32_t rr[4] = {rnd.x, rnd.y, rnd.z, rnd.w};
+#pragma unroll
+    for (int u = 0; u < 4; u++) {
+      const int i = g * 4 + u;
+      if (i >= V) break;
+      const float z = lg[i] * inv_t;
+      if (!(z == z)) continue;  // NaN never wins
+      if (z > m) {
+        l = l * expf(m - z) + 1.f;
+        m = z;
+      } else {
+        l += expf(z - m);
+      }
+      float score = z;
+      if (!greedy) score = z - logf(-logf(uniform_open(rr[u])));
+      Best c = {score, i};
+      best = better(best, c);
+    }
+  }
+  // block reductions
+  best = warp_best(best);
+  float wm = warp_max(m);
+  float wl = warp_sum(l * expf(m - wm));
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (lane == 0) {
+    s_v[warp] = best.v;
+    s_i[warp] = best.i;
+    s_m[warp] = wm;
+    s_l[warp] = wl;
+  }
+  __syncthreads();
+  if (warp == 0) {
+    Best b = {-FLT_MAX, 0x7fffffff};
+    float mm = -FLT_MAX, ll = 0.f;
+    if (lane < SAMPLE_THREADS / 32) {
+      b.v = s_v[lane];
+      b.i = s_i[lane];
+      mm = s_m[lane];
+      ll = s_l[lane];
+    }
+    b = warp_best(b);
+    const float gm = warp_max(mm);
+    const float gl = warp_sum(ll * expf(mm - gm));
+    if (lane == 0) {
+      s_choice = b.i < V ? b.i : 0;
+      s_lse = gm + logf(gl);
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const int c = s_choice;
+    out_ids[r] = c;
+    if (out_logprob) out_logprob[r] = lg[c] * inv_t - s_lse;
+    if (last_token && row_slot && row_slot[r] >= 0) last_token[row_slot[r]] = c;
+  }
+}
+
+// Top-k log-probabilities under softmax(logits / T): k rounds of "largest entry that comes after
+// the previous pick in (value descending, index ascending) order".
+__global__ void __launch_bounds__(SAMPLE_THREADS)
+topk_logprobs_kernel(const float* __restrict__ logits, const float* __restrict__ temperature,
+                     int* __restrict__ out_idx, float* __restrict__ out_lp, int V, int k) {
+  __shared__ float s_v[SAMPLE_THREADS / 32];
+  __shared__ int s_i[SAMPLE_THREADS / 32];
+  __shared__ float s_m[SAMPLE_THREADS / 32];
+  __shared__ float s_l[SAMPLE_THREADS / 32];
+  __shared__ Best s_prev;
+  __shared__ float s_lse;
+  const int r = blockIdx.x;
+  const float* lg = logits + (size_t)r * V;
+  const float T = temperature ? temperature[r] : 0.f;
+  const float inv_t = T > 0.f ? 1.f / T : 1.f;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  // log-sum-exp
+  float m = -FLT_MAX, l = 0.f;
+  for (int i = threadIdx.x; i < V; i += SAMPLE_THREADS) {
+    const float z = lg[i] * inv_t;
+    if (!(z == z)) continue;
+    if (z > m) {
+      l = l * expf(m - z) + 1.f;
+      m = z;
+    } else {
+      l += expf(z - m);
+    }
+  }
+  float wm = warp_max(m);
+  float wl = warp_sum(l * expf(m - wm));
+  if (lane == 0) {
+    s_m[warp] = wm;
+    s_l[warp] = wl;
+  }
+  __syncthreads();
+  if (warp == 0) {
+    float mm = lane < SAMPLE_THREADS / 32 ? s_m[lane] : -FLT_MAX;
+    float ll = lane < SAMPLE_THREADS / 32 ? s_l[lane] : 0.f;
+    const float gm = warp_max(mm);
+    const float gl = warp_sum(ll * expf(mm - gm));
+    if (lane == 0) {
+      s_lse = gm + logf(gl);
+      s_prev.v = FLT_MAX;
+      s_prev.i = -1;
+    }
+  }
+  __syncthreads();
+  for (int round = 0; round < k; round++) {
+    const Best prev = s_prev;
+    Best best = {-FLT_MAX, 0x7fffffff};
+    for (int i = threadIdx.x; i < V; i += SAMPLE_THREADS) {
+      const float z = lg[i] * inv_t;
+      if (!(z == z)) continue;
+      const bool after = z < prev.v || (z == prev.v && i > prev.i);
+      if (after) {
+        Best c = {z, i};
+        best = better(best, c);
+      }
+    }
+    best = warp_best(best);
+    __syncthreads();
+    if (lane == 0) {
+      s_v[warp] = best.v;
+      s_i[warp] = best.i;
+    }
+    __syncthreads();
+    if (warp == 0) {
+      Best b = {-FLT_MAX, 0x7fffffff};
+      if (lane < SAMPLE_THREADS / 32) {
+        b.v = s_v[lane];
+        b.i = s_i[lane];
+      }
+      b = warp_best(b);
+      if (lane == 0) {
+        const bool found = b.i < V;
+        out_idx[(size_t)r * k + round] = found ? b.i : -1;
+        out_lp[(size_t)r * k + round] = found ? b.v - s_lse : -INFINITY;
+        s_prev = b;
+      }
+    }
+    __syncthreads();
+  }
+}
+
+}  // namespace
+
+TKB_EXPORT int tkb_sample(const float* logits, const float* temperature, const unsigned long long* stream_key,
+                          const int* sample_pos, const int* row_slot, int* out_ids, float* out_logprob,
+                          int* last_token, int R, int V, void* st) {
+  if (R <= 0) return 0;
+  if (V <= 0) return -2;
+  sample_kernel<<<R, SAMPLE_THREADS, 0, (cudaStream_t)st>>>(logits, temperature, stream_key, sample_pos, row_slot,
+                                                           out_ids, out_logprob, last_token, V);
+  return launch_status();
+}
+
+TKB_EXPORT int tkb_topk_logprobs(const float* logits, const float* temperature, int* out_idx, float* out_lp, int R,
+                                 int V, int k, void* st) {
+  if (R <= 0 || k <= 0) return 0;
+  if (V <= 0) return -2;
+  topk_logprobs_kernel<<<R, SAMPLE_THREADS, 0, (cudaStream_t)st>>>(logits, temperature, out_idx, out_lp, V, k);
+  return launch_status();
+}

@@ -1,0 +1,177 @@
+"""One step's input: a batch of (request, its next tokens), turned into device arrays.
+
+The reference ships a step as Python lists (``ModelInput``, tokasaurus/model/types.py:343-384,
+built by ``seqs_to_input``, tokasaurus/manager/input_building.py:151-320) and turns them into
+several tensors that are copied one by one (tokasaurus/model/utils.py:113-202,227-264).  Here
+all integer arrays of a step are packed into one pinned buffer and reach the device in one copy;
+the views below are slices of that device buffer.
+
+Per token: id (or -1: "the token this request sampled last", read on the device from the slot
+table as in tokasaurus/model/basic_worker.py:101-114), position, and the row of its request in the
+batch.  Per request: state slot, first token row, number of tokens, key/value length after this
+step.  Per cache group: the block tables in CSR form (``indptr`` over requests, ``page_ids``), as in
+tokasaurus/model/types.py:41-56,122-147.  ``logit_rows``: token rows whose logits are wanted.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Sequence
+
+import numpy as np
+import torch
+
+
+@dataclass
+class StepEntry:
+    request: object
+    tokens: Sequence[int] | None  # None: one token, the one this request sampled last (kept on the device)
+    start: int  # position of the first of these tokens within the request
+    want: Sequence[int] = ()  # indices into ``tokens`` whose logits are wanted
+
+    @property
+    def n_tokens(self) -> int:
+        return 1 if self.tokens is None else len(self.tokens)
+
+
+@dataclass
+class GroupTables:
+    indptr: torch.Tensor  # int32 [S + 1]
+    page_ids: torch.Tensor  # int32 [sum of pages]
+
+
+@dataclass
+class HostBatch:
+    """The same step as plain numpy arrays, for planners and for mixers that loop over requests."""
+
+    token_ids: np.ndarray
+    positions: np.ndarray
+    token_seq: np.ndarray
+    seq_slot: np.ndarray
+    seq_q_start: np.ndarray
+    seq_q_len: np.ndarray
+    seq_kv_len: np.ndarray
+    logit_rows: np.ndarray
+    table_indptr: list[np.ndarray]
+    table_pages: list[np.ndarray]
+    requests: list[object] = field(default_factory=list)
+
+
+class StepContext:
+    """Everything a part may look at while it runs one step."""
+
+    def __init__(self, host: HostBatch, cache_manager, device: torch.device, stager: "Stager"):
+        self.host = host
+        self.cache_manager = cache_manager
+        self.device = device
+        self.n_tokens = int(host.token_ids.shape[0])
+        self.n_seqs = int(host.seq_slot.shape[0])
+        self.all_rows_wanted = (
+            host.logit_rows.shape[0] == self.n_tokens
+            and bool(np.array_equal(host.logit_rows, np.arange(self.n_tokens, dtype=np.int32)))
+        )
+        arrays = [host.token_ids, host.positions, host.token_seq, host.seq_slot, host.seq_q_start, host.seq_q_len,
+                  host.seq_kv_len, host.logit_rows]
+        for ip, pg in zip(host.table_indptr, host.table_pages):
+            arrays += [ip, pg]
+        views = stager.upload(arrays)
+        (self.token_ids, self.positions, self.token_seq, self.seq_slot, self.seq_q_start, self.seq_q_len,
+         self.seq_kv_len, self.logit_rows) = views[:8]
+        self.tables = [GroupTables(views[8 + 2 * g], views[9 + 2 * g]) for g in range(len(host.table_indptr))]
+        self.last_token = cache_manager.last_token
+        self.status = stager.status
+
+    def layer_cache(self, entry: int, writable: bool = True):
+        return self.cache_manager.layer_cache(entry, writable)
+
+
+class Stager:
+    """A pinned host buffer and its device twin; ``upload`` packs int32 arrays into the first and
+    copies once.  Segments start on 16-byte boundaries."""
+
+    def __init__(self, device: torch.device, capacity_ints: int = 1 << 16):
+        self.device = device
+        self.status = torch.zeros((1,), dtype=torch.int32, device=device)
+        self._alloc(capacity_ints)
+
+    def _alloc(self, n: int) -> None:
+        self.capacity = n
+        pin = self.device.type == "cuda"
+        self.host = torch.empty((n,), dtype=torch.int32, pin_memory=pin)
+        self.host_np = self.host.numpy()
+        self.dev = torch.empty((n,), dtype=torch.int32, device=self.device)
+        self.bytes_last_upload = 0
+        self._copied = torch.cuda.Event() if pin else None
+        self._pending = False
+
+    def upload(self, arrays: Sequence[np.ndarray]) -> list[torch.Tensor]:
+        offs = []
+        total = 0
+        for a in arrays:
+            offs.append(total)
+            total += (a.shape[0] + 3) & ~3
+        total = max(total, 4)
+        if total > self.capacity:
+            # wait for copies in flight from the old pinned buffer before dropping it
+            if self.device.type == "cuda":
+                torch.cuda.current_stream(self.device).synchronize()
+            self._alloc(max(total, 2 * self.capacity))
+        if self._pending:
+            self._copied.synchronize()  # the last copy out of the pinned buffer must be over before it is rewritten
+            self._pending = False
+        for a, o in zip(arrays, offs):
+            if a.dtype != np.int32:
+                raise TypeError("step arrays are int32")
+            self.host_np[o:o + a.shape[0]] = a
+        self.dev[:total].copy_(self.host[:total], non_blocking=True)
+        if self._copied is not None:
+            self._copied.record()
+            self._pending = True
+        self.bytes_last_upload = total * 4
+        return [self.dev[o:o + a.shape[0]] for a, o in zip(arrays, offs)]
+
+
+def build_host_batch(entries: Sequence[StepEntry], cache_manager) -> HostBatch:
+    """Lay the entries out as one batch.  Every request must already hold pages for the positions
+    it brings (``CacheManager.ensure_capacity``)."""
+    seen = set()
+    tok: list[int] = []
+    pos: list[int] = []
+    tseq: list[int] = []
+    rows: list[int] = []
+    slot, q_start, q_len, kv_len = [], [], [], []
+    ps = cache_manager.page_size
+    n_groups = len(cache_manager.groups)
+    indptr = [[0] for _ in range(n_groups)]
+    pages: list[list[int]] = [[] for _ in range(n_groups)]
+    for s, e in enumerate(entries):
+        if e.request in seen:
+            raise ValueError(f"request {e.request!r} appears twice in one step")
+        seen.add(e.request)
+        n = e.n_tokens
+        if n <= 0:
+            raise ValueError(f"request {e.request!r} brings no tokens")
+        rc = cache_manager.requests[e.request]
+        end = e.start + n
+        for g in range(n_groups):
+            table = rc.tables[g]
+            need = (end + ps - 1) // ps
+            if len(table) < need:
+                raise ValueError(f"request {e.request!r} holds {len(table)} pages of group {g}, needs {need}")
+            pages[g].extend(table[:need])
+            indptr[g].append(len(pages[g]))
+        base = len(tok)
+        tok.extend([-1] if e.tokens is None else [int(t) for t in e.tokens])
+        pos.extend(range(e.start, end))
+        tseq.extend([s] * n)
+        for w in e.want:
+            if not 0 <= w < n:
+                raise ValueError(f"request {e.request!r}: wanted place {w} is outside its {n} tokens")
+            rows.append(base + w)
+        slot.append(rc.slot)
+        q_start.append(base)
+        q_len.append(n)
+        kv_len.append(end)
+    i32 = lambda x: np.asarray(x, dtype=np.int32)  # noqa: E731
+    return HostBatch(i32(tok), i32(pos), i32(tseq), i32(slot), i32(q_start), i32(q_len), i32(kv_len), i32(rows),
+                     [i32(x) for x in indptr], [i32(x) for x in pages], [e.request for e in entries])

@@ -1,0 +1,255 @@
+"""Tensor-level entry points of the hand-written kernels.
+
+Each function checks its arguments, then launches one kernel on the current CUDA stream through
+the ctypes library built by ``tokasaurus_b200.kernels.build``.  There is no other
+implementation behind these functions: a tensor that is not on a CUDA device, or a library
+that cannot be built or loaded, raises.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import math
+from ctypes import c_float, c_int, c_void_p
+
+import torch
+
+from tokasaurus_b200.kernels import build
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+_SUFFIX = {torch.float32: "f32", torch.bfloat16: "bf16"}
+
+
+def _suffix(dtype: torch.dtype) -> str:
+    try:
+        return _SUFFIX[dtype]
+    except KeyError:
+        raise KernelError(f"kernels exist for float32 and bfloat16 activations, not {dtype}") from None
+
+
+def _ptr(t: torch.Tensor | None) -> c_void_p:
+    if t is None:
+        return c_void_p(0)
+    return c_void_p(t.data_ptr())
+
+
+def _stream() -> c_void_p:
+    return c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _need_cuda(*tensors: torch.Tensor | None) -> None:
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise KernelError(
+                "this engine runs on CUDA devices only; got a tensor on " + str(t.device)
+            )
+
+
+def _need(cond: bool, msg: str) -> None:
+    if not cond:
+        raise KernelError(msg)
+
+
+def _check(code: int, what: str) -> None:
+    if code != 0:
+        if code > 0:
+            raise KernelError(f"{what}: CUDA launch failed with error {code}")
+        reason = {-2: "sizes not supported", -3: "grid too large", -4: "size beyond the built-in scratch"}.get(
+            code, "refused"
+        )
+        raise KernelError(f"{what}: {reason} (code {code})")
+
+
+def _fn(lib: ctypes.CDLL, name: str):
+    try:
+        f = getattr(lib, name)
+    except AttributeError:
+        raise KernelError(f"compiled kernel library lacks the symbol {name}") from None
+    f.restype = c_int
+    return f
+
+
+class _Libs:
+    def __init__(self) -> None:
+        self._cache: dict[tuple, ctypes.CDLL] = {}
+
+    def get(self, source: str, **defines) -> ctypes.CDLL:
+        key = (source, tuple(sorted(defines.items())))
+        lib = self._cache.get(key)
+        if lib is None:
+            lib = build.load_module(source, defines or None)
+            self._cache[key] = lib
+        return lib
+
+
+_libs = _Libs()
+
+
+def check_head_dim(hd: int) -> None:
+    if hd % 16 or not 16 <= hd <= 256:
+        raise KernelError(f"attention kernels take head sizes that are multiples of 16 up to 256, not {hd}")
+
+
+def prepare(head_dims=(), dtype: torch.dtype = torch.bfloat16) -> None:
+    """Build and load everything a model with these head sizes needs (first call compiles)."""
+    _libs.get("elementwise.cu")
+    _libs.get("sgemm.cu")
+    _libs.get("sampling.cu")
+    for hd in head_dims:
+        check_head_dim(hd)
+        _libs.get("attention_simt.cu", TKB_HD=hd)
+
+
+# ---------------------------------------------------------------------------------------------
+def embed_gather(table: torch.Tensor, ids: torch.Tensor, token_seq: torch.Tensor, seq_slot: torch.Tensor,
+                 last_token: torch.Tensor, x_out: torch.Tensor, status: torch.Tensor) -> None:
+    """x_out[t] = table[ids[t]] as float32; ids[t] < 0 takes last_token[seq_slot[token_seq[t]]]."""
+    _need_cuda(table, ids, token_seq, seq_slot, last_token, x_out, status)
+    n, H = x_out.shape
+    V = table.shape[0]
+    _need(table.shape[1] == H and table.is_contiguous() and x_out.is_contiguous(), "embed_gather: bad table/x shapes")
+    _need(x_out.dtype == torch.float32, "embed_gather: the residual stream is float32")
+    _need(ids.dtype == torch.int32 and ids.numel() >= n and token_seq.numel() >= n, "embed_gather: ids int32 [T]")
+    f = _fn(_libs.get("elementwise.cu"), f"tkb_embed_gather_{_suffix(table.dtype)}")
+    _check(f(_ptr(table), _ptr(ids), _ptr(token_seq), _ptr(seq_slot), _ptr(last_token), _ptr(x_out), c_int(n),
+             c_int(H), c_int(V), _ptr(status), _stream()), "embed_gather")
+
+
+def add_rmsnorm(x: torch.Tensor, delta: torch.Tensor | None, weight: torch.Tensor, eps: float,
+                out: torch.Tensor) -> None:
+    """x += delta (float32, in place) if delta is given; out = rmsnorm(x) * weight in out's dtype."""
+    _need_cuda(x, delta, weight, out)
+    rows, H = x.shape
+    _need(x.dtype == torch.float32 and x.is_contiguous(), "add_rmsnorm: x must be contiguous float32")
+    _need(weight.dtype == torch.float32 and weight.numel() == H, "add_rmsnorm: weight must be float32 [H]")
+    _need(out.shape == x.shape and out.is_contiguous(), "add_rmsnorm: out shape")
+    if delta is not None:
+        _need(delta.shape == x.shape and delta.dtype == out.dtype and delta.is_contiguous(), "add_rmsnorm: delta")
+    f = _fn(_libs.get("elementwise.cu"), f"tkb_add_rmsnorm_{_suffix(out.dtype)}")
+    _check(f(_ptr(x), _ptr(delta), _ptr(weight), _ptr(out), c_float(eps), c_int(rows), c_int(H), _stream()),
+           "add_rmsnorm")
+
+
+def rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, token_seq: torch.Tensor, page_indptr: torch.Tensor,
+                  page_ids: torch.Tensor, inv_freq: torch.Tensor | None, kcache: torch.Tensor, vcache: torch.Tensor,
+                  n_heads: int, n_kv_heads: int, head_dim: int, rotary_dim: int, page_size: int,
+                  write_cache: bool, status: torch.Tensor) -> None:
+    """Rotate q (in place) and k by position, write rotated k and v into the request's pages.
+
+    kcache/vcache: [pages, n_kv_heads, page_size, head_dim]."""
+    _need_cuda(qkv, positions, token_seq, page_indptr, page_ids, inv_freq, kcache, vcache, status)
+    n = qkv.shape[0]
+    _need(qkv.is_contiguous() and qkv.shape[1] == (n_heads + 2 * n_kv_heads) * head_dim, "rope_kv_write: qkv shape")
+    _need(kcache.is_contiguous() and vcache.is_contiguous() and kcache.dtype == qkv.dtype, "rope_kv_write: cache")
+    _need(tuple(kcache.shape[1:]) == (n_kv_heads, page_size, head_dim), "rope_kv_write: cache layout")
+    _need(0 <= rotary_dim <= head_dim and rotary_dim % 2 == 0, "rope_kv_write: rotary_dim")
+    if rotary_dim:
+        _need(inv_freq is not None and inv_freq.dtype == torch.float32 and inv_freq.numel() == rotary_dim // 2,
+              "rope_kv_write: inv_freq must be float32 [rotary_dim/2]")
+    f = _fn(_libs.get("elementwise.cu"), f"tkb_rope_kv_write_{_suffix(qkv.dtype)}")
+    _check(f(_ptr(qkv), _ptr(positions), _ptr(token_seq), _ptr(page_indptr), _ptr(page_ids), _ptr(inv_freq),
+             _ptr(kcache), _ptr(vcache), c_int(n), c_int(n_heads), c_int(n_kv_heads), c_int(head_dim),
+             c_int(rotary_dim), c_int(page_size), c_int(kcache.shape[0]), c_int(1 if write_cache else 0),
+             _ptr(status), _stream()), "rope_kv_write")
+
+
+def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> None:
+    """out[t, i] = silu(gate_up[t, i]) * gate_up[t, I + i]."""
+    _need_cuda(gate_up, out)
+    rows, two_i = gate_up.shape
+    _need(two_i % 2 == 0 and out.shape == (rows, two_i // 2), "silu_mul: shapes")
+    _need(gate_up.is_contiguous() and out.is_contiguous() and out.dtype == gate_up.dtype, "silu_mul: layout")
+    f = _fn(_libs.get("elementwise.cu"), f"tkb_silu_mul_{_suffix(out.dtype)}")
+    _check(f(_ptr(gate_up), _ptr(out), c_int(rows), c_int(two_i // 2), _stream()), "silu_mul")
+
+
+def gather_rows(src: torch.Tensor, rows: torch.Tensor, out: torch.Tensor) -> None:
+    """out[r] = src[rows[r]]."""
+    _need_cuda(src, rows, out)
+    _need(src.is_contiguous() and out.is_contiguous() and src.dtype == out.dtype, "gather_rows: layout")
+    _need(rows.dtype == torch.int32 and out.shape[0] == rows.numel() and out.shape[1:] == src.shape[1:],
+          "gather_rows: shapes")
+    row_bytes = src[0].numel() * src.element_size() if src.shape[0] else 0
+    f = _fn(_libs.get("elementwise.cu"), "tkb_gather_rows")
+    _check(f(_ptr(src), _ptr(out), _ptr(rows), c_int(rows.numel()), c_int(row_bytes), _stream()), "gather_rows")
+
+
+def sgemm_tn(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
+    """out[M, N] = a[M, K] @ w[N, K]^T in true float32 (FP32 FMA, fixed summation order)."""
+    _need_cuda(a, w, out)
+    M, K = a.shape
+    N = w.shape[0]
+    _need(w.shape[1] == K and out.shape == (M, N), "sgemm_tn: shapes")
+    _need(a.dtype == w.dtype == out.dtype == torch.float32, "sgemm_tn: float32 only")
+    _need(a.stride(1) == 1 and w.stride(1) == 1 and out.stride(1) == 1, "sgemm_tn: rows must be contiguous")
+    f = _fn(_libs.get("sgemm.cu"), "tkb_sgemm_tn_f32")
+    _check(f(_ptr(a), _ptr(w), _ptr(out), c_int(M), c_int(N), c_int(K), c_int(a.stride(0) if M > 1 else K),
+             c_int(w.stride(0) if N > 1 else K), c_int(out.stride(0) if M > 1 else N), _stream()), "sgemm_tn")
+
+
+def attn_paged(q: torch.Tensor, q_stride: int, out: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor,
+               token_seq: torch.Tensor, positions: torch.Tensor, page_indptr: torch.Tensor, page_ids: torch.Tensor,
+               rows: torch.Tensor | None, n_rows: int, n_heads: int, n_kv_heads: int, head_dim: int,
+               page_size: int, scale: float, window: int | None) -> None:
+    """Causal GQA attention over the paged cache on the FP32 pipes (any mix of portions and single tokens).
+
+    q: first n_heads*head_dim columns of each row of a [T, q_stride] buffer; out: [n_rows, n_heads*head_dim]."""
+    _need_cuda(q, out, kcache, vcache, token_seq, positions, page_indptr, page_ids, rows)
+    check_head_dim(head_dim)
+    _need(out.is_contiguous() and out.shape[1] == n_heads * head_dim and out.shape[0] >= n_rows, "attn_paged: out")
+    _need(kcache.dtype == q.dtype == out.dtype, "attn_paged: dtypes")
+    _need(tuple(kcache.shape[1:]) == (n_kv_heads, page_size, head_dim), "attn_paged: cache layout")
+    f = _fn(_libs.get("attention_simt.cu", TKB_HD=head_dim), f"tkb_attn_paged_simt_{_suffix(q.dtype)}")
+    _check(f(_ptr(q), c_int(q_stride), _ptr(out), c_int(out.shape[1]), _ptr(kcache), _ptr(vcache), _ptr(token_seq),
+             _ptr(positions), _ptr(page_indptr), _ptr(page_ids), _ptr(rows), c_int(n_rows), c_int(n_heads),
+             c_int(n_kv_heads), c_int(page_size), c_float(scale), c_int(window or 0), _stream()), "attn_paged")
+
+
+def sample(logits: torch.Tensor, temperature: torch.Tensor | None, stream_key: torch.Tensor | None,
+           sample_pos: torch.Tensor | None, row_slot: torch.Tensor | None, out_ids: torch.Tensor,
+           out_logprob: torch.Tensor | None, last_token: torch.Tensor | None) -> None:
+    """Greedy (temperature <= 0) or Gumbel-max temperature sampling of one id per row of logits [R, V]."""
+    _need_cuda(logits, temperature, stream_key, sample_pos, row_slot, out_ids, out_logprob, last_token)
+    R, V = logits.shape
+    _need(logits.dtype == torch.float32 and logits.is_contiguous(), "sample: logits must be contiguous float32")
+    _need(out_ids.dtype == torch.int32 and out_ids.numel() >= R, "sample: out_ids int32 [R]")
+    if stream_key is not None:
+        _need(stream_key.dtype == torch.int64, "sample: stream_key int64 [R]")
+    f = _fn(_libs.get("sampling.cu"), "tkb_sample")
+    _check(f(_ptr(logits), _ptr(temperature), _ptr(stream_key), _ptr(sample_pos), _ptr(row_slot), _ptr(out_ids),
+             _ptr(out_logprob), _ptr(last_token), c_int(R), c_int(V), _stream()), "sample")
+
+
+def topk_logprobs(logits: torch.Tensor, temperature: torch.Tensor | None, k: int, out_idx: torch.Tensor,
+                  out_lp: torch.Tensor) -> None:
+    _need_cuda(logits, temperature, out_idx, out_lp)
+    R, V = logits.shape
+    _need(logits.dtype == torch.float32 and logits.is_contiguous(), "topk_logprobs: logits")
+    _need(out_idx.shape == (R, k) and out_lp.shape == (R, k) and out_idx.dtype == torch.int32, "topk_logprobs: outs")
+    f = _fn(_libs.get("sampling.cu"), "tkb_topk_logprobs")
+    _check(f(_ptr(logits), _ptr(temperature), _ptr(out_idx), _ptr(out_lp), c_int(R), c_int(V), c_int(k), _stream()),
+           "topk_logprobs")
+
+
+def linear(a: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None = None) -> torch.Tensor:
+    """a[M, K] @ w[N, K]^T.  float32: this engine's FP32 kernel (no tf32).  bfloat16: the library
+    matrix product (cuBLAS through torch), float32 accumulation, output bfloat16 or float32."""
+    _need_cuda(a, w)
+    M = a.shape[0]
+    N = w.shape[0]
+    if a.dtype == torch.float32:
+        out = torch.empty((M, N), dtype=torch.float32, device=a.device)
+        sgemm_tn(a, w, out)
+        return out
+    _need(a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16, "linear: operands must share the engine dtype")
+    if out_dtype is None or out_dtype == torch.bfloat16:
+        return torch.mm(a, w.t())
+    return torch.mm(a, w.t(), out_dtype=out_dtype)
+
+
+def softmax_scale(head_dim: int) -> float:
+    return 1.0 / math.sqrt(head_dim)

@@ -1,0 +1,38 @@
+"""SiLU-gated feed-forward: ``down(silu(gate(h)) * up(h))`` without biases
+(tokasaurus/model/llama.py:319-339; :329-332 are the three products and the activation).  The
+gate and up matrices are stacked so that one matrix product makes gate|up."""
+
+from __future__ import annotations
+
+import torch
+
+from tokasaurus_b200.kernels import ops
+from tokasaurus_b200.parts.base import FeedForward, WeightSpec
+
+
+class GatedMLP(FeedForward):
+    def __init__(self, width: int, inner: int, gate_name: str, up_name: str, down_name: str):
+        self.width = width
+        self.inner = inner
+        self.names = (gate_name, up_name, down_name)
+        self.w_gate_up: torch.Tensor | None = None
+        self.w_down: torch.Tensor | None = None
+
+    def weight_specs(self):
+        g, u, d = self.names
+        return (
+            WeightSpec(g, (self.inner, self.width)),
+            WeightSpec(u, (self.inner, self.width)),
+            WeightSpec(d, (self.width, self.inner)),
+        )
+
+    def bind(self, weights, rt) -> None:
+        g, u, d = self.names
+        self.w_gate_up = torch.cat([weights[g], weights[u]], dim=0).contiguous()
+        self.w_down = weights[d].contiguous()
+
+    def forward(self, ctx, h: torch.Tensor) -> torch.Tensor:
+        gu = ops.linear(h, self.w_gate_up)
+        act = torch.empty((h.shape[0], self.inner), dtype=h.dtype, device=h.device)
+        ops.silu_mul(gu, act)
+        return ops.linear(act, self.w_down)
