@@ -1,0 +1,90 @@
+"""Scheduler, sampler glue and Python entry point on the CPU (plain kernel statements in the
+kernels' place): greedy generation equals the plain implementation under chunked prefill and
+when requests are pushed out for lack of pages."""
+
+import pytest
+import torch
+
+import cuttings
+import kernel_refs
+from plain_llama import PlainLlama, TINY_WEIGHTS, tiny_configs
+
+
+@pytest.fixture()
+def cpu_kernels(monkeypatch):
+    kernel_refs.install_cpu_kernels(monkeypatch)
+
+
+def make_engine(model_dir, **kw):
+    from tokasaurus_b200.engine.engine import Engine
+
+    opts = dict(dtype="float32", device="cpu", use_cudagraphs=False, page_size=16, kv_cache_num_tokens=1024,
+                allocator_sanity_checks=True)
+    opts.update(kw)
+    return Engine(model=str(model_dir), **opts)
+
+
+def test_greedy_generation_matches_plain(cpu_kernels, tiny_model_dirs):
+    d = tiny_model_dirs[0]
+    prompts = [cuttings.random_tokens(n, 256, 40 + n) for n in (5, 17, 32)]
+    eng = make_engine(d)
+    outs = eng.generate(prompts, max_num_tokens=8, ignore_eos=True)
+    plain = PlainLlama(d, torch.float64)
+    for p, o in zip(prompts, outs):
+        assert o.completion_ids == plain.greedy(p, 8)
+        assert o.finish_reason == "length" and len(o.logprobs) == 8
+    eng.runner.cache.check()
+    assert not eng.runner.cache.requests
+
+
+def test_chunked_prefill_mixed_with_decode(cpu_kernels, tiny_model_dirs):
+    d = tiny_model_dirs[1]
+    prompts = [cuttings.random_tokens(n, 509, 3 * n) for n in (1, 40, 63, 30)]
+    plain = PlainLlama(d, torch.float64)
+    want = [plain.greedy(p, 6) for p in prompts]
+    eng = make_engine(d, page_size=8, max_tokens_per_forward=24, kv_cache_num_tokens=512)
+    outs = eng.generate(prompts, max_num_tokens=6, ignore_eos=True)
+    assert [o.completion_ids for o in outs] == want
+    assert eng.scheduler.stats["steps"] > 6  # prompts were cut
+
+
+def test_pushed_out_requests_give_the_same_tokens(cpu_kernels, tiny_model_dirs):
+    d = tiny_model_dirs[0]
+    prompts = [cuttings.random_tokens(n, 256, 11 * n) for n in (30, 28, 31, 20)]
+    plain = PlainLlama(d, torch.float64)
+    want = [plain.greedy(p, 20) for p in prompts]
+    # 8 pages of 16: four prompts take 2 pages each, and each wants a third and fourth page while decoding
+    eng = make_engine(d, kv_cache_num_tokens=128, bump_city_population_me=True)
+    outs = eng.generate(prompts, max_num_tokens=20, ignore_eos=True)
+    assert eng.scheduler.stats["bumps"] > 0
+    assert [o.completion_ids for o in outs] == want
+    assert sum(o.num_preemptions for o in outs) == eng.scheduler.stats["bumps"]
+    assert not eng.runner.cache.requests
+
+
+def test_temperature_sampling_is_keyed_by_request_not_by_batch(cpu_kernels, tiny_model_dirs):
+    from tokasaurus_b200 import SamplingParams
+
+    d = tiny_model_dirs[1]
+    prompts = [cuttings.random_tokens(n, 509, n) for n in (9, 21, 14)]
+    sp = SamplingParams(temperature=0.7, seed=7)
+    together = make_engine(d, page_size=8).generate(prompts, sp, max_num_tokens=10, ignore_eos=True)
+    again = make_engine(d, page_size=8).generate(prompts, sp, max_num_tokens=10, ignore_eos=True)
+    assert [o.completion_ids for o in together] == [o.completion_ids for o in again]
+    # chunked differently: the draws are the same because the key is (seed, request, position)
+    chunked = make_engine(d, page_size=8, max_tokens_per_forward=8).generate(prompts, sp, max_num_tokens=10,
+                                                                              ignore_eos=True)
+    assert [o.completion_ids for o in together] == [o.completion_ids for o in chunked]
+    other = make_engine(d, page_size=8).generate(prompts, SamplingParams(temperature=0.7, seed=8), max_num_tokens=10,
+                                                 ignore_eos=True)
+    assert [o.completion_ids for o in together] != [o.completion_ids for o in other]
+
+
+def test_stop_tokens_and_eos(cpu_kernels, tiny_model_dirs):
+    d = tiny_model_dirs[0]
+    p = cuttings.random_tokens(12, 256, 5)
+    full = PlainLlama(d, torch.float64).greedy(p, 8)
+    eng = make_engine(d)
+    out = eng.generate([p], max_num_tokens=8, stop_token_ids=[full[3]])[0]
+    first = full.index(full[3])
+    assert out.completion_ids == full[:first + 1] and out.finish_reason == "stop"

@@ -1,0 +1,163 @@
+"""The engine on the GPU through its Python entry point and command line: greedy generation,
+chunked prefill beside decoding, requests pushed out for lack of pages, temperature sampling,
+long decoding and the first tokens of a sequence."""
+
+import json
+import subprocess
+import sys
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+import cuttings
+from plain_llama import PlainLlama, TINY_WEIGHTS, tiny_configs
+
+pytestmark = pytest.mark.gpu
+ROOT = Path(__file__).resolve().parent.parent
+
+
+def make_engine(model_dir, **kw):
+    from tokasaurus_b200.engine.engine import Engine
+
+    opts = dict(dtype="float32", kv_cache_num_tokens=2048, allocator_sanity_checks=True)
+    opts.update(kw)
+    return Engine(model=str(model_dir), **opts)
+
+
+def near_best(plain, prompt, completion, frac=0.03):
+    logits = plain.logits(prompt + completion[:-1])[len(prompt) - 1:]
+    top = logits.abs().max().item()
+    return all(logits[i, t] >= logits[i].max() - frac * top for i, t in enumerate(completion))
+
+
+@pytest.mark.parametrize("cfg_index", [0, 1])
+def test_greedy_generation_float32_equals_plain(tiny_model_dirs, cfg_index):
+    d = tiny_model_dirs[cfg_index]
+    vocab = tiny_configs()[cfg_index]["vocab_size"]
+    lengths = (5, 17, 32) if cfg_index == 0 else (1, 40, 63, 100)
+    prompts = [cuttings.random_tokens(n, vocab, 40 + n) for n in lengths]
+    plain = PlainLlama(d, torch.float64)
+    want = [plain.greedy(p, 16) for p in prompts]
+    eng = make_engine(d, page_size=TINY_WEIGHTS[cfg_index]["page_size"])
+    outs = eng.generate(prompts, max_num_tokens=16, ignore_eos=True)
+    assert [o.completion_ids for o in outs] == want
+    # chunked prefill (24 tokens a step) mixed with decoding gives the same tokens
+    eng2 = make_engine(d, page_size=TINY_WEIGHTS[cfg_index]["page_size"], max_tokens_per_forward=24)
+    outs2 = eng2.generate(prompts, max_num_tokens=16, ignore_eos=True)
+    assert [o.completion_ids for o in outs2] == want
+    for o, o2 in zip(outs, outs2):
+        np.testing.assert_allclose(o.logprobs, o2.logprobs, atol=1e-4)
+    assert not eng2.runner.cache.requests
+
+
+@pytest.mark.parametrize("cfg_index", [0, 1])
+def test_greedy_generation_bfloat16(tiny_model_dirs, cfg_index):
+    d = tiny_model_dirs[cfg_index]
+    vocab = tiny_configs()[cfg_index]["vocab_size"]
+    prompts = [cuttings.random_tokens(n, vocab, 90 + n) for n in (3, 29, 64)]
+    plain = PlainLlama(d, torch.float64)
+    eng = make_engine(d, dtype="bfloat16", page_size=TINY_WEIGHTS[cfg_index]["page_size"], max_tokens_per_forward=40)
+    outs = eng.generate(prompts, max_num_tokens=20, ignore_eos=True)
+    for p, o in zip(prompts, outs):
+        assert len(o.completion_ids) == 20 and near_best(plain, p, o.completion_ids)
+
+
+def test_pushed_out_requests_give_the_same_tokens(tiny_model_dirs):
+    d = tiny_model_dirs[0]
+    prompts = [cuttings.random_tokens(n, 256, 11 * n) for n in (30, 28, 31, 20)]
+    plain = PlainLlama(d, torch.float64)
+    want = [plain.greedy(p, 20) for p in prompts]
+    eng = make_engine(d, kv_cache_num_tokens=128, bump_city_population_me=True)
+    outs = eng.generate(prompts, max_num_tokens=20, ignore_eos=True)
+    assert eng.scheduler.stats["bumps"] > 0
+    assert [o.completion_ids for o in outs] == want
+
+
+def test_temperature_sampling_seeded(tiny_model_dirs):
+    from tokasaurus_b200 import SamplingParams
+
+    d = tiny_model_dirs[1]
+    prompts = [cuttings.random_tokens(n, 509, n) for n in (1, 40, 63, 100)]
+    sp = SamplingParams(temperature=0.7, seed=7)
+    a = make_engine(d, page_size=8, max_tokens_per_forward=24).generate(prompts, sp, max_num_tokens=20, ignore_eos=True)
+    b = make_engine(d, page_size=8).generate(prompts, sp, max_num_tokens=20, ignore_eos=True)
+    assert [o.completion_ids for o in a] == [o.completion_ids for o in b]
+    c = make_engine(d, page_size=8).generate(prompts, SamplingParams(temperature=0.7, seed=8), max_num_tokens=20,
+                                             ignore_eos=True)
+    assert [o.completion_ids for o in a] != [o.completion_ids for o in c]
+    # the sampled tokens have the log-probabilities the plain implementation gives them at T = 0.7
+    plain = PlainLlama(d, torch.float64)
+    o = a[1]
+    logits = plain.logits(prompts[1] + o.completion_ids[:-1])[len(prompts[1]) - 1:]
+    lp = torch.log_softmax(logits / 0.7, -1)
+    want = [lp[i, t].item() for i, t in enumerate(o.completion_ids)]
+    np.testing.assert_allclose(o.logprobs, want, atol=2e-4)
+    assert len(set(o.completion_ids)) > 3
+
+
+def test_topk_logprobs_through_the_entry_point(tiny_model_dirs):
+    d = tiny_model_dirs[0]
+    p = cuttings.random_tokens(9, 256, 1)
+    eng = make_engine(d, max_topk_logprobs=4)
+    o = eng.generate([p], max_num_tokens=5, ignore_eos=True, topk_logprobs=3)[0]
+    assert len(o.topk_ids) == 5 and all(len(t) == 3 for t in o.topk_ids)
+    for t, ids, lps, lp in zip(o.completion_ids, o.topk_ids, o.topk_logprobs, o.logprobs):
+        assert ids[0] == t and abs(lps[0] - lp) < 1e-5 and lps == sorted(lps, reverse=True)
+    with pytest.raises(ValueError):
+        eng.add_request(p, topk_logprobs=9)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decoding(tiny_model_dirs, dtype):
+    """A short prompt and then 248 single-token steps up to the model's last position."""
+    from test_replay_gpu import compare, replay
+
+    d = tiny_model_dirs[1]
+    reqs = {"long": cuttings.random_tokens(256, 509, 77)}
+    steps = cuttings.prefix_then_single(reqs, tail=248)
+    got = replay(d, dtype, steps, 8)
+    compare(got, cuttings.plain_logits(d, reqs), cuttings.plain_logits(d, reqs, torch.float32), dtype)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_first_tokens_of_a_sequence(tiny_model_dirs, dtype):
+    """Positions 0, 1, 2: one token alone; two tokens; a token, then a token, then a token."""
+    from test_replay_gpu import compare, replay
+
+    for i, d in enumerate(tiny_model_dirs):
+        vocab = tiny_configs()[i]["vocab_size"]
+        reqs = {"a": cuttings.random_tokens(1, vocab, 1), "b": cuttings.random_tokens(2, vocab, 2),
+                "c": cuttings.random_tokens(3, vocab, 3)}
+        p64, p32 = cuttings.plain_logits(d, reqs), cuttings.plain_logits(d, reqs, torch.float32)
+        for cut in (cuttings.whole, lambda r: cuttings.prefix_then_single(r, tail=2)):
+            compare(replay(d, dtype, cut(reqs), TINY_WEIGHTS[i]["page_size"]), p64, p32, dtype)
+
+
+def test_command_line(tiny_model_dirs, tmp_path):
+    d = tiny_model_dirs[0]
+    p = cuttings.random_tokens(12, 256, 5)
+    want = PlainLlama(d, torch.float64).greedy(p, 6)
+    proc = subprocess.run([sys.executable, str(ROOT / "bin" / "toka"), f"model={d}", "dtype=float32",
+                           "kv_cache_num_tokens=(16*64)", f"prompt_ids={json.dumps(p)}", "max_num_tokens=6",
+                           "ignore_eos=T"], capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    rec = json.loads(proc.stdout.strip().split("\n")[-1])
+    assert rec["completion_ids"] == want and rec["finish_reason"] == "length"
+    bad = subprocess.run([sys.executable, str(ROOT / "bin" / "toka"), f"model={d}", "nonsense=1"], capture_output=True,
+                         text=True, timeout=120)
+    assert bad.returncode == 2 and "unknown option" in bad.stderr
+
+
+def test_bad_token_id_is_refused_on_the_host(tiny_model_dirs):
+    eng = make_engine(tiny_model_dirs[0])
+    with pytest.raises(ValueError, match="vocabulary"):
+        eng.add_request([1, 2, 256])
+
+
+def test_no_cuda_no_engine(tiny_model_dirs):
+    from tokasaurus_b200.engine.engine import Engine
+
+    with pytest.raises(RuntimeError, match="no CPU execution path"):
+        Engine(model=str(tiny_model_dirs[0]), device="cpu")

@@ -1,0 +1,344 @@
+"""Each kernel alone against its plain statement (tests/kernel_refs.py), in float32 and bfloat16, at
+sizes other than the test models': widths and vocabularies that are no power of two, every head
+size class, odd numbers of heads and groups, page edges, windows, and inputs made so that a single
+wrong key, page or row shows."""
+
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import kernel_refs as ref
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from tokasaurus_b200.kernels import ops as o
+    return o
+
+
+def tol(dtype):
+    return dict(rtol=2e-5, atol=2e-5) if dtype == torch.float32 else dict(rtol=1.6e-2, atol=1e-2)
+
+
+def i32(x):
+    return torch.tensor(x, dtype=torch.int32, device=DEV)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("H,V", [(80, 509), (2048, 1000), (8, 3)])
+def test_embed_gather(ops, dtype, H, V):
+    g = torch.Generator(device="cpu").manual_seed(1)
+    table = torch.randn(V, H, generator=g).to(dtype).to(DEV)
+    ids = i32([0, V - 1, -1, 1 % V, -1, 2 % V])
+    token_seq = i32([0, 0, 1, 2, 2, -1])  # the last row is padding
+    seq_slot = i32([3, 1, 0])
+    last = i32([2 % V, V - 1, 7, 1 % V])
+    x = torch.full((6, H), 5.0, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    ops.embed_gather(table, ids, token_seq, seq_slot, last, x, status)
+    want = torch.stack([table[0], table[V - 1], table[int(last[1])], table[1 % V], table[int(last[0])],
+                        torch.zeros(H, device=DEV, dtype=dtype)]).float()
+    assert torch.equal(x, want) and int(status) == 0
+    ops.embed_gather(table, i32([V, 0, 0, 0, 0, 0]), token_seq, seq_slot, last, x, status)
+    assert int(status) & 1 and torch.equal(x[0], torch.zeros(H, device=DEV))  # refused, not read out of range
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("rows,H,eps", [(5, 96, 1e-6), (3, 2048, 1e-5), (7, 4000, 1e-2), (1, 17, 1e-5)])
+def test_add_rmsnorm(ops, dtype, rows, H, eps):
+    g = torch.Generator().manual_seed(rows * H)
+    x = (torch.randn(rows, H, generator=g) * 3).to(DEV)
+    delta = torch.randn(rows, H, generator=g).to(dtype).to(DEV)
+    w = (torch.rand(H, generator=g) + 0.5).to(DEV)
+    for d in (delta, None):
+        x1, x2 = x.clone(), x.clone()
+        out = torch.empty(rows, H, dtype=dtype, device=DEV)
+        want = torch.empty(rows, H, dtype=dtype, device=DEV)
+        ops.add_rmsnorm(x1, d, w, eps, out)
+        ref.add_rmsnorm(x2, d, w, eps, want)
+        assert torch.equal(x1, x2)  # the residual sum is a float32 add
+        torch.testing.assert_close(out.float(), want.float(), **tol(dtype))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("rows,I", [(4, 160), (3, 8192), (9, 37)])
+def test_silu_mul(ops, dtype, rows, I):
+    gu = (torch.randn(rows, 2 * I, generator=torch.Generator().manual_seed(I)) * 4).to(dtype).to(DEV)
+    out = torch.empty(rows, I, dtype=dtype, device=DEV)
+    want = torch.empty_like(out)
+    ops.silu_mul(gu, out)
+    ref.silu_mul(gu, want)
+    torch.testing.assert_close(out.float(), want.float(), **tol(dtype))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_gather_rows(ops, dtype):
+    for width in (96, 2048, 3):
+        src = torch.randn(11, width).to(dtype).to(DEV)
+        rows = i32([10, 0, 3, 3])
+        out = torch.empty(4, width, dtype=dtype, device=DEV)
+        ops.gather_rows(src, rows, out)
+        assert torch.equal(out, src[rows.long()])
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 509, 96), (5, 64, 64), (64, 64, 16), (65, 129, 33), (130, 70, 257),
+                                   (3, 2048, 8192), (200, 3, 7)])
+def test_sgemm_true_fp32(ops, M, N, K):
+    g = torch.Generator().manual_seed(M * N + K)
+    a = torch.randn(M, K, generator=g).to(DEV)
+    w = torch.randn(N, K, generator=g).to(DEV)
+    out = torch.empty(M, N, device=DEV)
+    ops.sgemm_tn(a, w, out)
+    want = (a.double() @ w.double().T)
+    err = (out.double() - want).abs().max().item()
+    bound = 4 * K * 2 ** -24 * (a.abs().double() @ w.abs().double().T).max().item()
+    assert err <= bound, (err, bound)
+    # far inside what a 10-bit (tf32) or 8-bit (bfloat16) mantissa could give
+    assert err < 2e-5 * math.sqrt(K) * 3
+    # a row's result does not depend on the other rows of the batch
+    if M > 1:
+        one = torch.empty(1, N, device=DEV)
+        ops.sgemm_tn(a[M - 1:M].contiguous(), w, one)
+        assert torch.equal(one[0], out[M - 1])
+
+
+def make_paged(dtype, n_seqs, lens, nkv, hd, ps, n_pages, seed, fill=1e3):
+    """Random keys/values scattered over shuffled pages; unused slots hold large garbage."""
+    g = torch.Generator().manual_seed(seed)
+    kc = torch.full((n_pages, nkv, ps, hd), fill, dtype=dtype)
+    vc = torch.full((n_pages, nkv, ps, hd), -fill, dtype=dtype)
+    perm = torch.randperm(n_pages, generator=g).tolist()
+    indptr, pages, K, V = [0], [], [], []
+    for L in lens:
+        npg = -(-L // ps)
+        mine = [perm.pop() for _ in range(npg)]
+        k = torch.randn(L, nkv, hd, generator=g).to(dtype)
+        v = torch.randn(L, nkv, hd, generator=g).to(dtype)
+        for j in range(L):
+            kc[mine[j // ps], :, j % ps] = k[j]
+            vc[mine[j // ps], :, j % ps] = v[j]
+        pages += mine
+        indptr.append(len(pages))
+        K.append(k)
+        V.append(v)
+    return kc.to(DEV), vc.to(DEV), i32(indptr), i32(pages), K, V
+
+
+def plain_attention(q, K, V, pos, scale, window):
+    """float64 softmax attention of one query [nh, hd] at position pos over K, V [L, nkv, hd]."""
+    nh, hd = q.shape
+    nkv = K.shape[1]
+    lo = max(0, pos - window + 1) if window else 0
+    k = K[lo:pos + 1].double().repeat_interleave(nh // nkv, dim=1)
+    v = V[lo:pos + 1].double().repeat_interleave(nh // nkv, dim=1)
+    s = torch.einsum("hd,khd->hk", q.double(), k) * scale
+    return torch.einsum("hk,khd->hd", torch.softmax(s, -1), v)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("hd,nh,nkv,ps,window", [(16, 4, 2, 16, None), (32, 3, 1, 8, None), (48, 6, 3, 4, 7),
+                                                  (64, 8, 2, 16, None), (80, 5, 5, 16, 33), (128, 8, 1, 32, None),
+                                                  (256, 2, 1, 16, None), (112, 7, 1, 5, None)])
+def test_attention_mixed_batch(ops, dtype, hd, nh, nkv, ps, window):
+    """Three requests in one batch: a whole prompt, a portion in the middle of a request that ends
+    just past a page edge, and a single decoded token far into its request."""
+    lens = [37, 2 * ps + 1, 150]
+    kc, vc, indptr, pages, K, V = make_paged(dtype, 3, lens, nkv, hd, ps, 64, seed=hd + nh)
+    q_pos = [list(range(37)), list(range(ps - 1, 2 * ps + 1)), [149]]
+    token_seq = i32([s for s, p in enumerate(q_pos) for _ in p])
+    positions = i32([x for p in q_pos for x in p])
+    T = token_seq.numel()
+    g = torch.Generator().manual_seed(7)
+    q = torch.randn(T, (nh + 2 * nkv) * hd, generator=g).to(dtype).to(DEV)
+    scale = 1 / math.sqrt(hd)
+    out = torch.zeros(T, nh * hd, dtype=dtype, device=DEV)
+    ops.attn_paged(q, q.shape[1], out, kc, vc, token_seq, positions, indptr, pages, None, T, nh, nkv, hd, ps, scale,
+                   window)
+    t = 0
+    for s, ps_ in enumerate(q_pos):
+        for p in ps_:
+            want = plain_attention(q[t, : nh * hd].view(nh, hd).cpu(), K[s], V[s], p, scale, window)
+            torch.testing.assert_close(out[t].view(nh, hd).cpu().double(), want, **tol(dtype), check_dtype=False)
+            t += 1
+    # wanted rows only
+    rows = i32([T - 1, 0, 40])
+    some = torch.zeros(3, nh * hd, dtype=dtype, device=DEV)
+    ops.attn_paged(q, q.shape[1], some, kc, vc, token_seq, positions, indptr, pages, rows, 3, nh, nkv, hd, ps, scale,
+                   window)
+    assert torch.equal(some, out[rows.long()])
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_attention_finds_one_far_key(ops, dtype):
+    """One key among 700 is made to stand out for one query head: the output must be that key's
+    value, wherever it lies (first slot of a page, last slot, the first key, the query's own)."""
+    hd, nh, nkv, ps, L = 64, 4, 2, 16, 700
+    for target in (0, 15, 16, 333, 687, 699):
+        kc, vc, indptr, pages, K, V = make_paged(dtype, 1, [L], nkv, hd, ps, 50, seed=target)
+        q = torch.zeros(1, (nh + 2 * nkv) * hd, dtype=dtype)
+        direction = K[0][target, 1].float()
+        q[0, 3 * hd:4 * hd] = (direction / direction.norm() * 60).to(dtype)  # head 3 reads kv head 1
+        scale = 1.0
+        out = torch.zeros(1, nh * hd, dtype=dtype, device=DEV)
+        ops.attn_paged(q.to(DEV), q.shape[1], out, kc, vc, i32([0]), i32([L - 1]), indptr, pages, None, 1, nh, nkv, hd,
+                       ps, scale, None)
+        want = plain_attention(q[0, : nh * hd].view(nh, hd), K[0], V[0], L - 1, scale, None)
+        assert (want[3] - V[0][target, 1].double()).abs().max() < 0.05  # the construction works
+        torch.testing.assert_close(out[0].view(nh, hd).cpu().double(), want, **tol(dtype), check_dtype=False)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_attention_window_edge(ops, dtype):
+    """The key just outside the window is made huge: it must not be seen; the one just inside must."""
+    hd, nh, nkv, ps, L, W = 32, 2, 1, 8, 100, 24
+    kc, vc, indptr, pages, K, V = make_paged(dtype, 1, [L], nkv, hd, ps, 20, seed=5)
+    p = L - 1
+    q = torch.randn(1, (nh + 2) * hd, generator=torch.Generator().manual_seed(2)).to(dtype)
+    scale = 1 / math.sqrt(hd)
+    for edge, seen in ((p - W, False), (p - W + 1, True)):
+        k2 = [K[0].clone()]
+        k2[0][edge, 0] = (q[0, :hd].float() * 30).to(dtype)
+        kc2 = kc.clone()
+        page = int(pages[edge // ps])
+        kc2[page, 0, edge % ps] = k2[0][edge, 0].to(DEV)
+        out = torch.zeros(1, nh * hd, dtype=dtype, device=DEV)
+        ops.attn_paged(q.to(DEV), q.shape[1], out, kc2, vc, i32([0]), i32([p]), indptr, pages, None, 1, nh, nkv, hd, ps,
+                       scale, W)
+        want = plain_attention(q[0, : nh * hd].view(nh, hd), k2[0], V[0], p, scale, W)
+        torch.testing.assert_close(out[0].view(nh, hd).cpu().double(), want, **tol(dtype), check_dtype=False)
+        hit = (out[0, :hd].cpu().double() - V[0][edge, 0].double()).abs().max() < 0.05
+        assert bool(hit) == seen
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("hd,rot,nh,nkv,ps", [(16, 16, 4, 2, 16), (32, 32, 3, 1, 8), (64, 64, 8, 2, 16), (128, 64, 2, 2, 4),
+                                              (48, 0, 2, 1, 16)])
+def test_rope_kv_write(ops, dtype, hd, rot, nh, nkv, ps):
+    from tokasaurus_b200.parts.rope import RotaryEncoding
+
+    T = 9
+    g = torch.Generator().manual_seed(hd)
+    qkv = torch.randn(T, (nh + 2 * nkv) * hd, generator=g).to(dtype).to(DEV)
+    positions = i32([0, 1, ps - 1, ps, 5000, 131071, 3, 7, 2])
+    token_seq = i32([0, 0, 0, 0, 1, 2, -1, 3, 3])
+    n_pages = 131072 // ps + 8
+    tables = {0: [5, 6], 1: list(range(10, 10 + 5000 // ps + 1)), 2: [0] * (131071 // ps) + [7], 3: [9]}
+    indptr, pages = [0], []
+    for s in range(4):
+        pages += tables[s]
+        indptr.append(len(pages))
+    inv = RotaryEncoding(rot, 500000.0, "llama3", 32.0, 1.0, 4.0, 8192).inv_freq().to(DEV) if rot else None
+    kc = torch.zeros(n_pages, nkv, ps, hd, dtype=dtype, device=DEV)
+    vc = torch.zeros_like(kc)
+    kc2, vc2 = kc.clone(), vc.clone()
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    a, b = qkv.clone(), qkv.clone()
+    ops.rope_kv_write(a, positions, token_seq, i32(indptr), i32(pages), inv, kc, vc, nh, nkv, hd, rot, ps, True, status)
+    ref.rope_kv_write(b, positions, token_seq, i32(indptr), i32(pages), inv, kc2, vc2, nh, nkv, hd, rot, ps, True,
+                      torch.zeros(1, dtype=torch.int32))
+    assert int(status) == 0
+    t = dict(rtol=1e-5, atol=2e-5) if dtype == torch.float32 else dict(rtol=1e-2, atol=1e-2)
+    torch.testing.assert_close(a.float(), b.float(), **t)
+    torch.testing.assert_close(kc.float(), kc2.float(), **t)
+    assert torch.equal(vc, vc2)
+    assert torch.equal(a[6], qkv[6])  # padding row untouched
+    # write_cache=False rotates q and leaves the cache alone
+    kc3 = torch.zeros_like(kc)
+    c = qkv.clone()
+    ops.rope_kv_write(c, positions, token_seq, i32(indptr), i32(pages), inv, kc3, vc.clone(), nh, nkv, hd, rot, ps, False,
+                      status)
+    assert torch.equal(c[:, : nh * hd], a[:, : nh * hd]) and not kc3.any()
+    # a page id outside the pool is refused
+    ops.rope_kv_write(qkv.clone(), positions, token_seq, i32(indptr), i32([n_pages + 3] * len(pages)), inv, kc3, vc.clone(),
+                      nh, nkv, hd, rot, ps, True, status)
+    assert int(status) & 2 and not kc3.any()
+
+
+def test_sampling_greedy_and_logprob(ops):
+    for V in (509, 128256, 3):
+        g = torch.Generator().manual_seed(V)
+        logits = (torch.randn(5, V, generator=g) * 3).to(DEV)
+        logits[1, V - 1] = 50.0
+        logits[2, 0] = logits[2].max() + 1
+        logits[3] = 0.25  # all equal: the first index wins
+        ids = torch.full((5,), -1, dtype=torch.int32, device=DEV)
+        lp = torch.zeros(5, device=DEV)
+        last = torch.full((8,), -1, dtype=torch.int32, device=DEV)
+        ops.sample(logits, torch.zeros(5, device=DEV), None, None, i32([4, -1, 0, 1, 2]), ids, lp, last)
+        assert ids.tolist() == logits.argmax(-1).tolist() or V == 3
+        assert int(ids[1]) == V - 1 and int(ids[2]) == 0 and int(ids[3]) == 0
+        want_lp = torch.log_softmax(logits.double(), -1).gather(1, ids.long().view(-1, 1)).view(-1)
+        torch.testing.assert_close(lp.double(), want_lp, rtol=1e-5, atol=1e-5)
+        assert last.tolist() == [int(ids[2]), int(ids[3]), int(ids[4]), -1, int(ids[0]), -1, -1, -1]
+
+
+def test_sampling_matches_plain_gumbel_draw(ops):
+    V = 1003
+    g = torch.Generator().manual_seed(3)
+    logits = (torch.randn(6, V, generator=g) * 2).to(DEV)
+    temp = torch.tensor([0.7, 1.0, 0.0, 1.5, 0.7, 0.7], device=DEV)
+    keys = torch.tensor([11, -5, 3, 2**62, 11, 12], dtype=torch.int64, device=DEV)
+    pos = i32([4, 4, 4, 100000, 5, 4])
+    ids = torch.zeros(6, dtype=torch.int32, device=DEV)
+    lp = torch.zeros(6, device=DEV)
+    ops.sample(logits, temp, keys, pos, None, ids, lp, None)
+    want_ids = torch.zeros(6, dtype=torch.int32)
+    want_lp = torch.zeros(6)
+    ref.sample(logits.cpu(), temp.cpu(), keys.cpu(), pos.cpu(), None, want_ids, want_lp, None)
+    for r in range(6):
+        if int(ids[r]) != int(want_ids[r]):  # only a near tie of the perturbed scores may differ
+            T = float(temp[r]) or 1.0
+            noise = ref.gumbel_noise(V, int(keys[r]) & (2**64 - 1), int(pos[r]))
+            sc = logits[r].double().cpu().numpy() / T + noise
+            assert abs(sc[int(ids[r])] - sc.max()) < 1e-4
+    torch.testing.assert_close(lp.cpu(), want_lp, rtol=1e-4, atol=1e-4)
+    # same key and position: the same draw whatever the row; another position or key: another stream
+    again = torch.zeros(6, dtype=torch.int32, device=DEV)
+    order = torch.tensor([5, 4, 3, 2, 1, 0], device=DEV)
+    ops.sample(logits[order].contiguous(), temp[order].contiguous(), keys[order].contiguous(), pos[order].contiguous(), None, again, None, None)
+    assert again.tolist() == ids[order].tolist()
+
+
+def test_sampling_follows_the_distribution(ops):
+    """20,000 draws from a 7-way distribution at T = 0.8: chi-square against softmax(logits / T)."""
+    V, N, T = 7, 20000, 0.8
+    logits = torch.tensor([1.0, 0.2, -0.5, 2.0, 0.0, -3.0, 1.5], device=DEV).repeat(N, 1).contiguous()
+    ids = torch.zeros(N, dtype=torch.int32, device=DEV)
+    ops.sample(logits, torch.full((N,), T, device=DEV), torch.arange(N, dtype=torch.int64, device=DEV) * 7919 + 13,
+               torch.zeros(N, dtype=torch.int32, device=DEV), None, ids, None, None)
+    counts = torch.bincount(ids.long().cpu(), minlength=V).double()
+    p = torch.softmax(logits[0].double().cpu() / T, -1)
+    chi2 = (((counts - N * p) ** 2) / (N * p)).sum().item()
+    assert chi2 < 24.1  # 99.95 % point of chi-square with 6 degrees of freedom
+
+
+def test_topk_logprobs(ops):
+    V, k = 509, 5
+    logits = (torch.randn(4, V, generator=torch.Generator().manual_seed(9)) * 2).to(DEV)
+    logits[2, 10] = logits[2, 20] = logits[2].max() + 1  # a tie: the smaller index first
+    temp = torch.tensor([0.0, 0.5, 1.0, 2.0], device=DEV)
+    idx = torch.zeros(4, k, dtype=torch.int32, device=DEV)
+    lp = torch.zeros(4, k, device=DEV)
+    ops.topk_logprobs(logits, temp, k, idx, lp)
+    widx, wlp = torch.zeros(4, k, dtype=torch.int32), torch.zeros(4, k)
+    ref.topk_logprobs(logits.cpu(), temp.cpu(), k, widx, wlp)
+    assert torch.equal(idx.cpu(), widx)
+    torch.testing.assert_close(lp.cpu(), wlp, rtol=1e-4, atol=1e-4)
+
+
+def test_refusals(ops):
+    with pytest.raises(ops.KernelError, match="multiples of 16"):
+        ops.check_head_dim(24)
+    with pytest.raises(ops.KernelError, match="CUDA"):
+        ops.silu_mul(torch.zeros(2, 4), torch.zeros(2, 2))
+    with pytest.raises(ops.KernelError):
+        ops.sgemm_tn(torch.zeros(2, 4, device=DEV), torch.zeros(3, 5, device=DEV), torch.zeros(2, 3, device=DEV))
+    with pytest.raises(ops.KernelError):
+        ops.add_rmsnorm(torch.zeros(2, 4, device=DEV, dtype=torch.bfloat16), None, torch.ones(4, device=DEV), 1e-5,
+                        torch.zeros(2, 4, device=DEV))

@@ -1,0 +1,129 @@
+"""The scheduler's decisions, with a cache manager that keeps books only and a stand-in for the
+model: admission, portions under the token budget, decoding, finishing, and pushing requests
+out when pages run out."""
+
+import pytest
+
+from tokasaurus_b200.cache import CacheManager, NoSpaceError
+from tokasaurus_b200.engine.scheduler import RequestTooLongError, Scheduler
+from tokasaurus_b200.parts.base import PagedCacheNeed
+from tokasaurus_b200.sampling.params import Request, SamplingParams
+
+
+def make(num_pages=64, page_size=4, max_tokens=16, max_seqs=8, **kw):
+    cache = CacheManager({0: PagedCacheNeed(1, 16)}, page_size=page_size, num_pages=num_pages, max_requests=max_seqs)
+    return Scheduler(cache, max_tokens, max_seqs, sanity_checks=True, **kw), cache
+
+
+def req(i, n, max_new=4, **kw):
+    return Request(f"r{i}", list(range(1, n + 1)), max_new, SamplingParams(), **kw)
+
+
+def run(s, token=lambda seq: 7, limit=10_000):
+    finished, plans = [], []
+    while s.has_work() and limit:
+        limit -= 1
+        plan = s.schedule()
+        plans.append(plan)
+        sampled = [token(p.seq) for p in plan.portions if p.samples]
+        finished += s.complete(plan, sampled, [0.0] * len(sampled))
+    return finished, plans
+
+
+def test_portions_follow_the_budget():
+    s, cache = make(max_tokens=16)
+    s.add_request(req(0, 40, 3))
+    s.add_request(req(1, 5, 3))
+    plan = s.schedule()
+    assert [(p.seq.id, p.start, p.n_tokens, p.samples) for p in plan.portions] == [("r0", 0, 16, False)]
+    s.complete(plan, [])
+    plan = s.schedule()
+    assert [(p.seq.id, p.start, p.n_tokens) for p in plan.portions] == [("r0", 16, 16)]
+    s.complete(plan, [])
+    plan = s.schedule()  # r0's last 8 tokens, then r1's 5 fit in the same step
+    assert [(p.seq.id, p.start, p.n_tokens, p.samples) for p in plan.portions] == [("r0", 32, 8, True), ("r1", 0, 5, True)]
+    s.complete(plan, [7, 7])
+    plan = s.schedule()  # both decode from the device's last-token table
+    assert [(p.seq.id, p.start, p.n_tokens, p.from_device) for p in plan.portions] == [("r0", 40, 1, True), ("r1", 5, 1, True)]
+    assert cache.pages_for(41) == len(cache.table("r0", 0))
+
+
+def test_decodes_come_first_and_prompt_is_cut_where_the_budget_ends():
+    s, _ = make(max_tokens=8)
+    s.add_request(req(0, 3, 10))
+    s.add_request(req(1, 3, 10))
+    fin, plans = run(s, limit=2)
+    s.add_request(req(2, 30, 2))
+    plan = s.schedule()
+    assert [(p.seq.id, p.n_tokens, p.from_device) for p in plan.portions] == [("r0", 1, True), ("r1", 1, True), ("r2", 6, False)]
+
+
+def test_finish_by_length_stop_and_eos():
+    s, cache = make(eos_token_ids=(9,))
+    s.add_request(req(0, 3, 5))
+    s.add_request(req(1, 3, 5, stop_token_ids=(8,)))
+    s.add_request(req(2, 3, 5, ignore_eos=True))
+    seqs = iter([1, 1, 1, 9, 8, 9, 2, 2, 2])
+    fin, _ = run(s, token=lambda seq: {"r0": [1, 9], "r1": [1, 8], "r2": [1, 9, 9, 9, 9]}[seq.id][len(seq.output.completion_ids)])
+    by = {o.id: o for o in fin}
+    assert by["r0"].completion_ids == [1, 9] and by["r0"].finish_reason == "stop"
+    assert by["r1"].completion_ids == [1, 8] and by["r1"].finish_reason == "stop"
+    assert by["r2"].completion_ids == [1, 9, 9, 9, 9] and by["r2"].finish_reason == "length"
+    assert not cache.requests and cache.num_free_pages() == [64]
+
+
+def test_worst_case_reservation_never_pushes_out():
+    s, cache = make(num_pages=12, page_size=4, max_tokens=64)
+    for i in range(6):
+        s.add_request(req(i, 8, 9))  # each can come to hold 4 pages: only 3 fit at a time
+    plan = s.schedule()
+    assert len(plan.portions) == 3 and len(s.queued) == 3
+    s.complete(plan, [7] * 3)
+    fin, _ = run(s)
+    assert s.stats["bumps"] == 0 and len(fin) == 6
+
+
+def test_pages_run_out_the_youngest_goes_back_to_the_head_of_the_queue():
+    s, cache = make(num_pages=6, page_size=4, max_tokens=64, bump_city_population_me=True)
+    for i in range(3):
+        s.add_request(req(i, 8, 12))  # 2 pages each at first: the pool is full after admission
+    plan = s.schedule()
+    assert [p.seq.id for p in plan.portions] == ["r0", "r1", "r2"] and cache.num_free_pages() == [0]
+    s.complete(plan, [7] * 3)
+    plan = s.schedule()  # all three want a third page for position 8
+    assert plan.bumped == ["r2"]  # the youngest; its two pages serve r0 and r1
+    assert [p.seq.id for p in plan.portions] == ["r0", "r1"]
+    assert [q.id for q in s.queued] == ["r2"] and cache.num_free_pages() == [0]
+    s.add_request(req(3, 4, 2))
+    assert [q.id for q in s.queued] == ["r2", "r3"]  # a pushed-out request waits at the head of the queue
+    s.complete(plan, [7, 7])
+    fin, plans = run(s)
+    assert sorted(o.id for o in fin) == ["r0", "r1", "r2", "r3"]
+    assert all(len(o.completion_ids) == 12 for o in fin if o.id != "r3")
+    # a pushed-out request is fed its prompt and what it had produced again, as one prompt
+    again = [p for pl in plans for p in pl.portions if p.seq.id == "r2" and not p.from_device]
+    assert again and again[0].start == 0 and again[0].n_tokens == 8 + 1
+    assert not cache.requests and cache.num_free_pages() == [6]
+
+
+def test_request_that_can_never_fit_is_refused():
+    s, _ = make(num_pages=4, page_size=4)
+    with pytest.raises(RequestTooLongError):
+        s.add_request(req(0, 10, 10))
+    s2, _ = make(max_num_tokens_per_request=12)
+    with pytest.raises(RequestTooLongError):
+        s2.add_request(req(0, 10, 3))
+    with pytest.raises(ValueError):
+        s.add_request(Request("e", [], 3))
+    with pytest.raises(ValueError):
+        s.add_request(Request("p", [1], 3, SamplingParams(top_p=0.9)))
+
+
+def test_slots_limit_admission():
+    s, _ = make(max_seqs=2, max_tokens=64)
+    for i in range(4):
+        s.add_request(req(i, 3, 2))
+    plan = s.schedule()
+    assert len(plan.portions) == 2
+    fin, _ = run(s)
+    assert len(fin) == 4

@@ -22,6 +22,9 @@ import numpy as np
 import torch
 
 
+_TORCH_OF = {"float32": torch.float32, "int64": torch.int64, "uint64": torch.int64, "uint32": torch.int32}
+
+
 @dataclass
 class StepEntry:
     request: object
@@ -60,7 +63,8 @@ class HostBatch:
 class StepContext:
     """Everything a part may look at while it runs one step."""
 
-    def __init__(self, host: HostBatch, cache_manager, device: torch.device, stager: "Stager"):
+    def __init__(self, host: HostBatch, cache_manager, device: torch.device, stager: "Stager",
+                 extra: dict[str, np.ndarray] | None = None):
         self.host = host
         self.cache_manager = cache_manager
         self.device = device
@@ -74,7 +78,9 @@ class StepContext:
                   host.seq_kv_len, host.logit_rows]
         for ip, pg in zip(host.table_indptr, host.table_pages):
             arrays += [ip, pg]
-        views = stager.upload(arrays)
+        extra = extra or {}
+        views = stager.upload(arrays + list(extra.values()))
+        self.extra = dict(zip(extra.keys(), views[len(arrays):]))
         (self.token_ids, self.positions, self.token_seq, self.seq_slot, self.seq_q_start, self.seq_q_len,
          self.seq_kv_len, self.logit_rows) = views[:8]
         self.tables = [GroupTables(views[8 + 2 * g], views[9 + 2 * g]) for g in range(len(host.table_indptr))]
@@ -107,7 +113,11 @@ class Stager:
     def upload(self, arrays: Sequence[np.ndarray]) -> list[torch.Tensor]:
         offs = []
         total = 0
-        for a in arrays:
+        kinds = [a.dtype for a in arrays]
+        arrays = [a if a.dtype == np.int32 else np.ascontiguousarray(a).view(np.int32) for a in arrays]
+        for a, k in zip(arrays, kinds):
+            if k.itemsize not in (4, 8):
+                raise TypeError("step arrays have 4- or 8-byte elements")
             offs.append(total)
             total += (a.shape[0] + 3) & ~3
         total = max(total, 4)
@@ -120,15 +130,17 @@ class Stager:
             self._copied.synchronize()  # the last copy out of the pinned buffer must be over before it is rewritten
             self._pending = False
         for a, o in zip(arrays, offs):
-            if a.dtype != np.int32:
-                raise TypeError("step arrays are int32")
             self.host_np[o:o + a.shape[0]] = a
         self.dev[:total].copy_(self.host[:total], non_blocking=True)
         if self._copied is not None:
             self._copied.record()
             self._pending = True
         self.bytes_last_upload = total * 4
-        return [self.dev[o:o + a.shape[0]] for a, o in zip(arrays, offs)]
+        out = []
+        for a, o, k in zip(arrays, offs, kinds):
+            v = self.dev[o:o + a.shape[0]]
+            out.append(v if k == np.int32 else v.view(_TORCH_OF[k.name]))
+        return out
 
 
 def build_host_batch(entries: Sequence[StepEntry], cache_manager) -> HostBatch:

@@ -1,0 +1,135 @@
+"""The Python entry point: an engine that takes token ids and gives back generated token ids.
+
+The reference is reached over HTTP; its in-process pieces are ``server_manager``
+(tokasaurus/entry.py:90-111) and the hand wiring of tokasaurus/benchmarks/bench_model.py:119-283.
+This class is the whole of that in one process: scheduler and cache manager on the host, the step
+function and the sampler on the GPU.
+
+    engine = Engine(model="/path/to/folder", dtype="bfloat16", kv_cache_num_tokens=65536)
+    outs = engine.generate([[1, 2, 3], [4, 5]], SamplingParams(temperature=0.7, seed=7), max_num_tokens=20)
+    outs[0].completion_ids
+"""
+
+from __future__ import annotations
+
+from typing import Any, Sequence
+
+import numpy as np
+import torch
+
+from tokasaurus_b200.config.engine_config import EngineConfig
+from tokasaurus_b200.engine.batch import StepEntry
+from tokasaurus_b200.engine.runner import ModelRunner
+from tokasaurus_b200.engine.scheduler import Scheduler, StepPlan
+from tokasaurus_b200.sampling.params import Request, RequestOutput, SamplingParams, stream_key
+from tokasaurus_b200.sampling.sampler import Sampler
+
+
+class Engine:
+    def __init__(self, model: str | None = None, config: EngineConfig | None = None,
+                 config_dict: dict[str, Any] | None = None, seed: int = 0, kv_reserve_fraction: float = 1.0,
+                 **options: Any):
+        """``model``: folder with config.json and model.safetensors.  ``options``: fields of
+        ``EngineConfig`` (the reference's option names).  ``config_dict`` with
+        ``random_weights=<seed>`` builds a model without a folder."""
+        cfg = config or EngineConfig()
+        if model is not None:
+            cfg.model = model
+        for k, v in options.items():
+            if not hasattr(cfg, k):
+                raise TypeError(f"unknown engine option {k!r}")
+            setattr(cfg, k, v)
+        if cfg.max_seqs_per_forward > cfg.max_tokens_per_forward:
+            cfg.max_seqs_per_forward = cfg.max_tokens_per_forward
+        self.config = cfg
+        self.seed = seed
+        self.runner = ModelRunner(cfg, config_dict)
+        self.scheduler = Scheduler(
+            self.runner.cache, cfg.max_tokens_per_forward, cfg.max_seqs_per_forward,
+            cfg.max_num_tokens_per_request, self.runner.eos_token_ids, kv_reserve_fraction,
+            cfg.bump_city_population_me, cfg.allocator_sanity_checks)
+        self.sampler = Sampler(self.runner.rt.device, max(64, min(cfg.max_seqs_per_forward, 4096)),
+                               cfg.enable_chosen_logprobs)
+        self._auto_id = 0
+        self.last_step_bytes = dict(h2d=0, d2h=0)
+
+    # ------------------------------------------------------------------ requests
+    def add_request(self, input_ids: Sequence[int], sampling_params: SamplingParams | None = None,
+                    max_num_tokens: int = 16, ignore_eos: bool = False, stop_token_ids: Sequence[int] = (),
+                    topk_logprobs: int | None = None, request_id: str | None = None) -> str:
+        vocab = self.runner.vocab
+        ids = [int(t) for t in input_ids]
+        bad = [t for t in ids if not 0 <= t < vocab]
+        if bad:
+            raise ValueError(f"token ids {bad[:5]} are outside the vocabulary of {vocab}")
+        if topk_logprobs is not None:
+            limit = self.config.max_topk_logprobs
+            if limit is None or topk_logprobs > limit:
+                raise ValueError(f"topk_logprobs={topk_logprobs} exceeds max_topk_logprobs={limit}")
+        if request_id is None:
+            request_id = f"req-{self._auto_id}"
+            self._auto_id += 1
+        req = Request(request_id, ids, int(max_num_tokens), sampling_params or SamplingParams(), ignore_eos,
+                      tuple(int(t) for t in stop_token_ids), topk_logprobs)
+        self.scheduler.add_request(req)
+        return request_id
+
+    def has_work(self) -> bool:
+        return self.scheduler.has_work()
+
+    # ------------------------------------------------------------------ one step
+    def _sampling_arrays(self, plan: StepPlan) -> dict[str, np.ndarray]:
+        rows = [p for p in plan.portions if p.samples]
+        temp = np.asarray([p.seq.request.sampling_params.temperature for p in rows], dtype=np.float32)
+        keys = np.asarray(
+            [stream_key(p.seq.request.sampling_params.seed if p.seq.request.sampling_params.seed is not None
+                        else self.seed, p.seq.index) for p in rows], dtype=np.int64)
+        pos = np.asarray([p.start + p.n_tokens for p in rows], dtype=np.int32)
+        slot = np.asarray([self.runner.cache.slot(p.seq.id) for p in rows], dtype=np.int32)
+        return dict(temperature=temp, stream_key=keys, sample_pos=pos, row_slot=slot)
+
+    def step(self) -> list[RequestOutput]:
+        """Schedule, run and account for one step; return the requests that ended in it."""
+        plan = self.scheduler.schedule()
+        if not plan.portions:
+            return []
+        entries = []
+        for p in plan.portions:
+            toks = None if p.from_device else p.seq.tokens[p.start:p.start + p.n_tokens]
+            entries.append(StepEntry(p.seq.id, toks, p.start, [p.n_tokens - 1] if p.samples else []))
+        extra = self._sampling_arrays(plan)
+        logits = self.runner.step(entries, extra)
+        R = logits.shape[0]
+        ids: list[int] = []
+        lps: list[float] = []
+        topk = None
+        if R:
+            ex = self.runner.last_context.extra
+            self.sampler.sample(logits, ex["temperature"], ex["stream_key"], ex["sample_pos"], ex["row_slot"],
+                                self.runner.cache.last_token)
+            kmax = max((p.seq.request.topk_logprobs or 0) for p in plan.portions if p.samples)
+            if kmax:
+                ti, tl = self.sampler.topk(logits, ex["temperature"], kmax)
+            ids, lps = self.sampler.read(R)
+            if kmax:
+                topk = list(zip(ti.tolist(), tl.tolist()))
+        self.runner.check_status()
+        self.last_step_bytes = dict(h2d=self.runner.last_upload_bytes, d2h=self.sampler.bytes_last_read if R else 4)
+        return self.scheduler.complete(plan, ids, lps if self.config.enable_chosen_logprobs else None, topk)
+
+    def run_until_done(self) -> list[RequestOutput]:
+        done: list[RequestOutput] = []
+        while self.scheduler.has_work():
+            done.extend(self.step())
+        return done
+
+    def generate(self, prompts: Sequence[Sequence[int]], sampling_params: SamplingParams | Sequence[SamplingParams] | None = None,
+                 max_num_tokens: int = 16, ignore_eos: bool = False, stop_token_ids: Sequence[int] = (),
+                 topk_logprobs: int | None = None) -> list[RequestOutput]:
+        """Generate for every prompt (lists of token ids); outputs come back in the prompts' order."""
+        ids = []
+        for i, p in enumerate(prompts):
+            sp = sampling_params[i] if isinstance(sampling_params, (list, tuple)) else sampling_params
+            ids.append(self.add_request(p, sp, max_num_tokens, ignore_eos, stop_token_ids, topk_logprobs))
+        by_id = {o.id: o for o in self.run_until_done()}
+        return [by_id[i] for i in ids]

@@ -91,13 +91,16 @@ class ModelRunner:
         self.last_upload_bytes = 0
 
     # ------------------------------------------------------------------
-    def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+    def step(self, entries: Sequence[StepEntry], extra: dict | None = None) -> torch.Tensor:
         """Run the tokens of ``entries`` as one batch from the cache and return float32 logits
         [wanted places, vocab] on the device, in the order of the entries and of their ``want``.
-        Pages for the new positions must have been given to the requests before."""
+        Pages for the new positions must have been given to the requests before.  ``extra``: further
+        numpy arrays (4- or 8-byte elements) that travel to the device in the same copy; their
+        device views are in ``self.last_context.extra``."""
         host = build_host_batch(entries, self.cache)
-        ctx = StepContext(host, self.cache, self.rt.device, self.stager)
+        ctx = StepContext(host, self.cache, self.rt.device, self.stager, extra)
         self.last_upload_bytes = self.stager.bytes_last_upload
+        self.last_context = ctx
         return self.model.forward(ctx)
 
     def check_status(self) -> None:

@@ -1,0 +1,264 @@
+"""The scheduler: admits requests, cuts prompts into portions under a token budget, decodes,
+finishes and frees.
+
+In the manner of the reference's manager (tokasaurus/manager/manager.py:981-1023 loop,
+tokasaurus/manager/scheduler.py:576-637 ``schedule``, :640-684 ``apply_decision``), much smaller:
+
+* Three FIFO stages: queued -> prefilling -> decoding (tokasaurus/manager/types.py:150-250).
+* Every decoding sequence is in every step with one token.  What is left of
+  ``max_tokens_per_forward`` goes to prompts, first come first served, and a prompt is cut
+  wherever the budget ends (``make_scheduling_decision``, scheduler.py:541-573; with
+  ``greedy_prefill`` the reference too takes all that fits, scheduler.py:604-637).
+* Admission: a queued request enters when a slot is free and the pool has pages for its whole
+  prompt (allocated at once, as ``allocate_with_prefix_match`` does, allocator.py:324-384) on top
+  of what is set aside for running requests.  ``kv_reserve_fraction`` = 1 sets aside every page a
+  running request can still come to need (no request is ever pushed out); smaller values admit
+  more and rely on the next rule; ``bump_city_population_me`` (the reference's debugging flag,
+  common_types.py:125) sets nothing aside.
+* When a decoding sequence needs a page and none is free, the most recently admitted running
+  sequence is pushed out ("bumped", manager.py:745-813): its pages and slot are given back and it
+  returns to the HEAD of the queue.  Unlike the reference, which restarts it from the bare prompt
+  and samples anew, it keeps the tokens it has produced: they are fed again as part of its
+  prompt, so its output is the same as without the bump.
+* A sequence ends on ``max_num_tokens``, on an end-of-sequence id (unless ``ignore_eos``) or on
+  one of its ``stop_token_ids`` (manager.py:201-206); its pages and slot are given back then.
+"""
+
+from __future__ import annotations
+
+from collections import deque
+from dataclasses import dataclass, field
+
+from tokasaurus_b200.cache.manager import CacheManager
+from tokasaurus_b200.cache.pages import NoSpaceError
+from tokasaurus_b200.sampling.params import Request, RequestOutput
+
+
+class RequestTooLongError(ValueError):
+    pass
+
+
+@dataclass
+class Sequence:
+    request: Request
+    index: int  # running number of the request within the engine (random stream, admission order)
+    output: RequestOutput
+    fed: int = 0  # tokens of prompt + completion that have gone through the model
+    admitted_at: int = -1
+
+    @property
+    def id(self) -> str:
+        return self.request.id
+
+    @property
+    def tokens(self) -> list[int]:
+        """Everything known of the sequence: prompt, then what it has produced."""
+        return self.request.input_ids + self.output.completion_ids
+
+    @property
+    def n_known(self) -> int:
+        return len(self.request.input_ids) + len(self.output.completion_ids)
+
+    def max_total(self) -> int:
+        # the last produced token is never fed back (tokasaurus/manager/types.py:117-122)
+        return len(self.request.input_ids) + self.request.max_num_tokens - 1
+
+
+@dataclass
+class ScheduledPortion:
+    seq: Sequence
+    start: int
+    n_tokens: int
+    samples: bool  # the last of these tokens yields the sequence's next token
+    from_device: bool  # single token that is still in the device's last-token table
+
+
+@dataclass
+class StepPlan:
+    portions: list[ScheduledPortion] = field(default_factory=list)
+    bumped: list[str] = field(default_factory=list)
+
+    @property
+    def n_tokens(self) -> int:
+        return sum(p.n_tokens for p in self.portions)
+
+
+class Scheduler:
+    def __init__(self, cache: CacheManager, max_tokens_per_forward: int, max_seqs_per_forward: int,
+                 max_num_tokens_per_request: int | None = None, eos_token_ids: tuple[int, ...] = (),
+                 kv_reserve_fraction: float = 1.0, bump_city_population_me: bool = False,
+                 sanity_checks: bool = False):
+        self.cache = cache
+        self.max_tokens = max_tokens_per_forward
+        self.max_seqs = max_seqs_per_forward
+        self.max_request_tokens = max_num_tokens_per_request
+        self.eos = set(eos_token_ids)
+        self.reserve_fraction = 0.0 if bump_city_population_me else kv_reserve_fraction
+        self.sanity_checks = sanity_checks
+        self.queued: deque[Sequence] = deque()
+        self.prefilling: list[Sequence] = []
+        self.decoding: list[Sequence] = []
+        self._counter = 0
+        self._admissions = 0
+        self.stats = dict(steps=0, prefill_tokens=0, decode_tokens=0, bumps=0, finished=0)
+
+    # ------------------------------------------------------------------ intake
+    def add_request(self, request: Request) -> Sequence:
+        request.sampling_params.validate()
+        n = len(request.input_ids)
+        if n == 0:
+            raise ValueError(f"request {request.id!r} has an empty prompt")
+        if request.max_num_tokens <= 0:
+            raise ValueError(f"request {request.id!r}: max_num_tokens must be positive")
+        total = n + request.max_num_tokens
+        if self.max_request_tokens is not None and total > self.max_request_tokens:
+            raise RequestTooLongError(
+                f"request {request.id!r}: prompt {n} + max_num_tokens {request.max_num_tokens} exceeds "
+                f"max_num_tokens_per_request={self.max_request_tokens}")
+        if self.cache.pages_for(total - 1) > self.cache.num_pages:
+            raise RequestTooLongError(
+                f"request {request.id!r} can need {self.cache.pages_for(total - 1)} pages, the pool has "
+                f"{self.cache.num_pages}")
+        seq = Sequence(request, self._counter, RequestOutput(request.id))
+        self._counter += 1
+        self.queued.append(seq)
+        return seq
+
+    def has_work(self) -> bool:
+        return bool(self.queued or self.prefilling or self.decoding)
+
+    def running(self) -> list[Sequence]:
+        return self.decoding + self.prefilling
+
+    # ------------------------------------------------------------------ pages
+    def _reserved_for_running(self) -> int:
+        """Pages that running sequences may still ask for, scaled by the reserve fraction."""
+        if self.reserve_fraction <= 0:
+            return 0
+        ps = self.cache.pages_for
+        need = 0
+        for s in self.running():
+            held = len(self.cache.requests[s.id].tables[0]) if self.cache.groups else 0
+            need += max(0, ps(s.max_total()) - held)
+        return int(need * self.reserve_fraction + 0.999999)
+
+    def _min_free(self) -> int:
+        free = self.cache.num_free_pages()
+        return min(free) if free else 1 << 30
+
+    def _admit(self) -> None:
+        while self.queued and len(self.prefilling) + len(self.decoding) < self.max_seqs \
+                and self.cache.slots.num_free > 0:
+            seq = self.queued[0]
+            first_need = self.cache.pages_for(seq.n_known)
+            reserve_own = 0
+            if self.reserve_fraction > 0:
+                reserve_own = int((self.cache.pages_for(seq.max_total()) - first_need) * self.reserve_fraction + 0.999999)
+            if self._min_free() - self._reserved_for_running() < first_need + max(0, reserve_own):
+                break
+            self.queued.popleft()
+            self.cache.admit(seq.id)
+            self.cache.ensure_capacity(seq.id, seq.n_known)
+            seq.fed = 0
+            seq.admitted_at = self._admissions
+            self._admissions += 1
+            self.prefilling.append(seq)
+
+    def _bump_one(self, protect: Sequence) -> Sequence | None:
+        """Push out the most recently admitted running sequence other than ``protect``."""
+        victims = [s for s in self.running() if s is not protect]
+        if not victims:
+            return None
+        victim = max(victims, key=lambda s: s.admitted_at)
+        self._release(victim)
+        victim.fed = 0
+        victim.output.num_preemptions += 1
+        self.queued.appendleft(victim)
+        self.stats["bumps"] += 1
+        return victim
+
+    def _release(self, seq: Sequence) -> None:
+        if seq in self.decoding:
+            self.decoding.remove(seq)
+        if seq in self.prefilling:
+            self.prefilling.remove(seq)
+        self.cache.free(seq.id)
+
+    # ------------------------------------------------------------------ one step
+    def schedule(self) -> StepPlan:
+        plan = StepPlan()
+        # 1. pages for the next token of every decoding sequence, pushing sequences out if the pool is dry
+        for seq in sorted(self.decoding, key=lambda s: s.admitted_at):
+            if seq not in self.decoding:
+                continue  # was pushed out a moment ago
+            while True:
+                try:
+                    self.cache.ensure_capacity(seq.id, seq.fed + 1)
+                    break
+                except NoSpaceError:
+                    victim = self._bump_one(protect=seq)
+                    if victim is None:
+                        raise
+                    plan.bumped.append(victim.id)
+        # 2. admission
+        self._admit()
+        if not self.decoding and not self.prefilling and self.queued:
+            seq = self.queued[0]
+            raise NoSpaceError(
+                f"request {seq.id!r} needs {self.cache.pages_for(seq.n_known)} pages for its prompt and "
+                f"{self._min_free()} are free with nothing running")
+        # 3. the batch: one token for each decoding sequence, then prompt portions under the budget
+        for seq in self.decoding:
+            plan.portions.append(ScheduledPortion(seq, seq.fed, 1, True, from_device=True))
+        budget = self.max_tokens - len(plan.portions)
+        for seq in self.prefilling:
+            if budget <= 0:
+                break
+            n = min(budget, seq.n_known - seq.fed)
+            plan.portions.append(ScheduledPortion(seq, seq.fed, n, seq.fed + n == seq.n_known, from_device=False))
+            budget -= n
+        return plan
+
+    def complete(self, plan: StepPlan, sampled: list[int], logprobs: list[float] | None = None,
+                 topk: list[tuple[list[int], list[float]]] | None = None) -> list[RequestOutput]:
+        """Account for a step that has run.  ``sampled`` holds one id per portion with ``samples``,
+        in plan order.  Returns the outputs of the requests that ended."""
+        finished: list[RequestOutput] = []
+        k = 0
+        self.stats["steps"] += 1
+        for p in plan.portions:
+            seq = p.seq
+            seq.fed += p.n_tokens
+            if p.from_device:
+                self.stats["decode_tokens"] += 1
+            else:
+                self.stats["prefill_tokens"] += p.n_tokens
+            self.cache.release_behind_window(seq.id, seq.fed)
+            if not p.samples:
+                continue
+            tok = int(sampled[k])
+            seq.output.completion_ids.append(tok)
+            if logprobs is not None:
+                seq.output.logprobs.append(float(logprobs[k]))
+            if topk is not None and seq.request.topk_logprobs:
+                seq.output.topk_ids.append(topk[k][0][: seq.request.topk_logprobs])
+                seq.output.topk_logprobs.append(topk[k][1][: seq.request.topk_logprobs])
+            k += 1
+            if seq in self.prefilling:
+                self.prefilling.remove(seq)
+                self.decoding.append(seq)
+            reason = None
+            if (not seq.request.ignore_eos and tok in self.eos) or tok in seq.request.stop_token_ids:
+                reason = "stop"
+            elif len(seq.output.completion_ids) >= seq.request.max_num_tokens:
+                reason = "length"
+            if reason:
+                seq.output.finish_reason = reason
+                self._release(seq)
+                finished.append(seq.output)
+                self.stats["finished"] += 1
+        if k != len(sampled):
+            raise ValueError(f"the step sampled {len(sampled)} tokens, the plan wanted {k}")
+        if self.sanity_checks:
+            self.cache.check()
+        return finished

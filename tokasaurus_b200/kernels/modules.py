@@ -1,0 +1,18 @@
+"""The list of kernel modules (source file, compile-time constants) that exist."""
+
+from __future__ import annotations
+
+
+def common_modules() -> list[tuple[str, dict | None]]:
+    return [("elementwise.cu", None), ("sgemm.cu", None), ("sampling.cu", None)]
+
+
+def head_dim_modules(head_dim: int) -> list[tuple[str, dict | None]]:
+    return [("attention_simt.cu", {"TKB_HD": head_dim})]
+
+
+def all_modules(head_dims) -> list[tuple[str, dict | None]]:
+    mods = common_modules()
+    for hd in head_dims:
+        mods += head_dim_modules(hd)
+    return mods

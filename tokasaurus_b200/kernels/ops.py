@@ -96,12 +96,12 @@ def check_head_dim(hd: int) -> None:
 
 def prepare(head_dims=(), dtype: torch.dtype = torch.bfloat16) -> None:
     """Build and load everything a model with these head sizes needs (first call compiles)."""
-    _libs.get("elementwise.cu")
-    _libs.get("sgemm.cu")
-    _libs.get("sampling.cu")
+    from tokasaurus_b200.kernels.modules import all_modules
+
     for hd in head_dims:
         check_head_dim(hd)
-        _libs.get("attention_simt.cu", TKB_HD=hd)
+    for source, defines in all_modules(head_dims):
+        _libs.get(source, **(defines or {}))
 
 
 # ---------------------------------------------------------------------------------------------
