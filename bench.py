@@ -1,0 +1,335 @@
+"""Throughput of the engine on one B200: decoded tokens a second at the sizes of Llama-3.2-1B with
+random weights (the metric and configuration of BASELINE.json's configs[2]).
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+
+Prints ONE JSON line.  ``value``: decoded tokens a second at batch 8, each request holding a
+2,048-token prompt in the cache, timed on the device with CUDA events around K decode steps
+(each step: the host builds the batch, one pinned copy to the device, the model, the sampler; the
+sampled tokens stay on the device).  ``e2e``: the same through the Python entry point
+(``Engine.step``: scheduler, pinned host-to-device copy of the step's inputs, model, sampler,
+device-to-host read of the sampled tokens), by the wall clock.  ``prefill``: one 2,048-token
+prompt in one step.  ``roofline``: bytes a decode step has to read (every weight it uses once, and
+the cache of the live requests) over its time, against the measured copy bandwidth.  ``points``:
+decode at batch 1 and 64.  The weights (2.5 GB) are larger than the L2 cache (126 MB), so every
+step reads them from HBM; nothing is flushed between steps.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+FALLBACK_PEAKS = dict(hbm_gbs=6650.0, bf16_tflops=1590.0, bf16_tflops_sustained=1400.0)
+
+
+def load_baseline_config() -> dict:
+    """Sizes of BASELINE.json's configs[2] (Llama-3.2-1B), as config.json keys."""
+    return dict(
+        architectures=["LlamaForCausalLM"], model_type="llama", num_hidden_layers=16, hidden_size=2048,
+        num_attention_heads=32, num_key_value_heads=8, intermediate_size=8192, vocab_size=128256, rope_theta=500000.0,
+        rope_scaling=dict(rope_type="llama3", factor=32.0, low_freq_factor=1.0, high_freq_factor=4.0,
+                          original_max_position_embeddings=8192),
+        rms_norm_eps=1e-5, tie_word_embeddings=True, max_position_embeddings=131072)
+
+
+def load_peaks() -> tuple[dict, str]:
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.isfile(path):
+        try:
+            with open(path) as f:
+                d = json.load(f)
+            peaks = dict(FALLBACK_PEAKS)
+            for k in peaks:
+                if isinstance(d.get(k), (int, float)):
+                    peaks[k] = float(d[k])
+            return peaks, "measured"
+        except (OSError, ValueError):
+            pass
+    return dict(FALLBACK_PEAKS), "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while a region is timed."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int = 0):
+        self.index = index
+        self.proc = None
+        self.lines: list[str] = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100", "-i",
+                 str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return dict(sm_mhz=None, sm_max_mhz=None, reasons=["nvidia-smi unavailable"])
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for n, v in zip(names, parts[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return dict(sm_mhz=statistics.median(sm) if sm else None, sm_max_mhz=max(mx) if mx else None,
+                    reasons=sorted(reasons), samples=len(sm))
+
+
+def model_numbers(cfg: dict, layers: int):
+    H, I, V = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"]
+    nh, nkv = cfg["num_attention_heads"], cfg["num_key_value_heads"]
+    hd = H // nh
+    per_layer = (nh + 2 * nkv) * hd * H + H * nh * hd + 3 * H * I
+    return dict(H=H, I=I, V=V, nh=nh, nkv=nkv, hd=hd, per_layer_params=per_layer, head_params=V * H, layers=layers)
+
+
+def decode_bytes(m: dict, batch: int, ctx_len: float, elt: int = 2) -> float:
+    weights = (m["layers"] * m["per_layer_params"] + m["head_params"]) * elt + (2 * m["layers"] + 1) * m["H"] * 4
+    kv = batch * ctx_len * 2 * m["nkv"] * m["hd"] * elt * m["layers"]
+    return weights + kv
+
+
+def prefill_flops(m: dict, T: int, rows: int = 1) -> float:
+    L = m["layers"]
+    attn_proj = (m["nh"] + 2 * m["nkv"]) * m["hd"] * m["H"]
+    rest = m["per_layer_params"] - attn_proj  # o, gate, up, down: only `rows` rows in the last layer
+    linear = 2.0 * T * (L * attn_proj + (L - 1) * rest) + 2.0 * rows * rest + 2.0 * rows * m["head_params"]
+    attention = L * m["nh"] * m["hd"] * 4.0 * T * (T + 1) / 2
+    return linear + attention
+
+
+def run_ours(args) -> dict:
+    import numpy as np
+    import torch
+
+    from tokasaurus_b200.engine.batch import StepEntry
+    from tokasaurus_b200.engine.engine import Engine
+    from tokasaurus_b200.kernels import ops
+    from tokasaurus_b200.sampling.params import SamplingParams
+
+    cfg = load_baseline_config()
+    full_layers = cfg["num_hidden_layers"]
+    layers = args.layers or full_layers
+    cfg["num_hidden_layers"] = layers
+    peaks, peak_src = load_peaks()
+    prompt_len, context_len, page_size = 2048, 4096, 16
+    max_batch = max(args.batch, 64 if not args.skip_points else args.batch)
+    pool_tokens = max_batch * context_len
+    eng = Engine(config_dict=cfg, random_weights=0, dtype="bfloat16", page_size=page_size,
+                 kv_cache_num_tokens=pool_tokens, max_tokens_per_forward=8192, max_seqs_per_forward=max(64, max_batch),
+                 device="cuda:0")
+    runner, cache, sampler = eng.runner, eng.runner.cache, eng.sampler
+    m = model_numbers(cfg, layers)
+    g = torch.Generator().manual_seed(0)
+    dev = runner.rt.device
+
+    def tokens(n):
+        return torch.randint(0, cfg["vocab_size"], (n,), generator=g).tolist()
+
+    def event_ms(fn, reps):
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(reps):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / reps
+
+    # ---------------------------------------------------------------- prefill: 2,048 tokens in one step
+    def prefill_once():
+        cache.admit("pf")
+        cache.ensure_capacity("pf", prompt_len)
+        out = runner.step([StepEntry("pf", pf_tokens, 0, [prompt_len - 1])])
+        cache.free("pf")
+        return out
+
+    pf_tokens = tokens(prompt_len)
+    for _ in range(max(3, args.warmup // 2)):
+        prefill_once()
+    pf_reps = 5
+    pf_ms = event_ms(prefill_once, pf_reps)
+    pf_flops = prefill_flops(m, prompt_len)
+    prefill = dict(value=round(prompt_len / (pf_ms / 1e3), 1), tokens=prompt_len, ms=round(pf_ms, 3),
+                   frac=round(pf_flops / (pf_ms / 1e3) / (peaks["bf16_tflops"] * 1e12), 4))
+
+    # ---------------------------------------------------------------- decode at a batch size, on the device
+    def fill(batch, tag):
+        ids = [f"{tag}{i}" for i in range(batch)]
+        for chunk in range(0, batch, 4):
+            entries = []
+            for rid in ids[chunk:chunk + 4]:
+                cache.admit(rid)
+                cache.ensure_capacity(rid, prompt_len)
+                entries.append(StepEntry(rid, tokens(prompt_len), 0, [prompt_len - 1]))
+            logits = runner.step(entries)
+            rows = len(entries)
+            slots = torch.tensor([cache.slot(e.request) for e in entries], dtype=torch.int32, device=dev)
+            sampler.sample(logits, torch.zeros(rows, device=dev), None, None, slots, cache.last_token)
+        torch.cuda.synchronize()
+        return ids
+
+    def decode_run(batch, steps, warmup, tag):
+        ids = fill(batch, tag)
+        length = {rid: prompt_len for rid in ids}
+        zeros = np.zeros(batch, dtype=np.float32)
+        keys = np.zeros(batch, dtype=np.int64)
+
+        def one():
+            entries = []
+            for rid in ids:
+                cache.ensure_capacity(rid, length[rid] + 1)
+                entries.append(StepEntry(rid, None, length[rid], [0]))
+                length[rid] += 1
+            pos = np.asarray([length[r] for r in ids], dtype=np.int32)
+            slot = np.asarray([cache.slot(r) for r in ids], dtype=np.int32)
+            logits = runner.step(entries, dict(temperature=zeros, stream_key=keys, sample_pos=pos, row_slot=slot))
+            ex = runner.last_context.extra
+            sampler.sample(logits, ex["temperature"], ex["stream_key"], ex["sample_pos"], ex["row_slot"], cache.last_token)
+
+        for _ in range(warmup):
+            one()
+        ops.LAUNCHES = 0
+        ms = event_ms(one, steps)
+        launches = ops.LAUNCHES
+        mean_ctx = prompt_len + warmup + steps / 2
+        runner.check_status()
+        for rid in ids:
+            cache.free(rid)
+        return ms, launches, mean_ctx
+
+    clocks = ClockSampler()
+    clocks.start()
+    ms, launches, mean_ctx = decode_run(args.batch, args.steps, args.warmup, "d")
+    clock_info = clocks.stop()
+    value = args.batch * 1e3 / ms
+    nbytes = decode_bytes(m, args.batch, mean_ctx)
+    achieved = nbytes / (ms / 1e3) / 1e9
+    roofline = dict(bound="hbm", achieved=round(achieved, 1), peak=peaks["hbm_gbs"], unit="GB/s",
+                    frac=round(achieved / peaks["hbm_gbs"], 4), of=peak_src)
+
+    points = {}
+    if not args.skip_points:
+        for b in (1, 64):
+            pms, _, _ = decode_run(b, max(10, args.steps // 2), max(3, args.warmup // 2), f"p{b}_")
+            points[f"decode_b{b}"] = round(b * 1e3 / pms, 1)
+
+    # ---------------------------------------------------------------- end to end through the entry point
+    prompts = [tokens(prompt_len) for _ in range(args.batch)]
+    for p in prompts:
+        eng.add_request(p, SamplingParams(temperature=0.0), max_num_tokens=args.warmup + args.steps + 8, ignore_eos=True)
+    while eng.scheduler.prefilling or eng.scheduler.queued:
+        eng.step()
+    for _ in range(args.warmup):
+        eng.step()
+    torch.cuda.synchronize()
+    h2d = d2h = 0
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        eng.step()
+        h2d += eng.last_step_bytes["h2d"]
+        d2h += eng.last_step_bytes["d2h"]
+    torch.cuda.synchronize()
+    e2e_s = time.perf_counter() - t0
+    e2e = dict(value=round(args.batch * args.steps / e2e_s, 1), unit="tokens/s",
+               h2d_bytes_per_step=h2d // args.steps, d2h_bytes_per_step=d2h // args.steps,
+               ms_per_step=round(e2e_s * 1e3 / args.steps, 4))
+
+    return {
+        "metric": "decode tokens/s (Llama-3.2-1B sizes, batch 8, 2,048-token prompts)",
+        "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic token ids (seeded uniform), random weights N(0, 0.02)",
+        "impl": "ours",
+        "config": {
+            "model": "Llama-3.2-1B sizes", "global_batch": args.batch, "seq_len": prompt_len, "context_len": context_len,
+            "parallelism": "1 GPU", "layers": layers, "layers_full": full_layers, "hidden": m["H"], "heads": m["nh"],
+            "kv_heads": m["nkv"], "head_dim": m["hd"], "intermediate": m["I"], "vocab": m["V"], "page_size": page_size,
+            "tied_embeddings": True, "rope": "llama3 factor 32", "l2": "inputs (2.5 GB of weights) larger than L2; no flush",
+            "cuda_graphs": bool(eng.config.use_cudagraphs and getattr(runner, "graphs_enabled", False)),
+        },
+        "e2e": e2e, "gpu_launches": launches, "clocks": clock_info, "prefill": prefill, "roofline": roofline,
+        "points": points,
+    }
+
+
+def run_reference(args) -> dict:
+    ref = os.path.join(ROOT, "baseline", "_ref")
+    why = None
+    if not os.path.isdir(os.path.join(ref, "tokasaurus")):
+        why = ("the reference is not installed under baseline/_ref (offline install lacks its pinned dependencies: "
+               "pydra-config, accelerate, art, statsd, flashinfer-python==0.2.0.post2)")
+    else:
+        missing = []
+        sys.path.insert(0, ref)
+        for mod in ("pydra", "accelerate", "art", "statsd"):
+            try:
+                __import__(mod)
+            except Exception:
+                missing.append(mod)
+        if missing:
+            why = f"the reference imports packages this image lacks and no wheel provides: {', '.join(missing)}"
+        else:
+            why = ("the reference's model code calls FlashInfer 0.2.0.post2 entry points (plan(head_dim=...), "
+                   "sampling_from_probs(probs, uniform)) that the installed FlashInfer 0.6.11 no longer has")
+    return {"impl": "reference", "unavailable": why}
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration (0: all)")
+    ap.add_argument("--skip-points", action="store_true", help="leave out the batch-1 and batch-64 points")
+    args = ap.parse_args()
+    if args.gpus != 1:
+        print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
+        return 2
+    args.warmup = max(3, args.warmup)
+    if args.impl == "reference":
+        print(json.dumps(run_reference(args)))
+        return 0
+    print(json.dumps(run_ours(args)))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -228,7 +228,8 @@ def test_rope_kv_write(ops, dtype, hd, rot, nh, nkv, ps):
     positions = i32([0, 1, ps - 1, ps, 5000, 131071, 3, 7, 2])
     token_seq = i32([0, 0, 0, 0, 1, 2, -1, 3, 3])
     n_pages = 131072 // ps + 8
-    tables = {0: [5, 6], 1: list(range(10, 10 + 5000 // ps + 1)), 2: [0] * (131071 // ps) + [7], 3: [9]}
+    tables = {0: [5, 6], 1: list(range(10, 10 + 5000 // ps + 1)), 2: [0] * (131071 // ps) + [7],
+              3: list(range(n_pages - 8, n_pages - 8 + 7 // ps + 1))}
     indptr, pages = [0], []
     for s in range(4):
         pages += tables[s]

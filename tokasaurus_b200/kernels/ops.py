@@ -54,7 +54,12 @@ def _need(cond: bool, msg: str) -> None:
         raise KernelError(msg)
 
 
+LAUNCHES = 0  # kernels of this engine launched so far (the benchmark reads and resets it)
+
+
 def _check(code: int, what: str) -> None:
+    global LAUNCHES
+    LAUNCHES += 1
     if code != 0:
         if code > 0:
             raise KernelError(f"{what}: CUDA launch failed with error {code}")
