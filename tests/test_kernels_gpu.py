@@ -343,3 +343,89 @@ def test_refusals(ops):
     with pytest.raises(ops.KernelError):
         ops.add_rmsnorm(torch.zeros(2, 4, device=DEV, dtype=torch.bfloat16), None, torch.ones(4, device=DEV), 1e-5,
                         torch.zeros(2, 4, device=DEV))
+
+
+# ------------------------------------------------------------------------------------------------
+# bfloat16 tensor-core attention (split-key kernel for single tokens, tiled kernel for portions)
+def run_mma_attention(ops, lens_q, lens_kv, nh, nkv, hd, ps, window, seed, n_pages=None, fill=1e3):
+    """A batch of requests with lens_q new tokens each at the end of lens_kv keys; returns (got, want)."""
+    from types import SimpleNamespace
+    from tokasaurus_b200.parts.attention import SPLIT_KEYS, plan_attention
+
+    dtype = torch.bfloat16
+    n_pages = n_pages or sum(-(-L // ps) for L in lens_kv) + 7
+    kc, vc, indptr, pages, K, V = make_paged(dtype, len(lens_kv), lens_kv, nkv, hd, ps, n_pages, seed=seed, fill=fill)
+    q_start, pos, tseq = [], [], []
+    for s, (n, kv) in enumerate(zip(lens_q, lens_kv)):
+        q_start.append(len(pos))
+        pos += list(range(kv - n, kv))
+        tseq += [s] * n
+    T = len(pos)
+    host = SimpleNamespace(seq_q_len=np.asarray(lens_q, dtype=np.int32), seq_kv_len=np.asarray(lens_kv, dtype=np.int32))
+    plan = plan_attention(host, window)
+    g = torch.Generator().manual_seed(seed + 1)
+    qkv = torch.randn(T, (nh + 2 * nkv) * hd, generator=g).to(dtype).to(DEV)
+    out = torch.full((T, nh * hd), float("nan"), dtype=dtype, device=DEV)
+    c = i32(plan["counts"])
+    scale = 1 / math.sqrt(hd)
+    n_items, n_dec, n_tiles = (int(x) for x in plan["counts"][:3])
+    if n_dec:
+        ops.attn_decode_mma(qkv, kc, vc, i32(q_start), i32(lens_kv), indptr, pages, i32(plan["items"]), c[0:1], n_items,
+                            i32(plan["dec_seqs"]), i32(plan["dec_item_start"]), c[1:2], n_dec, out, nh, nkv, hd, ps, scale,
+                            window, SPLIT_KEYS)
+    if n_tiles:
+        ops.attn_prefill_mma(qkv, out, kc, vc, i32(q_start), i32(lens_q), i32(lens_kv), indptr, pages, i32(plan["tiles"]),
+                             c[2:3], n_tiles, nh, nkv, hd, ps, scale, window)
+    want = torch.zeros(T, nh, hd, dtype=torch.float64)
+    for t in range(T):
+        s = tseq[t]
+        want[t] = plain_attention(qkv[t, : nh * hd].view(nh, hd).cpu(), K[s], V[s], pos[t], scale, window)
+    return out.view(T, nh, hd).cpu().double(), want
+
+
+@pytest.mark.parametrize("hd,nh,nkv,ps,window", [(64, 32, 8, 16, None), (16, 4, 2, 16, None), (32, 3, 1, 8, None),
+                                                  (128, 8, 1, 32, None), (48, 6, 3, 4, 300), (80, 5, 5, 16, None),
+                                                  (256, 2, 1, 16, None), (112, 34, 2, 5, None), (64, 4, 4, 64, 17)])
+def test_mma_attention_mixed_batch(ops, hd, nh, nkv, ps, window):
+    """Single tokens at short, page-edge and long contexts (several splits) beside portions that
+    start in the middle of a request, span several 64-query tiles and end on odd lengths."""
+    lens_q = [1, 1, 1, 1, 70, 2, 130, 1, 64]
+    lens_kv = [1, 2 * ps, 2 * ps + 1, 777, 70, 259, 400, 256, 64]
+    got, want = run_mma_attention(ops, lens_q, lens_kv, nh, nkv, hd, ps, window, seed=hd + nh)
+    assert not torch.isnan(got).any()
+    torch.testing.assert_close(got, want, rtol=1.6e-2, atol=1.2e-2)
+
+
+def test_mma_attention_finds_one_far_key(ops):
+    """One key among 1,500 stands out for one query head of a single-token request; and the same
+    for the last query of a long portion.  The output must be that key's value."""
+    hd, nh, nkv, ps, L = 64, 8, 2, 16, 1500
+    for target in (0, 255, 256, 257, 1023, 1499):
+        for lens_q in ([1], [200]):
+            kc, vc, indptr, pages, K, V = make_paged(torch.bfloat16, 1, [L], nkv, hd, ps, 100, seed=target)
+            from types import SimpleNamespace
+            from tokasaurus_b200.parts.attention import SPLIT_KEYS, plan_attention
+            n = lens_q[0]
+            plan = plan_attention(SimpleNamespace(seq_q_len=np.asarray(lens_q, dtype=np.int32),
+                                                  seq_kv_len=np.asarray([L], dtype=np.int32)), None)
+            qkv = torch.zeros(n, (nh + 2 * nkv) * hd, dtype=torch.bfloat16)
+            direction = K[0][target, 1].float()
+            qkv[n - 1, 6 * hd:7 * hd] = (direction / direction.norm() * 60).to(torch.bfloat16)  # head 6 reads kv head 1
+            out = torch.zeros(n, nh * hd, dtype=torch.bfloat16, device=DEV)
+            c = i32(plan["counts"])
+            if n == 1:
+                ops.attn_decode_mma(qkv.to(DEV), kc, vc, i32([0]), i32([L]), indptr, pages, i32(plan["items"]), c[0:1],
+                                    int(plan["counts"][0]), i32(plan["dec_seqs"]), i32(plan["dec_item_start"]), c[1:2], 1,
+                                    out, nh, nkv, hd, ps, 1.0, None, SPLIT_KEYS)
+            else:
+                ops.attn_prefill_mma(qkv.to(DEV), out, kc, vc, i32([0]), i32(lens_q), i32([L]), indptr, pages,
+                                     i32(plan["tiles"]), c[2:3], int(plan["counts"][2]), nh, nkv, hd, ps, 1.0, None)
+            got = out[n - 1].view(nh, hd)[6].cpu().double()
+            assert (got - V[0][target, 1].double()).abs().max() < 0.06, (target, n)
+
+
+def test_mma_attention_never_reads_what_a_page_held_before(ops):
+    """Slots of the last page beyond the request's length hold NaN: nothing of them may show."""
+    got, want = run_mma_attention(ops, [1, 37], [100, 37], 8, 2, 64, 16, None, seed=3, fill=float("nan"))
+    assert not torch.isnan(got).any()
+    torch.testing.assert_close(got, want, rtol=1.6e-2, atol=1.2e-2)

@@ -1,0 +1,491 @@
+// bfloat16 attention over the paged cache on the tensor cores (mma.sync m16n8k16, float32
+// accumulation; scores, softmax and the running rescale are float32).
+//
+//   attn_decode_mma:  one query token per request, keys split into chunks of `split_keys`
+//                     (work items built on the host), partial results merged by attn_decode_merge.
+//                     The 16 rows of the MMA tile are the query heads that share one key/value
+//                     head, so every key and value is read once for the whole group.
+//   attn_prefill_mma: portions of prompts; a block owns 64 consecutive query tokens of one head
+//                     (16 per warp) and walks the keys they may see.
+//
+// Compile with -DTKB_HD=<head size> (multiple of 16, at most 256).
+//
+// Keys and values reach shared memory with 16-byte cp.async copies, page by page through the
+// request's block table, double buffered; rows outside the request's keys are zero-filled, so
+// nothing that an earlier owner of a page left behind can reach a sum.  Shared-memory rows are padded
+// by 16 bytes, which keeps ldmatrix free of bank conflicts for every head size that is a
+// multiple of 16.
+#include "common.cuh"
+#include <float.h>
+
+#ifndef TKB_HD
+#error "compile with -DTKB_HD=<head size>"
+#endif
+static_assert(TKB_HD % 16 == 0 && TKB_HD >= 16 && TKB_HD <= 256, "head size must be a multiple of 16 up to 256");
+
+using namespace tkb;
+typedef __nv_bfloat16 bf16;
+
+namespace {
+
+constexpr int HD = TKB_HD;
+constexpr int KT = 64;                // keys per shared-memory tile
+constexpr int ROWB = HD * 2 + 16;     // bytes per padded row
+constexpr int CPR = HD / 8;           // 16-byte chunks per row
+constexpr int TILE_B = KT * ROWB;     // bytes of one K or V tile
+constexpr int STAGE_B = 2 * TILE_B;   // K tile then V tile
+constexpr int SMEM_B = 2 * STAGE_B;   // two stages
+constexpr int KSTEPS = HD / 16;       // k-steps of Q.K^T
+constexpr int DTILES = HD / 8;        // n-tiles of P.V
+constexpr float NEG_BIG = -1.0e30f;   // finite stand-in for -inf in running maxima
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool valid) {
+  const int n = valid ? 16 : 0;  // src-size 0: the 16 bytes are zero-filled
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(n));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3, uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3, uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// Copy keys [key_base, key_base + KT) of one kv head into a stage; keys outside [key_lo, key_hi) become zero.
+__device__ __forceinline__ void load_kv_tile(unsigned char* stage, const bf16* __restrict__ kcache,
+                                             const bf16* __restrict__ vcache, const int* __restrict__ table, int kvh,
+                                             int nkv, int ps, int key_base, int key_lo, int key_hi, int tid,
+                                             int nthreads) {
+  const uint32_t sk = smem_u32(stage), sv = sk + TILE_B;
+  for (int idx = tid; idx < KT * CPR; idx += nthreads) {
+    const int r = idx / CPR, c = idx - r * CPR;
+    const int key = key_base + r;
+    const bool valid = key >= key_lo && key < key_hi;
+    size_t off = 0;
+    if (valid) {
+      const int page = table[key / ps];
+      off = (((size_t)page * nkv + kvh) * ps + (key % ps)) * HD + c * 8;
+    }
+    const uint32_t d = r * ROWB + c * 16;
+    cp_async16(sk + d, kcache + off, valid);
+    cp_async16(sv + d, vcache + off, valid);
+  }
+}
+
+// S[16 x 16 keys] = Q . K^T for the 16 key rows starting at key_row of the K tile.  s[nt][4], nt = 0, 1.
+__device__ __forceinline__ void qk_16keys(float (&s)[2][4], const uint32_t (&qf)[KSTEPS][4], uint32_t k_tile,
+                                          int key_row, int lane) {
+#pragma unroll
+  for (int nt = 0; nt < 2; nt++)
+#pragma unroll
+    for (int i = 0; i < 4; i++) s[nt][i] = 0.f;
+  const int row = key_row + (lane & 7) + ((lane >> 4) << 3);
+  const int chunk_sel = (lane >> 3) & 1;
+#pragma unroll
+  for (int ks = 0; ks < KSTEPS; ks++) {
+    uint32_t b0, b1, b2, b3;
+    ldmatrix_x4(b0, b1, b2, b3, k_tile + row * ROWB + (ks * 2 + chunk_sel) * 16);
+    mma_bf16(s[0], qf[ks], b0, b1);
+    mma_bf16(s[1], qf[ks], b2, b3);
+  }
+}
+
+// O[16 x HD] += P[16 x 16 keys] . V for the 16 key rows starting at key_row of the V tile.
+__device__ __forceinline__ void pv_16keys(float (&o)[DTILES][4], const uint32_t (&pf)[4], uint32_t v_tile, int key_row,
+                                          int lane) {
+  const int row = key_row + (lane & 7) + (((lane >> 3) & 1) << 3);
+  const int chunk_sel = lane >> 4;
+#pragma unroll
+  for (int dt = 0; dt < DTILES; dt += 2) {
+    uint32_t b0, b1, b2, b3;
+    ldmatrix_x4_trans(b0, b1, b2, b3, v_tile + row * ROWB + (dt + chunk_sel) * 16);
+    mma_bf16(o[dt], pf, b0, b1);
+    mma_bf16(o[dt + 1], pf, b2, b3);
+  }
+}
+
+// Online softmax over a 16-row x 16-key block held as s[2][4] (rows lane/4 and lane/4 + 8).
+// lim_lo/lim_hi: per-row inclusive key limits; key0: key index of the block's first column.
+__device__ __forceinline__ void softmax_16keys(float (&s)[2][4], float (&m)[2], float (&l)[2], float (&alpha)[2],
+                                               uint32_t (&pf)[4], const int (&lim_lo)[2], const int (&lim_hi)[2],
+                                               int key0, float scale_log2, int lane) {
+  const int c0 = key0 + (lane & 3) * 2;
+#pragma unroll
+  for (int h = 0; h < 2; h++) {  // h: row half (rows r and r + 8)
+    float mx = NEG_BIG;
+#pragma unroll
+    for (int nt = 0; nt < 2; nt++)
+#pragma unroll
+      for (int e = 0; e < 2; e++) {
+        const int key = c0 + nt * 8 + e;
+        float v = s[nt][h * 2 + e] * scale_log2;
+        if (key < lim_lo[h] || key > lim_hi[h]) v = -INFINITY;
+        s[nt][h * 2 + e] = v;
+        mx = fmaxf(mx, v);
+      }
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+    const float m_new = fmaxf(m[h], mx);
+    alpha[h] = exp2f(m[h] - m_new);
+    m[h] = m_new;
+    float sum = 0.f;
+#pragma unroll
+    for (int nt = 0; nt < 2; nt++)
+#pragma unroll
+      for (int e = 0; e < 2; e++) {
+        const float p = exp2f(s[nt][h * 2 + e] - m_new);
+        s[nt][h * 2 + e] = p;
+        sum += p;
+      }
+    l[h] = l[h] * alpha[h] + sum;  // per-thread partial; the four threads of a row are summed at the end
+  }
+  pf[0] = pack_bf16(s[0][0], s[0][1]);
+  pf[1] = pack_bf16(s[0][2], s[0][3]);
+  pf[2] = pack_bf16(s[1][0], s[1][1]);
+  pf[3] = pack_bf16(s[1][2], s[1][3]);
+}
+
+// ------------------------------------------------------------------------------------------------
+// Decode: blockIdx.x = work item (request row, split), blockIdx.y = kv head * head_tiles + head tile.
+__global__ void __launch_bounds__(128)
+attn_decode_mma_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restrict__ kcache,
+                       const bf16* __restrict__ vcache, const int* __restrict__ seq_q_start,
+                       const int* __restrict__ seq_kv_len, const int* __restrict__ page_indptr,
+                       const int* __restrict__ page_ids, const int* __restrict__ items,
+                       const int* __restrict__ n_items_ptr, float* __restrict__ part_o, float* __restrict__ part_ml,
+                       int nh, int nkv, int ps, float scale_log2, int window, int split_keys, int head_tiles) {
+  extern __shared__ __align__(128) unsigned char smem[];
+  const int item = blockIdx.x;
+  if (item >= *n_items_ptr) return;
+  const int s = items[2 * item], split = items[2 * item + 1];
+  const int kvh = blockIdx.y / head_tiles, ht = blockIdx.y - kvh * head_tiles;
+  const int group = nh / nkv;
+  const int g0 = ht * 16;
+  const int gn = min(16, group - g0);  // live rows of the MMA tile
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int kv_len = seq_kv_len[s];
+  const int p = kv_len - 1;
+  int lo = 0;
+  if (window > 0 && p - window + 1 > 0) lo = p - window + 1;
+  const int k_begin = lo + split * split_keys;
+  const int k_end = min(kv_len, k_begin + split_keys);
+  const int* table = page_ids + page_indptr[s];
+  const int t = seq_q_start[s];
+  const bf16* qrow = q + (size_t)t * q_stride + (size_t)(kvh * group + g0) * HD;
+
+  // Q fragments: row r of the tile is query head g0 + r; rows >= gn are zero.
+  uint32_t qf[KSTEPS][4];
+  {
+    const int r = lane >> 2, cq = (lane & 3) * 2;
+#pragma unroll
+    for (int ks = 0; ks < KSTEPS; ks++) {
+#pragma unroll
+      for (int i = 0; i < 4; i++) {
+        const int row = r + (i & 1) * 8, col = ks * 16 + cq + (i >> 1) * 8;
+        qf[ks][i] = row < gn ? *reinterpret_cast<const uint32_t*>(qrow + (size_t)row * HD + col) : 0u;
+      }
+    }
+  }
+  float o[DTILES][4];
+#pragma unroll
+  for (int dt = 0; dt < DTILES; dt++)
+#pragma unroll
+    for (int i = 0; i < 4; i++) o[dt][i] = 0.f;
+  float m[2] = {NEG_BIG, NEG_BIG}, l[2] = {0.f, 0.f};
+  const int lim_lo[2] = {k_begin, k_begin}, lim_hi[2] = {k_end - 1, k_end - 1};
+
+  const int n_tiles = (k_end - k_begin + KT - 1) / KT;
+  if (n_tiles > 0) load_kv_tile(smem, kcache, vcache, table, kvh, nkv, ps, k_begin, k_begin, k_end, tid, 128);
+  cp_async_commit();
+  for (int it = 0; it < n_tiles; it++) {
+    unsigned char* cur = smem + (it & 1) * STAGE_B;
+    if (it + 1 < n_tiles)
+      load_kv_tile(smem + ((it + 1) & 1) * STAGE_B, kcache, vcache, table, kvh, nkv, ps, k_begin + (it + 1) * KT,
+                   k_begin, k_end, tid, 128);
+    cp_async_commit();
+    cp_async_wait<1>();
+    __syncthreads();
+    const int key0 = k_begin + it * KT + warp * 16;
+    if (key0 < k_end) {  // warp-uniform: this warp's 16 keys hold at least one live key
+      float sc[2][4], alpha[2];
+      uint32_t pf[4];
+      qk_16keys(sc, qf, smem_u32(cur), warp * 16, lane);
+      softmax_16keys(sc, m, l, alpha, pf, lim_lo, lim_hi, key0, scale_log2, lane);
+#pragma unroll
+      for (int dt = 0; dt < DTILES; dt++) {
+        o[dt][0] *= alpha[0];
+        o[dt][1] *= alpha[0];
+        o[dt][2] *= alpha[1];
+        o[dt][3] *= alpha[1];
+      }
+      pv_16keys(o, pf, smem_u32(cur) + TILE_B, warp * 16, lane);
+    }
+    __syncthreads();
+  }
+  cp_async_wait<0>();
+  __syncthreads();
+  // row sums over the four threads of a row
+#pragma unroll
+  for (int h = 0; h < 2; h++) {
+    l[h] += __shfl_xor_sync(0xffffffffu, l[h], 1);
+    l[h] += __shfl_xor_sync(0xffffffffu, l[h], 2);
+  }
+  // combine the four warps through shared memory: so[warp][row][HD], sml[warp][row][2]
+  float* so = reinterpret_cast<float*>(smem);
+  float* sml = so + 4 * 16 * HD;
+  {
+    const int r = lane >> 2, cq = (lane & 3) * 2;
+#pragma unroll
+    for (int dt = 0; dt < DTILES; dt++) {
+      float* b = so + ((warp * 16 + r) * HD) + dt * 8 + cq;
+      b[0] = o[dt][0];
+      b[1] = o[dt][1];
+      b[8 * HD] = o[dt][2];
+      b[8 * HD + 1] = o[dt][3];
+    }
+    if ((lane & 3) == 0) {
+      sml[(warp * 16 + r) * 2] = m[0];
+      sml[(warp * 16 + r) * 2 + 1] = l[0];
+      sml[(warp * 16 + r + 8) * 2] = m[1];
+      sml[(warp * 16 + r + 8) * 2 + 1] = l[1];
+    }
+  }
+  __syncthreads();
+  for (int idx = tid; idx < gn * HD; idx += 128) {
+    const int r = idx / HD, d = idx - r * HD;
+    float mm = NEG_BIG;
+#pragma unroll
+    for (int w = 0; w < 4; w++) mm = fmaxf(mm, sml[(w * 16 + r) * 2]);
+    float acc = 0.f, ll = 0.f;
+#pragma unroll
+    for (int w = 0; w < 4; w++) {
+      const float f = exp2f(sml[(w * 16 + r) * 2] - mm);
+      acc += f * so[(w * 16 + r) * HD + d];
+      ll += f * sml[(w * 16 + r) * 2 + 1];
+    }
+    const int head = kvh * group + g0 + r;
+    part_o[((size_t)item * nh + head) * HD + d] = acc;
+    if (d == 0) {
+      part_ml[((size_t)item * nh + head) * 2] = mm;
+      part_ml[((size_t)item * nh + head) * 2 + 1] = ll;
+    }
+  }
+}
+
+// Merge the splits of each decode request: grid (request entry, head), HD threads (rounded up to 32).
+__global__ void attn_decode_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                         const int* __restrict__ dec_seqs, const int* __restrict__ dec_item_start,
+                                         const int* __restrict__ n_dec_ptr, const int* __restrict__ seq_q_start,
+                                         bf16* __restrict__ out, int out_stride, int nh) {
+  const int e = blockIdx.x;
+  if (e >= *n_dec_ptr) return;
+  const int head = blockIdx.y;
+  const int s = dec_seqs[e];
+  const int i0 = dec_item_start[e], i1 = dec_item_start[e + 1];
+  float mm = NEG_BIG;
+  for (int i = i0; i < i1; i++) mm = fmaxf(mm, part_ml[((size_t)i * nh + head) * 2]);
+  float ll = 0.f;
+  for (int i = i0; i < i1; i++)
+    ll += exp2f(part_ml[((size_t)i * nh + head) * 2] - mm) * part_ml[((size_t)i * nh + head) * 2 + 1];
+  const float inv = 1.f / ll;
+  const int t = seq_q_start[s];
+  for (int d = threadIdx.x; d < HD; d += blockDim.x) {
+    float acc = 0.f;
+    for (int i = i0; i < i1; i++)
+      acc += exp2f(part_ml[((size_t)i * nh + head) * 2] - mm) * part_o[((size_t)i * nh + head) * HD + d];
+    out[(size_t)t * out_stride + (size_t)head * HD + d] = __float2bfloat16_rn(acc * inv);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// Prefill: blockIdx.x = tile (request row, first query of the tile within the portion), blockIdx.y = head.
+__global__ void __launch_bounds__(128)
+attn_prefill_mma_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out, int out_stride,
+                        const bf16* __restrict__ kcache, const bf16* __restrict__ vcache,
+                        const int* __restrict__ seq_q_start, const int* __restrict__ seq_q_len,
+                        const int* __restrict__ seq_kv_len, const int* __restrict__ page_indptr,
+                        const int* __restrict__ page_ids, const int* __restrict__ tiles,
+                        const int* __restrict__ n_tiles_ptr, int nh, int nkv, int ps, float scale_log2, int window) {
+  extern __shared__ __align__(128) unsigned char smem[];
+  if ((int)blockIdx.x >= *n_tiles_ptr) return;
+  const int s = tiles[2 * blockIdx.x], qt0 = tiles[2 * blockIdx.x + 1];
+  const int head = blockIdx.y;
+  const int kvh = head / (nh / nkv);
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int q_len = seq_q_len[s], kv_len = seq_kv_len[s];
+  const int rows_live = min(64, q_len - qt0);
+  const int pos0 = kv_len - q_len + qt0;  // position of the tile's first query
+  const int pos_last = pos0 + rows_live - 1;
+  int k_begin = 0;
+  if (window > 0 && pos0 - window + 1 > 0) k_begin = pos0 - window + 1;
+  const int k_end = pos_last + 1;
+  const int* table = page_ids + page_indptr[s];
+  const int t0 = seq_q_start[s] + qt0;
+
+  // this warp's rows: r and r + 8 of its 16
+  const int r = lane >> 2, cq = (lane & 3) * 2;
+  const int row_a = warp * 16 + r, row_b = row_a + 8;
+  uint32_t qf[KSTEPS][4];
+#pragma unroll
+  for (int ks = 0; ks < KSTEPS; ks++) {
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+      const int row = (i & 1) ? row_b : row_a, col = ks * 16 + cq + (i >> 1) * 8;
+      qf[ks][i] = row < rows_live
+                      ? *reinterpret_cast<const uint32_t*>(q + (size_t)(t0 + row) * q_stride + (size_t)head * HD + col)
+                      : 0u;
+    }
+  }
+  float o[DTILES][4];
+#pragma unroll
+  for (int dt = 0; dt < DTILES; dt++)
+#pragma unroll
+    for (int i = 0; i < 4; i++) o[dt][i] = 0.f;
+  float m[2] = {NEG_BIG, NEG_BIG}, l[2] = {0.f, 0.f};
+  int lim_lo[2], lim_hi[2];
+  lim_hi[0] = pos0 + row_a;
+  lim_hi[1] = pos0 + row_b;
+  lim_lo[0] = window > 0 ? lim_hi[0] - window + 1 : 0;
+  lim_lo[1] = window > 0 ? lim_hi[1] - window + 1 : 0;
+  // what this warp's 16 rows can see at all
+  const int warp_hi = pos0 + warp * 16 + 15;
+  const int warp_lo = window > 0 ? pos0 + warp * 16 - window + 1 : 0;
+
+  const int n_tiles = (k_end - k_begin + KT - 1) / KT;
+  load_kv_tile(smem, kcache, vcache, table, kvh, nkv, ps, k_begin, k_begin, k_end, tid, 128);
+  cp_async_commit();
+  for (int it = 0; it < n_tiles; it++) {
+    unsigned char* cur = smem + (it & 1) * STAGE_B;
+    if (it + 1 < n_tiles)
+      load_kv_tile(smem + ((it + 1) & 1) * STAGE_B, kcache, vcache, table, kvh, nkv, ps, k_begin + (it + 1) * KT,
+                   k_begin, k_end, tid, 128);
+    cp_async_commit();
+    cp_async_wait<1>();
+    __syncthreads();
+    const int tile_key0 = k_begin + it * KT;
+    if (warp * 16 < rows_live && tile_key0 <= warp_hi && tile_key0 + KT - 1 >= warp_lo) {
+#pragma unroll
+      for (int kb = 0; kb < KT / 16; kb++) {
+        const int key0 = tile_key0 + kb * 16;
+        if (key0 > warp_hi || key0 >= k_end || key0 + 15 < warp_lo) continue;  // warp-uniform
+        float sc[2][4], alpha[2];
+        uint32_t pf[4];
+        qk_16keys(sc, qf, smem_u32(cur), kb * 16, lane);
+        softmax_16keys(sc, m, l, alpha, pf, lim_lo, lim_hi, key0, scale_log2, lane);
+#pragma unroll
+        for (int dt = 0; dt < DTILES; dt++) {
+          o[dt][0] *= alpha[0];
+          o[dt][1] *= alpha[0];
+          o[dt][2] *= alpha[1];
+          o[dt][3] *= alpha[1];
+        }
+        pv_16keys(o, pf, smem_u32(cur) + TILE_B, kb * 16, lane);
+      }
+    }
+    __syncthreads();
+  }
+  cp_async_wait<0>();
+#pragma unroll
+  for (int h = 0; h < 2; h++) {
+    l[h] += __shfl_xor_sync(0xffffffffu, l[h], 1);
+    l[h] += __shfl_xor_sync(0xffffffffu, l[h], 2);
+  }
+  const float inv_a = 1.f / l[0], inv_b = 1.f / l[1];
+#pragma unroll
+  for (int dt = 0; dt < DTILES; dt++) {
+    const int col = dt * 8 + cq;
+    if (row_a < rows_live)
+      *reinterpret_cast<uint32_t*>(out + (size_t)(t0 + row_a) * out_stride + (size_t)head * HD + col) =
+          pack_bf16(o[dt][0] * inv_a, o[dt][1] * inv_a);
+    if (row_b < rows_live)
+      *reinterpret_cast<uint32_t*>(out + (size_t)(t0 + row_b) * out_stride + (size_t)head * HD + col) =
+          pack_bf16(o[dt][2] * inv_b, o[dt][3] * inv_b);
+  }
+}
+
+static bool g_attr_set = false;
+static int ensure_smem_attr() {
+  if (g_attr_set) return 0;
+  cudaError_t e = cudaSuccess;
+  if (SMEM_B > 48 * 1024) {
+    e = cudaFuncSetAttribute(attn_decode_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_B);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(attn_prefill_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_B);
+  }
+  if (e != cudaSuccess) return (int)e;
+  g_attr_set = true;
+  return 0;
+}
+
+}  // namespace
+
+// Scratch a decode launch needs for `items_cap` work items: floats of part_o and of part_ml.
+TKB_EXPORT long long tkb_attn_decode_scratch_floats(int items_cap, int nh) {
+  return (long long)items_cap * nh * (HD + 2);
+}
+
+// items: int32 [n_items_cap * 2] (request row, split); n_items_ptr: device int32 with the live count.
+// The grid is sized by items_cap, so a captured graph serves any count up to it.
+TKB_EXPORT int tkb_attn_decode_mma_bf16(const void* q, int q_stride, const void* kcache, const void* vcache,
+                                        const int* seq_q_start, const int* seq_kv_len, const int* page_indptr,
+                                        const int* page_ids, const int* items, const int* n_items_ptr, int items_cap,
+                                        float* part_o, float* part_ml, int nh, int nkv, int ps, float scale, int window,
+                                        int split_keys, void* st) {
+  if (items_cap <= 0) return 0;
+  if (nkv <= 0 || nh % nkv != 0 || ps <= 0 || split_keys <= 0) return -2;
+  int rc = ensure_smem_attr();
+  if (rc) return rc;
+  const int group = nh / nkv;
+  const int head_tiles = (group + 15) / 16;
+  if ((long long)nkv * head_tiles > 65535) return -3;
+  dim3 grid(items_cap, nkv * head_tiles);
+  attn_decode_mma_kernel<<<grid, 128, SMEM_B, (cudaStream_t)st>>>(
+      (const bf16*)q, q_stride, (const bf16*)kcache, (const bf16*)vcache, seq_q_start, seq_kv_len, page_indptr, page_ids,
+      items, n_items_ptr, part_o, part_ml, nh, nkv, ps, scale * 1.4426950408889634f, window, split_keys, head_tiles);
+  return launch_status();
+}
+
+TKB_EXPORT int tkb_attn_decode_merge_bf16(const float* part_o, const float* part_ml, const int* dec_seqs,
+                                          const int* dec_item_start, const int* n_dec_ptr, int dec_cap,
+                                          const int* seq_q_start, void* out, int out_stride, int nh, void* st) {
+  if (dec_cap <= 0) return 0;
+  if (nh > 65535) return -3;
+  dim3 grid(dec_cap, nh);
+  const int threads = HD >= 128 ? 128 : (HD >= 64 ? 64 : 32);
+  attn_decode_merge_kernel<<<grid, threads, 0, (cudaStream_t)st>>>(part_o, part_ml, dec_seqs, dec_item_start,
+                                                                  n_dec_ptr, seq_q_start, (bf16*)out, out_stride, nh);
+  return launch_status();
+}
+
+TKB_EXPORT int tkb_attn_prefill_mma_bf16(const void* q, int q_stride, void* out, int out_stride, const void* kcache,
+                                         const void* vcache, const int* seq_q_start, const int* seq_q_len,
+                                         const int* seq_kv_len, const int* page_indptr, const int* page_ids,
+                                         const int* tiles, const int* n_tiles_ptr, int tiles_cap, int nh, int nkv, int ps,
+                                         float scale, int window, void* st) {
+  if (tiles_cap <= 0) return 0;
+  if (nkv <= 0 || nh % nkv != 0 || ps <= 0) return -2;
+  if (nh > 65535) return -3;
+  int rc = ensure_smem_attr();
+  if (rc) return rc;
+  dim3 grid(tiles_cap, nh);
+  attn_prefill_mma_kernel<<<grid, 128, SMEM_B, (cudaStream_t)st>>>(
+      (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)kcache, (const bf16*)vcache, seq_q_start, seq_q_len,
+      seq_kv_len, page_indptr, page_ids, tiles, n_tiles_ptr, nh, nkv, ps, scale * 1.4426950408889634f, window);
+  return launch_status();
+}
+TKB_EXPORT int tkb_attn_mma_head_dim() { return HD; }

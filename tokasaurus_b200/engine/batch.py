@@ -64,7 +64,7 @@ class StepContext:
     """Everything a part may look at while it runs one step."""
 
     def __init__(self, host: HostBatch, cache_manager, device: torch.device, stager: "Stager",
-                 extra: dict[str, np.ndarray] | None = None):
+                 extra: dict[str, np.ndarray] | None = None, plans: dict | None = None):
         self.host = host
         self.cache_manager = cache_manager
         self.device = device
@@ -79,8 +79,15 @@ class StepContext:
         for ip, pg in zip(host.table_indptr, host.table_pages):
             arrays += [ip, pg]
         extra = extra or {}
-        views = stager.upload(arrays + list(extra.values()))
+        plans = plans or {}
+        flat = [(key, name, arr) for key, d in plans.items() for name, arr in d.items()]
+        views = stager.upload(arrays + list(extra.values()) + [a for _, _, a in flat])
         self.extra = dict(zip(extra.keys(), views[len(arrays):]))
+        self.plans: dict = {}
+        self.plan_caps: dict | None = None
+        self.host_plans = plans
+        for (key, name, _), v in zip(flat, views[len(arrays) + len(extra):]):
+            self.plans.setdefault(key, {})[name] = v
         (self.token_ids, self.positions, self.token_seq, self.seq_slot, self.seq_q_start, self.seq_q_len,
          self.seq_kv_len, self.logit_rows) = views[:8]
         self.tables = [GroupTables(views[8 + 2 * g], views[9 + 2 * g]) for g in range(len(host.table_indptr))]

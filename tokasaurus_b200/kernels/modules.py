@@ -8,7 +8,7 @@ def common_modules() -> list[tuple[str, dict | None]]:
 
 
 def head_dim_modules(head_dim: int) -> list[tuple[str, dict | None]]:
-    return [("attention_simt.cu", {"TKB_HD": head_dim})]
+    return [("attention_simt.cu", {"TKB_HD": head_dim}), ("attention_mma.cu", {"TKB_HD": head_dim})]
 
 
 def all_modules(head_dims) -> list[tuple[str, dict | None]]:

@@ -214,6 +214,58 @@ def attn_paged(q: torch.Tensor, q_stride: int, out: torch.Tensor, kcache: torch.
              c_int(n_kv_heads), c_int(page_size), c_float(scale), c_int(window or 0), _stream()), "attn_paged")
 
 
+def attn_decode_mma(qkv: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, seq_q_start: torch.Tensor,
+                    seq_kv_len: torch.Tensor, page_indptr: torch.Tensor, page_ids: torch.Tensor, items: torch.Tensor,
+                    n_items: torch.Tensor, items_cap: int, dec_seqs: torch.Tensor, dec_item_start: torch.Tensor,
+                    n_dec: torch.Tensor, dec_cap: int, out: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int,
+                    page_size: int, scale: float, window: int | None, split_keys: int) -> None:
+    """bfloat16 split-key attention for requests that bring one token: ``items`` are (request row,
+    split) pairs of ``split_keys`` keys each, computed into float32 partial results and merged into
+    ``out`` [T, n_heads*head_dim] at each request's token row.  ``n_items``/``n_dec`` are device
+    counters; the launch grids are sized by ``items_cap``/``dec_cap``."""
+    _need_cuda(qkv, kcache, vcache, seq_q_start, seq_kv_len, page_indptr, page_ids, items, n_items, dec_seqs,
+               dec_item_start, n_dec, out)
+    check_head_dim(head_dim)
+    _need(qkv.dtype == torch.bfloat16 and kcache.dtype == torch.bfloat16 and out.dtype == torch.bfloat16,
+          "attn_decode_mma: bfloat16 only")
+    _need(tuple(kcache.shape[1:]) == (n_kv_heads, page_size, head_dim), "attn_decode_mma: cache layout")
+    _need(out.is_contiguous() and out.shape[1] == n_heads * head_dim, "attn_decode_mma: out")
+    _need(items.numel() >= 2 * items_cap and dec_item_start.numel() >= dec_cap + 1, "attn_decode_mma: plan arrays")
+    lib = _libs.get("attention_mma.cu", TKB_HD=head_dim)
+    part_o = torch.empty((items_cap, n_heads, head_dim), dtype=torch.float32, device=qkv.device)
+    part_ml = torch.empty((items_cap, n_heads, 2), dtype=torch.float32, device=qkv.device)
+    _check(_fn(lib, "tkb_attn_decode_mma_bf16")(
+        _ptr(qkv), c_int(qkv.shape[1]), _ptr(kcache), _ptr(vcache), _ptr(seq_q_start), _ptr(seq_kv_len),
+        _ptr(page_indptr), _ptr(page_ids), _ptr(items), _ptr(n_items), c_int(items_cap), _ptr(part_o), _ptr(part_ml),
+        c_int(n_heads), c_int(n_kv_heads), c_int(page_size), c_float(scale), c_int(window or 0), c_int(split_keys),
+        _stream()), "attn_decode_mma")
+    _check(_fn(lib, "tkb_attn_decode_merge_bf16")(
+        _ptr(part_o), _ptr(part_ml), _ptr(dec_seqs), _ptr(dec_item_start), _ptr(n_dec), c_int(dec_cap),
+        _ptr(seq_q_start), _ptr(out), c_int(out.shape[1]), c_int(n_heads), _stream()), "attn_decode_merge")
+
+
+def attn_prefill_mma(qkv: torch.Tensor, out: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor,
+                     seq_q_start: torch.Tensor, seq_q_len: torch.Tensor, seq_kv_len: torch.Tensor,
+                     page_indptr: torch.Tensor, page_ids: torch.Tensor, tiles: torch.Tensor, n_tiles: torch.Tensor,
+                     tiles_cap: int, n_heads: int, n_kv_heads: int, head_dim: int, page_size: int, scale: float,
+                     window: int | None) -> None:
+    """bfloat16 causal attention for prompt portions: ``tiles`` are (request row, first query of a
+    64-query tile within the portion) pairs; results go to ``out`` [T, n_heads*head_dim] at the token rows."""
+    _need_cuda(qkv, out, kcache, vcache, seq_q_start, seq_q_len, seq_kv_len, page_indptr, page_ids, tiles, n_tiles)
+    check_head_dim(head_dim)
+    _need(qkv.dtype == torch.bfloat16 and kcache.dtype == torch.bfloat16 and out.dtype == torch.bfloat16,
+          "attn_prefill_mma: bfloat16 only")
+    _need(tuple(kcache.shape[1:]) == (n_kv_heads, page_size, head_dim), "attn_prefill_mma: cache layout")
+    _need(out.is_contiguous() and out.shape[1] == n_heads * head_dim, "attn_prefill_mma: out")
+    _need(tiles.numel() >= 2 * tiles_cap, "attn_prefill_mma: plan arrays")
+    lib = _libs.get("attention_mma.cu", TKB_HD=head_dim)
+    _check(_fn(lib, "tkb_attn_prefill_mma_bf16")(
+        _ptr(qkv), c_int(qkv.shape[1]), _ptr(out), c_int(out.shape[1]), _ptr(kcache), _ptr(vcache), _ptr(seq_q_start),
+        _ptr(seq_q_len), _ptr(seq_kv_len), _ptr(page_indptr), _ptr(page_ids), _ptr(tiles), _ptr(n_tiles),
+        c_int(tiles_cap), c_int(n_heads), c_int(n_kv_heads), c_int(page_size), c_float(scale), c_int(window or 0),
+        _stream()), "attn_prefill_mma")
+
+
 def sample(logits: torch.Tensor, temperature: torch.Tensor | None, stream_key: torch.Tensor | None,
            sample_pos: torch.Tensor | None, row_slot: torch.Tensor | None, out_ids: torch.Tensor,
            out_logprob: torch.Tensor | None, last_token: torch.Tensor | None) -> None:

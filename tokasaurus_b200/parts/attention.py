@@ -5,14 +5,57 @@ head (:239-241), rotary encoding of q and k (:243-256), append of k and v to the
 causal attention over it with scale 1/sqrt(head_dim) (tokasaurus/model/attention_utils.py:108-175),
 restriction to the wanted rows (llama.py:273-278), output projection (:280).  The three
 projection matrices are stacked into one so that one matrix product makes q|k|v.
+
+Kernels: in float32 one FP32 kernel serves every token.  In bfloat16 the requests of a step are
+split as the reference splits them into a prefill and a decode call
+(attention_utils.py:129-151): requests that bring one token go to the split-key tensor-core
+kernel, longer portions to the tiled tensor-core kernel; the host plans the work items of both
+(the reference's ``plan`` calls, llama.py:698-764).
 """
 
 from __future__ import annotations
 
+import numpy as np
 import torch
 
 from tokasaurus_b200.kernels import ops
 from tokasaurus_b200.parts.base import Mixer, PagedCacheNeed, PositionEncoding, WeightSpec
+
+SPLIT_KEYS = 256  # keys per work item of the split-key kernel; fixed, so a request's result does not depend on the batch
+QUERY_TILE = 64  # queries per block of the tiled kernel
+
+
+def plan_attention(host, window: int | None, capacity: dict | None = None) -> dict[str, np.ndarray]:
+    """Work items for one step: (request row, split) pairs for requests with one token, (request
+    row, first query) pairs for 64-query tiles of longer portions."""
+    q_len, kv_len = host.seq_q_len, host.seq_kv_len
+    items: list[int] = []
+    dec_seqs: list[int] = []
+    dec_start = [0]
+    tiles: list[int] = []
+    for s in range(q_len.shape[0]):
+        n, kv = int(q_len[s]), int(kv_len[s])
+        if n == 1:
+            span = min(kv, window) if window else kv
+            n_splits = max(1, -(-span // SPLIT_KEYS))
+            for j in range(n_splits):
+                items += [s, j]
+            dec_seqs.append(s)
+            dec_start.append(len(items) // 2)
+        elif n > 1:
+            for q0 in range(0, n, QUERY_TILE):
+                tiles += [s, q0]
+    cap = capacity or {}
+    counts = np.asarray([len(items) // 2, len(dec_seqs), len(tiles) // 2, 0], dtype=np.int32)
+
+    def padded(x, n):
+        a = np.zeros(max(n, len(x), 1), dtype=np.int32)
+        a[:len(x)] = x
+        return a
+
+    return dict(counts=counts, items=padded(items, 2 * cap.get("items", 0)),
+                dec_seqs=padded(dec_seqs, cap.get("dec", 0)), dec_item_start=padded(dec_start, cap.get("dec", 0) + 1),
+                tiles=padded(tiles, 2 * cap.get("tiles", 0)))
 
 
 class PagedAttention(Mixer):
@@ -33,6 +76,7 @@ class PagedAttention(Mixer):
         self.w_qkv: torch.Tensor | None = None
         self.w_o: torch.Tensor | None = None
         self.inv_freq: torch.Tensor | None = None
+        self.dtype: torch.dtype | None = None
 
     # --- declarations ---
     def weight_specs(self):
@@ -54,6 +98,15 @@ class PagedAttention(Mixer):
         self.w_o = weights[o].contiguous()
         inv = self.position.inv_freq() if self.position.kind == "rotary" else None
         self.inv_freq = inv.to(rt.device) if inv is not None else None
+        self.dtype = rt.dtype
+
+    def plan_key(self):
+        return ("paged_attention", self.window)
+
+    def plan(self, host, capacity=None):
+        if self.dtype != torch.bfloat16:
+            return None
+        return self.plan_key(), plan_attention(host, self.window, capacity)
 
     # --- one step ---
     def forward(self, ctx, h: torch.Tensor, cache, out_rows=None) -> torch.Tensor:
@@ -64,8 +117,27 @@ class PagedAttention(Mixer):
         rot = self.position.rotary_dim if self.position.kind == "rotary" else 0
         ops.rope_kv_write(qkv, ctx.positions, ctx.token_seq, tables.indptr, tables.page_ids, self.inv_freq,
                           cache.k, cache.v, nh, nkv, hd, rot, cache.page_size, cache.writable, ctx.status)
-        n_rows = T if out_rows is None else out_rows.numel()
-        attn = torch.empty((n_rows, nh * hd), dtype=h.dtype, device=h.device)
-        ops.attn_paged(qkv, qkv.shape[1], attn, cache.k, cache.v, ctx.token_seq, ctx.positions, tables.indptr,
-                       tables.page_ids, out_rows, n_rows, nh, nkv, hd, cache.page_size, self.scale, self.window)
+        plan = ctx.plans.get(self.plan_key()) if h.dtype == torch.bfloat16 else None
+        if plan is None or out_rows is not None:
+            # float32, or only some rows are wanted: the FP32-pipe kernel, one warp per (row, head)
+            n_rows = T if out_rows is None else out_rows.numel()
+            attn = torch.empty((n_rows, nh * hd), dtype=h.dtype, device=h.device)
+            ops.attn_paged(qkv, qkv.shape[1], attn, cache.k, cache.v, ctx.token_seq, ctx.positions, tables.indptr,
+                           tables.page_ids, out_rows, n_rows, nh, nkv, hd, cache.page_size, self.scale, self.window)
+            return ops.linear(attn, self.w_o)
+        attn = torch.empty((T, nh * hd), dtype=h.dtype, device=h.device)
+        caps = ctx.plan_caps.get(self.plan_key()) if ctx.plan_caps else None
+        counts = ctx.host_plans[self.plan_key()]["counts"]
+        items_cap = caps["items"] if caps else int(counts[0])
+        dec_cap = caps["dec"] if caps else int(counts[1])
+        tiles_cap = caps["tiles"] if caps else int(counts[2])
+        c = plan["counts"]
+        if dec_cap:
+            ops.attn_decode_mma(qkv, cache.k, cache.v, ctx.seq_q_start, ctx.seq_kv_len, tables.indptr, tables.page_ids,
+                                plan["items"], c[0:1], items_cap, plan["dec_seqs"], plan["dec_item_start"], c[1:2],
+                                dec_cap, attn, nh, nkv, hd, cache.page_size, self.scale, self.window, SPLIT_KEYS)
+        if tiles_cap:
+            ops.attn_prefill_mma(qkv, attn, cache.k, cache.v, ctx.seq_q_start, ctx.seq_q_len, ctx.seq_kv_len,
+                                 tables.indptr, tables.page_ids, plan["tiles"], c[2:3], tiles_cap, nh, nkv, hd,
+                                 cache.page_size, self.scale, self.window)
         return ops.linear(attn, self.w_o)

@@ -85,6 +85,13 @@ class Mixer(Part):
     def cache_need(self) -> PagedCacheNeed | StateNeed | None:
         return None
 
+    def plan(self, host, capacity=None):
+        """Optional host-side work plan for this step: return ``(key, {name: int32 numpy array})`` or
+        None.  Mixers that return the same key share one plan; the arrays travel to the device with the
+        batch and are found at ``ctx.plans[key][name]``.  ``capacity`` (a dict or None) gives fixed
+        array sizes when the step will be captured in a CUDA graph."""
+        return None
+
     def forward(self, ctx: "StepContext", h: "torch.Tensor", cache, out_rows=None) -> "torch.Tensor":
         """``h`` [T, width]: normalised input rows of this step's tokens.  ``cache``: what the
         cache manager holds for this layer call (``PagedLayerCache`` or ``StateLayerCache`` or

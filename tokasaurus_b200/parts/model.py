@@ -58,6 +58,9 @@ class DecoderModel(Part):
         for part in [self.embedding, *self.blocks, self.head]:
             part.bind(weights, rt)
 
+    def mixers(self):
+        return [b.mixer for b in self.blocks]
+
     def cache_entries(self):
         """{cache entry: the need of the mixer that uses it}."""
         needs = {}
