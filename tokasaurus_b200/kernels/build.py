@@ -14,6 +14,7 @@ from __future__ import annotations
 import ctypes
 import hashlib
 import os
+import re
 import shutil
 import subprocess
 import sys
@@ -67,12 +68,21 @@ def build_dir() -> Path:
     raise KernelBuildError(f"no writable folder for compiled kernels among {[str(c) for c in cands]}")
 
 
-def _headers_text() -> bytes:
-    h = hashlib.sha256()
-    for p in sorted(CSRC.glob("*.cuh")):
-        h.update(p.name.encode())
-        h.update(p.read_bytes())
-    return h.digest()
+_INCLUDE = re.compile(r'^\s*#\s*include\s+"([^"]+)"', re.M)
+
+
+def _source_closure(src: Path) -> list[Path]:
+    """The source file and every file of this folder it includes, directly or not."""
+    seen: dict[Path, None] = {}
+    todo = [src]
+    while todo:
+        p = todo.pop()
+        if p in seen or not p.is_file():
+            continue
+        seen[p] = None
+        for name in _INCLUDE.findall(p.read_text()):
+            todo.append(CSRC / name)
+    return sorted(seen)
 
 
 def module_path(source: str, defines: dict[str, int | str] | None = None, extra_flags: tuple[str, ...] = ()) -> tuple[Path, list[str]]:
@@ -82,8 +92,9 @@ def module_path(source: str, defines: dict[str, int | str] | None = None, extra_
     defines = defines or {}
     dflags = [f"-D{k}={v}" for k, v in sorted(defines.items())]
     h = hashlib.sha256()
-    h.update(src.read_bytes())
-    h.update(_headers_text())
+    for dep in _source_closure(src):
+        h.update(dep.name.encode())
+        h.update(dep.read_bytes())
     h.update(" ".join(ARCH_FLAGS + BASE_FLAGS + dflags + list(extra_flags)).encode())
     tag = "_".join(f"{k.lower().replace('tkb_', '')}{v}" for k, v in sorted(defines.items()))
     name = f"{src.stem}{'_' + tag if tag else ''}_{h.hexdigest()[:12]}.so"
