@@ -11,6 +11,11 @@ def head_dim_modules(head_dim: int) -> list[tuple[str, dict | None]]:
     return [("attention_simt.cu", {"TKB_HD": head_dim}), ("attention_mma.cu", {"TKB_HD": head_dim})]
 
 
+def optional_modules(head_dim: int) -> list[tuple[str, dict | None]]:
+    """Built by the build check, loaded only by callers that ask for them."""
+    return [("attention_decode_static.cu", {"TKB_HD": head_dim})]
+
+
 def all_modules(head_dims) -> list[tuple[str, dict | None]]:
     mods = common_modules()
     for hd in head_dims:
