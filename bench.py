@@ -218,7 +218,11 @@ def run_ours(args) -> dict:
                 length[rid] += 1
             pos = np.asarray([length[r] for r in ids], dtype=np.int32)
             slot = np.asarray([cache.slot(r) for r in ids], dtype=np.int32)
-            logits = runner.step(entries, dict(temperature=zeros, stream_key=keys, sample_pos=pos, row_slot=slot))
+            extra = dict(temperature=zeros, stream_key=keys, sample_pos=pos, row_slot=slot)
+            if eng.graphs is not None and eng.graphs.usable(entries):
+                eng.graphs.run(entries, extra)
+                return
+            logits = runner.step(entries, extra)
             ex = runner.last_context.extra
             sampler.sample(logits, ex["temperature"], ex["stream_key"], ex["sample_pos"], ex["row_slot"], cache.last_token)
 
@@ -281,7 +285,7 @@ def run_ours(args) -> dict:
             "parallelism": "1 GPU", "layers": layers, "layers_full": full_layers, "hidden": m["H"], "heads": m["nh"],
             "kv_heads": m["nkv"], "head_dim": m["hd"], "intermediate": m["I"], "vocab": m["V"], "page_size": page_size,
             "tied_embeddings": True, "rope": "llama3 factor 32", "l2": "inputs (2.5 GB of weights) larger than L2; no flush",
-            "cuda_graphs": bool(eng.config.use_cudagraphs and getattr(runner, "graphs_enabled", False)),
+            "cuda_graphs": eng.graphs is not None,
         },
         "e2e": e2e, "gpu_launches": launches, "clocks": clock_info, "prefill": prefill, "roofline": roofline,
         "points": points,

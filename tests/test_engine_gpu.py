@@ -161,3 +161,24 @@ def test_no_cuda_no_engine(tiny_model_dirs):
 
     with pytest.raises(RuntimeError, match="no CPU execution path"):
         Engine(model=str(tiny_model_dirs[0]), device="cpu")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_cuda_graph_decode_equals_eager(tiny_model_dirs, dtype):
+    """Decode steps replayed from CUDA graphs give the tokens and log-probabilities of the eager
+    path, over batch sizes that need padding and contexts that cross pages and work-list capacities."""
+    from tokasaurus_b200 import SamplingParams
+
+    d = tiny_model_dirs[1]
+    prompts = [cuttings.random_tokens(n, 509, 5 * n) for n in (7, 30, 64, 3, 12)]
+    sp = [SamplingParams(temperature=t, seed=3) for t in (0.0, 0.8, 0.0, 1.2, 0.0)]
+    outs = {}
+    for graphs in (False, True):
+        eng = make_engine(d, dtype=dtype, page_size=8, use_cudagraphs=graphs, cudagraph_step=4, cudagraph_max_size=8)
+        outs[graphs] = eng.generate(prompts, sp, max_num_tokens=40, ignore_eos=True)
+        if graphs:
+            assert eng.graphs is not None and len(eng.graphs.graphs) >= 1
+            assert not eng.runner.cache.requests
+    for a, b in zip(outs[False], outs[True]):
+        assert a.completion_ids == b.completion_ids
+        np.testing.assert_allclose(a.logprobs, b.logprobs, atol=1e-5)

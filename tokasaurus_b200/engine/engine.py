@@ -48,8 +48,13 @@ class Engine:
             self.runner.cache, cfg.max_tokens_per_forward, cfg.max_seqs_per_forward,
             cfg.max_num_tokens_per_request, self.runner.eos_token_ids, kv_reserve_fraction,
             cfg.bump_city_population_me, cfg.allocator_sanity_checks)
-        self.sampler = Sampler(self.runner.rt.device, max(64, min(cfg.max_seqs_per_forward, 4096)),
+        self.sampler = Sampler(self.runner.rt.device, max(64, cfg.max_seqs_per_forward, cfg.cudagraph_max_size),
                                cfg.enable_chosen_logprobs)
+        self.graphs = None
+        if cfg.use_cudagraphs and self.runner.rt.device.type == "cuda":
+            from tokasaurus_b200.engine.graphs import DecodeGraphs
+
+            self.graphs = DecodeGraphs(self.runner, self.sampler, cfg.cudagraph_max_size, cfg.cudagraph_step)
         self._auto_id = 0
         self.last_step_bytes = dict(h2d=0, d2h=0)
 
@@ -98,6 +103,14 @@ class Engine:
             toks = None if p.from_device else p.seq.tokens[p.start:p.start + p.n_tokens]
             entries.append(StepEntry(p.seq.id, toks, p.start, [p.n_tokens - 1] if p.samples else []))
         extra = self._sampling_arrays(plan)
+        wants_topk = any(p.seq.request.topk_logprobs for p in plan.portions if p.samples)
+        if self.graphs is not None and not wants_topk and self.graphs.usable(entries):
+            padded = self.graphs.run(entries, extra)
+            ids, lps = self.sampler.read(padded)
+            ids, lps = ids[:len(entries)], lps[:len(entries)]
+            self.runner.check_status()
+            self.last_step_bytes = dict(h2d=self.runner.last_upload_bytes, d2h=self.sampler.bytes_last_read)
+            return self.scheduler.complete(plan, ids, lps if self.config.enable_chosen_logprobs else None, None)
         logits = self.runner.step(entries, extra)
         R = logits.shape[0]
         ids: list[int] = []

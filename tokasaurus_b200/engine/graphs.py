@@ -1,0 +1,126 @@
+"""CUDA graphs for steps in which every request brings one token.
+
+The reference records graphs for decode-only batches of 16, 32, ... 128 requests, pads a batch up
+to the next recorded size and sends padded rows to a spare page (tokasaurus/model/utils.py:512-720,
+:839-882; sizes from ``cudagraph_step``/``cudagraph_max_size``, tokasaurus/common_types.py:119-122).
+Here a graph holds the whole step, model and sampler, for one (padded batch size, capacity of the
+attention work list, capacity of the block tables); it is recorded the first time that shape comes
+up.  Every array of the step lives at a fixed place of the graph's own staging buffer, so a replay
+is: fill the pinned copy, one copy to the device, one graph launch.  Padded rows carry request
+row -1: the kernels skip them, nothing is written for them, no spare page is needed.
+"""
+
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+from tokasaurus_b200.engine.batch import HostBatch, Stager, StepContext, StepEntry, build_host_batch
+
+
+def _pow2_at_least(n: int, floor: int) -> int:
+    c = floor
+    while c < n:
+        c *= 2
+    return c
+
+
+def _pad(a: np.ndarray, n: int, fill: int = 0) -> np.ndarray:
+    out = np.full((n,), fill, dtype=a.dtype)
+    out[: a.shape[0]] = a
+    return out
+
+
+class DecodeGraphs:
+    def __init__(self, runner, sampler, max_size: int, step: int):
+        self.runner = runner
+        self.sampler = sampler
+        self.max_size = max_size
+        self.sizes = sorted({s for s in (1, 2, 4, 8) if s <= max_size} | set(range(step, max_size + 1, step)))
+        self.graphs: dict[tuple, dict] = {}
+        self.launches_per_replay = 0
+
+    def usable(self, entries) -> bool:
+        return (bool(self.sizes) and len(entries) <= self.sizes[-1] and self.runner.model.graph_safe
+                and all(e.n_tokens == 1 and list(e.want) == [0] for e in entries))
+
+    def _padded(self, host: HostBatch, bp: int, page_caps: list[int]) -> HostBatch:
+        last = [int(ip[-1]) for ip in host.table_indptr]
+        return HostBatch(
+            _pad(host.token_ids, bp), _pad(host.positions, bp), _pad(host.token_seq, bp, -1), _pad(host.seq_slot, bp),
+            _pad(host.seq_q_start, bp), _pad(host.seq_q_len, bp), _pad(host.seq_kv_len, bp),
+            np.arange(bp, dtype=np.int32),
+            [_pad(ip, bp + 1, l) for ip, l in zip(host.table_indptr, last)],
+            [_pad(pg, cap) for pg, cap in zip(host.table_pages, page_caps)], host.requests)
+
+    def run(self, entries: list[StepEntry], extra: dict[str, np.ndarray]) -> int:
+        """Run one decode step for ``entries`` and sample; returns the padded batch size (the
+        sampler's results for the real rows are the first ``len(entries)`` of each part)."""
+        from tokasaurus_b200.kernels import ops
+
+        runner = self.runner
+        B = len(entries)
+        bp = next(s for s in self.sizes if s >= B)
+        host = build_host_batch(entries, runner.cache)
+        page_caps = [_pow2_at_least(pg.shape[0], 64) for pg in host.table_pages]
+        plans_probe = {}
+        for mixer in runner.model.mixers():
+            made = mixer.plan(host)
+            if made is not None and made[0] not in plans_probe:
+                plans_probe[made[0]] = made[1]
+        caps = {key: dict(items=_pow2_at_least(int(p["counts"][0]), 8), dec=bp, tiles=0)
+                for key, p in plans_probe.items()}
+        key = (bp, tuple(page_caps), tuple(sorted((k, c["items"]) for k, c in caps.items())))
+        padded = self._padded(host, bp, page_caps)
+        plans = {}
+        for mixer in runner.model.mixers():
+            made = mixer.plan(host, caps.get(mixer.plan_key()) if hasattr(mixer, "plan_key") else None)
+            if made is not None and made[0] not in plans:
+                plans[made[0]] = made[1]
+        ex = dict(temperature=_pad(extra["temperature"], bp), stream_key=_pad(extra["stream_key"], bp),
+                  sample_pos=_pad(extra["sample_pos"], bp), row_slot=_pad(extra["row_slot"], bp, -1))
+        slot = self.graphs.get(key)
+        if slot is None:
+            slot = dict(stager=Stager(runner.rt.device, 1 << 12), graph=None)
+            slot["stager"].status = runner.stager.status
+            self.graphs[key] = slot
+        ctx = StepContext(padded, runner.cache, runner.rt.device, slot["stager"], ex, plans)
+        ctx.plan_caps = caps
+        runner.last_upload_bytes = slot["stager"].bytes_last_upload
+        runner.last_context = ctx
+        if slot["graph"] is None:
+            self._record(slot, ctx, bp)
+        slot["graph"].replay()
+        ops.LAUNCHES += slot["launches"]
+        return bp
+
+    def _record(self, slot: dict, ctx: StepContext, bp: int) -> None:
+        from tokasaurus_b200.kernels import ops
+
+        runner, sampler = self.runner, self.sampler
+        if bp > sampler.max_rows:
+            raise ValueError(f"graph batch {bp} exceeds the sampler's {sampler.max_rows} rows")
+        last = runner.cache.last_token
+
+        def body():
+            logits = runner.model.forward(ctx)
+            e = ctx.extra
+            sampler.sample(logits, e["temperature"], e["stream_key"], e["sample_pos"], e["row_slot"], last)
+            return logits
+
+        # One eager run first (library handles, kernel modules); it must not move the requests on,
+        # so the last-token table is put back afterwards.  Writes to the cache are the same ones the
+        # replay makes again.
+        saved = last.clone()
+        torch.cuda.synchronize()
+        body()
+        last.copy_(saved)
+        torch.cuda.synchronize()
+        before = ops.LAUNCHES
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            slot["logits"] = body()
+        slot["launches"] = ops.LAUNCHES - before
+        ops.LAUNCHES = before
+        slot["graph"] = g
+        slot["ctx"] = ctx  # keeps the views alive

@@ -59,6 +59,8 @@ def plan_attention(host, window: int | None, capacity: dict | None = None) -> di
 
 
 class PagedAttention(Mixer):
+    graph_safe = True
+
     def __init__(self, width: int, n_heads: int, n_kv_heads: int, head_dim: int, position: PositionEncoding,
                  q_name: str, k_name: str, v_name: str, o_name: str, window: int | None = None,
                  softmax_scale: float | None = None):

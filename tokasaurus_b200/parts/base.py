@@ -82,6 +82,11 @@ class PositionEncoding:
 
 
 class Mixer(Part):
+    # True if ``forward`` only launches work on the current stream and reads nothing of the step on
+    # the host that could change between two steps of the same shape: such a step can be replayed
+    # from a CUDA graph.
+    graph_safe = False
+
     def cache_need(self) -> PagedCacheNeed | StateNeed | None:
         return None
 

@@ -58,6 +58,10 @@ class DecoderModel(Part):
         for part in [self.embedding, *self.blocks, self.head]:
             part.bind(weights, rt)
 
+    @property
+    def graph_safe(self) -> bool:
+        return all(getattr(m, "graph_safe", False) for m in self.mixers())
+
     def mixers(self):
         return [b.mixer for b in self.blocks]
 

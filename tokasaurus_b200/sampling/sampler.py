@@ -32,7 +32,7 @@ class Sampler:
         """Fill ``self.out``: ids in [0, R), log-probabilities (float bits) in [R, 2R)."""
         R = logits.shape[0]
         if R > self.max_rows:
-            self._alloc(max(R, 2 * self.max_rows))
+            raise ValueError(f"{R} rows to sample, the sampler was made for {self.max_rows}")
         ids = self.out[:R]
         lp = self.out[R:2 * R].view(torch.float32) if self.want_logprobs else None
         ops.sample(logits, temperature, stream_key, sample_pos, row_slot, ids, lp, last_token)
