@@ -31,7 +31,9 @@ def embed_gather(table, ids, token_seq, seq_slot, last_token, x_out, status):
 
 
 def add_rmsnorm(x, delta, weight, eps, out):
-    if delta is not None:
+    if delta is not None and delta.dim() == 3:
+        x += delta.double().sum(0).float()
+    elif delta is not None:
         x += delta.float()
     var = x.double().pow(2).mean(-1, keepdim=True)
     out.copy_((x.double() * torch.rsqrt(var + eps) * weight.double()).to(out.dtype))
@@ -72,9 +74,13 @@ def rope_kv_write(qkv, positions, token_seq, page_indptr, page_ids, inv_freq, kc
         vcache[page, :, p % page_size, :] = v
 
 
-def silu_mul(gate_up, out):
+def silu_mul(gate_up, out, interleave=0):
     I = out.shape[1]
-    g, u = gate_up[:, :I].float(), gate_up[:, I:].float()
+    if interleave:
+        v = gate_up.view(gate_up.shape[0], I // 8, 2, 8)
+        g, u = v[:, :, 0].reshape(-1, I).float(), v[:, :, 1].reshape(-1, I).float()
+    else:
+        g, u = gate_up[:, :I].float(), gate_up[:, I:].float()
     out.copy_((g / (1 + torch.exp(-g)) * u).to(out.dtype))
 
 

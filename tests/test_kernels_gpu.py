@@ -429,3 +429,78 @@ def test_mma_attention_never_reads_what_a_page_held_before(ops):
     got, want = run_mma_attention(ops, [1, 37], [100, 37], 8, 2, 64, 16, None, seed=3, fill=float("nan"))
     assert not torch.isnan(got).any()
     torch.testing.assert_close(got, want, rtol=1.6e-2, atol=1.2e-2)
+
+
+# ------------------------------------------------------------------------------------------------
+# small-batch matrix products (K-split, float32 slices) and their consumers
+@pytest.mark.parametrize("M,N,K", [(1, 3072, 2048), (8, 2048, 8192), (3, 509, 96), (17, 130, 160), (33, 64, 64),
+                                   (64, 2048, 2048), (5, 128256, 2048), (2, 72, 8)])
+def test_linear_smallm(ops, M, N, K):
+    g = torch.Generator().manual_seed(M + N + K)
+    a = torch.randn(M, K, generator=g).to(torch.bfloat16).to(DEV)
+    w = (torch.randn(N, K, generator=g) * 0.05).to(torch.bfloat16).to(DEV)
+    for max_slices in (8, 1):
+        parts = ops.linear_smallm(a, w, max_slices)
+        assert parts.shape[1:] == (M, N) and parts.dtype == torch.float32 and (max_slices > 1 or parts.shape[0] == 1)
+        want = a.double() @ w.double().T
+        got = parts.double().sum(0)
+        scale = (a.abs().double() @ w.abs().double().T).max().item()
+        assert (got - want).abs().max().item() <= 2e-6 * scale * math.sqrt(K) + 1e-6, (parts.shape[0],)
+    # a row does not depend on the others in the batch
+    if M > 1:
+        alone = ops.linear_smallm(a[M - 1:M].contiguous(), w, 8)
+        torch.testing.assert_close(alone.sum(0)[0], ops.linear_smallm(a, w, 8).sum(0)[M - 1], rtol=1e-5, atol=1e-5)
+
+
+@pytest.mark.parametrize("M,I,K", [(1, 8192, 2048), (8, 160, 96), (20, 72, 64), (64, 256, 128)])
+def test_linear_smallm_gated(ops, M, I, K):
+    g = torch.Generator().manual_seed(M + I)
+    a = torch.randn(M, K, generator=g).to(torch.bfloat16).to(DEV)
+    gate = (torch.randn(I, K, generator=g) * 0.1).to(torch.bfloat16).to(DEV)
+    up = (torch.randn(I, K, generator=g) * 0.1).to(torch.bfloat16).to(DEV)
+    w = ops.interleave_gate_up(gate, up)
+    assert torch.equal(w[0:8], gate[0:8]) and torch.equal(w[8:16], up[0:8]) and torch.equal(w[16:24], gate[8:16])
+    got = ops.linear_smallm_gated(a, w)
+    want = torch.nn.functional.silu(a.double() @ gate.double().T) * (a.double() @ up.double().T)
+    torch.testing.assert_close(got.double(), want, rtol=1.6e-2, atol=2e-3 * want.abs().max().item())
+    # the unfused route over the same interleaved weights
+    gu = ops.linear(a, w)
+    act = torch.empty(M, I, dtype=torch.bfloat16, device=DEV)
+    ops.silu_mul(gu, act, 8)
+    torch.testing.assert_close(act.double(), want, rtol=3e-2, atol=1e-2 * want.abs().max().item())
+
+
+def test_partial_sums_reach_norm_and_rope(ops):
+    from tokasaurus_b200.parts.rope import RotaryEncoding
+
+    g = torch.Generator().manual_seed(4)
+    rows, H = 5, 96
+    x = torch.randn(rows, H, generator=g).to(DEV)
+    parts = torch.randn(3, rows, H, generator=g).to(DEV)
+    w = (torch.rand(H, generator=g) + 0.5).to(DEV)
+    x1, x2 = x.clone(), x.clone()
+    out = torch.empty(rows, H, dtype=torch.bfloat16, device=DEV)
+    want = torch.empty_like(out)
+    ops.add_rmsnorm(x1, parts, w, 1e-5, out)
+    ref.add_rmsnorm(x2, parts, w, 1e-5, want)
+    torch.testing.assert_close(x1, x2, rtol=1e-6, atol=1e-6)
+    torch.testing.assert_close(out.float(), want.float(), rtol=1.6e-2, atol=1e-2)
+    # rope from slices equals rope from their bfloat16 sum
+    nh, nkv, hd, ps = 6, 2, 48, 8
+    C = (nh + 2 * nkv) * hd
+    T = 4
+    qparts = torch.randn(2, T, C, generator=g).to(DEV)
+    qkv = qparts.sum(0).to(torch.bfloat16)
+    positions, token_seq = i32([0, 9, 10, 300]), i32([0, 0, 0, 1])
+    indptr, pages = i32([0, 2, 40]), i32(list(range(5, 7)) + list(range(10, 48)))
+    inv = RotaryEncoding(hd, 10000.0).inv_freq().to(DEV)
+    kc, vc = (torch.zeros(64, nkv, ps, hd, dtype=torch.bfloat16, device=DEV) for _ in range(2))
+    kc2, vc2 = kc.clone(), vc.clone()
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    q_out = torch.empty(T, nh * hd, dtype=torch.bfloat16, device=DEV)
+    ops.rope_kv_write_partials(qparts, q_out, positions, token_seq, indptr, pages, inv, kc, vc, nh, nkv, hd, hd, ps, True, status)
+    ops.rope_kv_write(qkv, positions, token_seq, indptr, pages, inv, kc2, vc2, nh, nkv, hd, hd, ps, True, status)
+    assert int(status) == 0
+    torch.testing.assert_close(q_out.float(), qkv[:, : nh * hd].float(), rtol=1e-2, atol=1e-2)
+    torch.testing.assert_close(kc.float(), kc2.float(), rtol=1e-2, atol=1e-2)
+    assert torch.equal(vc, vc2)

@@ -60,13 +60,23 @@ TKB_EXPORT int tkb_embed_gather_bf16(const void* table, const int* ids, const in
 // out = (x * rsqrt(mean(x^2) + eps)) * w, rounded once to the activation type.
 // One block per row.
 template <typename T>
-__global__ void add_rmsnorm_kernel(float* __restrict__ x, const T* __restrict__ delta, const float* __restrict__ w,
-                                   T* __restrict__ out, float eps, int H) {
+__global__ void add_rmsnorm_kernel(float* __restrict__ x, const T* __restrict__ delta,
+                                   const float* __restrict__ partials, int n_partials, long long partial_stride,
+                                   const float* __restrict__ w, T* __restrict__ out, float eps, int H) {
   __shared__ float scratch[33];
   const size_t base = (size_t)blockIdx.x * H;
   float* xr = x + base;
   float ss = 0.f;
-  if (delta != nullptr) {
+  if (partials != nullptr) {
+    // the update arrives as float32 slices of a split matrix product: add them in slice order
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+      float d = 0.f;
+      for (int p = 0; p < n_partials; p++) d += partials[(size_t)p * partial_stride + base + i];
+      float v = xr[i] + d;
+      xr[i] = v;
+      ss += v * v;
+    }
+  } else if (delta != nullptr) {
     const T* dr = delta + base;
     for (int i = threadIdx.x; i < H; i += blockDim.x) {
       float v = xr[i] + to_float(dr[i]);
@@ -86,20 +96,28 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const T* __restrict__ 
 }
 
 template <typename T>
-static int add_rmsnorm_launch(float* x, const void* delta, const float* w, void* out, float eps, int rows, int H,
+static int add_rmsnorm_launch(float* x, const void* delta, const float* partials, int n_partials,
+                              long long partial_stride, const float* w, void* out, float eps, int rows, int H,
                               cudaStream_t st) {
   if (rows <= 0) return 0;
   int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
-  add_rmsnorm_kernel<T><<<rows, threads, 0, st>>>(x, (const T*)delta, w, (T*)out, eps, H);
+  add_rmsnorm_kernel<T><<<rows, threads, 0, st>>>(x, (const T*)delta, partials, n_partials, partial_stride, w, (T*)out,
+                                                  eps, H);
   return launch_status();
 }
-TKB_EXPORT int tkb_add_rmsnorm_f32(float* x, const void* delta, const float* w, void* out, float eps, int rows,
-                                   int H, void* st) {
-  return add_rmsnorm_launch<float>(x, delta, w, out, eps, rows, H, (cudaStream_t)st);
+// delta: update in the activation type [rows, H], or null.  partials: the update as float32 slices
+// [n_partials][rows, H] spaced partial_stride floats apart, or null.  At most one of the two.
+TKB_EXPORT int tkb_add_rmsnorm_f32(float* x, const void* delta, const float* partials, int n_partials,
+                                   long long partial_stride, const float* w, void* out, float eps, int rows, int H,
+                                   void* st) {
+  return add_rmsnorm_launch<float>(x, delta, partials, n_partials, partial_stride, w, out, eps, rows, H,
+                                   (cudaStream_t)st);
 }
-TKB_EXPORT int tkb_add_rmsnorm_bf16(float* x, const void* delta, const float* w, void* out, float eps, int rows,
-                                    int H, void* st) {
-  return add_rmsnorm_launch<__nv_bfloat16>(x, delta, w, out, eps, rows, H, (cudaStream_t)st);
+TKB_EXPORT int tkb_add_rmsnorm_bf16(float* x, const void* delta, const float* partials, int n_partials,
+                                    long long partial_stride, const float* w, void* out, float eps, int rows, int H,
+                                    void* st) {
+  return add_rmsnorm_launch<__nv_bfloat16>(x, delta, partials, n_partials, partial_stride, w, out, eps, rows, H,
+                                           (cudaStream_t)st);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -198,34 +216,120 @@ TKB_EXPORT int tkb_rope_kv_write_bf16(void* qkv, const int* positions, const int
                                              status, (cudaStream_t)st);
 }
 
-// ------------------------------------------------------------------------------------------------
-// out[t, i] = silu(gu[t, i]) * gu[t, I + i]  (gate columns first, then up columns).
+// The same for q|k|v that arrive as float32 slices of a split matrix product, [n_partials][tokens, C]:
+// the slices are added in order into shared memory, q is rotated and written to q_out
+// [tokens, nh*hd] in the activation type, rotated k and v go to the cache.
 template <typename T>
-__global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, long long total, int I) {
+__global__ void rope_kv_write_partials_kernel(const float* __restrict__ partials, int n_partials,
+                                              long long partial_stride, T* __restrict__ q_out,
+                                              const int* __restrict__ positions, const int* __restrict__ token_seq,
+                                              const int* __restrict__ page_indptr, const int* __restrict__ page_ids,
+                                              const float* __restrict__ inv_freq, T* __restrict__ kcache,
+                                              T* __restrict__ vcache, int nh, int nkv, int hd, int rot, int page_size,
+                                              int num_pages, int write_cache, int* __restrict__ status) {
+  extern __shared__ float sm[];  // row[C], cos[rot/2], sin[rot/2]
+  const int C = (nh + 2 * nkv) * hd;
+  float* row = sm;
+  float* cs = sm + C;
+  const int t = blockIdx.x;
+  const int s = token_seq[t];
+  if (s < 0) return;
+  const int pos = positions[t];
+  const int half = rot >> 1;
+  for (int i = threadIdx.x; i < C; i += blockDim.x) {
+    float v = 0.f;
+    for (int p = 0; p < n_partials; p++) v += partials[(size_t)p * partial_stride + (size_t)t * C + i];
+    // the product's result in the activation type, as the unsplit path would have stored it
+    row[i] = to_float(from_float<T>(v));
+  }
+  for (int j = threadIdx.x; j < half; j += blockDim.x) {
+    float sn, c;
+    sincosf((float)pos * inv_freq[j], &sn, &c);
+    cs[j] = c;
+    cs[half + j] = sn;
+  }
+  __syncthreads();
+  T* qo = q_out + (size_t)t * nh * hd;
+  for (int idx = threadIdx.x; idx < nh * hd; idx += blockDim.x) {
+    const int d = idx % hd;
+    float v;
+    if (d < half) v = row[idx] * cs[d] - row[idx + half] * cs[half + d];
+    else if (d < rot) v = row[idx] * cs[d - half] + row[idx - half] * cs[d];
+    else v = row[idx];
+    qo[idx] = from_float<T>(v);
+  }
+  if (!write_cache) return;
+  const int page = page_ids[page_indptr[s] + pos / page_size];
+  if (page < 0 || page >= num_pages) {
+    if (threadIdx.x == 0) atomicOr(status, TKB_STATUS_BAD_PAGE);
+    return;
+  }
+  const int slot = pos % page_size;
+  const float* krow = row + nh * hd;
+  const float* vrow = krow + nkv * hd;
+  for (int idx = threadIdx.x; idx < nkv * hd; idx += blockDim.x) {
+    const int h = idx / hd, d = idx - h * hd;
+    const size_t dst = (((size_t)page * nkv + h) * page_size + slot) * hd + d;
+    float kv;
+    if (d < half) kv = krow[idx] * cs[d] - krow[idx + half] * cs[half + d];
+    else if (d < rot) kv = krow[idx] * cs[d - half] + krow[idx - half] * cs[d];
+    else kv = krow[idx];
+    kcache[dst] = from_float<T>(kv);
+    vcache[dst] = from_float<T>(vrow[idx]);
+  }
+}
+
+TKB_EXPORT int tkb_rope_kv_write_partials_bf16(const float* partials, int n_partials, long long partial_stride,
+                                               void* q_out, const int* positions, const int* token_seq,
+                                               const int* page_indptr, const int* page_ids, const float* inv_freq,
+                                               void* kcache, void* vcache, int n_tokens, int nh, int nkv, int hd,
+                                               int rot, int page_size, int num_pages, int write_cache, int* status,
+                                               void* st) {
+  typedef __nv_bfloat16 T;
+  if (n_tokens <= 0) return 0;
+  if (rot < 0 || rot > hd || (rot & 1) || n_partials < 1) return -2;
+  const size_t smem = ((size_t)(nh + 2 * nkv) * hd + (rot > 0 ? rot : 2)) * sizeof(float);
+  if (smem > 48 * 1024) return -2;
+  rope_kv_write_partials_kernel<T><<<n_tokens, 256, smem, (cudaStream_t)st>>>(
+      partials, n_partials, partial_stride, (T*)q_out, positions, token_seq, page_indptr, page_ids, inv_freq, (T*)kcache,
+      (T*)vcache, nh, nkv, hd, rot, page_size, num_pages, write_cache, status);
+  return launch_status();
+}
+
+// ------------------------------------------------------------------------------------------------
+// interleave == 0: gate columns first, then up columns.  interleave == 8: columns come in groups of 16, the
+// 8 gate columns of features 8j..8j+7 followed by their 8 up columns (the layout the small-batch
+// matrix product wants for its fused epilogue).
+template <typename T>
+__global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, long long total, int I,
+                                int interleave) {
   for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
        idx += (long long)gridDim.x * blockDim.x) {
     const long long t = idx / I;
     const int i = (int)(idx - t * I);
-    const float g = to_float(gu[t * 2 * I + i]);
-    const float u = to_float(gu[t * 2 * I + I + i]);
+    const int gc = interleave ? ((i >> 3) << 4) + (i & 7) : i;
+    const int uc = interleave ? gc + 8 : I + i;
+    const float g = to_float(gu[t * 2 * I + gc]);
+    const float u = to_float(gu[t * 2 * I + uc]);
     const float sg = g / (1.f + expf(-g));
     out[idx] = from_float<T>(sg * u);
   }
 }
 template <typename T>
-static int silu_mul_launch(const void* gu, void* out, int rows, int I, cudaStream_t st) {
+static int silu_mul_launch(const void* gu, void* out, int rows, int I, int interleave, cudaStream_t st) {
+  if (interleave != 0 && (interleave != 8 || (I & 7))) return -2;
   long long total = (long long)rows * I;
   if (total <= 0) return 0;
   long long blocks = (total + 255) / 256;
   if (blocks > 148 * 16) blocks = 148 * 16;
-  silu_mul_kernel<T><<<(int)blocks, 256, 0, st>>>((const T*)gu, (T*)out, total, I);
+  silu_mul_kernel<T><<<(int)blocks, 256, 0, st>>>((const T*)gu, (T*)out, total, I, interleave);
   return launch_status();
 }
-TKB_EXPORT int tkb_silu_mul_f32(const void* gu, void* out, int rows, int I, void* st) {
-  return silu_mul_launch<float>(gu, out, rows, I, (cudaStream_t)st);
+TKB_EXPORT int tkb_silu_mul_f32(const void* gu, void* out, int rows, int I, int interleave, void* st) {
+  return silu_mul_launch<float>(gu, out, rows, I, interleave, (cudaStream_t)st);
 }
-TKB_EXPORT int tkb_silu_mul_bf16(const void* gu, void* out, int rows, int I, void* st) {
-  return silu_mul_launch<__nv_bfloat16>(gu, out, rows, I, (cudaStream_t)st);
+TKB_EXPORT int tkb_silu_mul_bf16(const void* gu, void* out, int rows, int I, int interleave, void* st) {
+  return silu_mul_launch<__nv_bfloat16>(gu, out, rows, I, interleave, (cudaStream_t)st);
 }
 
 // ------------------------------------------------------------------------------------------------

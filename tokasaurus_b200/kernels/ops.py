@@ -126,17 +126,25 @@ def embed_gather(table: torch.Tensor, ids: torch.Tensor, token_seq: torch.Tensor
 
 def add_rmsnorm(x: torch.Tensor, delta: torch.Tensor | None, weight: torch.Tensor, eps: float,
                 out: torch.Tensor) -> None:
-    """x += delta (float32, in place) if delta is given; out = rmsnorm(x) * weight in out's dtype."""
+    """x += delta (float32, in place) if delta is given; out = rmsnorm(x) * weight in out's dtype.
+
+    ``delta`` is [rows, H] in out's dtype, or float32 [slices, rows, H]: the slices of a split matrix
+    product (``linear_smallm``), added in slice order."""
     _need_cuda(x, delta, weight, out)
     rows, H = x.shape
     _need(x.dtype == torch.float32 and x.is_contiguous(), "add_rmsnorm: x must be contiguous float32")
     _need(weight.dtype == torch.float32 and weight.numel() == H, "add_rmsnorm: weight must be float32 [H]")
     _need(out.shape == x.shape and out.is_contiguous(), "add_rmsnorm: out shape")
-    if delta is not None:
+    partials, n_part, stride = None, 0, 0
+    if delta is not None and delta.dim() == 3:
+        _need(delta.dtype == torch.float32 and tuple(delta.shape[1:]) == (rows, H) and delta.is_contiguous(),
+              "add_rmsnorm: partial sums must be contiguous float32 [slices, rows, H]")
+        partials, n_part, stride, delta = delta, delta.shape[0], rows * H, None
+    elif delta is not None:
         _need(delta.shape == x.shape and delta.dtype == out.dtype and delta.is_contiguous(), "add_rmsnorm: delta")
     f = _fn(_libs.get("elementwise.cu"), f"tkb_add_rmsnorm_{_suffix(out.dtype)}")
-    _check(f(_ptr(x), _ptr(delta), _ptr(weight), _ptr(out), c_float(eps), c_int(rows), c_int(H), _stream()),
-           "add_rmsnorm")
+    _check(f(_ptr(x), _ptr(delta), _ptr(partials), c_int(n_part), ctypes.c_longlong(stride), _ptr(weight), _ptr(out),
+             c_float(eps), c_int(rows), c_int(H), _stream()), "add_rmsnorm")
 
 
 def rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, token_seq: torch.Tensor, page_indptr: torch.Tensor,
@@ -162,14 +170,83 @@ def rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, token_seq: torch.T
              _ptr(status), _stream()), "rope_kv_write")
 
 
-def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> None:
-    """out[t, i] = silu(gate_up[t, i]) * gate_up[t, I + i]."""
+SMALL_M_MAX = 64
+
+
+def can_use_smallm(a: torch.Tensor, w: torch.Tensor) -> bool:
+    return (a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and 0 < a.shape[0] <= SMALL_M_MAX
+            and a.shape[1] % 8 == 0 and a.stride(0) % 8 == 0 and w.stride(0) % 8 == 0)
+
+
+def linear_smallm(a: torch.Tensor, w: torch.Tensor, max_slices: int = 8) -> torch.Tensor:
+    """a[M, K] @ w[N, K]^T for M <= 64 in bfloat16, as float32 slices [slices, M, N] of a K-split
+    product (the consumer adds the slices).  ``max_slices=1`` gives the whole product as [1, M, N]."""
+    _need_cuda(a, w)
+    _need(can_use_smallm(a, w), "linear_smallm: bfloat16, M <= 64, K a multiple of 8")
+    M, K = a.shape
+    N = w.shape[0]
+    _need(w.shape[1] == K and a.stride(1) == 1 and w.stride(1) == 1, "linear_smallm: shapes")
+    lib = _libs.get("linear_smallm.cu")
+    slices = lib.tkb_linear_smallm_slices(c_int(N), c_int(K), c_int(max_slices))
+    out = torch.empty((slices, M, N), dtype=torch.float32, device=a.device)
+    _check(_fn(lib, "tkb_linear_smallm_bf16")(_ptr(a), c_int(a.stride(0)), _ptr(w), c_int(w.stride(0)), _ptr(out),
+                                              c_int(M), c_int(N), c_int(K), c_int(slices), _stream()), "linear_smallm")
+    return out
+
+
+def linear_smallm_gated(a: torch.Tensor, w_interleaved: torch.Tensor) -> torch.Tensor:
+    """silu(a @ gate^T) * (a @ up^T) as bfloat16 [M, I] for M <= 64; ``w_interleaved`` [2I, K] holds gate
+    and up rows in groups of 8 (``interleave_gate_up``)."""
+    _need_cuda(a, w_interleaved)
+    _need(can_use_smallm(a, w_interleaved) and w_interleaved.shape[0] % 16 == 0, "linear_smallm_gated: operands")
+    M, K = a.shape
+    N = w_interleaved.shape[0]
+    out = torch.empty((M, N // 2), dtype=torch.bfloat16, device=a.device)
+    _check(_fn(_libs.get("linear_smallm.cu"), "tkb_linear_smallm_gated_bf16")(
+        _ptr(a), c_int(a.stride(0)), _ptr(w_interleaved), c_int(w_interleaved.stride(0)), _ptr(out), c_int(M), c_int(N),
+        c_int(K), _stream()), "linear_smallm_gated")
+    return out
+
+
+def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
+    """[2I, K]: for every 8 features, their 8 gate rows then their 8 up rows.  I must be a multiple of 8."""
+    I, K = gate.shape
+    _need(I % 8 == 0 and up.shape == gate.shape, "interleave_gate_up: I must be a multiple of 8")
+    return torch.stack([gate.view(I // 8, 8, K), up.view(I // 8, 8, K)], dim=1).reshape(2 * I, K).contiguous()
+
+
+def rope_kv_write_partials(partials: torch.Tensor, q_out: torch.Tensor, positions: torch.Tensor,
+                           token_seq: torch.Tensor, page_indptr: torch.Tensor, page_ids: torch.Tensor,
+                           inv_freq: torch.Tensor | None, kcache: torch.Tensor, vcache: torch.Tensor, n_heads: int,
+                           n_kv_heads: int, head_dim: int, rotary_dim: int, page_size: int, write_cache: bool,
+                           status: torch.Tensor) -> None:
+    """``rope_kv_write`` for q|k|v that arrive as float32 slices [slices, T, C] of a split product: the
+    slices are added, q is rotated into ``q_out`` [T, n_heads*head_dim] (bfloat16), k and v go to the cache."""
+    _need_cuda(partials, q_out, positions, token_seq, page_indptr, page_ids, inv_freq, kcache, vcache, status)
+    S, T, C = partials.shape
+    _need(partials.dtype == torch.float32 and partials.is_contiguous() and C == (n_heads + 2 * n_kv_heads) * head_dim,
+          "rope_kv_write_partials: partials")
+    _need(q_out.dtype == torch.bfloat16 and q_out.is_contiguous() and tuple(q_out.shape) == (T, n_heads * head_dim),
+          "rope_kv_write_partials: q_out")
+    _need(kcache.dtype == torch.bfloat16 and tuple(kcache.shape[1:]) == (n_kv_heads, page_size, head_dim),
+          "rope_kv_write_partials: cache layout")
+    _need((C + max(rotary_dim, 2)) * 4 <= 48 * 1024, "rope_kv_write_partials: row too wide for shared memory")
+    f = _fn(_libs.get("elementwise.cu"), "tkb_rope_kv_write_partials_bf16")
+    _check(f(_ptr(partials), c_int(S), ctypes.c_longlong(T * C), _ptr(q_out), _ptr(positions), _ptr(token_seq),
+             _ptr(page_indptr), _ptr(page_ids), _ptr(inv_freq), _ptr(kcache), _ptr(vcache), c_int(T), c_int(n_heads),
+             c_int(n_kv_heads), c_int(head_dim), c_int(rotary_dim), c_int(page_size), c_int(kcache.shape[0]),
+             c_int(1 if write_cache else 0), _ptr(status), _stream()), "rope_kv_write_partials")
+
+
+def silu_mul(gate_up: torch.Tensor, out: torch.Tensor, interleave: int = 0) -> None:
+    """out[t, i] = silu(gate[t, i]) * up[t, i].  interleave 0: gate_up = [gate | up]; interleave 8: columns in
+    groups of 16, 8 gate columns then the 8 up columns of the same features."""
     _need_cuda(gate_up, out)
     rows, two_i = gate_up.shape
     _need(two_i % 2 == 0 and out.shape == (rows, two_i // 2), "silu_mul: shapes")
     _need(gate_up.is_contiguous() and out.is_contiguous() and out.dtype == gate_up.dtype, "silu_mul: layout")
     f = _fn(_libs.get("elementwise.cu"), f"tkb_silu_mul_{_suffix(out.dtype)}")
-    _check(f(_ptr(gate_up), _ptr(out), c_int(rows), c_int(two_i // 2), _stream()), "silu_mul")
+    _check(f(_ptr(gate_up), _ptr(out), c_int(rows), c_int(two_i // 2), c_int(interleave), _stream()), "silu_mul")
 
 
 def gather_rows(src: torch.Tensor, rows: torch.Tensor, out: torch.Tensor) -> None:

@@ -114,11 +114,23 @@ class PagedAttention(Mixer):
     def forward(self, ctx, h: torch.Tensor, cache, out_rows=None) -> torch.Tensor:
         T = h.shape[0]
         hd, nh, nkv = self.head_dim, self.n_heads, self.n_kv_heads
-        qkv = ops.linear(h, self.w_qkv)
         tables = ctx.tables[cache.group]
         rot = self.position.rotary_dim if self.position.kind == "rotary" else 0
-        ops.rope_kv_write(qkv, ctx.positions, ctx.token_seq, tables.indptr, tables.page_ids, self.inv_freq,
-                          cache.k, cache.v, nh, nkv, hd, rot, cache.page_size, cache.writable, ctx.status)
+        small = (ops.can_use_smallm(h, self.w_qkv) and (nh * hd) % 8 == 0
+                 and (self.w_qkv.shape[0] + max(rot, 2)) * 4 <= 48 * 1024)
+        if small:
+            # few rows: K-split products whose float32 slices the next kernel adds
+            parts = ops.linear_smallm(h, self.w_qkv)
+            qkv = torch.empty((T, nh * hd), dtype=h.dtype, device=h.device)  # q only; k and v go straight to the cache
+            ops.rope_kv_write_partials(parts, qkv, ctx.positions, ctx.token_seq, tables.indptr, tables.page_ids,
+                                       self.inv_freq, cache.k, cache.v, nh, nkv, hd, rot, cache.page_size,
+                                       cache.writable, ctx.status)
+            project = ops.linear_smallm
+        else:
+            qkv = ops.linear(h, self.w_qkv)
+            ops.rope_kv_write(qkv, ctx.positions, ctx.token_seq, tables.indptr, tables.page_ids, self.inv_freq,
+                              cache.k, cache.v, nh, nkv, hd, rot, cache.page_size, cache.writable, ctx.status)
+            project = ops.linear
         plan = ctx.plans.get(self.plan_key()) if h.dtype == torch.bfloat16 else None
         if plan is None or out_rows is not None:
             # float32, or only some rows are wanted: the FP32-pipe kernel, one warp per (row, head)
@@ -126,7 +138,7 @@ class PagedAttention(Mixer):
             attn = torch.empty((n_rows, nh * hd), dtype=h.dtype, device=h.device)
             ops.attn_paged(qkv, qkv.shape[1], attn, cache.k, cache.v, ctx.token_seq, ctx.positions, tables.indptr,
                            tables.page_ids, out_rows, n_rows, nh, nkv, hd, cache.page_size, self.scale, self.window)
-            return ops.linear(attn, self.w_o)
+            return project(attn, self.w_o)
         attn = torch.empty((T, nh * hd), dtype=h.dtype, device=h.device)
         caps = ctx.plan_caps.get(self.plan_key()) if ctx.plan_caps else None
         counts = ctx.host_plans[self.plan_key()]["counts"]
@@ -142,4 +154,4 @@ class PagedAttention(Mixer):
             ops.attn_prefill_mma(qkv, attn, cache.k, cache.v, ctx.seq_q_start, ctx.seq_q_len, ctx.seq_kv_len,
                                  tables.indptr, tables.page_ids, plan["tiles"], c[2:3], tiles_cap, nh, nkv, hd,
                                  cache.page_size, self.scale, self.window)
-        return ops.linear(attn, self.w_o)
+        return project(attn, self.w_o)

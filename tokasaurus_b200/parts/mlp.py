@@ -15,6 +15,7 @@ class GatedMLP(FeedForward):
         self.width = width
         self.inner = inner
         self.names = (gate_name, up_name, down_name)
+        self.interleave = 0
         self.w_gate_up: torch.Tensor | None = None
         self.w_down: torch.Tensor | None = None
 
@@ -28,11 +29,22 @@ class GatedMLP(FeedForward):
 
     def bind(self, weights, rt) -> None:
         g, u, d = self.names
-        self.w_gate_up = torch.cat([weights[g], weights[u]], dim=0).contiguous()
+        # bfloat16: gate and up rows interleaved in groups of 8, the layout whose product the small-batch
+        # kernel can turn into silu(gate) * up in its epilogue
+        self.interleave = 8 if (rt.dtype == torch.bfloat16 and self.inner % 8 == 0) else 0
+        if self.interleave:
+            self.w_gate_up = ops.interleave_gate_up(weights[g], weights[u])
+        else:
+            self.w_gate_up = torch.cat([weights[g], weights[u]], dim=0).contiguous()
         self.w_down = weights[d].contiguous()
 
     def forward(self, ctx, h: torch.Tensor) -> torch.Tensor:
+        """Returns the update [rows, width] in h's dtype, or as float32 slices [slices, rows, width]
+        that the next norm adds (few rows, bfloat16)."""
+        if self.interleave and ops.can_use_smallm(h, self.w_gate_up) and self.inner % 8 == 0:
+            act = ops.linear_smallm_gated(h, self.w_gate_up)
+            return ops.linear_smallm(act, self.w_down)
         gu = ops.linear(h, self.w_gate_up)
         act = torch.empty((h.shape[0], self.inner), dtype=h.dtype, device=h.device)
-        ops.silu_mul(gu, act)
+        ops.silu_mul(gu, act, self.interleave)
         return ops.linear(act, self.w_down)
