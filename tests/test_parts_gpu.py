@@ -81,6 +81,8 @@ def test_feed_forward_part(dtype):
     m.bind(dev, rt(dtype))
     h = torch.randn(7, 80).to(dtype)
     out = m.forward(None, h.to(DEV))
+    if out.dim() == 3:  # few rows in bfloat16: float32 slices of a K-split product, added by the next norm
+        out = out.sum(0)
     hd = h.double()
     want = (torch.nn.functional.silu(hd @ host["g"].double().T) * (hd @ host["u"].double().T)) @ host["d"].double().T
     torch.testing.assert_close(out.cpu().double(), want, **tol(dtype, want))
@@ -114,6 +116,7 @@ def test_attention_mixer_part_whole_and_cut(dtype, nh, nkv, hd, scaled):
     needs = {0: a.cache_need()}
     ctx = context(needs, [("w", list(range(T)), 0, [])])
     out = a.forward(ctx, h.to(DEV), ctx.layer_cache(0))
+    out = out.sum(0) if out.dim() == 3 else out
     torch.testing.assert_close(out.cpu().double(), want, **tol(dtype, want))
     # cut: 7 + 2 + 20 + 1 + 1 + 14, a second request in between, wanted rows only at the end
     context.reuse = True
@@ -122,7 +125,8 @@ def test_attention_mixer_part_whole_and_cut(dtype, nh, nkv, hd, scaled):
         ctx = context(needs, [("other", [0] * 3, at // 2 * 0 + len(got) * 3, []), ("c", list(range(n)), at, [])])
         hh = torch.cat([torch.randn(3, width).to(dtype), h[at:at + n]]).to(DEV)
         rows = torch.arange(3, 3 + n, dtype=torch.int32, device=DEV)
-        got.append(a.forward(ctx, hh, ctx.layer_cache(0), out_rows=rows))
+        part = a.forward(ctx, hh, ctx.layer_cache(0), out_rows=rows)
+        got.append(part.sum(0) if part.dim() == 3 else part)
         at += n
     torch.testing.assert_close(torch.cat(got).cpu().double(), want, **tol(dtype, want))
     context.reuse = False

@@ -170,6 +170,8 @@ attn_decode_mma_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __r
                        const int* __restrict__ n_items_ptr, float* __restrict__ part_o, float* __restrict__ part_ml,
                        int nh, int nkv, int ps, float scale_log2, int window, int split_keys, int head_tiles) {
   extern __shared__ __align__(128) unsigned char smem[];
+  trigger_dependents();
+  grid_dependency_wait();
   const int item = blockIdx.x;
   if (item >= *n_items_ptr) return;
   const int s = items[2 * item], split = items[2 * item + 1];
@@ -292,6 +294,8 @@ __global__ void attn_decode_merge_kernel(const float* __restrict__ part_o, const
                                          const int* __restrict__ dec_seqs, const int* __restrict__ dec_item_start,
                                          const int* __restrict__ n_dec_ptr, const int* __restrict__ seq_q_start,
                                          bf16* __restrict__ out, int out_stride, int nh) {
+  trigger_dependents();
+  grid_dependency_wait();
   const int e = blockIdx.x;
   if (e >= *n_dec_ptr) return;
   const int head = blockIdx.y;
@@ -322,6 +326,8 @@ attn_prefill_mma_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restri
                         const int* __restrict__ page_ids, const int* __restrict__ tiles,
                         const int* __restrict__ n_tiles_ptr, int nh, int nkv, int ps, float scale_log2, int window) {
   extern __shared__ __align__(128) unsigned char smem[];
+  trigger_dependents();
+  grid_dependency_wait();
   if ((int)blockIdx.x >= *n_tiles_ptr) return;
   const int s = tiles[2 * blockIdx.x], qt0 = tiles[2 * blockIdx.x + 1];
   const int head = blockIdx.y;
@@ -454,10 +460,10 @@ TKB_EXPORT int tkb_attn_decode_mma_bf16(const void* q, int q_stride, const void*
   const int head_tiles = (group + 15) / 16;
   if ((long long)nkv * head_tiles > 65535) return -3;
   dim3 grid(items_cap, nkv * head_tiles);
-  attn_decode_mma_kernel<<<grid, 128, SMEM_B, (cudaStream_t)st>>>(
-      (const bf16*)q, q_stride, (const bf16*)kcache, (const bf16*)vcache, seq_q_start, seq_kv_len, page_indptr, page_ids,
-      items, n_items_ptr, part_o, part_ml, nh, nkv, ps, scale * 1.4426950408889634f, window, split_keys, head_tiles);
-  return launch_status();
+  return launch_pdl(attn_decode_mma_kernel, grid, dim3(128), (size_t)SMEM_B, (cudaStream_t)st, (const bf16*)q, q_stride,
+                    (const bf16*)kcache, (const bf16*)vcache, seq_q_start, seq_kv_len, page_indptr, page_ids, items,
+                    n_items_ptr, part_o, part_ml, nh, nkv, ps, scale * 1.4426950408889634f, window, split_keys,
+                    head_tiles);
 }
 
 TKB_EXPORT int tkb_attn_decode_merge_bf16(const float* part_o, const float* part_ml, const int* dec_seqs,
@@ -467,9 +473,8 @@ TKB_EXPORT int tkb_attn_decode_merge_bf16(const float* part_o, const float* part
   if (nh > 65535) return -3;
   dim3 grid(dec_cap, nh);
   const int threads = HD >= 128 ? 128 : (HD >= 64 ? 64 : 32);
-  attn_decode_merge_kernel<<<grid, threads, 0, (cudaStream_t)st>>>(part_o, part_ml, dec_seqs, dec_item_start,
-                                                                  n_dec_ptr, seq_q_start, (bf16*)out, out_stride, nh);
-  return launch_status();
+  return launch_pdl(attn_decode_merge_kernel, grid, dim3(threads), 0, (cudaStream_t)st, part_o, part_ml, dec_seqs,
+                    dec_item_start, n_dec_ptr, seq_q_start, (bf16*)out, out_stride, nh);
 }
 
 TKB_EXPORT int tkb_attn_prefill_mma_bf16(const void* q, int q_stride, void* out, int out_stride, const void* kcache,
@@ -483,9 +488,8 @@ TKB_EXPORT int tkb_attn_prefill_mma_bf16(const void* q, int q_stride, void* out,
   int rc = ensure_smem_attr();
   if (rc) return rc;
   dim3 grid(tiles_cap, nh);
-  attn_prefill_mma_kernel<<<grid, 128, SMEM_B, (cudaStream_t)st>>>(
-      (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)kcache, (const bf16*)vcache, seq_q_start, seq_q_len,
-      seq_kv_len, page_indptr, page_ids, tiles, n_tiles_ptr, nh, nkv, ps, scale * 1.4426950408889634f, window);
-  return launch_status();
+  return launch_pdl(attn_prefill_mma_kernel, grid, dim3(128), (size_t)SMEM_B, (cudaStream_t)st, (const bf16*)q, q_stride,
+                    (bf16*)out, out_stride, (const bf16*)kcache, (const bf16*)vcache, seq_q_start, seq_q_len, seq_kv_len,
+                    page_indptr, page_ids, tiles, n_tiles_ptr, nh, nkv, ps, scale * 1.4426950408889634f, window);
 }
 TKB_EXPORT int tkb_attn_mma_head_dim() { return HD; }

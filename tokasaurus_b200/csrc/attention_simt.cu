@@ -71,6 +71,8 @@ attn_paged_simt_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ ou
                        const int* __restrict__ page_indptr, const int* __restrict__ page_ids,
                        const int* __restrict__ rows, int nh, int nkv, int page_size, float scale_log2, int window) {
   __shared__ float qs[WARPS][HD];
+  trigger_dependents();
+  grid_dependency_wait();
   const int t = rows ? rows[blockIdx.x] : blockIdx.x;
   const int kvh = blockIdx.y;
   const int s = token_seq[t];
@@ -144,11 +146,9 @@ int attn_launch(const void* q, int q_stride, void* out, int out_stride, const vo
   if (nkv > 65535) return -3;
   dim3 grid(n_rows, nkv);
   const float scale_log2 = scale * 1.4426950408889634f;
-  attn_paged_simt_kernel<T><<<grid, WARPS * 32, 0, st>>>((const T*)q, q_stride, (T*)out, out_stride,
-                                                         (const T*)kcache, (const T*)vcache, token_seq, positions,
-                                                         page_indptr, page_ids, rows, nh, nkv, page_size, scale_log2,
-                                                         window);
-  return launch_status();
+  return launch_pdl(attn_paged_simt_kernel<T>, grid, dim3(WARPS * 32), 0, st, (const T*)q, q_stride, (T*)out, out_stride,
+                    (const T*)kcache, (const T*)vcache, token_seq, positions, page_indptr, page_ids, rows, nh, nkv,
+                    page_size, scale_log2, window);
 }
 
 }  // namespace

@@ -50,6 +50,31 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
   return scratch[32];
 }
 
+// Programmatic dependent launch: a kernel launched with `launch_pdl` may start while the kernel
+// before it in the stream is still running.  It must call grid_dependency_wait() before it reads
+// anything an earlier kernel wrote and before it writes anything at all; what it does before that
+// call (fetching weights, which no kernel writes) overlaps the earlier kernel.  Every kernel calls
+// trigger_dependents() at its start so that its successor can be brought onto the SMs early; without a
+// programmatic launch behind or before it, both calls do nothing.
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void trigger_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+inline int launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+  return static_cast<int>(e);
+}
+
 inline int launch_status() {
   cudaError_t e = cudaGetLastError();
   return static_cast<int>(e);

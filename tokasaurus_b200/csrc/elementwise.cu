@@ -14,6 +14,8 @@ __global__ void embed_gather_kernel(const T* __restrict__ table, const int* __re
                                     const int* __restrict__ token_seq, const int* __restrict__ seq_slot,
                                     const int* __restrict__ last_token, float* __restrict__ x, int H, int V,
                                     int* __restrict__ status) {
+  trigger_dependents();
+  grid_dependency_wait();
   const int t = blockIdx.x;
   const int s = token_seq[t];
   int id = ids[t];
@@ -38,9 +40,8 @@ static int embed_gather_launch(const void* table, const int* ids, const int* tok
                                cudaStream_t st) {
   if (n_tokens <= 0) return 0;
   int threads = H >= 1024 ? 256 : (H >= 256 ? 128 : 64);
-  embed_gather_kernel<T><<<n_tokens, threads, 0, st>>>((const T*)table, ids, token_seq, seq_slot, last_token, x, H,
-                                                       V, status);
-  return launch_status();
+  return launch_pdl(embed_gather_kernel<T>, dim3(n_tokens), dim3(threads), 0, st, (const T*)table, ids, token_seq, seq_slot,
+                    last_token, x, H, V, status);
 }
 TKB_EXPORT int tkb_embed_gather_f32(const void* table, const int* ids, const int* token_seq, const int* seq_slot,
                                     const int* last_token, float* x, int n_tokens, int H, int V, int* status,
@@ -63,6 +64,8 @@ template <typename T>
 __global__ void add_rmsnorm_kernel(float* __restrict__ x, const T* __restrict__ delta,
                                    const float* __restrict__ partials, int n_partials, long long partial_stride,
                                    const float* __restrict__ w, T* __restrict__ out, float eps, int H) {
+  trigger_dependents();
+  grid_dependency_wait();
   __shared__ float scratch[33];
   const size_t base = (size_t)blockIdx.x * H;
   float* xr = x + base;
@@ -101,9 +104,8 @@ static int add_rmsnorm_launch(float* x, const void* delta, const float* partials
                               cudaStream_t st) {
   if (rows <= 0) return 0;
   int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
-  add_rmsnorm_kernel<T><<<rows, threads, 0, st>>>(x, (const T*)delta, partials, n_partials, partial_stride, w, (T*)out,
-                                                  eps, H);
-  return launch_status();
+  return launch_pdl(add_rmsnorm_kernel<T>, dim3(rows), dim3(threads), 0, st, x, (const T*)delta, partials, n_partials,
+                    partial_stride, w, (T*)out, eps, H);
 }
 // delta: update in the activation type [rows, H], or null.  partials: the update as float32 slices
 // [n_partials][rows, H] spaced partial_stride floats apart, or null.  At most one of the two.
@@ -133,6 +135,8 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, const int* __restrict_
                                      const int* __restrict__ page_ids, const float* __restrict__ inv_freq,
                                      T* __restrict__ kcache, T* __restrict__ vcache, int nh, int nkv, int hd, int rot,
                                      int page_size, int num_pages, int write_cache, int* __restrict__ status) {
+  trigger_dependents();
+  grid_dependency_wait();
   extern __shared__ float cs[];  // cos[rot/2], sin[rot/2]
   const int t = blockIdx.x;
   const int s = token_seq[t];
@@ -194,10 +198,9 @@ static int rope_kv_write_launch(void* qkv, const int* positions, const int* toke
   int work = nh * (rot / 2) > nkv * hd ? nh * (rot / 2) : nkv * hd;
   int threads = work >= 512 ? 256 : (work >= 128 ? 128 : 64);
   size_t smem = (size_t)(rot > 0 ? rot : 2) * sizeof(float);
-  rope_kv_write_kernel<T><<<n_tokens, threads, smem, st>>>((T*)qkv, positions, token_seq, page_indptr, page_ids,
-                                                           inv_freq, (T*)kcache, (T*)vcache, nh, nkv, hd, rot,
-                                                           page_size, num_pages, write_cache, status);
-  return launch_status();
+  return launch_pdl(rope_kv_write_kernel<T>, dim3(n_tokens), dim3(threads), smem, st, (T*)qkv, positions, token_seq,
+                    page_indptr, page_ids, inv_freq, (T*)kcache, (T*)vcache, nh, nkv, hd, rot, page_size, num_pages,
+                    write_cache, status);
 }
 TKB_EXPORT int tkb_rope_kv_write_f32(void* qkv, const int* positions, const int* token_seq, const int* page_indptr,
                                      const int* page_ids, const float* inv_freq, void* kcache, void* vcache,
@@ -227,6 +230,8 @@ __global__ void rope_kv_write_partials_kernel(const float* __restrict__ partials
                                               const float* __restrict__ inv_freq, T* __restrict__ kcache,
                                               T* __restrict__ vcache, int nh, int nkv, int hd, int rot, int page_size,
                                               int num_pages, int write_cache, int* __restrict__ status) {
+  trigger_dependents();
+  grid_dependency_wait();
   extern __shared__ float sm[];  // row[C], cos[rot/2], sin[rot/2]
   const int C = (nh + 2 * nkv) * hd;
   float* row = sm;
@@ -290,10 +295,9 @@ TKB_EXPORT int tkb_rope_kv_write_partials_bf16(const float* partials, int n_part
   if (rot < 0 || rot > hd || (rot & 1) || n_partials < 1) return -2;
   const size_t smem = ((size_t)(nh + 2 * nkv) * hd + (rot > 0 ? rot : 2)) * sizeof(float);
   if (smem > 48 * 1024) return -2;
-  rope_kv_write_partials_kernel<T><<<n_tokens, 256, smem, (cudaStream_t)st>>>(
-      partials, n_partials, partial_stride, (T*)q_out, positions, token_seq, page_indptr, page_ids, inv_freq, (T*)kcache,
-      (T*)vcache, nh, nkv, hd, rot, page_size, num_pages, write_cache, status);
-  return launch_status();
+  return launch_pdl(rope_kv_write_partials_kernel<T>, dim3(n_tokens), dim3(256), smem, (cudaStream_t)st, partials,
+                    n_partials, partial_stride, (T*)q_out, positions, token_seq, page_indptr, page_ids, inv_freq,
+                    (T*)kcache, (T*)vcache, nh, nkv, hd, rot, page_size, num_pages, write_cache, status);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -303,6 +307,8 @@ TKB_EXPORT int tkb_rope_kv_write_partials_bf16(const float* partials, int n_part
 template <typename T>
 __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, long long total, int I,
                                 int interleave) {
+  trigger_dependents();
+  grid_dependency_wait();
   for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
        idx += (long long)gridDim.x * blockDim.x) {
     const long long t = idx / I;
@@ -322,8 +328,7 @@ static int silu_mul_launch(const void* gu, void* out, int rows, int I, int inter
   if (total <= 0) return 0;
   long long blocks = (total + 255) / 256;
   if (blocks > 148 * 16) blocks = 148 * 16;
-  silu_mul_kernel<T><<<(int)blocks, 256, 0, st>>>((const T*)gu, (T*)out, total, I, interleave);
-  return launch_status();
+  return launch_pdl(silu_mul_kernel<T>, dim3((int)blocks), dim3(256), 0, st, (const T*)gu, (T*)out, total, I, interleave);
 }
 TKB_EXPORT int tkb_silu_mul_f32(const void* gu, void* out, int rows, int I, int interleave, void* st) {
   return silu_mul_launch<float>(gu, out, rows, I, interleave, (cudaStream_t)st);
@@ -336,6 +341,8 @@ TKB_EXPORT int tkb_silu_mul_bf16(const void* gu, void* out, int rows, int I, int
 // dst[r, :] = src[rows[r], :], rows of row_bytes bytes (a multiple of 2).
 __global__ void gather_rows_kernel(const unsigned short* __restrict__ src, unsigned short* __restrict__ dst,
                                    const int* __restrict__ rows, int row_halfwords) {
+  trigger_dependents();
+  grid_dependency_wait();
   const int r = blockIdx.x;
   const unsigned short* s = src + (size_t)rows[r] * row_halfwords;
   unsigned short* d = dst + (size_t)r * row_halfwords;
@@ -350,7 +357,6 @@ __global__ void gather_rows_kernel(const unsigned short* __restrict__ src, unsig
 TKB_EXPORT int tkb_gather_rows(const void* src, void* dst, const int* rows, int n_rows, int row_bytes, void* st) {
   if (n_rows <= 0) return 0;
   if (row_bytes & 1) return -2;
-  gather_rows_kernel<<<n_rows, 128, 0, (cudaStream_t)st>>>((const unsigned short*)src, (unsigned short*)dst, rows,
-                                                          row_bytes / 2);
-  return launch_status();
+  return launch_pdl(gather_rows_kernel, dim3(n_rows), dim3(128), 0, (cudaStream_t)st, (const unsigned short*)src,
+                    (unsigned short*)dst, rows, row_bytes / 2);
 }

@@ -21,7 +21,6 @@ namespace {
 constexpr int BN = 64;               // output features per block
 constexpr int BK = 64;               // k per stage
 constexpr int ROWB = BK * 2 + 16;    // padded row bytes (conflict-free ldmatrix)
-constexpr int STAGES = 4;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool valid) {
@@ -43,14 +42,13 @@ __device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], 
 template <int NT> struct Tile {
   static constexpr int A_ROWS = NT * 8 < 16 ? 16 : NT * 8;  // token rows kept in shared memory (>= 16 for ldmatrix.x4)
   static constexpr int STAGE_B = (BN + A_ROWS) * ROWB;
+  static constexpr int STAGES = NT <= 2 ? 6 : 4;  // deep for few tokens: the weight tiles in flight are what is prefetched
   static constexpr int SMEM_B = STAGES * STAGE_B;
 };
 
-template <int NT>
-__device__ __forceinline__ void load_stage(unsigned char* stage, const bf16* __restrict__ A, int lda,
-                                           const bf16* __restrict__ W, int ldw, int M, int N, int K, int n0, int k0,
-                                           int k_end, int tid) {
-  const uint32_t sw = smem_u32(stage), sa = sw + BN * ROWB;
+__device__ __forceinline__ void load_w(unsigned char* stage, const bf16* __restrict__ W, int ldw, int N, int n0,
+                                       int k0, int k_end, int tid) {
+  const uint32_t sw = smem_u32(stage);
 #pragma unroll
   for (int i = 0; i < (BN * 8) / 128; i++) {
     const int idx = tid + i * 128;
@@ -59,6 +57,12 @@ __device__ __forceinline__ void load_stage(unsigned char* stage, const bf16* __r
     const bool valid = n < N && k < k_end;
     cp_async16(sw + r * ROWB + c * 16, W + (valid ? (size_t)n * ldw + k : 0), valid);
   }
+}
+
+template <int NT>
+__device__ __forceinline__ void load_a(unsigned char* stage, const bf16* __restrict__ A, int lda, int M, int k0,
+                                       int k_end, int tid) {
+  const uint32_t sa = smem_u32(stage) + BN * ROWB;
   constexpr int A_CHUNKS = Tile<NT>::A_ROWS * 8;
 #pragma unroll
   for (int i = 0; i < (A_CHUNKS + 127) / 128; i++) {
@@ -90,9 +94,17 @@ linear_smallm_kernel(const bf16* __restrict__ A, int lda, const bf16* __restrict
 #pragma unroll
     for (int i = 0; i < 4; i++) acc[j][i] = 0.f;
 
+  constexpr int STAGES = Tile<NT>::STAGES;
+  // Weights are written by no kernel: their first tiles are fetched while the kernel before this one
+  // may still be running.  The activations are read only after the wait.
+  trigger_dependents();
+#pragma unroll
+  for (int s = 0; s < STAGES - 1; s++)
+    if (s < nkb) load_w(smem + s * Tile<NT>::STAGE_B, W, ldw, N, n0, k_begin + s * BK, k_end, tid);
+  grid_dependency_wait();
 #pragma unroll
   for (int s = 0; s < STAGES - 1; s++) {
-    if (s < nkb) load_stage<NT>(smem + s * Tile<NT>::STAGE_B, A, lda, W, ldw, M, N, K, n0, k_begin + s * BK, k_end, tid);
+    if (s < nkb) load_a<NT>(smem + s * Tile<NT>::STAGE_B, A, lda, M, k_begin + s * BK, k_end, tid);
     cp_async_commit();
   }
   const int w_row = warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
@@ -105,9 +117,11 @@ linear_smallm_kernel(const bf16* __restrict__ A, int lda, const bf16* __restrict
     // refill the stage that was consumed in the previous iteration
     {
       const int nxt = kb + STAGES - 1;
-      if (nxt < nkb)
-        load_stage<NT>(smem + (nxt % STAGES) * Tile<NT>::STAGE_B, A, lda, W, ldw, M, N, K, n0, k_begin + nxt * BK,
-                       k_end, tid);
+      if (nxt < nkb) {
+        unsigned char* st = smem + (nxt % STAGES) * Tile<NT>::STAGE_B;
+        load_w(st, W, ldw, N, n0, k_begin + nxt * BK, k_end, tid);
+        load_a<NT>(st, A, lda, M, k_begin + nxt * BK, k_end, tid);
+      }
       cp_async_commit();
     }
     const uint32_t sw = smem_u32(smem + (kb % STAGES) * Tile<NT>::STAGE_B), sa = sw + BN * ROWB;
@@ -170,9 +184,8 @@ int launch(const void* A, int lda, const void* W, int ldw, void* out, int M, int
     attr_done = true;
   }
   dim3 grid((N + BN - 1) / BN, slices);
-  linear_smallm_kernel<NT, GATED><<<grid, 128, Tile<NT>::SMEM_B, st>>>((const bf16*)A, lda, (const bf16*)W, ldw, out, M,
-                                                                      N, K, kblocks_per_slice);
-  return launch_status();
+  return launch_pdl(linear_smallm_kernel<NT, GATED>, grid, dim3(128), (size_t)Tile<NT>::SMEM_B, st, (const bf16*)A, lda,
+                    (const bf16*)W, ldw, out, M, N, K, kblocks_per_slice);
 }
 
 template <bool GATED>

@@ -66,6 +66,8 @@ sample_kernel(const float* __restrict__ logits, const float* __restrict__ temper
   __shared__ float s_l[SAMPLE_THREADS / 32];
   __shared__ int s_choice;
   __shared__ float s_lse;
+  trigger_dependents();
+  grid_dependency_wait();
   const int r = blockIdx.x;
   const float* lg = logits + (size_t)r * V;
   const float T = temperature ? temperature[r] : 0.f;
@@ -229,9 +231,8 @@ TKB_EXPORT int tkb_sample(const float* logits, const float* temperature, const u
                           int* last_token, int R, int V, void* st) {
   if (R <= 0) return 0;
   if (V <= 0) return -2;
-  sample_kernel<<<R, SAMPLE_THREADS, 0, (cudaStream_t)st>>>(logits, temperature, stream_key, sample_pos, row_slot,
-                                                           out_ids, out_logprob, last_token, V);
-  return launch_status();
+  return launch_pdl(sample_kernel, dim3(R), dim3(SAMPLE_THREADS), 0, (cudaStream_t)st, logits, temperature, stream_key,
+                    sample_pos, row_slot, out_ids, out_logprob, last_token, V);
 }
 
 TKB_EXPORT int tkb_topk_logprobs(const float* logits, const float* temperature, int* out_idx, float* out_lp, int R,
