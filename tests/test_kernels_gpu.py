@@ -504,3 +504,97 @@ def test_partial_sums_reach_norm_and_rope(ops):
     torch.testing.assert_close(q_out.float(), qkv[:, : nh * hd].float(), rtol=1e-2, atol=1e-2)
     torch.testing.assert_close(kc.float(), kc2.float(), rtol=1e-2, atol=1e-2)
     assert torch.equal(vc, vc2)
+
+
+# ------------------------------------------------------------------------------------------------
+# fused products for at most 16 rows
+@pytest.mark.parametrize("M,N,K", [(1, 3072, 2048), (8, 2048, 8192), (3, 509, 96), (16, 130, 160), (9, 64, 1024),
+                                   (5, 128256, 2048), (2, 72, 8), (7, 40, 3000)])
+def test_linear_decode_store_and_add(ops, M, N, K):
+    g = torch.Generator().manual_seed(M + N + K)
+    a = torch.randn(M, K, generator=g).to(torch.bfloat16).to(DEV)
+    w = (torch.randn(N, K, generator=g) * 0.05).to(torch.bfloat16).to(DEV)
+    want = a.double() @ w.double().T
+    scale = (a.abs().double() @ w.abs().double().T).max().item()
+    f32 = ops.linear_decode(a, w, "f32")
+    assert (f32.double() - want).abs().max().item() <= 2e-6 * scale * math.sqrt(K) + 1e-6
+    b16 = ops.linear_decode(a, w, "bf16")
+    torch.testing.assert_close(b16.double(), want, rtol=1e-2, atol=4e-3 * want.abs().max().item())
+    x = torch.randn(M, N, generator=g).to(DEV)
+    x0 = x.clone()
+    ops.linear_decode(a, w, "add", out=x)
+    torch.testing.assert_close(x.double(), x0.double() + want, rtol=1e-5, atol=1e-5 * max(1.0, scale))
+    if M > 1:  # a row does not depend on the others
+        alone = ops.linear_decode(a[M - 1:].contiguous(), w, "f32")
+        assert torch.equal(alone[0], f32[M - 1])
+
+
+@pytest.mark.parametrize("M,N,K,eps", [(1, 3072, 2048, 1e-5), (8, 509, 96, 1e-6), (13, 64, 160, 1e-2)])
+def test_linear_decode_norm_prologue(ops, M, N, K, eps):
+    g = torch.Generator().manual_seed(N)
+    x = (torch.randn(M, K, generator=g) * 3).to(DEV)
+    nw = (torch.rand(K, generator=g) + 0.5).to(DEV)
+    w = (torch.randn(N, K, generator=g) * 0.05).to(torch.bfloat16).to(DEV)
+    xd = x.double()
+    h = xd * torch.rsqrt((xd * xd).mean(-1, keepdim=True) + eps) * nw.double()
+    want = h @ w.double().T
+    got = ops.linear_decode(x, w, "f32", nw, eps)
+    torch.testing.assert_close(got.double(), want, rtol=1e-2, atol=6e-3 * want.abs().max().item())
+    got16 = ops.linear_decode(x, w, "bf16", nw, eps)
+    torch.testing.assert_close(got16.double(), want, rtol=2e-2, atol=1e-2 * want.abs().max().item())
+
+
+@pytest.mark.parametrize("M,I,K", [(1, 8192, 2048), (8, 160, 96), (16, 72, 64)])
+def test_linear_decode_gated(ops, M, I, K):
+    g = torch.Generator().manual_seed(M + I)
+    x = torch.randn(M, K, generator=g).to(DEV)
+    nw = (torch.rand(K, generator=g) + 0.5).to(DEV)
+    gate = (torch.randn(I, K, generator=g) * 0.1).to(torch.bfloat16).to(DEV)
+    up = (torch.randn(I, K, generator=g) * 0.1).to(torch.bfloat16).to(DEV)
+    w = ops.interleave_gate_up(gate, up)
+    xd = x.double()
+    h = xd * torch.rsqrt((xd * xd).mean(-1, keepdim=True) + 1e-5) * nw.double()
+    want = torch.nn.functional.silu(h @ gate.double().T) * (h @ up.double().T)
+    got = ops.linear_decode(x, w, "gated", nw, 1e-5)
+    assert got.shape == (M, I)
+    torch.testing.assert_close(got.double(), want, rtol=2e-2, atol=1e-2 * want.abs().max().item())
+
+
+@pytest.mark.parametrize("hd,nh,nkv,ps,rot,window", [(64, 32, 8, 16, 64, None), (16, 4, 2, 16, 16, None), (32, 3, 1, 8, 32, None),
+                                                      (128, 8, 1, 32, 64, None), (48, 6, 3, 4, 0, 300), (80, 34, 2, 16, 80, None)])
+def test_fused_rope_decode_attention_equals_the_separate_kernels(ops, hd, nh, nkv, ps, rot, window):
+    from types import SimpleNamespace
+    from tokasaurus_b200.parts.attention import SPLIT_KEYS, plan_attention
+    from tokasaurus_b200.parts.rope import RotaryEncoding
+
+    lens_kv = [1, 2 * ps, 2 * ps + 1, 777, 256, 257, 513]
+    B = len(lens_kv)
+    dtype = torch.bfloat16
+    n_pages = sum(-(-L // ps) for L in lens_kv) + 5
+    kc, vc, indptr, pages, K, V = make_paged(dtype, B, lens_kv, nkv, hd, ps, n_pages, seed=hd)
+    g = torch.Generator().manual_seed(11)
+    qkv = torch.randn(B, (nh + 2 * nkv) * hd, generator=g).to(dtype).to(DEV)
+    plan = plan_attention(SimpleNamespace(seq_q_len=np.ones(B, dtype=np.int32), seq_kv_len=np.asarray(lens_kv, dtype=np.int32)), window)
+    c = i32(plan["counts"])
+    n_items, n_dec = int(plan["counts"][0]), int(plan["counts"][1])
+    q_start, kv_len = i32(list(range(B))), i32(lens_kv)
+    positions, token_seq = i32([L - 1 for L in lens_kv]), i32(list(range(B)))
+    inv = RotaryEncoding(rot, 10000.0).inv_freq().to(DEV) if rot else None
+    scale = 1 / math.sqrt(hd)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    # separate kernels
+    kc1, vc1, q1 = kc.clone(), vc.clone(), qkv.clone()
+    ops.rope_kv_write(q1, positions, token_seq, indptr, pages, inv, kc1, vc1, nh, nkv, hd, rot, ps, True, status)
+    want = torch.zeros(B, nh * hd, dtype=dtype, device=DEV)
+    ops.attn_decode_mma(q1, kc1, vc1, q_start, kv_len, indptr, pages, i32(plan["items"]), c[0:1], n_items, i32(plan["dec_seqs"]),
+                        i32(plan["dec_item_start"]), c[1:2], n_dec, want, nh, nkv, hd, ps, scale, window, SPLIT_KEYS)
+    # fused
+    kc2, vc2 = kc.clone(), vc.clone()
+    got = torch.zeros_like(want)
+    ops.attn_decode_rope_mma(qkv, kc2, vc2, q_start, kv_len, indptr, pages, i32(plan["items"]), c[0:1], n_items,
+                             i32(plan["dec_seqs"]), i32(plan["dec_item_start"]), c[1:2], n_dec, got, nh, nkv, hd, ps, scale,
+                             window, SPLIT_KEYS, inv, rot, True, status)
+    assert int(status) == 0
+    assert torch.equal(vc2, vc1)
+    torch.testing.assert_close(kc2.float().nan_to_num(7.0), kc1.float().nan_to_num(7.0), rtol=1e-2, atol=1e-2)
+    torch.testing.assert_close(got.float(), want.float(), rtol=1.6e-2, atol=1e-2)

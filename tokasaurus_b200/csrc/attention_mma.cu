@@ -162,13 +162,19 @@ __device__ __forceinline__ void softmax_16keys(float (&s)[2][4], float (&m)[2], 
 
 // ------------------------------------------------------------------------------------------------
 // Decode: blockIdx.x = work item (request row, split), blockIdx.y = kv head * head_tiles + head tile.
+// FUSED: q points at the un-rotated q|k|v rows of the step [tokens, (nh + 2 nkv) * HD]; the kernel rotates
+// q on the fly, and the block that owns the split holding the token's own position rotates this kv
+// head's k, writes it and v into the cache page, and only then reads its tiles.
+template <bool FUSED>
 __global__ void __launch_bounds__(128)
-attn_decode_mma_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restrict__ kcache,
-                       const bf16* __restrict__ vcache, const int* __restrict__ seq_q_start,
+attn_decode_mma_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ kcache,
+                       bf16* __restrict__ vcache, const int* __restrict__ seq_q_start,
                        const int* __restrict__ seq_kv_len, const int* __restrict__ page_indptr,
                        const int* __restrict__ page_ids, const int* __restrict__ items,
                        const int* __restrict__ n_items_ptr, float* __restrict__ part_o, float* __restrict__ part_ml,
-                       int nh, int nkv, int ps, float scale_log2, int window, int split_keys, int head_tiles) {
+                       int nh, int nkv, int ps, float scale_log2, int window, int split_keys, int head_tiles,
+                       const float* __restrict__ inv_freq, int rot, int write_cache, int num_pages,
+                       int* __restrict__ status) {
   extern __shared__ __align__(128) unsigned char smem[];
   trigger_dependents();
   grid_dependency_wait();
@@ -192,14 +198,63 @@ attn_decode_mma_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __r
 
   // Q fragments: row r of the tile is query head g0 + r; rows >= gn are zero.
   uint32_t qf[KSTEPS][4];
+  __shared__ float cs[FUSED ? HD : 2];  // cos[rot/2], sin[rot/2] of this token's position
+  if (FUSED) {
+    const int half = rot >> 1;
+    for (int j = tid; j < half; j += 128) {
+      float sn, c;
+      sincosf((float)p * inv_freq[j], &sn, &c);
+      cs[j] = c;
+      cs[half + j] = sn;
+    }
+    __syncthreads();
+    if (write_cache && k_end == kv_len) {
+      // this block's split holds position p: put the token's own key and value into the cache first
+      // (blocks of other head tiles of the same kv head write the same bytes)
+      const int page = table[p / ps];
+      if (page < 0 || page >= num_pages) {
+        if (tid == 0) atomicOr(status, TKB_STATUS_BAD_PAGE);
+      } else {
+        const bf16* krow = q + (size_t)t * q_stride + (size_t)(nh + kvh) * HD;
+        const bf16* vrow = krow + (size_t)nkv * HD;
+        const size_t dst = (((size_t)page * nkv + kvh) * ps + (p % ps)) * HD;
+        for (int d = tid; d < HD; d += 128) {
+          float kv = __bfloat162float(krow[d]);
+          if (d < half) kv = kv * cs[d] - __bfloat162float(krow[d + half]) * cs[half + d];
+          else if (d < rot) kv = kv * cs[d - half] + __bfloat162float(krow[d - half]) * cs[d];
+          kcache[dst + d] = __float2bfloat16_rn(kv);
+          vcache[dst + d] = vrow[d];
+        }
+      }
+      __syncthreads();  // the tile loads below must see these writes
+    }
+  }
   {
     const int r = lane >> 2, cq = (lane & 3) * 2;
+    const int half = rot >> 1;
 #pragma unroll
     for (int ks = 0; ks < KSTEPS; ks++) {
 #pragma unroll
       for (int i = 0; i < 4; i++) {
         const int row = r + (i & 1) * 8, col = ks * 16 + cq + (i >> 1) * 8;
-        qf[ks][i] = row < gn ? *reinterpret_cast<const uint32_t*>(qrow + (size_t)row * HD + col) : 0u;
+        uint32_t v = 0u;
+        if (row < gn) {
+          const bf16* src = qrow + (size_t)row * HD;
+          v = *reinterpret_cast<const uint32_t*>(src + col);
+          if (FUSED && col < rot) {
+            const __nv_bfloat162 x = *reinterpret_cast<const __nv_bfloat162*>(&v);
+            const bool low = col < half;
+            const int pc = low ? col + half : col - half;   // partner column
+            const int j = low ? col : col - half;           // angle index
+            const __nv_bfloat162 y = *reinterpret_cast<const __nv_bfloat162*>(src + pc);
+            const float x0 = __bfloat162float(x.x), x1 = __bfloat162float(x.y);
+            const float y0 = __bfloat162float(y.x), y1 = __bfloat162float(y.y);
+            const float r0 = low ? x0 * cs[j] - y0 * cs[half + j] : x0 * cs[j] + y0 * cs[half + j];
+            const float r1 = low ? x1 * cs[j + 1] - y1 * cs[half + j + 1] : x1 * cs[j + 1] + y1 * cs[half + j + 1];
+            v = pack_bf16(r0, r1);
+          }
+        }
+        qf[ks][i] = v;
       }
     }
   }
@@ -429,7 +484,9 @@ static int ensure_smem_attr() {
   if (g_attr_set) return 0;
   cudaError_t e = cudaSuccess;
   if (SMEM_B > 48 * 1024) {
-    e = cudaFuncSetAttribute(attn_decode_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_B);
+    e = cudaFuncSetAttribute(attn_decode_mma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_B);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(attn_decode_mma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_B);
     if (e == cudaSuccess)
       e = cudaFuncSetAttribute(attn_prefill_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_B);
   }
@@ -460,10 +517,33 @@ TKB_EXPORT int tkb_attn_decode_mma_bf16(const void* q, int q_stride, const void*
   const int head_tiles = (group + 15) / 16;
   if ((long long)nkv * head_tiles > 65535) return -3;
   dim3 grid(items_cap, nkv * head_tiles);
-  return launch_pdl(attn_decode_mma_kernel, grid, dim3(128), (size_t)SMEM_B, (cudaStream_t)st, (const bf16*)q, q_stride,
-                    (const bf16*)kcache, (const bf16*)vcache, seq_q_start, seq_kv_len, page_indptr, page_ids, items,
+  return launch_pdl(attn_decode_mma_kernel<false>, grid, dim3(128), (size_t)SMEM_B, (cudaStream_t)st, (const bf16*)q,
+                    q_stride, (bf16*)kcache, (bf16*)vcache, seq_q_start, seq_kv_len, page_indptr, page_ids, items,
                     n_items_ptr, part_o, part_ml, nh, nkv, ps, scale * 1.4426950408889634f, window, split_keys,
-                    head_tiles);
+                    head_tiles, (const float*)nullptr, 0, 0, 0, (int*)nullptr);
+}
+
+// The same with rotary encoding and the cache write folded in: qkv holds the step's un-rotated q|k|v rows
+// [tokens, (nh + 2 nkv) * HD]; rot is the rotary width (0: none); the pages of the requests must already
+// cover the tokens' positions.
+TKB_EXPORT int tkb_attn_decode_rope_mma_bf16(const void* qkv, int q_stride, void* kcache, void* vcache,
+                                             const int* seq_q_start, const int* seq_kv_len, const int* page_indptr,
+                                             const int* page_ids, const int* items, const int* n_items_ptr,
+                                             int items_cap, float* part_o, float* part_ml, int nh, int nkv, int ps,
+                                             float scale, int window, int split_keys, const float* inv_freq, int rot,
+                                             int write_cache, int num_pages, int* status, void* st) {
+  if (items_cap <= 0) return 0;
+  if (nkv <= 0 || nh % nkv != 0 || ps <= 0 || split_keys <= 0 || rot < 0 || rot > HD || (rot & 3)) return -2;
+  int rc = ensure_smem_attr();
+  if (rc) return rc;
+  const int group = nh / nkv;
+  const int head_tiles = (group + 15) / 16;
+  if ((long long)nkv * head_tiles > 65535) return -3;
+  dim3 grid(items_cap, nkv * head_tiles);
+  return launch_pdl(attn_decode_mma_kernel<true>, grid, dim3(128), (size_t)SMEM_B, (cudaStream_t)st, (const bf16*)qkv,
+                    q_stride, (bf16*)kcache, (bf16*)vcache, seq_q_start, seq_kv_len, page_indptr, page_ids, items,
+                    n_items_ptr, part_o, part_ml, nh, nkv, ps, scale * 1.4426950408889634f, window, split_keys,
+                    head_tiles, inv_freq, rot, write_cache, num_pages, status);
 }
 
 TKB_EXPORT int tkb_attn_decode_merge_bf16(const float* part_o, const float* part_ml, const int* dec_seqs,

@@ -171,6 +171,44 @@ def rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, token_seq: torch.T
 
 
 SMALL_M_MAX = 64
+DECODE_M_MAX = 16
+_EPILOGUES = {"bf16": 0, "add": 1, "gated": 2, "f32": 3}
+
+
+def can_use_linear_decode(a: torch.Tensor, w: torch.Tensor) -> bool:
+    return (w.dtype == torch.bfloat16 and a.dtype in (torch.bfloat16, torch.float32) and 0 < a.shape[0] <= DECODE_M_MAX
+            and a.shape[1] % 8 == 0 and a.stride(0) % 8 == 0 and w.stride(0) % 8 == 0 and a.stride(1) == 1)
+
+
+def linear_decode(a: torch.Tensor, w: torch.Tensor, epilogue: str = "bf16", norm_weight: torch.Tensor | None = None,
+                  eps: float = 0.0, out: torch.Tensor | None = None) -> torch.Tensor:
+    """Fused product for at most 16 rows: ``prologue(a) @ w^T`` with the epilogue applied in the same kernel.
+
+    ``a``: bfloat16 [M, K], or the float32 residual stream [M, K] with ``norm_weight`` (an RMS norm is
+    folded in).  ``epilogue``: "bf16" store; "f32" store; "add" adds into the float32 ``out`` [M, N] in place;
+    "gated": ``w`` interleaves gate/up rows (``interleave_gate_up``), result silu(gate)*up [M, N/2]."""
+    _need_cuda(a, w, norm_weight, out)
+    _need(can_use_linear_decode(a, w), "linear_decode: at most 16 rows, bfloat16 weights, K a multiple of 8")
+    M, K = a.shape
+    N = w.shape[0]
+    _need(w.shape[1] == K, "linear_decode: shapes")
+    pro = 1 if a.dtype == torch.float32 else 0
+    _need((pro == 1) == (norm_weight is not None), "linear_decode: a float32 input goes with a norm weight")
+    if pro:
+        _need(norm_weight.dtype == torch.float32 and norm_weight.numel() == K, "linear_decode: norm weight float32 [K]")
+    epi = _EPILOGUES[epilogue]
+    if epilogue == "add":
+        _need(out is not None and out.dtype == torch.float32 and tuple(out.shape) == (M, N) and out.stride(1) == 1,
+              "linear_decode: 'add' needs the float32 stream [M, N]")
+    elif epilogue == "gated":
+        _need(N % 16 == 0, "linear_decode: gated weights come in groups of 16 rows")
+        out = torch.empty((M, N // 2), dtype=torch.bfloat16, device=a.device)
+    else:
+        out = torch.empty((M, N), dtype=torch.bfloat16 if epilogue == "bf16" else torch.float32, device=a.device)
+    _check(_fn(_libs.get("linear_decode.cu"), "tkb_linear_decode_bf16")(
+        _ptr(a), c_int(a.stride(0)), _ptr(norm_weight), c_float(eps), _ptr(w), c_int(w.stride(0)), _ptr(out),
+        c_int(out.stride(0)), c_int(M), c_int(N), c_int(K), c_int(pro), c_int(epi), _stream()), "linear_decode")
+    return out
 
 
 def can_use_smallm(a: torch.Tensor, w: torch.Tensor) -> bool:
@@ -316,6 +354,41 @@ def attn_decode_mma(qkv: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tenso
         _ptr(page_indptr), _ptr(page_ids), _ptr(items), _ptr(n_items), c_int(items_cap), _ptr(part_o), _ptr(part_ml),
         c_int(n_heads), c_int(n_kv_heads), c_int(page_size), c_float(scale), c_int(window or 0), c_int(split_keys),
         _stream()), "attn_decode_mma")
+    _check(_fn(lib, "tkb_attn_decode_merge_bf16")(
+        _ptr(part_o), _ptr(part_ml), _ptr(dec_seqs), _ptr(dec_item_start), _ptr(n_dec), c_int(dec_cap),
+        _ptr(seq_q_start), _ptr(out), c_int(out.shape[1]), c_int(n_heads), _stream()), "attn_decode_merge")
+
+
+def attn_decode_rope_mma(qkv: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, seq_q_start: torch.Tensor,
+                         seq_kv_len: torch.Tensor, page_indptr: torch.Tensor, page_ids: torch.Tensor,
+                         items: torch.Tensor, n_items: torch.Tensor, items_cap: int, dec_seqs: torch.Tensor,
+                         dec_item_start: torch.Tensor, n_dec: torch.Tensor, dec_cap: int, out: torch.Tensor,
+                         n_heads: int, n_kv_heads: int, head_dim: int, page_size: int, scale: float,
+                         window: int | None, split_keys: int, inv_freq: torch.Tensor | None, rotary_dim: int,
+                         write_cache: bool, status: torch.Tensor) -> None:
+    """``attn_decode_mma`` with rotary encoding and the cache write folded in: ``qkv`` holds the step's
+    un-rotated q|k|v rows [T, (n_heads + 2 n_kv_heads) * head_dim] of requests that bring one token each."""
+    _need_cuda(qkv, kcache, vcache, seq_q_start, seq_kv_len, page_indptr, page_ids, items, n_items, dec_seqs,
+               dec_item_start, n_dec, out, inv_freq, status)
+    check_head_dim(head_dim)
+    _need(qkv.dtype == torch.bfloat16 and kcache.dtype == torch.bfloat16 and out.dtype == torch.bfloat16,
+          "attn_decode_rope_mma: bfloat16 only")
+    _need(qkv.is_contiguous() and qkv.shape[1] == (n_heads + 2 * n_kv_heads) * head_dim, "attn_decode_rope_mma: qkv")
+    _need(tuple(kcache.shape[1:]) == (n_kv_heads, page_size, head_dim), "attn_decode_rope_mma: cache layout")
+    _need(out.is_contiguous() and out.shape[1] == n_heads * head_dim, "attn_decode_rope_mma: out")
+    _need(rotary_dim % 4 == 0 and 0 <= rotary_dim <= head_dim, "attn_decode_rope_mma: rotary_dim")
+    if rotary_dim:
+        _need(inv_freq is not None and inv_freq.dtype == torch.float32 and inv_freq.numel() == rotary_dim // 2,
+              "attn_decode_rope_mma: inv_freq")
+    lib = _libs.get("attention_mma.cu", TKB_HD=head_dim)
+    part_o = torch.empty((items_cap, n_heads, head_dim), dtype=torch.float32, device=qkv.device)
+    part_ml = torch.empty((items_cap, n_heads, 2), dtype=torch.float32, device=qkv.device)
+    _check(_fn(lib, "tkb_attn_decode_rope_mma_bf16")(
+        _ptr(qkv), c_int(qkv.shape[1]), _ptr(kcache), _ptr(vcache), _ptr(seq_q_start), _ptr(seq_kv_len),
+        _ptr(page_indptr), _ptr(page_ids), _ptr(items), _ptr(n_items), c_int(items_cap), _ptr(part_o), _ptr(part_ml),
+        c_int(n_heads), c_int(n_kv_heads), c_int(page_size), c_float(scale), c_int(window or 0), c_int(split_keys),
+        _ptr(inv_freq), c_int(rotary_dim), c_int(1 if write_cache else 0), c_int(kcache.shape[0]), _ptr(status),
+        _stream()), "attn_decode_rope_mma")
     _check(_fn(lib, "tkb_attn_decode_merge_bf16")(
         _ptr(part_o), _ptr(part_ml), _ptr(dec_seqs), _ptr(dec_item_start), _ptr(n_dec), c_int(dec_cap),
         _ptr(seq_q_start), _ptr(out), c_int(out.shape[1]), c_int(n_heads), _stream()), "attn_decode_merge")

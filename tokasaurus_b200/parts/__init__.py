@@ -1,5 +1,6 @@
 from tokasaurus_b200.parts.base import (  # noqa: F401
     FeedForward,
+    LazyNorm,
     Mixer,
     Norm,
     PagedCacheNeed,

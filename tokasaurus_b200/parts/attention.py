@@ -19,7 +19,7 @@ import numpy as np
 import torch
 
 from tokasaurus_b200.kernels import ops
-from tokasaurus_b200.parts.base import Mixer, PagedCacheNeed, PositionEncoding, WeightSpec
+from tokasaurus_b200.parts.base import LazyNorm, Mixer, PagedCacheNeed, PositionEncoding, WeightSpec
 
 SPLIT_KEYS = 256  # keys per work item of the split-key kernel; fixed, so a request's result does not depend on the batch
 QUERY_TILE = 64  # queries per block of the tiled kernel
@@ -60,6 +60,8 @@ def plan_attention(host, window: int | None, capacity: dict | None = None) -> di
 
 class PagedAttention(Mixer):
     graph_safe = True
+    takes_lazy_norm = True
+    adds_residual = True
 
     def __init__(self, width: int, n_heads: int, n_kv_heads: int, head_dim: int, position: PositionEncoding,
                  q_name: str, k_name: str, v_name: str, o_name: str, window: int | None = None,
@@ -111,11 +113,33 @@ class PagedAttention(Mixer):
         return self.plan_key(), plan_attention(host, self.window, capacity)
 
     # --- one step ---
-    def forward(self, ctx, h: torch.Tensor, cache, out_rows=None) -> torch.Tensor:
+    def forward(self, ctx, h, cache, out_rows=None, residual: torch.Tensor | None = None):
         T = h.shape[0]
         hd, nh, nkv = self.head_dim, self.n_heads, self.n_kv_heads
         tables = ctx.tables[cache.group]
         rot = self.position.rotary_dim if self.position.kind == "rotary" else 0
+        if isinstance(h, LazyNorm):
+            plan = ctx.plans.get(self.plan_key())
+            counts = ctx.host_plans[self.plan_key()]["counts"] if plan is not None else None
+            if (plan is not None and out_rows is None and int(counts[2]) == 0 and int(counts[1]) > 0 and rot % 4 == 0
+                    and ops.can_use_linear_decode(h.x, self.w_qkv) and (nh * hd) % 8 == 0):
+                # every request brings one token: norm + q|k|v product, then rotary + cache write +
+                # split-key attention, merge, output product + residual add: four kernels
+                qkv = ops.linear_decode(h.x, self.w_qkv, "bf16", h.weight, h.eps)
+                attn = torch.empty((T, nh * hd), dtype=qkv.dtype, device=qkv.device)
+                caps = ctx.plan_caps.get(self.plan_key()) if ctx.plan_caps else None
+                c = plan["counts"]
+                ops.attn_decode_rope_mma(qkv, cache.k, cache.v, ctx.seq_q_start, ctx.seq_kv_len, tables.indptr,
+                                         tables.page_ids, plan["items"], c[0:1], caps["items"] if caps else int(counts[0]),
+                                         plan["dec_seqs"], plan["dec_item_start"], c[1:2],
+                                         caps["dec"] if caps else int(counts[1]), attn, nh, nkv, hd, cache.page_size,
+                                         self.scale, self.window, SPLIT_KEYS, self.inv_freq, rot, cache.writable,
+                                         ctx.status)
+                if residual is not None:
+                    ops.linear_decode(attn, self.w_o, "add", out=residual)
+                    return None
+                return ops.linear_decode(attn, self.w_o, "bf16")
+            h = h.materialize()
         small = (ops.can_use_smallm(h, self.w_qkv) and (nh * hd) % 8 == 0
                  and (self.w_qkv.shape[0] + max(rot, 2)) * 4 <= 48 * 1024)
         if small:

@@ -7,10 +7,13 @@ from __future__ import annotations
 import torch
 
 from tokasaurus_b200.kernels import ops
-from tokasaurus_b200.parts.base import FeedForward, WeightSpec
+from tokasaurus_b200.parts.base import FeedForward, LazyNorm, WeightSpec
 
 
 class GatedMLP(FeedForward):
+    takes_lazy_norm = True
+    adds_residual = True
+
     def __init__(self, width: int, inner: int, gate_name: str, up_name: str, down_name: str):
         self.width = width
         self.inner = inner
@@ -38,9 +41,18 @@ class GatedMLP(FeedForward):
             self.w_gate_up = torch.cat([weights[g], weights[u]], dim=0).contiguous()
         self.w_down = weights[d].contiguous()
 
-    def forward(self, ctx, h: torch.Tensor) -> torch.Tensor:
+    def forward(self, ctx, h, residual: torch.Tensor | None = None):
         """Returns the update [rows, width] in h's dtype, or as float32 slices [slices, rows, width]
-        that the next norm adds (few rows, bfloat16)."""
+        that the next norm adds (few rows, bfloat16); or None after adding the update to ``residual``
+        (at most 16 rows, bfloat16: norm, both products, gate and residual add in two kernels)."""
+        if isinstance(h, LazyNorm):
+            if self.interleave and ops.can_use_linear_decode(h.x, self.w_gate_up):
+                act = ops.linear_decode(h.x, self.w_gate_up, "gated", h.weight, h.eps)
+                if residual is not None:
+                    ops.linear_decode(act, self.w_down, "add", out=residual)
+                    return None
+                return ops.linear_decode(act, self.w_down, "bf16")
+            h = h.materialize()
         if self.interleave and ops.can_use_smallm(h, self.w_gate_up) and self.inner % 8 == 0:
             act = ops.linear_smallm_gated(h, self.w_gate_up)
             return ops.linear_smallm(act, self.w_down)
