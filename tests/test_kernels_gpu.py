@@ -279,8 +279,8 @@ def test_sampling_greedy_and_logprob(ops):
         assert last.tolist() == [int(ids[2]), int(ids[3]), int(ids[4]), -1, int(ids[0]), -1, -1, -1]
 
 
-def test_sampling_matches_plain_gumbel_draw(ops):
-    V = 1003
+@pytest.mark.parametrize("V", [1003, 150001])
+def test_sampling_matches_plain_gumbel_draw(ops, V):
     g = torch.Generator().manual_seed(3)
     logits = (torch.randn(6, V, generator=g) * 2).to(DEV)
     temp = torch.tensor([0.7, 1.0, 0.0, 1.5, 0.7, 0.7], device=DEV)
@@ -598,3 +598,15 @@ def test_fused_rope_decode_attention_equals_the_separate_kernels(ops, hd, nh, nk
     assert torch.equal(vc2, vc1)
     torch.testing.assert_close(kc2.float().nan_to_num(7.0), kc1.float().nan_to_num(7.0), rtol=1e-2, atol=1e-2)
     torch.testing.assert_close(got.float(), want.float(), rtol=1.6e-2, atol=1e-2)
+    # the same rows given as three float32 slices that add up to them
+    parts = torch.randn(3, *qkv.shape, generator=g).to(DEV)
+    parts[2] = qkv.float() - parts[0] - parts[1]
+    qsum = parts.sum(0).to(dtype)
+    kc3, vc3 = kc.clone(), vc.clone()
+    got3 = torch.zeros_like(want)
+    ops.attn_decode_rope_mma(parts, kc3, vc3, q_start, kv_len, indptr, pages, i32(plan["items"]), c[0:1], n_items,
+                             i32(plan["dec_seqs"]), i32(plan["dec_item_start"]), c[1:2], n_dec, got3, nh, nkv, hd, ps, scale,
+                             window, SPLIT_KEYS, inv, rot, True, status)
+    if torch.equal(qsum, qkv):
+        assert torch.equal(got3, got) and torch.equal(kc3.nan_to_num(7.0), kc2.nan_to_num(7.0))
+    torch.testing.assert_close(got3.float(), want.float(), rtol=3e-2, atol=3e-2)

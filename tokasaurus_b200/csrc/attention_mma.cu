@@ -34,7 +34,11 @@ constexpr int ROWB = HD * 2 + 16;     // bytes per padded row
 constexpr int CPR = HD / 8;           // 16-byte chunks per row
 constexpr int TILE_B = KT * ROWB;     // bytes of one K or V tile
 constexpr int STAGE_B = 2 * TILE_B;   // K tile then V tile
-constexpr int SMEM_B = 2 * STAGE_B;   // two stages
+constexpr int SMEM_B = 2 * STAGE_B;   // two stages (tiled kernel for portions)
+// The split-key kernel keeps as many tiles in flight as fit: with 256 keys a split, four stages put a whole
+// split on its way at once, which is what a memory-bound kernel with few blocks per SM needs.
+constexpr int DSTAGES = 4 * STAGE_B <= 80 * 1024 ? 4 : (3 * STAGE_B <= 110 * 1024 ? 3 : 2);
+constexpr int DEC_SMEM_B = DSTAGES * STAGE_B;
 constexpr int KSTEPS = HD / 16;       // k-steps of Q.K^T
 constexpr int DTILES = HD / 8;        // n-tiles of P.V
 constexpr float NEG_BIG = -1.0e30f;   // finite stand-in for -inf in running maxima
@@ -174,7 +178,8 @@ attn_decode_mma_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restric
                        const int* __restrict__ n_items_ptr, float* __restrict__ part_o, float* __restrict__ part_ml,
                        int nh, int nkv, int ps, float scale_log2, int window, int split_keys, int head_tiles,
                        const float* __restrict__ inv_freq, int rot, int write_cache, int num_pages,
-                       int* __restrict__ status) {
+                       int* __restrict__ status, const float* __restrict__ qkv_parts, int n_parts,
+                       long long part_stride) {
   extern __shared__ __align__(128) unsigned char smem[];
   trigger_dependents();
   grid_dependency_wait();
@@ -198,7 +203,8 @@ attn_decode_mma_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restric
 
   // Q fragments: row r of the tile is query head g0 + r; rows >= gn are zero.
   uint32_t qf[KSTEPS][4];
-  __shared__ float cs[FUSED ? HD : 2];  // cos[rot/2], sin[rot/2] of this token's position
+  __shared__ float cs[FUSED ? HD : 2];               // cos[rot/2], sin[rot/2] of this token's position
+  __shared__ float srow[FUSED ? 18 * HD : 2];        // the token's q rows of this head tile, then its k and v row
   if (FUSED) {
     const int half = rot >> 1;
     for (int j = tid; j < half; j += 128) {
@@ -206,6 +212,21 @@ attn_decode_mma_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restric
       sincosf((float)p * inv_freq[j], &sn, &c);
       cs[j] = c;
       cs[half + j] = sn;
+    }
+    // gather q (gn heads), k and v of this kv head as the activation type would hold them
+    const int C = (nh + 2 * nkv) * HD;
+    for (int idx = tid; idx < (gn + 2) * HD; idx += 128) {
+      const int r = idx / HD, d = idx - r * HD;
+      const int col = r < gn ? (kvh * group + g0 + r) * HD + d : (r == gn ? (nh + kvh) * HD + d : (nh + nkv + kvh) * HD + d);
+      float v;
+      if (n_parts > 0) {
+        v = 0.f;
+        for (int pi = 0; pi < n_parts; pi++) v += qkv_parts[(size_t)pi * part_stride + (size_t)t * C + col];
+        v = __bfloat162float(__float2bfloat16_rn(v));
+      } else {
+        v = __bfloat162float(q[(size_t)t * q_stride + col]);
+      }
+      srow[(r < gn ? r : 16 + (r - gn)) * HD + d] = v;
     }
     __syncthreads();
     if (write_cache && k_end == kv_len) {
@@ -215,15 +236,15 @@ attn_decode_mma_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restric
       if (page < 0 || page >= num_pages) {
         if (tid == 0) atomicOr(status, TKB_STATUS_BAD_PAGE);
       } else {
-        const bf16* krow = q + (size_t)t * q_stride + (size_t)(nh + kvh) * HD;
-        const bf16* vrow = krow + (size_t)nkv * HD;
+        const float* krow = srow + 16 * HD;
+        const float* vrow = srow + 17 * HD;
         const size_t dst = (((size_t)page * nkv + kvh) * ps + (p % ps)) * HD;
         for (int d = tid; d < HD; d += 128) {
-          float kv = __bfloat162float(krow[d]);
-          if (d < half) kv = kv * cs[d] - __bfloat162float(krow[d + half]) * cs[half + d];
-          else if (d < rot) kv = kv * cs[d - half] + __bfloat162float(krow[d - half]) * cs[d];
+          float kv = krow[d];
+          if (d < half) kv = kv * cs[d] - krow[d + half] * cs[half + d];
+          else if (d < rot) kv = kv * cs[d - half] + krow[d - half] * cs[d];
           kcache[dst + d] = __float2bfloat16_rn(kv);
-          vcache[dst + d] = vrow[d];
+          vcache[dst + d] = __float2bfloat16_rn(vrow[d]);
         }
       }
       __syncthreads();  // the tile loads below must see these writes
@@ -239,18 +260,19 @@ attn_decode_mma_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restric
         const int row = r + (i & 1) * 8, col = ks * 16 + cq + (i >> 1) * 8;
         uint32_t v = 0u;
         if (row < gn) {
-          const bf16* src = qrow + (size_t)row * HD;
-          v = *reinterpret_cast<const uint32_t*>(src + col);
-          if (FUSED && col < rot) {
-            const __nv_bfloat162 x = *reinterpret_cast<const __nv_bfloat162*>(&v);
-            const bool low = col < half;
-            const int pc = low ? col + half : col - half;   // partner column
-            const int j = low ? col : col - half;           // angle index
-            const __nv_bfloat162 y = *reinterpret_cast<const __nv_bfloat162*>(src + pc);
-            const float x0 = __bfloat162float(x.x), x1 = __bfloat162float(x.y);
-            const float y0 = __bfloat162float(y.x), y1 = __bfloat162float(y.y);
-            const float r0 = low ? x0 * cs[j] - y0 * cs[half + j] : x0 * cs[j] + y0 * cs[half + j];
-            const float r1 = low ? x1 * cs[j + 1] - y1 * cs[half + j + 1] : x1 * cs[j + 1] + y1 * cs[half + j + 1];
+          if (!FUSED) {
+            v = *reinterpret_cast<const uint32_t*>(qrow + (size_t)row * HD + col);
+          } else {
+            const float* src = srow + row * HD;
+            float r0 = src[col], r1 = src[col + 1];
+            if (col < rot) {
+              const bool low = col < half;
+              const int pc = low ? col + half : col - half;   // partner column
+              const int j = low ? col : col - half;           // angle index
+              const float y0 = src[pc], y1 = src[pc + 1];
+              r0 = low ? r0 * cs[j] - y0 * cs[half + j] : r0 * cs[j] + y0 * cs[half + j];
+              r1 = low ? r1 * cs[j + 1] - y1 * cs[half + j + 1] : r1 * cs[j + 1] + y1 * cs[half + j + 1];
+            }
             v = pack_bf16(r0, r1);
           }
         }
@@ -267,15 +289,22 @@ attn_decode_mma_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restric
   const int lim_lo[2] = {k_begin, k_begin}, lim_hi[2] = {k_end - 1, k_end - 1};
 
   const int n_tiles = (k_end - k_begin + KT - 1) / KT;
-  if (n_tiles > 0) load_kv_tile(smem, kcache, vcache, table, kvh, nkv, ps, k_begin, k_begin, k_end, tid, 128);
-  cp_async_commit();
-  for (int it = 0; it < n_tiles; it++) {
-    unsigned char* cur = smem + (it & 1) * STAGE_B;
-    if (it + 1 < n_tiles)
-      load_kv_tile(smem + ((it + 1) & 1) * STAGE_B, kcache, vcache, table, kvh, nkv, ps, k_begin + (it + 1) * KT,
-                   k_begin, k_end, tid, 128);
+#pragma unroll
+  for (int st = 0; st < DSTAGES - 1; st++) {
+    if (st < n_tiles)
+      load_kv_tile(smem + st * STAGE_B, kcache, vcache, table, kvh, nkv, ps, k_begin + st * KT, k_begin, k_end, tid, 128);
     cp_async_commit();
-    cp_async_wait<1>();
+  }
+  for (int it = 0; it < n_tiles; it++) {
+    unsigned char* cur = smem + (it % DSTAGES) * STAGE_B;
+    {
+      const int nxt = it + DSTAGES - 1;
+      if (nxt < n_tiles)
+        load_kv_tile(smem + (nxt % DSTAGES) * STAGE_B, kcache, vcache, table, kvh, nkv, ps, k_begin + nxt * KT, k_begin,
+                     k_end, tid, 128);
+      cp_async_commit();
+    }
+    cp_async_wait<DSTAGES - 1>();
     __syncthreads();
     const int key0 = k_begin + it * KT + warp * 16;
     if (key0 < k_end) {  // warp-uniform: this warp's 16 keys hold at least one live key
@@ -484,11 +513,12 @@ static int ensure_smem_attr() {
   if (g_attr_set) return 0;
   cudaError_t e = cudaSuccess;
   if (SMEM_B > 48 * 1024) {
-    e = cudaFuncSetAttribute(attn_decode_mma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_B);
+    e = cudaFuncSetAttribute(attn_prefill_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_B);
+  }
+  if (e == cudaSuccess && DEC_SMEM_B > 48 * 1024) {
+    e = cudaFuncSetAttribute(attn_decode_mma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, DEC_SMEM_B);
     if (e == cudaSuccess)
-      e = cudaFuncSetAttribute(attn_decode_mma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_B);
-    if (e == cudaSuccess)
-      e = cudaFuncSetAttribute(attn_prefill_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_B);
+      e = cudaFuncSetAttribute(attn_decode_mma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, DEC_SMEM_B);
   }
   if (e != cudaSuccess) return (int)e;
   g_attr_set = true;
@@ -517,16 +547,19 @@ TKB_EXPORT int tkb_attn_decode_mma_bf16(const void* q, int q_stride, const void*
   const int head_tiles = (group + 15) / 16;
   if ((long long)nkv * head_tiles > 65535) return -3;
   dim3 grid(items_cap, nkv * head_tiles);
-  return launch_pdl(attn_decode_mma_kernel<false>, grid, dim3(128), (size_t)SMEM_B, (cudaStream_t)st, (const bf16*)q,
+  return launch_pdl(attn_decode_mma_kernel<false>, grid, dim3(128), (size_t)DEC_SMEM_B, (cudaStream_t)st, (const bf16*)q,
                     q_stride, (bf16*)kcache, (bf16*)vcache, seq_q_start, seq_kv_len, page_indptr, page_ids, items,
                     n_items_ptr, part_o, part_ml, nh, nkv, ps, scale * 1.4426950408889634f, window, split_keys,
-                    head_tiles, (const float*)nullptr, 0, 0, 0, (int*)nullptr);
+                    head_tiles, (const float*)nullptr, 0, 0, 0, (int*)nullptr, (const float*)nullptr, 0, 0LL);
 }
 
 // The same with rotary encoding and the cache write folded in: qkv holds the step's un-rotated q|k|v rows
-// [tokens, (nh + 2 nkv) * HD]; rot is the rotary width (0: none); the pages of the requests must already
-// cover the tokens' positions.
-TKB_EXPORT int tkb_attn_decode_rope_mma_bf16(const void* qkv, int q_stride, void* kcache, void* vcache,
+// [tokens, (nh + 2 nkv) * HD] in bfloat16, or (n_parts > 0) qkv_parts holds them as float32 slices of a
+// K-split product, [n_parts][tokens, C] spaced part_stride floats apart, which are added in order and
+// rounded to bfloat16 first.  rot is the rotary width (0: none); the pages of the requests must
+// already cover the tokens' positions.
+TKB_EXPORT int tkb_attn_decode_rope_mma_bf16(const void* qkv, int q_stride, const float* qkv_parts, int n_parts,
+                                             long long part_stride, void* kcache, void* vcache,
                                              const int* seq_q_start, const int* seq_kv_len, const int* page_indptr,
                                              const int* page_ids, const int* items, const int* n_items_ptr,
                                              int items_cap, float* part_o, float* part_ml, int nh, int nkv, int ps,
@@ -540,10 +573,10 @@ TKB_EXPORT int tkb_attn_decode_rope_mma_bf16(const void* qkv, int q_stride, void
   const int head_tiles = (group + 15) / 16;
   if ((long long)nkv * head_tiles > 65535) return -3;
   dim3 grid(items_cap, nkv * head_tiles);
-  return launch_pdl(attn_decode_mma_kernel<true>, grid, dim3(128), (size_t)SMEM_B, (cudaStream_t)st, (const bf16*)qkv,
+  return launch_pdl(attn_decode_mma_kernel<true>, grid, dim3(128), (size_t)DEC_SMEM_B, (cudaStream_t)st, (const bf16*)qkv,
                     q_stride, (bf16*)kcache, (bf16*)vcache, seq_q_start, seq_kv_len, page_indptr, page_ids, items,
                     n_items_ptr, part_o, part_ml, nh, nkv, ps, scale * 1.4426950408889634f, window, split_keys,
-                    head_tiles, inv_freq, rot, write_cache, num_pages, status);
+                    head_tiles, inv_freq, rot, write_cache, num_pages, status, qkv_parts, n_parts, part_stride);
 }
 
 TKB_EXPORT int tkb_attn_decode_merge_bf16(const float* part_o, const float* part_ml, const int* dec_seqs,

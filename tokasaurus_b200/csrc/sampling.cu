@@ -224,6 +224,126 @@ topk_logprobs_kernel(const float* __restrict__ logits, const float* __restrict__
   }
 }
 
+
+// Two-stage form for large vocabularies: the vocabulary of each row is cut into `nch` chunks, one block
+// each, so that a handful of rows still fills the GPU.  part[r][c] = {best score, best index (bits),
+// running max, running sum}.  The second stage folds the chunks in chunk order.
+constexpr int CH_THREADS = 256;
+
+__global__ void __launch_bounds__(CH_THREADS)
+sample_chunk_kernel(const float* __restrict__ logits, const float* __restrict__ temperature,
+                    const unsigned long long* __restrict__ stream_key, const int* __restrict__ sample_pos,
+                    float4* __restrict__ part, int V, int nch, int groups_per_chunk) {
+  __shared__ float s_v[CH_THREADS / 32];
+  __shared__ int s_i[CH_THREADS / 32];
+  __shared__ float s_m[CH_THREADS / 32];
+  __shared__ float s_l[CH_THREADS / 32];
+  trigger_dependents();
+  grid_dependency_wait();
+  const int r = blockIdx.y, ch = blockIdx.x;
+  const float* lg = logits + (size_t)r * V;
+  const float T = temperature ? temperature[r] : 0.f;
+  const bool greedy = !(T > 0.f);
+  const float inv_t = greedy ? 1.f : 1.f / T;
+  const unsigned long long key = stream_key ? stream_key[r] : 0ull;
+  const uint2 k2 = make_uint2((uint32_t)key, (uint32_t)(key >> 32));
+  const uint32_t pos = sample_pos ? (uint32_t)sample_pos[r] : 0u;
+  const int ngroups = (V + 3) >> 2;
+  const int g_begin = ch * groups_per_chunk;
+  const int g_end = min(ngroups, g_begin + groups_per_chunk);
+  Best best = {-FLT_MAX, 0x7fffffff};
+  float m = -FLT_MAX, l = 0.f;
+  for (int g = g_begin + threadIdx.x; g < g_end; g += CH_THREADS) {
+    uint4 rnd = make_uint4(0, 0, 0, 0);
+    if (!greedy) rnd = Philox::run(make_uint4((uint32_t)g, pos, 0u, 0u), k2);
+    const uint32_t rr[4] = {rnd.x, rnd.y, rnd.z, rnd.w};
+    float z4[4];
+    if (g * 4 + 3 < V && ((((uintptr_t)lg) & 15) == 0)) {
+      const float4 v = *reinterpret_cast<const float4*>(lg + g * 4);
+      z4[0] = v.x; z4[1] = v.y; z4[2] = v.z; z4[3] = v.w;
+    } else {
+#pragma unroll
+      for (int u = 0; u < 4; u++) z4[u] = g * 4 + u < V ? lg[g * 4 + u] : -INFINITY;
+    }
+#pragma unroll
+    for (int u = 0; u < 4; u++) {
+      const int i = g * 4 + u;
+      if (i >= V) break;
+      const float z = z4[u] * inv_t;
+      if (!(z == z)) continue;
+      if (z > m) {
+        l = l * expf(m - z) + 1.f;
+        m = z;
+      } else {
+        l += expf(z - m);
+      }
+      float score = z;
+      if (!greedy) score = z - logf(-logf(uniform_open(rr[u])));
+      Best c = {score, i};
+      best = better(best, c);
+    }
+  }
+  best = warp_best(best);
+  const float wm = warp_max(m);
+  const float wl = warp_sum(l * expf(m - wm));
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (lane == 0) {
+    s_v[warp] = best.v;
+    s_i[warp] = best.i;
+    s_m[warp] = wm;
+    s_l[warp] = wl;
+  }
+  __syncthreads();
+  if (warp == 0) {
+    Best b = {-FLT_MAX, 0x7fffffff};
+    float mm = -FLT_MAX, ll = 0.f;
+    if (lane < CH_THREADS / 32) {
+      b.v = s_v[lane];
+      b.i = s_i[lane];
+      mm = s_m[lane];
+      ll = s_l[lane];
+    }
+    b = warp_best(b);
+    const float gm = warp_max(mm);
+    const float gl = warp_sum(ll * expf(mm - gm));
+    if (lane == 0) part[(size_t)r * nch + ch] = make_float4(b.v, __int_as_float(b.i), gm, gl);
+  }
+}
+
+__global__ void sample_finish_kernel(const float* __restrict__ logits, const float* __restrict__ temperature,
+                                     const float4* __restrict__ part, const int* __restrict__ row_slot,
+                                     int* __restrict__ out_ids, float* __restrict__ out_logprob,
+                                     int* __restrict__ last_token, int V, int nch) {
+  trigger_dependents();
+  grid_dependency_wait();
+  const int r = blockIdx.x;
+  const int lane = threadIdx.x;
+  Best b = {-FLT_MAX, 0x7fffffff};
+  float mm = -FLT_MAX, ll = 0.f;
+  for (int c = lane; c < nch; c += 32) {
+    const float4 p = part[(size_t)r * nch + c];
+    Best o = {p.x, __float_as_int(p.y)};
+    b = better(b, o);
+    if (p.z > mm) {
+      ll = ll * expf(mm - p.z) + p.w;
+      mm = p.z;
+    } else {
+      ll += p.w * expf(p.z - mm);
+    }
+  }
+  b = warp_best(b);
+  const float gm = warp_max(mm);
+  const float gl = warp_sum(ll * expf(mm - gm));
+  if (lane == 0) {
+    const int c = b.i < V ? b.i : 0;
+    const float T = temperature ? temperature[r] : 0.f;
+    const float inv_t = T > 0.f ? 1.f / T : 1.f;
+    out_ids[r] = c;
+    if (out_logprob) out_logprob[r] = logits[(size_t)r * V + c] * inv_t - (gm + logf(gl));
+    if (last_token && row_slot && row_slot[r] >= 0) last_token[row_slot[r]] = c;
+  }
+}
+
 }  // namespace
 
 TKB_EXPORT int tkb_sample(const float* logits, const float* temperature, const unsigned long long* stream_key,
@@ -233,6 +353,31 @@ TKB_EXPORT int tkb_sample(const float* logits, const float* temperature, const u
   if (V <= 0) return -2;
   return launch_pdl(sample_kernel, dim3(R), dim3(SAMPLE_THREADS), 0, (cudaStream_t)st, logits, temperature, stream_key,
                     sample_pos, row_slot, out_ids, out_logprob, last_token, V);
+}
+
+// The same result as tkb_sample through two kernels and `part` (R * nch float4 of scratch), for rows that
+// are too few to fill the GPU with one block each.  nch = tkb_sample_chunks(R, V).
+TKB_EXPORT int tkb_sample_chunks(int R, int V) {
+  if (R <= 0 || V < 32768) return 1;
+  int nch = (2 * 148 + R - 1) / R;
+  if (nch > 64) nch = 64;
+  const int ngroups = (V + 3) / 4;
+  if (nch > ngroups / 256) nch = ngroups / 256;
+  return nch < 1 ? 1 : nch;
+}
+
+TKB_EXPORT int tkb_sample_two_stage(const float* logits, const float* temperature, const unsigned long long* stream_key,
+                                    const int* sample_pos, const int* row_slot, int* out_ids, float* out_logprob,
+                                    int* last_token, void* part, int nch, int R, int V, void* st) {
+  if (R <= 0) return 0;
+  if (V <= 0 || nch < 1 || R > 65535) return -2;
+  const int ngroups = (V + 3) / 4;
+  const int gpc = (ngroups + nch - 1) / nch;
+  int rc = launch_pdl(sample_chunk_kernel, dim3(nch, R), dim3(CH_THREADS), 0, (cudaStream_t)st, logits, temperature,
+                      stream_key, sample_pos, (float4*)part, V, nch, gpc);
+  if (rc) return rc;
+  return launch_pdl(sample_finish_kernel, dim3(R), dim3(32), 0, (cudaStream_t)st, logits, temperature,
+                    (const float4*)part, row_slot, out_ids, out_logprob, last_token, V, nch);
 }
 
 TKB_EXPORT int tkb_topk_logprobs(const float* logits, const float* temperature, int* out_idx, float* out_lp, int R,

@@ -172,6 +172,7 @@ def rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, token_seq: torch.T
 
 SMALL_M_MAX = 64
 DECODE_M_MAX = 16
+LAZY_NORM_M_MAX = 2  # up to this many rows the norm is folded into the consumer's matrix product
 _EPILOGUES = {"bf16": 0, "add": 1, "gated": 2, "f32": 3}
 
 
@@ -367,13 +368,20 @@ def attn_decode_rope_mma(qkv: torch.Tensor, kcache: torch.Tensor, vcache: torch.
                          window: int | None, split_keys: int, inv_freq: torch.Tensor | None, rotary_dim: int,
                          write_cache: bool, status: torch.Tensor) -> None:
     """``attn_decode_mma`` with rotary encoding and the cache write folded in: ``qkv`` holds the step's
-    un-rotated q|k|v rows [T, (n_heads + 2 n_kv_heads) * head_dim] of requests that bring one token each."""
+    un-rotated q|k|v rows of requests that bring one token each, as bfloat16 [T, C] or as the float32 slices
+    [slices, T, C] of a K-split product (``linear_smallm``); C = (n_heads + 2 n_kv_heads) * head_dim."""
     _need_cuda(qkv, kcache, vcache, seq_q_start, seq_kv_len, page_indptr, page_ids, items, n_items, dec_seqs,
                dec_item_start, n_dec, out, inv_freq, status)
     check_head_dim(head_dim)
-    _need(qkv.dtype == torch.bfloat16 and kcache.dtype == torch.bfloat16 and out.dtype == torch.bfloat16,
-          "attn_decode_rope_mma: bfloat16 only")
-    _need(qkv.is_contiguous() and qkv.shape[1] == (n_heads + 2 * n_kv_heads) * head_dim, "attn_decode_rope_mma: qkv")
+    C = (n_heads + 2 * n_kv_heads) * head_dim
+    _need(kcache.dtype == torch.bfloat16 and out.dtype == torch.bfloat16, "attn_decode_rope_mma: bfloat16 only")
+    _need(qkv.is_contiguous() and qkv.shape[-1] == C, "attn_decode_rope_mma: qkv")
+    if qkv.dim() == 3:
+        _need(qkv.dtype == torch.float32, "attn_decode_rope_mma: slices are float32")
+        parts, n_parts, part_stride, qkv_ptr = qkv, qkv.shape[0], qkv.shape[1] * C, None
+    else:
+        _need(qkv.dtype == torch.bfloat16, "attn_decode_rope_mma: rows are bfloat16")
+        parts, n_parts, part_stride, qkv_ptr = None, 0, 0, qkv
     _need(tuple(kcache.shape[1:]) == (n_kv_heads, page_size, head_dim), "attn_decode_rope_mma: cache layout")
     _need(out.is_contiguous() and out.shape[1] == n_heads * head_dim, "attn_decode_rope_mma: out")
     _need(rotary_dim % 4 == 0 and 0 <= rotary_dim <= head_dim, "attn_decode_rope_mma: rotary_dim")
@@ -384,7 +392,8 @@ def attn_decode_rope_mma(qkv: torch.Tensor, kcache: torch.Tensor, vcache: torch.
     part_o = torch.empty((items_cap, n_heads, head_dim), dtype=torch.float32, device=qkv.device)
     part_ml = torch.empty((items_cap, n_heads, 2), dtype=torch.float32, device=qkv.device)
     _check(_fn(lib, "tkb_attn_decode_rope_mma_bf16")(
-        _ptr(qkv), c_int(qkv.shape[1]), _ptr(kcache), _ptr(vcache), _ptr(seq_q_start), _ptr(seq_kv_len),
+        _ptr(qkv_ptr), c_int(C), _ptr(parts), c_int(n_parts), ctypes.c_longlong(part_stride), _ptr(kcache),
+        _ptr(vcache), _ptr(seq_q_start), _ptr(seq_kv_len),
         _ptr(page_indptr), _ptr(page_ids), _ptr(items), _ptr(n_items), c_int(items_cap), _ptr(part_o), _ptr(part_ml),
         c_int(n_heads), c_int(n_kv_heads), c_int(page_size), c_float(scale), c_int(window or 0), c_int(split_keys),
         _ptr(inv_freq), c_int(rotary_dim), c_int(1 if write_cache else 0), c_int(kcache.shape[0]), _ptr(status),
@@ -426,7 +435,16 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor | None, stream_key: t
     _need(out_ids.dtype == torch.int32 and out_ids.numel() >= R, "sample: out_ids int32 [R]")
     if stream_key is not None:
         _need(stream_key.dtype == torch.int64, "sample: stream_key int64 [R]")
-    f = _fn(_libs.get("sampling.cu"), "tkb_sample")
+    lib = _libs.get("sampling.cu")
+    nch = lib.tkb_sample_chunks(c_int(R), c_int(V))
+    if nch > 1:
+        # few rows, large vocabulary: chunks of the vocabulary in parallel, then a fold in chunk order
+        part = torch.empty((R, nch, 4), dtype=torch.float32, device=logits.device)
+        _check(_fn(lib, "tkb_sample_two_stage")(
+            _ptr(logits), _ptr(temperature), _ptr(stream_key), _ptr(sample_pos), _ptr(row_slot), _ptr(out_ids),
+            _ptr(out_logprob), _ptr(last_token), _ptr(part), c_int(nch), c_int(R), c_int(V), _stream()), "sample")
+        return
+    f = _fn(lib, "tkb_sample")
     _check(f(_ptr(logits), _ptr(temperature), _ptr(stream_key), _ptr(sample_pos), _ptr(row_slot), _ptr(out_ids),
              _ptr(out_logprob), _ptr(last_token), c_int(R), c_int(V), _stream()), "sample")
 

@@ -145,6 +145,20 @@ class PagedAttention(Mixer):
         if small:
             # few rows: K-split products whose float32 slices the next kernel adds
             parts = ops.linear_smallm(h, self.w_qkv)
+            plan = ctx.plans.get(self.plan_key())
+            counts = ctx.host_plans[self.plan_key()]["counts"] if plan is not None else None
+            if plan is not None and out_rows is None and int(counts[2]) == 0 and int(counts[1]) > 0 and rot % 4 == 0:
+                # every request brings one token: the attention kernel adds the slices, rotates, writes the cache
+                attn = torch.empty((T, nh * hd), dtype=h.dtype, device=h.device)
+                caps = ctx.plan_caps.get(self.plan_key()) if ctx.plan_caps else None
+                c = plan["counts"]
+                ops.attn_decode_rope_mma(parts, cache.k, cache.v, ctx.seq_q_start, ctx.seq_kv_len, tables.indptr,
+                                         tables.page_ids, plan["items"], c[0:1], caps["items"] if caps else int(counts[0]),
+                                         plan["dec_seqs"], plan["dec_item_start"], c[1:2],
+                                         caps["dec"] if caps else int(counts[1]), attn, nh, nkv, hd, cache.page_size,
+                                         self.scale, self.window, SPLIT_KEYS, self.inv_freq, rot, cache.writable,
+                                         ctx.status)
+                return ops.linear_smallm(attn, self.w_o)
             qkv = torch.empty((T, nh * hd), dtype=h.dtype, device=h.device)  # q only; k and v go straight to the cache
             ops.rope_kv_write_partials(parts, qkv, ctx.positions, ctx.token_seq, tables.indptr, tables.page_ids,
                                        self.inv_freq, cache.k, cache.v, nh, nkv, hd, rot, cache.page_size,

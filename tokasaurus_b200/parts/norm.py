@@ -32,7 +32,7 @@ class RMSNorm(Norm):
 
     def forward(self, ctx, stream: ResidualStream, lazy_ok: bool = False):
         if (lazy_ok and stream.delta is None and self.out_dtype == torch.bfloat16
-                and 0 < stream.x.shape[0] <= ops.DECODE_M_MAX and self.width % 8 == 0):
+                and 0 < stream.x.shape[0] <= ops.LAZY_NORM_M_MAX and self.width % 8 == 0):
             # few rows and nothing to add: let the consumer fold the norm into its matrix product
             return LazyNorm(stream.x, self.weight, self.eps, self.out_dtype, self._run)
         out = self._run(stream.x, stream.delta)
