@@ -63,20 +63,12 @@ class DecodeGraphs:
         bp = next(s for s in self.sizes if s >= B)
         host = build_host_batch(entries, runner.cache)
         page_caps = [_pow2_at_least(pg.shape[0], 64) for pg in host.table_pages]
-        plans_probe = {}
-        for mixer in runner.model.mixers():
-            made = mixer.plan(host)
-            if made is not None and made[0] not in plans_probe:
-                plans_probe[made[0]] = made[1]
-        caps = {key: dict(items=_pow2_at_least(int(p["counts"][0]), 8), dec=bp, tiles=0)
-                for key, p in plans_probe.items()}
-        key = (bp, tuple(page_caps), tuple(sorted((k, c["items"]) for k, c in caps.items())))
+        planners = runner.model.planners()
+        probe = {key: m.plan(host) for key, m in planners.items()}
+        caps = {key: dict(items=_pow2_at_least(int(p["counts"][0]), 8), dec=bp, tiles=0) for key, p in probe.items()}
+        key = (bp, tuple(page_caps), tuple(sorted((str(k), c["items"]) for k, c in caps.items())))
         padded = self._padded(host, bp, page_caps)
-        plans = {}
-        for mixer in runner.model.mixers():
-            made = mixer.plan(host, caps.get(mixer.plan_key()) if hasattr(mixer, "plan_key") else None)
-            if made is not None and made[0] not in plans:
-                plans[made[0]] = made[1]
+        plans = {k: m.plan(host, caps[k]) for k, m in planners.items()}
         ex = dict(temperature=_pad(extra["temperature"], bp), stream_key=_pad(extra["stream_key"], bp),
                   sample_pos=_pad(extra["sample_pos"], bp), row_slot=_pad(extra["row_slot"], bp, -1))
         slot = self.graphs.get(key)

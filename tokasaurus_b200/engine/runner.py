@@ -98,11 +98,7 @@ class ModelRunner:
         numpy arrays (4- or 8-byte elements) that travel to the device in the same copy; their
         device views are in ``self.last_context.extra``."""
         host = build_host_batch(entries, self.cache)
-        plans = {}
-        for mixer in self.model.mixers():
-            made = mixer.plan(host)
-            if made is not None and made[0] not in plans:
-                plans[made[0]] = made[1]
+        plans = {key: mixer.plan(host) for key, mixer in self.model.planners().items()}
         ctx = StepContext(host, self.cache, self.rt.device, self.stager, extra, plans)
         self.last_upload_bytes = self.stager.bytes_last_upload
         self.last_context = ctx

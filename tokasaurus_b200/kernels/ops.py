@@ -170,7 +170,8 @@ def rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, token_seq: torch.T
              _ptr(status), _stream()), "rope_kv_write")
 
 
-SMALL_M_MAX = 64
+SMALL_M_MAX = 16   # above this many rows the library product is as fast or faster (measured on B200)
+GATED_M_MAX = 8    # the gated small-batch product wins only up to this many rows
 DECODE_M_MAX = 16
 LAZY_NORM_M_MAX = 2  # up to this many rows the norm is folded into the consumer's matrix product
 _EPILOGUES = {"bf16": 0, "add": 1, "gated": 2, "f32": 3}
@@ -212,8 +213,8 @@ def linear_decode(a: torch.Tensor, w: torch.Tensor, epilogue: str = "bf16", norm
     return out
 
 
-def can_use_smallm(a: torch.Tensor, w: torch.Tensor) -> bool:
-    return (a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and 0 < a.shape[0] <= SMALL_M_MAX
+def can_use_smallm(a: torch.Tensor, w: torch.Tensor, max_rows: int | None = None) -> bool:
+    return (a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and 0 < a.shape[0] <= (max_rows or SMALL_M_MAX)
             and a.shape[1] % 8 == 0 and a.stride(0) % 8 == 0 and w.stride(0) % 8 == 0)
 
 
@@ -221,7 +222,7 @@ def linear_smallm(a: torch.Tensor, w: torch.Tensor, max_slices: int = 8) -> torc
     """a[M, K] @ w[N, K]^T for M <= 64 in bfloat16, as float32 slices [slices, M, N] of a K-split
     product (the consumer adds the slices).  ``max_slices=1`` gives the whole product as [1, M, N]."""
     _need_cuda(a, w)
-    _need(can_use_smallm(a, w), "linear_smallm: bfloat16, M <= 64, K a multiple of 8")
+    _need(can_use_smallm(a, w, 64), "linear_smallm: bfloat16, M <= 64, K a multiple of 8")
     M, K = a.shape
     N = w.shape[0]
     _need(w.shape[1] == K and a.stride(1) == 1 and w.stride(1) == 1, "linear_smallm: shapes")
@@ -237,7 +238,7 @@ def linear_smallm_gated(a: torch.Tensor, w_interleaved: torch.Tensor) -> torch.T
     """silu(a @ gate^T) * (a @ up^T) as bfloat16 [M, I] for M <= 64; ``w_interleaved`` [2I, K] holds gate
     and up rows in groups of 8 (``interleave_gate_up``)."""
     _need_cuda(a, w_interleaved)
-    _need(can_use_smallm(a, w_interleaved) and w_interleaved.shape[0] % 16 == 0, "linear_smallm_gated: operands")
+    _need(can_use_smallm(a, w_interleaved, 64) and w_interleaved.shape[0] % 16 == 0, "linear_smallm_gated: operands")
     M, K = a.shape
     N = w_interleaved.shape[0]
     out = torch.empty((M, N // 2), dtype=torch.bfloat16, device=a.device)

@@ -28,29 +28,31 @@ QUERY_TILE = 64  # queries per block of the tiled kernel
 def plan_attention(host, window: int | None, capacity: dict | None = None) -> dict[str, np.ndarray]:
     """Work items for one step: (request row, split) pairs for requests with one token, (request
     row, first query) pairs for 64-query tiles of longer portions."""
-    q_len, kv_len = host.seq_q_len, host.seq_kv_len
-    items: list[int] = []
-    dec_seqs: list[int] = []
-    dec_start = [0]
-    tiles: list[int] = []
-    for s in range(q_len.shape[0]):
-        n, kv = int(q_len[s]), int(kv_len[s])
-        if n == 1:
-            span = min(kv, window) if window else kv
-            n_splits = max(1, -(-span // SPLIT_KEYS))
-            for j in range(n_splits):
-                items += [s, j]
-            dec_seqs.append(s)
-            dec_start.append(len(items) // 2)
-        elif n > 1:
-            for q0 in range(0, n, QUERY_TILE):
-                tiles += [s, q0]
+    q_len = np.asarray(host.seq_q_len, dtype=np.int64)
+    kv_len = np.asarray(host.seq_kv_len, dtype=np.int64)
+    dec_seqs = np.nonzero(q_len == 1)[0]
+    span = kv_len[dec_seqs]
+    if window:
+        span = np.minimum(span, window)
+    n_splits = np.maximum(1, -(-span // SPLIT_KEYS))
+    dec_start = np.concatenate([[0], np.cumsum(n_splits)])
+    n_items = int(dec_start[-1])
+    item_seq = np.repeat(dec_seqs, n_splits)
+    item_split = np.arange(n_items) - np.repeat(dec_start[:-1], n_splits)
+    items = np.stack([item_seq, item_split], axis=1).reshape(-1)
+    pre_seqs = np.nonzero(q_len > 1)[0]
+    n_tiles_seq = -(-q_len[pre_seqs] // QUERY_TILE)
+    tile_start = np.concatenate([[0], np.cumsum(n_tiles_seq)])
+    n_tiles = int(tile_start[-1])
+    tile_seq = np.repeat(pre_seqs, n_tiles_seq)
+    tile_q0 = (np.arange(n_tiles) - np.repeat(tile_start[:-1], n_tiles_seq)) * QUERY_TILE
+    tiles = np.stack([tile_seq, tile_q0], axis=1).reshape(-1)
     cap = capacity or {}
-    counts = np.asarray([len(items) // 2, len(dec_seqs), len(tiles) // 2, 0], dtype=np.int32)
+    counts = np.asarray([n_items, dec_seqs.shape[0], n_tiles, 0], dtype=np.int32)
 
     def padded(x, n):
-        a = np.zeros(max(n, len(x), 1), dtype=np.int32)
-        a[:len(x)] = x
+        a = np.zeros(max(n, x.shape[0], 1), dtype=np.int32)
+        a[: x.shape[0]] = x
         return a
 
     return dict(counts=counts, items=padded(items, 2 * cap.get("items", 0)),
@@ -105,12 +107,10 @@ class PagedAttention(Mixer):
         self.dtype = rt.dtype
 
     def plan_key(self):
-        return ("paged_attention", self.window)
+        return ("paged_attention", self.window) if self.dtype == torch.bfloat16 else None
 
     def plan(self, host, capacity=None):
-        if self.dtype != torch.bfloat16:
-            return None
-        return self.plan_key(), plan_attention(host, self.window, capacity)
+        return plan_attention(host, self.window, capacity)
 
     # --- one step ---
     def forward(self, ctx, h, cache, out_rows=None, residual: torch.Tensor | None = None):

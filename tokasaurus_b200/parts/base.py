@@ -118,12 +118,17 @@ class Mixer(Part):
     def cache_need(self) -> PagedCacheNeed | StateNeed | None:
         return None
 
-    def plan(self, host, capacity=None):
-        """Optional host-side work plan for this step: return ``(key, {name: int32 numpy array})`` or
-        None.  Mixers that return the same key share one plan; the arrays travel to the device with the
-        batch and are found at ``ctx.plans[key][name]``.  ``capacity`` (a dict or None) gives fixed
-        array sizes when the step will be captured in a CUDA graph."""
+    def plan_key(self):
+        """A hashable key if this mixer wants a host-side work plan for each step, else None.  Mixers
+        with equal keys share one plan."""
         return None
+
+    def plan(self, host, capacity=None):
+        """The plan for one step: ``{name: int32 numpy array}``, made from the step's host arrays.  The
+        arrays travel to the device with the batch and are found at ``ctx.plans[key][name]`` (host copy:
+        ``ctx.host_plans[key]``).  ``capacity`` (a dict or None) gives fixed array sizes when the step
+        is captured in a CUDA graph."""
+        return {}
 
     def forward(self, ctx: "StepContext", h: "torch.Tensor", cache, out_rows=None) -> "torch.Tensor":
         """``h`` [T, width]: normalised input rows of this step's tokens.  ``cache``: what the

@@ -53,10 +53,12 @@ class GatedMLP(FeedForward):
                     return None
                 return ops.linear_decode(act, self.w_down, "bf16")
             h = h.materialize()
-        if self.interleave and ops.can_use_smallm(h, self.w_gate_up) and self.inner % 8 == 0:
+        if self.interleave and ops.can_use_smallm(h, self.w_gate_up, ops.GATED_M_MAX):
             act = ops.linear_smallm_gated(h, self.w_gate_up)
             return ops.linear_smallm(act, self.w_down)
         gu = ops.linear(h, self.w_gate_up)
         act = torch.empty((h.shape[0], self.inner), dtype=h.dtype, device=h.device)
         ops.silu_mul(gu, act, self.interleave)
+        if ops.can_use_smallm(act, self.w_down):
+            return ops.linear_smallm(act, self.w_down)
         return ops.linear(act, self.w_down)

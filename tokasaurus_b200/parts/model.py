@@ -62,6 +62,15 @@ class DecoderModel(Part):
     def graph_safe(self) -> bool:
         return all(getattr(m, "graph_safe", False) for m in self.mixers())
 
+    def planners(self) -> dict:
+        """{plan key: one mixer that makes that plan}."""
+        out = {}
+        for m in self.mixers():
+            key = m.plan_key() if hasattr(m, "plan_key") else None
+            if key is not None and key not in out:
+                out[key] = m
+        return out
+
     def mixers(self):
         return [b.mixer for b in self.blocks]
 
