@@ -50,7 +50,8 @@ def test_embed_gather(ops, dtype, H, V):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("rows,H,eps", [(5, 96, 1e-6), (3, 2048, 1e-5), (7, 4000, 1e-2), (1, 17, 1e-5)])
+@pytest.mark.parametrize("rows,H,eps", [(5, 96, 1e-6), (3, 2048, 1e-5), (7, 4000, 1e-2), (1, 17, 1e-5), (2, 16384, 1e-5),
+                                          (3, 10240, 1e-5)])
 def test_add_rmsnorm(ops, dtype, rows, H, eps):
     g = torch.Generator().manual_seed(rows * H)
     x = (torch.randn(rows, H, generator=g) * 3).to(DEV)

@@ -60,6 +60,23 @@ TKB_EXPORT int tkb_embed_gather_bf16(const void* table, const int* ids, const in
 // x += delta (if delta is given; x is float32 and is written back), then
 // out = (x * rsqrt(mean(x^2) + eps)) * w, rounded once to the activation type.
 // One block per row.
+// 4 consecutive elements of the activation type
+__device__ __forceinline__ float4 load4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 load4(const __nv_bfloat16* p) {
+  const uint2 u = *reinterpret_cast<const uint2*>(p);
+  const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.x));
+  const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.y));
+  return make_float4(a.x, a.y, b.x, b.y);
+}
+__device__ __forceinline__ void store4(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+__device__ __forceinline__ void store4(__nv_bfloat16* p, float4 v) {
+  __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+  uint2 u;
+  u.x = *reinterpret_cast<uint32_t*>(&a);
+  u.y = *reinterpret_cast<uint32_t*>(&b);
+  *reinterpret_cast<uint2*>(p) = u;
+}
+
 template <typename T>
 __global__ void add_rmsnorm_kernel(float* __restrict__ x, const T* __restrict__ delta,
                                    const float* __restrict__ partials, int n_partials, long long partial_stride,
@@ -69,9 +86,44 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const T* __restrict__ 
   __shared__ float scratch[33];
   const size_t base = (size_t)blockIdx.x * H;
   float* xr = x + base;
+  T* orow = out + base;
   float ss = 0.f;
+  if ((H & 3) == 0) {
+    // four elements a thread and step; the first four steps' sums stay in registers for the second pass
+    constexpr int KEEP = 4;
+    const int n4 = H >> 2;
+    float4 kept[KEEP];
+    int k = 0;
+    for (int i4 = threadIdx.x; i4 < n4; i4 += blockDim.x, k++) {
+      float4 v = load4(xr + 4 * i4);
+      if (partials != nullptr) {
+        // the update arrives as float32 slices of a split matrix product: add them in slice order
+        float4 d = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int p = 0; p < n_partials; p++) {
+          const float4 q = load4(partials + (size_t)p * partial_stride + base + 4 * i4);
+          d.x += q.x; d.y += q.y; d.z += q.z; d.w += q.w;
+        }
+        v.x += d.x; v.y += d.y; v.z += d.z; v.w += d.w;
+        store4(xr + 4 * i4, v);
+      } else if (delta != nullptr) {
+        const float4 d = load4(delta + base + 4 * i4);
+        v.x += d.x; v.y += d.y; v.z += d.z; v.w += d.w;
+        store4(xr + 4 * i4, v);
+      }
+      ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+      if (k < KEEP) kept[k] = v;
+    }
+    const float total = block_sum(ss, scratch);
+    const float rstd = rsqrtf(total / (float)H + eps);
+    k = 0;
+    for (int i4 = threadIdx.x; i4 < n4; i4 += blockDim.x, k++) {
+      const float4 v = k < KEEP ? kept[k] : load4(xr + 4 * i4);
+      const float4 g = load4(w + 4 * i4);
+      store4(orow + 4 * i4, make_float4(v.x * rstd * g.x, v.y * rstd * g.y, v.z * rstd * g.z, v.w * rstd * g.w));
+    }
+    return;
+  }
   if (partials != nullptr) {
-    // the update arrives as float32 slices of a split matrix product: add them in slice order
     for (int i = threadIdx.x; i < H; i += blockDim.x) {
       float d = 0.f;
       for (int p = 0; p < n_partials; p++) d += partials[(size_t)p * partial_stride + base + i];
@@ -94,7 +146,6 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const T* __restrict__ 
   }
   const float total = block_sum(ss, scratch);
   const float rstd = rsqrtf(total / (float)H + eps);
-  T* orow = out + base;
   for (int i = threadIdx.x; i < H; i += blockDim.x) orow[i] = from_float<T>(xr[i] * rstd * w[i]);
 }
 
@@ -309,6 +360,30 @@ __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, l
                                 int interleave) {
   trigger_dependents();
   grid_dependency_wait();
+  if ((I & 7) == 0) {
+    // eight features a thread: two 4-element loads of gate, two of up
+    const long long total8 = total >> 3;
+    const int I8 = I >> 3;
+    for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total8;
+         idx += (long long)gridDim.x * blockDim.x) {
+      const long long t = idx / I8;
+      const int i = (int)(idx - t * I8) * 8;
+      const int gc = interleave ? ((i >> 3) << 4) : i;
+      const int uc = interleave ? gc + 8 : I + i;
+      const T* row = gu + t * 2 * I;
+#pragma unroll
+      for (int h = 0; h < 2; h++) {
+        const float4 g = load4(row + gc + 4 * h), u = load4(row + uc + 4 * h);
+        float4 r;
+        r.x = g.x / (1.f + expf(-g.x)) * u.x;
+        r.y = g.y / (1.f + expf(-g.y)) * u.y;
+        r.z = g.z / (1.f + expf(-g.z)) * u.z;
+        r.w = g.w / (1.f + expf(-g.w)) * u.w;
+        store4(out + t * I + i + 4 * h, r);
+      }
+    }
+    return;
+  }
   for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
        idx += (long long)gridDim.x * blockDim.x) {
     const long long t = idx / I;
@@ -326,8 +401,9 @@ static int silu_mul_launch(const void* gu, void* out, int rows, int I, int inter
   if (interleave != 0 && (interleave != 8 || (I & 7))) return -2;
   long long total = (long long)rows * I;
   if (total <= 0) return 0;
-  long long blocks = (total + 255) / 256;
+  long long blocks = (((I & 7) == 0 ? total / 8 : total) + 255) / 256;
   if (blocks > 148 * 16) blocks = 148 * 16;
+  if (blocks < 1) blocks = 1;
   return launch_pdl(silu_mul_kernel<T>, dim3((int)blocks), dim3(256), 0, st, (const T*)gu, (T*)out, total, I, interleave);
 }
 TKB_EXPORT int tkb_silu_mul_f32(const void* gu, void* out, int rows, int I, int interleave, void* st) {

@@ -335,11 +335,12 @@ def attn_decode_mma(qkv: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tenso
                     seq_kv_len: torch.Tensor, page_indptr: torch.Tensor, page_ids: torch.Tensor, items: torch.Tensor,
                     n_items: torch.Tensor, items_cap: int, dec_seqs: torch.Tensor, dec_item_start: torch.Tensor,
                     n_dec: torch.Tensor, dec_cap: int, out: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int,
-                    page_size: int, scale: float, window: int | None, split_keys: int) -> None:
+                    page_size: int, scale: float, window: int | None, split_keys: int,
+                    out_row_of: torch.Tensor | None = None) -> None:
     """bfloat16 split-key attention for requests that bring one token: ``items`` are (request row,
     split) pairs of ``split_keys`` keys each, computed into float32 partial results and merged into
-    ``out`` [T, n_heads*head_dim] at each request's token row.  ``n_items``/``n_dec`` are device
-    counters; the launch grids are sized by ``items_cap``/``dec_cap``."""
+    ``out`` [T, n_heads*head_dim] at each request's token row (or at row ``out_row_of[request]``).
+    ``n_items``/``n_dec`` are device counters; the launch grids are sized by ``items_cap``/``dec_cap``."""
     _need_cuda(qkv, kcache, vcache, seq_q_start, seq_kv_len, page_indptr, page_ids, items, n_items, dec_seqs,
                dec_item_start, n_dec, out)
     check_head_dim(head_dim)
@@ -358,7 +359,8 @@ def attn_decode_mma(qkv: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tenso
         _stream()), "attn_decode_mma")
     _check(_fn(lib, "tkb_attn_decode_merge_bf16")(
         _ptr(part_o), _ptr(part_ml), _ptr(dec_seqs), _ptr(dec_item_start), _ptr(n_dec), c_int(dec_cap),
-        _ptr(seq_q_start), _ptr(out), c_int(out.shape[1]), c_int(n_heads), _stream()), "attn_decode_merge")
+        _ptr(out_row_of if out_row_of is not None else seq_q_start), _ptr(out), c_int(out.shape[1]), c_int(n_heads),
+        _stream()), "attn_decode_merge")
 
 
 def attn_decode_rope_mma(qkv: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, seq_q_start: torch.Tensor,

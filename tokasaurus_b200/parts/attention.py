@@ -46,9 +46,31 @@ def plan_attention(host, window: int | None, capacity: dict | None = None) -> di
     n_tiles = int(tile_start[-1])
     tile_seq = np.repeat(pre_seqs, n_tiles_seq)
     tile_q0 = (np.arange(n_tiles) - np.repeat(tile_start[:-1], n_tiles_seq)) * QUERY_TILE
-    tiles = np.stack([tile_seq, tile_q0], axis=1).reshape(-1)
+    # tiles that see the most keys first: the long ones must not be left for the end of the launch
+    reach = kv_len[tile_seq] - q_len[tile_seq] + tile_q0
+    order = np.argsort(-reach, kind="stable")
+    tiles = np.stack([tile_seq[order], tile_q0[order]], axis=1).reshape(-1)
     cap = capacity or {}
-    counts = np.asarray([n_items, dec_seqs.shape[0], n_tiles, 0], dtype=np.int32)
+    # wanted rows, when they are only some of the step's rows: each is one query over the keys up to its
+    # own position, which is what the split-key kernel computes for a request that brings one token
+    extra = {}
+    n_row_items = n_rows = 0
+    rows = getattr(host, "logit_rows", None)
+    if rows is not None and capacity is None and 0 < rows.shape[0] and not (
+            rows.shape[0] == host.token_ids.shape[0] and np.array_equal(rows, np.arange(rows.shape[0]))):
+        rows = np.asarray(rows, dtype=np.int64)
+        r_kv = np.asarray(host.positions, dtype=np.int64)[rows] + 1
+        r_span = np.minimum(r_kv, window) if window else r_kv
+        r_splits = np.maximum(1, -(-r_span // SPLIT_KEYS))
+        r_start = np.concatenate([[0], np.cumsum(r_splits)])
+        n_row_items, n_rows = int(r_start[-1]), int(rows.shape[0])
+        r_item = np.repeat(np.arange(n_rows), r_splits)
+        r_split = np.arange(n_row_items) - np.repeat(r_start[:-1], r_splits)
+        i32 = lambda a: np.ascontiguousarray(a, dtype=np.int32)  # noqa: E731
+        extra = dict(row_items=i32(np.stack([r_item, r_split], axis=1).reshape(-1)), row_item_start=i32(r_start),
+                     row_token=i32(rows), row_kv_len=i32(r_kv), row_seq=i32(np.asarray(host.token_seq)[rows]),
+                     row_index=i32(np.arange(n_rows)))
+    counts = np.asarray([n_items, dec_seqs.shape[0], n_tiles, n_row_items, n_rows, 0, 0, 0], dtype=np.int32)
 
     def padded(x, n):
         a = np.zeros(max(n, x.shape[0], 1), dtype=np.int32)
@@ -57,7 +79,7 @@ def plan_attention(host, window: int | None, capacity: dict | None = None) -> di
 
     return dict(counts=counts, items=padded(items, 2 * cap.get("items", 0)),
                 dec_seqs=padded(dec_seqs, cap.get("dec", 0)), dec_item_start=padded(dec_start, cap.get("dec", 0) + 1),
-                tiles=padded(tiles, 2 * cap.get("tiles", 0)))
+                tiles=padded(tiles, 2 * cap.get("tiles", 0)), **extra)
 
 
 class PagedAttention(Mixer):
@@ -170,6 +192,18 @@ class PagedAttention(Mixer):
                               cache.k, cache.v, nh, nkv, hd, rot, cache.page_size, cache.writable, ctx.status)
             project = ops.linear
         plan = ctx.plans.get(self.plan_key()) if h.dtype == torch.bfloat16 else None
+        if plan is not None and out_rows is not None and out_rows is ctx.logit_rows and "row_items" in plan:
+            # only some rows are wanted (the last block of a step): one split-key query per wanted row
+            counts = ctx.host_plans[self.plan_key()]["counts"]
+            n_items, n_rows = int(counts[3]), int(counts[4])
+            attn = torch.empty((n_rows, nh * hd), dtype=h.dtype, device=h.device)
+            row_indptr = tables.indptr.index_select(0, plan["row_seq"])
+            c = plan["counts"]
+            ops.attn_decode_mma(qkv, cache.k, cache.v, plan["row_token"], plan["row_kv_len"], row_indptr,
+                                tables.page_ids, plan["row_items"], c[3:4], n_items, plan["row_index"],
+                                plan["row_item_start"], c[4:5], n_rows, attn, nh, nkv, hd, cache.page_size,
+                                self.scale, self.window, SPLIT_KEYS, out_row_of=plan["row_index"])
+            return project(attn, self.w_o)
         if plan is None or out_rows is not None:
             # float32, or only some rows are wanted: the FP32-pipe kernel, one warp per (row, head)
             n_rows = T if out_rows is None else out_rows.numel()
