@@ -469,21 +469,68 @@ attn_prefill_mma_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restri
     __syncthreads();
     const int tile_key0 = k_begin + it * KT;
     if (warp * 16 < rows_live && tile_key0 <= warp_hi && tile_key0 + KT - 1 >= warp_lo) {
+      // scores of the whole 64-key tile, one softmax update per row and tile
+      float sc[KT / 8][4];
 #pragma unroll
       for (int kb = 0; kb < KT / 16; kb++) {
-        const int key0 = tile_key0 + kb * 16;
-        if (key0 > warp_hi || key0 >= k_end || key0 + 15 < warp_lo) continue;  // warp-uniform
-        float sc[2][4], alpha[2];
-        uint32_t pf[4];
-        qk_16keys(sc, qf, smem_u32(cur), kb * 16, lane);
-        softmax_16keys(sc, m, l, alpha, pf, lim_lo, lim_hi, key0, scale_log2, lane);
+        float s2[2][4];
+        qk_16keys(s2, qf, smem_u32(cur), kb * 16, lane);
 #pragma unroll
-        for (int dt = 0; dt < DTILES; dt++) {
-          o[dt][0] *= alpha[0];
-          o[dt][1] *= alpha[0];
-          o[dt][2] *= alpha[1];
-          o[dt][3] *= alpha[1];
+        for (int i = 0; i < 4; i++) {
+          sc[2 * kb][i] = s2[0][i];
+          sc[2 * kb + 1][i] = s2[1][i];
         }
+      }
+      // a tile that every row of this warp sees whole needs no mask
+      const bool whole = tile_key0 + KT - 1 <= pos0 + warp * 16 && tile_key0 + KT <= k_end &&
+                         (window <= 0 || tile_key0 >= pos0 + warp * 16 + 15 - window + 1);
+      const int c0 = tile_key0 + cq;
+      float alpha[2];
+#pragma unroll
+      for (int h = 0; h < 2; h++) {
+        float mx = NEG_BIG;
+#pragma unroll
+        for (int nt = 0; nt < KT / 8; nt++)
+#pragma unroll
+          for (int e = 0; e < 2; e++) {
+            float v = sc[nt][h * 2 + e] * scale_log2;
+            if (!whole) {
+              const int key = c0 + nt * 8 + e;
+              if (key < lim_lo[h] || key > lim_hi[h]) v = -INFINITY;
+            }
+            sc[nt][h * 2 + e] = v;
+            mx = fmaxf(mx, v);
+          }
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+        const float m_new = fmaxf(m[h], mx);
+        alpha[h] = exp2f(m[h] - m_new);
+        m[h] = m_new;
+        float sum = 0.f;
+#pragma unroll
+        for (int nt = 0; nt < KT / 8; nt++)
+#pragma unroll
+          for (int e = 0; e < 2; e++) {
+            const float pr = exp2f(sc[nt][h * 2 + e] - m_new);
+            sc[nt][h * 2 + e] = pr;
+            sum += pr;
+          }
+        l[h] = l[h] * alpha[h] + sum;
+      }
+#pragma unroll
+      for (int dt = 0; dt < DTILES; dt++) {
+        o[dt][0] *= alpha[0];
+        o[dt][1] *= alpha[0];
+        o[dt][2] *= alpha[1];
+        o[dt][3] *= alpha[1];
+      }
+#pragma unroll
+      for (int kb = 0; kb < KT / 16; kb++) {
+        uint32_t pf[4];
+        pf[0] = pack_bf16(sc[2 * kb][0], sc[2 * kb][1]);
+        pf[1] = pack_bf16(sc[2 * kb][2], sc[2 * kb][3]);
+        pf[2] = pack_bf16(sc[2 * kb + 1][0], sc[2 * kb + 1][1]);
+        pf[3] = pack_bf16(sc[2 * kb + 1][2], sc[2 * kb + 1][3]);
         pv_16keys(o, pf, smem_u32(cur) + TILE_B, kb * 16, lane);
       }
     }

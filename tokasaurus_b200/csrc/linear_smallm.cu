@@ -4,7 +4,7 @@
 //   * the weight rows are the 16-row side of mma.sync m16n8k16 and the tokens the 8-column side,
 //     so a token count of 1..8 wastes nothing of W's traffic;
 //   * a block owns 64 output features and one slice of K; 64x64 weight tiles arrive through a
-//     four-stage cp.async pipeline; the grid is (feature tiles, K slices), sized by the host so that
+//     multi-stage cp.async pipeline; the grid is (feature tiles, K slices), sized by the host so that
 //     every SM holds several blocks;
 //   * K slices do not meet inside this kernel: each writes its float32 partial [slice, M, N] and the
 //     consumer (the fused add + norm kernel, or the rotary/cache-write kernel) adds the slices in a
@@ -19,7 +19,7 @@ typedef __nv_bfloat16 bf16;
 namespace {
 
 constexpr int BN = 64;               // output features per block
-constexpr int BK = 64;               // k per stage
+constexpr int BK = 128;              // k per stage
 constexpr int ROWB = BK * 2 + 16;    // padded row bytes (conflict-free ldmatrix)
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -42,17 +42,18 @@ __device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], 
 template <int NT> struct Tile {
   static constexpr int A_ROWS = NT * 8 < 16 ? 16 : NT * 8;  // token rows kept in shared memory (>= 16 for ldmatrix.x4)
   static constexpr int STAGE_B = (BN + A_ROWS) * ROWB;
-  static constexpr int STAGES = NT <= 2 ? 6 : 4;  // deep for few tokens: the weight tiles in flight are what is prefetched
+  static constexpr int STAGES = NT <= 2 ? 5 : 4;  // deep for few tokens: the weight tiles in flight are what is prefetched
   static constexpr int SMEM_B = STAGES * STAGE_B;
 };
 
 __device__ __forceinline__ void load_w(unsigned char* stage, const bf16* __restrict__ W, int ldw, int N, int n0,
                                        int k0, int k_end, int tid) {
   const uint32_t sw = smem_u32(stage);
+  constexpr int CPR = BK / 8;  // 16-byte chunks per row
 #pragma unroll
-  for (int i = 0; i < (BN * 8) / 128; i++) {
+  for (int i = 0; i < (BN * CPR) / 128; i++) {
     const int idx = tid + i * 128;
-    const int r = idx >> 3, c = idx & 7;
+    const int r = idx / CPR, c = idx % CPR;
     const int n = n0 + r, k = k0 + c * 8;
     const bool valid = n < N && k < k_end;
     cp_async16(sw + r * ROWB + c * 16, W + (valid ? (size_t)n * ldw + k : 0), valid);
@@ -63,12 +64,13 @@ template <int NT>
 __device__ __forceinline__ void load_a(unsigned char* stage, const bf16* __restrict__ A, int lda, int M, int k0,
                                        int k_end, int tid) {
   const uint32_t sa = smem_u32(stage) + BN * ROWB;
-  constexpr int A_CHUNKS = Tile<NT>::A_ROWS * 8;
+  constexpr int CPR = BK / 8;
+  constexpr int A_CHUNKS = Tile<NT>::A_ROWS * CPR;
 #pragma unroll
   for (int i = 0; i < (A_CHUNKS + 127) / 128; i++) {
     const int idx = tid + i * 128;
     if (idx < A_CHUNKS) {
-      const int r = idx >> 3, c = idx & 7;
+      const int r = idx / CPR, c = idx % CPR;
       const int k = k0 + c * 8;
       const bool valid = r < M && k < k_end;
       cp_async16(sa + r * ROWB + c * 16, A + (valid ? (size_t)r * lda + k : 0), valid);
@@ -206,7 +208,7 @@ TKB_EXPORT int tkb_linear_smallm_slices(int N, int K, int max_slices) {
   const int kblocks = (K + BK - 1) / BK;
   int s = (2 * 148 + tiles - 1) / tiles;
   if (s > max_slices) s = max_slices;
-  if (s > kblocks / 4) s = kblocks / 4;  // at least four k-blocks a slice
+  if (s > kblocks / 2) s = kblocks / 2;  // at least two k-blocks (256 k) a slice
   if (s < 1) s = 1;
   const int per = (kblocks + s - 1) / s;
   return (kblocks + per - 1) / per;
