@@ -65,6 +65,13 @@ __device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], 
                : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
                : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
+// 2^x on the special-function unit, one instruction (denormal results flush to zero, which is what a
+// softmax weight that small is worth)
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
@@ -76,14 +83,17 @@ __device__ __forceinline__ void load_kv_tile(unsigned char* stage, const bf16* _
                                              int nkv, int ps, int key_base, int key_lo, int key_hi, int tid,
                                              int nthreads) {
   const uint32_t sk = smem_u32(stage), sv = sk + TILE_B;
+  const int ps_shift = (ps & (ps - 1)) == 0 ? 31 - __clz(ps) : -1;  // page sizes that are powers of two: shifts
   for (int idx = tid; idx < KT * CPR; idx += nthreads) {
     const int r = idx / CPR, c = idx - r * CPR;
     const int key = key_base + r;
     const bool valid = key >= key_lo && key < key_hi;
     size_t off = 0;
     if (valid) {
-      const int page = table[key / ps];
-      off = (((size_t)page * nkv + kvh) * ps + (key % ps)) * HD + c * 8;
+      const int pi = ps_shift >= 0 ? key >> ps_shift : key / ps;
+      const int slot = ps_shift >= 0 ? key & (ps - 1) : key - pi * ps;
+      const int page = table[pi];
+      off = (((size_t)page * nkv + kvh) * ps + slot) * HD + c * 8;
     }
     const uint32_t d = r * ROWB + c * 16;
     cp_async16(sk + d, kcache + off, valid);
@@ -145,14 +155,14 @@ __device__ __forceinline__ void softmax_16keys(float (&s)[2][4], float (&m)[2], 
     mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
     mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
     const float m_new = fmaxf(m[h], mx);
-    alpha[h] = exp2f(m[h] - m_new);
+    alpha[h] = fast_exp2(m[h] - m_new);
     m[h] = m_new;
     float sum = 0.f;
 #pragma unroll
     for (int nt = 0; nt < 2; nt++)
 #pragma unroll
       for (int e = 0; e < 2; e++) {
-        const float p = exp2f(s[nt][h * 2 + e] - m_new);
+        const float p = fast_exp2(s[nt][h * 2 + e] - m_new);
         s[nt][h * 2 + e] = p;
         sum += p;
       }
@@ -201,9 +211,22 @@ attn_decode_mma_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restric
   const int t = seq_q_start[s];
   const bf16* qrow = q + (size_t)t * q_stride + (size_t)(kvh * group + g0) * HD;
 
+  // The first tiles of keys and values go on their way before anything else: older keys do not depend on
+  // this step.  (The token's own key, if this split holds it, is patched into the tile in shared memory.)
+  const int n_tiles = (k_end - k_begin + KT - 1) / KT;
+#pragma unroll
+  for (int st = 0; st < DSTAGES - 1; st++) {
+    if (st < n_tiles)
+      load_kv_tile(smem + st * STAGE_B, kcache, vcache, table, kvh, nkv, ps, k_begin + st * KT, k_begin, k_end, tid, 128);
+    cp_async_commit();
+  }
   // Q fragments: row r of the tile is query head g0 + r; rows >= gn are zero.
   uint32_t qf[KSTEPS][4];
   __shared__ float cs[FUSED ? HD : 2];               // cos[rot/2], sin[rot/2] of this token's position
+  __shared__ bf16 knew[FUSED ? HD : 2], vnew[FUSED ? HD : 2];  // the token's own rotated key and its value
+  // this split holds position p, and this layer call keeps its own keys (a call that reads another call's cache
+  // finds the key at p already there)
+  const bool owns_new = FUSED && write_cache && k_end == kv_len;
   __shared__ float srow[FUSED ? 18 * HD : 2];        // the token's q rows of this head tile, then its k and v row
   if (FUSED) {
     const int half = rot >> 1;
@@ -220,8 +243,14 @@ attn_decode_mma_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restric
       const int col = r < gn ? (kvh * group + g0 + r) * HD + d : (r == gn ? (nh + kvh) * HD + d : (nh + nkv + kvh) * HD + d);
       float v;
       if (n_parts > 0) {
+        const float* src = qkv_parts + (size_t)t * C + col;
+        float pv[8];
+#pragma unroll
+        for (int pi = 0; pi < 8; pi++) pv[pi] = pi < n_parts ? src[(size_t)pi * part_stride] : 0.f;  // loads in flight together
         v = 0.f;
-        for (int pi = 0; pi < n_parts; pi++) v += qkv_parts[(size_t)pi * part_stride + (size_t)t * C + col];
+#pragma unroll
+        for (int pi = 0; pi < 8; pi++) v += pv[pi];
+        for (int pi = 8; pi < n_parts; pi++) v += src[(size_t)pi * part_stride];
         v = __bfloat162float(__float2bfloat16_rn(v));
       } else {
         v = __bfloat162float(q[(size_t)t * q_stride + col]);
@@ -229,25 +258,28 @@ attn_decode_mma_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restric
       srow[(r < gn ? r : 16 + (r - gn)) * HD + d] = v;
     }
     __syncthreads();
-    if (write_cache && k_end == kv_len) {
-      // this block's split holds position p: put the token's own key and value into the cache first
-      // (blocks of other head tiles of the same kv head write the same bytes)
+    if (owns_new) {
+      // this block's split holds position p: rotate the token's own key, keep it and the value for the patch
+      // of the tile, and store them in the cache page for later steps (blocks of other head tiles of the
+      // same kv head store the same bytes)
+      const float* krow = srow + 16 * HD;
+      const float* vrow = srow + 17 * HD;
       const int page = table[p / ps];
-      if (page < 0 || page >= num_pages) {
-        if (tid == 0) atomicOr(status, TKB_STATUS_BAD_PAGE);
-      } else {
-        const float* krow = srow + 16 * HD;
-        const float* vrow = srow + 17 * HD;
-        const size_t dst = (((size_t)page * nkv + kvh) * ps + (p % ps)) * HD;
-        for (int d = tid; d < HD; d += 128) {
-          float kv = krow[d];
-          if (d < half) kv = kv * cs[d] - krow[d + half] * cs[half + d];
-          else if (d < rot) kv = kv * cs[d - half] + krow[d - half] * cs[d];
-          kcache[dst + d] = __float2bfloat16_rn(kv);
-          vcache[dst + d] = __float2bfloat16_rn(vrow[d]);
+      const bool page_ok = page >= 0 && page < num_pages;
+      if (!page_ok && tid == 0) atomicOr(status, TKB_STATUS_BAD_PAGE);
+      const size_t dst = (((size_t)(page_ok ? page : 0) * nkv + kvh) * ps + (p % ps)) * HD;
+      for (int d = tid; d < HD; d += 128) {
+        float kv = krow[d];
+        if (d < half) kv = kv * cs[d] - krow[d + half] * cs[half + d];
+        else if (d < rot) kv = kv * cs[d - half] + krow[d - half] * cs[d];
+        const bf16 kb = __float2bfloat16_rn(kv), vb = __float2bfloat16_rn(vrow[d]);
+        knew[d] = kb;
+        vnew[d] = vb;
+        if (page_ok) {
+          kcache[dst + d] = kb;
+          vcache[dst + d] = vb;
         }
       }
-      __syncthreads();  // the tile loads below must see these writes
     }
   }
   {
@@ -288,13 +320,6 @@ attn_decode_mma_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restric
   float m[2] = {NEG_BIG, NEG_BIG}, l[2] = {0.f, 0.f};
   const int lim_lo[2] = {k_begin, k_begin}, lim_hi[2] = {k_end - 1, k_end - 1};
 
-  const int n_tiles = (k_end - k_begin + KT - 1) / KT;
-#pragma unroll
-  for (int st = 0; st < DSTAGES - 1; st++) {
-    if (st < n_tiles)
-      load_kv_tile(smem + st * STAGE_B, kcache, vcache, table, kvh, nkv, ps, k_begin + st * KT, k_begin, k_end, tid, 128);
-    cp_async_commit();
-  }
   for (int it = 0; it < n_tiles; it++) {
     unsigned char* cur = smem + (it % DSTAGES) * STAGE_B;
     {
@@ -306,6 +331,17 @@ attn_decode_mma_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restric
     }
     cp_async_wait<DSTAGES - 1>();
     __syncthreads();
+    if (owns_new && it == n_tiles - 1) {
+      // the tile came from the cache as it was before this step: put the token's own key and value in
+      const int row = p - (k_begin + it * KT);
+      bf16* kt = reinterpret_cast<bf16*>(cur + row * ROWB);
+      bf16* vt = reinterpret_cast<bf16*>(cur + TILE_B + row * ROWB);
+      for (int d = tid; d < HD; d += 128) {
+        kt[d] = knew[d];
+        vt[d] = vnew[d];
+      }
+      __syncthreads();
+    }
     const int key0 = k_begin + it * KT + warp * 16;
     if (key0 < k_end) {  // warp-uniform: this warp's 16 keys hold at least one live key
       float sc[2][4], alpha[2];
@@ -488,30 +524,31 @@ attn_prefill_mma_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restri
       float alpha[2];
 #pragma unroll
       for (int h = 0; h < 2; h++) {
-        float mx = NEG_BIG;
+        // running maximum in units of the raw score (the scale is positive); one FMA and one ex2 an element
+        float mx = -INFINITY;
 #pragma unroll
         for (int nt = 0; nt < KT / 8; nt++)
 #pragma unroll
           for (int e = 0; e < 2; e++) {
-            float v = sc[nt][h * 2 + e] * scale_log2;
+            float v = sc[nt][h * 2 + e];
             if (!whole) {
               const int key = c0 + nt * 8 + e;
               if (key < lim_lo[h] || key > lim_hi[h]) v = -INFINITY;
+              sc[nt][h * 2 + e] = v;
             }
-            sc[nt][h * 2 + e] = v;
             mx = fmaxf(mx, v);
           }
         mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
         mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-        const float m_new = fmaxf(m[h], mx);
-        alpha[h] = exp2f(m[h] - m_new);
+        const float m_new = fmaxf(m[h], mx * scale_log2);  // m[] is kept in scaled units; NEG_BIG until a key is seen
+        alpha[h] = fast_exp2(m[h] - m_new);
         m[h] = m_new;
         float sum = 0.f;
 #pragma unroll
         for (int nt = 0; nt < KT / 8; nt++)
 #pragma unroll
           for (int e = 0; e < 2; e++) {
-            const float pr = exp2f(sc[nt][h * 2 + e] - m_new);
+            const float pr = fast_exp2(fmaf(sc[nt][h * 2 + e], scale_log2, -m_new));
             sc[nt][h * 2 + e] = pr;
             sum += pr;
           }
