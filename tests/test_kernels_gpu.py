@@ -351,7 +351,7 @@ def test_refusals(ops):
 def run_mma_attention(ops, lens_q, lens_kv, nh, nkv, hd, ps, window, seed, n_pages=None, fill=1e3):
     """A batch of requests with lens_q new tokens each at the end of lens_kv keys; returns (got, want)."""
     from types import SimpleNamespace
-    from tokasaurus_b200.parts.attention import SPLIT_KEYS, plan_attention
+    from tokasaurus_b200.parts.attention import plan_attention
 
     dtype = torch.bfloat16
     n_pages = n_pages or sum(-(-L // ps) for L in lens_kv) + 7
@@ -373,7 +373,7 @@ def run_mma_attention(ops, lens_q, lens_kv, nh, nkv, hd, ps, window, seed, n_pag
     if n_dec:
         ops.attn_decode_mma(qkv, kc, vc, i32(q_start), i32(lens_kv), indptr, pages, i32(plan["items"]), c[0:1], n_items,
                             i32(plan["dec_seqs"]), i32(plan["dec_item_start"]), c[1:2], n_dec, out, nh, nkv, hd, ps, scale,
-                            window, SPLIT_KEYS)
+                            window, int(plan["counts"][5]))
     if n_tiles:
         ops.attn_prefill_mma(qkv, out, kc, vc, i32(q_start), i32(lens_q), i32(lens_kv), indptr, pages, i32(plan["tiles"]),
                              c[2:3], n_tiles, nh, nkv, hd, ps, scale, window)
@@ -405,7 +405,7 @@ def test_mma_attention_finds_one_far_key(ops):
         for lens_q in ([1], [200]):
             kc, vc, indptr, pages, K, V = make_paged(torch.bfloat16, 1, [L], nkv, hd, ps, 100, seed=target)
             from types import SimpleNamespace
-            from tokasaurus_b200.parts.attention import SPLIT_KEYS, plan_attention
+            from tokasaurus_b200.parts.attention import plan_attention
             n = lens_q[0]
             plan = plan_attention(SimpleNamespace(seq_q_len=np.asarray(lens_q, dtype=np.int32),
                                                   seq_kv_len=np.asarray([L], dtype=np.int32)), None)
@@ -417,7 +417,7 @@ def test_mma_attention_finds_one_far_key(ops):
             if n == 1:
                 ops.attn_decode_mma(qkv.to(DEV), kc, vc, i32([0]), i32([L]), indptr, pages, i32(plan["items"]), c[0:1],
                                     int(plan["counts"][0]), i32(plan["dec_seqs"]), i32(plan["dec_item_start"]), c[1:2], 1,
-                                    out, nh, nkv, hd, ps, 1.0, None, SPLIT_KEYS)
+                                    out, nh, nkv, hd, ps, 1.0, None, int(plan["counts"][5]))
             else:
                 ops.attn_prefill_mma(qkv.to(DEV), out, kc, vc, i32([0]), i32(lens_q), i32([L]), indptr, pages,
                                      i32(plan["tiles"]), c[2:3], int(plan["counts"][2]), nh, nkv, hd, ps, 1.0, None)
@@ -565,7 +565,7 @@ def test_linear_decode_gated(ops, M, I, K):
                                                       (128, 8, 1, 32, 64, None), (48, 6, 3, 4, 0, 300), (80, 34, 2, 16, 80, None)])
 def test_fused_rope_decode_attention_equals_the_separate_kernels(ops, hd, nh, nkv, ps, rot, window):
     from types import SimpleNamespace
-    from tokasaurus_b200.parts.attention import SPLIT_KEYS, plan_attention
+    from tokasaurus_b200.parts.attention import plan_attention
     from tokasaurus_b200.parts.rope import RotaryEncoding
 
     lens_kv = [1, 2 * ps, 2 * ps + 1, 777, 256, 257, 513]
@@ -588,13 +588,13 @@ def test_fused_rope_decode_attention_equals_the_separate_kernels(ops, hd, nh, nk
     ops.rope_kv_write(q1, positions, token_seq, indptr, pages, inv, kc1, vc1, nh, nkv, hd, rot, ps, True, status)
     want = torch.zeros(B, nh * hd, dtype=dtype, device=DEV)
     ops.attn_decode_mma(q1, kc1, vc1, q_start, kv_len, indptr, pages, i32(plan["items"]), c[0:1], n_items, i32(plan["dec_seqs"]),
-                        i32(plan["dec_item_start"]), c[1:2], n_dec, want, nh, nkv, hd, ps, scale, window, SPLIT_KEYS)
+                        i32(plan["dec_item_start"]), c[1:2], n_dec, want, nh, nkv, hd, ps, scale, window, int(plan["counts"][5]))
     # fused
     kc2, vc2 = kc.clone(), vc.clone()
     got = torch.zeros_like(want)
     ops.attn_decode_rope_mma(qkv, kc2, vc2, q_start, kv_len, indptr, pages, i32(plan["items"]), c[0:1], n_items,
                              i32(plan["dec_seqs"]), i32(plan["dec_item_start"]), c[1:2], n_dec, got, nh, nkv, hd, ps, scale,
-                             window, SPLIT_KEYS, inv, rot, True, status)
+                             window, int(plan["counts"][5]), inv, rot, True, status)
     assert int(status) == 0
     assert torch.equal(vc2, vc1)
     torch.testing.assert_close(kc2.float().nan_to_num(7.0), kc1.float().nan_to_num(7.0), rtol=1e-2, atol=1e-2)
@@ -607,7 +607,16 @@ def test_fused_rope_decode_attention_equals_the_separate_kernels(ops, hd, nh, nk
     got3 = torch.zeros_like(want)
     ops.attn_decode_rope_mma(parts, kc3, vc3, q_start, kv_len, indptr, pages, i32(plan["items"]), c[0:1], n_items,
                              i32(plan["dec_seqs"]), i32(plan["dec_item_start"]), c[1:2], n_dec, got3, nh, nkv, hd, ps, scale,
-                             window, SPLIT_KEYS, inv, rot, True, status)
+                             window, int(plan["counts"][5]), inv, rot, True, status)
     if torch.equal(qsum, qkv):
         assert torch.equal(got3, got) and torch.equal(kc3.nan_to_num(7.0), kc2.nan_to_num(7.0))
     torch.testing.assert_close(got3.float(), want.float(), rtol=3e-2, atol=3e-2)
+    # a layer call that reads another call's cache: nothing is written, the key already in the cache at the
+    # token's position is the one that counts
+    kc4, vc4 = kc1.clone(), vc1.clone()
+    got4 = torch.zeros_like(want)
+    ops.attn_decode_rope_mma(qkv, kc4, vc4, q_start, kv_len, indptr, pages, i32(plan["items"]), c[0:1], n_items,
+                             i32(plan["dec_seqs"]), i32(plan["dec_item_start"]), c[1:2], n_dec, got4, nh, nkv, hd, ps, scale,
+                             window, int(plan["counts"][5]), inv, rot, False, status)
+    assert torch.equal(kc4.nan_to_num(7.0), kc1.nan_to_num(7.0)) and torch.equal(vc4, vc1)
+    torch.testing.assert_close(got4.float(), want.float(), rtol=1.6e-2, atol=1e-2)

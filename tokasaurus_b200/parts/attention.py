@@ -21,7 +21,8 @@ import torch
 from tokasaurus_b200.kernels import ops
 from tokasaurus_b200.parts.base import LazyNorm, Mixer, PagedCacheNeed, PositionEncoding, WeightSpec
 
-SPLIT_KEYS = 256  # keys per work item of the split-key kernel; fixed, so a request's result does not depend on the batch
+SPLIT_KEYS = 512  # keys per work item of the split-key kernel when there is much work
+SPLIT_KEYS_FEW = 256  # ... and when the whole step has few work items, so that more blocks share it
 QUERY_TILE = 64  # queries per block of the tiled kernel
 
 
@@ -34,7 +35,9 @@ def plan_attention(host, window: int | None, capacity: dict | None = None) -> di
     span = kv_len[dec_seqs]
     if window:
         span = np.minimum(span, window)
-    n_splits = np.maximum(1, -(-span // SPLIT_KEYS))
+    # smaller splits while the step's work items are few (more blocks in flight), larger ones otherwise
+    split_keys = SPLIT_KEYS_FEW if int(np.sum(-(-span // SPLIT_KEYS_FEW))) <= 48 else SPLIT_KEYS
+    n_splits = np.maximum(1, -(-span // split_keys))
     dec_start = np.concatenate([[0], np.cumsum(n_splits)])
     n_items = int(dec_start[-1])
     item_seq = np.repeat(dec_seqs, n_splits)
@@ -61,7 +64,7 @@ def plan_attention(host, window: int | None, capacity: dict | None = None) -> di
         rows = np.asarray(rows, dtype=np.int64)
         r_kv = np.asarray(host.positions, dtype=np.int64)[rows] + 1
         r_span = np.minimum(r_kv, window) if window else r_kv
-        r_splits = np.maximum(1, -(-r_span // SPLIT_KEYS))
+        r_splits = np.maximum(1, -(-r_span // SPLIT_KEYS))  # wanted rows always use the large split
         r_start = np.concatenate([[0], np.cumsum(r_splits)])
         n_row_items, n_rows = int(r_start[-1]), int(rows.shape[0])
         r_item = np.repeat(np.arange(n_rows), r_splits)
@@ -70,7 +73,7 @@ def plan_attention(host, window: int | None, capacity: dict | None = None) -> di
         extra = dict(row_items=i32(np.stack([r_item, r_split], axis=1).reshape(-1)), row_item_start=i32(r_start),
                      row_token=i32(rows), row_kv_len=i32(r_kv), row_seq=i32(np.asarray(host.token_seq)[rows]),
                      row_index=i32(np.arange(n_rows)))
-    counts = np.asarray([n_items, dec_seqs.shape[0], n_tiles, n_row_items, n_rows, 0, 0, 0], dtype=np.int32)
+    counts = np.asarray([n_items, dec_seqs.shape[0], n_tiles, n_row_items, n_rows, split_keys, 0, 0], dtype=np.int32)
 
     def padded(x, n):
         a = np.zeros(max(n, x.shape[0], 1), dtype=np.int32)
@@ -155,7 +158,7 @@ class PagedAttention(Mixer):
                                          tables.page_ids, plan["items"], c[0:1], caps["items"] if caps else int(counts[0]),
                                          plan["dec_seqs"], plan["dec_item_start"], c[1:2],
                                          caps["dec"] if caps else int(counts[1]), attn, nh, nkv, hd, cache.page_size,
-                                         self.scale, self.window, SPLIT_KEYS, self.inv_freq, rot, cache.writable,
+                                         self.scale, self.window, int(counts[5]), self.inv_freq, rot, cache.writable,
                                          ctx.status)
                 if residual is not None:
                     ops.linear_decode(attn, self.w_o, "add", out=residual)
@@ -178,7 +181,7 @@ class PagedAttention(Mixer):
                                          tables.page_ids, plan["items"], c[0:1], caps["items"] if caps else int(counts[0]),
                                          plan["dec_seqs"], plan["dec_item_start"], c[1:2],
                                          caps["dec"] if caps else int(counts[1]), attn, nh, nkv, hd, cache.page_size,
-                                         self.scale, self.window, SPLIT_KEYS, self.inv_freq, rot, cache.writable,
+                                         self.scale, self.window, int(counts[5]), self.inv_freq, rot, cache.writable,
                                          ctx.status)
                 return ops.linear_smallm(attn, self.w_o)
             qkv = torch.empty((T, nh * hd), dtype=h.dtype, device=h.device)  # q only; k and v go straight to the cache
@@ -221,7 +224,7 @@ class PagedAttention(Mixer):
         if dec_cap:
             ops.attn_decode_mma(qkv, cache.k, cache.v, ctx.seq_q_start, ctx.seq_kv_len, tables.indptr, tables.page_ids,
                                 plan["items"], c[0:1], items_cap, plan["dec_seqs"], plan["dec_item_start"], c[1:2],
-                                dec_cap, attn, nh, nkv, hd, cache.page_size, self.scale, self.window, SPLIT_KEYS)
+                                dec_cap, attn, nh, nkv, hd, cache.page_size, self.scale, self.window, int(counts[5]))
         if tiles_cap:
             ops.attn_prefill_mma(qkv, attn, cache.k, cache.v, ctx.seq_q_start, ctx.seq_q_len, ctx.seq_kv_len,
                                  tables.indptr, tables.page_ids, plan["tiles"], c[2:3], tiles_cap, nh, nkv, hd,
