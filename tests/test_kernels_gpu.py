@@ -620,3 +620,44 @@ def test_fused_rope_decode_attention_equals_the_separate_kernels(ops, hd, nh, nk
                              window, int(plan["counts"][5]), inv, rot, False, status)
     assert torch.equal(kc4.nan_to_num(7.0), kc1.nan_to_num(7.0)) and torch.equal(vc4, vc1)
     torch.testing.assert_close(got4.float(), want.float(), rtol=1.6e-2, atol=1e-2)
+
+
+# ------------------------------------------------------------------------------------------------
+# tcgen05 / TMA matrix product for many rows
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (128, 128, 64), (256, 512, 128), (100, 300, 72), (1, 16, 8),
+                                   (300, 509 * 8, 96), (2048, 3072, 2048), (130, 264, 2056), (640, 2048, 8192)])
+def test_gemm_tcgen05(ops, M, N, K):
+    g = torch.Generator().manual_seed(M + N + K)
+    a = torch.randn(M, K, generator=g).to(torch.bfloat16).to(DEV)
+    w = (torch.randn(N, K, generator=g) * 0.1).to(torch.bfloat16).to(DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    out = ops.gemm_tcgen05(a, w, status)
+    assert int(status) == 0
+    want = a.double() @ w.double().T
+    torch.testing.assert_close(out.double(), want, rtol=1e-2, atol=4e-3 * want.abs().max().item())
+    # rows are independent of the batch they come in
+    if M > 130:
+        part = ops.gemm_tcgen05(a[128:130].contiguous(), w, status)
+        assert torch.equal(part, out[128:130])
+
+
+@pytest.mark.parametrize("M,I,K", [(128, 128, 64), (2048, 8192, 2048), (77, 72, 96), (300, 160, 2048)])
+def test_gemm_tcgen05_gated(ops, M, I, K):
+    g = torch.Generator().manual_seed(M + I)
+    a = torch.randn(M, K, generator=g).to(torch.bfloat16).to(DEV)
+    gate = (torch.randn(I, K, generator=g) * 0.1).to(torch.bfloat16).to(DEV)
+    up = (torch.randn(I, K, generator=g) * 0.1).to(torch.bfloat16).to(DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    got = ops.gemm_tcgen05(a, ops.interleave_gate_up(gate, up), status, gated=True)
+    assert int(status) == 0 and got.shape == (M, I)
+    want = torch.nn.functional.silu(a.double() @ gate.double().T) * (a.double() @ up.double().T)
+    torch.testing.assert_close(got.double(), want, rtol=2e-2, atol=6e-3 * want.abs().max().item())
+
+
+def test_gemm_tcgen05_refuses_what_tma_cannot_address(ops):
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    a = torch.zeros(4, 20, dtype=torch.bfloat16, device=DEV)  # K not a multiple of 8
+    with pytest.raises(ops.KernelError):
+        ops.gemm_tcgen05(a, torch.zeros(16, 20, dtype=torch.bfloat16, device=DEV), status)
+    with pytest.raises(ops.KernelError):
+        ops.gemm_tcgen05(torch.zeros(4, 16, device=DEV), torch.zeros(16, 16, device=DEV), status)  # float32

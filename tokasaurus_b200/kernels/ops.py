@@ -463,6 +463,31 @@ def topk_logprobs(logits: torch.Tensor, temperature: torch.Tensor | None, k: int
            "topk_logprobs")
 
 
+TCGEN05_M_MIN = 128  # from this many rows on the gated tcgen05 product beats library product + activation kernel
+
+
+def can_use_tcgen05(a: torch.Tensor, w: torch.Tensor) -> bool:
+    return (a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and a.dim() == 2 and a.shape[1] % 8 == 0
+            and a.stride(1) == 1 and w.stride(1) == 1 and a.stride(0) % 8 == 0 and w.stride(0) % 8 == 0
+            and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+
+def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, status: torch.Tensor, gated: bool = False) -> torch.Tensor:
+    """a[M, K] @ w[N, K]^T in bfloat16 on the tcgen05 tensor cores (TMA-fed, accumulator in tensor memory).
+    ``gated``: ``w`` interleaves gate/up rows (``interleave_gate_up``); the result is silu(gate)*up [M, N/2].
+    ``status``: the device status word; a bounded wait that runs out sets its bit 4."""
+    _need_cuda(a, w, status)
+    _need(can_use_tcgen05(a, w), "gemm_tcgen05: bfloat16 operands, K and strides multiples of 8, 16-byte aligned")
+    M, K = a.shape
+    N = w.shape[0]
+    _need(w.shape[1] == K and (not gated or N % 16 == 0), "gemm_tcgen05: shapes")
+    out = torch.empty((M, N // 2 if gated else N), dtype=torch.bfloat16, device=a.device)
+    _check(_fn(_libs.get("gemm_tcgen05.cu"), "tkb_gemm_tcgen05_bf16")(
+        _ptr(a), c_int(a.stride(0)), _ptr(w), c_int(w.stride(0)), _ptr(out), c_int(out.stride(0)), c_int(M), c_int(N),
+        c_int(K), c_int(1 if gated else 0), _ptr(status), _stream()), "gemm_tcgen05")
+    return out
+
+
 def linear(a: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None = None) -> torch.Tensor:
     """a[M, K] @ w[N, K]^T.  float32: this engine's FP32 kernel (no tf32).  bfloat16: the library
     matrix product (cuBLAS through torch), float32 accumulation, output bfloat16 or float32."""
