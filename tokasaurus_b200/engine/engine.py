@@ -18,6 +18,7 @@ import numpy as np
 import torch
 
 from tokasaurus_b200.config.engine_config import EngineConfig
+from tokasaurus_b200.cache.pages import NoSpaceError
 from tokasaurus_b200.engine.batch import StepEntry
 from tokasaurus_b200.engine.runner import ModelRunner
 from tokasaurus_b200.engine.scheduler import Scheduler, StepPlan
@@ -56,6 +57,7 @@ class Engine:
 
             self.graphs = DecodeGraphs(self.runner, self.sampler, cfg.cudagraph_max_size, cfg.cudagraph_step)
         self._auto_id = 0
+        self._prepared_next = None  # host arrays of the step after this one, built while the GPU was busy
         self.last_step_bytes = dict(h2d=0, d2h=0)
 
     # ------------------------------------------------------------------ requests
@@ -105,7 +107,11 @@ class Engine:
         extra = self._sampling_arrays(plan)
         wants_topk = any(p.seq.request.topk_logprobs for p in plan.portions if p.samples)
         if self.graphs is not None and not wants_topk and self.graphs.usable(entries):
-            padded = self.graphs.run(entries, extra)
+            prep, self._prepared_next = self._prepared_next, None
+            if prep is None or prep["signature"] != [(e.request, e.start) for e in entries]:
+                prep = self.graphs.prepare(entries, extra)
+            padded = self.graphs.launch(prep)
+            self._prepared_next = self._prepare_following(plan)  # overlaps the GPU's work on this step
             ids, lps = self.sampler.read(padded)
             ids, lps = ids[:len(entries)], lps[:len(entries)]
             self.runner.check_status()
@@ -129,6 +135,35 @@ class Engine:
         self.runner.check_status()
         self.last_step_bytes = dict(h2d=self.runner.last_upload_bytes, d2h=self.sampler.bytes_last_read if R else 4)
         return self.scheduler.complete(plan, ids, lps if self.config.enable_chosen_logprobs else None, topk)
+
+    def _prepare_following(self, plan: StepPlan):
+        """While the GPU runs the step of ``plan``: build the host arrays of the step after it, on the guess
+        that every request of this step goes on decoding (none ends on an end-of-sequence or stop token, none is
+        pushed out, nothing new is admitted).  The next ``step`` checks the guess against what the scheduler
+        really decides and builds the arrays afresh if it was wrong."""
+        if self.scheduler.queued or any(not p.samples for p in plan.portions):
+            return None
+        entries, rows = [], []
+        try:
+            for p in plan.portions:
+                req = p.seq.request
+                if len(p.seq.output.completion_ids) + 1 >= req.max_num_tokens:
+                    return None  # ends by length in this step
+                start = p.start + p.n_tokens
+                self.runner.cache.ensure_capacity(p.seq.id, start + 1)
+                entries.append(StepEntry(p.seq.id, None, start, [0]))
+                rows.append((p, start))
+        except (NoSpaceError, KeyError):
+            return None  # no page free, or the request is gone: let the scheduler sort it out
+        if not entries or not self.graphs.usable(entries):
+            return None
+        temp = np.asarray([p.seq.request.sampling_params.temperature for p, _ in rows], dtype=np.float32)
+        keys = np.asarray(
+            [stream_key(p.seq.request.sampling_params.seed if p.seq.request.sampling_params.seed is not None
+                        else self.seed, p.seq.index) for p, _ in rows], dtype=np.int64)
+        pos = np.asarray([start + 1 for _, start in rows], dtype=np.int32)
+        slot = np.asarray([self.runner.cache.slot(p.seq.id) for p, _ in rows], dtype=np.int32)
+        return self.graphs.prepare(entries, dict(temperature=temp, stream_key=keys, sample_pos=pos, row_slot=slot))
 
     def run_until_done(self) -> list[RequestOutput]:
         done: list[RequestOutput] = []

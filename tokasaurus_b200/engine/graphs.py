@@ -53,38 +53,49 @@ class DecodeGraphs:
             [_pad(ip, bp + 1, l) for ip, l in zip(host.table_indptr, last)],
             [_pad(pg, cap) for pg, cap in zip(host.table_pages, page_caps)], host.requests)
 
-    def run(self, entries: list[StepEntry], extra: dict[str, np.ndarray]) -> int:
-        """Run one decode step for ``entries`` and sample; returns the padded batch size (the
-        sampler's results for the real rows are the first ``len(entries)`` of each part)."""
-        from tokasaurus_b200.kernels import ops
-
+    def prepare(self, entries: list[StepEntry], extra: dict[str, np.ndarray]) -> dict:
+        """All host work of a step that needs no result of the step before it: the batch arrays padded to
+        the graph's sizes, the work plans, the sampling arrays.  The engine calls this for the NEXT step
+        while the GPU is still busy with the current one."""
         runner = self.runner
         B = len(entries)
         bp = next(s for s in self.sizes if s >= B)
         host = build_host_batch(entries, runner.cache)
         page_caps = [_pow2_at_least(pg.shape[0], 64) for pg in host.table_pages]
         planners = runner.model.planners()
-        probe = {key: m.plan(host) for key, m in planners.items()}
-        caps = {key: dict(items=_pow2_at_least(int(p["counts"][0]), 8), dec=bp, tiles=0) for key, p in probe.items()}
+        raw = {key: m.plan(host) for key, m in planners.items()}
+        caps = {key: dict(items=_pow2_at_least(int(p["counts"][0]), 8), dec=bp, tiles=0) for key, p in raw.items()}
         key = (bp, tuple(page_caps), tuple(sorted((str(k), c["items"]) for k, c in caps.items())))
-        padded = self._padded(host, bp, page_caps)
-        plans = {k: m.plan(host, caps[k]) for k, m in planners.items()}
+        plans = {k: planners[k].pad_plan(p, caps[k]) for k, p in raw.items()}
         ex = dict(temperature=_pad(extra["temperature"], bp), stream_key=_pad(extra["stream_key"], bp),
                   sample_pos=_pad(extra["sample_pos"], bp), row_slot=_pad(extra["row_slot"], bp, -1))
-        slot = self.graphs.get(key)
+        return dict(key=key, bp=bp, padded=self._padded(host, bp, page_caps), plans=plans, caps=caps, ex=ex,
+                    signature=[(e.request, e.start) for e in entries])
+
+    def launch(self, prep: dict) -> int:
+        """Copy a prepared step to the device and replay (or first record) its graph; returns the padded
+        batch size (the sampler's results for the real rows are the first rows of each part)."""
+        from tokasaurus_b200.kernels import ops
+
+        runner = self.runner
+        slot = self.graphs.get(prep["key"])
         if slot is None:
             slot = dict(stager=Stager(runner.rt.device, 1 << 12), graph=None)
             slot["stager"].status = runner.stager.status
-            self.graphs[key] = slot
-        ctx = StepContext(padded, runner.cache, runner.rt.device, slot["stager"], ex, plans)
-        ctx.plan_caps = caps
+            self.graphs[prep["key"]] = slot
+        ctx = StepContext(prep["padded"], runner.cache, runner.rt.device, slot["stager"], prep["ex"], prep["plans"])
+        ctx.plan_caps = prep["caps"]
         runner.last_upload_bytes = slot["stager"].bytes_last_upload
         runner.last_context = ctx
         if slot["graph"] is None:
-            self._record(slot, ctx, bp)
+            self._record(slot, ctx, prep["bp"])
         slot["graph"].replay()
         ops.LAUNCHES += slot["launches"]
-        return bp
+        return prep["bp"]
+
+    def run(self, entries: list[StepEntry], extra: dict[str, np.ndarray]) -> int:
+        """Prepare and launch one decode step for ``entries``, sampling included."""
+        return self.launch(self.prepare(entries, extra))
 
     def _record(self, slot: dict, ctx: StepContext, bp: int) -> None:
         from tokasaurus_b200.kernels import ops

@@ -137,6 +137,20 @@ class PagedAttention(Mixer):
     def plan(self, host, capacity=None):
         return plan_attention(host, self.window, capacity)
 
+    def pad_plan(self, plan: dict, capacity: dict) -> dict:
+        """The same plan with its arrays at the fixed sizes of a CUDA graph."""
+        def padded(x, n):
+            a = np.zeros(max(n, x.shape[0], 1), dtype=np.int32)
+            a[: x.shape[0]] = x
+            return a
+
+        out = dict(plan)
+        out["items"] = padded(plan["items"], 2 * capacity.get("items", 0))
+        out["dec_seqs"] = padded(plan["dec_seqs"], capacity.get("dec", 0))
+        out["dec_item_start"] = padded(plan["dec_item_start"], capacity.get("dec", 0) + 1)
+        out["tiles"] = padded(plan["tiles"], 2 * capacity.get("tiles", 0))
+        return out
+
     # --- one step ---
     def forward(self, ctx, h, cache, out_rows=None, residual: torch.Tensor | None = None):
         T = h.shape[0]

@@ -130,6 +130,10 @@ class Mixer(Part):
         is captured in a CUDA graph."""
         return {}
 
+    def pad_plan(self, plan: dict, capacity: dict) -> dict:
+        """A plan made without capacities, brought to the fixed array sizes ``capacity`` asks for."""
+        return plan
+
     def forward(self, ctx: "StepContext", h: "torch.Tensor", cache, out_rows=None) -> "torch.Tensor":
         """``h`` [T, width]: normalised input rows of this step's tokens.  ``cache``: what the
         cache manager holds for this layer call (``PagedLayerCache`` or ``StateLayerCache`` or
