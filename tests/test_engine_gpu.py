@@ -182,3 +182,34 @@ def test_cuda_graph_decode_equals_eager(tiny_model_dirs, dtype):
     for a, b in zip(outs[False], outs[True]):
         assert a.completion_ids == b.completion_ids
         np.testing.assert_allclose(a.logprobs, b.logprobs, atol=1e-5)
+
+
+def test_cuda_graph_decode_with_requests_ending_at_different_times(tiny_model_dirs):
+    """Requests that end by length at different steps and on stop tokens, and late arrivals: the engine's
+    guess about the next step (made while the GPU is busy) is wrong again and again and must be dropped."""
+    from tokasaurus_b200 import SamplingParams
+
+    d = tiny_model_dirs[0]
+    prompts = [cuttings.random_tokens(n, 256, 9 * n) for n in (7, 30, 64, 3, 12, 20)]
+    limits = [5, 17, 40, 2, 33, 1]
+    plain = PlainLlama(d, torch.float64)
+    full = [plain.greedy(p, m) for p, m in zip(prompts, limits)]
+    stop_at = full[2][9]  # request 2 stops when it first produces this token
+    want = [list(f) for f in full]
+    want[2] = full[2][: full[2].index(stop_at) + 1]
+    for graphs in (False, True):
+        eng = make_engine(d, use_cudagraphs=graphs, cudagraph_step=4, cudagraph_max_size=8)
+        ids = []
+        for i, (p, m) in enumerate(zip(prompts[:4], limits[:4])):
+            ids.append(eng.add_request(p, SamplingParams(), max_num_tokens=m, ignore_eos=True,
+                                       stop_token_ids=[stop_at] if i == 2 else ()))
+        done = []
+        for _ in range(6):
+            done += eng.step()
+        for p, m in zip(prompts[4:], limits[4:]):  # arrivals while the others decode
+            ids.append(eng.add_request(p, SamplingParams(), max_num_tokens=m, ignore_eos=True))
+        done += eng.run_until_done()
+        by_id = {o.id: o for o in done}
+        assert [by_id[i].completion_ids for i in ids] == want, f"graphs={graphs}"
+        assert by_id[ids[2]].finish_reason == "stop"
+        assert not eng.runner.cache.requests

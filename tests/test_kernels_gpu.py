@@ -348,7 +348,7 @@ def test_refusals(ops):
 
 # ------------------------------------------------------------------------------------------------
 # bfloat16 tensor-core attention (split-key kernel for single tokens, tiled kernel for portions)
-def run_mma_attention(ops, lens_q, lens_kv, nh, nkv, hd, ps, window, seed, n_pages=None, fill=1e3):
+def run_mma_attention(ops, lens_q, lens_kv, nh, nkv, hd, ps, window, seed, n_pages=None, fill=1e3, merged=True):
     """A batch of requests with lens_q new tokens each at the end of lens_kv keys; returns (got, want)."""
     from types import SimpleNamespace
     from tokasaurus_b200.parts.attention import plan_attention
@@ -373,7 +373,7 @@ def run_mma_attention(ops, lens_q, lens_kv, nh, nkv, hd, ps, window, seed, n_pag
     if n_dec:
         ops.attn_decode_mma(qkv, kc, vc, i32(q_start), i32(lens_kv), indptr, pages, i32(plan["items"]), c[0:1], n_items,
                             i32(plan["dec_seqs"]), i32(plan["dec_item_start"]), c[1:2], n_dec, out, nh, nkv, hd, ps, scale,
-                            window, int(plan["counts"][5]))
+                            window, int(plan["counts"][5]), item_entry=i32(plan["item_entry"]) if merged else None)
     if n_tiles:
         ops.attn_prefill_mma(qkv, out, kc, vc, i32(q_start), i32(lens_q), i32(lens_kv), indptr, pages, i32(plan["tiles"]),
                              c[2:3], n_tiles, nh, nkv, hd, ps, scale, window)
@@ -395,6 +395,12 @@ def test_mma_attention_mixed_batch(ops, hd, nh, nkv, ps, window):
     got, want = run_mma_attention(ops, lens_q, lens_kv, nh, nkv, hd, ps, window, seed=hd + nh)
     assert not torch.isnan(got).any()
     torch.testing.assert_close(got, want, rtol=1.6e-2, atol=1.2e-2)
+    # merge of the splits by a second kernel instead of inside the attention kernel: the same sums in the same order
+    got2, _ = run_mma_attention(ops, lens_q, lens_kv, nh, nkv, hd, ps, window, seed=hd + nh, merged=False)
+    assert torch.equal(got, got2)
+    # and again: the arrival counters must have been left at zero
+    got3, _ = run_mma_attention(ops, lens_q, lens_kv, nh, nkv, hd, ps, window, seed=hd + nh)
+    assert torch.equal(got, got3)
 
 
 def test_mma_attention_finds_one_far_key(ops):
@@ -594,7 +600,7 @@ def test_fused_rope_decode_attention_equals_the_separate_kernels(ops, hd, nh, nk
     got = torch.zeros_like(want)
     ops.attn_decode_rope_mma(qkv, kc2, vc2, q_start, kv_len, indptr, pages, i32(plan["items"]), c[0:1], n_items,
                              i32(plan["dec_seqs"]), i32(plan["dec_item_start"]), c[1:2], n_dec, got, nh, nkv, hd, ps, scale,
-                             window, int(plan["counts"][5]), inv, rot, True, status)
+                             window, int(plan["counts"][5]), inv, rot, True, status, item_entry=i32(plan["item_entry"]))
     assert int(status) == 0
     assert torch.equal(vc2, vc1)
     torch.testing.assert_close(kc2.float().nan_to_num(7.0), kc1.float().nan_to_num(7.0), rtol=1e-2, atol=1e-2)

@@ -189,7 +189,9 @@ attn_decode_mma_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restric
                        int nh, int nkv, int ps, float scale_log2, int window, int split_keys, int head_tiles,
                        const float* __restrict__ inv_freq, int rot, int write_cache, int num_pages,
                        int* __restrict__ status, const float* __restrict__ qkv_parts, int n_parts,
-                       long long part_stride) {
+                       long long part_stride, int* __restrict__ counters, const int* __restrict__ item_entry,
+                       const int* __restrict__ dec_item_start, const int* __restrict__ out_row_of,
+                       bf16* __restrict__ out, int out_stride) {
   extern __shared__ __align__(128) unsigned char smem[];
   trigger_dependents();
   grid_dependency_wait();
@@ -388,6 +390,16 @@ attn_decode_mma_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restric
     }
   }
   __syncthreads();
+  // With `counters` the merge of the splits happens here too: the block that finishes last for its
+  // (request, kv head, head tile) adds up all splits in split order; a request with one split is finished
+  // by its only block.  Without `counters` the partial results are left for attn_decode_merge_kernel.
+  int e = 0, i0 = 0, i1 = 0;
+  if (counters != nullptr) {
+    e = item_entry[item];
+    i0 = dec_item_start[e];
+    i1 = dec_item_start[e + 1];
+  }
+  const bool single = counters != nullptr && i1 - i0 == 1;
   for (int idx = tid; idx < gn * HD; idx += 128) {
     const int r = idx / HD, d = idx - r * HD;
     float mm = NEG_BIG;
@@ -401,11 +413,42 @@ attn_decode_mma_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restric
       ll += f * sml[(w * 16 + r) * 2 + 1];
     }
     const int head = kvh * group + g0 + r;
+    if (single) {
+      out[(size_t)out_row_of[s] * out_stride + (size_t)head * HD + d] = __float2bfloat16_rn(acc / ll);
+      continue;
+    }
     part_o[((size_t)item * nh + head) * HD + d] = acc;
     if (d == 0) {
       part_ml[((size_t)item * nh + head) * 2] = mm;
       part_ml[((size_t)item * nh + head) * 2 + 1] = ll;
     }
+  }
+  if (counters == nullptr || single) return;
+  __shared__ int s_last;
+  __threadfence();  // this block's partial results are visible before its arrival is counted
+  __syncthreads();
+  if (tid == 0) {
+    int* c = counters + (size_t)e * gridDim.y + blockIdx.y;
+    const int prev = atomicAdd(c, 1);
+    s_last = prev == i1 - i0 - 1;
+    if (s_last) *c = 0;  // every block of this group has arrived: leave the counter ready for the next launch
+  }
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  const size_t orow = (size_t)out_row_of[s] * out_stride;
+  for (int idx = tid; idx < gn * HD; idx += 128) {
+    const int r = idx / HD, d = idx - r * HD;
+    const int head = kvh * group + g0 + r;
+    float mm = NEG_BIG;
+    for (int i = i0; i < i1; i++) mm = fmaxf(mm, __ldcg(part_ml + ((size_t)i * nh + head) * 2));
+    float acc = 0.f, ll = 0.f;
+    for (int i = i0; i < i1; i++) {
+      const float f = exp2f(__ldcg(part_ml + ((size_t)i * nh + head) * 2) - mm);
+      ll += f * __ldcg(part_ml + ((size_t)i * nh + head) * 2 + 1);
+      acc += f * __ldcg(part_o + ((size_t)i * nh + head) * HD + d);
+    }
+    out[orow + (size_t)head * HD + d] = __float2bfloat16_rn(acc / ll);
   }
 }
 
@@ -634,7 +677,8 @@ TKB_EXPORT int tkb_attn_decode_mma_bf16(const void* q, int q_stride, const void*
   return launch_pdl(attn_decode_mma_kernel<false>, grid, dim3(128), (size_t)DEC_SMEM_B, (cudaStream_t)st, (const bf16*)q,
                     q_stride, (bf16*)kcache, (bf16*)vcache, seq_q_start, seq_kv_len, page_indptr, page_ids, items,
                     n_items_ptr, part_o, part_ml, nh, nkv, ps, scale * 1.4426950408889634f, window, split_keys,
-                    head_tiles, (const float*)nullptr, 0, 0, 0, (int*)nullptr, (const float*)nullptr, 0, 0LL);
+                    head_tiles, (const float*)nullptr, 0, 0, 0, (int*)nullptr, (const float*)nullptr, 0, 0LL,
+                    (int*)nullptr, (const int*)nullptr, (const int*)nullptr, (const int*)nullptr, (bf16*)nullptr, 0);
 }
 
 // The same with rotary encoding and the cache write folded in: qkv holds the step's un-rotated q|k|v rows
@@ -660,7 +704,45 @@ TKB_EXPORT int tkb_attn_decode_rope_mma_bf16(const void* qkv, int q_stride, cons
   return launch_pdl(attn_decode_mma_kernel<true>, grid, dim3(128), (size_t)DEC_SMEM_B, (cudaStream_t)st, (const bf16*)qkv,
                     q_stride, (bf16*)kcache, (bf16*)vcache, seq_q_start, seq_kv_len, page_indptr, page_ids, items,
                     n_items_ptr, part_o, part_ml, nh, nkv, ps, scale * 1.4426950408889634f, window, split_keys,
-                    head_tiles, inv_freq, rot, write_cache, num_pages, status, qkv_parts, n_parts, part_stride);
+                    head_tiles, inv_freq, rot, write_cache, num_pages, status, qkv_parts, n_parts, part_stride,
+                    (int*)nullptr, (const int*)nullptr, (const int*)nullptr, (const int*)nullptr, (bf16*)nullptr, 0);
+}
+
+// Split-key attention with the merge of the splits inside the same kernel (the last block to finish a request's
+// group of heads adds the splits up).  qkv/q_stride as in tkb_attn_decode_mma_bf16 when fused == 0 (rotated q),
+// as in tkb_attn_decode_rope_mma_bf16 when fused != 0.  counters: int32 [dec_cap * grid.y] that are zero
+// before the first launch and are left zero by every launch; item_entry[i]: index of item i's request in the
+// decode list; dec_item_start: CSR over that list; out_row_of[request row]: row of `out` to write.
+TKB_EXPORT int tkb_attn_decode_merged_bf16(const void* qkv, int q_stride, const float* qkv_parts, int n_parts,
+                                           long long part_stride, void* kcache, void* vcache, const int* seq_q_start,
+                                           const int* seq_kv_len, const int* page_indptr, const int* page_ids,
+                                           const int* items, const int* n_items_ptr, int items_cap, float* part_o,
+                                           float* part_ml, int nh, int nkv, int ps, float scale, int window,
+                                           int split_keys, int fused, const float* inv_freq, int rot, int write_cache,
+                                           int num_pages, int* status, int* counters, const int* item_entry,
+                                           const int* dec_item_start, const int* out_row_of, void* out, int out_stride,
+                                           void* st) {
+  if (items_cap <= 0) return 0;
+  if (nkv <= 0 || nh % nkv != 0 || ps <= 0 || split_keys <= 0 || counters == nullptr) return -2;
+  if (fused && (rot < 0 || rot > HD || (rot & 3))) return -2;
+  int rc = ensure_smem_attr();
+  if (rc) return rc;
+  const int group = nh / nkv;
+  const int head_tiles = (group + 15) / 16;
+  if ((long long)nkv * head_tiles > 65535) return -3;
+  dim3 grid(items_cap, nkv * head_tiles);
+  const float sl2 = scale * 1.4426950408889634f;
+  if (fused)
+    return launch_pdl(attn_decode_mma_kernel<true>, grid, dim3(128), (size_t)DEC_SMEM_B, (cudaStream_t)st,
+                      (const bf16*)qkv, q_stride, (bf16*)kcache, (bf16*)vcache, seq_q_start, seq_kv_len, page_indptr,
+                      page_ids, items, n_items_ptr, part_o, part_ml, nh, nkv, ps, sl2, window, split_keys, head_tiles,
+                      inv_freq, rot, write_cache, num_pages, status, qkv_parts, n_parts, part_stride, counters,
+                      item_entry, dec_item_start, out_row_of, (bf16*)out, out_stride);
+  return launch_pdl(attn_decode_mma_kernel<false>, grid, dim3(128), (size_t)DEC_SMEM_B, (cudaStream_t)st,
+                    (const bf16*)qkv, q_stride, (bf16*)kcache, (bf16*)vcache, seq_q_start, seq_kv_len, page_indptr,
+                    page_ids, items, n_items_ptr, part_o, part_ml, nh, nkv, ps, sl2, window, split_keys, head_tiles,
+                    (const float*)nullptr, 0, 0, 0, (int*)nullptr, (const float*)nullptr, 0, 0LL, counters, item_entry,
+                    dec_item_start, out_row_of, (bf16*)out, out_stride);
 }
 
 TKB_EXPORT int tkb_attn_decode_merge_bf16(const float* part_o, const float* part_ml, const int* dec_seqs,

@@ -204,14 +204,29 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, const int* __restrict_
   __syncthreads();
 
   T* row = qkv + (size_t)t * (size_t)(nh + 2 * nkv) * hd;
+  const bool vec = (half & 3) == 0 && (hd & 3) == 0;  // four elements a thread and step
   // q heads: rotate in place.
-  for (int idx = threadIdx.x; idx < nh * half; idx += blockDim.x) {
-    const int h = idx / half, j = idx - h * half;
-    T* p = row + h * hd;
-    const float x1 = to_float(p[j]), x2 = to_float(p[j + half]);
-    const float c = cs[j], sn = cs[half + j];
-    p[j] = from_float<T>(x1 * c - x2 * sn);
-    p[j + half] = from_float<T>(x2 * c + x1 * sn);
+  if (vec) {
+    const int h4 = half >> 2;
+    for (int idx = threadIdx.x; idx < nh * h4; idx += blockDim.x) {
+      const int h = idx / h4, j = (idx - h * h4) * 4;
+      T* p = row + h * hd;
+      const float4 x1 = load4(p + j), x2 = load4(p + j + half);
+      const float4 c = *reinterpret_cast<const float4*>(cs + j), sn = *reinterpret_cast<const float4*>(cs + half + j);
+      store4(p + j, make_float4(x1.x * c.x - x2.x * sn.x, x1.y * c.y - x2.y * sn.y, x1.z * c.z - x2.z * sn.z,
+                                x1.w * c.w - x2.w * sn.w));
+      store4(p + j + half, make_float4(x2.x * c.x + x1.x * sn.x, x2.y * c.y + x1.y * sn.y, x2.z * c.z + x1.z * sn.z,
+                                       x2.w * c.w + x1.w * sn.w));
+    }
+  } else {
+    for (int idx = threadIdx.x; idx < nh * half; idx += blockDim.x) {
+      const int h = idx / half, j = idx - h * half;
+      T* p = row + h * hd;
+      const float x1 = to_float(p[j]), x2 = to_float(p[j + half]);
+      const float c = cs[j], sn = cs[half + j];
+      p[j] = from_float<T>(x1 * c - x2 * sn);
+      p[j + half] = from_float<T>(x2 * c + x1 * sn);
+    }
   }
   if (!write_cache) return;  // a layer call that reads another call's cache writes none of its own
   const int page = page_ids[page_indptr[s] + pos / page_size];
@@ -222,6 +237,28 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, const int* __restrict_
   const int slot = pos % page_size;
   const T* krow = row + nh * hd;
   const T* vrow = krow + nkv * hd;
+  if (vec) {
+    const int d4n = hd >> 2;
+    for (int idx = threadIdx.x; idx < nkv * d4n; idx += blockDim.x) {
+      const int h = idx / d4n, d = (idx - h * d4n) * 4;
+      const size_t dst = (((size_t)page * nkv + h) * page_size + slot) * hd + d;
+      const T* kh = krow + h * hd;
+      float4 kv = load4(kh + d);
+      if (d < half) {
+        const float4 y = load4(kh + d + half);
+        const float4 c = *reinterpret_cast<const float4*>(cs + d), sn = *reinterpret_cast<const float4*>(cs + half + d);
+        kv = make_float4(kv.x * c.x - y.x * sn.x, kv.y * c.y - y.y * sn.y, kv.z * c.z - y.z * sn.z, kv.w * c.w - y.w * sn.w);
+      } else if (d < rot) {
+        const int j = d - half;
+        const float4 y = load4(kh + j);
+        const float4 c = *reinterpret_cast<const float4*>(cs + j), sn = *reinterpret_cast<const float4*>(cs + half + j);
+        kv = make_float4(kv.x * c.x + y.x * sn.x, kv.y * c.y + y.y * sn.y, kv.z * c.z + y.z * sn.z, kv.w * c.w + y.w * sn.w);
+      }
+      store4(kcache + dst, kv);
+      store4(vcache + dst, load4(vrow + h * hd + d));
+    }
+    return;
+  }
   for (int idx = threadIdx.x; idx < nkv * hd; idx += blockDim.x) {
     const int h = idx / hd, d = idx - h * hd;
     const size_t dst = (((size_t)page * nkv + h) * page_size + slot) * hd + d;

@@ -173,7 +173,7 @@ def rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, token_seq: torch.T
 SMALL_M_MAX = 16   # above this many rows the library product is as fast or faster (measured on B200)
 GATED_M_MAX = 8    # the gated small-batch product wins only up to this many rows
 DECODE_M_MAX = 16
-LAZY_NORM_M_MAX = 2  # up to this many rows the norm is folded into the consumer's matrix product
+LAZY_NORM_M_MAX = 0  # up to this many rows the norm is folded into the consumer's matrix product
 _EPILOGUES = {"bf16": 0, "add": 1, "gated": 2, "f32": 3}
 
 
@@ -331,12 +331,31 @@ def attn_paged(q: torch.Tensor, q_stride: int, out: torch.Tensor, kcache: torch.
              c_int(n_kv_heads), c_int(page_size), c_float(scale), c_int(window or 0), _stream()), "attn_paged")
 
 
+_COUNTERS: dict = {}
+_COUNTER_INTS = 1 << 20
+
+
+def _decode_counters(device: torch.device, dec_cap: int, n_heads: int, n_kv_heads: int) -> torch.Tensor | None:
+    """Arrival counters of the split-key kernel's in-kernel merge: one fixed zero-initialised array per device
+    (every launch leaves it zero again).  None if a launch would need more than it holds."""
+    group = n_heads // n_kv_heads
+    need = dec_cap * n_kv_heads * ((group + 15) // 16)
+    if need > _COUNTER_INTS:
+        return None
+    key = (device.type, device.index)
+    t = _COUNTERS.get(key)
+    if t is None:
+        t = torch.zeros((_COUNTER_INTS,), dtype=torch.int32, device=device)
+        _COUNTERS[key] = t
+    return t
+
+
 def attn_decode_mma(qkv: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, seq_q_start: torch.Tensor,
                     seq_kv_len: torch.Tensor, page_indptr: torch.Tensor, page_ids: torch.Tensor, items: torch.Tensor,
                     n_items: torch.Tensor, items_cap: int, dec_seqs: torch.Tensor, dec_item_start: torch.Tensor,
                     n_dec: torch.Tensor, dec_cap: int, out: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int,
                     page_size: int, scale: float, window: int | None, split_keys: int,
-                    out_row_of: torch.Tensor | None = None) -> None:
+                    out_row_of: torch.Tensor | None = None, item_entry: torch.Tensor | None = None) -> None:
     """bfloat16 split-key attention for requests that bring one token: ``items`` are (request row,
     split) pairs of ``split_keys`` keys each, computed into float32 partial results and merged into
     ``out`` [T, n_heads*head_dim] at each request's token row (or at row ``out_row_of[request]``).
@@ -352,6 +371,18 @@ def attn_decode_mma(qkv: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tenso
     lib = _libs.get("attention_mma.cu", TKB_HD=head_dim)
     part_o = torch.empty((items_cap, n_heads, head_dim), dtype=torch.float32, device=qkv.device)
     part_ml = torch.empty((items_cap, n_heads, 2), dtype=torch.float32, device=qkv.device)
+    counters = _decode_counters(qkv.device, dec_cap, n_heads, n_kv_heads) if item_entry is not None else None
+    if counters is not None:
+        # the merge of the splits happens inside the attention kernel
+        _check(_fn(lib, "tkb_attn_decode_merged_bf16")(
+            _ptr(qkv), c_int(qkv.shape[1]), _ptr(None), c_int(0), ctypes.c_longlong(0), _ptr(kcache), _ptr(vcache),
+            _ptr(seq_q_start), _ptr(seq_kv_len), _ptr(page_indptr), _ptr(page_ids), _ptr(items), _ptr(n_items),
+            c_int(items_cap), _ptr(part_o), _ptr(part_ml), c_int(n_heads), c_int(n_kv_heads), c_int(page_size),
+            c_float(scale), c_int(window or 0), c_int(split_keys), c_int(0), _ptr(None), c_int(0), c_int(0), c_int(0),
+            _ptr(None), _ptr(counters), _ptr(item_entry), _ptr(dec_item_start),
+            _ptr(out_row_of if out_row_of is not None else seq_q_start), _ptr(out), c_int(out.shape[1]), _stream()),
+            "attn_decode_merged")
+        return
     _check(_fn(lib, "tkb_attn_decode_mma_bf16")(
         _ptr(qkv), c_int(qkv.shape[1]), _ptr(kcache), _ptr(vcache), _ptr(seq_q_start), _ptr(seq_kv_len),
         _ptr(page_indptr), _ptr(page_ids), _ptr(items), _ptr(n_items), c_int(items_cap), _ptr(part_o), _ptr(part_ml),
@@ -369,7 +400,7 @@ def attn_decode_rope_mma(qkv: torch.Tensor, kcache: torch.Tensor, vcache: torch.
                          dec_item_start: torch.Tensor, n_dec: torch.Tensor, dec_cap: int, out: torch.Tensor,
                          n_heads: int, n_kv_heads: int, head_dim: int, page_size: int, scale: float,
                          window: int | None, split_keys: int, inv_freq: torch.Tensor | None, rotary_dim: int,
-                         write_cache: bool, status: torch.Tensor) -> None:
+                         write_cache: bool, status: torch.Tensor, item_entry: torch.Tensor | None = None) -> None:
     """``attn_decode_mma`` with rotary encoding and the cache write folded in: ``qkv`` holds the step's
     un-rotated q|k|v rows of requests that bring one token each, as bfloat16 [T, C] or as the float32 slices
     [slices, T, C] of a K-split product (``linear_smallm``); C = (n_heads + 2 n_kv_heads) * head_dim."""
@@ -394,6 +425,17 @@ def attn_decode_rope_mma(qkv: torch.Tensor, kcache: torch.Tensor, vcache: torch.
     lib = _libs.get("attention_mma.cu", TKB_HD=head_dim)
     part_o = torch.empty((items_cap, n_heads, head_dim), dtype=torch.float32, device=qkv.device)
     part_ml = torch.empty((items_cap, n_heads, 2), dtype=torch.float32, device=qkv.device)
+    counters = _decode_counters(qkv.device, dec_cap, n_heads, n_kv_heads) if item_entry is not None else None
+    if counters is not None:
+        _check(_fn(lib, "tkb_attn_decode_merged_bf16")(
+            _ptr(qkv_ptr), c_int(C), _ptr(parts), c_int(n_parts), ctypes.c_longlong(part_stride), _ptr(kcache),
+            _ptr(vcache), _ptr(seq_q_start), _ptr(seq_kv_len), _ptr(page_indptr), _ptr(page_ids), _ptr(items),
+            _ptr(n_items), c_int(items_cap), _ptr(part_o), _ptr(part_ml), c_int(n_heads), c_int(n_kv_heads),
+            c_int(page_size), c_float(scale), c_int(window or 0), c_int(split_keys), c_int(1), _ptr(inv_freq),
+            c_int(rotary_dim), c_int(1 if write_cache else 0), c_int(kcache.shape[0]), _ptr(status), _ptr(counters),
+            _ptr(item_entry), _ptr(dec_item_start), _ptr(seq_q_start), _ptr(out), c_int(out.shape[1]), _stream()),
+            "attn_decode_merged")
+        return
     _check(_fn(lib, "tkb_attn_decode_rope_mma_bf16")(
         _ptr(qkv_ptr), c_int(C), _ptr(parts), c_int(n_parts), ctypes.c_longlong(part_stride), _ptr(kcache),
         _ptr(vcache), _ptr(seq_q_start), _ptr(seq_kv_len),

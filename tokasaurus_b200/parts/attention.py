@@ -43,6 +43,7 @@ def plan_attention(host, window: int | None, capacity: dict | None = None) -> di
     item_seq = np.repeat(dec_seqs, n_splits)
     item_split = np.arange(n_items) - np.repeat(dec_start[:-1], n_splits)
     items = np.stack([item_seq, item_split], axis=1).reshape(-1)
+    item_entry = np.repeat(np.arange(dec_seqs.shape[0]), n_splits)  # index of each item's request in dec_seqs
     pre_seqs = np.nonzero(q_len > 1)[0]
     n_tiles_seq = -(-q_len[pre_seqs] // QUERY_TILE)
     tile_start = np.concatenate([[0], np.cumsum(n_tiles_seq)])
@@ -71,6 +72,7 @@ def plan_attention(host, window: int | None, capacity: dict | None = None) -> di
         r_split = np.arange(n_row_items) - np.repeat(r_start[:-1], r_splits)
         i32 = lambda a: np.ascontiguousarray(a, dtype=np.int32)  # noqa: E731
         extra = dict(row_items=i32(np.stack([r_item, r_split], axis=1).reshape(-1)), row_item_start=i32(r_start),
+                     row_item_entry=i32(r_item),
                      row_token=i32(rows), row_kv_len=i32(r_kv), row_seq=i32(np.asarray(host.token_seq)[rows]),
                      row_index=i32(np.arange(n_rows)))
     counts = np.asarray([n_items, dec_seqs.shape[0], n_tiles, n_row_items, n_rows, split_keys, 0, 0], dtype=np.int32)
@@ -81,6 +83,7 @@ def plan_attention(host, window: int | None, capacity: dict | None = None) -> di
         return a
 
     return dict(counts=counts, items=padded(items, 2 * cap.get("items", 0)),
+                item_entry=padded(item_entry, cap.get("items", 0)),
                 dec_seqs=padded(dec_seqs, cap.get("dec", 0)), dec_item_start=padded(dec_start, cap.get("dec", 0) + 1),
                 tiles=padded(tiles, 2 * cap.get("tiles", 0)), **extra)
 
@@ -146,6 +149,7 @@ class PagedAttention(Mixer):
 
         out = dict(plan)
         out["items"] = padded(plan["items"], 2 * capacity.get("items", 0))
+        out["item_entry"] = padded(plan["item_entry"], capacity.get("items", 0))
         out["dec_seqs"] = padded(plan["dec_seqs"], capacity.get("dec", 0))
         out["dec_item_start"] = padded(plan["dec_item_start"], capacity.get("dec", 0) + 1)
         out["tiles"] = padded(plan["tiles"], 2 * capacity.get("tiles", 0))
@@ -173,7 +177,7 @@ class PagedAttention(Mixer):
                                          plan["dec_seqs"], plan["dec_item_start"], c[1:2],
                                          caps["dec"] if caps else int(counts[1]), attn, nh, nkv, hd, cache.page_size,
                                          self.scale, self.window, int(counts[5]), self.inv_freq, rot, cache.writable,
-                                         ctx.status)
+                                         ctx.status, item_entry=plan["item_entry"])
                 if residual is not None:
                     ops.linear_decode(attn, self.w_o, "add", out=residual)
                     return None
@@ -196,7 +200,7 @@ class PagedAttention(Mixer):
                                          plan["dec_seqs"], plan["dec_item_start"], c[1:2],
                                          caps["dec"] if caps else int(counts[1]), attn, nh, nkv, hd, cache.page_size,
                                          self.scale, self.window, int(counts[5]), self.inv_freq, rot, cache.writable,
-                                         ctx.status)
+                                         ctx.status, item_entry=plan["item_entry"])
                 return ops.linear_smallm(attn, self.w_o)
             qkv = torch.empty((T, nh * hd), dtype=h.dtype, device=h.device)  # q only; k and v go straight to the cache
             ops.rope_kv_write_partials(parts, qkv, ctx.positions, ctx.token_seq, tables.indptr, tables.page_ids,
@@ -219,7 +223,8 @@ class PagedAttention(Mixer):
             ops.attn_decode_mma(qkv, cache.k, cache.v, plan["row_token"], plan["row_kv_len"], row_indptr,
                                 tables.page_ids, plan["row_items"], c[3:4], n_items, plan["row_index"],
                                 plan["row_item_start"], c[4:5], n_rows, attn, nh, nkv, hd, cache.page_size,
-                                self.scale, self.window, SPLIT_KEYS, out_row_of=plan["row_index"])
+                                self.scale, self.window, SPLIT_KEYS, out_row_of=plan["row_index"],
+                                item_entry=plan["row_item_entry"])
             return project(attn, self.w_o)
         if plan is None or out_rows is not None:
             # float32, or only some rows are wanted: the FP32-pipe kernel, one warp per (row, head)
@@ -238,7 +243,8 @@ class PagedAttention(Mixer):
         if dec_cap:
             ops.attn_decode_mma(qkv, cache.k, cache.v, ctx.seq_q_start, ctx.seq_kv_len, tables.indptr, tables.page_ids,
                                 plan["items"], c[0:1], items_cap, plan["dec_seqs"], plan["dec_item_start"], c[1:2],
-                                dec_cap, attn, nh, nkv, hd, cache.page_size, self.scale, self.window, int(counts[5]))
+                                dec_cap, attn, nh, nkv, hd, cache.page_size, self.scale, self.window, int(counts[5]),
+                                item_entry=plan["item_entry"])
         if tiles_cap:
             ops.attn_prefill_mma(qkv, attn, cache.k, cache.v, ctx.seq_q_start, ctx.seq_q_len, ctx.seq_kv_len,
                                  tables.indptr, tables.page_ids, plan["tiles"], c[2:3], tiles_cap, nh, nkv, hd,
