@@ -65,7 +65,9 @@ class DecodeGraphs:
         planners = runner.model.planners()
         raw = {key: m.plan(host) for key, m in planners.items()}
         caps = {key: dict(items=_pow2_at_least(int(p["counts"][0]), 8), dec=bp, tiles=0) for key, p in raw.items()}
-        key = (bp, tuple(page_caps), tuple(sorted((str(k), c["items"]) for k, c in caps.items())))
+        # the plans' shape: capacities, and whether every request has a single work item (another kernel path)
+        key = (bp, tuple(page_caps), tuple(sorted((str(k), c["items"], int(raw[k]["counts"][0]) == int(raw[k]["counts"][1]))
+                                                    for k, c in caps.items())))
         plans = {k: planners[k].pad_plan(p, caps[k]) for k, p in raw.items()}
         ex = dict(temperature=_pad(extra["temperature"], bp), stream_key=_pad(extra["stream_key"], bp),
                   sample_pos=_pad(extra["sample_pos"], bp), row_slot=_pad(extra["row_slot"], bp, -1))

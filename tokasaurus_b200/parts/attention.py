@@ -6,6 +6,10 @@ causal attention over it with scale 1/sqrt(head_dim) (tokasaurus/model/attention
 restriction to the wanted rows (llama.py:273-278), output projection (:280).  The three
 projection matrices are stacked into one so that one matrix product makes q|k|v.
 
+When every request of a step has a single split (short contexts) the split-key kernel writes the final
+result itself; otherwise a second small kernel merges the splits (measured faster on B200 than letting the
+last block of each request merge them inside the attention kernel, which the kernel can also do).
+
 Kernels: in float32 one FP32 kernel serves every token.  In bfloat16 the requests of a step are
 split as the reference splits them into a prefill and a decode call
 (attention_utils.py:129-151): requests that bring one token go to the split-key tensor-core
@@ -177,7 +181,7 @@ class PagedAttention(Mixer):
                                          plan["dec_seqs"], plan["dec_item_start"], c[1:2],
                                          caps["dec"] if caps else int(counts[1]), attn, nh, nkv, hd, cache.page_size,
                                          self.scale, self.window, int(counts[5]), self.inv_freq, rot, cache.writable,
-                                         ctx.status, item_entry=plan["item_entry"])
+                                         ctx.status, item_entry=plan["item_entry"] if int(counts[0]) == int(counts[1]) else None)
                 if residual is not None:
                     ops.linear_decode(attn, self.w_o, "add", out=residual)
                     return None
@@ -200,7 +204,7 @@ class PagedAttention(Mixer):
                                          plan["dec_seqs"], plan["dec_item_start"], c[1:2],
                                          caps["dec"] if caps else int(counts[1]), attn, nh, nkv, hd, cache.page_size,
                                          self.scale, self.window, int(counts[5]), self.inv_freq, rot, cache.writable,
-                                         ctx.status, item_entry=plan["item_entry"])
+                                         ctx.status, item_entry=plan["item_entry"] if int(counts[0]) == int(counts[1]) else None)
                 return ops.linear_smallm(attn, self.w_o)
             qkv = torch.empty((T, nh * hd), dtype=h.dtype, device=h.device)  # q only; k and v go straight to the cache
             ops.rope_kv_write_partials(parts, qkv, ctx.positions, ctx.token_seq, tables.indptr, tables.page_ids,
@@ -224,7 +228,7 @@ class PagedAttention(Mixer):
                                 tables.page_ids, plan["row_items"], c[3:4], n_items, plan["row_index"],
                                 plan["row_item_start"], c[4:5], n_rows, attn, nh, nkv, hd, cache.page_size,
                                 self.scale, self.window, SPLIT_KEYS, out_row_of=plan["row_index"],
-                                item_entry=plan["row_item_entry"])
+                                item_entry=plan["row_item_entry"] if n_items == n_rows else None)
             return project(attn, self.w_o)
         if plan is None or out_rows is not None:
             # float32, or only some rows are wanted: the FP32-pipe kernel, one warp per (row, head)
@@ -244,7 +248,7 @@ class PagedAttention(Mixer):
             ops.attn_decode_mma(qkv, cache.k, cache.v, ctx.seq_q_start, ctx.seq_kv_len, tables.indptr, tables.page_ids,
                                 plan["items"], c[0:1], items_cap, plan["dec_seqs"], plan["dec_item_start"], c[1:2],
                                 dec_cap, attn, nh, nkv, hd, cache.page_size, self.scale, self.window, int(counts[5]),
-                                item_entry=plan["item_entry"])
+                                item_entry=plan["item_entry"] if int(counts[0]) == int(counts[1]) else None)
         if tiles_cap:
             ops.attn_prefill_mma(qkv, attn, cache.k, cache.v, ctx.seq_q_start, ctx.seq_q_len, ctx.seq_kv_len,
                                  tables.indptr, tables.page_ids, plan["tiles"], c[2:3], tiles_cap, nh, nkv, hd,
