@@ -667,3 +667,24 @@ def test_gemm_tcgen05_refuses_what_tma_cannot_address(ops):
         ops.gemm_tcgen05(a, torch.zeros(16, 20, dtype=torch.bfloat16, device=DEV), status)
     with pytest.raises(ops.KernelError):
         ops.gemm_tcgen05(torch.zeros(4, 16, device=DEV), torch.zeros(16, 16, device=DEV), status)  # float32
+
+
+@pytest.mark.parametrize("M,N,K", [(8, 128, 64), (1, 256, 128), (16, 3072, 2048), (5, 509, 96), (8, 2048, 8192), (3, 130, 72)])
+def test_linear_tc_decode(ops, M, N, K):
+    """The tcgen05 form of the small-batch product (weights on the 128-row side, TMA ring): same contract as
+    linear_smallm."""
+    g = torch.Generator().manual_seed(M * N + K)
+    a = torch.randn(M, K, generator=g).to(torch.bfloat16).to(DEV)
+    w = (torch.randn(N, K, generator=g) * 0.1).to(torch.bfloat16).to(DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    parts = ops.linear_tc_decode(a, w, status)
+    assert int(status) == 0 and parts.shape[1:] == (M, N)
+    want = a.double() @ w.double().T
+    scale = (a.abs().double() @ w.abs().double().T).max().item()
+    assert (parts.double().sum(0) - want).abs().max().item() <= 2e-6 * scale * math.sqrt(K) + 1e-6
+    if N % 16 == 0 and N >= 32:
+        gate, up = w[: N // 2].contiguous(), w[N // 2:].contiguous()
+        got = ops.linear_tc_decode(a, ops.interleave_gate_up(gate, up), status, gated=True)
+        ref_ = torch.nn.functional.silu(a.double() @ gate.double().T) * (a.double() @ up.double().T)
+        torch.testing.assert_close(got.double(), ref_, rtol=2e-2, atol=6e-3 * ref_.abs().max().item())
+        assert int(status) == 0

@@ -4,7 +4,7 @@ from __future__ import annotations
 
 
 def common_modules() -> list[tuple[str, dict | None]]:
-    return [("elementwise.cu", None), ("sgemm.cu", None), ("sampling.cu", None), ("linear_smallm.cu", None), ("linear_decode.cu", None), ("gemm_tcgen05.cu", None)]
+    return [("elementwise.cu", None), ("sgemm.cu", None), ("sampling.cu", None), ("linear_smallm.cu", None), ("linear_decode.cu", None), ("gemm_tcgen05.cu", None), ("gemm_tcgen05_decode.cu", None)]
 
 
 def head_dim_modules(head_dim: int) -> list[tuple[str, dict | None]]:

@@ -530,6 +530,31 @@ def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, status: torch.Tensor, gated: 
     return out
 
 
+TC_DECODE_M_MAX = 16
+
+
+def linear_tc_decode(a: torch.Tensor, w: torch.Tensor, status: torch.Tensor, max_slices: int = 16,
+                     gated: bool = False) -> torch.Tensor:
+    """a[M, K] @ w[N, K]^T for M <= 16 on the tcgen05 tensor cores with the weights on the 128-row side
+    (TMA-fed ten-stage ring).  Returns float32 slices [slices, M, N] of a K-split product, or with ``gated``
+    (``w`` from ``interleave_gate_up``) silu(gate)*up as bfloat16 [M, N/2]."""
+    _need_cuda(a, w, status)
+    _need(can_use_tcgen05(a, w) and 0 < a.shape[0] <= TC_DECODE_M_MAX, "linear_tc_decode: bfloat16, M <= 16, K % 8 == 0")
+    M, K = a.shape
+    N = w.shape[0]
+    _need(w.shape[1] == K and (not gated or N % 16 == 0), "linear_tc_decode: shapes")
+    lib = _libs.get("gemm_tcgen05_decode.cu")
+    slices = 1 if gated else lib.tkb_linear_tcgen05_decode_slices(c_int(N), c_int(K), c_int(max_slices))
+    if gated:
+        out = torch.empty((M, N // 2), dtype=torch.bfloat16, device=a.device)
+    else:
+        out = torch.empty((slices, M, N), dtype=torch.float32, device=a.device)
+    _check(_fn(lib, "tkb_linear_tcgen05_decode_bf16")(
+        _ptr(a), c_int(a.stride(0)), _ptr(w), c_int(w.stride(0)), _ptr(out), c_int(M), c_int(N), c_int(K),
+        c_int(slices), c_int(1 if gated else 0), _ptr(status), _stream()), "linear_tc_decode")
+    return out
+
+
 def linear(a: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None = None) -> torch.Tensor:
     """a[M, K] @ w[N, K]^T.  float32: this engine's FP32 kernel (no tf32).  bfloat16: the library
     matrix product (cuBLAS through torch), float32 accumulation, output bfloat16 or float32."""
