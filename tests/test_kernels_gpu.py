@@ -373,7 +373,7 @@ def run_mma_attention(ops, lens_q, lens_kv, nh, nkv, hd, ps, window, seed, n_pag
     if n_dec:
         ops.attn_decode_mma(qkv, kc, vc, i32(q_start), i32(lens_kv), indptr, pages, i32(plan["items"]), c[0:1], n_items,
                             i32(plan["dec_seqs"]), i32(plan["dec_item_start"]), c[1:2], n_dec, out, nh, nkv, hd, ps, scale,
-                            window, int(plan["counts"][5]), item_entry=i32(plan["item_entry"]) if merged else None)
+                            window, item_entry=i32(plan["item_entry"]) if merged else None)
     if n_tiles:
         ops.attn_prefill_mma(qkv, out, kc, vc, i32(q_start), i32(lens_q), i32(lens_kv), indptr, pages, i32(plan["tiles"]),
                              c[2:3], n_tiles, nh, nkv, hd, ps, scale, window)
@@ -423,7 +423,7 @@ def test_mma_attention_finds_one_far_key(ops):
             if n == 1:
                 ops.attn_decode_mma(qkv.to(DEV), kc, vc, i32([0]), i32([L]), indptr, pages, i32(plan["items"]), c[0:1],
                                     int(plan["counts"][0]), i32(plan["dec_seqs"]), i32(plan["dec_item_start"]), c[1:2], 1,
-                                    out, nh, nkv, hd, ps, 1.0, None, int(plan["counts"][5]))
+                                    out, nh, nkv, hd, ps, 1.0, None)
             else:
                 ops.attn_prefill_mma(qkv.to(DEV), out, kc, vc, i32([0]), i32(lens_q), i32([L]), indptr, pages,
                                      i32(plan["tiles"]), c[2:3], int(plan["counts"][2]), nh, nkv, hd, ps, 1.0, None)
@@ -594,13 +594,13 @@ def test_fused_rope_decode_attention_equals_the_separate_kernels(ops, hd, nh, nk
     ops.rope_kv_write(q1, positions, token_seq, indptr, pages, inv, kc1, vc1, nh, nkv, hd, rot, ps, True, status)
     want = torch.zeros(B, nh * hd, dtype=dtype, device=DEV)
     ops.attn_decode_mma(q1, kc1, vc1, q_start, kv_len, indptr, pages, i32(plan["items"]), c[0:1], n_items, i32(plan["dec_seqs"]),
-                        i32(plan["dec_item_start"]), c[1:2], n_dec, want, nh, nkv, hd, ps, scale, window, int(plan["counts"][5]))
+                        i32(plan["dec_item_start"]), c[1:2], n_dec, want, nh, nkv, hd, ps, scale, window)
     # fused
     kc2, vc2 = kc.clone(), vc.clone()
     got = torch.zeros_like(want)
     ops.attn_decode_rope_mma(qkv, kc2, vc2, q_start, kv_len, indptr, pages, i32(plan["items"]), c[0:1], n_items,
                              i32(plan["dec_seqs"]), i32(plan["dec_item_start"]), c[1:2], n_dec, got, nh, nkv, hd, ps, scale,
-                             window, int(plan["counts"][5]), inv, rot, True, status, item_entry=i32(plan["item_entry"]))
+                             window, inv, rot, True, status, item_entry=i32(plan["item_entry"]))
     assert int(status) == 0
     assert torch.equal(vc2, vc1)
     torch.testing.assert_close(kc2.float().nan_to_num(7.0), kc1.float().nan_to_num(7.0), rtol=1e-2, atol=1e-2)
@@ -613,7 +613,7 @@ def test_fused_rope_decode_attention_equals_the_separate_kernels(ops, hd, nh, nk
     got3 = torch.zeros_like(want)
     ops.attn_decode_rope_mma(parts, kc3, vc3, q_start, kv_len, indptr, pages, i32(plan["items"]), c[0:1], n_items,
                              i32(plan["dec_seqs"]), i32(plan["dec_item_start"]), c[1:2], n_dec, got3, nh, nkv, hd, ps, scale,
-                             window, int(plan["counts"][5]), inv, rot, True, status)
+                             window, inv, rot, True, status)
     if torch.equal(qsum, qkv):
         assert torch.equal(got3, got) and torch.equal(kc3.nan_to_num(7.0), kc2.nan_to_num(7.0))
     torch.testing.assert_close(got3.float(), want.float(), rtol=3e-2, atol=3e-2)
@@ -623,7 +623,7 @@ def test_fused_rope_decode_attention_equals_the_separate_kernels(ops, hd, nh, nk
     got4 = torch.zeros_like(want)
     ops.attn_decode_rope_mma(qkv, kc4, vc4, q_start, kv_len, indptr, pages, i32(plan["items"]), c[0:1], n_items,
                              i32(plan["dec_seqs"]), i32(plan["dec_item_start"]), c[1:2], n_dec, got4, nh, nkv, hd, ps, scale,
-                             window, int(plan["counts"][5]), inv, rot, False, status)
+                             window, inv, rot, False, status)
     assert torch.equal(kc4.nan_to_num(7.0), kc1.nan_to_num(7.0)) and torch.equal(vc4, vc1)
     torch.testing.assert_close(got4.float(), want.float(), rtol=1.6e-2, atol=1e-2)
 

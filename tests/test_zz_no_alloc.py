@@ -66,14 +66,14 @@ def test_static_scratch_entry_point_matches_the_usual_one():
         scale = 1 / math.sqrt(hd)
         want = torch.zeros(B, nh * hd, dtype=torch.bfloat16, device=DEV)
         ops.attn_decode_mma(qkv, kc, vc, q_start, kv_len, indptr, pages, items, counts[0:1], n_items, dec_seqs, dec_start,
-                            counts[1:2], n_dec, want, nh, nkv, hd, ps, scale, None, int(plan["counts"][5]))
+                            counts[1:2], n_dec, want, nh, nkv, hd, ps, scale, None)
         got = torch.zeros_like(want)
         stream = c_void_p(torch.cuda.current_stream().cuda_stream)
         before = torch.cuda.memory_allocated()
         rc = fn(ptr(qkv), c_int(qkv.shape[1]), ptr(kc), ptr(vc), ptr(q_start), ptr(kv_len), ptr(indptr), ptr(pages),
                 ptr(items), ptr(counts[0:1]), c_int(n_items), ptr(dec_seqs), ptr(dec_start), ptr(counts[1:2]),
                 c_int(n_dec), ptr(got), c_int(got.shape[1]), c_int(nh), c_int(nkv), c_int(ps), c_float(scale), c_int(0),
-                c_int(int(plan["counts"][5])), stream)
+                stream)
         assert rc == 0
         torch.cuda.synchronize()
         assert torch.cuda.memory_allocated() == before
@@ -84,7 +84,7 @@ def test_static_scratch_entry_point_matches_the_usual_one():
     too_many = capacity // (nh * (hd + 2)) + 1
     rc = fn(ptr(qkv), c_int(qkv.shape[1]), ptr(kc), ptr(vc), ptr(q_start), ptr(kv_len), ptr(indptr), ptr(pages),
             ptr(items), ptr(counts[0:1]), c_int(too_many), ptr(dec_seqs), ptr(dec_start), ptr(counts[1:2]), c_int(n_dec),
-            ptr(got), c_int(got.shape[1]), c_int(nh), c_int(nkv), c_int(ps), c_float(scale), c_int(0), c_int(int(plan["counts"][5])),
+            ptr(got), c_int(got.shape[1]), c_int(nh), c_int(nkv), c_int(ps), c_float(scale), c_int(0),
             stream)
     assert rc == -4
     torch.cuda.synchronize()

@@ -42,7 +42,7 @@ int tkb_attn_decode_static_scratch_bf16(const void* q, int q_stride, const void*
                                         const int* page_ids, const int* items, const int* n_items_ptr, int items_cap,
                                         const int* dec_seqs, const int* dec_item_start, const int* n_dec_ptr,
                                         int dec_cap, void* out, int out_stride, int nh, int nkv, int ps, float scale,
-                                        int window, int split_keys, void* stream);
+                                        int window, void* stream);
 
 #ifdef __cplusplus
 }

@@ -1,8 +1,8 @@
 // bfloat16 attention over the paged cache on the tensor cores (mma.sync m16n8k16, float32
 // accumulation; scores, softmax and the running rescale are float32).
 //
-//   attn_decode_mma:  one query token per request, keys split into chunks of `split_keys`
-//                     (work items built on the host), partial results merged by attn_decode_merge.
+//   attn_decode_mma:  one query token per request, keys split into chunks
+//                     (work items (request, first key, keys) built on the host), partial results merged by attn_decode_merge.
 //                     The 16 rows of the MMA tile are the query heads that share one key/value
 //                     head, so every key and value is read once for the whole group.
 //   attn_prefill_mma: portions of prompts; a block owns 64 consecutive query tokens of one head
@@ -37,7 +37,7 @@ constexpr int STAGE_B = 2 * TILE_B;   // K tile then V tile
 constexpr int SMEM_B = 2 * STAGE_B;   // two stages (tiled kernel for portions)
 // The split-key kernel keeps as many tiles in flight as fit: with 256 keys a split, four stages put a whole
 // split on its way at once, which is what a memory-bound kernel with few blocks per SM needs.
-constexpr int DSTAGES = 4 * STAGE_B <= 80 * 1024 ? 4 : (3 * STAGE_B <= 110 * 1024 ? 3 : 2);
+constexpr int DSTAGES = 3 * STAGE_B <= 110 * 1024 ? 3 : 2;  // three stages leave room for three blocks an SM at head size 64
 constexpr int DEC_SMEM_B = DSTAGES * STAGE_B;
 constexpr int KSTEPS = HD / 16;       // k-steps of Q.K^T
 constexpr int DTILES = HD / 8;        // n-tiles of P.V
@@ -186,7 +186,7 @@ attn_decode_mma_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restric
                        const int* __restrict__ seq_kv_len, const int* __restrict__ page_indptr,
                        const int* __restrict__ page_ids, const int* __restrict__ items,
                        const int* __restrict__ n_items_ptr, float* __restrict__ part_o, float* __restrict__ part_ml,
-                       int nh, int nkv, int ps, float scale_log2, int window, int split_keys, int head_tiles,
+                       int nh, int nkv, int ps, float scale_log2, int window, int head_tiles,
                        const float* __restrict__ inv_freq, int rot, int write_cache, int num_pages,
                        int* __restrict__ status, const float* __restrict__ qkv_parts, int n_parts,
                        long long part_stride, int* __restrict__ counters, const int* __restrict__ item_entry,
@@ -197,7 +197,7 @@ attn_decode_mma_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restric
   grid_dependency_wait();
   const int item = blockIdx.x;
   if (item >= *n_items_ptr) return;
-  const int s = items[2 * item], split = items[2 * item + 1];
+  const int s = items[3 * item];  // work item: request row, first key (counted from the first visible key), keys
   const int kvh = blockIdx.y / head_tiles, ht = blockIdx.y - kvh * head_tiles;
   const int group = nh / nkv;
   const int g0 = ht * 16;
@@ -207,8 +207,8 @@ attn_decode_mma_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restric
   const int p = kv_len - 1;
   int lo = 0;
   if (window > 0 && p - window + 1 > 0) lo = p - window + 1;
-  const int k_begin = lo + split * split_keys;
-  const int k_end = min(kv_len, k_begin + split_keys);
+  const int k_begin = lo + items[3 * item + 1];
+  const int k_end = min(kv_len, k_begin + items[3 * item + 2]);
   const int* table = page_ids + page_indptr[s];
   const int t = seq_q_start[s];
   const bf16* qrow = q + (size_t)t * q_stride + (size_t)(kvh * group + g0) * HD;
@@ -659,15 +659,15 @@ TKB_EXPORT long long tkb_attn_decode_scratch_floats(int items_cap, int nh) {
   return (long long)items_cap * nh * (HD + 2);
 }
 
-// items: int32 [n_items_cap * 2] (request row, split); n_items_ptr: device int32 with the live count.
+// items: int32 [n_items_cap * 3] (request row, first key counted from the first visible one, number of keys); n_items_ptr: device int32 with the live count.
 // The grid is sized by items_cap, so a captured graph serves any count up to it.
 TKB_EXPORT int tkb_attn_decode_mma_bf16(const void* q, int q_stride, const void* kcache, const void* vcache,
                                         const int* seq_q_start, const int* seq_kv_len, const int* page_indptr,
                                         const int* page_ids, const int* items, const int* n_items_ptr, int items_cap,
                                         float* part_o, float* part_ml, int nh, int nkv, int ps, float scale, int window,
-                                        int split_keys, void* st) {
+                                        void* st) {
   if (items_cap <= 0) return 0;
-  if (nkv <= 0 || nh % nkv != 0 || ps <= 0 || split_keys <= 0) return -2;
+  if (nkv <= 0 || nh % nkv != 0 || ps <= 0) return -2;
   int rc = ensure_smem_attr();
   if (rc) return rc;
   const int group = nh / nkv;
@@ -676,7 +676,7 @@ TKB_EXPORT int tkb_attn_decode_mma_bf16(const void* q, int q_stride, const void*
   dim3 grid(items_cap, nkv * head_tiles);
   return launch_pdl(attn_decode_mma_kernel<false>, grid, dim3(128), (size_t)DEC_SMEM_B, (cudaStream_t)st, (const bf16*)q,
                     q_stride, (bf16*)kcache, (bf16*)vcache, seq_q_start, seq_kv_len, page_indptr, page_ids, items,
-                    n_items_ptr, part_o, part_ml, nh, nkv, ps, scale * 1.4426950408889634f, window, split_keys,
+                    n_items_ptr, part_o, part_ml, nh, nkv, ps, scale * 1.4426950408889634f, window,
                     head_tiles, (const float*)nullptr, 0, 0, 0, (int*)nullptr, (const float*)nullptr, 0, 0LL,
                     (int*)nullptr, (const int*)nullptr, (const int*)nullptr, (const int*)nullptr, (bf16*)nullptr, 0);
 }
@@ -691,10 +691,10 @@ TKB_EXPORT int tkb_attn_decode_rope_mma_bf16(const void* qkv, int q_stride, cons
                                              const int* seq_q_start, const int* seq_kv_len, const int* page_indptr,
                                              const int* page_ids, const int* items, const int* n_items_ptr,
                                              int items_cap, float* part_o, float* part_ml, int nh, int nkv, int ps,
-                                             float scale, int window, int split_keys, const float* inv_freq, int rot,
+                                             float scale, int window, const float* inv_freq, int rot,
                                              int write_cache, int num_pages, int* status, void* st) {
   if (items_cap <= 0) return 0;
-  if (nkv <= 0 || nh % nkv != 0 || ps <= 0 || split_keys <= 0 || rot < 0 || rot > HD || (rot & 3)) return -2;
+  if (nkv <= 0 || nh % nkv != 0 || ps <= 0 || rot < 0 || rot > HD || (rot & 3)) return -2;
   int rc = ensure_smem_attr();
   if (rc) return rc;
   const int group = nh / nkv;
@@ -703,7 +703,7 @@ TKB_EXPORT int tkb_attn_decode_rope_mma_bf16(const void* qkv, int q_stride, cons
   dim3 grid(items_cap, nkv * head_tiles);
   return launch_pdl(attn_decode_mma_kernel<true>, grid, dim3(128), (size_t)DEC_SMEM_B, (cudaStream_t)st, (const bf16*)qkv,
                     q_stride, (bf16*)kcache, (bf16*)vcache, seq_q_start, seq_kv_len, page_indptr, page_ids, items,
-                    n_items_ptr, part_o, part_ml, nh, nkv, ps, scale * 1.4426950408889634f, window, split_keys,
+                    n_items_ptr, part_o, part_ml, nh, nkv, ps, scale * 1.4426950408889634f, window,
                     head_tiles, inv_freq, rot, write_cache, num_pages, status, qkv_parts, n_parts, part_stride,
                     (int*)nullptr, (const int*)nullptr, (const int*)nullptr, (const int*)nullptr, (bf16*)nullptr, 0);
 }
@@ -718,12 +718,12 @@ TKB_EXPORT int tkb_attn_decode_merged_bf16(const void* qkv, int q_stride, const 
                                            const int* seq_kv_len, const int* page_indptr, const int* page_ids,
                                            const int* items, const int* n_items_ptr, int items_cap, float* part_o,
                                            float* part_ml, int nh, int nkv, int ps, float scale, int window,
-                                           int split_keys, int fused, const float* inv_freq, int rot, int write_cache,
+                                           int fused, const float* inv_freq, int rot, int write_cache,
                                            int num_pages, int* status, int* counters, const int* item_entry,
                                            const int* dec_item_start, const int* out_row_of, void* out, int out_stride,
                                            void* st) {
   if (items_cap <= 0) return 0;
-  if (nkv <= 0 || nh % nkv != 0 || ps <= 0 || split_keys <= 0 || counters == nullptr) return -2;
+  if (nkv <= 0 || nh % nkv != 0 || ps <= 0 || counters == nullptr) return -2;
   if (fused && (rot < 0 || rot > HD || (rot & 3))) return -2;
   int rc = ensure_smem_attr();
   if (rc) return rc;
@@ -735,12 +735,12 @@ TKB_EXPORT int tkb_attn_decode_merged_bf16(const void* qkv, int q_stride, const 
   if (fused)
     return launch_pdl(attn_decode_mma_kernel<true>, grid, dim3(128), (size_t)DEC_SMEM_B, (cudaStream_t)st,
                       (const bf16*)qkv, q_stride, (bf16*)kcache, (bf16*)vcache, seq_q_start, seq_kv_len, page_indptr,
-                      page_ids, items, n_items_ptr, part_o, part_ml, nh, nkv, ps, sl2, window, split_keys, head_tiles,
+                      page_ids, items, n_items_ptr, part_o, part_ml, nh, nkv, ps, sl2, window, head_tiles,
                       inv_freq, rot, write_cache, num_pages, status, qkv_parts, n_parts, part_stride, counters,
                       item_entry, dec_item_start, out_row_of, (bf16*)out, out_stride);
   return launch_pdl(attn_decode_mma_kernel<false>, grid, dim3(128), (size_t)DEC_SMEM_B, (cudaStream_t)st,
                     (const bf16*)qkv, q_stride, (bf16*)kcache, (bf16*)vcache, seq_q_start, seq_kv_len, page_indptr,
-                    page_ids, items, n_items_ptr, part_o, part_ml, nh, nkv, ps, sl2, window, split_keys, head_tiles,
+                    page_ids, items, n_items_ptr, part_o, part_ml, nh, nkv, ps, sl2, window, head_tiles,
                     (const float*)nullptr, 0, 0, 0, (int*)nullptr, (const float*)nullptr, 0, 0LL, counters, item_entry,
                     dec_item_start, out_row_of, (bf16*)out, out_stride);
 }

@@ -354,10 +354,10 @@ def attn_decode_mma(qkv: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tenso
                     seq_kv_len: torch.Tensor, page_indptr: torch.Tensor, page_ids: torch.Tensor, items: torch.Tensor,
                     n_items: torch.Tensor, items_cap: int, dec_seqs: torch.Tensor, dec_item_start: torch.Tensor,
                     n_dec: torch.Tensor, dec_cap: int, out: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int,
-                    page_size: int, scale: float, window: int | None, split_keys: int,
+                    page_size: int, scale: float, window: int | None,
                     out_row_of: torch.Tensor | None = None, item_entry: torch.Tensor | None = None) -> None:
     """bfloat16 split-key attention for requests that bring one token: ``items`` are (request row,
-    split) pairs of ``split_keys`` keys each, computed into float32 partial results and merged into
+    first key, number of keys) triples, computed into float32 partial results and merged into
     ``out`` [T, n_heads*head_dim] at each request's token row (or at row ``out_row_of[request]``).
     ``n_items``/``n_dec`` are device counters; the launch grids are sized by ``items_cap``/``dec_cap``."""
     _need_cuda(qkv, kcache, vcache, seq_q_start, seq_kv_len, page_indptr, page_ids, items, n_items, dec_seqs,
@@ -367,7 +367,7 @@ def attn_decode_mma(qkv: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tenso
           "attn_decode_mma: bfloat16 only")
     _need(tuple(kcache.shape[1:]) == (n_kv_heads, page_size, head_dim), "attn_decode_mma: cache layout")
     _need(out.is_contiguous() and out.shape[1] == n_heads * head_dim, "attn_decode_mma: out")
-    _need(items.numel() >= 2 * items_cap and dec_item_start.numel() >= dec_cap + 1, "attn_decode_mma: plan arrays")
+    _need(items.numel() >= 3 * items_cap and dec_item_start.numel() >= dec_cap + 1, "attn_decode_mma: plan arrays")
     lib = _libs.get("attention_mma.cu", TKB_HD=head_dim)
     part_o = torch.empty((items_cap, n_heads, head_dim), dtype=torch.float32, device=qkv.device)
     part_ml = torch.empty((items_cap, n_heads, 2), dtype=torch.float32, device=qkv.device)
@@ -378,7 +378,7 @@ def attn_decode_mma(qkv: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tenso
             _ptr(qkv), c_int(qkv.shape[1]), _ptr(None), c_int(0), ctypes.c_longlong(0), _ptr(kcache), _ptr(vcache),
             _ptr(seq_q_start), _ptr(seq_kv_len), _ptr(page_indptr), _ptr(page_ids), _ptr(items), _ptr(n_items),
             c_int(items_cap), _ptr(part_o), _ptr(part_ml), c_int(n_heads), c_int(n_kv_heads), c_int(page_size),
-            c_float(scale), c_int(window or 0), c_int(split_keys), c_int(0), _ptr(None), c_int(0), c_int(0), c_int(0),
+            c_float(scale), c_int(window or 0), c_int(0), _ptr(None), c_int(0), c_int(0), c_int(0),
             _ptr(None), _ptr(counters), _ptr(item_entry), _ptr(dec_item_start),
             _ptr(out_row_of if out_row_of is not None else seq_q_start), _ptr(out), c_int(out.shape[1]), _stream()),
             "attn_decode_merged")
@@ -386,7 +386,7 @@ def attn_decode_mma(qkv: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tenso
     _check(_fn(lib, "tkb_attn_decode_mma_bf16")(
         _ptr(qkv), c_int(qkv.shape[1]), _ptr(kcache), _ptr(vcache), _ptr(seq_q_start), _ptr(seq_kv_len),
         _ptr(page_indptr), _ptr(page_ids), _ptr(items), _ptr(n_items), c_int(items_cap), _ptr(part_o), _ptr(part_ml),
-        c_int(n_heads), c_int(n_kv_heads), c_int(page_size), c_float(scale), c_int(window or 0), c_int(split_keys),
+        c_int(n_heads), c_int(n_kv_heads), c_int(page_size), c_float(scale), c_int(window or 0),
         _stream()), "attn_decode_mma")
     _check(_fn(lib, "tkb_attn_decode_merge_bf16")(
         _ptr(part_o), _ptr(part_ml), _ptr(dec_seqs), _ptr(dec_item_start), _ptr(n_dec), c_int(dec_cap),
@@ -399,7 +399,7 @@ def attn_decode_rope_mma(qkv: torch.Tensor, kcache: torch.Tensor, vcache: torch.
                          items: torch.Tensor, n_items: torch.Tensor, items_cap: int, dec_seqs: torch.Tensor,
                          dec_item_start: torch.Tensor, n_dec: torch.Tensor, dec_cap: int, out: torch.Tensor,
                          n_heads: int, n_kv_heads: int, head_dim: int, page_size: int, scale: float,
-                         window: int | None, split_keys: int, inv_freq: torch.Tensor | None, rotary_dim: int,
+                         window: int | None, inv_freq: torch.Tensor | None, rotary_dim: int,
                          write_cache: bool, status: torch.Tensor, item_entry: torch.Tensor | None = None) -> None:
     """``attn_decode_mma`` with rotary encoding and the cache write folded in: ``qkv`` holds the step's
     un-rotated q|k|v rows of requests that bring one token each, as bfloat16 [T, C] or as the float32 slices
@@ -431,7 +431,7 @@ def attn_decode_rope_mma(qkv: torch.Tensor, kcache: torch.Tensor, vcache: torch.
             _ptr(qkv_ptr), c_int(C), _ptr(parts), c_int(n_parts), ctypes.c_longlong(part_stride), _ptr(kcache),
             _ptr(vcache), _ptr(seq_q_start), _ptr(seq_kv_len), _ptr(page_indptr), _ptr(page_ids), _ptr(items),
             _ptr(n_items), c_int(items_cap), _ptr(part_o), _ptr(part_ml), c_int(n_heads), c_int(n_kv_heads),
-            c_int(page_size), c_float(scale), c_int(window or 0), c_int(split_keys), c_int(1), _ptr(inv_freq),
+            c_int(page_size), c_float(scale), c_int(window or 0), c_int(1), _ptr(inv_freq),
             c_int(rotary_dim), c_int(1 if write_cache else 0), c_int(kcache.shape[0]), _ptr(status), _ptr(counters),
             _ptr(item_entry), _ptr(dec_item_start), _ptr(seq_q_start), _ptr(out), c_int(out.shape[1]), _stream()),
             "attn_decode_merged")
@@ -440,7 +440,7 @@ def attn_decode_rope_mma(qkv: torch.Tensor, kcache: torch.Tensor, vcache: torch.
         _ptr(qkv_ptr), c_int(C), _ptr(parts), c_int(n_parts), ctypes.c_longlong(part_stride), _ptr(kcache),
         _ptr(vcache), _ptr(seq_q_start), _ptr(seq_kv_len),
         _ptr(page_indptr), _ptr(page_ids), _ptr(items), _ptr(n_items), c_int(items_cap), _ptr(part_o), _ptr(part_ml),
-        c_int(n_heads), c_int(n_kv_heads), c_int(page_size), c_float(scale), c_int(window or 0), c_int(split_keys),
+        c_int(n_heads), c_int(n_kv_heads), c_int(page_size), c_float(scale), c_int(window or 0),
         _ptr(inv_freq), c_int(rotary_dim), c_int(1 if write_cache else 0), c_int(kcache.shape[0]), _ptr(status),
         _stream()), "attn_decode_rope_mma")
     _check(_fn(lib, "tkb_attn_decode_merge_bf16")(

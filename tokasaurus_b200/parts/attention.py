@@ -25,28 +25,48 @@ import torch
 from tokasaurus_b200.kernels import ops
 from tokasaurus_b200.parts.base import LazyNorm, Mixer, PagedCacheNeed, PositionEncoding, WeightSpec
 
-SPLIT_KEYS = 512  # keys per work item of the split-key kernel when there is much work
-SPLIT_KEYS_FEW = 256  # ... and when the whole step has few work items, so that more blocks share it
+SPLIT_KEYS = 512  # keys per work item of the split-key kernel when a step has more work than one wave of blocks
+MIN_SPLIT_KEYS = 128
 QUERY_TILE = 64  # queries per block of the tiled kernel
+DECODE_BLOCK_SLOTS = 148 * 3  # blocks of the split-key kernel that a B200 holds at once (head size 64)
 
 
-def plan_attention(host, window: int | None, capacity: dict | None = None) -> dict[str, np.ndarray]:
-    """Work items for one step: (request row, split) pairs for requests with one token, (request
-    row, first query) pairs for 64-query tiles of longer portions."""
+def split_keys_evenly(span: np.ndarray, blocks_per_item: int) -> tuple[np.ndarray, np.ndarray]:
+    """How many work items each single-token request gets and how many keys each item holds (a multiple of
+    64, the kernel's tile).  If 512-key items of all requests fit into one wave of blocks, the requests are
+    cut finer, evenly, so that the wave is full; otherwise 512 keys an item."""
+    max_items = max(1, DECODE_BLOCK_SLOTS // max(1, blocks_per_item))
+    coarse = np.maximum(1, -(-span // SPLIT_KEYS))
+    if int(coarse.sum()) > max_items or span.shape[0] == 0:
+        return coarse, np.full(span.shape, SPLIT_KEYS, dtype=np.int64)
+    target = max(MIN_SPLIT_KEYS, -(-int(span.sum()) // max_items))
+    n = np.maximum(1, span // target)
+    # shrink until the wave holds them all (integer division above can overshoot by a few items)
+    while int(n.sum()) > max_items and int(n.max()) > 1:
+        n[np.argmax(n)] -= 1
+    size = -(-(-(-span // n)) // 64) * 64
+    n = np.maximum(1, -(-span // size))
+    return n, size
+
+
+def plan_attention(host, window: int | None, capacity: dict | None = None, blocks_per_item: int = 8
+                   ) -> dict[str, np.ndarray]:
+    """Work items for one step: (request row, first key, keys) triples for requests with one token,
+    (request row, first query) pairs for 64-query tiles of longer portions.  ``blocks_per_item``: blocks the
+    split-key kernel launches per item (kv heads x head tiles)."""
     q_len = np.asarray(host.seq_q_len, dtype=np.int64)
     kv_len = np.asarray(host.seq_kv_len, dtype=np.int64)
     dec_seqs = np.nonzero(q_len == 1)[0]
     span = kv_len[dec_seqs]
     if window:
         span = np.minimum(span, window)
-    # smaller splits while the step's work items are few (more blocks in flight), larger ones otherwise
-    split_keys = SPLIT_KEYS_FEW if int(np.sum(-(-span // SPLIT_KEYS_FEW))) <= 48 else SPLIT_KEYS
-    n_splits = np.maximum(1, -(-span // split_keys))
+    n_splits, split_size = split_keys_evenly(span, blocks_per_item)
     dec_start = np.concatenate([[0], np.cumsum(n_splits)])
     n_items = int(dec_start[-1])
     item_seq = np.repeat(dec_seqs, n_splits)
-    item_split = np.arange(n_items) - np.repeat(dec_start[:-1], n_splits)
-    items = np.stack([item_seq, item_split], axis=1).reshape(-1)
+    item_size = np.repeat(split_size, n_splits)
+    item_first = (np.arange(n_items) - np.repeat(dec_start[:-1], n_splits)) * item_size
+    items = np.stack([item_seq, item_first, item_size], axis=1).reshape(-1)
     item_entry = np.repeat(np.arange(dec_seqs.shape[0]), n_splits)  # index of each item's request in dec_seqs
     pre_seqs = np.nonzero(q_len > 1)[0]
     n_tiles_seq = -(-q_len[pre_seqs] // QUERY_TILE)
@@ -69,24 +89,25 @@ def plan_attention(host, window: int | None, capacity: dict | None = None) -> di
         rows = np.asarray(rows, dtype=np.int64)
         r_kv = np.asarray(host.positions, dtype=np.int64)[rows] + 1
         r_span = np.minimum(r_kv, window) if window else r_kv
-        r_splits = np.maximum(1, -(-r_span // SPLIT_KEYS))  # wanted rows always use the large split
+        r_splits, r_size = split_keys_evenly(r_span, blocks_per_item)
         r_start = np.concatenate([[0], np.cumsum(r_splits)])
         n_row_items, n_rows = int(r_start[-1]), int(rows.shape[0])
         r_item = np.repeat(np.arange(n_rows), r_splits)
-        r_split = np.arange(n_row_items) - np.repeat(r_start[:-1], r_splits)
+        r_isize = np.repeat(r_size, r_splits)
+        r_first = (np.arange(n_row_items) - np.repeat(r_start[:-1], r_splits)) * r_isize
         i32 = lambda a: np.ascontiguousarray(a, dtype=np.int32)  # noqa: E731
-        extra = dict(row_items=i32(np.stack([r_item, r_split], axis=1).reshape(-1)), row_item_start=i32(r_start),
+        extra = dict(row_items=i32(np.stack([r_item, r_first, r_isize], axis=1).reshape(-1)), row_item_start=i32(r_start),
                      row_item_entry=i32(r_item),
                      row_token=i32(rows), row_kv_len=i32(r_kv), row_seq=i32(np.asarray(host.token_seq)[rows]),
                      row_index=i32(np.arange(n_rows)))
-    counts = np.asarray([n_items, dec_seqs.shape[0], n_tiles, n_row_items, n_rows, split_keys, 0, 0], dtype=np.int32)
+    counts = np.asarray([n_items, dec_seqs.shape[0], n_tiles, n_row_items, n_rows, 0, 0, 0], dtype=np.int32)
 
     def padded(x, n):
         a = np.zeros(max(n, x.shape[0], 1), dtype=np.int32)
         a[: x.shape[0]] = x
         return a
 
-    return dict(counts=counts, items=padded(items, 2 * cap.get("items", 0)),
+    return dict(counts=counts, items=padded(items, 3 * cap.get("items", 0)),
                 item_entry=padded(item_entry, cap.get("items", 0)),
                 dec_seqs=padded(dec_seqs, cap.get("dec", 0)), dec_item_start=padded(dec_start, cap.get("dec", 0) + 1),
                 tiles=padded(tiles, 2 * cap.get("tiles", 0)), **extra)
@@ -139,10 +160,13 @@ class PagedAttention(Mixer):
         self.dtype = rt.dtype
 
     def plan_key(self):
-        return ("paged_attention", self.window) if self.dtype == torch.bfloat16 else None
+        return ("paged_attention", self.window, self._blocks_per_item()) if self.dtype == torch.bfloat16 else None
+
+    def _blocks_per_item(self) -> int:
+        return self.n_kv_heads * ((self.n_heads // self.n_kv_heads + 15) // 16)
 
     def plan(self, host, capacity=None):
-        return plan_attention(host, self.window, capacity)
+        return plan_attention(host, self.window, capacity, self._blocks_per_item())
 
     def pad_plan(self, plan: dict, capacity: dict) -> dict:
         """The same plan with its arrays at the fixed sizes of a CUDA graph."""
@@ -152,7 +176,7 @@ class PagedAttention(Mixer):
             return a
 
         out = dict(plan)
-        out["items"] = padded(plan["items"], 2 * capacity.get("items", 0))
+        out["items"] = padded(plan["items"], 3 * capacity.get("items", 0))
         out["item_entry"] = padded(plan["item_entry"], capacity.get("items", 0))
         out["dec_seqs"] = padded(plan["dec_seqs"], capacity.get("dec", 0))
         out["dec_item_start"] = padded(plan["dec_item_start"], capacity.get("dec", 0) + 1)
@@ -180,7 +204,7 @@ class PagedAttention(Mixer):
                                          tables.page_ids, plan["items"], c[0:1], caps["items"] if caps else int(counts[0]),
                                          plan["dec_seqs"], plan["dec_item_start"], c[1:2],
                                          caps["dec"] if caps else int(counts[1]), attn, nh, nkv, hd, cache.page_size,
-                                         self.scale, self.window, int(counts[5]), self.inv_freq, rot, cache.writable,
+                                         self.scale, self.window, self.inv_freq, rot, cache.writable,
                                          ctx.status, item_entry=plan["item_entry"] if int(counts[0]) == int(counts[1]) else None)
                 if residual is not None:
                     ops.linear_decode(attn, self.w_o, "add", out=residual)
@@ -203,7 +227,7 @@ class PagedAttention(Mixer):
                                          tables.page_ids, plan["items"], c[0:1], caps["items"] if caps else int(counts[0]),
                                          plan["dec_seqs"], plan["dec_item_start"], c[1:2],
                                          caps["dec"] if caps else int(counts[1]), attn, nh, nkv, hd, cache.page_size,
-                                         self.scale, self.window, int(counts[5]), self.inv_freq, rot, cache.writable,
+                                         self.scale, self.window, self.inv_freq, rot, cache.writable,
                                          ctx.status, item_entry=plan["item_entry"] if int(counts[0]) == int(counts[1]) else None)
                 return ops.linear_smallm(attn, self.w_o)
             qkv = torch.empty((T, nh * hd), dtype=h.dtype, device=h.device)  # q only; k and v go straight to the cache
@@ -227,7 +251,7 @@ class PagedAttention(Mixer):
             ops.attn_decode_mma(qkv, cache.k, cache.v, plan["row_token"], plan["row_kv_len"], row_indptr,
                                 tables.page_ids, plan["row_items"], c[3:4], n_items, plan["row_index"],
                                 plan["row_item_start"], c[4:5], n_rows, attn, nh, nkv, hd, cache.page_size,
-                                self.scale, self.window, SPLIT_KEYS, out_row_of=plan["row_index"],
+                                self.scale, self.window, out_row_of=plan["row_index"],
                                 item_entry=plan["row_item_entry"] if n_items == n_rows else None)
             return project(attn, self.w_o)
         if plan is None or out_rows is not None:
@@ -247,7 +271,7 @@ class PagedAttention(Mixer):
         if dec_cap:
             ops.attn_decode_mma(qkv, cache.k, cache.v, ctx.seq_q_start, ctx.seq_kv_len, tables.indptr, tables.page_ids,
                                 plan["items"], c[0:1], items_cap, plan["dec_seqs"], plan["dec_item_start"], c[1:2],
-                                dec_cap, attn, nh, nkv, hd, cache.page_size, self.scale, self.window, int(counts[5]),
+                                dec_cap, attn, nh, nkv, hd, cache.page_size, self.scale, self.window,
                                 item_entry=plan["item_entry"] if int(counts[0]) == int(counts[1]) else None)
         if tiles_cap:
             ops.attn_prefill_mma(qkv, attn, cache.k, cache.v, ctx.seq_q_start, ctx.seq_q_len, ctx.seq_kv_len,
