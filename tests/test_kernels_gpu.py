@@ -669,7 +669,8 @@ def test_gemm_tcgen05_refuses_what_tma_cannot_address(ops):
         ops.gemm_tcgen05(torch.zeros(4, 16, device=DEV), torch.zeros(16, 16, device=DEV), status)  # float32
 
 
-@pytest.mark.parametrize("M,N,K", [(8, 128, 64), (1, 256, 128), (16, 3072, 2048), (5, 509, 96), (8, 2048, 8192), (3, 130, 72)])
+@pytest.mark.parametrize("M,N,K", [(8, 128, 64), (1, 256, 128), (16, 3072, 2048), (5, 509, 96), (8, 2048, 8192), (3, 130, 72),
+                                   (17, 256, 128), (32, 2048, 2048), (33, 509, 96), (64, 3072, 2048), (50, 2048, 8192)])
 def test_linear_tc_decode(ops, M, N, K):
     """The tcgen05 form of the small-batch product (weights on the 128-row side, TMA ring): same contract as
     linear_smallm."""

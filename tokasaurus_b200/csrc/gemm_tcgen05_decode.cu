@@ -1,9 +1,9 @@
 // Matrix products for steps with few tokens (decode) on the fifth-generation tensor cores, built to stream the
 // weights at memory speed:
 //
-//   out[M, N] = A[M, K] . W[N, K]^T,   M <= 16,   bfloat16 operands, float32 accumulation in tensor memory
+//   out[M, N] = A[M, K] . W[N, K]^T,   M <= 64,   bfloat16 operands, float32 accumulation in tensor memory
 //
-// The WEIGHT rows are the 128-row side of tcgen05.mma and the tokens its 16-column side, so the instruction's
+// The WEIGHT rows are the 128-row side of tcgen05.mma and the tokens its 16-, 32- or 64-column side, so the instruction's
 // shape wastes nothing of the weight traffic.  A block owns 128 output features and one slice of K:
 //   warp 0   one lane issues TMA loads (128 x 64 weight box, 16 x 64 token box, 128-byte swizzle) into a
 //            ten-stage ring: 160 KiB of weights in flight per SM, issued by a handful of instructions;
@@ -23,14 +23,17 @@ using namespace tkb5;
 namespace {
 
 constexpr int BMW = 128;   // weight rows (features) per block
-constexpr int NTOK = 16;   // token columns of the MMA
 constexpr int THREADS = 192;
-constexpr int W_BYTES = BMW * BK * 2;          // 16 KiB
-constexpr int T_BYTES = NTOK * BK * 2;         // 2 KiB
-constexpr int STAGE_BYTES = W_BYTES + T_BYTES;  // 18 KiB: both parts start on 1,024-byte boundaries
-constexpr int STAGES = 10;
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024;
-constexpr int TMEM_COLS = 32;
+constexpr int W_BYTES = BMW * BK * 2;  // 16 KiB
+
+// NTOK: token columns of the MMA (16, 32 or 64)
+template <int NTOK> struct DCfg {
+  static constexpr int T_BYTES = NTOK * BK * 2;           // 2, 4 or 8 KiB
+  static constexpr int STAGE_BYTES = W_BYTES + T_BYTES;   // both parts start on 1,024-byte boundaries
+  static constexpr int STAGES = NTOK == 16 ? 10 : (NTOK == 32 ? 9 : 8);
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024;
+  static constexpr int TMEM_COLS = NTOK < 32 ? 32 : NTOK;
+};
 
 __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
   asm volatile(
@@ -41,12 +44,13 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
-template <bool GATED>
+template <int NTOK, bool GATED>
 __global__ void __launch_bounds__(THREADS, 1)
 linear_tcgen05_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a,
                              void* __restrict__ out_, int M, int N, int K, int kblocks_per_slice,
                              int* __restrict__ status) {
   extern __shared__ unsigned char smem_raw[];
+  constexpr int STAGES = DCfg<NTOK>::STAGES, STAGE_BYTES = DCfg<NTOK>::STAGE_BYTES, TMEM_COLS = DCfg<NTOK>::TMEM_COLS;
   __shared__ __align__(8) uint64_t full_bar[STAGES], empty_bar[STAGES], acc_bar;
   __shared__ uint32_t tmem_base_slot;
   __shared__ int failed;
@@ -124,27 +128,31 @@ linear_tcgen05_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __
     tcgen05_fence_after();
     if (!ok) failed = 1;
     if (ok) {
-      uint32_t r[16];
-      tmem_ld16(tmem_acc + ((uint32_t)(q * 32) << 16), r);
       const int f = n0 + q * 32 + lane;
-      if (!GATED) {
-        float* o = reinterpret_cast<float*>(out_) + (size_t)slice * M * N;
-        if (f < N) {
+#pragma unroll 1
+      for (int c0 = 0; c0 < NTOK; c0 += 16) {
+        uint32_t r[16];
+        tmem_ld16(tmem_acc + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, r);
+        if (!GATED) {
+          float* o = reinterpret_cast<float*>(out_) + (size_t)slice * M * N;
+          if (f < N) {
 #pragma unroll
-          for (int t = 0; t < NTOK; t++)
-            if (t < M) o[(size_t)t * N + f] = __uint_as_float(r[t]);
-        }
-      } else {
-        // weight rows come in groups of 16: 8 gate rows, then the 8 up rows of the same features
-        bf16* o = reinterpret_cast<bf16*>(out_);
-        const int I = N >> 1;
-        const bool is_gate = (lane & 8) == 0;
-        const int g = ((n0 + q * 32 + (lane & 16)) >> 1) + (lane & 7);
+            for (int t = 0; t < 16; t++)
+              if (c0 + t < M) o[(size_t)(c0 + t) * N + f] = __uint_as_float(r[t]);
+          }
+        } else {
+          // weight rows come in groups of 16: 8 gate rows, then the 8 up rows of the same features
+          bf16* o = reinterpret_cast<bf16*>(out_);
+          const int I = N >> 1;
+          const bool is_gate = (lane & 8) == 0;
+          const int g = ((n0 + q * 32 + (lane & 16)) >> 1) + (lane & 7);
 #pragma unroll
-        for (int t = 0; t < NTOK; t++) {
-          const float mine = __uint_as_float(r[t]);
-          const float other = __shfl_xor_sync(0xffffffffu, mine, 8);
-          if (is_gate && t < M && f + 8 < N) o[(size_t)t * I + g] = __float2bfloat16_rn(silu_mul_fast(mine, other));
+          for (int t = 0; t < 16; t++) {
+            const float mine = __uint_as_float(r[t]);
+            const float other = __shfl_xor_sync(0xffffffffu, mine, 8);
+            if (is_gate && c0 + t < M && f + 8 < N)
+              o[(size_t)(c0 + t) * I + g] = __float2bfloat16_rn(silu_mul_fast(mine, other));
+          }
         }
       }
     }
@@ -158,13 +166,14 @@ linear_tcgen05_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __
   if (threadIdx.x == 0 && failed) atomicOr(status, TKB_STATUS_WAIT_TIMEOUT);
 }
 
-template <bool GATED>
+template <int NTOK, bool GATED>
 int launch(const void* A, int lda, const void* W, int ldw, void* out, int M, int N, int K, int slices, int per,
            int* status, cudaStream_t st) {
   static bool attr_done = false;
+  constexpr int SMEM_BYTES = DCfg<NTOK>::SMEM_BYTES;
   if (!attr_done) {
-    cudaError_t e = cudaFuncSetAttribute(linear_tcgen05_decode_kernel<GATED>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         SMEM_BYTES);
+    cudaError_t e = cudaFuncSetAttribute(linear_tcgen05_decode_kernel<NTOK, GATED>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
     if (e != cudaSuccess) return (int)e;
     attr_done = true;
   }
@@ -174,8 +183,8 @@ int launch(const void* A, int lda, const void* W, int ldw, void* out, int M, int
   rc = make_map(&map_a, A, M, K, lda, NTOK);
   if (rc) return rc;
   dim3 grid((N + BMW - 1) / BMW, slices);
-  return launch_pdl(linear_tcgen05_decode_kernel<GATED>, grid, dim3(THREADS), (size_t)SMEM_BYTES, st, map_w, map_a, out, M,
-                    N, K, per, status);
+  return launch_pdl(linear_tcgen05_decode_kernel<NTOK, GATED>, grid, dim3(THREADS), (size_t)SMEM_BYTES, st, map_w, map_a,
+                    out, M, N, K, per, status);
 }
 
 }  // namespace
@@ -194,13 +203,13 @@ TKB_EXPORT int tkb_linear_tcgen05_decode_slices(int N, int K, int max_slices) {
 }
 
 // out: float32 [slices, M, N] (gated == 0) or bfloat16 [M, N/2] = silu(gate) * up (gated != 0, slices == 1,
-// W interleaved in groups of 8 rows, N a multiple of 16).  M <= 16; K and the row strides multiples of 8; base
+// W interleaved in groups of 8 rows, N a multiple of 16).  M <= 64; K and the row strides multiples of 8; base
 // addresses 16-byte aligned.
 TKB_EXPORT int tkb_linear_tcgen05_decode_bf16(const void* A, int lda, const void* W, int ldw, void* out, int M, int N,
                                               int K, int slices, int gated, int* status, void* st_) {
   cudaStream_t st = (cudaStream_t)st_;
   if (M <= 0 || N <= 0) return 0;
-  if (M > NTOK || K <= 0 || (K & 7) || (lda & 7) || (ldw & 7) || (((uintptr_t)A) & 15) || (((uintptr_t)W) & 15) ||
+  if (M > 64 || K <= 0 || (K & 7) || (lda & 7) || (ldw & 7) || (((uintptr_t)A) & 15) || (((uintptr_t)W) & 15) ||
       slices < 1 || slices > 65535)
     return -2;
   if (gated && ((N & 15) || slices != 1)) return -2;
@@ -209,6 +218,11 @@ TKB_EXPORT int tkb_linear_tcgen05_decode_bf16(const void* A, int lda, const void
   const int kblocks = (K + BK - 1) / BK;
   const int per = (kblocks + slices - 1) / slices;
   if ((long long)(slices - 1) * per >= kblocks) return -2;  // an empty slice would leave its partial unwritten
-  return gated ? launch<true>(A, lda, W, ldw, out, M, N, K, slices, per, status, st)
-               : launch<false>(A, lda, W, ldw, out, M, N, K, slices, per, status, st);
+#define TKB_GO(NT) \
+  return gated ? launch<NT, true>(A, lda, W, ldw, out, M, N, K, slices, per, status, st) \
+               : launch<NT, false>(A, lda, W, ldw, out, M, N, K, slices, per, status, st);
+  if (M <= 16) { TKB_GO(16) }
+  if (M <= 32) { TKB_GO(32) }
+  TKB_GO(64)
+#undef TKB_GO
 }

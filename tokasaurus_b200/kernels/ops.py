@@ -530,16 +530,16 @@ def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, status: torch.Tensor, gated: 
     return out
 
 
-TC_DECODE_M_MAX = 16
+TC_DECODE_M_MAX = 64
 
 
 def linear_tc_decode(a: torch.Tensor, w: torch.Tensor, status: torch.Tensor, max_slices: int = 16,
                      gated: bool = False) -> torch.Tensor:
-    """a[M, K] @ w[N, K]^T for M <= 16 on the tcgen05 tensor cores with the weights on the 128-row side
+    """a[M, K] @ w[N, K]^T for M <= 64 on the tcgen05 tensor cores with the weights on the 128-row side
     (TMA-fed ten-stage ring).  Returns float32 slices [slices, M, N] of a K-split product, or with ``gated``
     (``w`` from ``interleave_gate_up``) silu(gate)*up as bfloat16 [M, N/2]."""
     _need_cuda(a, w, status)
-    _need(can_use_tcgen05(a, w) and 0 < a.shape[0] <= TC_DECODE_M_MAX, "linear_tc_decode: bfloat16, M <= 16, K % 8 == 0")
+    _need(can_use_tcgen05(a, w) and 0 < a.shape[0] <= TC_DECODE_M_MAX, "linear_tc_decode: bfloat16, M <= 64, K % 8 == 0")
     M, K = a.shape
     N = w.shape[0]
     _need(w.shape[1] == K and (not gated or N % 16 == 0), "linear_tc_decode: shapes")
@@ -553,6 +553,35 @@ def linear_tc_decode(a: torch.Tensor, w: torch.Tensor, status: torch.Tensor, max
         _ptr(a), c_int(a.stride(0)), _ptr(w), c_int(w.stride(0)), _ptr(out), c_int(M), c_int(N), c_int(K),
         c_int(slices), c_int(1 if gated else 0), _ptr(status), _stream()), "linear_tc_decode")
     return out
+
+
+FEW_ROWS_MAX = 64
+
+
+def can_use_few_rows(a: torch.Tensor, w: torch.Tensor) -> bool:
+    """Steps with at most 64 rows (decode) use K-split products whose float32 slices the consumer adds."""
+    if a.shape[0] <= SMALL_M_MAX:
+        return can_use_smallm(a, w)
+    return a.shape[0] <= FEW_ROWS_MAX and can_use_tcgen05(a, w)
+
+
+def linear_few_rows(a: torch.Tensor, w: torch.Tensor, status: torch.Tensor | None) -> torch.Tensor:
+    """Float32 slices [slices, M, N] of a[M, K] @ w[N, K]^T: the mma.sync kernel up to 16 rows (measured
+    faster there), the tcgen05 kernel from 17 to 64."""
+    if a.shape[0] <= SMALL_M_MAX:
+        return linear_smallm(a, w)
+    if status is None:
+        status = torch.zeros(1, dtype=torch.int32, device=a.device)
+    return linear_tc_decode(a, w, status)
+
+
+def linear_few_rows_gated(a: torch.Tensor, w_interleaved: torch.Tensor, status: torch.Tensor | None) -> torch.Tensor:
+    """silu(gate) * up [M, I] for at most 64 rows: mma.sync kernel up to 8 rows, tcgen05 kernel above."""
+    if a.shape[0] <= GATED_M_MAX:
+        return linear_smallm_gated(a, w_interleaved)
+    if status is None:
+        status = torch.zeros(1, dtype=torch.int32, device=a.device)
+    return linear_tc_decode(a, w_interleaved, status, gated=True)
 
 
 def linear(a: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None = None) -> torch.Tensor:

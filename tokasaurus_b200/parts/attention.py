@@ -211,11 +211,12 @@ class PagedAttention(Mixer):
                     return None
                 return ops.linear_decode(attn, self.w_o, "bf16")
             h = h.materialize()
-        small = (ops.can_use_smallm(h, self.w_qkv) and (nh * hd) % 8 == 0
+        small = (ops.can_use_few_rows(h, self.w_qkv) and (nh * hd) % 8 == 0
                  and (self.w_qkv.shape[0] + max(rot, 2)) * 4 <= 48 * 1024)
+        few = lambda a, w: ops.linear_few_rows(a, w, ctx.status)  # noqa: E731
         if small:
             # few rows: K-split products whose float32 slices the next kernel adds
-            parts = ops.linear_smallm(h, self.w_qkv)
+            parts = few(h, self.w_qkv)
             plan = ctx.plans.get(self.plan_key())
             counts = ctx.host_plans[self.plan_key()]["counts"] if plan is not None else None
             if plan is not None and out_rows is None and int(counts[2]) == 0 and int(counts[1]) > 0 and rot % 4 == 0:
@@ -229,12 +230,12 @@ class PagedAttention(Mixer):
                                          caps["dec"] if caps else int(counts[1]), attn, nh, nkv, hd, cache.page_size,
                                          self.scale, self.window, self.inv_freq, rot, cache.writable,
                                          ctx.status, item_entry=plan["item_entry"] if int(counts[0]) == int(counts[1]) else None)
-                return ops.linear_smallm(attn, self.w_o)
+                return few(attn, self.w_o)
             qkv = torch.empty((T, nh * hd), dtype=h.dtype, device=h.device)  # q only; k and v go straight to the cache
             ops.rope_kv_write_partials(parts, qkv, ctx.positions, ctx.token_seq, tables.indptr, tables.page_ids,
                                        self.inv_freq, cache.k, cache.v, nh, nkv, hd, rot, cache.page_size,
                                        cache.writable, ctx.status)
-            project = ops.linear_smallm
+            project = few
         else:
             qkv = ops.linear(h, self.w_qkv)
             ops.rope_kv_write(qkv, ctx.positions, ctx.token_seq, tables.indptr, tables.page_ids, self.inv_freq,

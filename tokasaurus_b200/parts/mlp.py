@@ -53,17 +53,19 @@ class GatedMLP(FeedForward):
                     return None
                 return ops.linear_decode(act, self.w_down, "bf16")
             h = h.materialize()
-        if self.interleave and ops.can_use_smallm(h, self.w_gate_up, ops.GATED_M_MAX):
-            act = ops.linear_smallm_gated(h, self.w_gate_up)
-            return ops.linear_smallm(act, self.w_down)
+        status = ctx.status if ctx is not None else None
+        if self.interleave and ops.can_use_few_rows(h, self.w_gate_up) and self.w_gate_up.shape[0] % 16 == 0:
+            act = ops.linear_few_rows_gated(h, self.w_gate_up, status)
+            return ops.linear_few_rows(act, self.w_down, status)
         if self.interleave and h.shape[0] >= ops.TCGEN05_M_MIN and ops.can_use_tcgen05(h, self.w_gate_up):
             # many rows: the tcgen05 product with the SiLU gate in its epilogue (no activation pass over memory)
-            status = ctx.status if ctx is not None else torch.zeros(1, dtype=torch.int32, device=h.device)
-            act = ops.gemm_tcgen05(h, self.w_gate_up, status, gated=True)
+            act = ops.gemm_tcgen05(h, self.w_gate_up,
+                                   status if status is not None else torch.zeros(1, dtype=torch.int32, device=h.device),
+                                   gated=True)
         else:
             gu = ops.linear(h, self.w_gate_up)
             act = torch.empty((h.shape[0], self.inner), dtype=h.dtype, device=h.device)
             ops.silu_mul(gu, act, self.interleave)
-        if ops.can_use_smallm(act, self.w_down):
-            return ops.linear_smallm(act, self.w_down)
+        if ops.can_use_few_rows(act, self.w_down):
+            return ops.linear_few_rows(act, self.w_down, status)
         return ops.linear(act, self.w_down)
