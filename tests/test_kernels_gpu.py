@@ -348,7 +348,8 @@ def test_refusals(ops):
 
 # ------------------------------------------------------------------------------------------------
 # bfloat16 tensor-core attention (split-key kernel for single tokens, tiled kernel for portions)
-def run_mma_attention(ops, lens_q, lens_kv, nh, nkv, hd, ps, window, seed, n_pages=None, fill=1e3, merged=True):
+def run_mma_attention(ops, lens_q, lens_kv, nh, nkv, hd, ps, window, seed, n_pages=None, fill=1e3, merged=True,
+                      tc=False):
     """A batch of requests with lens_q new tokens each at the end of lens_kv keys; returns (got, want)."""
     from types import SimpleNamespace
     from tokasaurus_b200.parts.attention import plan_attention
@@ -363,7 +364,7 @@ def run_mma_attention(ops, lens_q, lens_kv, nh, nkv, hd, ps, window, seed, n_pag
         tseq += [s] * n
     T = len(pos)
     host = SimpleNamespace(seq_q_len=np.asarray(lens_q, dtype=np.int32), seq_kv_len=np.asarray(lens_kv, dtype=np.int32))
-    plan = plan_attention(host, window)
+    plan = plan_attention(host, window, query_tile=128 if tc else 64)
     g = torch.Generator().manual_seed(seed + 1)
     qkv = torch.randn(T, (nh + 2 * nkv) * hd, generator=g).to(dtype).to(DEV)
     out = torch.full((T, nh * hd), float("nan"), dtype=dtype, device=DEV)
@@ -374,7 +375,12 @@ def run_mma_attention(ops, lens_q, lens_kv, nh, nkv, hd, ps, window, seed, n_pag
         ops.attn_decode_mma(qkv, kc, vc, i32(q_start), i32(lens_kv), indptr, pages, i32(plan["items"]), c[0:1], n_items,
                             i32(plan["dec_seqs"]), i32(plan["dec_item_start"]), c[1:2], n_dec, out, nh, nkv, hd, ps, scale,
                             window, item_entry=i32(plan["item_entry"]) if merged else None)
-    if n_tiles:
+    if n_tiles and tc:
+        status = torch.zeros(1, dtype=torch.int32, device=DEV)
+        ops.attn_prefill_tc(qkv, out, kc, vc, i32(q_start), i32(lens_q), i32(lens_kv), indptr, pages, i32(plan["tiles"]),
+                            c[2:3], n_tiles, nh, nkv, hd, ps, scale, window, status)
+        assert int(status.item()) == 0
+    elif n_tiles:
         ops.attn_prefill_mma(qkv, out, kc, vc, i32(q_start), i32(lens_q), i32(lens_kv), indptr, pages, i32(plan["tiles"]),
                              c[2:3], n_tiles, nh, nkv, hd, ps, scale, window)
     want = torch.zeros(T, nh, hd, dtype=torch.float64)
@@ -403,18 +409,40 @@ def test_mma_attention_mixed_batch(ops, hd, nh, nkv, ps, window):
     assert torch.equal(got, got3)
 
 
+@pytest.mark.parametrize("nh,nkv,ps,window", [(32, 8, 16, None), (3, 1, 8, None), (5, 5, 5, None), (4, 2, 64, 17),
+                                              (6, 3, 4, 300), (8, 2, 16, 128), (4, 2, 256, None), (2, 1, 128, 200)])
+def test_tc_attention_mixed_batch(ops, nh, nkv, ps, window):
+    """The tcgen05 kernel for portions (head size 64): portions that start in the middle of a request, span
+    several 128-query tiles and several 128-key tiles, end on odd lengths, or are two tokens long."""
+    lens_q = [1, 70, 2, 130, 1, 64, 128, 300, 129]
+    lens_kv = [777, 70, 259, 400, 256, 64, 128, 1000, 129]
+    got, want = run_mma_attention(ops, lens_q, lens_kv, nh, nkv, 64, ps, window, seed=nh + ps, tc=True)
+    assert not torch.isnan(got).any()
+    torch.testing.assert_close(got, want, rtol=1.6e-2, atol=1.2e-2)
+    got2, _ = run_mma_attention(ops, lens_q, lens_kv, nh, nkv, 64, ps, window, seed=nh + ps, tc=True)
+    assert torch.equal(got, got2)
+
+
+def test_tc_attention_never_reads_what_a_page_held_before(ops):
+    got, want = run_mma_attention(ops, [1, 37, 150], [100, 37, 333], 8, 2, 64, 16, None, seed=3, fill=float("nan"), tc=True)
+    assert not torch.isnan(got).any()
+    torch.testing.assert_close(got, want, rtol=1.6e-2, atol=1.2e-2)
+
+
 def test_mma_attention_finds_one_far_key(ops):
     """One key among 1,500 stands out for one query head of a single-token request; and the same
     for the last query of a long portion.  The output must be that key's value."""
     hd, nh, nkv, ps, L = 64, 8, 2, 16, 1500
     for target in (0, 255, 256, 257, 1023, 1499):
-        for lens_q in ([1], [200]):
+        for lens_q in ([1], [200], [-200]):
+            tc, lens_q = lens_q[0] < 0, [abs(lens_q[0])]
             kc, vc, indptr, pages, K, V = make_paged(torch.bfloat16, 1, [L], nkv, hd, ps, 100, seed=target)
             from types import SimpleNamespace
             from tokasaurus_b200.parts.attention import plan_attention
             n = lens_q[0]
             plan = plan_attention(SimpleNamespace(seq_q_len=np.asarray(lens_q, dtype=np.int32),
-                                                  seq_kv_len=np.asarray([L], dtype=np.int32)), None)
+                                                  seq_kv_len=np.asarray([L], dtype=np.int32)), None,
+                                  query_tile=128 if tc else 64)
             qkv = torch.zeros(n, (nh + 2 * nkv) * hd, dtype=torch.bfloat16)
             direction = K[0][target, 1].float()
             qkv[n - 1, 6 * hd:7 * hd] = (direction / direction.norm() * 60).to(torch.bfloat16)  # head 6 reads kv head 1
@@ -424,6 +452,10 @@ def test_mma_attention_finds_one_far_key(ops):
                 ops.attn_decode_mma(qkv.to(DEV), kc, vc, i32([0]), i32([L]), indptr, pages, i32(plan["items"]), c[0:1],
                                     int(plan["counts"][0]), i32(plan["dec_seqs"]), i32(plan["dec_item_start"]), c[1:2], 1,
                                     out, nh, nkv, hd, ps, 1.0, None)
+            elif tc:
+                ops.attn_prefill_tc(qkv.to(DEV), out, kc, vc, i32([0]), i32(lens_q), i32([L]), indptr, pages,
+                                    i32(plan["tiles"]), c[2:3], int(plan["counts"][2]), nh, nkv, hd, ps, 1.0, None,
+                                    torch.zeros(1, dtype=torch.int32, device=DEV))
             else:
                 ops.attn_prefill_mma(qkv.to(DEV), out, kc, vc, i32([0]), i32(lens_q), i32([L]), indptr, pages,
                                      i32(plan["tiles"]), c[2:3], int(plan["counts"][2]), nh, nkv, hd, ps, 1.0, None)

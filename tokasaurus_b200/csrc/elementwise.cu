@@ -154,7 +154,8 @@ static int add_rmsnorm_launch(float* x, const void* delta, const float* partials
                               long long partial_stride, const float* w, void* out, float eps, int rows, int H,
                               cudaStream_t st) {
   if (rows <= 0) return 0;
-  int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
+  // few rows: many threads a row, they hide the latency; many rows: several rows an SM in flight do
+  int threads = H >= 8192 || (H >= 2048 && rows < 592) ? 512 : (H >= 512 ? 256 : 128);
   return launch_pdl(add_rmsnorm_kernel<T>, dim3(rows), dim3(threads), 0, st, x, (const T*)delta, partials, n_partials,
                     partial_stride, w, (T*)out, eps, H);
 }

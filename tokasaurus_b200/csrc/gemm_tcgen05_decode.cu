@@ -63,6 +63,7 @@ linear_tcgen05_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __
   const int nkb = min(kblocks_per_slice, kb_total - kb_begin);
 
   trigger_dependents();
+  const int first = nkb < STAGES ? nkb : STAGES;
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; s++) {
       mbar_init(&full_bar[s], 1);
@@ -71,8 +72,17 @@ linear_tcgen05_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __
     mbar_init(&acc_bar, 1);
     failed = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    // Weights first: no kernel writes them, so their boxes may be on their way while the kernel before this
+    // one still runs.
+    for (int kb = 0; kb < first; kb++) {
+      mbar_expect_tx(&full_bar[kb], STAGE_BYTES);
+      tma_load_2d(ring + kb * STAGE_BYTES, &map_w, &full_bar[kb], (kb_begin + kb) * BK, n0);
+    }
   }
   if (warp == 1) {
+    // Tensor memory is taken only after the kernel ahead has finished: a block of that kernel that still
+    // waits for columns on this SM could otherwise wait for this block, which waits for that kernel.
+    grid_dependency_wait();
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)),
                  "r"((uint32_t)TMEM_COLS) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
@@ -84,13 +94,7 @@ linear_tcgen05_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __
 
   if (warp == 0) {
     if (lane == 0) {
-      // ---------------- TMA producer.  Weights first: no kernel writes them, so their boxes may be on their
-      // way while the kernel before this one still runs; the tokens only after it has finished.
-      const int first = nkb < STAGES ? nkb : STAGES;
-      for (int kb = 0; kb < first; kb++) {
-        mbar_expect_tx(&full_bar[kb], STAGE_BYTES);
-        tma_load_2d(ring + kb * STAGE_BYTES, &map_w, &full_bar[kb], (kb_begin + kb) * BK, n0);
-      }
+      // ---------------- TMA producer: the tokens only after the kernel ahead has finished
       grid_dependency_wait();
       for (int kb = 0; kb < first; kb++)
         tma_load_2d(ring + kb * STAGE_BYTES + W_BYTES, &map_a, &full_bar[kb], (kb_begin + kb) * BK, 0);

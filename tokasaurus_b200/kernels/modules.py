@@ -8,7 +8,10 @@ def common_modules() -> list[tuple[str, dict | None]]:
 
 
 def head_dim_modules(head_dim: int) -> list[tuple[str, dict | None]]:
-    return [("attention_simt.cu", {"TKB_HD": head_dim}), ("attention_mma.cu", {"TKB_HD": head_dim})]
+    mods = [("attention_simt.cu", {"TKB_HD": head_dim}), ("attention_mma.cu", {"TKB_HD": head_dim})]
+    if head_dim == 64:
+        mods.append(("attention_tc.cu", None))  # tcgen05 kernel for prompt portions
+    return mods
 
 
 def optional_modules(head_dim: int) -> list[tuple[str, dict | None]]:

@@ -470,6 +470,40 @@ def attn_prefill_mma(qkv: torch.Tensor, out: torch.Tensor, kcache: torch.Tensor,
         _stream()), "attn_prefill_mma")
 
 
+ATTN_PREFILL_TC = True  # portions of prompts on the tcgen05 kernel where it takes the head size
+
+
+def can_use_attn_prefill_tc(head_dim: int) -> bool:
+    return ATTN_PREFILL_TC and head_dim == 64
+
+
+def attn_prefill_tc(qkv: torch.Tensor, out: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor,
+                    seq_q_start: torch.Tensor, seq_q_len: torch.Tensor, seq_kv_len: torch.Tensor,
+                    page_indptr: torch.Tensor, page_ids: torch.Tensor, tiles: torch.Tensor, n_tiles: torch.Tensor,
+                    tiles_cap: int, n_heads: int, n_kv_heads: int, head_dim: int, page_size: int, scale: float,
+                    window: int | None, status: torch.Tensor) -> None:
+    """bfloat16 causal attention for prompt portions on tcgen05 tensor cores (head size 64): ``tiles`` are
+    (request row, first query of a 128-query tile within the portion) pairs; results go to ``out``
+    [T, n_heads*head_dim] at the token rows.  ``status`` collects a wait that ran out."""
+    _need_cuda(qkv, out, kcache, vcache, seq_q_start, seq_q_len, seq_kv_len, page_indptr, page_ids, tiles, n_tiles,
+               status)
+    _need(head_dim == 64, f"attn_prefill_tc: head size 64 only, got {head_dim}")
+    _need(qkv.dtype == torch.bfloat16 and kcache.dtype == torch.bfloat16 and out.dtype == torch.bfloat16,
+          "attn_prefill_tc: bfloat16 only")
+    _need(tuple(kcache.shape[1:]) == (n_kv_heads, page_size, head_dim) and kcache.is_contiguous()
+          and vcache.shape == kcache.shape and vcache.is_contiguous(), "attn_prefill_tc: cache layout")
+    _need(out.is_contiguous() and out.shape[1] == n_heads * head_dim, "attn_prefill_tc: out")
+    _need(qkv.stride(1) == 1 and qkv.stride(0) % 8 == 0 and qkv.data_ptr() % 16 == 0 and out.data_ptr() % 16 == 0,
+          "attn_prefill_tc: rows of q must start on 16-byte boundaries")
+    _need(tiles.numel() >= 2 * tiles_cap, "attn_prefill_tc: plan arrays")
+    lib = _libs.get("attention_tc.cu")
+    _check(_fn(lib, "tkb_attn_prefill_tc_bf16")(
+        _ptr(qkv), c_int(qkv.stride(0)), _ptr(out), c_int(out.shape[1]), _ptr(kcache), _ptr(vcache),
+        c_int(kcache.shape[0]), _ptr(seq_q_start), _ptr(seq_q_len), _ptr(seq_kv_len), _ptr(page_indptr), _ptr(page_ids),
+        _ptr(tiles), _ptr(n_tiles), c_int(tiles_cap), c_int(n_heads), c_int(n_kv_heads), c_int(page_size), c_float(scale),
+        c_int(window or 0), _ptr(status), _stream()), "attn_prefill_tc")
+
+
 def sample(logits: torch.Tensor, temperature: torch.Tensor | None, stream_key: torch.Tensor | None,
            sample_pos: torch.Tensor | None, row_slot: torch.Tensor | None, out_ids: torch.Tensor,
            out_logprob: torch.Tensor | None, last_token: torch.Tensor | None) -> None:

@@ -27,7 +27,8 @@ from tokasaurus_b200.parts.base import LazyNorm, Mixer, PagedCacheNeed, Position
 
 SPLIT_KEYS = 512  # keys per work item of the split-key kernel when a step has more work than one wave of blocks
 MIN_SPLIT_KEYS = 128
-QUERY_TILE = 64  # queries per block of the tiled kernel
+QUERY_TILE = 64  # queries per block of the tiled mma.sync kernel
+QUERY_TILE_TC = 128  # queries per block of the tcgen05 kernel
 DECODE_BLOCK_SLOTS = 148 * 3  # blocks of the split-key kernel that a B200 holds at once (head size 64)
 
 
@@ -49,11 +50,11 @@ def split_keys_evenly(span: np.ndarray, blocks_per_item: int) -> tuple[np.ndarra
     return n, size
 
 
-def plan_attention(host, window: int | None, capacity: dict | None = None, blocks_per_item: int = 8
-                   ) -> dict[str, np.ndarray]:
+def plan_attention(host, window: int | None, capacity: dict | None = None, blocks_per_item: int = 8,
+                   query_tile: int = QUERY_TILE) -> dict[str, np.ndarray]:
     """Work items for one step: (request row, first key, keys) triples for requests with one token,
-    (request row, first query) pairs for 64-query tiles of longer portions.  ``blocks_per_item``: blocks the
-    split-key kernel launches per item (kv heads x head tiles)."""
+    (request row, first query) pairs for ``query_tile``-query tiles of longer portions.  ``blocks_per_item``:
+    blocks the split-key kernel launches per item (kv heads x head tiles)."""
     q_len = np.asarray(host.seq_q_len, dtype=np.int64)
     kv_len = np.asarray(host.seq_kv_len, dtype=np.int64)
     dec_seqs = np.nonzero(q_len == 1)[0]
@@ -69,11 +70,11 @@ def plan_attention(host, window: int | None, capacity: dict | None = None, block
     items = np.stack([item_seq, item_first, item_size], axis=1).reshape(-1)
     item_entry = np.repeat(np.arange(dec_seqs.shape[0]), n_splits)  # index of each item's request in dec_seqs
     pre_seqs = np.nonzero(q_len > 1)[0]
-    n_tiles_seq = -(-q_len[pre_seqs] // QUERY_TILE)
+    n_tiles_seq = -(-q_len[pre_seqs] // query_tile)
     tile_start = np.concatenate([[0], np.cumsum(n_tiles_seq)])
     n_tiles = int(tile_start[-1])
     tile_seq = np.repeat(pre_seqs, n_tiles_seq)
-    tile_q0 = (np.arange(n_tiles) - np.repeat(tile_start[:-1], n_tiles_seq)) * QUERY_TILE
+    tile_q0 = (np.arange(n_tiles) - np.repeat(tile_start[:-1], n_tiles_seq)) * query_tile
     # tiles that see the most keys first: the long ones must not be left for the end of the launch
     reach = kv_len[tile_seq] - q_len[tile_seq] + tile_q0
     order = np.argsort(-reach, kind="stable")
@@ -160,13 +161,18 @@ class PagedAttention(Mixer):
         self.dtype = rt.dtype
 
     def plan_key(self):
-        return ("paged_attention", self.window, self._blocks_per_item()) if self.dtype == torch.bfloat16 else None
+        if self.dtype != torch.bfloat16:
+            return None
+        return ("paged_attention", self.window, self._blocks_per_item(), self._query_tile())
+
+    def _query_tile(self) -> int:
+        return QUERY_TILE_TC if ops.can_use_attn_prefill_tc(self.head_dim) else QUERY_TILE
 
     def _blocks_per_item(self) -> int:
         return self.n_kv_heads * ((self.n_heads // self.n_kv_heads + 15) // 16)
 
     def plan(self, host, capacity=None):
-        return plan_attention(host, self.window, capacity, self._blocks_per_item())
+        return plan_attention(host, self.window, capacity, self._blocks_per_item(), self._query_tile())
 
     def pad_plan(self, plan: dict, capacity: dict) -> dict:
         """The same plan with its arrays at the fixed sizes of a CUDA graph."""
@@ -274,7 +280,11 @@ class PagedAttention(Mixer):
                                 plan["items"], c[0:1], items_cap, plan["dec_seqs"], plan["dec_item_start"], c[1:2],
                                 dec_cap, attn, nh, nkv, hd, cache.page_size, self.scale, self.window,
                                 item_entry=plan["item_entry"] if int(counts[0]) == int(counts[1]) else None)
-        if tiles_cap:
+        if tiles_cap and self._query_tile() == QUERY_TILE_TC:
+            ops.attn_prefill_tc(qkv, attn, cache.k, cache.v, ctx.seq_q_start, ctx.seq_q_len, ctx.seq_kv_len,
+                                tables.indptr, tables.page_ids, plan["tiles"], c[2:3], tiles_cap, nh, nkv, hd,
+                                cache.page_size, self.scale, self.window, ctx.status)
+        elif tiles_cap:
             ops.attn_prefill_mma(qkv, attn, cache.k, cache.v, ctx.seq_q_start, ctx.seq_q_len, ctx.seq_kv_len,
                                  tables.indptr, tables.page_ids, plan["tiles"], c[2:3], tiles_cap, nh, nkv, hd,
                                  cache.page_size, self.scale, self.window)
