@@ -185,8 +185,9 @@ def test_cuda_graph_decode_equals_eager(tiny_model_dirs, dtype):
 
 
 def test_cuda_graph_decode_with_requests_ending_at_different_times(tiny_model_dirs):
-    """Requests that end by length at different steps and on stop tokens, and late arrivals: the engine's
-    guess about the next step (made while the GPU is busy) is wrong again and again and must be dropped."""
+    """Requests that end by length at different steps and on stop tokens, and late arrivals: the engine launches
+    the next step before it has read the current one, on a guess that is wrong again and again; the rows of
+    requests that had ended after all must be dropped, with and without that run-ahead."""
     from tokasaurus_b200 import SamplingParams
 
     d = tiny_model_dirs[0]
@@ -197,8 +198,8 @@ def test_cuda_graph_decode_with_requests_ending_at_different_times(tiny_model_di
     stop_at = full[2][9]  # request 2 stops when it first produces this token
     want = [list(f) for f in full]
     want[2] = full[2][: full[2].index(stop_at) + 1]
-    for graphs in (False, True):
-        eng = make_engine(d, use_cudagraphs=graphs, cudagraph_step=4, cudagraph_max_size=8)
+    for graphs, ahead in ((False, True), (True, False), (True, True)):
+        eng = make_engine(d, use_cudagraphs=graphs, cudagraph_step=4, cudagraph_max_size=8, run_ahead=ahead)
         ids = []
         for i, (p, m) in enumerate(zip(prompts[:4], limits[:4])):
             ids.append(eng.add_request(p, SamplingParams(), max_num_tokens=m, ignore_eos=True,
@@ -210,6 +211,29 @@ def test_cuda_graph_decode_with_requests_ending_at_different_times(tiny_model_di
             ids.append(eng.add_request(p, SamplingParams(), max_num_tokens=m, ignore_eos=True))
         done += eng.run_until_done()
         by_id = {o.id: o for o in done}
-        assert [by_id[i].completion_ids for i in ids] == want, f"graphs={graphs}"
+        assert [by_id[i].completion_ids for i in ids] == want, f"graphs={graphs} run_ahead={ahead}"
         assert by_id[ids[2]].finish_reason == "stop"
-        assert not eng.runner.cache.requests
+        assert not eng.runner.cache.requests and not eng.has_work()
+
+
+def test_run_ahead_with_stop_tokens_under_sampling(tiny_model_dirs):
+    """Several requests with temperature sampling that stop on tokens at different steps: the same outputs with
+    and without the run-ahead, and every page given back."""
+    from tokasaurus_b200 import SamplingParams
+
+    d = tiny_model_dirs[1]
+    prompts = [cuttings.random_tokens(n, 509, 3 * n + 1) for n in (9, 31, 5, 18, 2)]
+    sp = [SamplingParams(temperature=t, seed=11 + i) for i, t in enumerate((0.9, 0.0, 1.1, 0.7, 0.0))]
+    ref = make_engine(d, dtype="bfloat16", page_size=8, run_ahead=False).generate(prompts, sp, max_num_tokens=30, ignore_eos=True)
+    stops = [[o.completion_ids[4 + 3 * i]] for i, o in enumerate(ref)]
+    outs = {}
+    for ahead in (False, True):
+        eng = make_engine(d, dtype="bfloat16", page_size=8, run_ahead=ahead)
+        ids = [eng.add_request(p, s, max_num_tokens=30, ignore_eos=True, stop_token_ids=st)
+               for p, s, st in zip(prompts, sp, stops)]
+        by_id = {o.id: o for o in eng.run_until_done()}
+        outs[ahead] = [by_id[i] for i in ids]
+        assert not eng.runner.cache.requests and not eng.has_work()
+    for a, b, r, st in zip(outs[False], outs[True], ref, stops):
+        assert a.completion_ids == b.completion_ids and a.finish_reason == b.finish_reason == "stop"
+        assert a.completion_ids == r.completion_ids[: r.completion_ids.index(st[0]) + 1]

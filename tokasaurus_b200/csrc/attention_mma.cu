@@ -78,26 +78,38 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 }
 
 // Copy keys [key_base, key_base + KT) of one kv head into a stage; keys outside [key_lo, key_hi) become zero.
+template <int NTHREADS>
 __device__ __forceinline__ void load_kv_tile(unsigned char* stage, const bf16* __restrict__ kcache,
                                              const bf16* __restrict__ vcache, const int* __restrict__ table, int kvh,
-                                             int nkv, int ps, int key_base, int key_lo, int key_hi, int tid,
-                                             int nthreads) {
+                                             int nkv, int ps, int key_base, int key_lo, int key_hi, int tid) {
   const uint32_t sk = smem_u32(stage), sv = sk + TILE_B;
   const int ps_shift = (ps & (ps - 1)) == 0 ? 31 - __clz(ps) : -1;  // page sizes that are powers of two: shifts
-  for (int idx = tid; idx < KT * CPR; idx += nthreads) {
+  constexpr int ITERS = (KT * CPR + NTHREADS - 1) / NTHREADS;
+  size_t off[ITERS];
+  bool valid[ITERS];
+  // the page lookups of the whole tile first, so that they are in flight together
+#pragma unroll
+  for (int i = 0; i < ITERS; i++) {
+    const int idx = tid + i * NTHREADS;
     const int r = idx / CPR, c = idx - r * CPR;
     const int key = key_base + r;
-    const bool valid = key >= key_lo && key < key_hi;
-    size_t off = 0;
-    if (valid) {
+    valid[i] = idx < KT * CPR && key >= key_lo && key < key_hi;
+    off[i] = 0;
+    if (valid[i]) {
       const int pi = ps_shift >= 0 ? key >> ps_shift : key / ps;
       const int slot = ps_shift >= 0 ? key & (ps - 1) : key - pi * ps;
-      const int page = table[pi];
-      off = (((size_t)page * nkv + kvh) * ps + slot) * HD + c * 8;
+      off[i] = (((size_t)table[pi] * nkv + kvh) * ps + slot) * HD + c * 8;
     }
-    const uint32_t d = r * ROWB + c * 16;
-    cp_async16(sk + d, kcache + off, valid);
-    cp_async16(sv + d, vcache + off, valid);
+  }
+#pragma unroll
+  for (int i = 0; i < ITERS; i++) {
+    const int idx = tid + i * NTHREADS;
+    if (idx < KT * CPR) {
+      const int r = idx / CPR, c = idx - r * CPR;
+      const uint32_t d = r * ROWB + c * 16;
+      cp_async16(sk + d, kcache + off[i], valid[i]);
+      cp_async16(sv + d, vcache + off[i], valid[i]);
+    }
   }
 }
 
@@ -179,6 +191,47 @@ __device__ __forceinline__ void softmax_16keys(float (&s)[2][4], float (&m)[2], 
 // FUSED: q points at the un-rotated q|k|v rows of the step [tokens, (nh + 2 nkv) * HD]; the kernel rotates
 // q on the fly, and the block that owns the split holding the token's own position rotates this kv
 // head's k, writes it and v into the cache page, and only then reads its tiles.
+// Two neighbouring output elements (d, d + 1) of the merge of splits i0 .. i1-1 of one head.  All loads of up
+// to eight splits are in flight together (one trip to the L2 for the usual case); the sums run in split order,
+// so every caller gets the same bits.
+__device__ __forceinline__ float2 merge_splits(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                               int i0, int i1, int nh, int head, int d) {
+  const float* ml = part_ml + ((size_t)i0 * nh + head) * 2;
+  const float* po = part_o + ((size_t)i0 * nh + head) * HD + d;
+  const size_t ml_step = (size_t)nh * 2, po_step = (size_t)nh * HD;
+  const int n = i1 - i0;
+  float2 mlv[8], ov[8];
+#pragma unroll
+  for (int k = 0; k < 8; k++) {
+    const bool live = k < n;
+    mlv[k] = live ? __ldcg(reinterpret_cast<const float2*>(ml + (size_t)k * ml_step)) : make_float2(NEG_BIG, 0.f);
+    ov[k] = live ? __ldcg(reinterpret_cast<const float2*>(po + (size_t)k * po_step)) : make_float2(0.f, 0.f);
+  }
+  float mm = NEG_BIG;
+#pragma unroll
+  for (int k = 0; k < 8; k++) mm = fmaxf(mm, mlv[k].x);
+  for (int k = 8; k < n; k++) mm = fmaxf(mm, __ldcg(ml + (size_t)k * ml_step));
+  float ax = 0.f, ay = 0.f, ll = 0.f;
+#pragma unroll
+  for (int k = 0; k < 8; k++) {
+    if (k < n) {
+      const float f = exp2f(mlv[k].x - mm);
+      ll += f * mlv[k].y;
+      ax += f * ov[k].x;
+      ay += f * ov[k].y;
+    }
+  }
+  for (int k = 8; k < n; k++) {
+    const float2 e = __ldcg(reinterpret_cast<const float2*>(ml + (size_t)k * ml_step));
+    const float2 o = __ldcg(reinterpret_cast<const float2*>(po + (size_t)k * po_step));
+    const float f = exp2f(e.x - mm);
+    ll += f * e.y;
+    ax += f * o.x;
+    ay += f * o.y;
+  }
+  return make_float2(ax / ll, ay / ll);
+}
+
 template <bool FUSED>
 __global__ void __launch_bounds__(128)
 attn_decode_mma_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ kcache,
@@ -194,7 +247,8 @@ attn_decode_mma_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restric
                        bf16* __restrict__ out, int out_stride) {
   extern __shared__ __align__(128) unsigned char smem[];
   trigger_dependents();
-  grid_dependency_wait();
+  // What the host wrote for this step (work items, lengths, block tables) is there before any kernel of the
+  // step starts, so the block works out its geometry while the kernel ahead (the q|k|v product) still runs.
   const int item = blockIdx.x;
   if (item >= *n_items_ptr) return;
   const int s = items[3 * item];  // work item: request row, first key (counted from the first visible key), keys
@@ -212,14 +266,18 @@ attn_decode_mma_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restric
   const int* table = page_ids + page_indptr[s];
   const int t = seq_q_start[s];
   const bf16* qrow = q + (size_t)t * q_stride + (size_t)(kvh * group + g0) * HD;
-
-  // The first tiles of keys and values go on their way before anything else: older keys do not depend on
-  // this step.  (The token's own key, if this split holds it, is patched into the tile in shared memory.)
   const int n_tiles = (k_end - k_begin + KT - 1) / KT;
+
+  // The first tiles of keys and values go on their way before anything else.  With the rotary encoding fused
+  // the only key of this step is the token's own (position p), which is patched into the last tile in shared
+  // memory; all older keys were written by earlier steps, so tiles that end before p may be read even before
+  // the kernel ahead has finished.  Otherwise (keys of this step come from a kernel ahead) the wait comes first.
+  const bool early = FUSED && (k_end < kv_len || n_tiles > DSTAGES - 1);
+  if (!early) grid_dependency_wait();
 #pragma unroll
   for (int st = 0; st < DSTAGES - 1; st++) {
     if (st < n_tiles)
-      load_kv_tile(smem + st * STAGE_B, kcache, vcache, table, kvh, nkv, ps, k_begin + st * KT, k_begin, k_end, tid, 128);
+      load_kv_tile<128>(smem + st * STAGE_B, kcache, vcache, table, kvh, nkv, ps, k_begin + st * KT, k_begin, k_end, tid);
     cp_async_commit();
   }
   // Q fragments: row r of the tile is query head g0 + r; rows >= gn are zero.
@@ -229,7 +287,7 @@ attn_decode_mma_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restric
   // this split holds position p, and this layer call keeps its own keys (a call that reads another call's cache
   // finds the key at p already there)
   const bool owns_new = FUSED && write_cache && k_end == kv_len;
-  __shared__ float srow[FUSED ? 18 * HD : 2];        // the token's q rows of this head tile, then its k and v row
+  __shared__ __align__(16) float srow[FUSED ? 18 * HD : 4];  // the token's q rows of this head tile, then its k and v row
   if (FUSED) {
     const int half = rot >> 1;
     for (int j = tid; j < half; j += 128) {
@@ -238,26 +296,50 @@ attn_decode_mma_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restric
       cs[j] = c;
       cs[half + j] = sn;
     }
+  }
+  if (early) grid_dependency_wait();
+  if (FUSED) {
+    const int half = rot >> 1;
     // gather q (gn heads), k and v of this kv head as the activation type would hold them
     const int C = (nh + 2 * nkv) * HD;
-    for (int idx = tid; idx < (gn + 2) * HD; idx += 128) {
-      const int r = idx / HD, d = idx - r * HD;
-      const int col = r < gn ? (kvh * group + g0 + r) * HD + d : (r == gn ? (nh + kvh) * HD + d : (nh + nkv + kvh) * HD + d);
-      float v;
-      if (n_parts > 0) {
+    if (n_parts > 0) {
+      // float32 slices of a K-split product: four columns a thread, the loads of up to eight slices in flight
+      // together, added in slice order
+      for (int idx = tid; idx < (gn + 2) * (HD / 4); idx += 128) {
+        const int r = idx / (HD / 4), d = (idx - r * (HD / 4)) * 4;
+        const int col = r < gn ? (kvh * group + g0 + r) * HD + d : (r == gn ? (nh + kvh) * HD + d : (nh + nkv + kvh) * HD + d);
         const float* src = qkv_parts + (size_t)t * C + col;
-        float pv[8];
+        float4 pv[8];
 #pragma unroll
-        for (int pi = 0; pi < 8; pi++) pv[pi] = pi < n_parts ? src[(size_t)pi * part_stride] : 0.f;  // loads in flight together
-        v = 0.f;
+        for (int pi = 0; pi < 8; pi++)
+          pv[pi] = pi < n_parts ? *reinterpret_cast<const float4*>(src + (size_t)pi * part_stride) : make_float4(0.f, 0.f, 0.f, 0.f);
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-        for (int pi = 0; pi < 8; pi++) v += pv[pi];
-        for (int pi = 8; pi < n_parts; pi++) v += src[(size_t)pi * part_stride];
-        v = __bfloat162float(__float2bfloat16_rn(v));
-      } else {
-        v = __bfloat162float(q[(size_t)t * q_stride + col]);
+        for (int pi = 0; pi < 8; pi++) {
+          v.x += pv[pi].x;
+          v.y += pv[pi].y;
+          v.z += pv[pi].z;
+          v.w += pv[pi].w;
+        }
+        for (int pi = 8; pi < n_parts; pi++) {
+          const float4 e = *reinterpret_cast<const float4*>(src + (size_t)pi * part_stride);
+          v.x += e.x;
+          v.y += e.y;
+          v.z += e.z;
+          v.w += e.w;
+        }
+        v.x = __bfloat162float(__float2bfloat16_rn(v.x));
+        v.y = __bfloat162float(__float2bfloat16_rn(v.y));
+        v.z = __bfloat162float(__float2bfloat16_rn(v.z));
+        v.w = __bfloat162float(__float2bfloat16_rn(v.w));
+        *reinterpret_cast<float4*>(srow + (r < gn ? r : 16 + (r - gn)) * HD + d) = v;
       }
-      srow[(r < gn ? r : 16 + (r - gn)) * HD + d] = v;
+    } else {
+      for (int idx = tid; idx < (gn + 2) * HD; idx += 128) {
+        const int r = idx / HD, d = idx - r * HD;
+        const int col = r < gn ? (kvh * group + g0 + r) * HD + d : (r == gn ? (nh + kvh) * HD + d : (nh + nkv + kvh) * HD + d);
+        srow[(r < gn ? r : 16 + (r - gn)) * HD + d] = __bfloat162float(q[(size_t)t * q_stride + col]);
+      }
     }
     __syncthreads();
     if (owns_new) {
@@ -327,8 +409,8 @@ attn_decode_mma_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restric
     {
       const int nxt = it + DSTAGES - 1;
       if (nxt < n_tiles)
-        load_kv_tile(smem + (nxt % DSTAGES) * STAGE_B, kcache, vcache, table, kvh, nkv, ps, k_begin + nxt * KT, k_begin,
-                     k_end, tid, 128);
+        load_kv_tile<128>(smem + (nxt % DSTAGES) * STAGE_B, kcache, vcache, table, kvh, nkv, ps, k_begin + nxt * KT,
+                          k_begin, k_end, tid);
       cp_async_commit();
     }
     cp_async_wait<DSTAGES - 1>();
@@ -437,18 +519,11 @@ attn_decode_mma_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restric
   if (!s_last) return;
   __threadfence();
   const size_t orow = (size_t)out_row_of[s] * out_stride;
-  for (int idx = tid; idx < gn * HD; idx += 128) {
-    const int r = idx / HD, d = idx - r * HD;
+  for (int idx = tid; idx < gn * (HD / 2); idx += 128) {
+    const int r = idx / (HD / 2), d = (idx - r * (HD / 2)) * 2;
     const int head = kvh * group + g0 + r;
-    float mm = NEG_BIG;
-    for (int i = i0; i < i1; i++) mm = fmaxf(mm, __ldcg(part_ml + ((size_t)i * nh + head) * 2));
-    float acc = 0.f, ll = 0.f;
-    for (int i = i0; i < i1; i++) {
-      const float f = exp2f(__ldcg(part_ml + ((size_t)i * nh + head) * 2) - mm);
-      ll += f * __ldcg(part_ml + ((size_t)i * nh + head) * 2 + 1);
-      acc += f * __ldcg(part_o + ((size_t)i * nh + head) * HD + d);
-    }
-    out[orow + (size_t)head * HD + d] = __float2bfloat16_rn(acc / ll);
+    const float2 v = merge_splits(part_o, part_ml, i0, i1, nh, head, d);
+    *reinterpret_cast<uint32_t*>(out + orow + (size_t)head * HD + d) = pack_bf16(v.x, v.y);
   }
 }
 
@@ -464,18 +539,10 @@ __global__ void attn_decode_merge_kernel(const float* __restrict__ part_o, const
   const int head = blockIdx.y;
   const int s = dec_seqs[e];
   const int i0 = dec_item_start[e], i1 = dec_item_start[e + 1];
-  float mm = NEG_BIG;
-  for (int i = i0; i < i1; i++) mm = fmaxf(mm, part_ml[((size_t)i * nh + head) * 2]);
-  float ll = 0.f;
-  for (int i = i0; i < i1; i++)
-    ll += exp2f(part_ml[((size_t)i * nh + head) * 2] - mm) * part_ml[((size_t)i * nh + head) * 2 + 1];
-  const float inv = 1.f / ll;
   const int t = seq_q_start[s];
-  for (int d = threadIdx.x; d < HD; d += blockDim.x) {
-    float acc = 0.f;
-    for (int i = i0; i < i1; i++)
-      acc += exp2f(part_ml[((size_t)i * nh + head) * 2] - mm) * part_o[((size_t)i * nh + head) * HD + d];
-    out[(size_t)t * out_stride + (size_t)head * HD + d] = __float2bfloat16_rn(acc * inv);
+  for (int d = 2 * threadIdx.x; d < HD; d += 2 * blockDim.x) {
+    const float2 v = merge_splits(part_o, part_ml, i0, i1, nh, head, d);
+    *reinterpret_cast<uint32_t*>(out + (size_t)t * out_stride + (size_t)head * HD + d) = pack_bf16(v.x, v.y);
   }
 }
 
@@ -536,13 +603,13 @@ attn_prefill_mma_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restri
   const int warp_lo = window > 0 ? pos0 + warp * 16 - window + 1 : 0;
 
   const int n_tiles = (k_end - k_begin + KT - 1) / KT;
-  load_kv_tile(smem, kcache, vcache, table, kvh, nkv, ps, k_begin, k_begin, k_end, tid, 128);
+  load_kv_tile<128>(smem, kcache, vcache, table, kvh, nkv, ps, k_begin, k_begin, k_end, tid);
   cp_async_commit();
   for (int it = 0; it < n_tiles; it++) {
     unsigned char* cur = smem + (it & 1) * STAGE_B;
     if (it + 1 < n_tiles)
-      load_kv_tile(smem + ((it + 1) & 1) * STAGE_B, kcache, vcache, table, kvh, nkv, ps, k_begin + (it + 1) * KT,
-                   k_begin, k_end, tid, 128);
+      load_kv_tile<128>(smem + ((it + 1) & 1) * STAGE_B, kcache, vcache, table, kvh, nkv, ps, k_begin + (it + 1) * KT,
+                        k_begin, k_end, tid);
     cp_async_commit();
     cp_async_wait<1>();
     __syncthreads();

@@ -12,6 +12,7 @@ function and the sampler on the GPU.
 
 from __future__ import annotations
 
+from dataclasses import dataclass
 from typing import Any, Sequence
 
 import numpy as np
@@ -21,18 +22,28 @@ from tokasaurus_b200.config.engine_config import EngineConfig
 from tokasaurus_b200.cache.pages import NoSpaceError
 from tokasaurus_b200.engine.batch import StepEntry
 from tokasaurus_b200.engine.runner import ModelRunner
-from tokasaurus_b200.engine.scheduler import Scheduler, StepPlan
+from tokasaurus_b200.engine.scheduler import ScheduledPortion, Scheduler, StepPlan
 from tokasaurus_b200.sampling.params import Request, RequestOutput, SamplingParams, stream_key
 from tokasaurus_b200.sampling.sampler import Sampler
+
+
+@dataclass
+class _InFlight:
+    """A decode step that has been launched and whose results are on their way to the host."""
+    plan: StepPlan
+    rows: int    # rows of the plan
+    slot: int    # the sampler's landing place on the host
+    h2d: int
 
 
 class Engine:
     def __init__(self, model: str | None = None, config: EngineConfig | None = None,
                  config_dict: dict[str, Any] | None = None, seed: int = 0, kv_reserve_fraction: float = 1.0,
-                 **options: Any):
+                 run_ahead: bool = True, **options: Any):
         """``model``: folder with config.json and model.safetensors.  ``options``: fields of
         ``EngineConfig`` (the reference's option names).  ``config_dict`` with
-        ``random_weights=<seed>`` builds a model without a folder."""
+        ``random_weights=<seed>`` builds a model without a folder.  ``run_ahead``: launch the next decode step
+        before the results of the current one have been read (see ``step``)."""
         cfg = config or EngineConfig()
         if model is not None:
             cfg.model = model
@@ -57,7 +68,9 @@ class Engine:
 
             self.graphs = DecodeGraphs(self.runner, self.sampler, cfg.cudagraph_max_size, cfg.cudagraph_step)
         self._auto_id = 0
-        self._prepared_next = None  # host arrays of the step after this one, built while the GPU was busy
+        self.run_ahead = run_ahead
+        self._inflight: _InFlight | None = None
+        self._next_slot = 0
         self.last_step_bytes = dict(h2d=0, d2h=0)
 
     # ------------------------------------------------------------------ requests
@@ -82,7 +95,7 @@ class Engine:
         return request_id
 
     def has_work(self) -> bool:
-        return self.scheduler.has_work()
+        return self.scheduler.has_work() or self._inflight is not None
 
     # ------------------------------------------------------------------ one step
     def _sampling_arrays(self, plan: StepPlan) -> dict[str, np.ndarray]:
@@ -96,7 +109,33 @@ class Engine:
         return dict(temperature=temp, stream_key=keys, sample_pos=pos, row_slot=slot)
 
     def step(self) -> list[RequestOutput]:
-        """Schedule, run and account for one step; return the requests that ended in it."""
+        """Run one step and account for it; return the requests that ended in it.
+
+        Decode steps that run as CUDA graphs are pipelined, as the reference overlaps its manager with its
+        model worker (tokasaurus/manager/manager.py:981-1023 keeps steps queued ahead of the model): before the
+        results of step t are read, step t+1 is launched on the guess that every request of step t goes on (the
+        token it feeds is still on the device, in the last-token table).  If a request of step t ends on an
+        end-of-sequence or stop token after all, its row of step t+1 is thrown away: one wasted row, no wrong
+        result, and its pages, freed meanwhile, are not written again by anything that follows in the stream
+        before their next owner's own writes.  Ends by length are known beforehand and never guessed."""
+        if self._inflight is None:
+            done = self._start()
+            if done is not None:
+                return done
+        cur = self._inflight
+        self._inflight = self._launch_following(cur) if self.run_ahead else None
+        return self._finish(cur)
+
+    def _launch(self, plan: StepPlan, entries: list[StepEntry], extra: dict[str, np.ndarray]) -> _InFlight:
+        padded = self.graphs.launch(self.graphs.prepare(entries, extra))
+        slot = self._next_slot
+        self._next_slot ^= 1
+        self.sampler.start_read(padded, slot, self.runner.stager.status)
+        return _InFlight(plan, padded, slot, self.runner.last_upload_bytes)
+
+    def _start(self) -> list[RequestOutput] | None:
+        """Schedule a step.  A decode step that runs as a graph is launched and left in flight (returns None);
+        anything else runs to its end here."""
         plan = self.scheduler.schedule()
         if not plan.portions:
             return []
@@ -107,16 +146,8 @@ class Engine:
         extra = self._sampling_arrays(plan)
         wants_topk = any(p.seq.request.topk_logprobs for p in plan.portions if p.samples)
         if self.graphs is not None and not wants_topk and self.graphs.usable(entries):
-            prep, self._prepared_next = self._prepared_next, None
-            if prep is None or prep["signature"] != [(e.request, e.start) for e in entries]:
-                prep = self.graphs.prepare(entries, extra)
-            padded = self.graphs.launch(prep)
-            self._prepared_next = self._prepare_following(plan)  # overlaps the GPU's work on this step
-            ids, lps = self.sampler.read(padded)
-            ids, lps = ids[:len(entries)], lps[:len(entries)]
-            self.runner.check_status()
-            self.last_step_bytes = dict(h2d=self.runner.last_upload_bytes, d2h=self.sampler.bytes_last_read)
-            return self.scheduler.complete(plan, ids, lps if self.config.enable_chosen_logprobs else None, None)
+            self._inflight = self._launch(plan, entries, extra)
+            return None
         logits = self.runner.step(entries, extra)
         R = logits.shape[0]
         ids: list[int] = []
@@ -136,38 +167,50 @@ class Engine:
         self.last_step_bytes = dict(h2d=self.runner.last_upload_bytes, d2h=self.sampler.bytes_last_read if R else 4)
         return self.scheduler.complete(plan, ids, lps if self.config.enable_chosen_logprobs else None, topk)
 
-    def _prepare_following(self, plan: StepPlan):
-        """While the GPU runs the step of ``plan``: build the host arrays of the step after it, on the guess
-        that every request of this step goes on decoding (none ends on an end-of-sequence or stop token, none is
-        pushed out, nothing new is admitted).  The next ``step`` checks the guess against what the scheduler
-        really decides and builds the arrays afresh if it was wrong."""
-        if self.scheduler.queued or any(not p.samples for p in plan.portions):
+    def _finish(self, cur: _InFlight) -> list[RequestOutput]:
+        """Wait for an in-flight step and account for it.  Rows of requests that ended in the step before it
+        (it was launched before that was known) are dropped."""
+        ids, lps, status = self.sampler.finish_read(cur.rows, cur.slot)
+        self.runner.check_status(status)
+        running = set(map(id, self.scheduler.decoding)) | set(map(id, self.scheduler.prefilling))
+        keep = [i for i, p in enumerate(cur.plan.portions) if id(p.seq) in running]
+        plan = cur.plan
+        if len(keep) != len(plan.portions):
+            plan = StepPlan([plan.portions[i] for i in keep], plan.bumped)
+        ids, lps = [ids[i] for i in keep], [lps[i] for i in keep]
+        self.last_step_bytes = dict(h2d=cur.h2d, d2h=self.sampler.bytes_last_read)
+        return self.scheduler.complete(plan, ids, lps if self.config.enable_chosen_logprobs else None, None)
+
+    def _launch_following(self, cur: _InFlight) -> _InFlight | None:
+        """Launch the decode step after ``cur`` before ``cur``'s results are known: every request of ``cur`` that
+        is still running and does not end by length in ``cur`` brings the token ``cur`` samples for it.  None if
+        the scheduler has decisions to make first (something is queued or mid-prompt, a page is missing)."""
+        sched = self.scheduler
+        if sched.queued or sched.prefilling:
             return None
-        entries, rows = [], []
+        running = set(map(id, sched.decoding))
+        portions, entries = [], []
         try:
-            for p in plan.portions:
-                req = p.seq.request
-                if len(p.seq.output.completion_ids) + 1 >= req.max_num_tokens:
-                    return None  # ends by length in this step
+            for p in cur.plan.portions:
+                seq = p.seq
+                if id(seq) not in running:
+                    continue  # ended in the step before ``cur``
+                if len(seq.output.completion_ids) + 1 >= seq.request.max_num_tokens:
+                    continue  # ends by length in ``cur``
                 start = p.start + p.n_tokens
-                self.runner.cache.ensure_capacity(p.seq.id, start + 1)
-                entries.append(StepEntry(p.seq.id, None, start, [0]))
-                rows.append((p, start))
+                self.runner.cache.ensure_capacity(seq.id, start + 1)
+                portions.append(ScheduledPortion(seq, start, 1, True, from_device=True))
+                entries.append(StepEntry(seq.id, None, start, [0]))
         except (NoSpaceError, KeyError):
-            return None  # no page free, or the request is gone: let the scheduler sort it out
+            return None  # no page free: the scheduler decides who is pushed out
         if not entries or not self.graphs.usable(entries):
             return None
-        temp = np.asarray([p.seq.request.sampling_params.temperature for p, _ in rows], dtype=np.float32)
-        keys = np.asarray(
-            [stream_key(p.seq.request.sampling_params.seed if p.seq.request.sampling_params.seed is not None
-                        else self.seed, p.seq.index) for p, _ in rows], dtype=np.int64)
-        pos = np.asarray([start + 1 for _, start in rows], dtype=np.int32)
-        slot = np.asarray([self.runner.cache.slot(p.seq.id) for p, _ in rows], dtype=np.int32)
-        return self.graphs.prepare(entries, dict(temperature=temp, stream_key=keys, sample_pos=pos, row_slot=slot))
+        plan = StepPlan(portions)
+        return self._launch(plan, entries, self._sampling_arrays(plan))
 
     def run_until_done(self) -> list[RequestOutput]:
         done: list[RequestOutput] = []
-        while self.scheduler.has_work():
+        while self.has_work():
             done.extend(self.step())
         return done
 

@@ -104,10 +104,12 @@ class ModelRunner:
         self.last_context = ctx
         return self.model.forward(ctx)
 
-    def check_status(self) -> None:
+    def check_status(self, code: int | None = None) -> None:
         """Raise if a kernel met a token id or a page outside its table since the last check
-        (the kernels skip such accesses and set a flag instead of faulting)."""
-        code = int(self.stager.status.item())
+        (the kernels skip such accesses and set a flag instead of faulting).  ``code``: the status word if
+        the caller has read it already (with a step's results); else it is read here, which waits."""
+        if code is None:
+            code = int(self.stager.status.item())
         if code:
             self.stager.status.zero_()
             what = []

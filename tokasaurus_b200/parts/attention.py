@@ -211,7 +211,7 @@ class PagedAttention(Mixer):
                                          plan["dec_seqs"], plan["dec_item_start"], c[1:2],
                                          caps["dec"] if caps else int(counts[1]), attn, nh, nkv, hd, cache.page_size,
                                          self.scale, self.window, self.inv_freq, rot, cache.writable,
-                                         ctx.status, item_entry=plan["item_entry"] if int(counts[0]) == int(counts[1]) else None)
+                                         ctx.status, item_entry=plan["item_entry"])
                 if residual is not None:
                     ops.linear_decode(attn, self.w_o, "add", out=residual)
                     return None
@@ -235,7 +235,7 @@ class PagedAttention(Mixer):
                                          plan["dec_seqs"], plan["dec_item_start"], c[1:2],
                                          caps["dec"] if caps else int(counts[1]), attn, nh, nkv, hd, cache.page_size,
                                          self.scale, self.window, self.inv_freq, rot, cache.writable,
-                                         ctx.status, item_entry=plan["item_entry"] if int(counts[0]) == int(counts[1]) else None)
+                                         ctx.status, item_entry=plan["item_entry"])
                 return few(attn, self.w_o)
             qkv = torch.empty((T, nh * hd), dtype=h.dtype, device=h.device)  # q only; k and v go straight to the cache
             ops.rope_kv_write_partials(parts, qkv, ctx.positions, ctx.token_seq, tables.indptr, tables.page_ids,
@@ -279,7 +279,7 @@ class PagedAttention(Mixer):
             ops.attn_decode_mma(qkv, cache.k, cache.v, ctx.seq_q_start, ctx.seq_kv_len, tables.indptr, tables.page_ids,
                                 plan["items"], c[0:1], items_cap, plan["dec_seqs"], plan["dec_item_start"], c[1:2],
                                 dec_cap, attn, nh, nkv, hd, cache.page_size, self.scale, self.window,
-                                item_entry=plan["item_entry"] if int(counts[0]) == int(counts[1]) else None)
+                                item_entry=plan["item_entry"])
         if tiles_cap and self._query_tile() == QUERY_TILE_TC:
             ops.attn_prefill_tc(qkv, attn, cache.k, cache.v, ctx.seq_q_start, ctx.seq_q_len, ctx.seq_kv_len,
                                 tables.indptr, tables.page_ids, plan["tiles"], c[2:3], tiles_cap, nh, nkv, hd,

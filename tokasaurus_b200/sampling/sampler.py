@@ -25,7 +25,11 @@ class Sampler:
     def _alloc(self, n: int) -> None:
         self.max_rows = n
         self.out = torch.zeros((2 * n,), dtype=torch.int32, device=self.device)
-        self.host = torch.zeros((2 * n,), dtype=torch.int32, pin_memory=self.device.type == "cuda")
+        cuda = self.device.type == "cuda"
+        # two landing places on the host, so that the results of a step can be on their way while the
+        # step before it is still being read; the last word of each holds the device's status flag
+        self.host = [torch.zeros((2 * n + 1,), dtype=torch.int32, pin_memory=cuda) for _ in range(2)]
+        self.events = [torch.cuda.Event() if cuda else None for _ in range(2)]
 
     def sample(self, logits: torch.Tensor, temperature: torch.Tensor, stream_key: torch.Tensor,
                sample_pos: torch.Tensor, row_slot: torch.Tensor, last_token: torch.Tensor) -> None:
@@ -37,15 +41,33 @@ class Sampler:
         lp = self.out[R:2 * R].view(torch.float32) if self.want_logprobs else None
         ops.sample(logits, temperature, stream_key, sample_pos, row_slot, ids, lp, last_token)
 
+    def start_read(self, R: int, slot: int = 0, status: torch.Tensor | None = None) -> None:
+        """Put the copy of the last results (and of the device's status word) to landing place ``slot`` into
+        the stream; does not wait."""
+        n = 2 * R if self.want_logprobs else R
+        host = self.host[slot]
+        host[:n].copy_(self.out[:n], non_blocking=True)
+        if status is not None:
+            host[-1:].copy_(status, non_blocking=True)
+        else:
+            host[-1] = 0
+        if self.events[slot] is not None:
+            self.events[slot].record(torch.cuda.current_stream(self.device))
+        self.bytes_last_read = 4 * n + (4 if status is not None else 0)
+
+    def finish_read(self, R: int, slot: int = 0) -> tuple[list[int], list[float], int]:
+        """Wait for ``start_read`` of ``slot``; ids, log-probabilities and the status word."""
+        if self.events[slot] is not None:
+            self.events[slot].synchronize()
+        host = self.host[slot]
+        ids = host[:R].tolist()
+        lps = host[R:2 * R].view(torch.float32).tolist() if self.want_logprobs else [0.0] * R
+        return ids, lps, int(host[-1])
+
     def read(self, R: int) -> tuple[list[int], list[float]]:
         """Copy the last results to the host (waits for the step)."""
-        n = 2 * R if self.want_logprobs else R
-        self.host[:n].copy_(self.out[:n], non_blocking=True)
-        if self.device.type == "cuda":
-            torch.cuda.current_stream(self.device).synchronize()
-        self.bytes_last_read = 4 * n
-        ids = self.host[:R].tolist()
-        lps = self.host[R:2 * R].view(torch.float32).tolist() if self.want_logprobs else [0.0] * R
+        self.start_read(R, 0)
+        ids, lps, _ = self.finish_read(R, 0)
         return ids, lps
 
     def topk(self, logits: torch.Tensor, temperature: torch.Tensor, k: int) -> tuple[torch.Tensor, torch.Tensor]:
