@@ -406,15 +406,15 @@ attn_decode_mma_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restric
 
   for (int it = 0; it < n_tiles; it++) {
     unsigned char* cur = smem + (it % DSTAGES) * STAGE_B;
+    cp_async_wait<DSTAGES - 2>();
+    __syncthreads();  // tile `it` is there for every warp, and every warp is through with tile it - 1
     {
-      const int nxt = it + DSTAGES - 1;
+      const int nxt = it + DSTAGES - 1;  // into the stage that tile it - 1 has just left
       if (nxt < n_tiles)
         load_kv_tile<128>(smem + (nxt % DSTAGES) * STAGE_B, kcache, vcache, table, kvh, nkv, ps, k_begin + nxt * KT,
                           k_begin, k_end, tid);
       cp_async_commit();
     }
-    cp_async_wait<DSTAGES - 1>();
-    __syncthreads();
     if (owns_new && it == n_tiles - 1) {
       // the tile came from the cache as it was before this step: put the token's own key and value in
       const int row = p - (k_begin + it * KT);
@@ -441,7 +441,6 @@ attn_decode_mma_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restric
       }
       pv_16keys(o, pf, smem_u32(cur) + TILE_B, warp * 16, lane);
     }
-    __syncthreads();
   }
   cp_async_wait<0>();
   __syncthreads();
