@@ -82,7 +82,6 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const T* __restrict__ 
                                    const float* __restrict__ partials, int n_partials, long long partial_stride,
                                    const float* __restrict__ w, T* __restrict__ out, float eps, int H) {
   trigger_dependents();
-  grid_dependency_wait();
   __shared__ float scratch[33];
   const size_t base = (size_t)blockIdx.x * H;
   float* xr = x + base;
@@ -92,16 +91,32 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const T* __restrict__ 
     // four elements a thread and step; the first four steps' sums stay in registers for the second pass
     constexpr int KEEP = 4;
     const int n4 = H >> 2;
-    float4 kept[KEEP];
-    int k = 0;
-    for (int i4 = threadIdx.x; i4 < n4; i4 += blockDim.x, k++) {
+    float4 kept[KEEP], gain[KEEP];
+    // the norm's weight is written by no kernel: it is fetched while the kernel ahead still runs
+#pragma unroll
+    for (int k = 0; k < KEEP; k++) {
+      const int i4 = threadIdx.x + k * blockDim.x;
+      if (i4 < n4) gain[k] = load4(w + 4 * i4);
+    }
+    grid_dependency_wait();
+    // x + update of four elements at 4 * i4, stored back; the update arrives as float32 slices of a split
+    // matrix product (eight loads in flight together, added in slice order) or in the activation type
+    auto updated = [&](int i4) {
       float4 v = load4(xr + 4 * i4);
       if (partials != nullptr) {
-        // the update arrives as float32 slices of a split matrix product: add them in slice order
         float4 d = make_float4(0.f, 0.f, 0.f, 0.f);
-        for (int p = 0; p < n_partials; p++) {
-          const float4 q = load4(partials + (size_t)p * partial_stride + base + 4 * i4);
-          d.x += q.x; d.y += q.y; d.z += q.z; d.w += q.w;
+        const float* src = partials + base + 4 * i4;
+        for (int p0 = 0; p0 < n_partials; p0 += 8) {
+          float4 q[8];
+#pragma unroll
+          for (int j = 0; j < 8; j++)
+            q[j] = p0 + j < n_partials ? load4(src + (size_t)(p0 + j) * partial_stride) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+          for (int j = 0; j < 8; j++) {
+            if (p0 + j < n_partials) {
+              d.x += q[j].x; d.y += q[j].y; d.z += q[j].z; d.w += q[j].w;
+            }
+          }
         }
         v.x += d.x; v.y += d.y; v.z += d.z; v.w += d.w;
         store4(xr + 4 * i4, v);
@@ -111,18 +126,31 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const T* __restrict__ 
         store4(xr + 4 * i4, v);
       }
       ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
-      if (k < KEEP) kept[k] = v;
+      return v;
+    };
+#pragma unroll
+    for (int k = 0; k < KEEP; k++) {
+      const int i4 = threadIdx.x + k * blockDim.x;
+      if (i4 < n4) kept[k] = updated(i4);
     }
+    for (int i4 = threadIdx.x + KEEP * blockDim.x; i4 < n4; i4 += blockDim.x) updated(i4);
     const float total = block_sum(ss, scratch);
     const float rstd = rsqrtf(total / (float)H + eps);
-    k = 0;
-    for (int i4 = threadIdx.x; i4 < n4; i4 += blockDim.x, k++) {
-      const float4 v = k < KEEP ? kept[k] : load4(xr + 4 * i4);
-      const float4 g = load4(w + 4 * i4);
+#pragma unroll
+    for (int k = 0; k < KEEP; k++) {
+      const int i4 = threadIdx.x + k * blockDim.x;
+      if (i4 < n4) {
+        const float4 v = kept[k], g = gain[k];
+        store4(orow + 4 * i4, make_float4(v.x * rstd * g.x, v.y * rstd * g.y, v.z * rstd * g.z, v.w * rstd * g.w));
+      }
+    }
+    for (int i4 = threadIdx.x + KEEP * blockDim.x; i4 < n4; i4 += blockDim.x) {
+      const float4 v = load4(xr + 4 * i4), g = load4(w + 4 * i4);
       store4(orow + 4 * i4, make_float4(v.x * rstd * g.x, v.y * rstd * g.y, v.z * rstd * g.z, v.w * rstd * g.w));
     }
     return;
   }
+  grid_dependency_wait();
   if (partials != nullptr) {
     for (int i = threadIdx.x; i < H; i += blockDim.x) {
       float d = 0.f;
@@ -149,11 +177,119 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const T* __restrict__ 
   for (int i = threadIdx.x; i < H; i += blockDim.x) orow[i] = from_float<T>(xr[i] * rstd * w[i]);
 }
 
+// The same for few rows whose update arrives as slices: the row of x and the rows of the slices come into shared
+// memory by bulk copies (the copy engine keeps all of them in flight at once; 512 threads with nine 16-byte loads
+// each do not: the load phase of 8 slices of 2,048 took 2.5 us that way, twice that of 4 slices).  One thread
+// issues the copies and everybody waits on their mbarrier, with a limit; if the limit runs out the block reads
+// from global memory instead, so the result does not depend on the wait.
+__device__ __forceinline__ uint32_t ew_smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+template <typename T>
+__global__ void add_rmsnorm_bulk_kernel(float* __restrict__ x, const float* __restrict__ partials, int n_partials,
+                                        long long partial_stride, const float* __restrict__ w, T* __restrict__ out,
+                                        float eps, int H) {
+  extern __shared__ __align__(128) unsigned char ew_smem[];
+  float* rows = reinterpret_cast<float*>(ew_smem);  // [1 + n_partials][H]
+  __shared__ __align__(8) unsigned long long bar;
+  __shared__ float scratch[33];
+  trigger_dependents();
+  const size_t base = (size_t)blockIdx.x * H;
+  float* xr = x + base;
+  T* orow = out + base;
+  constexpr int KEEP = 4;
+  const int n4 = H >> 2;
+  float4 kept[KEEP], gain[KEEP];
+#pragma unroll
+  for (int k = 0; k < KEEP; k++) {
+    const int i4 = threadIdx.x + k * blockDim.x;
+    if (i4 < n4) gain[k] = load4(w + 4 * i4);
+  }
+  const uint32_t bar_a = ew_smem_u32(&bar);
+  if (threadIdx.x == 0) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar_a));
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  grid_dependency_wait();
+  const uint32_t row_bytes = (uint32_t)H * 4u;
+  if (threadIdx.x == 0) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar_a), "r"(row_bytes * (uint32_t)(n_partials + 1)) : "memory");
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(ew_smem_u32(rows)), "l"(xr), "r"(row_bytes), "r"(bar_a) : "memory");
+    for (int p = 0; p < n_partials; p++)
+      asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                   ::"r"(ew_smem_u32(rows + (size_t)(p + 1) * H)), "l"(partials + (size_t)p * partial_stride + base),
+                     "r"(row_bytes), "r"(bar_a) : "memory");
+  }
+  bool arrived = false;
+  for (uint32_t i = 0; i < (1u << 20) && !arrived; i++) {
+    uint32_t done;
+    asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], 0;\nselp.u32 %0, 1, 0, p;\n}"
+                 : "=r"(done) : "r"(bar_a) : "memory");
+    arrived = done != 0;
+  }
+  float ss = 0.f;
+  auto updated = [&](int i4) {
+    float4 v, d = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (arrived) {
+      v = load4(rows + 4 * i4);
+      for (int p = 0; p < n_partials; p++) {
+        const float4 q = load4(rows + (size_t)(p + 1) * H + 4 * i4);
+        d.x += q.x; d.y += q.y; d.z += q.z; d.w += q.w;
+      }
+    } else {
+      v = load4(xr + 4 * i4);
+      for (int p = 0; p < n_partials; p++) {
+        const float4 q = load4(partials + (size_t)p * partial_stride + base + 4 * i4);
+        d.x += q.x; d.y += q.y; d.z += q.z; d.w += q.w;
+      }
+    }
+    v.x += d.x; v.y += d.y; v.z += d.z; v.w += d.w;
+    store4(xr + 4 * i4, v);
+    ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+    return v;
+  };
+#pragma unroll
+  for (int k = 0; k < KEEP; k++) {
+    const int i4 = threadIdx.x + k * blockDim.x;
+    if (i4 < n4) kept[k] = updated(i4);
+  }
+  for (int i4 = threadIdx.x + KEEP * blockDim.x; i4 < n4; i4 += blockDim.x) updated(i4);
+  const float total = block_sum(ss, scratch);
+  const float rstd = rsqrtf(total / (float)H + eps);
+#pragma unroll
+  for (int k = 0; k < KEEP; k++) {
+    const int i4 = threadIdx.x + k * blockDim.x;
+    if (i4 < n4) {
+      const float4 v = kept[k], g = gain[k];
+      store4(orow + 4 * i4, make_float4(v.x * rstd * g.x, v.y * rstd * g.y, v.z * rstd * g.z, v.w * rstd * g.w));
+    }
+  }
+  for (int i4 = threadIdx.x + KEEP * blockDim.x; i4 < n4; i4 += blockDim.x) {
+    const float4 v = load4(xr + 4 * i4), g = load4(w + 4 * i4);
+    store4(orow + 4 * i4, make_float4(v.x * rstd * g.x, v.y * rstd * g.y, v.z * rstd * g.z, v.w * rstd * g.w));
+  }
+}
+
 template <typename T>
 static int add_rmsnorm_launch(float* x, const void* delta, const float* partials, int n_partials,
                               long long partial_stride, const float* w, void* out, float eps, int rows, int H,
                               cudaStream_t st) {
   if (rows <= 0) return 0;
+  // few rows with slices: bulk copies into shared memory (rows of 16-byte multiples, everything 16-byte aligned)
+  const size_t bulk_bytes = (size_t)(n_partials + 1) * H * 4;
+  if (partials != nullptr && rows <= 64 && (H & 3) == 0 && bulk_bytes <= 200 * 1024 && ((uintptr_t)x & 15) == 0 &&
+      ((uintptr_t)partials & 15) == 0 && (partial_stride & 3) == 0) {
+    static bool attr_done[2] = {false, false};
+    constexpr int which = sizeof(T) == 4 ? 0 : 1;
+    if (!attr_done[which]) {
+      cudaError_t e = cudaFuncSetAttribute(add_rmsnorm_bulk_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+      if (e != cudaSuccess) return (int)e;
+      attr_done[which] = true;
+    }
+    return launch_pdl(add_rmsnorm_bulk_kernel<T>, dim3(rows), dim3(H >= 2048 ? 512 : 256), bulk_bytes, st, x, partials,
+                      n_partials, partial_stride, w, (T*)out, eps, H);
+  }
   // few rows: many threads a row, they hide the latency; many rows: several rows an SM in flight do
   int threads = H >= 8192 || (H >= 2048 && rows < 592) ? 512 : (H >= 512 ? 256 : 128);
   return launch_pdl(add_rmsnorm_kernel<T>, dim3(rows), dim3(threads), 0, st, x, (const T*)delta, partials, n_partials,
