@@ -37,7 +37,14 @@ def _ptr(t: torch.Tensor | None) -> c_void_p:
     return c_void_p(t.data_ptr())
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def _stream() -> c_void_p:
+    """The current CUDA stream of the current device as a raw handle (the direct binding where torch has
+    it: ``torch.cuda.current_stream()`` costs more on the host than a kernel launch)."""
+    if _raw_stream is not None:
+        return c_void_p(_raw_stream(torch.cuda.current_device()))
     return c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
@@ -70,6 +77,9 @@ def _check(code: int, what: str) -> None:
 
 
 def _fn(lib: ctypes.CDLL, name: str):
+    f = lib.__dict__.get(name)  # ctypes keeps a function it has looked up once as an attribute of the library
+    if f is not None:
+        return f
     try:
         f = getattr(lib, name)
     except AttributeError:
@@ -83,7 +93,7 @@ class _Libs:
         self._cache: dict[tuple, ctypes.CDLL] = {}
 
     def get(self, source: str, **defines) -> ctypes.CDLL:
-        key = (source, tuple(sorted(defines.items())))
+        key = (source, tuple(defines.items())) if len(defines) < 2 else (source, tuple(sorted(defines.items())))
         lib = self._cache.get(key)
         if lib is None:
             lib = build.load_module(source, defines or None)
