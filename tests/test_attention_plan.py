@@ -1,0 +1,60 @@
+"""The host-side work list of the attention kernels: every visible key of every single-token request lies in
+exactly one work item, items are whole tiles, a step fills one wave of blocks where it can, and portions are
+cut into query tiles that cover them exactly."""
+
+from types import SimpleNamespace
+
+import numpy as np
+import pytest
+
+from tokasaurus_b200.parts.attention import DECODE_BLOCK_SLOTS, MIN_SPLIT_KEYS, plan_attention, split_keys_evenly
+
+
+@pytest.mark.parametrize("spans", [[1], [2053] * 8, [2053] * 16, [2053] * 32, [2053] * 64, [17, 40000, 300, 64, 65],
+                                   [100000] + [100] * 63, [128] * 500])
+@pytest.mark.parametrize("blocks_per_item", [1, 8, 16])
+def test_split_covers_every_key_once(spans, blocks_per_item):
+    span = np.asarray(spans, dtype=np.int64)
+    n, size = split_keys_evenly(span, blocks_per_item)
+    assert n.shape == span.shape and (n >= 1).all()
+    assert (size % 64 == 0).all() and (size >= 64).all()
+    assert ((n - 1) * size < span).all() and (n * size >= span).all()  # no empty item, none missing
+    # a request is cut only down to the floor, and one long request among short ones is still cut
+    assert (size[n > 1] >= MIN_SPLIT_KEYS).all()
+    slots = DECODE_BLOCK_SLOTS // blocks_per_item
+    if span.max() > 4 * span.sum() / max(1, slots) and span.max() > 4 * MIN_SPLIT_KEYS:
+        assert n[np.argmax(span)] > 1
+
+
+def test_one_wave_where_the_batch_allows():
+    for batch, want_items in ((8, 48), (16, 48), (32, 64), (64, 64)):
+        n, _ = split_keys_evenly(np.full((batch,), 2053, dtype=np.int64), 8)
+        assert int(n.sum()) == want_items, batch
+
+
+@pytest.mark.parametrize("window", [None, 100])
+@pytest.mark.parametrize("query_tile", [64, 128])
+def test_plan_items_and_tiles(window, query_tile):
+    q_len = np.asarray([1, 1, 70, 2, 130, 1, 128], dtype=np.int32)
+    kv_len = np.asarray([1, 777, 70, 259, 400, 256, 128], dtype=np.int32)
+    plan = plan_attention(SimpleNamespace(seq_q_len=q_len, seq_kv_len=kv_len), window, query_tile=query_tile)
+    n_items, n_dec, n_tiles = (int(x) for x in plan["counts"][:3])
+    items = plan["items"][: 3 * n_items].reshape(-1, 3)
+    dec = plan["dec_seqs"][:n_dec]
+    assert list(dec) == [0, 1, 5]
+    start = plan["dec_item_start"][: n_dec + 1]
+    for e, s in enumerate(dec):
+        mine = items[start[e]:start[e + 1]]
+        assert (mine[:, 0] == s).all() and (plan["item_entry"][start[e]:start[e + 1]] == e).all()
+        span = min(int(kv_len[s]), window) if window else int(kv_len[s])
+        covered = np.zeros(span, dtype=np.int32)
+        for _, first, count in mine:
+            covered[first:min(span, first + count)] += 1
+        assert (covered == 1).all()
+    tiles = plan["tiles"][: 2 * n_tiles].reshape(-1, 2)
+    for s in (2, 3, 4, 6):
+        firsts = sorted(int(q0) for r, q0 in tiles if r == s)
+        assert firsts == list(range(0, int(q_len[s]), query_tile))
+    # the tiles that reach the furthest come first
+    reach = [int(kv_len[r] - q_len[r] + q0) for r, q0 in tiles]
+    assert reach == sorted(reach, reverse=True)
