@@ -58,3 +58,19 @@ def test_plan_items_and_tiles(window, query_tile):
     # the tiles that reach the furthest come first
     reach = [int(kv_len[r] - q_len[r] + q0) for r, q0 in tiles]
     assert reach == sorted(reach, reverse=True)
+
+
+def test_item_count_stays_under_the_bound_of_the_graphs():
+    """CUDA graphs of decode steps size the work list for a batch size alone; no mix of contexts may need more."""
+    from tokasaurus_b200.parts.attention import PagedAttention
+    from tokasaurus_b200.parts.rope import NoPositionEncoding
+
+    rng = np.random.default_rng(0)
+    for nh, nkv in ((32, 8), (4, 4), (64, 1)):
+        mixer = PagedAttention(nh * 16, nh, nkv, 16, NoPositionEncoding(), "q", "k", "v", "o")
+        for _ in range(300):
+            r = int(rng.integers(1, 130))
+            kind = int(rng.integers(0, 3))
+            span = rng.integers(1, [200, 5000, 200000][kind], size=r).astype(np.int64)
+            n, _ = split_keys_evenly(span, mixer._blocks_per_item())
+            assert int(n.sum()) <= mixer.plan_capacity(r)["items"], (nh, nkv, r, kind)

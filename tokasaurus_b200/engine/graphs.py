@@ -3,11 +3,14 @@
 The reference records graphs for decode-only batches of 16, 32, ... 128 requests, pads a batch up
 to the next recorded size and sends padded rows to a spare page (tokasaurus/model/utils.py:512-720,
 :839-882; sizes from ``cudagraph_step``/``cudagraph_max_size``, tokasaurus/common_types.py:119-122).
-Here a graph holds the whole step, model and sampler, for one (padded batch size, capacity of the
-attention work list, capacity of the block tables); it is recorded the first time that shape comes
-up.  Every array of the step lives at a fixed place of the graph's own staging buffer, so a replay
-is: fill the pinned copy, one copy to the device, one graph launch.  Padded rows carry request
-row -1: the kernels skip them, nothing is written for them, no spare page is needed.
+Here a graph holds the whole step, model and sampler, for one padded batch size; it is recorded the
+first time that size comes up.  The block tables are staged at the capacity of the whole page pool
+and the attention work list at the most items the planner can make for that batch size, so neither
+the contexts' lengths nor their growth ever ask for another graph.  All graphs share one memory
+pool (they never run at the same time).  Every array of the step lives at a fixed place of the
+graph's own staging buffer, so a replay is: fill the pinned copy, one copy to the device, one graph
+launch.  Padded rows carry request row -1: the kernels skip them, nothing is written for them, no
+spare page is needed.
 """
 
 from __future__ import annotations
@@ -39,6 +42,7 @@ class DecodeGraphs:
         self.sizes = sorted({s for s in (1, 2, 4, 8) if s <= max_size} | set(range(step, max_size + 1, step)))
         self.graphs: dict[tuple, dict] = {}
         self.launches_per_replay = 0
+        self.pool = None  # memory pool shared by all graphs
 
     def usable(self, entries) -> bool:
         return (bool(self.sizes) and len(entries) <= self.sizes[-1] and self.runner.model.graph_safe
@@ -61,13 +65,18 @@ class DecodeGraphs:
         B = len(entries)
         bp = next(s for s in self.sizes if s >= B)
         host = build_host_batch(entries, runner.cache)
-        page_caps = [_pow2_at_least(pg.shape[0], 64) for pg in host.table_pages]
+        # block tables at the capacity of the pool: a request's table never outgrows it
+        page_caps = [max(g.allocator.num_pages, pg.shape[0], 1) for g, pg in zip(runner.cache.groups, host.table_pages)]
         planners = runner.model.planners()
         raw = {key: m.plan(host) for key, m in planners.items()}
-        caps = {key: dict(items=_pow2_at_least(int(p["counts"][0]), 8), dec=bp, tiles=0) for key, p in raw.items()}
-        # the plans' shape: capacities, and whether every request has a single work item (another kernel path)
-        key = (bp, tuple(page_caps), tuple(sorted((str(k), c["items"], int(raw[k]["counts"][0]) == int(raw[k]["counts"][1]))
-                                                    for k, c in caps.items())))
+        caps = {}
+        for key, p in raw.items():
+            bound = planners[key].plan_capacity(bp) if hasattr(planners[key], "plan_capacity") else None
+            items = int(p["counts"][0])
+            # the planner's own bound for this batch size; a plan beyond it (there should be none) gets a graph of its own
+            cap = bound["items"] if bound is not None and items <= bound["items"] else _pow2_at_least(items, 8)
+            caps[key] = dict(items=cap, dec=bp, tiles=0)
+        key = (bp, tuple(page_caps), tuple(sorted((str(k), c["items"]) for k, c in caps.items())))
         plans = {k: planners[k].pad_plan(p, caps[k]) for k, p in raw.items()}
         ex = dict(temperature=_pad(extra["temperature"], bp), stream_key=_pad(extra["stream_key"], bp),
                   sample_pos=_pad(extra["sample_pos"], bp), row_slot=_pad(extra["row_slot"], bp, -1))
@@ -123,7 +132,9 @@ class DecodeGraphs:
         torch.cuda.synchronize()
         before = ops.LAUNCHES
         g = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(g):
+        if self.pool is None:
+            self.pool = torch.cuda.graph_pool_handle()
+        with torch.cuda.graph(g, pool=self.pool):
             slot["logits"] = body()
         slot["launches"] = ops.LAUNCHES - before
         ops.LAUNCHES = before

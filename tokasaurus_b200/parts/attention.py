@@ -182,6 +182,12 @@ class PagedAttention(Mixer):
     def plan(self, host, capacity=None):
         return plan_attention(host, self.window, capacity, self._blocks_per_item(), self._query_tile())
 
+    def plan_capacity(self, n_requests: int) -> dict:
+        """The most work items ``plan`` can make for a step of ``n_requests`` single-token requests, whatever
+        their contexts: each request gets at most (its keys // the item size) items, at least one."""
+        wave = max(1, DECODE_BLOCK_SLOTS // max(1, self._blocks_per_item()))
+        return dict(items=n_requests + wave + wave // 4 + 1, dec=n_requests, tiles=0)
+
     def pad_plan(self, plan: dict, capacity: dict) -> dict:
         """The same plan with its arrays at the fixed sizes of a CUDA graph."""
         def padded(x, n):
