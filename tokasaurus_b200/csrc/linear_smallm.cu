@@ -18,7 +18,7 @@ typedef __nv_bfloat16 bf16;
 
 namespace {
 
-constexpr int BN = 64;               // output features per block
+constexpr int BN = 64;               // output features per block of four warps (16 a warp)
 constexpr int BK = 128;              // k per stage
 constexpr int ROWB = BK * 2 + 16;    // padded row bytes (conflict-free ldmatrix)
 
@@ -39,20 +39,27 @@ __device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], 
                : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
-template <int NT> struct Tile {
+// WARPS warps a block, 16 output features a warp.  Four warps and two blocks an SM is the general shape; a wide
+// product whose feature tiles do not divide evenly over the SMs that way (gate/up of 16,384 rows: 256 blocks
+// on 148 SMs, so most SMs stream twice what the others do, and an SM streams at a fixed rate) runs as one
+// block of up to eight warps an SM instead.
+template <int NT, int WARPS = 4> struct Tile {
   static constexpr int A_ROWS = NT * 8 < 16 ? 16 : NT * 8;  // token rows kept in shared memory (>= 16 for ldmatrix.x4)
-  static constexpr int STAGE_B = (BN + A_ROWS) * ROWB;
-  static constexpr int STAGES = NT <= 2 ? 5 : 4;  // deep for few tokens: the weight tiles in flight are what is prefetched
+  static constexpr int ROWS = WARPS * 16;                    // weight rows (output features) per block
+  static constexpr int STAGE_B = (ROWS + A_ROWS) * ROWB;
+  // deep for few tokens: the weight tiles in flight are what is prefetched; one block an SM takes what fits
+  static constexpr int STAGES = WARPS > 4 ? (200 * 1024) / STAGE_B : (NT <= 2 ? 5 : 4);
   static constexpr int SMEM_B = STAGES * STAGE_B;
 };
 
+template <int WARPS>
 __device__ __forceinline__ void load_w(unsigned char* stage, const bf16* __restrict__ W, int ldw, int N, int n0,
                                        int k0, int k_end, int tid) {
   const uint32_t sw = smem_u32(stage);
   constexpr int CPR = BK / 8;  // 16-byte chunks per row
 #pragma unroll
-  for (int i = 0; i < (BN * CPR) / 128; i++) {
-    const int idx = tid + i * 128;
+  for (int i = 0; i < (16 * CPR) / 32; i++) {
+    const int idx = tid + i * (WARPS * 32);
     const int r = idx / CPR, c = idx % CPR;
     const int n = n0 + r, k = k0 + c * 8;
     const bool valid = n < N && k < k_end;
@@ -60,15 +67,16 @@ __device__ __forceinline__ void load_w(unsigned char* stage, const bf16* __restr
   }
 }
 
-template <int NT>
+template <int NT, int WARPS>
 __device__ __forceinline__ void load_a(unsigned char* stage, const bf16* __restrict__ A, int lda, int M, int k0,
                                        int k_end, int tid) {
-  const uint32_t sa = smem_u32(stage) + BN * ROWB;
+  const uint32_t sa = smem_u32(stage) + Tile<NT, WARPS>::ROWS * ROWB;
   constexpr int CPR = BK / 8;
-  constexpr int A_CHUNKS = Tile<NT>::A_ROWS * CPR;
+  constexpr int A_CHUNKS = Tile<NT, WARPS>::A_ROWS * CPR;
+  constexpr int THREADS = WARPS * 32;
 #pragma unroll
-  for (int i = 0; i < (A_CHUNKS + 127) / 128; i++) {
-    const int idx = tid + i * 128;
+  for (int i = 0; i < (A_CHUNKS + THREADS - 1) / THREADS; i++) {
+    const int idx = tid + i * THREADS;
     if (idx < A_CHUNKS) {
       const int r = idx / CPR, c = idx % CPR;
       const int k = k0 + c * 8;
@@ -78,13 +86,14 @@ __device__ __forceinline__ void load_a(unsigned char* stage, const bf16* __restr
   }
 }
 
-template <int NT, bool GATED>
-__global__ void __launch_bounds__(128)
+template <int NT, bool GATED, int WARPS = 4>
+__global__ void __launch_bounds__(WARPS * 32)
 linear_smallm_kernel(const bf16* __restrict__ A, int lda, const bf16* __restrict__ W, int ldw, void* __restrict__ out,
                      int M, int N, int K, int kblocks_per_slice) {
   extern __shared__ __align__(128) unsigned char smem[];
+  using T = Tile<NT, WARPS>;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int n0 = blockIdx.x * BN;
+  const int n0 = blockIdx.x * T::ROWS;
   const int slice = blockIdx.y;
   const int k_begin = slice * kblocks_per_slice * BK;
   const int k_end = min(K, k_begin + kblocks_per_slice * BK);
@@ -96,17 +105,17 @@ linear_smallm_kernel(const bf16* __restrict__ A, int lda, const bf16* __restrict
 #pragma unroll
     for (int i = 0; i < 4; i++) acc[j][i] = 0.f;
 
-  constexpr int STAGES = Tile<NT>::STAGES;
+  constexpr int STAGES = T::STAGES;
   // Weights are written by no kernel: their first tiles are fetched while the kernel before this one
   // may still be running.  The activations are read only after the wait.
   trigger_dependents();
 #pragma unroll
   for (int s = 0; s < STAGES - 1; s++)
-    if (s < nkb) load_w(smem + s * Tile<NT>::STAGE_B, W, ldw, N, n0, k_begin + s * BK, k_end, tid);
+    if (s < nkb) load_w<WARPS>(smem + s * T::STAGE_B, W, ldw, N, n0, k_begin + s * BK, k_end, tid);
   grid_dependency_wait();
 #pragma unroll
   for (int s = 0; s < STAGES - 1; s++) {
-    if (s < nkb) load_a<NT>(smem + s * Tile<NT>::STAGE_B, A, lda, M, k_begin + s * BK, k_end, tid);
+    if (s < nkb) load_a<NT, WARPS>(smem + s * T::STAGE_B, A, lda, M, k_begin + s * BK, k_end, tid);
     cp_async_commit();
   }
   const int w_row = warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
@@ -120,13 +129,13 @@ linear_smallm_kernel(const bf16* __restrict__ A, int lda, const bf16* __restrict
     {
       const int nxt = kb + STAGES - 1;
       if (nxt < nkb) {
-        unsigned char* st = smem + (nxt % STAGES) * Tile<NT>::STAGE_B;
-        load_w(st, W, ldw, N, n0, k_begin + nxt * BK, k_end, tid);
-        load_a<NT>(st, A, lda, M, k_begin + nxt * BK, k_end, tid);
+        unsigned char* st = smem + (nxt % STAGES) * T::STAGE_B;
+        load_w<WARPS>(st, W, ldw, N, n0, k_begin + nxt * BK, k_end, tid);
+        load_a<NT, WARPS>(st, A, lda, M, k_begin + nxt * BK, k_end, tid);
       }
       cp_async_commit();
     }
-    const uint32_t sw = smem_u32(smem + (kb % STAGES) * Tile<NT>::STAGE_B), sa = sw + BN * ROWB;
+    const uint32_t sw = smem_u32(smem + (kb % STAGES) * T::STAGE_B), sa = sw + T::ROWS * ROWB;
 #pragma unroll
     for (int ks = 0; ks < BK / 16; ks++) {
       uint32_t wf[4];
@@ -175,28 +184,37 @@ linear_smallm_kernel(const bf16* __restrict__ A, int lda, const bf16* __restrict
   }
 }
 
-template <int NT, bool GATED>
+template <int NT, bool GATED, int WARPS>
 int launch(const void* A, int lda, const void* W, int ldw, void* out, int M, int N, int K, int slices,
            int kblocks_per_slice, cudaStream_t st) {
+  using T = Tile<NT, WARPS>;
   static bool attr_done = false;
-  if (!attr_done && Tile<NT>::SMEM_B > 48 * 1024) {
-    cudaError_t e = cudaFuncSetAttribute(linear_smallm_kernel<NT, GATED>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         Tile<NT>::SMEM_B);
+  if (!attr_done && T::SMEM_B > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(linear_smallm_kernel<NT, GATED, WARPS>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, T::SMEM_B);
     if (e != cudaSuccess) return (int)e;
     attr_done = true;
   }
-  dim3 grid((N + BN - 1) / BN, slices);
-  return launch_pdl(linear_smallm_kernel<NT, GATED>, grid, dim3(128), (size_t)Tile<NT>::SMEM_B, st, (const bf16*)A, lda,
-                    (const bf16*)W, ldw, out, M, N, K, kblocks_per_slice);
+  dim3 grid((N + T::ROWS - 1) / T::ROWS, slices);
+  return launch_pdl(linear_smallm_kernel<NT, GATED, WARPS>, grid, dim3(WARPS * 32), (size_t)T::SMEM_B, st, (const bf16*)A,
+                    lda, (const bf16*)W, ldw, out, M, N, K, kblocks_per_slice);
 }
 
 template <bool GATED>
 int dispatch(const void* A, int lda, const void* W, int ldw, void* out, int M, int N, int K, int slices,
              int kblocks_per_slice, cudaStream_t st) {
-  if (M <= 8) return launch<1, GATED>(A, lda, W, ldw, out, M, N, K, slices, kblocks_per_slice, st);
-  if (M <= 16) return launch<2, GATED>(A, lda, W, ldw, out, M, N, K, slices, kblocks_per_slice, st);
-  if (M <= 32) return launch<4, GATED>(A, lda, W, ldw, out, M, N, K, slices, kblocks_per_slice, st);
-  return launch<8, GATED>(A, lda, W, ldw, out, M, N, K, slices, kblocks_per_slice, st);
+  if (GATED && M <= 8 && slices == 1) {
+    // one block an SM when that gives every SM the same share of the weights (see Tile)
+    const int per_sm = ((N + 15) / 16 + 147) / 148;  // 16-row tiles an SM
+    if (per_sm == 5) return launch<1, GATED, 5>(A, lda, W, ldw, out, M, N, K, slices, kblocks_per_slice, st);
+    if (per_sm == 6) return launch<1, GATED, 6>(A, lda, W, ldw, out, M, N, K, slices, kblocks_per_slice, st);
+    if (per_sm == 7) return launch<1, GATED, 7>(A, lda, W, ldw, out, M, N, K, slices, kblocks_per_slice, st);
+    if (per_sm == 8) return launch<1, GATED, 8>(A, lda, W, ldw, out, M, N, K, slices, kblocks_per_slice, st);
+  }
+  if (M <= 8) return launch<1, GATED, 4>(A, lda, W, ldw, out, M, N, K, slices, kblocks_per_slice, st);
+  if (M <= 16) return launch<2, GATED, 4>(A, lda, W, ldw, out, M, N, K, slices, kblocks_per_slice, st);
+  if (M <= 32) return launch<4, GATED, 4>(A, lda, W, ldw, out, M, N, K, slices, kblocks_per_slice, st);
+  return launch<8, GATED, 4>(A, lda, W, ldw, out, M, N, K, slices, kblocks_per_slice, st);
 }
 
 }  // namespace
