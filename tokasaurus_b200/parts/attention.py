@@ -28,10 +28,20 @@ from tokasaurus_b200.parts.base import LazyNorm, Mixer, PagedCacheNeed, Position
 MIN_SPLIT_KEYS = 128  # no work item of the split-key kernel is cut finer than this
 QUERY_TILE = 64  # queries per block of the tiled mma.sync kernel
 QUERY_TILE_TC = 128  # queries per block of the tcgen05 kernel
-DECODE_BLOCK_SLOTS = 148 * 3  # blocks of the split-key kernel that a B200 holds at once (head size 64)
+DECODE_BLOCK_SLOTS = 148 * 3  # blocks of the split-key kernel that a B200 holds at once (head sizes up to 64)
 
 
-def split_keys_evenly(span: np.ndarray, blocks_per_item: int) -> tuple[np.ndarray, np.ndarray]:
+def decode_block_slots(head_dim: int) -> int:
+    """Blocks of the split-key kernel that the GPU holds at once: what of an SM's 227 KiB of shared memory the
+    kernel's stages take (two tiles of 64 rows of head_dim * 2 + 16 bytes a stage; three stages, two when three
+    pass 110 KiB), at most three blocks an SM."""
+    stage = 2 * 64 * (head_dim * 2 + 16)
+    stages = 3 if 3 * stage <= 110 * 1024 else 2
+    return 148 * max(1, min(3, (227 * 1024) // (stages * stage + 1024)))
+
+
+def split_keys_evenly(span: np.ndarray, blocks_per_item: int, slots: int = DECODE_BLOCK_SLOTS
+                      ) -> tuple[np.ndarray, np.ndarray]:
     """How many work items each single-token request gets and how many keys each item holds (a multiple of
     64, the kernel's tile): requests are cut evenly, in proportion to their keys, so that the step's items fill
     one wave of blocks.  A request shorter than an item's share stays whole (such items may take the count over
@@ -39,7 +49,7 @@ def split_keys_evenly(span: np.ndarray, blocks_per_item: int) -> tuple[np.ndarra
     full beats any finer cut into a second wave (batches 8 and 16: 0.86 of a wave), but a wave less than 0.7
     full loses to 1.15 waves of items half the size (batch 32), and requests that cannot be cut to fit
     (batch 64: 1.15 waves of whole requests) are best left whole."""
-    max_items = max(1, DECODE_BLOCK_SLOTS // max(1, blocks_per_item))
+    max_items = max(1, slots // max(1, blocks_per_item))
     if span.shape[0] == 0:
         return np.zeros((0,), dtype=np.int64), np.zeros((0,), dtype=np.int64)
     total = int(span.sum())
@@ -59,7 +69,7 @@ def split_keys_evenly(span: np.ndarray, blocks_per_item: int) -> tuple[np.ndarra
 
 
 def plan_attention(host, window: int | None, capacity: dict | None = None, blocks_per_item: int = 8,
-                   query_tile: int = QUERY_TILE) -> dict[str, np.ndarray]:
+                   query_tile: int = QUERY_TILE, slots: int = DECODE_BLOCK_SLOTS) -> dict[str, np.ndarray]:
     """Work items for one step: (request row, first key, keys) triples for requests with one token,
     (request row, first query) pairs for ``query_tile``-query tiles of longer portions.  ``blocks_per_item``:
     blocks the split-key kernel launches per item (kv heads x head tiles)."""
@@ -69,7 +79,7 @@ def plan_attention(host, window: int | None, capacity: dict | None = None, block
     span = kv_len[dec_seqs]
     if window:
         span = np.minimum(span, window)
-    n_splits, split_size = split_keys_evenly(span, blocks_per_item)
+    n_splits, split_size = split_keys_evenly(span, blocks_per_item, slots)
     dec_start = np.concatenate([[0], np.cumsum(n_splits)])
     n_items = int(dec_start[-1])
     item_seq = np.repeat(dec_seqs, n_splits)
@@ -98,7 +108,7 @@ def plan_attention(host, window: int | None, capacity: dict | None = None, block
         rows = np.asarray(rows, dtype=np.int64)
         r_kv = np.asarray(host.positions, dtype=np.int64)[rows] + 1
         r_span = np.minimum(r_kv, window) if window else r_kv
-        r_splits, r_size = split_keys_evenly(r_span, blocks_per_item)
+        r_splits, r_size = split_keys_evenly(r_span, blocks_per_item, slots)
         r_start = np.concatenate([[0], np.cumsum(r_splits)])
         n_row_items, n_rows = int(r_start[-1]), int(rows.shape[0])
         r_item = np.repeat(np.arange(n_rows), r_splits)
@@ -171,7 +181,7 @@ class PagedAttention(Mixer):
     def plan_key(self):
         if self.dtype != torch.bfloat16:
             return None
-        return ("paged_attention", self.window, self._blocks_per_item(), self._query_tile())
+        return ("paged_attention", self.window, self._blocks_per_item(), self._query_tile(), self.head_dim)
 
     def _query_tile(self) -> int:
         return QUERY_TILE_TC if ops.can_use_attn_prefill_tc(self.head_dim) else QUERY_TILE
@@ -180,12 +190,13 @@ class PagedAttention(Mixer):
         return self.n_kv_heads * ((self.n_heads // self.n_kv_heads + 15) // 16)
 
     def plan(self, host, capacity=None):
-        return plan_attention(host, self.window, capacity, self._blocks_per_item(), self._query_tile())
+        return plan_attention(host, self.window, capacity, self._blocks_per_item(), self._query_tile(),
+                              decode_block_slots(self.head_dim))
 
     def plan_capacity(self, n_requests: int) -> dict:
         """The most work items ``plan`` can make for a step of ``n_requests`` single-token requests, whatever
         their contexts: each request gets at most (its keys // the item size) items, at least one."""
-        wave = max(1, DECODE_BLOCK_SLOTS // max(1, self._blocks_per_item()))
+        wave = max(1, decode_block_slots(self.head_dim) // max(1, self._blocks_per_item()))
         return dict(items=n_requests + wave + wave // 4 + 1, dec=n_requests, tiles=0)
 
     def pad_plan(self, plan: dict, capacity: dict) -> dict:
