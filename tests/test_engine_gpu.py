@@ -174,7 +174,10 @@ def test_cuda_graph_decode_equals_eager(tiny_model_dirs, dtype):
     sp = [SamplingParams(temperature=t, seed=3) for t in (0.0, 0.8, 0.0, 1.2, 0.0)]
     outs = {}
     for graphs in (False, True):
-        eng = make_engine(d, dtype=dtype, page_size=8, use_cudagraphs=graphs, cudagraph_step=4, cudagraph_max_size=8)
+        # prompt steps launched kernel by kernel in both runs (their graphs have tests of their own): with the same
+        # kernels on the same shapes the two runs agree bit for bit, so sampled tokens cannot part ways
+        eng = make_engine(d, dtype=dtype, page_size=8, use_cudagraphs=graphs, cudagraph_step=4, cudagraph_max_size=8,
+                          graph_max_tokens=0)
         outs[graphs] = eng.generate(prompts, sp, max_num_tokens=40, ignore_eos=True)
         if graphs:
             assert eng.graphs is not None and len(eng.graphs.graphs) >= 1
@@ -237,3 +240,44 @@ def test_run_ahead_with_stop_tokens_under_sampling(tiny_model_dirs):
     for a, b, r, st in zip(outs[False], outs[True], ref, stops):
         assert a.completion_ids == b.completion_ids and a.finish_reason == b.finish_reason == "stop"
         assert a.completion_ids == r.completion_ids[: r.completion_ids.index(st[0]) + 1]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_graphs_of_steps_with_prompt_portions_equal_eager(tiny_model_dirs, dtype):
+    """Steps that mix prompt portions (cut by a small token budget) with decoded tokens, replayed from CUDA graphs
+    of their padded shape, against the same steps launched kernel by kernel; arrivals while others decode,
+    requests ending at different times.  float32: the same tokens and log-probabilities (its products add in the
+    same order whatever the padding).  bfloat16: library products pick their kernel by the padded row count, so
+    the runs agree to rounding; greedy tokens of both must be (nearly) the best under the plain model."""
+    from tokasaurus_b200 import SamplingParams
+
+    d = tiny_model_dirs[1]
+    prompts = [cuttings.random_tokens(n, 509, 11 * n + 2) for n in (7, 30, 64, 3, 12, 45, 2)]
+    temps = (0.0, 0.8, 0.0, 1.2, 0.0, 0.6, 0.0) if dtype == "float32" else (0.0,) * 7
+    sp = [SamplingParams(temperature=t, seed=5) for t in temps]
+    limits = [9, 25, 14, 3, 30, 1, 18]
+    outs = {}
+    for max_tokens in (0, 1024):
+        eng = make_engine(d, dtype=dtype, page_size=8, max_tokens_per_forward=20, cudagraph_step=4, cudagraph_max_size=8,
+                          graph_max_tokens=max_tokens)
+        ids = [eng.add_request(p, s, max_num_tokens=m, ignore_eos=True) for p, s, m in zip(prompts[:4], sp, limits)]
+        done = []
+        for _ in range(5):
+            done += eng.step()
+        ids += [eng.add_request(p, s, max_num_tokens=m, ignore_eos=True)
+                for p, s, m in zip(prompts[4:], sp[4:], limits[4:])]
+        done += eng.run_until_done()
+        by_id = {o.id: o for o in done}
+        outs[max_tokens] = [by_id[i] for i in ids]
+        assert not eng.runner.cache.requests and not eng.has_work()
+        general = [k for k in eng.graphs.graphs if k[0] == "general"]
+        assert bool(general) == bool(max_tokens)
+    if dtype == "float32":
+        for a, b, m in zip(outs[0], outs[1024], limits):
+            assert a.completion_ids == b.completion_ids and len(a.completion_ids) == m
+            np.testing.assert_allclose(a.logprobs, b.logprobs, atol=1e-5)
+    else:
+        plain = PlainLlama(d, torch.float64)
+        for mode in (0, 1024):
+            for o, p, m in zip(outs[mode], prompts, limits):
+                assert len(o.completion_ids) == m and near_best(plain, p, o.completion_ids), mode

@@ -146,3 +146,63 @@ def test_trace_run_program(tiny_model_dirs, tmp_path):
     p64 = cuttings.plain_logits(tiny_model_dirs[0], reqs, torch.float64)
     p32 = cuttings.plain_logits(tiny_model_dirs[0], reqs, torch.float32)
     compare(got, p64, p32, "float32")
+
+
+def replay_through_graphs(model_dir, dtype, steps, page_size):
+    """The steps of a cutting, each entry wanting the logits of its last token only (what generation asks of a
+    step), run through the engine's CUDA graphs: decode graphs for steps of single tokens, graphs of the padded
+    shape for steps with portions.  Returns {request: {position: logits}} and how many steps ran as graphs."""
+    from tokasaurus_b200.engine.batch import StepEntry
+    from tokasaurus_b200.engine.engine import Engine
+
+    eng = Engine(model=str(model_dir), dtype=dtype, page_size=page_size, kv_cache_num_tokens=cuttings.max_live_tokens(steps),
+                 max_seqs_per_forward=8, cudagraph_max_size=8, cudagraph_step=4, graph_max_tokens=4096)
+    cache, graphs = eng.runner.cache, eng.graphs
+    lengths, got, n_graph = {}, {}, 0
+    for st in steps:
+        entries = []
+        for e in st["entries"]:
+            if e["id"] not in lengths:
+                cache.admit(e["id"])
+                lengths[e["id"]] = 0
+            cache.ensure_capacity(e["id"], lengths[e["id"]] + len(e["tokens"]))
+            entries.append(StepEntry(e["id"], list(e["tokens"]), lengths[e["id"]], [len(e["tokens"]) - 1]))
+        R = len(entries)
+        extra = dict(temperature=np.zeros(R, dtype=np.float32), stream_key=np.zeros(R, dtype=np.int64),
+                     sample_pos=np.zeros(R, dtype=np.int32), row_slot=np.full(R, -1, dtype=np.int32))
+        prep = None
+        if graphs.usable(entries):
+            prep = graphs.prepare(entries, extra)
+        elif graphs.usable_general(entries):
+            prep = graphs.prepare_general(entries, extra)
+        if prep is not None:
+            graphs.launch(prep)
+            logits = graphs.graphs[prep["key"]]["logits"][:R].float().cpu().numpy()
+            n_graph += 1
+        else:
+            logits = eng.runner.step(entries).float().cpu().numpy()
+        eng.runner.check_status()
+        for en, row in zip(entries, logits):
+            lengths[en.request] += en.n_tokens
+            got.setdefault(en.request, {})[lengths[en.request] - 1] = row
+        for rid in st["end"]:
+            cache.free(rid)
+            del lengths[rid]
+        cache.check()
+    assert not cache.requests
+    return got, n_graph
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("cut", ["prefix_then_single", "changing_portions", "mixed"])
+@pytest.mark.parametrize("cfg_index", [0, 1])
+def test_cuttings_through_step_graphs_match_plain(tiny_model_dirs, plain, cfg_index, cut, dtype):
+    reqs, p64, p32 = plain[cfg_index]
+    steps = CUTS[cut](reqs)
+    got, n_graph = replay_through_graphs(tiny_model_dirs[cfg_index], dtype, steps, TINY_WEIGHTS[cfg_index]["page_size"])
+    assert n_graph > len(steps) // 2
+    for rid, ref in p64.items():
+        tol = cuttings.tolerance(dtype, ref, p32[rid])
+        for pos, row in got[rid].items():
+            err = float(np.abs(row - ref[pos]).max())
+            assert err <= tol, f"{dtype} {cut}: request {rid} position {pos}: error {err:.3g}, tolerance {tol:.3g}"

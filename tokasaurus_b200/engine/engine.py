@@ -39,11 +39,13 @@ class _InFlight:
 class Engine:
     def __init__(self, model: str | None = None, config: EngineConfig | None = None,
                  config_dict: dict[str, Any] | None = None, seed: int = 0, kv_reserve_fraction: float = 1.0,
-                 run_ahead: bool = True, **options: Any):
+                 run_ahead: bool = True, graph_max_tokens: int = 1024, **options: Any):
         """``model``: folder with config.json and model.safetensors.  ``options``: fields of
         ``EngineConfig`` (the reference's option names).  ``config_dict`` with
         ``random_weights=<seed>`` builds a model without a folder.  ``run_ahead``: launch the next decode step
-        before the results of the current one have been read (see ``step``)."""
+        before the results of the current one have been read (see ``step``).  ``graph_max_tokens``: steps with prompt
+        portions of up to this many tokens are replayed from CUDA graphs of their padded shape, like decode steps
+        (0: only decode steps are)."""
         cfg = config or EngineConfig()
         if model is not None:
             cfg.model = model
@@ -66,7 +68,8 @@ class Engine:
         if cfg.use_cudagraphs and self.runner.rt.device.type == "cuda":
             from tokasaurus_b200.engine.graphs import DecodeGraphs
 
-            self.graphs = DecodeGraphs(self.runner, self.sampler, cfg.cudagraph_max_size, cfg.cudagraph_step)
+            self.graphs = DecodeGraphs(self.runner, self.sampler, cfg.cudagraph_max_size, cfg.cudagraph_step,
+                                       graph_max_tokens)
         self._auto_id = 0
         self.run_ahead = run_ahead
         self._inflight: _InFlight | None = None
@@ -126,8 +129,9 @@ class Engine:
         self._inflight = self._launch_following(cur) if self.run_ahead else None
         return self._finish(cur)
 
-    def _launch(self, plan: StepPlan, entries: list[StepEntry], extra: dict[str, np.ndarray]) -> _InFlight:
-        padded = self.graphs.launch(self.graphs.prepare(entries, extra))
+    def _launch(self, plan: StepPlan, entries: list[StepEntry], extra: dict[str, np.ndarray],
+                prep: dict | None = None) -> _InFlight:
+        padded = self.graphs.launch(prep if prep is not None else self.graphs.prepare(entries, extra))
         slot = self._next_slot
         self._next_slot ^= 1
         self.sampler.start_read(padded, slot, self.runner.stager.status)
@@ -145,9 +149,15 @@ class Engine:
             entries.append(StepEntry(p.seq.id, toks, p.start, [p.n_tokens - 1] if p.samples else []))
         extra = self._sampling_arrays(plan)
         wants_topk = any(p.seq.request.topk_logprobs for p in plan.portions if p.samples)
-        if self.graphs is not None and not wants_topk and self.graphs.usable(entries):
-            self._inflight = self._launch(plan, entries, extra)
-            return None
+        if self.graphs is not None and not wants_topk:
+            if self.graphs.usable(entries):
+                self._inflight = self._launch(plan, entries, extra)
+                return None
+            if self.graphs.usable_general(entries):
+                prep = self.graphs.prepare_general(entries, extra)
+                if prep is not None:
+                    self._inflight = self._launch(plan, entries, extra, prep)
+                    return None
         logits = self.runner.step(entries, extra)
         R = logits.shape[0]
         ids: list[int] = []
@@ -173,13 +183,20 @@ class Engine:
         ids, lps, status = self.sampler.finish_read(cur.rows, cur.slot)
         self.runner.check_status(status)
         running = set(map(id, self.scheduler.decoding)) | set(map(id, self.scheduler.prefilling))
-        keep = [i for i, p in enumerate(cur.plan.portions) if id(p.seq) in running]
-        plan = cur.plan
-        if len(keep) != len(plan.portions):
-            plan = StepPlan([plan.portions[i] for i in keep], plan.bumped)
-        ids, lps = [ids[i] for i in keep], [lps[i] for i in keep]
+        portions, kept_ids, kept_lps = [], [], []
+        k = 0  # the k-th portion that samples owns the k-th row of the results
+        for p in cur.plan.portions:
+            alive = id(p.seq) in running
+            if alive:
+                portions.append(p)
+            if p.samples:
+                if alive:
+                    kept_ids.append(ids[k])
+                    kept_lps.append(lps[k])
+                k += 1
+        plan = cur.plan if len(portions) == len(cur.plan.portions) else StepPlan(portions, cur.plan.bumped)
         self.last_step_bytes = dict(h2d=cur.h2d, d2h=self.sampler.bytes_last_read)
-        return self.scheduler.complete(plan, ids, lps if self.config.enable_chosen_logprobs else None, None)
+        return self.scheduler.complete(plan, kept_ids, kept_lps if self.config.enable_chosen_logprobs else None, None)
 
     def _launch_following(self, cur: _InFlight) -> _InFlight | None:
         """Launch the decode step after ``cur`` before ``cur``'s results are known: every request of ``cur`` that

@@ -28,6 +28,10 @@ def _pow2_at_least(n: int, floor: int) -> int:
     return c
 
 
+# padded token counts of steps that bring prompt portions (a step is padded up to the next of these)
+TOKEN_BUCKETS = (16, 32, 48, 64, 96, 128, 192, 256, 384, 512, 768, 1024, 1536, 2048, 3072, 4096, 6144, 8192)
+
+
 def _pad(a: np.ndarray, n: int, fill: int = 0) -> np.ndarray:
     out = np.full((n,), fill, dtype=a.dtype)
     out[: a.shape[0]] = a
@@ -35,10 +39,11 @@ def _pad(a: np.ndarray, n: int, fill: int = 0) -> np.ndarray:
 
 
 class DecodeGraphs:
-    def __init__(self, runner, sampler, max_size: int, step: int):
+    def __init__(self, runner, sampler, max_size: int, step: int, max_tokens: int = 0):
         self.runner = runner
         self.sampler = sampler
         self.max_size = max_size
+        self.max_tokens = max_tokens  # steps with prompt portions of up to this many tokens run as graphs too (0: none)
         self.sizes = sorted({s for s in (1, 2, 4, 8) if s <= max_size} | set(range(step, max_size + 1, step)))
         self.graphs: dict[tuple, dict] = {}
         self.launches_per_replay = 0
@@ -47,6 +52,49 @@ class DecodeGraphs:
     def usable(self, entries) -> bool:
         return (bool(self.sizes) and len(entries) <= self.sizes[-1] and self.runner.model.graph_safe
                 and all(e.n_tokens == 1 and list(e.want) == [0] for e in entries))
+
+    def usable_general(self, entries) -> bool:
+        """A step with prompt portions that is small enough for a graph of its padded shape: what it costs on
+        the host to launch its kernels one by one is then more than the GPU needs for them."""
+        if not self.sizes or self.max_tokens <= 0 or not self.runner.model.graph_safe:
+            return False
+        return (len(entries) <= self.sizes[-1] and sum(e.n_tokens for e in entries) <= min(self.max_tokens, TOKEN_BUCKETS[-1])
+                and all(len(e.want) <= 1 for e in entries))
+
+    def prepare_general(self, entries: list[StepEntry], extra: dict[str, np.ndarray]) -> dict | None:
+        """``prepare`` for a step with prompt portions: tokens padded to a bucket (padding tokens carry request
+        row -1), requests and wanted rows to a batch size, every work list to its bound for that shape.  None if
+        a work list is longer than its bound (the step then runs without a graph)."""
+        runner = self.runner
+        host = build_host_batch(entries, runner.cache)
+        T, S, R = host.token_ids.shape[0], len(entries), host.logit_rows.shape[0]
+        tp = next(b for b in TOKEN_BUCKETS if b >= T)
+        sp = next(s for s in self.sizes if s >= S)
+        page_caps = [max(g.allocator.num_pages, pg.shape[0], 1) for g, pg in zip(runner.cache.groups, host.table_pages)]
+        planners = runner.model.planners()
+        raw = {key: m.plan(host) for key, m in planners.items()}
+        caps = {}
+        for key, p in raw.items():
+            if not hasattr(planners[key], "plan_capacity_general"):
+                return None
+            c = planners[key].plan_capacity_general(tp, sp, sp, p["counts"])
+            n = p["counts"]
+            if int(n[0]) > c["items"] or int(n[1]) > c["dec"] or int(n[2]) > c["tiles"] or int(n[3]) > c["row_items"] \
+                    or int(n[4]) > c["rows"]:
+                return None
+            caps[key] = c
+        key = ("general", tp, sp, tuple(page_caps), tuple(sorted((str(k), tuple(sorted(c.items()))) for k, c in caps.items())))
+        plans = {k: planners[k].pad_plan(p, caps[k]) for k, p in raw.items()}
+        last = [int(ip[-1]) for ip in host.table_indptr]
+        padded = HostBatch(
+            _pad(host.token_ids, tp), _pad(host.positions, tp), _pad(host.token_seq, tp, -1), _pad(host.seq_slot, sp),
+            _pad(host.seq_q_start, sp), _pad(host.seq_q_len, sp), _pad(host.seq_kv_len, sp), _pad(host.logit_rows, sp),
+            [_pad(ip, sp + 1, l) for ip, l in zip(host.table_indptr, last)],
+            [_pad(pg, cap) for pg, cap in zip(host.table_pages, page_caps)], host.requests)
+        ex = dict(temperature=_pad(extra["temperature"], sp), stream_key=_pad(extra["stream_key"], sp),
+                  sample_pos=_pad(extra["sample_pos"], sp), row_slot=_pad(extra["row_slot"], sp, -1))
+        return dict(key=key, bp=sp, padded=padded, plans=plans, caps=caps, ex=ex,
+                    signature=[(e.request, e.start) for e in entries])
 
     def _padded(self, host: HostBatch, bp: int, page_caps: list[int]) -> HostBatch:
         last = [int(ip[-1]) for ip in host.table_indptr]

@@ -199,6 +199,17 @@ class PagedAttention(Mixer):
         wave = max(1, decode_block_slots(self.head_dim) // max(1, self._blocks_per_item()))
         return dict(items=n_requests + wave + wave // 4 + 1, dec=n_requests, tiles=0)
 
+    def plan_capacity_general(self, n_tokens: int, n_requests: int, n_rows: int, counts) -> dict:
+        """Capacities of every work list for a step of up to ``n_tokens`` tokens in ``n_requests`` requests with
+        ``n_rows`` wanted rows; a list the step does not use at all (``counts`` are the plan's own) gets 0, so that
+        its kernel is not launched."""
+        wave = max(1, decode_block_slots(self.head_dim) // max(1, self._blocks_per_item()))
+        spare = wave + wave // 4 + 1
+        has_dec, has_tiles, has_rows = int(counts[1]) > 0, int(counts[2]) > 0, int(counts[4]) > 0
+        return dict(items=(n_requests + spare) if has_dec else 0, dec=n_requests if has_dec else 0,
+                    tiles=(n_tokens // self._query_tile() + n_requests) if has_tiles else 0,
+                    row_items=(n_rows + spare) if has_rows else 0, rows=n_rows if has_rows else 0)
+
     def pad_plan(self, plan: dict, capacity: dict) -> dict:
         """The same plan with its arrays at the fixed sizes of a CUDA graph."""
         def padded(x, n):
@@ -212,6 +223,13 @@ class PagedAttention(Mixer):
         out["dec_seqs"] = padded(plan["dec_seqs"], capacity.get("dec", 0))
         out["dec_item_start"] = padded(plan["dec_item_start"], capacity.get("dec", 0) + 1)
         out["tiles"] = padded(plan["tiles"], 2 * capacity.get("tiles", 0))
+        if "row_items" in plan:
+            ri, rows = capacity.get("row_items", 0), capacity.get("rows", 0)
+            out["row_items"] = padded(plan["row_items"], 3 * ri)
+            out["row_item_entry"] = padded(plan["row_item_entry"], ri)
+            out["row_item_start"] = padded(plan["row_item_start"], rows + 1)
+            for name in ("row_token", "row_kv_len", "row_seq", "row_index"):
+                out[name] = padded(plan[name], rows)
         return out
 
     # --- one step ---
@@ -276,7 +294,9 @@ class PagedAttention(Mixer):
         if plan is not None and out_rows is not None and out_rows is ctx.logit_rows and "row_items" in plan:
             # only some rows are wanted (the last block of a step): one split-key query per wanted row
             counts = ctx.host_plans[self.plan_key()]["counts"]
-            n_items, n_rows = int(counts[3]), int(counts[4])
+            caps = ctx.plan_caps.get(self.plan_key()) if ctx.plan_caps else None
+            n_items = caps["row_items"] if caps else int(counts[3])
+            n_rows = caps["rows"] if caps else int(counts[4])
             attn = torch.empty((n_rows, nh * hd), dtype=h.dtype, device=h.device)
             row_indptr = tables.indptr.index_select(0, plan["row_seq"])
             c = plan["counts"]
@@ -284,7 +304,7 @@ class PagedAttention(Mixer):
                                 tables.page_ids, plan["row_items"], c[3:4], n_items, plan["row_index"],
                                 plan["row_item_start"], c[4:5], n_rows, attn, nh, nkv, hd, cache.page_size,
                                 self.scale, self.window, out_row_of=plan["row_index"],
-                                item_entry=plan["row_item_entry"] if n_items == n_rows else None)
+                                item_entry=plan["row_item_entry"])
             return project(attn, self.w_o)
         if plan is None or out_rows is not None:
             # float32, or only some rows are wanted: the FP32-pipe kernel, one warp per (row, head)
