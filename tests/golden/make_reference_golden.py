@@ -1,7 +1,7 @@
 """Compare the plain implementation (tests/plain_llama.py) ONCE with the reference's own model
 code on a tiny random model, on the CPU, and store the reference's logits as a golden file.
 
-Run by hand:  python tests/golden/make_reference_golden.py [path of the tokasaurus checkout]
+Run by hand:  python tests/golden/make_reference_golden.py <path of the tokasaurus checkout>
 
 What runs of the reference: ``tokasaurus.model.llama.LlamaForCausalLM`` in float32 (its RMSNorm,
 projections, rotary tables and application, cache append indexing, residual order, last-layer row
@@ -31,7 +31,9 @@ HERE = Path(__file__).resolve().parent
 ROOT = HERE.parent.parent
 sys.path.insert(0, str(ROOT))
 sys.path.insert(0, str(HERE.parent))
-REF = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+if len(sys.argv) < 2:
+    sys.exit("usage: make_reference_golden.py <folder of the reference's source tree>")
+REF = sys.argv[1]
 sys.path.insert(0, REF)
 
 
