@@ -1,17 +1,18 @@
 // bfloat16 attention over the paged cache on the tensor cores (mma.sync m16n8k16, float32
 // accumulation; scores, softmax and the running rescale are float32).
 //
-//   attn_decode_mma:  one query token per request, keys split into chunks
-//                     (work items (request, first key, keys) built on the host), partial results merged by attn_decode_merge.
-//                     The 16 rows of the MMA tile are the query heads that share one key/value
-//                     head, so every key and value is read once for the whole group.
+//   attn_decode_mma:  one query token per request, keys split into chunks (work items (request, first key,
+//                     keys) built on the host); the last block of a request to finish merges the partial
+//                     results (an arrival counter; nobody waits), or attn_decode_merge does for callers
+//                     without counters.  The 16 rows of the MMA tile are the query heads that share one
+//                     key/value head, so every key and value is read once for the whole group.
 //   attn_prefill_mma: portions of prompts; a block owns 64 consecutive query tokens of one head
 //                     (16 per warp) and walks the keys they may see.
 //
 // Compile with -DTKB_HD=<head size> (multiple of 16, at most 256).
 //
 // Keys and values reach shared memory with 16-byte cp.async copies, page by page through the
-// request's block table, double buffered; rows outside the request's keys are zero-filled, so
+// request's block table, two or three stages deep; rows outside the request's keys are zero-filled, so
 // nothing that an earlier owner of a page left behind can reach a sum.  Shared-memory rows are padded
 // by 16 bytes, which keeps ldmatrix free of bank conflicts for every head size that is a
 // multiple of 16.
@@ -35,9 +36,10 @@ constexpr int CPR = HD / 8;           // 16-byte chunks per row
 constexpr int TILE_B = KT * ROWB;     // bytes of one K or V tile
 constexpr int STAGE_B = 2 * TILE_B;   // K tile then V tile
 constexpr int SMEM_B = 2 * STAGE_B;   // two stages (tiled kernel for portions)
-// The split-key kernel keeps as many tiles in flight as fit: with 256 keys a split, four stages put a whole
-// split on its way at once, which is what a memory-bound kernel with few blocks per SM needs.
-constexpr int DSTAGES = 3 * STAGE_B <= 110 * 1024 ? 3 : 2;  // three stages leave room for three blocks an SM at head size 64
+// The split-key kernel: three stages where they leave room for two or three blocks an SM (three at head sizes
+// to 80, two to 128), else two.  Four stages at head size 64 were measured slower: the blocks of a step then
+// no longer fit the SMs all at once.
+constexpr int DSTAGES = 3 * STAGE_B <= 110 * 1024 ? 3 : 2;
 constexpr int DEC_SMEM_B = DSTAGES * STAGE_B;
 constexpr int KSTEPS = HD / 16;       // k-steps of Q.K^T
 constexpr int DTILES = HD / 8;        // n-tiles of P.V
