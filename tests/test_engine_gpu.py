@@ -281,3 +281,48 @@ def test_graphs_of_steps_with_prompt_portions_equal_eager(tiny_model_dirs, dtype
         for mode in (0, 1024):
             for o, p, m in zip(outs[mode], prompts, limits):
                 assert len(o.completion_ids) == m and near_best(plain, p, o.completion_ids), mode
+
+
+def test_everything_at_once_equals_the_plain_path(tiny_model_dirs):
+    """Twenty requests of random lengths arriving over time into a pool so tight that requests are pushed out,
+    some ending on stop tokens, some sampled with a temperature: with CUDA graphs for decode steps and for steps
+    with prompt portions and with the run-ahead, the engine gives, in float32, exactly what it gives with all of
+    that switched off."""
+    from tokasaurus_b200 import SamplingParams
+
+    d = tiny_model_dirs[1]
+    rng = np.random.default_rng(4)
+    prompts = [cuttings.random_tokens(int(n), 509, 1000 + i) for i, n in enumerate(rng.integers(1, 90, size=20))]
+    limits = [int(x) for x in rng.integers(1, 40, size=20)]
+    temps = [float(t) for t in rng.choice([0.0, 0.0, 0.7, 1.3], size=20)]
+    arrive = sorted(int(x) for x in rng.integers(0, 60, size=20))
+    outs = {}
+    stops = None
+    for fancy in (False, True):
+        eng = make_engine(d, page_size=8, kv_cache_num_tokens=256, max_tokens_per_forward=48, max_seqs_per_forward=6,
+                          kv_reserve_fraction=0.0, use_cudagraphs=fancy, cudagraph_step=2, cudagraph_max_size=6,
+                          run_ahead=fancy, graph_max_tokens=1024 if fancy else 0)
+        if stops is None:
+            # stop tokens taken from an unconstrained run of every fourth request, so that they are really met
+            probe = make_engine(d, page_size=8, kv_cache_num_tokens=4096, use_cudagraphs=False)
+            full = probe.generate(prompts, [SamplingParams(temperature=t, seed=9) for t in temps], max_num_tokens=40,
+                                  ignore_eos=True)
+            stops = [[o.completion_ids[min(len(o.completion_ids) - 1, 5)]] if i % 4 == 0 else [] for i, o in enumerate(full)]
+        ids, done, step, nxt = [], [], 0, 0
+        while nxt < len(prompts) or eng.has_work():
+            while nxt < len(prompts) and arrive[nxt] <= step:
+                ids.append(eng.add_request(prompts[nxt], SamplingParams(temperature=temps[nxt], seed=9),
+                                           max_num_tokens=limits[nxt], ignore_eos=True, stop_token_ids=stops[nxt]))
+                nxt += 1
+            done += eng.step()
+            step += 1
+            assert step < 5000
+        by_id = {o.id: o for o in done}
+        outs[fancy] = [by_id[i] for i in ids]
+        assert not eng.runner.cache.requests and not eng.has_work()
+        if fancy:
+            assert eng.scheduler.stats["bumps"] > 0 and any(k[0] == "general" for k in eng.graphs.graphs)
+    for a, b in zip(outs[False], outs[True]):
+        assert a.completion_ids == b.completion_ids and a.finish_reason == b.finish_reason
+        np.testing.assert_allclose(a.logprobs, b.logprobs, atol=1e-5)
+    assert any(o.finish_reason == "stop" for o in outs[True]) and any(o.finish_reason == "length" for o in outs[True])
