@@ -8,7 +8,8 @@ Prints ONE JSON line.  ``value``: decoded tokens a second at batch 8, each reque
 (each step: the host builds the batch, one pinned copy to the device, the model, the sampler; the
 sampled tokens stay on the device).  ``e2e``: the same through the Python entry point
 (``Engine.step``: scheduler, pinned host-to-device copy of the step's inputs, model, sampler,
-device-to-host read of the sampled tokens), by the wall clock.  ``prefill``: one 2,048-token
+device-to-host read of the sampled tokens; the engine launches step t+1 before it reads step t, so
+each call reads the step before the one it launches), by the wall clock.  ``prefill``: one 2,048-token
 prompt in one step.  ``roofline``: bytes a decode step has to read (every weight it uses once, and
 the cache of the live requests) over its time, against the measured copy bandwidth.  ``points``:
 decode at batch 1 and 64.  The weights (2.5 GB) are larger than the L2 cache (126 MB), so every
