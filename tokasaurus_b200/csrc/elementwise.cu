@@ -77,10 +77,14 @@ __device__ __forceinline__ void store4(__nv_bfloat16* p, float4 v) {
   *reinterpret_cast<uint2*>(p) = u;
 }
 
-template <typename T>
-__global__ void add_rmsnorm_kernel(float* __restrict__ x, const T* __restrict__ delta,
-                                   const float* __restrict__ partials, int n_partials, long long partial_stride,
-                                   const float* __restrict__ w, T* __restrict__ out, float eps, int H) {
+// MODE: 0 no update, 1 update in the activation type, 2 update as float32 slices.  One instantiation a mode,
+// and only two steps' worth of values kept in registers: with many rows (a prompt) what matters is how many
+// rows an SM holds at once, and that is set by the registers a thread takes.
+template <typename T, int MODE, int MAXT>
+__global__ void __launch_bounds__(MAXT, MAXT <= 256 ? 6 : 2)
+add_rmsnorm_kernel(float* __restrict__ x, const T* __restrict__ delta, const float* __restrict__ partials,
+                   int n_partials, long long partial_stride, const float* __restrict__ w, T* __restrict__ out,
+                   float eps, int H) {
   trigger_dependents();
   __shared__ float scratch[33];
   const size_t base = (size_t)blockIdx.x * H;
@@ -88,8 +92,8 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const T* __restrict__ 
   T* orow = out + base;
   float ss = 0.f;
   if ((H & 3) == 0) {
-    // four elements a thread and step; the first four steps' sums stay in registers for the second pass
-    constexpr int KEEP = 4;
+    // four elements a thread and step; the first two steps' sums stay in registers for the second pass
+    constexpr int KEEP = 2;
     const int n4 = H >> 2;
     float4 kept[KEEP], gain[KEEP];
     // the norm's weight is written by no kernel: it is fetched while the kernel ahead still runs
@@ -99,20 +103,20 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const T* __restrict__ 
       if (i4 < n4) gain[k] = load4(w + 4 * i4);
     }
     grid_dependency_wait();
-    // x + update of four elements at 4 * i4, stored back; the update arrives as float32 slices of a split
-    // matrix product (eight loads in flight together, added in slice order) or in the activation type
+    // x + update of four elements at 4 * i4, stored back
     auto updated = [&](int i4) {
       float4 v = load4(xr + 4 * i4);
-      if (partials != nullptr) {
+      if (MODE == 2) {
+        // float32 slices of a split matrix product: four loads in flight together, added in slice order
         float4 d = make_float4(0.f, 0.f, 0.f, 0.f);
         const float* src = partials + base + 4 * i4;
-        for (int p0 = 0; p0 < n_partials; p0 += 8) {
-          float4 q[8];
+        for (int p0 = 0; p0 < n_partials; p0 += 4) {
+          float4 q[4];
 #pragma unroll
-          for (int j = 0; j < 8; j++)
+          for (int j = 0; j < 4; j++)
             q[j] = p0 + j < n_partials ? load4(src + (size_t)(p0 + j) * partial_stride) : make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-          for (int j = 0; j < 8; j++) {
+          for (int j = 0; j < 4; j++) {
             if (p0 + j < n_partials) {
               d.x += q[j].x; d.y += q[j].y; d.z += q[j].z; d.w += q[j].w;
             }
@@ -120,7 +124,7 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const T* __restrict__ 
         }
         v.x += d.x; v.y += d.y; v.z += d.z; v.w += d.w;
         store4(xr + 4 * i4, v);
-      } else if (delta != nullptr) {
+      } else if (MODE == 1) {
         const float4 d = load4(delta + base + 4 * i4);
         v.x += d.x; v.y += d.y; v.z += d.z; v.w += d.w;
         store4(xr + 4 * i4, v);
@@ -151,7 +155,7 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const T* __restrict__ 
     return;
   }
   grid_dependency_wait();
-  if (partials != nullptr) {
+  if (MODE == 2) {
     for (int i = threadIdx.x; i < H; i += blockDim.x) {
       float d = 0.f;
       for (int p = 0; p < n_partials; p++) d += partials[(size_t)p * partial_stride + base + i];
@@ -159,7 +163,7 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const T* __restrict__ 
       xr[i] = v;
       ss += v * v;
     }
-  } else if (delta != nullptr) {
+  } else if (MODE == 1) {
     const T* dr = delta + base;
     for (int i = threadIdx.x; i < H; i += blockDim.x) {
       float v = xr[i] + to_float(dr[i]);
@@ -292,8 +296,19 @@ static int add_rmsnorm_launch(float* x, const void* delta, const float* partials
   }
   // few rows: many threads a row, they hide the latency; many rows: several rows an SM in flight do
   int threads = H >= 8192 || (H >= 2048 && rows < 592) ? 512 : (H >= 512 ? 256 : 128);
-  return launch_pdl(add_rmsnorm_kernel<T>, dim3(rows), dim3(threads), 0, st, x, (const T*)delta, partials, n_partials,
-                    partial_stride, w, (T*)out, eps, H);
+#define TKB_NORM(MODE, MAXT)                                                                                        \
+  return launch_pdl(add_rmsnorm_kernel<T, MODE, MAXT>, dim3(rows), dim3(threads), 0, st, x, (const T*)delta, partials, \
+                    n_partials, partial_stride, w, (T*)out, eps, H)
+  const int mode = partials != nullptr ? 2 : (delta != nullptr ? 1 : 0);
+  if (threads <= 256) {  // up to 256 threads a row: six rows an SM (40 registers a thread)
+    if (mode == 2) TKB_NORM(2, 256);
+    if (mode == 1) TKB_NORM(1, 256);
+    TKB_NORM(0, 256);
+  }
+  if (mode == 2) TKB_NORM(2, 512);
+  if (mode == 1) TKB_NORM(1, 512);
+  TKB_NORM(0, 512);
+#undef TKB_NORM
 }
 // delta: update in the activation type [rows, H], or null.  partials: the update as float32 slices
 // [n_partials][rows, H] spaced partial_stride floats apart, or null.  At most one of the two.
@@ -324,12 +339,14 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, const int* __restrict_
                                      T* __restrict__ kcache, T* __restrict__ vcache, int nh, int nkv, int hd, int rot,
                                      int page_size, int num_pages, int write_cache, int* __restrict__ status) {
   trigger_dependents();
-  grid_dependency_wait();
+  // What the host wrote for the step (positions, request rows, block tables) is there before any kernel of the
+  // step runs: the token's page and its angles are worked out before the wait for the kernel that makes q|k|v.
   extern __shared__ float cs[];  // cos[rot/2], sin[rot/2]
   const int t = blockIdx.x;
   const int s = token_seq[t];
   if (s < 0) return;
   const int pos = positions[t];
+  const int page = write_cache ? page_ids[page_indptr[s] + pos / page_size] : 0;  // on its way during the sin/cos
   const int half = rot >> 1;
   for (int j = threadIdx.x; j < half; j += blockDim.x) {
     float ang = (float)pos * inv_freq[j];
@@ -339,6 +356,7 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, const int* __restrict_
     cs[half + j] = sn;
   }
   __syncthreads();
+  grid_dependency_wait();
 
   T* row = qkv + (size_t)t * (size_t)(nh + 2 * nkv) * hd;
   const bool vec = (half & 3) == 0 && (hd & 3) == 0;  // four elements a thread and step
@@ -366,7 +384,6 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, const int* __restrict_
     }
   }
   if (!write_cache) return;  // a layer call that reads another call's cache writes none of its own
-  const int page = page_ids[page_indptr[s] + pos / page_size];
   if (page < 0 || page >= num_pages) {
     if (threadIdx.x == 0) atomicOr(status, TKB_STATUS_BAD_PAGE);
     return;
