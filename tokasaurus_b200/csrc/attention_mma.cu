@@ -189,10 +189,6 @@ __device__ __forceinline__ void softmax_16keys(float (&s)[2][4], float (&m)[2], 
 }
 
 // ------------------------------------------------------------------------------------------------
-// Decode: blockIdx.x = work item (request row, split), blockIdx.y = kv head * head_tiles + head tile.
-// FUSED: q points at the un-rotated q|k|v rows of the step [tokens, (nh + 2 nkv) * HD]; the kernel rotates
-// q on the fly, and the block that owns the split holding the token's own position rotates this kv
-// head's k, writes it and v into the cache page, and only then reads its tiles.
 // Two neighbouring output elements (d, d + 1) of the merge of splits i0 .. i1-1 of one head.  All loads of up
 // to eight splits are in flight together (one trip to the L2 for the usual case); the sums run in split order,
 // so every caller gets the same bits.
@@ -234,6 +230,11 @@ __device__ __forceinline__ float2 merge_splits(const float* __restrict__ part_o,
   return make_float2(ax / ll, ay / ll);
 }
 
+// ------------------------------------------------------------------------------------------------
+// Decode: blockIdx.x = work item (request row, split), blockIdx.y = kv head * head_tiles + head tile.
+// FUSED: q points at the un-rotated q|k|v rows of the step [tokens, (nh + 2 nkv) * HD]; the kernel rotates
+// q on the fly, and the block that owns the split holding the token's own position rotates this kv
+// head's k, writes it and v into the cache page, and only then reads its tiles.
 template <bool FUSED>
 __global__ void __launch_bounds__(128)
 attn_decode_mma_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ kcache,
