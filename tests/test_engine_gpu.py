@@ -326,3 +326,20 @@ def test_everything_at_once_equals_the_plain_path(tiny_model_dirs):
         assert a.completion_ids == b.completion_ids and a.finish_reason == b.finish_reason
         np.testing.assert_allclose(a.logprobs, b.logprobs, atol=1e-5)
     assert any(o.finish_reason == "stop" for o in outs[True]) and any(o.finish_reason == "length" for o in outs[True])
+
+
+def test_warm_up_records_the_decode_graphs(tiny_model_dirs):
+    """After ``warm_up`` decoding records nothing more, and the tokens are those of an engine that was not warmed."""
+    d = tiny_model_dirs[0]
+    prompts = [cuttings.random_tokens(n, 256, 3 * n) for n in (5, 17, 32)]
+    cold = make_engine(d, graph_max_tokens=0)
+    want = [o.completion_ids for o in cold.generate(prompts, max_num_tokens=12, ignore_eos=True)]
+    eng = make_engine(d, graph_max_tokens=0, max_seqs_per_forward=8, cudagraph_step=4, cudagraph_max_size=8)
+    made = eng.warm_up()
+    assert made == len(eng.graphs.sizes) == len(eng.graphs.graphs) and not eng.runner.cache.requests
+    eng.runner.cache.check()
+    assert [o.completion_ids for o in eng.generate(prompts, max_num_tokens=12, ignore_eos=True)] == want
+    assert len(eng.graphs.graphs) == made
+    with pytest.raises(RuntimeError):
+        eng.add_request(prompts[0], max_num_tokens=4)
+        eng.warm_up()

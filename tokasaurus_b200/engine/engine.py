@@ -225,6 +225,43 @@ class Engine:
         plan = StepPlan(portions)
         return self._launch(plan, entries, self._sampling_arrays(plan))
 
+    def warm_up(self, batch_sizes: Sequence[int] | None = None) -> int:
+        """Record the CUDA graphs of decode steps before the first request needs them, as the reference records
+        its graphs at start-up (tokasaurus/model/utils.py:839-882); else a batch size is recorded (some tens of
+        milliseconds) the first time it comes up.  ``batch_sizes``: padded sizes to record (all that the request
+        slots allow by default).  Returns how many graphs were recorded.  Only with no request in the engine."""
+        if self.graphs is None:
+            return 0
+        if self.has_work() or self.runner.cache.requests:
+            raise RuntimeError("warm_up() wants an engine without requests")
+        cache = self.runner.cache
+        made = 0
+        for bp in (batch_sizes if batch_sizes is not None else self.graphs.sizes):
+            if bp > cache.slots.num_free or any(bp > f for f in cache.num_free_pages()):
+                continue
+            ids = [f"__warm_up_{i}" for i in range(bp)]
+            try:
+                for rid in ids:
+                    cache.admit(rid)
+                    cache.ensure_capacity(rid, 1)
+                entries = [StepEntry(rid, [0], 0, [0]) for rid in ids]
+                if self.graphs.usable(entries):
+                    # rows without a slot: the sampler leaves the last-token table alone
+                    extra = dict(temperature=np.zeros(bp, dtype=np.float32), stream_key=np.zeros(bp, dtype=np.int64),
+                                 sample_pos=np.ones(bp, dtype=np.int32), row_slot=np.full(bp, -1, dtype=np.int32))
+                    prep = self.graphs.prepare(entries, extra)
+                    if prep["key"] not in self.graphs.graphs:
+                        self.graphs.launch(prep)
+                        made += 1
+            finally:
+                for rid in ids:
+                    if rid in cache.requests:
+                        cache.free(rid)
+        if self.runner.rt.device.type == "cuda":
+            torch.cuda.synchronize(self.runner.rt.device)
+        self.runner.check_status()
+        return made
+
     def run_until_done(self) -> list[RequestOutput]:
         done: list[RequestOutput] = []
         while self.has_work():
