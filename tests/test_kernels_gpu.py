@@ -409,32 +409,70 @@ def test_mma_attention_mixed_batch(ops, hd, nh, nkv, ps, window):
     assert torch.equal(got, got3)
 
 
+@pytest.mark.parametrize("hd", [64, 128])
 @pytest.mark.parametrize("nh,nkv,ps,window", [(32, 8, 16, None), (3, 1, 8, None), (5, 5, 5, None), (4, 2, 64, 17),
                                               (6, 3, 4, 300), (8, 2, 16, 128), (4, 2, 256, None), (2, 1, 128, 200)])
-def test_tc_attention_mixed_batch(ops, nh, nkv, ps, window):
-    """The tcgen05 kernel for portions (head size 64): portions that start in the middle of a request, span
-    several 128-query tiles and several 128-key tiles, end on odd lengths, or are two tokens long."""
+def test_tc_attention_mixed_batch(ops, hd, nh, nkv, ps, window):
+    """The tcgen05 kernels for portions (head sizes 64 and 128): portions that start in the middle of a request,
+    span several 128-query tiles and several key tiles, end on odd lengths, or are two tokens long."""
     lens_q = [1, 70, 2, 130, 1, 64, 128, 300, 129]
     lens_kv = [777, 70, 259, 400, 256, 64, 128, 1000, 129]
-    got, want = run_mma_attention(ops, lens_q, lens_kv, nh, nkv, 64, ps, window, seed=nh + ps, tc=True)
+    got, want = run_mma_attention(ops, lens_q, lens_kv, nh, nkv, hd, ps, window, seed=nh + ps, tc=True)
     assert not torch.isnan(got).any()
     torch.testing.assert_close(got, want, rtol=1.6e-2, atol=1.2e-2)
-    got2, _ = run_mma_attention(ops, lens_q, lens_kv, nh, nkv, 64, ps, window, seed=nh + ps, tc=True)
+    got2, _ = run_mma_attention(ops, lens_q, lens_kv, nh, nkv, hd, ps, window, seed=nh + ps, tc=True)
     assert torch.equal(got, got2)
 
 
-def test_tc_attention_never_reads_what_a_page_held_before(ops):
-    got, want = run_mma_attention(ops, [1, 37, 150], [100, 37, 333], 8, 2, 64, 16, None, seed=3, fill=float("nan"), tc=True)
+@pytest.mark.parametrize("hd", [64, 128])
+def test_tc_attention_never_reads_what_a_page_held_before(ops, hd):
+    got, want = run_mma_attention(ops, [1, 37, 150], [100, 37, 333], 8, 2, hd, 16, None, seed=3, fill=float("nan"), tc=True)
     assert not torch.isnan(got).any()
     torch.testing.assert_close(got, want, rtol=1.6e-2, atol=1.2e-2)
+
+
+@pytest.mark.parametrize("hd", [64, 128])
+@pytest.mark.parametrize("slope", [0.02, 0.4, -0.4])
+def test_tc_attention_with_scores_that_grow_along_the_keys(ops, hd, slope):
+    """Keys whose scores rise (or fall) steadily with their position: the running reference of a row's
+    exponentials has to move again and again, late in the row as well as early (the kernel that keeps its output
+    in tensor memory rescales it only then), or never after the first tile."""
+    from types import SimpleNamespace
+    from tokasaurus_b200.parts.attention import plan_attention
+
+    nh, nkv, ps, L, n = 4, 2, 16, 1100, 900
+    kc, vc, indptr, pages, K, V = make_paged(torch.bfloat16, 1, [L], nkv, hd, ps, 90, seed=11)
+    # every key gets a component along e_0 that grows with its position; queries have e_0 = 1 / scale
+    table = pages.cpu().tolist()
+    ramp = (torch.arange(L, dtype=torch.float32) * slope).to(torch.bfloat16)
+    for i in range(L):
+        kc[table[i // ps], :, i % ps, 0] = ramp[i].to(DEV)
+        K[0][i, :, 0] = ramp[i]
+    g = torch.Generator().manual_seed(5)
+    qkv = (torch.randn(n, (nh + 2 * nkv) * hd, generator=g) * 0.5).to(torch.bfloat16)
+    scale = 1 / math.sqrt(hd)
+    qkv[:, 0:nh * hd:hd] = 1.0 / scale
+    plan = plan_attention(SimpleNamespace(seq_q_len=np.asarray([n], dtype=np.int32), seq_kv_len=np.asarray([L], dtype=np.int32)),
+                          None, query_tile=128)
+    out = torch.zeros(n, nh * hd, dtype=torch.bfloat16, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    c = i32(plan["counts"])
+    ops.attn_prefill_tc(qkv.to(DEV), out, kc, vc, i32([0]), i32([n]), i32([L]), indptr, pages, i32(plan["tiles"]), c[2:3],
+                        int(plan["counts"][2]), nh, nkv, hd, ps, scale, None, status)
+    assert int(status.item()) == 0
+    want = torch.zeros(n, nh, hd, dtype=torch.float64)
+    for t in range(n):
+        want[t] = plain_attention(qkv[t, : nh * hd].view(nh, hd), K[0], V[0], L - n + t, scale, None)
+    torch.testing.assert_close(out.view(n, nh, hd).cpu().double(), want, rtol=1.6e-2, atol=1.2e-2)
 
 
 def test_mma_attention_finds_one_far_key(ops):
     """One key among 1,500 stands out for one query head of a single-token request; and the same
     for the last query of a long portion.  The output must be that key's value."""
-    hd, nh, nkv, ps, L = 64, 8, 2, 16, 1500
+    nh, nkv, ps, L = 8, 2, 16, 1500
     for target in (0, 255, 256, 257, 1023, 1499):
-        for lens_q in ([1], [200], [-200]):
+        for lens_q in ([1], [200], [-200], [-200, 128]):
+            hd = lens_q[1] if len(lens_q) > 1 else 64
             tc, lens_q = lens_q[0] < 0, [abs(lens_q[0])]
             kc, vc, indptr, pages, K, V = make_paged(torch.bfloat16, 1, [L], nkv, hd, ps, 100, seed=target)
             from types import SimpleNamespace

@@ -89,7 +89,8 @@ def test_feed_forward_part(dtype):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("nh,nkv,hd,scaled", [(6, 2, 48, True), (4, 4, 16, False), (5, 1, 80, True)])
+@pytest.mark.parametrize("nh,nkv,hd,scaled", [(6, 2, 48, True), (4, 4, 16, False), (5, 1, 80, True), (4, 2, 64, False),
+                                                 (2, 1, 128, True)])
 def test_attention_mixer_part_whole_and_cut(dtype, nh, nkv, hd, scaled):
     """The mixer alone: a whole sequence in one step equals the plain attention block's inner part;
     the same sequence cut into portions and single tokens gives the same rows."""

@@ -11,6 +11,8 @@ def head_dim_modules(head_dim: int) -> list[tuple[str, dict | None]]:
     mods = [("attention_simt.cu", {"TKB_HD": head_dim}), ("attention_mma.cu", {"TKB_HD": head_dim})]
     if head_dim == 64:
         mods.append(("attention_tc.cu", None))  # tcgen05 kernel for prompt portions
+    if head_dim == 128:
+        mods.append(("attention_tc_acc.cu", {"TKB_HD": 128}))  # the same with the output in tensor memory
     return mods
 
 

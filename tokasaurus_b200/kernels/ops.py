@@ -480,11 +480,17 @@ def attn_prefill_mma(qkv: torch.Tensor, out: torch.Tensor, kcache: torch.Tensor,
         _stream()), "attn_prefill_mma")
 
 
-ATTN_PREFILL_TC = True  # portions of prompts on the tcgen05 kernel where it takes the head size
+ATTN_PREFILL_TC = True  # portions of prompts on the tcgen05 kernels where one takes the head size
+# head size -> (source, compile-time constants, entry point).  Head size 64 folds the output tiles in registers
+# (the faster of the two there); head size 128 accumulates the output in tensor memory.
+ATTN_PREFILL_TC_KERNELS = {
+    64: ("attention_tc.cu", {}, "tkb_attn_prefill_tc_bf16"),
+    128: ("attention_tc_acc.cu", {"TKB_HD": 128}, "tkb_attn_prefill_acc_bf16"),
+}
 
 
 def can_use_attn_prefill_tc(head_dim: int) -> bool:
-    return ATTN_PREFILL_TC and head_dim == 64
+    return ATTN_PREFILL_TC and head_dim in ATTN_PREFILL_TC_KERNELS
 
 
 def attn_prefill_tc(qkv: torch.Tensor, out: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor,
@@ -492,12 +498,13 @@ def attn_prefill_tc(qkv: torch.Tensor, out: torch.Tensor, kcache: torch.Tensor, 
                     page_indptr: torch.Tensor, page_ids: torch.Tensor, tiles: torch.Tensor, n_tiles: torch.Tensor,
                     tiles_cap: int, n_heads: int, n_kv_heads: int, head_dim: int, page_size: int, scale: float,
                     window: int | None, status: torch.Tensor) -> None:
-    """bfloat16 causal attention for prompt portions on tcgen05 tensor cores (head size 64): ``tiles`` are
+    """bfloat16 causal attention for prompt portions on tcgen05 tensor cores (head sizes 64 and 128): ``tiles`` are
     (request row, first query of a 128-query tile within the portion) pairs; results go to ``out``
     [T, n_heads*head_dim] at the token rows.  ``status`` collects a wait that ran out."""
     _need_cuda(qkv, out, kcache, vcache, seq_q_start, seq_q_len, seq_kv_len, page_indptr, page_ids, tiles, n_tiles,
                status)
-    _need(head_dim == 64, f"attn_prefill_tc: head size 64 only, got {head_dim}")
+    _need(head_dim in ATTN_PREFILL_TC_KERNELS,
+          f"attn_prefill_tc: head sizes {sorted(ATTN_PREFILL_TC_KERNELS)} only, got {head_dim}")
     _need(qkv.dtype == torch.bfloat16 and kcache.dtype == torch.bfloat16 and out.dtype == torch.bfloat16,
           "attn_prefill_tc: bfloat16 only")
     _need(tuple(kcache.shape[1:]) == (n_kv_heads, page_size, head_dim) and kcache.is_contiguous()
@@ -506,8 +513,8 @@ def attn_prefill_tc(qkv: torch.Tensor, out: torch.Tensor, kcache: torch.Tensor, 
     _need(qkv.stride(1) == 1 and qkv.stride(0) % 8 == 0 and qkv.data_ptr() % 16 == 0 and out.data_ptr() % 16 == 0,
           "attn_prefill_tc: rows of q must start on 16-byte boundaries")
     _need(tiles.numel() >= 2 * tiles_cap, "attn_prefill_tc: plan arrays")
-    lib = _libs.get("attention_tc.cu")
-    _check(_fn(lib, "tkb_attn_prefill_tc_bf16")(
+    source, defines, entry = ATTN_PREFILL_TC_KERNELS[head_dim]
+    _check(_fn(_libs.get(source, **defines), entry)(
         _ptr(qkv), c_int(qkv.stride(0)), _ptr(out), c_int(out.shape[1]), _ptr(kcache), _ptr(vcache),
         c_int(kcache.shape[0]), _ptr(seq_q_start), _ptr(seq_q_len), _ptr(seq_kv_len), _ptr(page_indptr), _ptr(page_ids),
         _ptr(tiles), _ptr(n_tiles), c_int(tiles_cap), c_int(n_heads), c_int(n_kv_heads), c_int(page_size), c_float(scale),
