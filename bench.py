@@ -1,7 +1,7 @@
 """Throughput of the engine on one B200: decoded tokens a second at the sizes of Llama-3.2-1B with
 random weights (the metric and configuration of BASELINE.json's configs[2]).
 
-    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference] [--config 2|3|4]
 
 Prints ONE JSON line.  ``value``: decoded tokens a second at batch 8, each request holding a
 2,048-token prompt in the cache, timed on the device with CUDA events around K decode steps
@@ -41,6 +41,21 @@ def load_baseline_config() -> dict:
         rope_scaling=dict(rope_type="llama3", factor=32.0, low_freq_factor=1.0, high_freq_factor=4.0,
                           original_max_position_embeddings=8192),
         rms_norm_eps=1e-5, tie_word_embeddings=True, max_position_embeddings=131072)
+
+
+def load_other_config(index: int) -> dict:
+    """Sizes of BASELINE.json's configs[3] (Llama-3.2-3B) and configs[4] (Llama-3.1-8B), as config.json keys."""
+    cfg = load_baseline_config()
+    if index == 3:
+        cfg.update(num_hidden_layers=28, hidden_size=3072, num_attention_heads=24, num_key_value_heads=8,
+                   intermediate_size=8192)
+    elif index == 4:
+        cfg.update(num_hidden_layers=32, hidden_size=4096, num_attention_heads=32, num_key_value_heads=8,
+                   intermediate_size=14336, tie_word_embeddings=False)
+        cfg["rope_scaling"] = dict(cfg["rope_scaling"], factor=8.0)
+    else:
+        raise ValueError(f"no configuration {index}")
+    return cfg
 
 
 def load_peaks() -> tuple[dict, str]:
@@ -293,6 +308,159 @@ def run_ours(args) -> dict:
     }
 
 
+def run_further(args) -> dict:
+    """The further workloads BASELINE.json names, with the same kind of line: configs[3], one mixed step at
+    Llama-3.2-3B sizes (32 requests that decode at contexts of 1,024 to 4,096 beside the second 2,048-token
+    portion of a 4,096-token prompt), and configs[4], decode at batch 64 with every request at context 8,192 at
+    Llama-3.1-8B sizes.  Fewer layers than the models have by default (the random weights are drawn on the host);
+    ``config`` names both numbers."""
+    import numpy as np
+    import torch
+
+    from tokasaurus_b200.engine.batch import StepEntry
+    from tokasaurus_b200.engine.engine import Engine
+    from tokasaurus_b200.kernels import ops
+
+    cfg = load_other_config(args.config)
+    full_layers = cfg["num_hidden_layers"]
+    layers = args.layers or (14 if args.config == 3 else 8)
+    cfg["num_hidden_layers"] = layers
+    peaks, peak_src = load_peaks()
+    page_size = 16
+    g = torch.Generator().manual_seed(0)
+    rng = np.random.default_rng(0)
+    if args.config == 3:
+        batch, chunk = 32, 2048
+        contexts = [int(c) for c in rng.integers(1024, 4097, size=batch)]
+        pool_tokens = sum(-(-(c + 1) // page_size) * page_size for c in contexts) + 4096 + 64 * page_size
+    else:
+        batch, chunk = 64, 0
+        contexts = [8192] * batch
+        pool_tokens = batch * (8192 + 512)
+    eng = Engine(config_dict=cfg, random_weights=0, dtype="bfloat16", page_size=page_size,
+                 kv_cache_num_tokens=pool_tokens, max_tokens_per_forward=8192, max_seqs_per_forward=max(64, batch + 1),
+                 device="cuda:0")
+    runner, cache, sampler = eng.runner, eng.runner.cache, eng.sampler
+    m = model_numbers(cfg, layers)
+    dev = runner.rt.device
+
+    def tokens(n):
+        return torch.randint(0, cfg["vocab_size"], (n,), generator=g).tolist()
+
+    def sample_rows(logits, entries):
+        slots = torch.tensor([cache.slot(e.request) for e in entries], dtype=torch.int32, device=dev)
+        sampler.sample(logits, torch.zeros(len(entries), device=dev), None, None, slots, cache.last_token)
+
+    # the requests' contexts go into the cache through the step function, up to 8,192 tokens a step
+    ids = [f"d{i}" for i in range(batch)]
+    done = {rid: 0 for rid in ids}
+    want = dict(zip(ids, contexts))
+    for rid in ids:
+        cache.admit(rid)
+        cache.ensure_capacity(rid, want[rid] + 1)
+    while any(done[r] < want[r] for r in ids):
+        entries, room = [], 8192
+        for rid in ids:
+            n = min(want[rid] - done[rid], room)
+            if n > 0:
+                last = done[rid] + n == want[rid]
+                entries.append(StepEntry(rid, tokens(n), done[rid], [n - 1] if last else []))
+                done[rid] += n
+                room -= n
+        logits = runner.step(entries)
+        finishing = [e for e in entries if e.want]
+        if finishing:
+            sample_rows(logits, finishing)
+    torch.cuda.synchronize()
+
+    def event_ms(fn, reps):
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(reps):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / reps
+
+    zeros = np.zeros(batch + (1 if chunk else 0), dtype=np.float32)
+    keys = np.zeros(len(zeros), dtype=np.int64)
+    if args.config == 3:
+        # the mixed step, repeated as it is: the same positions are computed and written again
+        cache.admit("pf")
+        cache.ensure_capacity("pf", 2 * chunk)
+        runner.step([StepEntry("pf", tokens(chunk), 0, [])])
+        pf_tokens = tokens(chunk)
+
+        def one():
+            entries = [StepEntry("pf", pf_tokens, chunk, [chunk - 1])]
+            entries += [StepEntry(rid, None, want[rid], [0]) for rid in ids]
+            pos = np.asarray([2 * chunk] + [want[r] + 1 for r in ids], dtype=np.int32)
+            slot = np.asarray([cache.slot(e.request) for e in entries], dtype=np.int32)
+            logits = runner.step(entries, dict(temperature=zeros, stream_key=keys, sample_pos=pos, row_slot=slot))
+            ex = runner.last_context.extra
+            sampler.sample(logits, ex["temperature"], ex["stream_key"], ex["sample_pos"], ex["row_slot"], cache.last_token)
+
+        step_tokens = batch + chunk
+        rows = batch + 1
+        flops = prefill_flops(m, chunk, rows) + 2.0 * batch * (layers - 1) * m["per_layer_params"] \
+            + layers * m["nh"] * m["hd"] * 4.0 * (chunk * chunk + sum(contexts))  # the chunk's queries see 2,048 keys more
+        nbytes = decode_bytes(m, batch, sum(contexts) / batch) + decode_bytes(m, 1, 2 * chunk) - decode_bytes(m, 0, 0)
+        metric = "tokens/s of a mixed step (Llama-3.2-3B sizes: 32 decoding requests beside a 2,048-token prompt portion)"
+    else:
+        length = dict(want)
+
+        def one():
+            entries = []
+            for rid in ids:
+                cache.ensure_capacity(rid, length[rid] + 1)
+                entries.append(StepEntry(rid, None, length[rid], [0]))
+                length[rid] += 1
+            pos = np.asarray([length[r] for r in ids], dtype=np.int32)
+            slot = np.asarray([cache.slot(r) for r in ids], dtype=np.int32)
+            extra = dict(temperature=zeros, stream_key=keys, sample_pos=pos, row_slot=slot)
+            if eng.graphs is not None and eng.graphs.usable(entries):
+                eng.graphs.run(entries, extra)
+                return
+            logits = runner.step(entries, extra)
+            ex = runner.last_context.extra
+            sampler.sample(logits, ex["temperature"], ex["stream_key"], ex["sample_pos"], ex["row_slot"], cache.last_token)
+
+        step_tokens = batch
+        flops = 2.0 * batch * (layers * m["per_layer_params"] + m["head_params"])
+        nbytes = decode_bytes(m, batch, 8192 + args.warmup + args.steps / 2)
+        metric = "decode tokens/s (Llama-3.1-8B sizes, batch 64, every request at context 8,192)"
+
+    for _ in range(args.warmup):
+        one()
+    clocks = ClockSampler()
+    clocks.start()
+    ops.LAUNCHES = 0
+    ms = event_ms(one, args.steps)
+    launches = ops.LAUNCHES
+    clock_info = clocks.stop()
+    runner.check_status()
+    achieved = nbytes / (ms / 1e3) / 1e9
+    return {
+        "metric": metric, "value": round(step_tokens * 1e3 / ms, 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic token ids (seeded uniform), random weights N(0, 0.02)",
+        "impl": "ours",
+        "config": {
+            "model": "Llama-3.2-3B sizes" if args.config == 3 else "Llama-3.1-8B sizes", "baseline_config": args.config,
+            "global_batch": batch, "prompt_portion": chunk, "context_mean": round(sum(contexts) / batch, 1),
+            "parallelism": "1 GPU", "layers": layers, "layers_full": full_layers, "hidden": m["H"], "heads": m["nh"],
+            "kv_heads": m["nkv"], "head_dim": m["hd"], "intermediate": m["I"], "vocab": m["V"], "page_size": page_size,
+            "l2": "weights and cache larger than L2; no flush",
+        },
+        "gpu_launches": launches, "clocks": clock_info,
+        "roofline": dict(bound="hbm", achieved=round(achieved, 1), peak=peaks["hbm_gbs"], unit="GB/s",
+                         frac=round(achieved / peaks["hbm_gbs"], 4), of=peak_src),
+        "compute": dict(tflops=round(flops / (ms / 1e3) / 1e12, 1), peak=peaks["bf16_tflops"],
+                        frac=round(flops / (ms / 1e3) / (peaks["bf16_tflops"] * 1e12), 4), of=peak_src),
+    }
+
+
 def run_reference(args) -> dict:
     ref = os.path.join(ROOT, "baseline", "_ref")
     why = None
@@ -324,6 +492,8 @@ def main() -> int:
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration (0: all)")
     ap.add_argument("--skip-points", action="store_true", help="leave out the batch-1 and batch-64 points")
+    ap.add_argument("--config", type=int, default=2, choices=[2, 3, 4],
+                    help="2: the headline metric (default); 3 and 4: the further workloads, see run_further")
     args = ap.parse_args()
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
@@ -332,7 +502,7 @@ def main() -> int:
     if args.impl == "reference":
         print(json.dumps(run_reference(args)))
         return 0
-    print(json.dumps(run_ours(args)))
+    print(json.dumps(run_ours(args) if args.config == 2 else run_further(args)))
     return 0
 
 
