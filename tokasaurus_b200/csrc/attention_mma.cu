@@ -80,39 +80,53 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 }
 
 // Copy keys [key_base, key_base + KT) of one kv head into a stage; keys outside [key_lo, key_hi) become zero.
+// In two halves, so that a caller may look the pages up an iteration before it issues the copies (a lookup is a
+// load that the copies' addresses depend on: done together, its latency is paid in every iteration).
+template <int NTHREADS>
+struct KvTileLoad {
+  static constexpr int ITERS = (KT * CPR + NTHREADS - 1) / NTHREADS;
+  int page[ITERS];  // page of each row this thread copies; -1: the row is outside the keys wanted
+
+  __device__ __forceinline__ void lookup(const int* __restrict__ table, int ps, int key_base, int key_lo, int key_hi,
+                                         int tid) {
+    const int ps_shift = (ps & (ps - 1)) == 0 ? 31 - __clz(ps) : -1;  // page sizes that are powers of two: shifts
+#pragma unroll
+    for (int i = 0; i < ITERS; i++) {
+      const int idx = tid + i * NTHREADS;
+      const int key = key_base + idx / CPR;
+      page[i] = -1;
+      if (idx < KT * CPR && key >= key_lo && key < key_hi) page[i] = table[ps_shift >= 0 ? key >> ps_shift : key / ps];
+    }
+  }
+  __device__ __forceinline__ void issue(unsigned char* stage, const bf16* __restrict__ kcache,
+                                        const bf16* __restrict__ vcache, int kvh, int nkv, int ps, int key_base,
+                                        int tid) const {
+    const uint32_t sk = smem_u32(stage), sv = sk + TILE_B;
+    const int ps_shift = (ps & (ps - 1)) == 0 ? 31 - __clz(ps) : -1;
+#pragma unroll
+    for (int i = 0; i < ITERS; i++) {
+      const int idx = tid + i * NTHREADS;
+      if (idx < KT * CPR) {
+        const int r = idx / CPR, c = idx - r * CPR;
+        const int key = key_base + r;
+        const int slot = ps_shift >= 0 ? key & (ps - 1) : key % ps;
+        const bool valid = page[i] >= 0;
+        const size_t off = valid ? (((size_t)page[i] * nkv + kvh) * ps + slot) * HD + c * 8 : 0;
+        const uint32_t d = r * ROWB + c * 16;
+        cp_async16(sk + d, kcache + off, valid);
+        cp_async16(sv + d, vcache + off, valid);
+      }
+    }
+  }
+};
+
 template <int NTHREADS>
 __device__ __forceinline__ void load_kv_tile(unsigned char* stage, const bf16* __restrict__ kcache,
                                              const bf16* __restrict__ vcache, const int* __restrict__ table, int kvh,
                                              int nkv, int ps, int key_base, int key_lo, int key_hi, int tid) {
-  const uint32_t sk = smem_u32(stage), sv = sk + TILE_B;
-  const int ps_shift = (ps & (ps - 1)) == 0 ? 31 - __clz(ps) : -1;  // page sizes that are powers of two: shifts
-  constexpr int ITERS = (KT * CPR + NTHREADS - 1) / NTHREADS;
-  size_t off[ITERS];
-  bool valid[ITERS];
-  // the page lookups of the whole tile first, so that they are in flight together
-#pragma unroll
-  for (int i = 0; i < ITERS; i++) {
-    const int idx = tid + i * NTHREADS;
-    const int r = idx / CPR, c = idx - r * CPR;
-    const int key = key_base + r;
-    valid[i] = idx < KT * CPR && key >= key_lo && key < key_hi;
-    off[i] = 0;
-    if (valid[i]) {
-      const int pi = ps_shift >= 0 ? key >> ps_shift : key / ps;
-      const int slot = ps_shift >= 0 ? key & (ps - 1) : key - pi * ps;
-      off[i] = (((size_t)table[pi] * nkv + kvh) * ps + slot) * HD + c * 8;
-    }
-  }
-#pragma unroll
-  for (int i = 0; i < ITERS; i++) {
-    const int idx = tid + i * NTHREADS;
-    if (idx < KT * CPR) {
-      const int r = idx / CPR, c = idx - r * CPR;
-      const uint32_t d = r * ROWB + c * 16;
-      cp_async16(sk + d, kcache + off[i], valid[i]);
-      cp_async16(sv + d, vcache + off[i], valid[i]);
-    }
-  }
+  KvTileLoad<NTHREADS> t;
+  t.lookup(table, ps, key_base, key_lo, key_hi, tid);
+  t.issue(stage, kcache, vcache, kvh, nkv, ps, key_base, tid);
 }
 
 // S[16 x 16 keys] = Q . K^T for the 16 key rows starting at key_row of the K tile.  s[nt][4], nt = 0, 1.
@@ -407,16 +421,19 @@ attn_decode_mma_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restric
   float m[2] = {NEG_BIG, NEG_BIG}, l[2] = {0.f, 0.f};
   const int lim_lo[2] = {k_begin, k_begin}, lim_hi[2] = {k_end - 1, k_end - 1};
 
+  // the pages of the tile that the loop's first iteration sends for; from then on each iteration looks up the
+  // pages of the tile that the next one sends for, so that no iteration waits for a lookup
+  KvTileLoad<128> ahead;
+  if (DSTAGES - 1 < n_tiles) ahead.lookup(table, ps, k_begin + (DSTAGES - 1) * KT, k_begin, k_end, tid);
   for (int it = 0; it < n_tiles; it++) {
     unsigned char* cur = smem + (it % DSTAGES) * STAGE_B;
     cp_async_wait<DSTAGES - 2>();
     __syncthreads();  // tile `it` is there for every warp, and every warp is through with tile it - 1
     {
       const int nxt = it + DSTAGES - 1;  // into the stage that tile it - 1 has just left
-      if (nxt < n_tiles)
-        load_kv_tile<128>(smem + (nxt % DSTAGES) * STAGE_B, kcache, vcache, table, kvh, nkv, ps, k_begin + nxt * KT,
-                          k_begin, k_end, tid);
+      if (nxt < n_tiles) ahead.issue(smem + (nxt % DSTAGES) * STAGE_B, kcache, vcache, kvh, nkv, ps, k_begin + nxt * KT, tid);
       cp_async_commit();
+      if (nxt + 1 < n_tiles) ahead.lookup(table, ps, k_begin + (nxt + 1) * KT, k_begin, k_end, tid);
     }
     if (owns_new && it == n_tiles - 1) {
       // the tile came from the cache as it was before this step: put the token's own key and value in
