@@ -16,7 +16,7 @@
 // nothing that an earlier owner of a page left behind can reach a sum.  Shared-memory rows are padded
 // by 16 bytes, which keeps ldmatrix free of bank conflicts for every head size that is a
 // multiple of 16.
-#include "common.cuh"
+#include "tcgen05.cuh"
 #include <float.h>
 
 #ifndef TKB_HD
@@ -31,16 +31,29 @@ namespace {
 
 constexpr int HD = TKB_HD;
 constexpr int KT = 64;                // keys per shared-memory tile
-constexpr int ROWB = HD * 2 + 16;     // bytes per padded row
-constexpr int CPR = HD / 8;           // 16-byte chunks per row
-constexpr int TILE_B = KT * ROWB;     // bytes of one K or V tile
+// Layout of a K or V tile in shared memory.  Head sizes that are multiples of 64: blocks of 64 columns, each
+// [KT rows x 128 bytes] with the 128-byte swizzle (16-byte chunk c of row r lies at chunk c ^ (r & 7)), which is
+// what a TMA box leaves and keeps ldmatrix free of bank conflicts.  Other head sizes: rows padded by 16 bytes.
+constexpr bool SWZ = HD % 64 == 0;
+constexpr int ROWB = SWZ ? 128 : HD * 2 + 16;  // bytes from one row to the next
+constexpr int CPR = HD / 8;                    // 16-byte chunks per row
+constexpr int ATOM_B = KT * 128;               // one 64-column block (swizzled layout)
+constexpr int TILE_B = SWZ ? KT * HD * 2 : KT * ROWB;  // bytes of one K or V tile
 constexpr int STAGE_B = 2 * TILE_B;   // K tile then V tile
-constexpr int SMEM_B = 2 * STAGE_B;   // two stages (tiled kernel for portions)
+constexpr int SMEM_ALIGN = SWZ ? 1024 : 128;   // the swizzle pattern repeats every 1,024 bytes
+constexpr int SMEM_B = 2 * STAGE_B + SMEM_ALIGN;  // two stages (tiled kernel for portions)
 // The split-key kernel: three stages where they leave room for two or three blocks an SM (three at head sizes
 // to 80, two to 128), else two.  Four stages at head size 64 were measured slower: the blocks of a step then
 // no longer fit the SMs all at once.
 constexpr int DSTAGES = 3 * STAGE_B <= 110 * 1024 ? 3 : 2;
-constexpr int DEC_SMEM_B = DSTAGES * STAGE_B;
+constexpr int DEC_SMEM_B = DSTAGES * STAGE_B + SMEM_ALIGN;
+// byte offset of 16-byte chunk `chunk` of row `row` within a tile
+__device__ __forceinline__ int tile_off(int row, int chunk) {
+  return SWZ ? (chunk >> 3) * ATOM_B + row * 128 + (((chunk & 7) ^ (row & 7)) << 4) : row * ROWB + chunk * 16;
+}
+__device__ __forceinline__ unsigned char* align_smem(unsigned char* p) {
+  return reinterpret_cast<unsigned char*>(((uintptr_t)p + (SMEM_ALIGN - 1)) & ~(uintptr_t)(SMEM_ALIGN - 1));
+}
 constexpr int KSTEPS = HD / 16;       // k-steps of Q.K^T
 constexpr int DTILES = HD / 8;        // n-tiles of P.V
 constexpr float NEG_BIG = -1.0e30f;   // finite stand-in for -inf in running maxima
@@ -112,7 +125,7 @@ struct KvTileLoad {
         const int slot = ps_shift >= 0 ? key & (ps - 1) : key % ps;
         const bool valid = page[i] >= 0;
         const size_t off = valid ? (((size_t)page[i] * nkv + kvh) * ps + slot) * HD + c * 8 : 0;
-        const uint32_t d = r * ROWB + c * 16;
+        const uint32_t d = tile_off(r, c);
         cp_async16(sk + d, kcache + off, valid);
         cp_async16(sv + d, vcache + off, valid);
       }
@@ -141,7 +154,7 @@ __device__ __forceinline__ void qk_16keys(float (&s)[2][4], const uint32_t (&qf)
 #pragma unroll
   for (int ks = 0; ks < KSTEPS; ks++) {
     uint32_t b0, b1, b2, b3;
-    ldmatrix_x4(b0, b1, b2, b3, k_tile + row * ROWB + (ks * 2 + chunk_sel) * 16);
+    ldmatrix_x4(b0, b1, b2, b3, k_tile + tile_off(row, ks * 2 + chunk_sel));
     mma_bf16(s[0], qf[ks], b0, b1);
     mma_bf16(s[1], qf[ks], b2, b3);
   }
@@ -155,7 +168,7 @@ __device__ __forceinline__ void pv_16keys(float (&o)[DTILES][4], const uint32_t 
 #pragma unroll
   for (int dt = 0; dt < DTILES; dt += 2) {
     uint32_t b0, b1, b2, b3;
-    ldmatrix_x4_trans(b0, b1, b2, b3, v_tile + row * ROWB + (dt + chunk_sel) * 16);
+    ldmatrix_x4_trans(b0, b1, b2, b3, v_tile + tile_off(row, dt + chunk_sel));
     mma_bf16(o[dt], pf, b0, b1);
     mma_bf16(o[dt + 1], pf, b2, b3);
   }
@@ -251,7 +264,8 @@ __device__ __forceinline__ float2 merge_splits(const float* __restrict__ part_o,
 // head's k, writes it and v into the cache page, and only then reads its tiles.
 template <bool FUSED>
 __global__ void __launch_bounds__(128)
-attn_decode_mma_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ kcache,
+attn_decode_mma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, int tma_rows,
+                       const bf16* __restrict__ q, int q_stride, bf16* __restrict__ kcache,
                        bf16* __restrict__ vcache, const int* __restrict__ seq_q_start,
                        const int* __restrict__ seq_kv_len, const int* __restrict__ page_indptr,
                        const int* __restrict__ page_ids, const int* __restrict__ items,
@@ -262,7 +276,8 @@ attn_decode_mma_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restric
                        long long part_stride, int* __restrict__ counters, const int* __restrict__ item_entry,
                        const int* __restrict__ dec_item_start, const int* __restrict__ out_row_of,
                        bf16* __restrict__ out, int out_stride) {
-  extern __shared__ __align__(128) unsigned char smem[];
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  unsigned char* smem = align_smem(smem_raw);
   trigger_dependents();
   // What the host wrote for this step (work items, lengths, block tables) is there before any kernel of the
   // step starts, so the block works out its geometry while the kernel ahead (the q|k|v product) still runs.
@@ -290,11 +305,52 @@ attn_decode_mma_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restric
   // memory; all older keys were written by earlier steps, so tiles that end before p may be read even before
   // the kernel ahead has finished.  Otherwise (keys of this step come from a kernel ahead) the wait comes first.
   const bool early = FUSED && (k_end < kv_len || n_tiles > DSTAGES - 1);
+  // Tiles whose keys all exist come by TMA where the page size allows it (tma_rows > 0: a power of two from 8
+  // up) and the item starts on a tile boundary: warp 0 asks for one box a page and 64-column block, nobody
+  // computes an address or issues a copy of its own; the tile's arrival is counted by an mbarrier.  The
+  // request's last, partial tile and everything else is gathered with cp.async, zero-filling what lies outside.
+  __shared__ __align__(8) uint64_t kv_full[DSTAGES];
+  const bool use_tma = SWZ && tma_rows > 0 && (k_begin & (KT - 1)) == 0 && n_tiles > DSTAGES;  // short items gain nothing
+  const int ps_shift = 31 - __clz(ps);  // used with TMA only (page sizes that are powers of two)
+  auto by_tma = [&](int tile) { return use_tma && k_begin + (tile + 1) * KT <= kv_len; };
+  // warp 0: the page of the box that this lane asks for (lanes beyond the tile's boxes ask for nothing)
+  const int tma_boxes = use_tma ? KT / tma_rows : 1;
+  const int tma_atom = lane / tma_boxes, tma_box = lane - tma_atom * tma_boxes;
+  const bool tma_lane = use_tma && warp == 0 && tma_atom < HD / 64;
+  auto tma_lookup = [&](int tile) {
+    return tma_lane ? table[(k_begin + tile * KT + tma_box * tma_rows) >> ps_shift] : 0;
+  };
+  auto tma_issue = [&](int tile, int page) {  // warp 0, all lanes
+    unsigned char* stage = smem + (tile % DSTAGES) * STAGE_B;
+    uint64_t* bar = &kv_full[tile % DSTAGES];
+    if (lane == 0) tkb5::mbar_expect_tx(bar, STAGE_B);
+    __syncwarp();
+    if (tma_lane) {
+      const int key = k_begin + tile * KT + tma_box * tma_rows;
+      const int row = (page * nkv + kvh) * ps + (key & (ps - 1));
+      unsigned char* dst = stage + tma_atom * ATOM_B + tma_box * tma_rows * 128;
+      tkb5::tma_load_2d(dst, &map_k, bar, tma_atom * 64, row);
+      tkb5::tma_load_2d(dst + TILE_B, &map_v, bar, tma_atom * 64, row);
+    }
+  };
+  if (use_tma) {
+    if (tid == 0) {
+#pragma unroll
+      for (int i = 0; i < DSTAGES; i++) tkb5::mbar_init(&kv_full[i], 1);
+      asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+  }
   if (!early) grid_dependency_wait();
 #pragma unroll
   for (int st = 0; st < DSTAGES - 1; st++) {
-    if (st < n_tiles)
-      load_kv_tile<128>(smem + st * STAGE_B, kcache, vcache, table, kvh, nkv, ps, k_begin + st * KT, k_begin, k_end, tid);
+    if (st < n_tiles) {
+      if (by_tma(st)) {
+        if (warp == 0) tma_issue(st, tma_lookup(st));
+      } else {
+        load_kv_tile<128>(smem + st * STAGE_B, kcache, vcache, table, kvh, nkv, ps, k_begin + st * KT, k_begin, k_end, tid);
+      }
+    }
     cp_async_commit();
   }
   // Q fragments: row r of the tile is query head g0 + r; rows >= gn are zero.
@@ -424,25 +480,38 @@ attn_decode_mma_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restric
   // the pages of the tile that the loop's first iteration sends for; from then on each iteration looks up the
   // pages of the tile that the next one sends for, so that no iteration waits for a lookup
   KvTileLoad<128> ahead;
-  if (DSTAGES - 1 < n_tiles) ahead.lookup(table, ps, k_begin + (DSTAGES - 1) * KT, k_begin, k_end, tid);
+  int ahead_page = 0;
+  auto look_ahead = [&](int tile) {
+    if (tile >= n_tiles) return;
+    if (by_tma(tile)) ahead_page = tma_lookup(tile);
+    else ahead.lookup(table, ps, k_begin + tile * KT, k_begin, k_end, tid);
+  };
+  look_ahead(DSTAGES - 1);
+  bool timed_out = false;
   for (int it = 0; it < n_tiles; it++) {
     unsigned char* cur = smem + (it % DSTAGES) * STAGE_B;
     cp_async_wait<DSTAGES - 2>();
+    if (by_tma(it) && !tkb5::mbar_wait(&kv_full[it % DSTAGES], (it / DSTAGES) & 1)) timed_out = true;
     __syncthreads();  // tile `it` is there for every warp, and every warp is through with tile it - 1
     {
       const int nxt = it + DSTAGES - 1;  // into the stage that tile it - 1 has just left
-      if (nxt < n_tiles) ahead.issue(smem + (nxt % DSTAGES) * STAGE_B, kcache, vcache, kvh, nkv, ps, k_begin + nxt * KT, tid);
+      if (nxt < n_tiles) {
+        if (by_tma(nxt)) {
+          if (warp == 0) tma_issue(nxt, ahead_page);
+        } else {
+          ahead.issue(smem + (nxt % DSTAGES) * STAGE_B, kcache, vcache, kvh, nkv, ps, k_begin + nxt * KT, tid);
+        }
+      }
       cp_async_commit();
-      if (nxt + 1 < n_tiles) ahead.lookup(table, ps, k_begin + (nxt + 1) * KT, k_begin, k_end, tid);
+      look_ahead(nxt + 1);
     }
     if (owns_new && it == n_tiles - 1) {
       // the tile came from the cache as it was before this step: put the token's own key and value in
       const int row = p - (k_begin + it * KT);
-      bf16* kt = reinterpret_cast<bf16*>(cur + row * ROWB);
-      bf16* vt = reinterpret_cast<bf16*>(cur + TILE_B + row * ROWB);
       for (int d = tid; d < HD; d += 128) {
-        kt[d] = knew[d];
-        vt[d] = vnew[d];
+        const int at = tile_off(row, d >> 3) + (d & 7) * 2;
+        *reinterpret_cast<bf16*>(cur + at) = knew[d];
+        *reinterpret_cast<bf16*>(cur + TILE_B + at) = vnew[d];
       }
       __syncthreads();
     }
@@ -463,6 +532,7 @@ attn_decode_mma_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restric
     }
   }
   cp_async_wait<0>();
+  if (timed_out && status != nullptr) atomicOr(status, TKB_STATUS_WAIT_TIMEOUT);
   __syncthreads();
   // row sums over the four threads of a row
 #pragma unroll
@@ -574,7 +644,8 @@ attn_prefill_mma_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restri
                         const int* __restrict__ seq_kv_len, const int* __restrict__ page_indptr,
                         const int* __restrict__ page_ids, const int* __restrict__ tiles,
                         const int* __restrict__ n_tiles_ptr, int nh, int nkv, int ps, float scale_log2, int window) {
-  extern __shared__ __align__(128) unsigned char smem[];
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  unsigned char* smem = align_smem(smem_raw);
   trigger_dependents();
   grid_dependency_wait();
   if ((int)blockIdx.x >= *n_tiles_ptr) return;
@@ -738,6 +809,48 @@ static int ensure_smem_attr() {
   return 0;
 }
 
+// TMA descriptors of the K and V cache of one layer, seen as [pages * kv heads * page size, HD] matrices, with
+// boxes of 64 columns x min(page size, 64) rows.  rows == 0: no TMA (the head size is no multiple of 64, the page
+// size no power of two from 8 up, or the caller did not say how many pages there are).  The last descriptors made
+// are kept: a model asks for the same few (one pair a layer) at every step.
+struct KvMaps {
+  CUtensorMap k, v;
+  int rows;
+};
+struct KvMapsKey {
+  const void *k, *v;
+  long long pages;
+  int nkv, ps;
+};
+static int kv_maps(KvMaps& m, const void* kcache, const void* vcache, long long num_pages, int nkv, int ps) {
+  memset(&m, 0, sizeof(m));
+  const long long rows = num_pages * nkv * ps;
+  if (!SWZ || num_pages <= 0 || ps < 8 || (ps & (ps - 1)) != 0 || rows >= (1ll << 31) || ((uintptr_t)kcache & 15) ||
+      ((uintptr_t)vcache & 15))
+    return 0;
+  constexpr int SLOTS = 128;
+  static KvMapsKey keys[SLOTS];
+  static KvMaps maps[SLOTS];
+  static int used = 0, next = 0;
+  for (int i = 0; i < used; i++) {
+    if (keys[i].k == kcache && keys[i].v == vcache && keys[i].pages == num_pages && keys[i].nkv == nkv && keys[i].ps == ps) {
+      m = maps[i];
+      return 0;
+    }
+  }
+  int rc = tkb5::get_encode();
+  const int box = ps < KT ? ps : KT;
+  if (rc == 0) rc = tkb5::make_map(&m.k, kcache, (int)rows, HD, HD, box);
+  if (rc == 0) rc = tkb5::make_map(&m.v, vcache, (int)rows, HD, HD, box);
+  if (rc != 0) return rc;
+  m.rows = box;
+  keys[next] = KvMapsKey{kcache, vcache, num_pages, nkv, ps};
+  maps[next] = m;
+  next = (next + 1) % SLOTS;
+  if (used < SLOTS) used++;
+  return 0;
+}
+
 }  // namespace
 
 // Scratch a decode launch needs for `items_cap` work items: floats of part_o and of part_ml.
@@ -760,8 +873,10 @@ TKB_EXPORT int tkb_attn_decode_mma_bf16(const void* q, int q_stride, const void*
   const int head_tiles = (group + 15) / 16;
   if ((long long)nkv * head_tiles > 65535) return -3;
   dim3 grid(items_cap, nkv * head_tiles);
-  return launch_pdl(attn_decode_mma_kernel<false>, grid, dim3(128), (size_t)DEC_SMEM_B, (cudaStream_t)st, (const bf16*)q,
-                    q_stride, (bf16*)kcache, (bf16*)vcache, seq_q_start, seq_kv_len, page_indptr, page_ids, items,
+  KvMaps maps;
+  memset(&maps, 0, sizeof(maps));  // this entry point does not know the size of the pool: every tile is gathered
+  return launch_pdl(attn_decode_mma_kernel<false>, grid, dim3(128), (size_t)DEC_SMEM_B, (cudaStream_t)st, maps.k, maps.v,
+                    maps.rows, (const bf16*)q, q_stride, (bf16*)kcache, (bf16*)vcache, seq_q_start, seq_kv_len, page_indptr, page_ids, items,
                     n_items_ptr, part_o, part_ml, nh, nkv, ps, scale * 1.4426950408889634f, window,
                     head_tiles, (const float*)nullptr, 0, 0, 0, (int*)nullptr, (const float*)nullptr, 0, 0LL,
                     (int*)nullptr, (const int*)nullptr, (const int*)nullptr, (const int*)nullptr, (bf16*)nullptr, 0);
@@ -787,8 +902,11 @@ TKB_EXPORT int tkb_attn_decode_rope_mma_bf16(const void* qkv, int q_stride, cons
   const int head_tiles = (group + 15) / 16;
   if ((long long)nkv * head_tiles > 65535) return -3;
   dim3 grid(items_cap, nkv * head_tiles);
-  return launch_pdl(attn_decode_mma_kernel<true>, grid, dim3(128), (size_t)DEC_SMEM_B, (cudaStream_t)st, (const bf16*)qkv,
-                    q_stride, (bf16*)kcache, (bf16*)vcache, seq_q_start, seq_kv_len, page_indptr, page_ids, items,
+  KvMaps maps;
+  rc = kv_maps(maps, kcache, vcache, num_pages, nkv, ps);
+  if (rc) return rc;
+  return launch_pdl(attn_decode_mma_kernel<true>, grid, dim3(128), (size_t)DEC_SMEM_B, (cudaStream_t)st, maps.k, maps.v,
+                    maps.rows, (const bf16*)qkv, q_stride, (bf16*)kcache, (bf16*)vcache, seq_q_start, seq_kv_len, page_indptr, page_ids, items,
                     n_items_ptr, part_o, part_ml, nh, nkv, ps, scale * 1.4426950408889634f, window,
                     head_tiles, inv_freq, rot, write_cache, num_pages, status, qkv_parts, n_parts, part_stride,
                     (int*)nullptr, (const int*)nullptr, (const int*)nullptr, (const int*)nullptr, (bf16*)nullptr, 0);
@@ -818,16 +936,19 @@ TKB_EXPORT int tkb_attn_decode_merged_bf16(const void* qkv, int q_stride, const 
   if ((long long)nkv * head_tiles > 65535) return -3;
   dim3 grid(items_cap, nkv * head_tiles);
   const float sl2 = scale * 1.4426950408889634f;
+  KvMaps maps;
+  rc = kv_maps(maps, kcache, vcache, num_pages, nkv, ps);
+  if (rc) return rc;
   if (fused)
-    return launch_pdl(attn_decode_mma_kernel<true>, grid, dim3(128), (size_t)DEC_SMEM_B, (cudaStream_t)st,
-                      (const bf16*)qkv, q_stride, (bf16*)kcache, (bf16*)vcache, seq_q_start, seq_kv_len, page_indptr,
+    return launch_pdl(attn_decode_mma_kernel<true>, grid, dim3(128), (size_t)DEC_SMEM_B, (cudaStream_t)st, maps.k,
+                      maps.v, maps.rows, (const bf16*)qkv, q_stride, (bf16*)kcache, (bf16*)vcache, seq_q_start, seq_kv_len, page_indptr,
                       page_ids, items, n_items_ptr, part_o, part_ml, nh, nkv, ps, sl2, window, head_tiles,
                       inv_freq, rot, write_cache, num_pages, status, qkv_parts, n_parts, part_stride, counters,
                       item_entry, dec_item_start, out_row_of, (bf16*)out, out_stride);
-  return launch_pdl(attn_decode_mma_kernel<false>, grid, dim3(128), (size_t)DEC_SMEM_B, (cudaStream_t)st,
-                    (const bf16*)qkv, q_stride, (bf16*)kcache, (bf16*)vcache, seq_q_start, seq_kv_len, page_indptr,
-                    page_ids, items, n_items_ptr, part_o, part_ml, nh, nkv, ps, sl2, window, head_tiles,
-                    (const float*)nullptr, 0, 0, 0, (int*)nullptr, (const float*)nullptr, 0, 0LL, counters, item_entry,
+  return launch_pdl(attn_decode_mma_kernel<false>, grid, dim3(128), (size_t)DEC_SMEM_B, (cudaStream_t)st, maps.k,
+                    maps.v, maps.rows, (const bf16*)qkv, q_stride, (bf16*)kcache, (bf16*)vcache, seq_q_start, seq_kv_len,
+                    page_indptr, page_ids, items, n_items_ptr, part_o, part_ml, nh, nkv, ps, sl2, window, head_tiles,
+                    (const float*)nullptr, 0, 0, num_pages, status, (const float*)nullptr, 0, 0LL, counters, item_entry,
                     dec_item_start, out_row_of, (bf16*)out, out_stride);
 }
 

@@ -388,7 +388,7 @@ def attn_decode_mma(qkv: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tenso
             _ptr(qkv), c_int(qkv.shape[1]), _ptr(None), c_int(0), ctypes.c_longlong(0), _ptr(kcache), _ptr(vcache),
             _ptr(seq_q_start), _ptr(seq_kv_len), _ptr(page_indptr), _ptr(page_ids), _ptr(items), _ptr(n_items),
             c_int(items_cap), _ptr(part_o), _ptr(part_ml), c_int(n_heads), c_int(n_kv_heads), c_int(page_size),
-            c_float(scale), c_int(window or 0), c_int(0), _ptr(None), c_int(0), c_int(0), c_int(0),
+            c_float(scale), c_int(window or 0), c_int(0), _ptr(None), c_int(0), c_int(0), c_int(kcache.shape[0]),
             _ptr(None), _ptr(counters), _ptr(item_entry), _ptr(dec_item_start),
             _ptr(out_row_of if out_row_of is not None else seq_q_start), _ptr(out), c_int(out.shape[1]), _stream()),
             "attn_decode_merged")

@@ -33,11 +33,11 @@ DECODE_BLOCK_SLOTS = 148 * 3  # blocks of the split-key kernel that a B200 holds
 
 def decode_block_slots(head_dim: int) -> int:
     """Blocks of the split-key kernel that the GPU holds at once: what of an SM's 227 KiB of shared memory the
-    kernel's stages take (two tiles of 64 rows of head_dim * 2 + 16 bytes a stage; three stages, two when three
-    pass 110 KiB), at most three blocks an SM."""
-    stage = 2 * 64 * (head_dim * 2 + 16)
+    kernel's stages take (two tiles of 64 rows a stage, rows of head_dim * 2 bytes, padded by 16 where the head
+    size is no multiple of 64; three stages, two when three pass 110 KiB), at most three blocks an SM."""
+    stage = 2 * 64 * (head_dim * 2 + (0 if head_dim % 64 == 0 else 16))
     stages = 3 if 3 * stage <= 110 * 1024 else 2
-    return 148 * max(1, min(3, (227 * 1024) // (stages * stage + 1024)))
+    return 148 * max(1, min(3, (227 * 1024) // (stages * stage + 2048)))
 
 
 def split_keys_evenly(span: np.ndarray, blocks_per_item: int, slots: int = DECODE_BLOCK_SLOTS
