@@ -506,6 +506,11 @@ def test_mma_attention_never_reads_what_a_page_held_before(ops):
     got, want = run_mma_attention(ops, [1, 37], [100, 37], 8, 2, 64, 16, None, seed=3, fill=float("nan"))
     assert not torch.isnan(got).any()
     torch.testing.assert_close(got, want, rtol=1.6e-2, atol=1.2e-2)
+    # long requests, whose whole tiles come by TMA and whose last tile is gathered; one ends on a tile's edge
+    for hd, ps in ((64, 16), (128, 8), (128, 64), (64, 128)):
+        got, want = run_mma_attention(ops, [1, 1, 1], [1000, 640, 333], 8, 2, hd, ps, None, seed=4, fill=float("nan"))
+        assert not torch.isnan(got).any()
+        torch.testing.assert_close(got, want, rtol=1.6e-2, atol=1.2e-2)
 
 
 # ------------------------------------------------------------------------------------------------

@@ -11,11 +11,18 @@
 //
 // Compile with -DTKB_HD=<head size> (multiple of 16, at most 256).
 //
-// Keys and values reach shared memory with 16-byte cp.async copies, page by page through the
-// request's block table, two or three stages deep; rows outside the request's keys are zero-filled, so
-// nothing that an earlier owner of a page left behind can reach a sum.  Shared-memory rows are padded
-// by 16 bytes, which keeps ldmatrix free of bank conflicts for every head size that is a
-// multiple of 16.
+// Keys and values reach shared memory page by page through the request's block table, two or three stages
+// deep.  In the split-key kernel a tile whose 64 keys all exist comes by TMA (head sizes that are multiples
+// of 64, page sizes that are powers of two from 8 up, items that start on a tile boundary and are longer than
+// the pipeline): one warp asks for one box a page and 64-column block and an mbarrier counts the bytes, so
+// no thread works out addresses or issues copies of its own.  That was what bounded the loop: with two or
+// three blocks of four warps an SM, the 16 cp.async a thread and tile and their address arithmetic were a
+// third of a warp's instructions (measured at head size 128, 64 requests at context 8,192: 505 us gathered,
+// 367 us by TMA, 0.88 of the HBM roofline).  Everything else (the request's last, partial tile, other head and
+// page sizes, the kernel for portions) is gathered with 16-byte cp.async copies; rows outside the request's
+// keys are zero-filled, so nothing that an earlier owner of a page left behind can reach a sum.  Tiles of
+// head sizes that are multiples of 64 lie in shared memory as the TMA leaves them (128-byte swizzle); rows of
+// other head sizes are padded by 16 bytes; both keep ldmatrix free of bank conflicts.
 #include "tcgen05.cuh"
 #include <float.h>
 
