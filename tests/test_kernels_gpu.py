@@ -644,19 +644,23 @@ def test_linear_decode_gated(ops, M, I, K):
 
 @pytest.mark.parametrize("hd,nh,nkv,ps,rot,window", [(64, 32, 8, 16, 64, None), (16, 4, 2, 16, 16, None), (32, 3, 1, 8, 32, None),
                                                       (128, 8, 1, 32, 64, None), (48, 6, 3, 4, 0, 300), (80, 34, 2, 16, 80, None)])
-def test_fused_rope_decode_attention_equals_the_separate_kernels(ops, hd, nh, nkv, ps, rot, window):
+@pytest.mark.parametrize("long_items", [False, True])
+def test_fused_rope_decode_attention_equals_the_separate_kernels(ops, hd, nh, nkv, ps, rot, window, long_items):
+    """``long_items``: few, long work items (their whole tiles come by TMA where the sizes allow), among them
+    requests that end on a tile's edge, one key past it, and in the middle of a page."""
     from types import SimpleNamespace
     from tokasaurus_b200.parts.attention import plan_attention
     from tokasaurus_b200.parts.rope import RotaryEncoding
 
-    lens_kv = [1, 2 * ps, 2 * ps + 1, 777, 256, 257, 513]
+    lens_kv = [1600, 1024, 1025, 333, 2 * ps + 1] if long_items else [1, 2 * ps, 2 * ps + 1, 777, 256, 257, 513]
     B = len(lens_kv)
     dtype = torch.bfloat16
     n_pages = sum(-(-L // ps) for L in lens_kv) + 5
     kc, vc, indptr, pages, K, V = make_paged(dtype, B, lens_kv, nkv, hd, ps, n_pages, seed=hd)
     g = torch.Generator().manual_seed(11)
     qkv = torch.randn(B, (nh + 2 * nkv) * hd, generator=g).to(dtype).to(DEV)
-    plan = plan_attention(SimpleNamespace(seq_q_len=np.ones(B, dtype=np.int32), seq_kv_len=np.asarray(lens_kv, dtype=np.int32)), window)
+    plan = plan_attention(SimpleNamespace(seq_q_len=np.ones(B, dtype=np.int32), seq_kv_len=np.asarray(lens_kv, dtype=np.int32)), window,
+                          **(dict(slots=8 * 8) if long_items else {}))
     c = i32(plan["counts"])
     n_items, n_dec = int(plan["counts"][0]), int(plan["counts"][1])
     q_start, kv_len = i32(list(range(B))), i32(lens_kv)
