@@ -206,3 +206,33 @@ def test_cuttings_through_step_graphs_match_plain(tiny_model_dirs, plain, cfg_in
         for pos, row in got[rid].items():
             err = float(np.abs(row - ref[pos]).max())
             assert err <= tol, f"{dtype} {cut}: request {rid} position {pos}: error {err:.3g}, tolerance {tol:.3g}"
+
+
+@pytest.mark.parametrize("hd", [64, 128])
+def test_wide_heads_and_long_requests_match_plain(tmp_path, monkeypatch, hd):
+    """Head sizes 64 and 128 in bfloat16 take the kernels that the tiny models' heads of 16 and 32 never reach:
+    attention for portions on tcgen05, and whole tiles of keys by TMA in the split-key kernel, which needs
+    work items of more than three tiles: the planner is told of a GPU that holds one block, so that it leaves
+    requests of several hundred tokens whole.  Whole, decoded at the end, in portions, mixed, and the decoded
+    tail through the step graphs (rotation and cache write inside the attention kernel)."""
+    import tokasaurus_b200.parts.attention as attention
+    from tokasaurus_b200.weights import write_model_folder
+
+    monkeypatch.setattr(attention, "decode_block_slots", lambda head_dim: 1)
+    cfg = dict(architectures=["LlamaForCausalLM"], model_type="llama", num_hidden_layers=2, hidden_size=2 * hd,
+               num_attention_heads=2, num_key_value_heads=1, intermediate_size=96, vocab_size=300, rope_theta=10000.0,
+               rope_scaling=None, rms_norm_eps=1e-5, tie_word_embeddings=True, max_position_embeddings=1024)
+    d = write_model_folder(tmp_path / "wide", cfg, seed=3, std=0.05, norm_init="uniform")
+    reqs = {f"w{i}": cuttings.random_tokens(n, 300, 500 + i) for i, n in enumerate([700, 289, 513, 64])}
+    p64 = cuttings.plain_logits(d, reqs, torch.float64)
+    for cut in ("whole", "prefix_then_single", "changing_portions", "mixed"):
+        steps = CUTS[cut](reqs)
+        compare(replay(d, "bfloat16", steps, 16), p64, None, "bfloat16")
+    steps = cuttings.prefix_then_single(reqs)
+    got, n_graph = replay_through_graphs(d, "bfloat16", steps, 16)
+    assert n_graph > len(steps) // 2
+    for rid, ref in p64.items():
+        tol = cuttings.tolerance("bfloat16", ref, None)
+        for pos, row in got[rid].items():
+            err = float(np.abs(row - ref[pos]).max())
+            assert err <= tol, f"request {rid} position {pos}: error {err:.3g}, tolerance {tol:.3g}"
