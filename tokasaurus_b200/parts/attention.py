@@ -260,7 +260,7 @@ class PagedAttention(Mixer):
                     return None
                 return ops.linear_decode(attn, self.w_o, "bf16")
             h = h.materialize()
-        small = (ops.can_use_few_rows(h, self.w_qkv) and (nh * hd) % 8 == 0
+        small = (ops.can_use_few_rows(h, self.w_qkv, ops.ATTN_FEW_ROWS_MAX) and (nh * hd) % 8 == 0
                  and (self.w_qkv.shape[0] + max(rot, 2)) * 4 <= 48 * 1024)
         few = lambda a, w: ops.linear_few_rows(a, w, ctx.status)  # noqa: E731
         if small:
