@@ -74,3 +74,20 @@ def test_item_count_stays_under_the_bound_of_the_graphs():
             span = rng.integers(1, [200, 5000, 200000][kind], size=r).astype(np.int64)
             n, _ = split_keys_evenly(span, mixer._blocks_per_item())
             assert int(n.sum()) <= mixer.plan_capacity(r)["items"], (nh, nkv, r, kind)
+
+
+def test_plan_says_whether_some_item_is_longer_than_three_tiles():
+    """counts[5] picks the split-key kernel's variant (tiles by TMA or not); it must follow the items' sizes."""
+    from types import SimpleNamespace
+
+    def flag(kv):
+        host = SimpleNamespace(seq_q_len=np.ones(len(kv), dtype=np.int32), seq_kv_len=np.asarray(kv, dtype=np.int32))
+        plan = plan_attention(host, None)
+        sizes = plan["items"].reshape(-1, 3)[: int(plan["counts"][0]), 2]
+        assert int(plan["counts"][5]) == int(sizes.max() > 192)
+        return int(plan["counts"][5])
+
+    assert flag([2048]) == 0           # one request: cut into items of 128 keys
+    assert flag([100, 7]) == 0
+    assert flag([2048] * 8) == 1       # items of 384 keys
+    assert flag([50, 40000]) == 1

@@ -269,7 +269,7 @@ __device__ __forceinline__ float2 merge_splits(const float* __restrict__ part_o,
 // FUSED: q points at the un-rotated q|k|v rows of the step [tokens, (nh + 2 nkv) * HD]; the kernel rotates
 // q on the fly, and the block that owns the split holding the token's own position rotates this kv
 // head's k, writes it and v into the cache page, and only then reads its tiles.
-template <bool FUSED>
+template <bool FUSED, bool TMA>
 __global__ void __launch_bounds__(128)
 attn_decode_mma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, int tma_rows,
                        const bf16* __restrict__ q, int q_stride, bf16* __restrict__ kcache,
@@ -317,7 +317,7 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
   // computes an address or issues a copy of its own; the tile's arrival is counted by an mbarrier.  The
   // request's last, partial tile and everything else is gathered with cp.async, zero-filling what lies outside.
   __shared__ __align__(8) uint64_t kv_full[DSTAGES];
-  const bool use_tma = SWZ && tma_rows > 0 && (k_begin & (KT - 1)) == 0 && n_tiles > DSTAGES;  // short items gain nothing
+  const bool use_tma = TMA && SWZ && tma_rows > 0 && (k_begin & (KT - 1)) == 0 && n_tiles > DSTAGES;  // short items gain nothing
   const int ps_shift = 31 - __clz(ps);  // used with TMA only (page sizes that are powers of two)
   auto by_tma = [&](int tile) { return use_tma && k_begin + (tile + 1) * KT <= kv_len; };
   // warp 0: the page of the box that this lane asks for (lanes beyond the tile's boxes ask for nothing)
@@ -807,9 +807,13 @@ static int ensure_smem_attr() {
     e = cudaFuncSetAttribute(attn_prefill_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_B);
   }
   if (e == cudaSuccess && DEC_SMEM_B > 48 * 1024) {
-    e = cudaFuncSetAttribute(attn_decode_mma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, DEC_SMEM_B);
+    e = cudaFuncSetAttribute(attn_decode_mma_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, DEC_SMEM_B);
     if (e == cudaSuccess)
-      e = cudaFuncSetAttribute(attn_decode_mma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, DEC_SMEM_B);
+      e = cudaFuncSetAttribute(attn_decode_mma_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, DEC_SMEM_B);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(attn_decode_mma_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, DEC_SMEM_B);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(attn_decode_mma_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, DEC_SMEM_B);
   }
   if (e != cudaSuccess) return (int)e;
   g_attr_set = true;
@@ -882,7 +886,7 @@ TKB_EXPORT int tkb_attn_decode_mma_bf16(const void* q, int q_stride, const void*
   dim3 grid(items_cap, nkv * head_tiles);
   KvMaps maps;
   memset(&maps, 0, sizeof(maps));  // this entry point does not know the size of the pool: every tile is gathered
-  return launch_pdl(attn_decode_mma_kernel<false>, grid, dim3(128), (size_t)DEC_SMEM_B, (cudaStream_t)st, maps.k, maps.v,
+  return launch_pdl(attn_decode_mma_kernel<false, false>, grid, dim3(128), (size_t)DEC_SMEM_B, (cudaStream_t)st, maps.k, maps.v,
                     maps.rows, (const bf16*)q, q_stride, (bf16*)kcache, (bf16*)vcache, seq_q_start, seq_kv_len, page_indptr, page_ids, items,
                     n_items_ptr, part_o, part_ml, nh, nkv, ps, scale * 1.4426950408889634f, window,
                     head_tiles, (const float*)nullptr, 0, 0, 0, (int*)nullptr, (const float*)nullptr, 0, 0LL,
@@ -894,13 +898,16 @@ TKB_EXPORT int tkb_attn_decode_mma_bf16(const void* q, int q_stride, const void*
 // K-split product, [n_parts][tokens, C] spaced part_stride floats apart, which are added in order and
 // rounded to bfloat16 first.  rot is the rotary width (0: none); the pages of the requests must
 // already cover the tokens' positions.
+// tma: the step has work items of more than three tiles, so the instantiation that fetches whole tiles by TMA
+// is worth its registers and code; steps of short items (a request or two at short contexts) take the one
+// without, which measured 3 % faster a step there.
 TKB_EXPORT int tkb_attn_decode_rope_mma_bf16(const void* qkv, int q_stride, const float* qkv_parts, int n_parts,
                                              long long part_stride, void* kcache, void* vcache,
                                              const int* seq_q_start, const int* seq_kv_len, const int* page_indptr,
                                              const int* page_ids, const int* items, const int* n_items_ptr,
                                              int items_cap, float* part_o, float* part_ml, int nh, int nkv, int ps,
                                              float scale, int window, const float* inv_freq, int rot,
-                                             int write_cache, int num_pages, int* status, void* st) {
+                                             int write_cache, int num_pages, int tma, int* status, void* st) {
   if (items_cap <= 0) return 0;
   if (nkv <= 0 || nh % nkv != 0 || ps <= 0 || rot < 0 || rot > HD || (rot & 3)) return -2;
   int rc = ensure_smem_attr();
@@ -912,7 +919,8 @@ TKB_EXPORT int tkb_attn_decode_rope_mma_bf16(const void* qkv, int q_stride, cons
   KvMaps maps;
   rc = kv_maps(maps, kcache, vcache, num_pages, nkv, ps);
   if (rc) return rc;
-  return launch_pdl(attn_decode_mma_kernel<true>, grid, dim3(128), (size_t)DEC_SMEM_B, (cudaStream_t)st, maps.k, maps.v,
+  auto kernel = maps.rows > 0 && tma ? attn_decode_mma_kernel<true, true> : attn_decode_mma_kernel<true, false>;
+  return launch_pdl(kernel, grid, dim3(128), (size_t)DEC_SMEM_B, (cudaStream_t)st, maps.k, maps.v,
                     maps.rows, (const bf16*)qkv, q_stride, (bf16*)kcache, (bf16*)vcache, seq_q_start, seq_kv_len, page_indptr, page_ids, items,
                     n_items_ptr, part_o, part_ml, nh, nkv, ps, scale * 1.4426950408889634f, window,
                     head_tiles, inv_freq, rot, write_cache, num_pages, status, qkv_parts, n_parts, part_stride,
@@ -930,7 +938,7 @@ TKB_EXPORT int tkb_attn_decode_merged_bf16(const void* qkv, int q_stride, const 
                                            const int* items, const int* n_items_ptr, int items_cap, float* part_o,
                                            float* part_ml, int nh, int nkv, int ps, float scale, int window,
                                            int fused, const float* inv_freq, int rot, int write_cache,
-                                           int num_pages, int* status, int* counters, const int* item_entry,
+                                           int num_pages, int tma, int* status, int* counters, const int* item_entry,
                                            const int* dec_item_start, const int* out_row_of, void* out, int out_stride,
                                            void* st) {
   if (items_cap <= 0) return 0;
@@ -946,13 +954,14 @@ TKB_EXPORT int tkb_attn_decode_merged_bf16(const void* qkv, int q_stride, const 
   KvMaps maps;
   rc = kv_maps(maps, kcache, vcache, num_pages, nkv, ps);
   if (rc) return rc;
+  const bool with_tma = maps.rows > 0 && tma;
   if (fused)
-    return launch_pdl(attn_decode_mma_kernel<true>, grid, dim3(128), (size_t)DEC_SMEM_B, (cudaStream_t)st, maps.k,
+    return launch_pdl(with_tma ? attn_decode_mma_kernel<true, true> : attn_decode_mma_kernel<true, false>, grid, dim3(128), (size_t)DEC_SMEM_B, (cudaStream_t)st, maps.k,
                       maps.v, maps.rows, (const bf16*)qkv, q_stride, (bf16*)kcache, (bf16*)vcache, seq_q_start, seq_kv_len, page_indptr,
                       page_ids, items, n_items_ptr, part_o, part_ml, nh, nkv, ps, sl2, window, head_tiles,
                       inv_freq, rot, write_cache, num_pages, status, qkv_parts, n_parts, part_stride, counters,
                       item_entry, dec_item_start, out_row_of, (bf16*)out, out_stride);
-  return launch_pdl(attn_decode_mma_kernel<false>, grid, dim3(128), (size_t)DEC_SMEM_B, (cudaStream_t)st, maps.k,
+  return launch_pdl(with_tma ? attn_decode_mma_kernel<false, true> : attn_decode_mma_kernel<false, false>, grid, dim3(128), (size_t)DEC_SMEM_B, (cudaStream_t)st, maps.k,
                     maps.v, maps.rows, (const bf16*)qkv, q_stride, (bf16*)kcache, (bf16*)vcache, seq_q_start, seq_kv_len,
                     page_indptr, page_ids, items, n_items_ptr, part_o, part_ml, nh, nkv, ps, sl2, window, head_tiles,
                     (const float*)nullptr, 0, 0, num_pages, status, (const float*)nullptr, 0, 0LL, counters, item_entry,

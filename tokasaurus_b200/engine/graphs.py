@@ -83,7 +83,9 @@ class DecodeGraphs:
                     or int(n[4]) > c["rows"]:
                 return None
             caps[key] = c
-        key = ("general", tp, sp, tuple(page_caps), tuple(sorted((str(k), tuple(sorted(c.items()))) for k, c in caps.items())))
+        key = ("general", tp, sp, tuple(page_caps),
+               tuple(sorted((str(k), tuple(sorted(c.items())), int(raw[k]["counts"][5]), int(raw[k]["counts"][6]))
+                            for k, c in caps.items())))
         plans = {k: planners[k].pad_plan(p, caps[k]) for k, p in raw.items()}
         last = [int(ip[-1]) for ip in host.table_indptr]
         padded = HostBatch(
@@ -124,7 +126,8 @@ class DecodeGraphs:
             # the planner's own bound for this batch size; a plan beyond it (there should be none) gets a graph of its own
             cap = bound["items"] if bound is not None and items <= bound["items"] else _pow2_at_least(items, 8)
             caps[key] = dict(items=cap, dec=bp, tiles=0)
-        key = (bp, tuple(page_caps), tuple(sorted((str(k), c["items"]) for k, c in caps.items())))
+        # the kernels a graph holds are chosen at recording: whatever of a plan decides between variants is in the key
+        key = (bp, tuple(page_caps), tuple(sorted((str(k), c["items"], int(raw[k]["counts"][5])) for k, c in caps.items())))
         plans = {k: planners[k].pad_plan(p, caps[k]) for k, p in raw.items()}
         ex = dict(temperature=_pad(extra["temperature"], bp), stream_key=_pad(extra["stream_key"], bp),
                   sample_pos=_pad(extra["sample_pos"], bp), row_slot=_pad(extra["row_slot"], bp, -1))

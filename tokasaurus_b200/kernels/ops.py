@@ -365,11 +365,13 @@ def attn_decode_mma(qkv: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tenso
                     n_items: torch.Tensor, items_cap: int, dec_seqs: torch.Tensor, dec_item_start: torch.Tensor,
                     n_dec: torch.Tensor, dec_cap: int, out: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int,
                     page_size: int, scale: float, window: int | None,
-                    out_row_of: torch.Tensor | None = None, item_entry: torch.Tensor | None = None) -> None:
+                    out_row_of: torch.Tensor | None = None, item_entry: torch.Tensor | None = None,
+                    tma: bool = True) -> None:
     """bfloat16 split-key attention for requests that bring one token: ``items`` are (request row,
     first key, number of keys) triples, computed into float32 partial results and merged into
     ``out`` [T, n_heads*head_dim] at each request's token row (or at row ``out_row_of[request]``).
-    ``n_items``/``n_dec`` are device counters; the launch grids are sized by ``items_cap``/``dec_cap``."""
+    ``n_items``/``n_dec`` are device counters; the launch grids are sized by ``items_cap``/``dec_cap``.
+    ``tma``: some work item is longer than three tiles (the kernel variant that fetches tiles by TMA pays)."""
     _need_cuda(qkv, kcache, vcache, seq_q_start, seq_kv_len, page_indptr, page_ids, items, n_items, dec_seqs,
                dec_item_start, n_dec, out)
     check_head_dim(head_dim)
@@ -389,7 +391,7 @@ def attn_decode_mma(qkv: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tenso
             _ptr(seq_q_start), _ptr(seq_kv_len), _ptr(page_indptr), _ptr(page_ids), _ptr(items), _ptr(n_items),
             c_int(items_cap), _ptr(part_o), _ptr(part_ml), c_int(n_heads), c_int(n_kv_heads), c_int(page_size),
             c_float(scale), c_int(window or 0), c_int(0), _ptr(None), c_int(0), c_int(0), c_int(kcache.shape[0]),
-            _ptr(None), _ptr(counters), _ptr(item_entry), _ptr(dec_item_start),
+            c_int(1 if tma else 0), _ptr(None), _ptr(counters), _ptr(item_entry), _ptr(dec_item_start),
             _ptr(out_row_of if out_row_of is not None else seq_q_start), _ptr(out), c_int(out.shape[1]), _stream()),
             "attn_decode_merged")
         return
@@ -410,7 +412,8 @@ def attn_decode_rope_mma(qkv: torch.Tensor, kcache: torch.Tensor, vcache: torch.
                          dec_item_start: torch.Tensor, n_dec: torch.Tensor, dec_cap: int, out: torch.Tensor,
                          n_heads: int, n_kv_heads: int, head_dim: int, page_size: int, scale: float,
                          window: int | None, inv_freq: torch.Tensor | None, rotary_dim: int,
-                         write_cache: bool, status: torch.Tensor, item_entry: torch.Tensor | None = None) -> None:
+                         write_cache: bool, status: torch.Tensor, item_entry: torch.Tensor | None = None,
+                         tma: bool = True) -> None:
     """``attn_decode_mma`` with rotary encoding and the cache write folded in: ``qkv`` holds the step's
     un-rotated q|k|v rows of requests that bring one token each, as bfloat16 [T, C] or as the float32 slices
     [slices, T, C] of a K-split product (``linear_smallm``); C = (n_heads + 2 n_kv_heads) * head_dim."""
@@ -442,7 +445,8 @@ def attn_decode_rope_mma(qkv: torch.Tensor, kcache: torch.Tensor, vcache: torch.
             _ptr(vcache), _ptr(seq_q_start), _ptr(seq_kv_len), _ptr(page_indptr), _ptr(page_ids), _ptr(items),
             _ptr(n_items), c_int(items_cap), _ptr(part_o), _ptr(part_ml), c_int(n_heads), c_int(n_kv_heads),
             c_int(page_size), c_float(scale), c_int(window or 0), c_int(1), _ptr(inv_freq),
-            c_int(rotary_dim), c_int(1 if write_cache else 0), c_int(kcache.shape[0]), _ptr(status), _ptr(counters),
+            c_int(rotary_dim), c_int(1 if write_cache else 0), c_int(kcache.shape[0]), c_int(1 if tma else 0),
+            _ptr(status), _ptr(counters),
             _ptr(item_entry), _ptr(dec_item_start), _ptr(seq_q_start), _ptr(out), c_int(out.shape[1]), _stream()),
             "attn_decode_merged")
         return
@@ -451,8 +455,8 @@ def attn_decode_rope_mma(qkv: torch.Tensor, kcache: torch.Tensor, vcache: torch.
         _ptr(vcache), _ptr(seq_q_start), _ptr(seq_kv_len),
         _ptr(page_indptr), _ptr(page_ids), _ptr(items), _ptr(n_items), c_int(items_cap), _ptr(part_o), _ptr(part_ml),
         c_int(n_heads), c_int(n_kv_heads), c_int(page_size), c_float(scale), c_int(window or 0),
-        _ptr(inv_freq), c_int(rotary_dim), c_int(1 if write_cache else 0), c_int(kcache.shape[0]), _ptr(status),
-        _stream()), "attn_decode_rope_mma")
+        _ptr(inv_freq), c_int(rotary_dim), c_int(1 if write_cache else 0), c_int(kcache.shape[0]),
+        c_int(1 if tma else 0), _ptr(status), _stream()), "attn_decode_rope_mma")
     _check(_fn(lib, "tkb_attn_decode_merge_bf16")(
         _ptr(part_o), _ptr(part_ml), _ptr(dec_seqs), _ptr(dec_item_start), _ptr(n_dec), c_int(dec_cap),
         _ptr(seq_q_start), _ptr(out), c_int(out.shape[1]), c_int(n_heads), _stream()), "attn_decode_merge")

@@ -119,7 +119,12 @@ def plan_attention(host, window: int | None, capacity: dict | None = None, block
                      row_item_entry=i32(r_item),
                      row_token=i32(rows), row_kv_len=i32(r_kv), row_seq=i32(np.asarray(host.token_seq)[rows]),
                      row_index=i32(np.arange(n_rows)))
-    counts = np.asarray([n_items, dec_seqs.shape[0], n_tiles, n_row_items, n_rows, 0, 0, 0], dtype=np.int32)
+    # counts[5], counts[6]: some work item of the requests that decode (of the wanted rows) is longer than three
+    # tiles of 64 keys; the split-key kernel then runs in the variant that fetches whole tiles by TMA
+    long_items = int(n_items > 0 and int(item_size.max()) > 3 * 64)
+    long_row_items = int(n_row_items > 0 and int(r_isize.max()) > 3 * 64)
+    counts = np.asarray([n_items, dec_seqs.shape[0], n_tiles, n_row_items, n_rows, long_items, long_row_items, 0],
+                        dtype=np.int32)
 
     def padded(x, n):
         a = np.zeros(max(n, x.shape[0], 1), dtype=np.int32)
@@ -254,7 +259,7 @@ class PagedAttention(Mixer):
                                          plan["dec_seqs"], plan["dec_item_start"], c[1:2],
                                          caps["dec"] if caps else int(counts[1]), attn, nh, nkv, hd, cache.page_size,
                                          self.scale, self.window, self.inv_freq, rot, cache.writable,
-                                         ctx.status, item_entry=plan["item_entry"])
+                                         ctx.status, item_entry=plan["item_entry"], tma=bool(counts[5]))
                 if residual is not None:
                     ops.linear_decode(attn, self.w_o, "add", out=residual)
                     return None
@@ -278,7 +283,7 @@ class PagedAttention(Mixer):
                                          plan["dec_seqs"], plan["dec_item_start"], c[1:2],
                                          caps["dec"] if caps else int(counts[1]), attn, nh, nkv, hd, cache.page_size,
                                          self.scale, self.window, self.inv_freq, rot, cache.writable,
-                                         ctx.status, item_entry=plan["item_entry"])
+                                         ctx.status, item_entry=plan["item_entry"], tma=bool(counts[5]))
                 return few(attn, self.w_o)
             qkv = torch.empty((T, nh * hd), dtype=h.dtype, device=h.device)  # q only; k and v go straight to the cache
             ops.rope_kv_write_partials(parts, qkv, ctx.positions, ctx.token_seq, tables.indptr, tables.page_ids,
@@ -304,7 +309,7 @@ class PagedAttention(Mixer):
                                 tables.page_ids, plan["row_items"], c[3:4], n_items, plan["row_index"],
                                 plan["row_item_start"], c[4:5], n_rows, attn, nh, nkv, hd, cache.page_size,
                                 self.scale, self.window, out_row_of=plan["row_index"],
-                                item_entry=plan["row_item_entry"])
+                                item_entry=plan["row_item_entry"], tma=bool(counts[6]))
             return project(attn, self.w_o)
         if plan is None or out_rows is not None:
             # float32, or only some rows are wanted: the FP32-pipe kernel, one warp per (row, head)
@@ -324,7 +329,7 @@ class PagedAttention(Mixer):
             ops.attn_decode_mma(qkv, cache.k, cache.v, ctx.seq_q_start, ctx.seq_kv_len, tables.indptr, tables.page_ids,
                                 plan["items"], c[0:1], items_cap, plan["dec_seqs"], plan["dec_item_start"], c[1:2],
                                 dec_cap, attn, nh, nkv, hd, cache.page_size, self.scale, self.window,
-                                item_entry=plan["item_entry"])
+                                item_entry=plan["item_entry"], tma=bool(counts[5]))
         if tiles_cap and self._query_tile() == QUERY_TILE_TC:
             ops.attn_prefill_tc(qkv, attn, cache.k, cache.v, ctx.seq_q_start, ctx.seq_q_len, ctx.seq_kv_len,
                                 tables.indptr, tables.page_ids, plan["tiles"], c[2:3], tiles_cap, nh, nkv, hd,
