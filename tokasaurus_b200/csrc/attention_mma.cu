@@ -50,8 +50,9 @@ constexpr int STAGE_B = 2 * TILE_B;   // K tile then V tile
 constexpr int SMEM_ALIGN = SWZ ? 1024 : 128;   // the swizzle pattern repeats every 1,024 bytes
 constexpr int SMEM_B = 2 * STAGE_B + SMEM_ALIGN;  // two stages (tiled kernel for portions)
 // The split-key kernel: three stages where they leave room for two or three blocks an SM (three at head sizes
-// to 80, two to 128), else two.  Four stages at head size 64 were measured slower: the blocks of a step then
-// no longer fit the SMs all at once.
+// to 80, two to 128), else two.  Four stages at head size 64 were measured slower, with padded rows (the
+// blocks of a step then no longer fit the SMs all at once) and again with the swizzled layout, where three
+// blocks of 65 KiB should fit an SM (batch 64: 38 k -> 30 k tok/s; batch 8 unchanged).
 constexpr int DSTAGES = 3 * STAGE_B <= 110 * 1024 ? 3 : 2;
 constexpr int DEC_SMEM_B = DSTAGES * STAGE_B + SMEM_ALIGN;
 // byte offset of 16-byte chunk `chunk` of row `row` within a tile
