@@ -343,3 +343,61 @@ def test_warm_up_records_the_decode_graphs(tiny_model_dirs):
     with pytest.raises(RuntimeError):
         eng.add_request(prompts[0], max_num_tokens=4)
         eng.warm_up()
+
+
+def test_llama_1b_layer_sizes_bfloat16_against_float32():
+    """Two layers of the sizes the benchmark runs (hidden 2,048, 32 heads of 64 on 8 kv heads, inner 8,192,
+    vocabulary 128,256), random weights: the bfloat16 path (tcgen05 attention and gate/up product for the
+    prompts, K-split products, fused rotary + split-key attention with TMA tiles and the step graph for the
+    decoded tokens) against the float32 path of the same engine, which the tiny models tie to the plain
+    implementation.  Eight prompts of about 1,400 tokens, so that the split-key kernel gets work items of four
+    tiles; then five decoded tokens each (the float32 path's greedy choice is fed to both)."""
+    from tokasaurus_b200.engine.batch import StepEntry
+    from tokasaurus_b200.engine.engine import Engine
+
+    cfg = dict(architectures=["LlamaForCausalLM"], model_type="llama", num_hidden_layers=2, hidden_size=2048,
+               num_attention_heads=32, num_key_value_heads=8, intermediate_size=8192, vocab_size=128256,
+               rope_theta=500000.0, rope_scaling=dict(rope_type="llama3", factor=32.0, low_freq_factor=1.0,
+                                                      high_freq_factor=4.0, original_max_position_embeddings=8192),
+               rms_norm_eps=1e-5, tie_word_embeddings=True, max_position_embeddings=131072)
+    lengths = [1400, 1337, 1290, 1411, 1376, 1302, 1455, 1360]
+    prompts = [cuttings.random_tokens(n, cfg["vocab_size"], 900 + i) for i, n in enumerate(lengths)]
+    ids = [f"p{i}" for i in range(len(prompts))]
+
+    def run(dtype, feed=None):
+        eng = Engine(config_dict=cfg, random_weights=0, dtype=dtype, page_size=16, kv_cache_num_tokens=8 * 1536,
+                     max_tokens_per_forward=8192, max_seqs_per_forward=8)
+        runner, cache = eng.runner, eng.runner.cache
+        rows = []  # [step][request] -> logits
+        for rid, p in zip(ids, prompts):
+            cache.admit(rid)
+            cache.ensure_capacity(rid, len(p) + 6)
+        first = []
+        for half in (slice(0, 4), slice(4, 8)):
+            entries = [StepEntry(rid, p, 0, [len(p) - 1]) for rid, p in zip(ids[half], prompts[half])]
+            first.append(runner.step(entries).float().cpu())
+        rows.append(torch.cat(first))
+        for t in range(5):
+            tokens = rows[-1].argmax(-1).tolist() if feed is None else feed[t]
+            entries = [StepEntry(rid, [tok], len(p) + t, [0]) for rid, p, tok in zip(ids, prompts, tokens)]
+            R = len(entries)
+            extra = dict(temperature=np.zeros(R, dtype=np.float32), stream_key=np.zeros(R, dtype=np.int64),
+                         sample_pos=np.zeros(R, dtype=np.int32), row_slot=np.full(R, -1, dtype=np.int32))
+            if dtype == "bfloat16" and eng.graphs is not None and eng.graphs.usable(entries):
+                prep = eng.graphs.prepare(entries, extra)
+                assert int(prep["plans"][next(iter(prep["plans"]))]["counts"][5]) == 1, "work items of four tiles expected"
+                eng.graphs.launch(prep)
+                rows.append(eng.graphs.graphs[prep["key"]]["logits"][:R].float().cpu())
+            else:
+                rows.append(runner.step(entries).float().cpu())
+        runner.check_status()
+        return rows
+
+    want = run("float32")
+    feed = [w.argmax(-1).tolist() for w in want[:-1]]
+    got = run("bfloat16", feed)
+    for t, (g, w) in enumerate(zip(got, want)):
+        tol = 0.03 * w.abs().max().item()
+        err = (g - w).abs().max(dim=1).values
+        print(f"step {t}: largest error {err.max().item():.3g} of max |logit| {w.abs().max().item():.3g} (tolerance {tol:.3g})")
+        assert (err <= tol).all(), f"step {t}: largest error {err.max().item():.3g}, tolerance {tol:.3g}, rows {err.tolist()}"
