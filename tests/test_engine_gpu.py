@@ -345,9 +345,11 @@ def test_warm_up_records_the_decode_graphs(tiny_model_dirs):
         eng.warm_up()
 
 
-def test_llama_1b_layer_sizes_bfloat16_against_float32():
+@pytest.mark.parametrize("sizes", ["1b", "8b"])
+def test_llama_layer_sizes_bfloat16_against_float32(sizes):
     """Two layers of the sizes the benchmark runs (hidden 2,048, 32 heads of 64 on 8 kv heads, inner 8,192,
-    vocabulary 128,256), random weights: the bfloat16 path (tcgen05 attention and gate/up product for the
+    vocabulary 128,256), or one layer of Llama-3.1-8B's (hidden 4,096, 32 heads of 128 on 8 kv heads, inner
+    14,336; vocabulary 32,000, untied), random weights: the bfloat16 path (tcgen05 attention and gate/up product for the
     prompts, K-split products, fused rotary + split-key attention with TMA tiles and the step graph for the
     decoded tokens) against the float32 path of the same engine, which the tiny models tie to the plain
     implementation.  Eight prompts of about 1,400 tokens, so that the split-key kernel gets work items of four
@@ -360,6 +362,9 @@ def test_llama_1b_layer_sizes_bfloat16_against_float32():
                rope_theta=500000.0, rope_scaling=dict(rope_type="llama3", factor=32.0, low_freq_factor=1.0,
                                                       high_freq_factor=4.0, original_max_position_embeddings=8192),
                rms_norm_eps=1e-5, tie_word_embeddings=True, max_position_embeddings=131072)
+    if sizes == "8b":
+        cfg.update(num_hidden_layers=1, hidden_size=4096, intermediate_size=14336, vocab_size=32000,
+                   tie_word_embeddings=False)
     lengths = [1400, 1337, 1290, 1411, 1376, 1302, 1455, 1360]
     prompts = [cuttings.random_tokens(n, cfg["vocab_size"], 900 + i) for i, n in enumerate(lengths)]
     ids = [f"p{i}" for i in range(len(prompts))]
