@@ -270,9 +270,18 @@ __device__ __forceinline__ float2 merge_splits(const float* __restrict__ part_o,
 // FUSED: q points at the un-rotated q|k|v rows of the step [tokens, (nh + 2 nkv) * HD]; the kernel rotates
 // q on the fly, and the block that owns the split holding the token's own position rotates this kv
 // head's k, writes it and v into the cache page, and only then reads its tiles.
+// The TMA descriptors of the K and V cache as a kernel parameter: two of them for the instantiation that uses
+// them, nothing for the other (256 bytes of parameters less to hand to every launch).
+template <bool TMA>
+struct KvMapsParam {
+  CUtensorMap k, v;
+};
+template <>
+struct KvMapsParam<false> {};
+
 template <bool FUSED, bool TMA>
 __global__ void __launch_bounds__(128)
-attn_decode_mma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, int tma_rows,
+attn_decode_mma_kernel(const __grid_constant__ KvMapsParam<TMA> maps, int tma_rows,
                        const bf16* __restrict__ q, int q_stride, bf16* __restrict__ kcache,
                        bf16* __restrict__ vcache, const int* __restrict__ seq_q_start,
                        const int* __restrict__ seq_kv_len, const int* __restrict__ page_indptr,
@@ -337,8 +346,10 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
       const int key = k_begin + tile * KT + tma_box * tma_rows;
       const int row = (page * nkv + kvh) * ps + (key & (ps - 1));
       unsigned char* dst = stage + tma_atom * ATOM_B + tma_box * tma_rows * 128;
-      tkb5::tma_load_2d(dst, &map_k, bar, tma_atom * 64, row);
-      tkb5::tma_load_2d(dst + TILE_B, &map_v, bar, tma_atom * 64, row);
+      if constexpr (TMA) {
+        tkb5::tma_load_2d(dst, &maps.k, bar, tma_atom * 64, row);
+        tkb5::tma_load_2d(dst + TILE_B, &maps.v, bar, tma_atom * 64, row);
+      }
     }
   };
   if (use_tma) {
@@ -863,6 +874,16 @@ static int kv_maps(KvMaps& m, const void* kcache, const void* vcache, long long 
   return 0;
 }
 
+template <bool FUSED, bool TMA, typename... Rest>
+static int launch_decode(dim3 grid, cudaStream_t st, const KvMaps& maps, Rest... rest) {
+  KvMapsParam<TMA> param;
+  if constexpr (TMA) {
+    param.k = maps.k;
+    param.v = maps.v;
+  }
+  return launch_pdl(attn_decode_mma_kernel<FUSED, TMA>, grid, dim3(128), (size_t)DEC_SMEM_B, st, param, maps.rows, rest...);
+}
+
 }  // namespace
 
 // Scratch a decode launch needs for `items_cap` work items: floats of part_o and of part_ml.
@@ -887,8 +908,7 @@ TKB_EXPORT int tkb_attn_decode_mma_bf16(const void* q, int q_stride, const void*
   dim3 grid(items_cap, nkv * head_tiles);
   KvMaps maps;
   memset(&maps, 0, sizeof(maps));  // this entry point does not know the size of the pool: every tile is gathered
-  return launch_pdl(attn_decode_mma_kernel<false, false>, grid, dim3(128), (size_t)DEC_SMEM_B, (cudaStream_t)st, maps.k, maps.v,
-                    maps.rows, (const bf16*)q, q_stride, (bf16*)kcache, (bf16*)vcache, seq_q_start, seq_kv_len, page_indptr, page_ids, items,
+  return launch_decode<false, false>(grid, (cudaStream_t)st, maps, (const bf16*)q, q_stride, (bf16*)kcache, (bf16*)vcache, seq_q_start, seq_kv_len, page_indptr, page_ids, items,
                     n_items_ptr, part_o, part_ml, nh, nkv, ps, scale * 1.4426950408889634f, window,
                     head_tiles, (const float*)nullptr, 0, 0, 0, (int*)nullptr, (const float*)nullptr, 0, 0LL,
                     (int*)nullptr, (const int*)nullptr, (const int*)nullptr, (const int*)nullptr, (bf16*)nullptr, 0);
@@ -920,9 +940,12 @@ TKB_EXPORT int tkb_attn_decode_rope_mma_bf16(const void* qkv, int q_stride, cons
   KvMaps maps;
   rc = kv_maps(maps, kcache, vcache, num_pages, nkv, ps);
   if (rc) return rc;
-  auto kernel = maps.rows > 0 && tma ? attn_decode_mma_kernel<true, true> : attn_decode_mma_kernel<true, false>;
-  return launch_pdl(kernel, grid, dim3(128), (size_t)DEC_SMEM_B, (cudaStream_t)st, maps.k, maps.v,
-                    maps.rows, (const bf16*)qkv, q_stride, (bf16*)kcache, (bf16*)vcache, seq_q_start, seq_kv_len, page_indptr, page_ids, items,
+  if (maps.rows > 0 && tma)
+    return launch_decode<true, true>(grid, (cudaStream_t)st, maps, (const bf16*)qkv, q_stride, (bf16*)kcache, (bf16*)vcache, seq_q_start, seq_kv_len, page_indptr, page_ids, items,
+                    n_items_ptr, part_o, part_ml, nh, nkv, ps, scale * 1.4426950408889634f, window,
+                    head_tiles, inv_freq, rot, write_cache, num_pages, status, qkv_parts, n_parts, part_stride,
+                    (int*)nullptr, (const int*)nullptr, (const int*)nullptr, (const int*)nullptr, (bf16*)nullptr, 0);
+  return launch_decode<true, false>(grid, (cudaStream_t)st, maps, (const bf16*)qkv, q_stride, (bf16*)kcache, (bf16*)vcache, seq_q_start, seq_kv_len, page_indptr, page_ids, items,
                     n_items_ptr, part_o, part_ml, nh, nkv, ps, scale * 1.4426950408889634f, window,
                     head_tiles, inv_freq, rot, write_cache, num_pages, status, qkv_parts, n_parts, part_stride,
                     (int*)nullptr, (const int*)nullptr, (const int*)nullptr, (const int*)nullptr, (bf16*)nullptr, 0);
@@ -957,13 +980,21 @@ TKB_EXPORT int tkb_attn_decode_merged_bf16(const void* qkv, int q_stride, const 
   if (rc) return rc;
   const bool with_tma = maps.rows > 0 && tma;
   if (fused)
-    return launch_pdl(with_tma ? attn_decode_mma_kernel<true, true> : attn_decode_mma_kernel<true, false>, grid, dim3(128), (size_t)DEC_SMEM_B, (cudaStream_t)st, maps.k,
-                      maps.v, maps.rows, (const bf16*)qkv, q_stride, (bf16*)kcache, (bf16*)vcache, seq_q_start, seq_kv_len, page_indptr,
+  {
+    if (with_tma) return launch_decode<true, true>(grid, (cudaStream_t)st, maps, (const bf16*)qkv, q_stride, (bf16*)kcache, (bf16*)vcache, seq_q_start, seq_kv_len, page_indptr,
                       page_ids, items, n_items_ptr, part_o, part_ml, nh, nkv, ps, sl2, window, head_tiles,
                       inv_freq, rot, write_cache, num_pages, status, qkv_parts, n_parts, part_stride, counters,
                       item_entry, dec_item_start, out_row_of, (bf16*)out, out_stride);
-  return launch_pdl(with_tma ? attn_decode_mma_kernel<false, true> : attn_decode_mma_kernel<false, false>, grid, dim3(128), (size_t)DEC_SMEM_B, (cudaStream_t)st, maps.k,
-                    maps.v, maps.rows, (const bf16*)qkv, q_stride, (bf16*)kcache, (bf16*)vcache, seq_q_start, seq_kv_len,
+    return launch_decode<true, false>(grid, (cudaStream_t)st, maps, (const bf16*)qkv, q_stride, (bf16*)kcache, (bf16*)vcache, seq_q_start, seq_kv_len, page_indptr,
+                      page_ids, items, n_items_ptr, part_o, part_ml, nh, nkv, ps, sl2, window, head_tiles,
+                      inv_freq, rot, write_cache, num_pages, status, qkv_parts, n_parts, part_stride, counters,
+                      item_entry, dec_item_start, out_row_of, (bf16*)out, out_stride);
+  }
+  if (with_tma) return launch_decode<false, true>(grid, (cudaStream_t)st, maps, (const bf16*)qkv, q_stride, (bf16*)kcache, (bf16*)vcache, seq_q_start, seq_kv_len,
+                    page_indptr, page_ids, items, n_items_ptr, part_o, part_ml, nh, nkv, ps, sl2, window, head_tiles,
+                    (const float*)nullptr, 0, 0, num_pages, status, (const float*)nullptr, 0, 0LL, counters, item_entry,
+                    dec_item_start, out_row_of, (bf16*)out, out_stride);
+  return launch_decode<false, false>(grid, (cudaStream_t)st, maps, (const bf16*)qkv, q_stride, (bf16*)kcache, (bf16*)vcache, seq_q_start, seq_kv_len,
                     page_indptr, page_ids, items, n_items_ptr, part_o, part_ml, nh, nkv, ps, sl2, window, head_tiles,
                     (const float*)nullptr, 0, 0, num_pages, status, (const float*)nullptr, 0, 0LL, counters, item_entry,
                     dec_item_start, out_row_of, (bf16*)out, out_stride);
