@@ -874,14 +874,20 @@ static int kv_maps(KvMaps& m, const void* kcache, const void* vcache, long long 
   return 0;
 }
 
+// Launch of the split-key kernel: the instantiation with TMA tiles if `tma` and there are descriptors
 template <bool FUSED, bool TMA, typename... Rest>
-static int launch_decode(dim3 grid, cudaStream_t st, const KvMaps& maps, Rest... rest) {
+static int launch_decode_as(dim3 grid, cudaStream_t st, const KvMaps& maps, Rest... rest) {
   KvMapsParam<TMA> param;
   if constexpr (TMA) {
     param.k = maps.k;
     param.v = maps.v;
   }
   return launch_pdl(attn_decode_mma_kernel<FUSED, TMA>, grid, dim3(128), (size_t)DEC_SMEM_B, st, param, maps.rows, rest...);
+}
+template <bool FUSED, typename... Rest>
+static int launch_decode(bool tma, dim3 grid, void* st, const KvMaps& maps, Rest... rest) {
+  if (tma && maps.rows > 0) return launch_decode_as<FUSED, true>(grid, (cudaStream_t)st, maps, rest...);
+  return launch_decode_as<FUSED, false>(grid, (cudaStream_t)st, maps, rest...);
 }
 
 }  // namespace
@@ -908,10 +914,11 @@ TKB_EXPORT int tkb_attn_decode_mma_bf16(const void* q, int q_stride, const void*
   dim3 grid(items_cap, nkv * head_tiles);
   KvMaps maps;
   memset(&maps, 0, sizeof(maps));  // this entry point does not know the size of the pool: every tile is gathered
-  return launch_decode<false, false>(grid, (cudaStream_t)st, maps, (const bf16*)q, q_stride, (bf16*)kcache, (bf16*)vcache, seq_q_start, seq_kv_len, page_indptr, page_ids, items,
-                    n_items_ptr, part_o, part_ml, nh, nkv, ps, scale * 1.4426950408889634f, window,
-                    head_tiles, (const float*)nullptr, 0, 0, 0, (int*)nullptr, (const float*)nullptr, 0, 0LL,
-                    (int*)nullptr, (const int*)nullptr, (const int*)nullptr, (const int*)nullptr, (bf16*)nullptr, 0);
+  return launch_decode<false>(false, grid, st, maps, (const bf16*)q, q_stride, (bf16*)kcache, (bf16*)vcache, seq_q_start,
+                              seq_kv_len, page_indptr, page_ids, items, n_items_ptr, part_o, part_ml, nh, nkv, ps,
+                              scale * 1.4426950408889634f, window, head_tiles, (const float*)nullptr, 0, 0, 0,
+                              (int*)nullptr, (const float*)nullptr, 0, 0LL, (int*)nullptr, (const int*)nullptr,
+                              (const int*)nullptr, (const int*)nullptr, (bf16*)nullptr, 0);
 }
 
 // The same with rotary encoding and the cache write folded in: qkv holds the step's un-rotated q|k|v rows
@@ -940,15 +947,11 @@ TKB_EXPORT int tkb_attn_decode_rope_mma_bf16(const void* qkv, int q_stride, cons
   KvMaps maps;
   rc = kv_maps(maps, kcache, vcache, num_pages, nkv, ps);
   if (rc) return rc;
-  if (maps.rows > 0 && tma)
-    return launch_decode<true, true>(grid, (cudaStream_t)st, maps, (const bf16*)qkv, q_stride, (bf16*)kcache, (bf16*)vcache, seq_q_start, seq_kv_len, page_indptr, page_ids, items,
-                    n_items_ptr, part_o, part_ml, nh, nkv, ps, scale * 1.4426950408889634f, window,
-                    head_tiles, inv_freq, rot, write_cache, num_pages, status, qkv_parts, n_parts, part_stride,
-                    (int*)nullptr, (const int*)nullptr, (const int*)nullptr, (const int*)nullptr, (bf16*)nullptr, 0);
-  return launch_decode<true, false>(grid, (cudaStream_t)st, maps, (const bf16*)qkv, q_stride, (bf16*)kcache, (bf16*)vcache, seq_q_start, seq_kv_len, page_indptr, page_ids, items,
-                    n_items_ptr, part_o, part_ml, nh, nkv, ps, scale * 1.4426950408889634f, window,
-                    head_tiles, inv_freq, rot, write_cache, num_pages, status, qkv_parts, n_parts, part_stride,
-                    (int*)nullptr, (const int*)nullptr, (const int*)nullptr, (const int*)nullptr, (bf16*)nullptr, 0);
+  return launch_decode<true>(tma != 0, grid, st, maps, (const bf16*)qkv, q_stride, (bf16*)kcache, (bf16*)vcache, seq_q_start,
+                             seq_kv_len, page_indptr, page_ids, items, n_items_ptr, part_o, part_ml, nh, nkv, ps,
+                             scale * 1.4426950408889634f, window, head_tiles, inv_freq, rot, write_cache, num_pages,
+                             status, qkv_parts, n_parts, part_stride, (int*)nullptr, (const int*)nullptr,
+                             (const int*)nullptr, (const int*)nullptr, (bf16*)nullptr, 0);
 }
 
 // Split-key attention with the merge of the splits inside the same kernel (the last block to finish a request's
@@ -978,26 +981,17 @@ TKB_EXPORT int tkb_attn_decode_merged_bf16(const void* qkv, int q_stride, const 
   KvMaps maps;
   rc = kv_maps(maps, kcache, vcache, num_pages, nkv, ps);
   if (rc) return rc;
-  const bool with_tma = maps.rows > 0 && tma;
   if (fused)
-  {
-    if (with_tma) return launch_decode<true, true>(grid, (cudaStream_t)st, maps, (const bf16*)qkv, q_stride, (bf16*)kcache, (bf16*)vcache, seq_q_start, seq_kv_len, page_indptr,
-                      page_ids, items, n_items_ptr, part_o, part_ml, nh, nkv, ps, sl2, window, head_tiles,
-                      inv_freq, rot, write_cache, num_pages, status, qkv_parts, n_parts, part_stride, counters,
-                      item_entry, dec_item_start, out_row_of, (bf16*)out, out_stride);
-    return launch_decode<true, false>(grid, (cudaStream_t)st, maps, (const bf16*)qkv, q_stride, (bf16*)kcache, (bf16*)vcache, seq_q_start, seq_kv_len, page_indptr,
-                      page_ids, items, n_items_ptr, part_o, part_ml, nh, nkv, ps, sl2, window, head_tiles,
-                      inv_freq, rot, write_cache, num_pages, status, qkv_parts, n_parts, part_stride, counters,
-                      item_entry, dec_item_start, out_row_of, (bf16*)out, out_stride);
-  }
-  if (with_tma) return launch_decode<false, true>(grid, (cudaStream_t)st, maps, (const bf16*)qkv, q_stride, (bf16*)kcache, (bf16*)vcache, seq_q_start, seq_kv_len,
-                    page_indptr, page_ids, items, n_items_ptr, part_o, part_ml, nh, nkv, ps, sl2, window, head_tiles,
-                    (const float*)nullptr, 0, 0, num_pages, status, (const float*)nullptr, 0, 0LL, counters, item_entry,
-                    dec_item_start, out_row_of, (bf16*)out, out_stride);
-  return launch_decode<false, false>(grid, (cudaStream_t)st, maps, (const bf16*)qkv, q_stride, (bf16*)kcache, (bf16*)vcache, seq_q_start, seq_kv_len,
-                    page_indptr, page_ids, items, n_items_ptr, part_o, part_ml, nh, nkv, ps, sl2, window, head_tiles,
-                    (const float*)nullptr, 0, 0, num_pages, status, (const float*)nullptr, 0, 0LL, counters, item_entry,
-                    dec_item_start, out_row_of, (bf16*)out, out_stride);
+    return launch_decode<true>(tma != 0, grid, st, maps, (const bf16*)qkv, q_stride, (bf16*)kcache, (bf16*)vcache,
+                               seq_q_start, seq_kv_len, page_indptr, page_ids, items, n_items_ptr, part_o, part_ml, nh, nkv,
+                               ps, sl2, window, head_tiles, inv_freq, rot, write_cache, num_pages, status, qkv_parts,
+                               n_parts, part_stride, counters, item_entry, dec_item_start, out_row_of, (bf16*)out,
+                               out_stride);
+  return launch_decode<false>(tma != 0, grid, st, maps, (const bf16*)qkv, q_stride, (bf16*)kcache, (bf16*)vcache,
+                              seq_q_start, seq_kv_len, page_indptr, page_ids, items, n_items_ptr, part_o, part_ml, nh, nkv,
+                              ps, sl2, window, head_tiles, (const float*)nullptr, 0, 0, num_pages, status,
+                              (const float*)nullptr, 0, 0LL, counters, item_entry, dec_item_start, out_row_of, (bf16*)out,
+                              out_stride);
 }
 
 TKB_EXPORT int tkb_attn_decode_merge_bf16(const float* part_o, const float* part_ml, const int* dec_seqs,
