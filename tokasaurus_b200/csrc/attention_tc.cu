@@ -8,20 +8,26 @@
 //     softmax          a warpgroup per head, one thread per query row (a lane of tensor memory): two passes of
 //                      tcgen05.ld over S (row maximum, then exp2 and row sum), no shuffles; P (bfloat16) goes to
 //                      shared memory in the 128-byte-swizzled K-major layout
-//     O_tile = P . V   tcgen05.mma 128 x 64 x 16, eight per tile; V stays as the cache holds it ([key][head
-//                      size]), described to the tensor core as an MN-major operand
-//     O = O * alpha + O_tile   in registers (float32), alpha from the running maximum
+//     O += P . V       tcgen05.mma 128 x 64 x 16, eight per tile, accumulating in tensor memory over ALL tiles; V
+//                      stays as the cache holds it ([key][head size]), described to the tensor core as an
+//                      MN-major operand
+// The exponentials of a row use a reference that stays put while the row's scores stay below reference + 16
+// (probabilities up to 2^16 are no problem for bfloat16 or for float32 sums).  When a row tops that, its warp
+// waits for the P . V products issued so far, reads its 32 lanes of O, scales the rows concerned and writes
+// them back (tcgen05.st): rare after the first tiles, so the loop has no pass over O and a thread keeps no
+// output in registers (104 registers a thread; folding an O tile into registers every key tile took 158 and
+// measured 2 % slower).  The row sum l follows the same reference; O / l at the end does not depend on it.
 // Roles: warps 0-3 and 4-7 softmax and output of the two heads; warp 8 brings K tiles and warp 9 V tiles, two
 // buffers each: a tile whose 128 keys all exist comes by TMA, one box per page through the block table (page
 // sizes that are powers of two from 8 up); the request's last, partial tile and other page sizes are gathered
 // with cp.async, zero-filling keys beyond the request.  Warps 10 and 11 issue the MMAs, one lane each, one
 // warp per head: the tensor core is fed by single threads, and two instruction streams feed it twice as fast.
 // Warp 10 also allocates tensor memory.  The second head starts half a tile behind the first, so that one
-// head's exponentials run while the other folds O and scans for its row maxima.
-// P and the O tile are double buffered, and a thread folds the O tile of two tiles ago: after it has handed
-// P_j over it never waits for P_j . V; the tensor core computes Q . K_{j+1}^T first, then P_j . V, while the
-// thread folds O_{j-1} and starts on S_{j+1}.  The exponentials (the special-function unit) are the bound.
-// One block per SM (225 KiB of shared memory, all 512 columns of tensor memory).  Tensor memory is taken only
+// head's exponentials run while the other scans for its row maxima.  P is double buffered: after a thread has
+// handed P_j over it never waits for P_j . V; the tensor core computes Q . K_{j+1}^T first, then P_j . V, while
+// the thread starts on S_{j+1}.  The softmax warps (one a scheduler and head) are the bound: trading ex2 for a
+// polynomial on the FMA pipe, or pairs of float32 operations for the packed f32x2 forms, measured no faster.
+// One block per SM (225 KiB of shared memory, 384 columns of tensor memory in use).  Tensor memory is taken only
 // after the kernel ahead in the stream has finished.  Every wait on an mbarrier is bounded; after the limit
 // the block sets TKB_STATUS_WAIT_TIMEOUT and leaves.
 #include "tcgen05.cuh"
@@ -38,7 +44,7 @@ constexpr int Q_BYTES = BQ * HD * 2;    // 16 KiB
 constexpr int KV_BYTES = BKV * HD * 2;  // 16 KiB
 constexpr int P_BYTES = BQ * BKV * 2;   // 32 KiB: two [128 x 64] atoms
 constexpr int SMEM_BYTES = 2 * Q_BYTES + 2 * KV_BYTES + 2 * KV_BYTES + 4 * P_BYTES + 1024;
-constexpr uint32_t TMEM_COLS = 512;     // S of head 0, S of head 1, two O tiles for each
+constexpr uint32_t TMEM_COLS = 512;     // S of head 0, S of head 1 (128 columns each), O of each head (64 of 128)
 constexpr uint32_t TMEM_S = 0, TMEM_O = 256;
 constexpr float NEG_BIG = -1.0e30f;
 
@@ -65,6 +71,20 @@ __device__ __forceinline__ void tmem_ld32_issue(uint32_t taddr, uint32_t (&r)[32
       : "r"(taddr) : "memory");
 }
 __device__ __forceinline__ void tmem_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+        "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]),
+        "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]),
+        "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+constexpr float REF_SLACK = 16.f;  // a row's reference moves when a score tops it by more than this (log2)
 
 // MN-major operand (V as [key][64]): rows of 128 bytes, 8-key groups 1,024 bytes apart
 __device__ __forceinline__ uint64_t make_desc_mn(uint32_t smem_addr) {
@@ -179,7 +199,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
                        const int* __restrict__ n_tiles_ptr, int nh, int nkv, int ps, float scale_log2, int window,
                        int* __restrict__ status) {
   extern __shared__ unsigned char smem_raw[];
-  __shared__ __align__(8) uint64_t k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], p_full[2], o_full[2][2], skew;
+  __shared__ __align__(8) uint64_t k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], p_full[2], pv_done[2][2], skew;
   __shared__ uint32_t tmem_slot;
   __shared__ int failed;
   trigger_dependents();
@@ -218,8 +238,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
       mbar_init(&v_empty[i], n_heads_here);
       mbar_init(&s_full[i], 1);
       mbar_init(&p_full[i], 128);
-      mbar_init(&o_full[i][0], 1);
-      mbar_init(&o_full[i][1], 1);
+      mbar_init(&pv_done[i][0], 1);
+      mbar_init(&pv_done[i][1], 1);
     }
     mbar_init(&skew, 128);
     failed = 0;
@@ -310,10 +330,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         const uint64_t dp = desc_p0 + (uint64_t)(vb * (P_BYTES / 16)), dv = desc_v0 + (uint64_t)(vb * (KV_BYTES / 16));
 #pragma unroll
         for (int k = 0; k < BKV / UMMA_K; k++)
-          umma(tmem + TMEM_O + hh * 128 + vb * HD, dp + (uint64_t)((k >> 2) * (BQ * 128 / 16) + (k & 3) * 2),
-                  dv + (uint64_t)(k * (2048 / 16)), idesc_pv, k > 0 ? 1u : 0u);
+          umma(tmem + TMEM_O + hh * 128, dp + (uint64_t)((k >> 2) * (BQ * 128 / 16) + (k & 3) * 2),
+                  dv + (uint64_t)(k * (2048 / 16)), idesc_pv, (k > 0 || j > 0) ? 1u : 0u);
         tcgen05_commit(&v_empty[vb]);
-        tcgen05_commit(&o_full[hh][vb]);
+        tcgen05_commit(&pv_done[hh][vb]);
       }
       if (!ok) failed = 1;
     }
@@ -326,65 +346,67 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     const int lim_lo = window > 0 ? max(pos - window + 1, 0) : 0;
     const uint32_t lane_addr = tmem + ((uint32_t)((warp & 3) * 32) << 16);
     const uint32_t s_addr = lane_addr + TMEM_S + hh * 128, o_addr = lane_addr + TMEM_O + hh * 128;
-    float o[HD];
-#pragma unroll
-    for (int d = 0; d < HD; d++) o[d] = 0.f;
-    float m = NEG_BIG, l = 0.f;
-    float alpha1 = 1.f, alpha2 = 1.f;  // of the last tile and the one before it
+    float m = NEG_BIG, l = 0.f;  // reference of the row's exponentials (and so of O and l); row sum
     bool ok = true;
-    // O = O * alpha_k + O_tile_k for tile k, whose P . V product has long been issued
-    auto fold = [&](int k, float alpha) {
-      if (!mbar_wait(&o_full[hh][k & 1], (k >> 1) & 1)) return false;
-      tcgen05_fence_after();
-      uint32_t a[32], b[32];
-      tmem_ld32_issue(o_addr + (k & 1) * HD, a);
-      tmem_ld32_issue(o_addr + (k & 1) * HD + 32, b);
-      tmem_wait();
-#pragma unroll
-      for (int i = 0; i < 32; i++) {
-        o[i] = fmaf(o[i], alpha, __uint_as_float(a[i]));
-        o[32 + i] = fmaf(o[32 + i], alpha, __uint_as_float(b[i]));
-      }
-      tcgen05_fence_before();
-      return true;
-    };
     // the second head starts when the first has handed over its first P
     if (hh == 1 && !mbar_wait(&skew, 0)) ok = false;
     for (int j = 0; j < n_kv_tiles && ok; j++) {
       const int key0 = k_begin + j * BKV;
-      if (j >= 2 && !fold(j - 2, alpha2)) { ok = false; break; }
       if (!mbar_wait(&s_full[hh], j & 1)) { ok = false; break; }
       tcgen05_fence_after();
-      // a tile every row of the block sees whole needs no mask; else columns [lo, lo + span] of this tile are visible
       const bool whole = key0 + BKV - 1 <= pos0 && key0 + BKV <= k_end && (window <= 0 || key0 >= pos0 + BQ - window);
       const int lo = lim_hi >= lim_lo ? lim_lo - key0 : (1 << 30);
       const uint32_t span = lim_hi >= lim_lo ? (uint32_t)(lim_hi - lim_lo) : 0u;
-      const float mx = whole ? row_max<false>(s_addr, lo, span) : row_max<true>(s_addr, lo, span);
-      const float m_new = fmaxf(m, mx * scale_log2);
-      const float alpha = fast_exp2(m - m_new);
-      m = m_new;
+      const float tile_max = (whole ? row_max<false>(s_addr, lo, span) : row_max<true>(s_addr, lo, span)) * scale_log2;
+      const bool moves = tile_max - m > REF_SLACK;
+      if (j == 0) {
+        if (moves) m = tile_max;
+      } else if (__any_sync(0xffffffffu, moves)) {
+        if (!mbar_wait(&pv_done[hh][(j - 1) & 1], ((j - 1) >> 1) & 1)) { ok = false; break; }
+        tcgen05_fence_after();
+        const float m_new = moves ? fmaxf(m, tile_max) : m;
+        const float alpha = fast_exp2(m - m_new);
+#pragma unroll 1
+        for (int c0 = 0; c0 < HD; c0 += 32) {
+          uint32_t v[32];
+          tmem_ld32_issue(o_addr + c0, v);
+          tmem_wait();
+#pragma unroll
+          for (int i = 0; i < 32; i++) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
+          tmem_st32(o_addr + c0, v);
+        }
+        tmem_wait_st();
+        l *= alpha;
+        m = m_new;
+      }
+      if (j >= 2 && !mbar_wait(&pv_done[hh][j & 1], ((j - 2) >> 1) & 1)) { ok = false; break; }
       unsigned char* prow = sP + (hh * 2 + (j & 1)) * P_BYTES + r * 128;
-      const float sum = whole ? row_exp<false>(s_addr, prow, r, lo, span, scale_log2, -m_new)
-                              : row_exp<true>(s_addr, prow, r, lo, span, scale_log2, -m_new);
-      l = l * alpha + sum;
-      alpha2 = alpha1;
-      alpha1 = alpha;
+      l += whole ? row_exp<false>(s_addr, prow, r, lo, span, scale_log2, -m) : row_exp<true>(s_addr, prow, r, lo, span, scale_log2, -m);
       tcgen05_fence_before();
       fence_proxy_async();
       mbar_arrive(&p_full[hh]);
       if (j == 0 && hh == 0) mbar_arrive(&skew);
     }
-    if (ok && n_kv_tiles >= 2) ok = fold(n_kv_tiles - 2, alpha2);
-    if (ok) ok = fold(n_kv_tiles - 1, alpha1);
+    if (ok) ok = mbar_wait(&pv_done[hh][(n_kv_tiles - 1) & 1], ((n_kv_tiles - 1) >> 1) & 1);
     if (!ok) failed = 1;
-    if (ok && r < rows_live) {
-      const float inv = 1.f / l;
-      bf16* dst = out + (size_t)(t0 + r) * out_stride + (size_t)(head0 + hh) * HD;
+    if (ok) {
+      tcgen05_fence_after();
+      uint32_t a[32], b[32];
+      tmem_ld32_issue(o_addr, a);
+      tmem_ld32_issue(o_addr + 32, b);
+      tmem_wait();
+      if (r < rows_live) {
+        const float inv = 1.f / l;
+        bf16* dst = out + (size_t)(t0 + r) * out_stride + (size_t)(head0 + hh) * HD;
+        auto two = [&](const uint32_t (&v)[32], int i) {
+          return pack_bf16(__uint_as_float(v[i]) * inv, __uint_as_float(v[i + 1]) * inv);
+        };
 #pragma unroll
-      for (int c = 0; c < HD / 8; c++)
-        *reinterpret_cast<uint4*>(dst + c * 8) =
-            make_uint4(pack_bf16(o[8 * c] * inv, o[8 * c + 1] * inv), pack_bf16(o[8 * c + 2] * inv, o[8 * c + 3] * inv),
-                       pack_bf16(o[8 * c + 4] * inv, o[8 * c + 5] * inv), pack_bf16(o[8 * c + 6] * inv, o[8 * c + 7] * inv));
+        for (int c = 0; c < 4; c++) {
+          *reinterpret_cast<uint4*>(dst + c * 8) = make_uint4(two(a, 8 * c), two(a, 8 * c + 2), two(a, 8 * c + 4), two(a, 8 * c + 6));
+          *reinterpret_cast<uint4*>(dst + 32 + c * 8) = make_uint4(two(b, 8 * c), two(b, 8 * c + 2), two(b, 8 * c + 4), two(b, 8 * c + 6));
+        }
+      }
     }
   }
   tcgen05_fence_before();

@@ -485,8 +485,8 @@ def attn_prefill_mma(qkv: torch.Tensor, out: torch.Tensor, kcache: torch.Tensor,
 
 
 ATTN_PREFILL_TC = True  # portions of prompts on the tcgen05 kernels where one takes the head size
-# head size -> (source, compile-time constants, entry point).  Head size 64 folds the output tiles in registers
-# (the faster of the two there); head size 128 accumulates the output in tensor memory.
+# head size -> (source, compile-time constants, entry point).  Both accumulate the output in tensor memory; head
+# size 64 has 128-key tiles and one S tile a head (the faster of the two there), head size 128 64-key tiles and two.
 ATTN_PREFILL_TC_KERNELS = {
     64: ("attention_tc.cu", {}, "tkb_attn_prefill_tc_bf16"),
     128: ("attention_tc_acc.cu", {"TKB_HD": 128}, "tkb_attn_prefill_acc_bf16"),
