@@ -154,37 +154,53 @@ __device__ __forceinline__ float row_max(uint32_t s_addr, int lo, uint32_t span)
   return fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
 }
 
+// 32 columns of one row: p = 2^(s * scale - m) as bfloat16 into the row's place of the swizzled P tile; returns
+// the sum of the even columns and adds that of the odd ones to `odd`.
+template <bool MASKED>
+__device__ __forceinline__ float exp_32_columns(const uint32_t (&v)[32], unsigned char* prow, int r, int c0, int lo,
+                                                uint32_t span, float scale, float neg_m, float& odd) {
+  float s0 = 0.f, s1 = 0.f;
+  uint32_t pk[16];
+#pragma unroll
+  for (int i = 0; i < 32; i += 2) {
+    float x0 = __uint_as_float(v[i]), x1 = __uint_as_float(v[i + 1]);
+    if (MASKED) {
+      const int c = c0 + i - lo;
+      if ((uint32_t)c > span) x0 = -INFINITY;
+      if ((uint32_t)(c + 1) > span) x1 = -INFINITY;
+    }
+    const float p0 = fast_exp2(fmaf(x0, scale, neg_m)), p1 = fast_exp2(fmaf(x1, scale, neg_m));
+    s0 += p0;
+    s1 += p1;
+    pk[i >> 1] = pack_bf16(p0, p1);
+  }
+  // 32 keys = four 16-byte chunks of this row in atom c0 / 64
+  unsigned char* dst = prow + (c0 >> 6) * (BQ * 128);
+  const int cbase = (c0 & 63) >> 3;
+#pragma unroll
+  for (int cc = 0; cc < 4; cc++)
+    *reinterpret_cast<uint4*>(dst + (((cbase + cc) ^ (r & 7)) << 4)) =
+        make_uint4(pk[4 * cc], pk[4 * cc + 1], pk[4 * cc + 2], pk[4 * cc + 3]);
+  odd += s1;
+  return s0;
+}
+
 // p = 2^(s * scale - m) of one row: bfloat16 into the row's place of the swizzled P tile; returns the row sum.
 template <bool MASKED>
 __device__ __forceinline__ float row_exp(uint32_t s_addr, unsigned char* prow, int r, int lo, uint32_t span, float scale,
                                          float neg_m) {
   float s0 = 0.f, s1 = 0.f;
+  // 32 columns at a time; the load of the next 32 is on its way while these are worked on
+  uint32_t v[32], w[32];
+  tmem_ld32_issue(s_addr, v);
 #pragma unroll 1
-  for (int c0 = 0; c0 < BKV; c0 += 32) {
-    uint32_t v[32];
-    tmem_ld32_issue(s_addr + c0, v);
+  for (int c0 = 0; c0 < BKV; c0 += 64) {
     tmem_wait();
-    uint32_t pk[16];
-#pragma unroll
-    for (int i = 0; i < 32; i += 2) {
-      float x0 = __uint_as_float(v[i]), x1 = __uint_as_float(v[i + 1]);
-      if (MASKED) {
-        const int c = c0 + i - lo;
-        if ((uint32_t)c > span) x0 = -INFINITY;
-        if ((uint32_t)(c + 1) > span) x1 = -INFINITY;
-      }
-      const float p0 = fast_exp2(fmaf(x0, scale, neg_m)), p1 = fast_exp2(fmaf(x1, scale, neg_m));
-      s0 += p0;
-      s1 += p1;
-      pk[i >> 1] = pack_bf16(p0, p1);
-    }
-    // 32 keys = four 16-byte chunks of this row in atom c0 / 64
-    unsigned char* dst = prow + (c0 >> 6) * (BQ * 128);
-    const int cbase = (c0 & 63) >> 3;
-#pragma unroll
-    for (int cc = 0; cc < 4; cc++)
-      *reinterpret_cast<uint4*>(dst + (((cbase + cc) ^ (r & 7)) << 4)) =
-          make_uint4(pk[4 * cc], pk[4 * cc + 1], pk[4 * cc + 2], pk[4 * cc + 3]);
+    tmem_ld32_issue(s_addr + c0 + 32, w);
+    s0 += exp_32_columns<MASKED>(v, prow, r, c0, lo, span, scale, neg_m, s1);
+    tmem_wait();
+    if (c0 + 64 < BKV) tmem_ld32_issue(s_addr + c0 + 64, v);
+    s0 += exp_32_columns<MASKED>(w, prow, r, c0 + 32, lo, span, scale, neg_m, s1);
   }
   return s0 + s1;
 }
