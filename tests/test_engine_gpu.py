@@ -343,6 +343,16 @@ def test_warm_up_records_the_decode_graphs(tiny_model_dirs):
     with pytest.raises(RuntimeError):
         eng.add_request(prompts[0], max_num_tokens=4)
         eng.warm_up()
+    # bfloat16: the attention picks its kernel by the length of the step's work items, so each batch size is
+    # recorded twice, at a short and at a long context, and decoding at either records nothing more
+    eng = make_engine(d, dtype="bfloat16", graph_max_tokens=0, max_seqs_per_forward=8, cudagraph_step=4, cudagraph_max_size=8,
+                      kv_cache_num_tokens=8 * 16384)  # this model's items pass three tiles only at contexts of 16,384
+    made = eng.warm_up()
+    assert made == 2 * len(eng.graphs.sizes) == len(eng.graphs.graphs) and not eng.runner.cache.requests
+    eng.runner.cache.check()
+    eng.generate(prompts, max_num_tokens=12, ignore_eos=True)
+    eng.generate([cuttings.random_tokens(100, 256, 5)] * 3, max_num_tokens=20, ignore_eos=True)
+    assert len(eng.graphs.graphs) == made
 
 
 @pytest.mark.parametrize("sizes", ["1b", "8b"])

@@ -236,27 +236,41 @@ class Engine:
             raise RuntimeError("warm_up() wants an engine without requests")
         cache = self.runner.cache
         made = 0
+        page = self.runner.config.page_size
+        # without work plans (float32) nothing depends on the context
+        contexts = (1, 256, 1024, 4096, 16384, 65536) if self.runner.model.planners() else (1,)
         for bp in (batch_sizes if batch_sizes is not None else self.graphs.sizes):
-            if bp > cache.slots.num_free or any(bp > f for f in cache.num_free_pages()):
-                continue
-            ids = [f"__warm_up_{i}" for i in range(bp)]
-            try:
-                for rid in ids:
-                    cache.admit(rid)
-                    cache.ensure_capacity(rid, 1)
-                entries = [StepEntry(rid, [0], 0, [0]) for rid in ids]
-                if self.graphs.usable(entries):
+            # A graph holds the kernels chosen when it was recorded, and the attention's choice depends on how long
+            # the step's work items are: each batch size is recorded at context 1 and again at the shortest of a
+            # few longer contexts that the free pages allow and that gives another graph (what the pages hold
+            # does not matter here: nothing is read back).
+            seen = set()
+            for context in contexts:
+                if len(seen) >= 2:
+                    break
+                need = bp * -(-context // page)
+                if bp > cache.slots.num_free or any(need > f for f in cache.num_free_pages()):
+                    break
+                ids = [f"__warm_up_{i}" for i in range(bp)]
+                try:
+                    for rid in ids:
+                        cache.admit(rid)
+                        cache.ensure_capacity(rid, context)
+                    entries = [StepEntry(rid, [0], context - 1, [0]) for rid in ids]
+                    if not self.graphs.usable(entries):
+                        break
                     # rows without a slot: the sampler leaves the last-token table alone
                     extra = dict(temperature=np.zeros(bp, dtype=np.float32), stream_key=np.zeros(bp, dtype=np.int64),
-                                 sample_pos=np.ones(bp, dtype=np.int32), row_slot=np.full(bp, -1, dtype=np.int32))
+                                 sample_pos=np.full(bp, context, dtype=np.int32), row_slot=np.full(bp, -1, dtype=np.int32))
                     prep = self.graphs.prepare(entries, extra)
+                    seen.add(prep["key"])
                     if prep["key"] not in self.graphs.graphs:
                         self.graphs.launch(prep)
                         made += 1
-            finally:
-                for rid in ids:
-                    if rid in cache.requests:
-                        cache.free(rid)
+                finally:
+                    for rid in ids:
+                        if rid in cache.requests:
+                            cache.free(rid)
         if self.runner.rt.device.type == "cuda":
             torch.cuda.synchronize(self.runner.rt.device)
         self.runner.check_status()
