@@ -88,3 +88,39 @@ def test_stop_tokens_and_eos(cpu_kernels, tiny_model_dirs):
     out = eng.generate([p], max_num_tokens=8, stop_token_ids=[full[3]])[0]
     first = full.index(full[3])
     assert out.completion_ids == full[:first + 1] and out.finish_reason == "stop"
+
+
+def test_statistics_are_logged(cpu_kernels, tiny_model_dirs, caplog):
+    """``stats_report_seconds`` and ``log_level`` keep the reference's meaning: a line of counts and rates at
+    level INFO every so many seconds (0: after every step); nothing at WARNING."""
+    import logging
+
+    d = tiny_model_dirs[0]
+    prompts = [cuttings.random_tokens(n, 256, 7 * n) for n in (9, 20)]
+    with caplog.at_level(logging.DEBUG, logger="tokasaurus_b200"):
+        eng = make_engine(d, stats_report_seconds=0.0, log_level="INFO")
+        eng.generate(prompts, max_num_tokens=5, ignore_eos=True)
+    lines = [r.getMessage() for r in caplog.records if r.name == "tokasaurus_b200"]
+    assert len(lines) == eng.scheduler.stats["steps"] and all("new tokens" in m and "free pages" in m for m in lines)
+    assert sum(int(m.split("prompt tokens ")[1].split(" ")[0]) for m in lines) == 29
+    assert sum(int(m.split("new tokens ")[1].split(" ")[0]) for m in lines) == 2 * 5 - 2  # the first of each comes with its prompt
+    caplog.clear()
+    eng = make_engine(d, stats_report_seconds=0.0, log_level="WARNING")
+    eng.generate(prompts, max_num_tokens=5, ignore_eos=True)
+    assert not [r for r in caplog.records if r.name == "tokasaurus_b200"]
+    with pytest.raises(ValueError, match="log_level"):
+        make_engine(d, log_level="LOUD")
+
+
+def test_steps_ahead_and_paced_prefill_options_reach_the_engine(cpu_kernels, tiny_model_dirs):
+    d = tiny_model_dirs[0]
+    eng = make_engine(d, scheduling_steps_ahead=0, greedy_prefill=False, prefill_round_up_multiple=4)
+    assert eng.run_ahead is False and eng.scheduler.greedy_prefill is False and eng.scheduler.prefill_multiple == 4
+    eng = make_engine(d, scheduling_steps_ahead=8)
+    assert eng.run_ahead is True and eng.scheduler.greedy_prefill is True
+    # paced prefill changes when tokens run, not which tokens come out
+    prompts = [cuttings.random_tokens(n, 256, 5 * n) for n in (30, 3, 40, 25)]
+    plain = PlainLlama(d, torch.float64)
+    eng = make_engine(d, greedy_prefill=False, prefill_round_up_multiple=4, max_seqs_per_forward=2, max_tokens_per_forward=32)
+    outs = eng.generate(prompts, max_num_tokens=6, ignore_eos=True)
+    assert [o.completion_ids for o in outs] == [plain.greedy(p, 6) for p in prompts]

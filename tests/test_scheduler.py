@@ -127,3 +127,74 @@ def test_slots_limit_admission():
     assert len(plan.portions) == 2
     fin, _ = run(s)
     assert len(fin) == 4
+
+
+def test_prefill_without_greed_is_paced():
+    """``greedy_prefill=F``: all that fits while nobody queues; exactly the first prompt while nobody decodes;
+    else the prompt tokens outstanding by the time a decoding sequence ends and makes room for the queue's
+    head, spread over the steps until then and rounded up to ``prefill_round_up_multiple``."""
+    def scene(**kw):
+        s, cache = make(num_pages=200, page_size=4, max_tokens=32, max_seqs=2, greedy_prefill=False, **kw)
+        s.add_request(req(0, 3, 21))  # 3 + 21 - 1 = 23 tokens go through the model
+        plan = s.schedule()
+        assert [(p.seq.id, p.n_tokens) for p in plan.portions] == [("r0", 3)]  # nobody queues: all that fits
+        s.complete(plan, [7], [0.0])
+        s.add_request(req(1, 100, 2))
+        s.add_request(req(2, 60, 2))
+        s.add_request(req(3, 10, 2))
+        return s
+
+    # r0 ends 20 steps from now; its slot then goes to r2 (r3 still waits), so 100 + 60 prompt tokens are due
+    # in 20 steps: 8 a step
+    s = scene(prefill_round_up_multiple=4)
+    plan = s.schedule()
+    assert [(p.seq.id, p.n_tokens, p.from_device) for p in plan.portions] == [("r0", 1, True), ("r1", 8, False)]
+    s = scene(prefill_round_up_multiple=16)
+    plan = s.schedule()
+    assert [(p.seq.id, p.n_tokens) for p in plan.portions] == [("r0", 1), ("r1", 16)]
+    # and everything still ends
+    fin, plans = run(s)
+    assert sorted(o.id for o in fin) == ["r0", "r1", "r2", "r3"]
+    assert all(p.n_tokens <= 32 for p in plans)
+
+    # nobody decodes, somebody queues: exactly the first prompt, although the second would fit beside it
+    s, _ = make(num_pages=200, page_size=4, max_tokens=32, max_seqs=2, greedy_prefill=False)
+    for i in range(3):
+        s.add_request(req(i, 5, 3))
+    plan = s.schedule()
+    assert [(p.seq.id, p.n_tokens) for p in plan.portions] == [("r0", 5)]
+    greedy, _ = make(num_pages=200, page_size=4, max_tokens=32, max_seqs=2)
+    for i in range(3):
+        greedy.add_request(req(i, 5, 3))
+    assert [(p.seq.id, p.n_tokens) for p in greedy.schedule().portions] == [("r0", 5), ("r1", 5)]
+
+
+def test_paced_prefill_counts_pages_as_admission_does():
+    """The queue's head does not fit when the first decoding sequence has given its pages back, only when the
+    second has: each end is a candidate (what is outstanding by then over the steps until then), the smallest
+    wins, and ends after the one at which the whole queue fits ask for nothing slower."""
+    def scene(extra):
+        s, cache = make(num_pages=40, page_size=4, max_tokens=64, max_seqs=8, greedy_prefill=False,
+                        prefill_round_up_multiple=1)
+        s.add_request(req(0, 4, 9))    # 12 tokens, 3 pages, ends 8 steps after its prompt
+        s.add_request(req(1, 4, 41))   # 44 tokens, 11 pages, ends 40 steps after its prompt
+        plan = s.schedule()
+        s.complete(plan, [7, 7], [0.0, 0.0])
+        s.add_request(req(2, 40, 5))   # 44 tokens, 11 pages: admitted; 15 pages are left beside the reserves
+        s.add_request(req(3, 72, 5))   # 76 tokens, 19 pages: waits; r0's 3 pages do not make room, r1's 11 do
+        for r in extra:
+            s.add_request(r)
+        return s
+
+    s = scene([])
+    plan = s.schedule()
+    assert [q.id for q in s.queued] == ["r3"]
+    # r0's end: r3 still waits, 40 tokens in 8 steps; r1's end: the queue is empty, no further candidate
+    assert [(p.seq.id, p.n_tokens) for p in plan.portions] == [("r0", 1), ("r1", 1), ("r2", 5)]
+    s = scene([req(4, 40, 5)])
+    plan = s.schedule()
+    assert [q.id for q in s.queued] == ["r3", "r4"]
+    # r1's end: r3 is in, r4 waits behind it: 40 + 72 tokens in 40 steps, slower than 40 in 8
+    assert [(p.seq.id, p.n_tokens) for p in plan.portions] == [("r0", 1), ("r1", 1), ("r2", 3)]
+    fin, _ = run(s)
+    assert sorted(o.id for o in fin) == ["r0", "r1", "r2", "r3", "r4"]

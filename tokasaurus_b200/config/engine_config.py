@@ -28,20 +28,20 @@ class EngineConfig:
     rope_scaling: str | None = None  # JSON text that replaces config.json's rope_scaling
     enable_chosen_logprobs: bool = True
     max_topk_logprobs: int | None = None
-    log_level: str = "INFO"
-    stats_report_seconds: float = 5.0
+    log_level: str = "INFO"  # of the logger "tokasaurus_b200"
+    stats_report_seconds: float = 5.0  # a line of counts and rates at level INFO this often
     page_size: int = 16
     kv_cache_num_tokens: int = 1024 * 128
     max_tokens_per_forward: int = 8192
     max_seqs_per_forward: int = 1024
-    prefill_round_up_multiple: int = 16
-    scheduling_steps_ahead: int = 1
+    prefill_round_up_multiple: int = 16  # of the paced prompt tokens a step (greedy_prefill=F)
+    scheduling_steps_ahead: int = 1  # 0: no run-ahead; this engine looks one step ahead, never more (reference: 8)
     max_num_tokens_per_request: int | None = None
     greedy_prefill: bool = True
     use_cudagraphs: bool = True
     cudagraph_max_size: int = 128
     cudagraph_step: int = 16
-    cudagraph_max_kv_indices_per_seq: int = 32768
+    cudagraph_max_kv_indices_per_seq: int = 32768  # a request with more pages keeps its step out of the graphs
     allocator_sanity_checks: bool = False
     bump_city_population_me: bool = False
     # --- this engine's own options ---

@@ -62,9 +62,13 @@ def main(argv: list[str] | None = None) -> int:
     if not prompts:
         print("toka: give prompt_ids='[...]' or prompts_file=<jsonl>", file=sys.stderr)
         return 2
+    import logging
+
     from tokasaurus_b200.engine.engine import Engine
     from tokasaurus_b200.sampling.params import SamplingParams
 
+    # the engine's statistics lines (level INFO, every stats_report_seconds) go to the standard error stream
+    logging.basicConfig(stream=sys.stderr, format="[toka] %(message)s")
     engine = Engine(config=cfg, seed=opts.get("seed") or 0, kv_reserve_fraction=opts.get("kv_reserve_fraction", 1.0))
     sp = SamplingParams(temperature=opts.get("temperature") or 0.0, seed=opts.get("seed"))
     t0 = time.time()

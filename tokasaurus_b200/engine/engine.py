@@ -12,6 +12,8 @@ function and the sampler on the GPU.
 
 from __future__ import annotations
 
+import logging
+import time
 from dataclasses import dataclass
 from typing import Any, Sequence
 
@@ -61,7 +63,8 @@ class Engine:
         self.scheduler = Scheduler(
             self.runner.cache, cfg.max_tokens_per_forward, cfg.max_seqs_per_forward,
             cfg.max_num_tokens_per_request, self.runner.eos_token_ids, kv_reserve_fraction,
-            cfg.bump_city_population_me, cfg.allocator_sanity_checks)
+            cfg.bump_city_population_me, cfg.allocator_sanity_checks, cfg.greedy_prefill,
+            cfg.prefill_round_up_multiple)
         self.sampler = Sampler(self.runner.rt.device, max(64, cfg.max_seqs_per_forward, cfg.cudagraph_max_size),
                                cfg.enable_chosen_logprobs)
         self.graphs = None
@@ -69,12 +72,23 @@ class Engine:
             from tokasaurus_b200.engine.graphs import DecodeGraphs
 
             self.graphs = DecodeGraphs(self.runner, self.sampler, cfg.cudagraph_max_size, cfg.cudagraph_step,
-                                       graph_max_tokens)
+                                       graph_max_tokens, cfg.cudagraph_max_kv_indices_per_seq)
         self._auto_id = 0
-        self.run_ahead = run_ahead
+        # the reference schedules up to ``scheduling_steps_ahead`` steps before it has seen their results; this
+        # engine looks one step ahead (0 switches that off, larger values mean one)
+        self.run_ahead = run_ahead and cfg.scheduling_steps_ahead >= 1
         self._inflight: _InFlight | None = None
         self._next_slot = 0
         self.last_step_bytes = dict(h2d=0, d2h=0)
+        # a line of statistics every ``stats_report_seconds`` at level INFO, as the reference's manager reports
+        # (tokasaurus/manager/manager.py: stats_report_seconds); ``log_level`` is this logger's level
+        self.log = logging.getLogger("tokasaurus_b200")
+        level = logging.getLevelName(str(cfg.log_level).upper())
+        if not isinstance(level, int):
+            raise ValueError(f"log_level={cfg.log_level!r} is not a logging level")
+        self.log.setLevel(level)
+        self._stats_at = time.monotonic()
+        self._stats_last = dict(self.scheduler.stats)
 
     # ------------------------------------------------------------------ requests
     def add_request(self, input_ids: Sequence[int], sampling_params: SamplingParams | None = None,
@@ -121,6 +135,11 @@ class Engine:
         end-of-sequence or stop token after all, its row of step t+1 is thrown away: one wasted row, no wrong
         result, and its pages, freed meanwhile, are not written again by anything that follows in the stream
         before their next owner's own writes.  Ends by length are known beforehand and never guessed."""
+        done = self._step()
+        self._report_stats()
+        return done
+
+    def _step(self) -> list[RequestOutput]:
         if self._inflight is None:
             done = self._start()
             if done is not None:
@@ -128,6 +147,23 @@ class Engine:
         cur = self._inflight
         self._inflight = self._launch_following(cur) if self.run_ahead else None
         return self._finish(cur)
+
+    def _report_stats(self) -> None:
+        now = time.monotonic()
+        dt = now - self._stats_at
+        if dt < self.config.stats_report_seconds or not self.log.isEnabledFor(logging.INFO):
+            return
+        st, last, sched = self.scheduler.stats, self._stats_last, self.scheduler
+        d = {k: st[k] - last.get(k, 0) for k in st}
+        dt = max(dt, 1e-9)
+        self.log.info(
+            "steps %d (%.1f/s), prompt tokens %d (%.0f/s), new tokens %d (%.0f/s), finished %d, pushed out %d; "
+            "decoding %d, in prompt %d, queued %d; free pages %s",
+            d["steps"], d["steps"] / dt, d["prefill_tokens"], d["prefill_tokens"] / dt, d["decode_tokens"],
+            d["decode_tokens"] / dt, d["finished"], d["bumps"], len(sched.decoding), len(sched.prefilling),
+            len(sched.queued), self.runner.cache.num_free_pages())
+        self._stats_at = now
+        self._stats_last = dict(st)
 
     def _launch(self, plan: StepPlan, entries: list[StepEntry], extra: dict[str, np.ndarray],
                 prep: dict | None = None) -> _InFlight:

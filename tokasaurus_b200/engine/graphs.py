@@ -39,7 +39,12 @@ def _pad(a: np.ndarray, n: int, fill: int = 0) -> np.ndarray:
 
 
 class DecodeGraphs:
-    def __init__(self, runner, sampler, max_size: int, step: int, max_tokens: int = 0):
+    def __init__(self, runner, sampler, max_size: int, step: int, max_tokens: int = 0,
+                 max_pages_per_request: int | None = None):
+        """``max_pages_per_request``: the reference's ``cudagraph_max_kv_indices_per_seq`` (common_types.py:117):
+        a step with a request that holds more pages than this runs without a graph.  (The reference sizes its
+        graphs' block tables by it; here they are sized by the pool, so the option only keeps its meaning.)"""
+        self.max_pages_per_request = max_pages_per_request
         self.runner = runner
         self.sampler = sampler
         self.max_size = max_size
@@ -49,9 +54,16 @@ class DecodeGraphs:
         self.launches_per_replay = 0
         self.pool = None  # memory pool shared by all graphs
 
+    def _tables_fit(self, entries) -> bool:
+        limit = self.max_pages_per_request
+        if limit is None:
+            return True
+        pages_for = self.runner.cache.pages_for
+        return all(pages_for(e.start + e.n_tokens) <= limit for e in entries)
+
     def usable(self, entries) -> bool:
         return (bool(self.sizes) and len(entries) <= self.sizes[-1] and self.runner.model.graph_safe
-                and all(e.n_tokens == 1 and list(e.want) == [0] for e in entries))
+                and all(e.n_tokens == 1 and list(e.want) == [0] for e in entries) and self._tables_fit(entries))
 
     def usable_general(self, entries) -> bool:
         """A step with prompt portions that is small enough for a graph of its padded shape: what it costs on
@@ -59,7 +71,7 @@ class DecodeGraphs:
         if not self.sizes or self.max_tokens <= 0 or not self.runner.model.graph_safe:
             return False
         return (len(entries) <= self.sizes[-1] and sum(e.n_tokens for e in entries) <= min(self.max_tokens, TOKEN_BUCKETS[-1])
-                and all(len(e.want) <= 1 for e in entries))
+                and all(len(e.want) <= 1 for e in entries) and self._tables_fit(entries))
 
     def prepare_general(self, entries: list[StepEntry], extra: dict[str, np.ndarray]) -> dict | None:
         """``prepare`` for a step with prompt portions: tokens padded to a bucket (padding tokens carry request

@@ -8,7 +8,8 @@ tokasaurus/manager/scheduler.py:576-637 ``schedule``, :640-684 ``apply_decision`
 * Every decoding sequence is in every step with one token.  What is left of
   ``max_tokens_per_forward`` goes to prompts, first come first served, and a prompt is cut
   wherever the budget ends (``make_scheduling_decision``, scheduler.py:541-573; with
-  ``greedy_prefill`` the reference too takes all that fits, scheduler.py:604-637).
+  ``greedy_prefill``, the default, the reference too takes all that fits, scheduler.py:604-637; without it
+  the prompts are paced, see ``_prefill_budget``).
 * Admission: a queued request enters when a slot is free and the pool has pages for its whole
   prompt (allocated at once, as ``allocate_with_prefix_match`` does, allocator.py:324-384) on top
   of what is set aside for running requests.  ``kv_reserve_fraction`` = 1 sets aside every page a
@@ -87,8 +88,10 @@ class Scheduler:
     def __init__(self, cache: CacheManager, max_tokens_per_forward: int, max_seqs_per_forward: int,
                  max_num_tokens_per_request: int | None = None, eos_token_ids: tuple[int, ...] = (),
                  kv_reserve_fraction: float = 1.0, bump_city_population_me: bool = False,
-                 sanity_checks: bool = False):
+                 sanity_checks: bool = False, greedy_prefill: bool = True, prefill_round_up_multiple: int = 16):
         self.cache = cache
+        self.greedy_prefill = greedy_prefill
+        self.prefill_multiple = max(1, int(prefill_round_up_multiple))
         self.max_tokens = max_tokens_per_forward
         self.max_seqs = max_seqs_per_forward
         self.max_request_tokens = max_num_tokens_per_request
@@ -210,7 +213,7 @@ class Scheduler:
         # 3. the batch: one token for each decoding sequence, then prompt portions under the budget
         for seq in self.decoding:
             plan.portions.append(ScheduledPortion(seq, seq.fed, 1, True, from_device=True))
-        budget = self.max_tokens - len(plan.portions)
+        budget = self._prefill_budget(self.max_tokens - len(plan.portions))
         for seq in self.prefilling:
             if budget <= 0:
                 break
@@ -218,6 +221,65 @@ class Scheduler:
             plan.portions.append(ScheduledPortion(seq, seq.fed, n, seq.fed + n == seq.n_known, from_device=False))
             budget -= n
         return plan
+
+    # ------------------------------------------------------------------ how much of the prompts goes into a step
+    def _prefill_budget(self, room: int) -> int:
+        """Prompt tokens for this step, of the ``room`` that the decoding sequences leave under
+        ``max_tokens_per_forward``.  With ``greedy_prefill`` (the default, here and in the reference): all that
+        fits.  Without it, as the reference decides (tokasaurus/manager/scheduler.py:604-637): all that fits when
+        nobody waits in the queue (everything outstanding is in the cache already, so it may as well start);
+        exactly the first prompt when nobody decodes; else a paced amount (``_paced_prefill``), rounded up to
+        ``prefill_round_up_multiple``."""
+        if self.greedy_prefill or not self.prefilling or not self.queued:
+            return room
+        if not self.decoding:
+            first = self.prefilling[0]
+            return min(room, first.n_known - first.fed)
+        pace = self._paced_prefill()
+        if pace == float("inf"):
+            return room
+        m = self.prefill_multiple
+        return min(room, max(m, -(-int(pace + 0.999999) // m) * m))
+
+    def _paced_prefill(self) -> float:
+        """Prompt tokens a step such that the prompts are through the model just when the cache has room for what
+        follows them, instead of all at once at the cost of the decoding sequences' latency: the idea of the
+        reference's ``calc_prefill_per_forward`` (tokasaurus/manager/scheduler.py:434-538) in this scheduler's
+        own page accounting.  The decoding sequences are taken in the order in which they end by length; after
+        each end, queued sequences are admitted in thought, first come first served, while slots and pages
+        (those the ended sequences give back, less what the admitted ones reserve) allow; the prompt tokens
+        outstanding by then, spread over the steps until then, are one candidate, and the smallest candidate
+        wins.  Once the whole queue fits, later ends ask for nothing slower."""
+        cache, f = self.cache, self.reserve_fraction
+        pages_for = cache.pages_for
+        outstanding = sum(s.n_known - s.fed for s in self.prefilling)
+        available = self._min_free() - self._reserved_for_running()
+        running = len(self.prefilling) + len(self.decoding)
+        slots = min(self.max_seqs, running + cache.slots.num_free)
+        queue = list(self.queued)
+        at = 0  # next queued sequence to admit in thought
+        onboarded = 0
+        pace = float("inf")
+        for seq in sorted(self.decoding, key=lambda s: s.max_total() - s.fed):
+            steps = max(1, seq.max_total() - seq.fed)  # steps from now after which this sequence has ended
+            held = len(cache.requests[seq.id].tables[0]) if cache.groups else 0
+            growth = max(0, pages_for(seq.max_total()) - held)
+            available += held + int(f * growth)
+            running -= 1
+            while at < len(queue) and running < slots:
+                q = queue[at]
+                first_need = pages_for(q.n_known)
+                need = first_need + max(0, int((pages_for(q.max_total()) - first_need) * f + 0.999999))
+                if need > available:
+                    break
+                available -= need
+                onboarded += q.n_known
+                running += 1
+                at += 1
+            if at == len(queue):
+                break
+            pace = min(pace, (outstanding + onboarded) / steps)
+        return pace
 
     def complete(self, plan: StepPlan, sampled: list[int], logprobs: list[float] | None = None,
                  topk: list[tuple[list[int], list[float]]] | None = None) -> list[RequestOutput]:
