@@ -41,3 +41,28 @@ def test_replay_on_cpu_matches_plain(cpu_kernels, tiny_model_dirs, cfg_index, cu
     for rid in reqs:
         err = np.abs(got[rid] - want[rid]).max(axis=1)
         assert err.max() < 1e-4 * max(1.0, np.abs(want[rid]).max()), (rid, int(err.argmax()), float(err.max()))
+
+
+def test_graph_eligibility_of_a_step():
+    """Which steps may run as CUDA graphs (host-side rule, no GPU needed): single tokens that want their logits,
+    no more requests than the largest recorded batch, and no request beyond ``cudagraph_max_kv_indices_per_seq``
+    pages."""
+    from types import SimpleNamespace
+
+    from tokasaurus_b200.engine.batch import StepEntry
+    from tokasaurus_b200.engine.graphs import DecodeGraphs
+
+    runner = SimpleNamespace(model=SimpleNamespace(graph_safe=True), cache=SimpleNamespace(pages_for=lambda n: -(-n // 16)))
+    g = DecodeGraphs(runner, None, max_size=8, step=4, max_tokens=64, max_pages_per_request=10)
+    assert g.sizes == [1, 2, 4, 8]
+    one = lambda rid, start: StepEntry(rid, None, start, [0])  # noqa: E731
+    assert g.usable([one("a", 5), one("b", 159)])            # 160 tokens: 10 pages
+    assert not g.usable([one("a", 5), one("b", 160)])        # 161 tokens: 11 pages
+    assert not g.usable([one(i, 3) for i in range(9)])       # more requests than the largest graph
+    assert not g.usable([StepEntry("a", [1, 2], 0, [1])])    # a prompt portion
+    assert not g.usable([StepEntry("a", [1], 0, [])])        # nothing wanted
+    assert g.usable_general([StepEntry("a", [1, 2, 3], 0, [2]), one("b", 7)])
+    assert not g.usable_general([StepEntry("a", list(range(65)), 0, [64])])   # more tokens than graph_max_tokens
+    assert not g.usable_general([StepEntry("a", [1, 2, 3], 158, [2])])        # 161 tokens: 11 pages
+    unlimited = DecodeGraphs(runner, None, max_size=8, step=4, max_tokens=0)
+    assert unlimited.usable([one("b", 10 ** 6)]) and not unlimited.usable_general([StepEntry("a", [1, 2], 0, [1])])
