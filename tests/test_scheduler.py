@@ -198,3 +198,39 @@ def test_paced_prefill_counts_pages_as_admission_does():
     assert [(p.seq.id, p.n_tokens) for p in plan.portions] == [("r0", 1), ("r1", 1), ("r2", 3)]
     fin, _ = run(s)
     assert sorted(o.id for o in fin) == ["r0", "r1", "r2", "r3", "r4"]
+
+
+@pytest.mark.parametrize("seed", range(6))
+def test_paced_prefill_under_random_load_always_ends(seed):
+    """Whatever the mix of prompts, lengths, pool and reserve: without greed every request still ends, a step
+    never passes the token budget, no page is lost, and the produced tokens are those of the greedy scheduler
+    (only when a token runs changes)."""
+    import random
+
+    rnd = random.Random(seed)
+    reqs = [(rnd.randint(1, 60), rnd.randint(1, 30)) for _ in range(rnd.randint(5, 25))]
+    kw = dict(num_pages=rnd.choice([40, 64, 200]), page_size=rnd.choice([4, 8]), max_tokens=rnd.choice([8, 16, 48]),
+              max_seqs=rnd.choice([2, 4, 8]), kv_reserve_fraction=rnd.choice([1.0, 0.5, 0.0]))
+    outs = {}
+    for greedy in (True, False):
+        s, cache = make(greedy_prefill=greedy, prefill_round_up_multiple=rnd.choice([1, 4, 16]), **kw)
+        pending = list(enumerate(reqs))
+        finished, steps = [], 0
+        while s.has_work() or pending:
+            for _ in range(rnd.randint(0, 2)):
+                if pending:
+                    i, (n, new) = pending.pop(0)
+                    s.add_request(req(i, n, new))
+            if not s.has_work():
+                continue
+            plan = s.schedule()
+            assert 0 < plan.n_tokens <= kw["max_tokens"]
+            sampled = [(len(p.seq.output.completion_ids) * 31 + p.seq.index) % 97 for p in plan.portions if p.samples]
+            finished += s.complete(plan, sampled, [0.0] * len(sampled))
+            cache.check()
+            steps += 1
+            assert steps < 20_000
+        assert sorted(o.id for o in finished) == sorted(f"r{i}" for i in range(len(reqs)))
+        assert not cache.requests
+        outs[greedy] = {o.id: o.completion_ids for o in finished}
+    assert outs[True] == outs[False]
