@@ -17,6 +17,7 @@ from __future__ import annotations
 from dataclasses import dataclass, field
 from typing import Mapping
 
+import numpy as np
 import torch
 
 from tokasaurus_b200.cache.pages import NoSpaceError, PageAllocator
@@ -59,9 +60,21 @@ class RequestCache:
     slot: int
     tables: list[list[int]]  # per group; -1 where a page was given back behind a window
     released: list[int] = field(default_factory=list)  # per group: leading pages already given back
+    arrays: dict[int, np.ndarray] = field(default_factory=dict)  # per group: tables[g] as int32, made on demand
 
     def live_pages(self, g: int) -> list[int]:
         return [p for p in self.tables[g] if p >= 0]
+
+    def table_array(self, g: int) -> np.ndarray:
+        """``tables[g]`` as an int32 array.  A step of many requests at long contexts brings thousands of page
+        ids; turning Python lists into an array every step costs more than everything else the host does for
+        the step, so the array is kept and made anew only when the table has grown (or lost pages behind a
+        window, which drops it)."""
+        a = self.arrays.get(g)
+        if a is None or a.shape[0] != len(self.tables[g]):
+            a = np.asarray(self.tables[g], dtype=np.int32)
+            self.arrays[g] = a
+        return a
 
 
 class CacheManager:
@@ -171,6 +184,7 @@ class CacheManager:
                 g.allocator.release(pages, request)
                 for i in range(lo, full_pages_behind):
                     rc.tables[g.index][i] = -1
+                rc.arrays.pop(g.index, None)
                 rc.released[g.index] = full_pages_behind
                 count += len(pages)
         return count

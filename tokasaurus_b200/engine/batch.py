@@ -162,7 +162,7 @@ def build_host_batch(entries: Sequence[StepEntry], cache_manager) -> HostBatch:
     ps = cache_manager.page_size
     n_groups = len(cache_manager.groups)
     indptr = [[0] for _ in range(n_groups)]
-    pages: list[list[int]] = [[] for _ in range(n_groups)]
+    pages: list[list[np.ndarray]] = [[] for _ in range(n_groups)]  # per group: each request's page ids
     for s, e in enumerate(entries):
         if e.request in seen:
             raise ValueError(f"request {e.request!r} appears twice in one step")
@@ -173,12 +173,12 @@ def build_host_batch(entries: Sequence[StepEntry], cache_manager) -> HostBatch:
         rc = cache_manager.requests[e.request]
         end = e.start + n
         for g in range(n_groups):
-            table = rc.tables[g]
+            table = rc.table_array(g)
             need = (end + ps - 1) // ps
-            if len(table) < need:
-                raise ValueError(f"request {e.request!r} holds {len(table)} pages of group {g}, needs {need}")
-            pages[g].extend(table[:need])
-            indptr[g].append(len(pages[g]))
+            if table.shape[0] < need:
+                raise ValueError(f"request {e.request!r} holds {table.shape[0]} pages of group {g}, needs {need}")
+            pages[g].append(table[:need])
+            indptr[g].append(indptr[g][-1] + need)
         base = len(tok)
         tok.extend([-1] if e.tokens is None else [int(t) for t in e.tokens])
         pos.extend(range(e.start, end))
@@ -193,4 +193,6 @@ def build_host_batch(entries: Sequence[StepEntry], cache_manager) -> HostBatch:
         kv_len.append(end)
     i32 = lambda x: np.asarray(x, dtype=np.int32)  # noqa: E731
     return HostBatch(i32(tok), i32(pos), i32(tseq), i32(slot), i32(q_start), i32(q_len), i32(kv_len), i32(rows),
-                     [i32(x) for x in indptr], [i32(x) for x in pages], [e.request for e in entries])
+                     [i32(x) for x in indptr],
+                     [np.concatenate(x) if x else np.zeros((0,), dtype=np.int32) for x in pages],
+                     [e.request for e in entries])
