@@ -118,12 +118,19 @@ class Engine:
     def _sampling_arrays(self, plan: StepPlan) -> dict[str, np.ndarray]:
         rows = [p for p in plan.portions if p.samples]
         temp = np.asarray([p.seq.request.sampling_params.temperature for p in rows], dtype=np.float32)
-        keys = np.asarray(
-            [stream_key(p.seq.request.sampling_params.seed if p.seq.request.sampling_params.seed is not None
-                        else self.seed, p.seq.index) for p in rows], dtype=np.int64)
+        keys = np.asarray([self._stream_key(p.seq) for p in rows], dtype=np.int64)
         pos = np.asarray([p.start + p.n_tokens for p in rows], dtype=np.int32)
         slot = np.asarray([self.runner.cache.slot(p.seq.id) for p in rows], dtype=np.int32)
         return dict(temperature=temp, stream_key=keys, sample_pos=pos, row_slot=slot)
+
+    def _stream_key(self, seq) -> int:
+        """The key of the request's random stream (its seed, or the engine's, and its running number): worked out
+        once a request, not once a step."""
+        key = getattr(seq, "stream_key", None)
+        if key is None:
+            sp = seq.request.sampling_params
+            key = seq.stream_key = stream_key(sp.seed if sp.seed is not None else self.seed, seq.index)
+        return key
 
     def step(self) -> list[RequestOutput]:
         """Run one step and account for it; return the requests that ended in it.
