@@ -150,3 +150,18 @@ def test_stored_32bit_policy(tmp_path):
     assert target_dtype(WeightSpec("m", (2, 2)), torch.float32, torch.bfloat16) == torch.bfloat16
     assert target_dtype(WeightSpec("t", (2,), role="table"), torch.int64, torch.bfloat16) == torch.int32
     assert target_dtype(WeightSpec("v", (2,), role="vector"), torch.bfloat16, torch.bfloat16) == torch.float32
+
+
+def test_command_line_help_lists_every_option(capsys):
+    from dataclasses import fields
+
+    from tokasaurus_b200.config.engine_config import EngineConfig
+    from tokasaurus_b200.engine import cli
+
+    assert cli.main(["--help"]) == 0
+    out = capsys.readouterr().out
+    for f in fields(EngineConfig):
+        assert f"  {f.name}=" in out
+    for k in cli.RUN_OPTIONS:
+        assert f"  {k}=<" in out
+    assert "greedy_prefill=True" in out and "page_size=16" in out

@@ -45,10 +45,22 @@ def _read_prompts(opts: dict) -> list[list[int]]:
     return prompts
 
 
+def help_text() -> str:
+    """The module's description, then every option with its default: the engine's (``EngineConfig``, under the
+    reference's names) and those of this command."""
+    from dataclasses import fields
+
+    lines = [__doc__.rstrip(), "", "engine options (key=value):"]
+    lines += [f"  {f.name}={f.default!r}" for f in fields(EngineConfig)]
+    lines += ["", "options of this command:"]
+    lines += [f"  {k}=<{t.__name__}>" for k, t in RUN_OPTIONS.items()]
+    return "\n".join(lines)
+
+
 def main(argv: list[str] | None = None) -> int:
     argv = sys.argv[1:] if argv is None else argv
     if not argv or argv[0] in ("-h", "--help"):
-        print(__doc__)
+        print(help_text())
         return 0
     try:
         cfg, opts = parse_overrides(argv, EngineConfig, RUN_OPTIONS)
