@@ -462,25 +462,41 @@ def run_further(args) -> dict:
 
 
 def run_reference(args) -> dict:
+    """The reference arm: baseline/reference_arm.py in a process of its own (it imports nothing of this
+    repository's package), which drives the unmodified reference installed under baseline/_ref.  Its JSON line
+    is passed on; if it cannot run, the line says why."""
     ref = os.path.join(ROOT, "baseline", "_ref")
-    why = None
     if not os.path.isdir(os.path.join(ref, "tokasaurus")):
-        why = ("the reference is not installed under baseline/_ref (offline install lacks its pinned dependencies: "
-               "pydra-config, accelerate, art, statsd, flashinfer-python==0.2.0.post2)")
-    else:
-        missing = []
-        sys.path.insert(0, ref)
-        for mod in ("pydra", "accelerate", "art", "statsd"):
-            try:
-                __import__(mod)
-            except Exception:
-                missing.append(mod)
-        if missing:
-            why = f"the reference imports packages this image lacks and no wheel provides: {', '.join(missing)}"
-        else:
-            why = ("the reference's model code calls FlashInfer 0.2.0.post2 entry points (plan(head_dim=...), "
-                   "sampling_from_probs(probs, uniform)) that the installed FlashInfer 0.6.11 no longer has")
-    return {"impl": "reference", "unavailable": why}
+        return {"impl": "reference", "unavailable": "the reference is not installed under baseline/_ref (pip install "
+                "--no-index --no-deps --target baseline/_ref from a copy of the reference's tree)"}
+    cmd = [sys.executable, os.path.join(ROOT, "baseline", "reference_arm.py"), "--steps", str(args.steps), "--warmup",
+           str(args.warmup), "--batch", str(args.batch)]
+    if args.layers:
+        cmd += ["--layers", str(args.layers)]
+    if args.skip_points:
+        cmd += ["--skip-points"]
+    env = dict(os.environ)
+    env.pop("PYTHONPATH", None)
+    clocks = ClockSampler()
+    clocks.start()
+    try:
+        proc = subprocess.run(cmd, cwd=os.path.join(ROOT, "baseline"), env=env, stdout=subprocess.PIPE,
+                              stderr=subprocess.PIPE, text=True, timeout=args.reference_timeout)
+    except subprocess.TimeoutExpired:
+        clocks.stop()
+        return {"impl": "reference", "unavailable": f"the reference arm did not finish in {args.reference_timeout} s"}
+    clock_info = clocks.stop()
+    line = None
+    for text in reversed(proc.stdout.splitlines()):
+        if text.startswith("{") and '"impl"' in text:
+            line = text
+            break
+    if proc.returncode != 0 or line is None:
+        tail = " | ".join((proc.stderr or proc.stdout).strip().splitlines()[-3:])[-400:]
+        return {"impl": "reference", "unavailable": f"the reference arm exited with {proc.returncode}: {tail}"}
+    out = json.loads(line)
+    out["clocks"] = clock_info
+    return out
 
 
 def main() -> int:
@@ -492,6 +508,7 @@ def main() -> int:
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration (0: all)")
     ap.add_argument("--skip-points", action="store_true", help="leave out the batch-1 and batch-64 points")
+    ap.add_argument("--reference-timeout", type=int, default=1500, help="seconds the reference arm may take")
     ap.add_argument("--config", type=int, default=2, choices=[2, 3, 4],
                     help="2: the headline metric (default); 3 and 4: the further workloads, see run_further")
     args = ap.parse_args()
