@@ -132,15 +132,22 @@ def philox4x32_10(ctr: np.ndarray, key: np.ndarray) -> np.ndarray:
     return c.astype(np.uint32)
 
 
+def uniform_open(bits: np.ndarray) -> np.ndarray:
+    """32 random bits -> a float32 inside (0, 1), with the kernel's float32 operations: 23 bits plus one half
+    are exact in a 24-bit significand (24 bits plus one half are not: the largest would round up to 1)."""
+    return ((bits.astype(np.uint32) >> np.uint32(9)).astype(np.float32) + np.float32(0.5)) * np.float32(1.0 / 8388608.0)
+
+
 def gumbel_noise(vocab: int, stream_key: int, pos: int) -> np.ndarray:
-    """The Gumbel noise the sampling kernel adds to row logits / T (float64 here)."""
+    """The Gumbel noise the sampling kernel adds to row logits / T (the uniform in float32 as in the kernel,
+    the logarithms in float64)."""
     groups = (vocab + 3) // 4
     ctr = np.zeros((groups, 4), dtype=np.uint32)
     ctr[:, 0] = np.arange(groups, dtype=np.uint32)
     ctr[:, 1] = np.uint32(pos)
     key = np.array([stream_key & 0xFFFFFFFF, (stream_key >> 32) & 0xFFFFFFFF], dtype=np.uint32)
     r = philox4x32_10(ctr, key).reshape(-1)[:vocab]
-    u = ((r >> 8).astype(np.float64) + 0.5) / 16777216.0
+    u = uniform_open(r).astype(np.float64)
     return -np.log(-np.log(u))
 
 

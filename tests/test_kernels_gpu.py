@@ -307,6 +307,23 @@ def test_sampling_matches_plain_gumbel_draw(ops, V):
     assert again.tolist() == ids[order].tolist()
 
 
+def test_sampling_noise_at_the_extremes_of_the_random_bits(ops):
+    """All bits set must not round the uniform number up to 1 (Gumbel value +inf: that entry would win whatever
+    its logit), no bit set must not give 0; the kernel's float32 uniform equals the plain statement bit for bit."""
+    patterns = np.array([0xFFFFFFFF, 0xFFFFFE00, 0xFFFFFDFF, 0, 1, 0x1FF, 0x200, 0x80000000, 0x7FFFFFFF, 12345678],
+                        dtype=np.uint32)
+    rnd = np.random.default_rng(0).integers(0, 2**32, size=4096, dtype=np.uint64).astype(np.uint32)
+    bits = np.concatenate([patterns, rnd])
+    u, gum = ops.noise_of_bits(torch.from_numpy(bits.view(np.int32)).to(DEV))
+    u, gum = u.cpu().numpy(), gum.cpu().numpy()
+    assert (u > 0).all() and (u < 1).all() and np.isfinite(gum).all()
+    want = ref.uniform_open(bits)
+    assert want.dtype == np.float32 and np.array_equal(u, want)
+    np.testing.assert_allclose(gum, -np.log(-np.log(want.astype(np.float64))), rtol=2e-5, atol=2e-6)
+    # a row whose every entry but one is far ahead: the far-behind entry never wins, whatever the noise can be
+    assert gum.max() < 17 and gum.min() > -3
+
+
 def test_sampling_follows_the_distribution(ops):
     """20,000 draws from a 7-way distribution at T = 0.8: chi-square against softmax(logits / T)."""
     V, N, T = 7, 20000, 0.8

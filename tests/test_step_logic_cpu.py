@@ -66,3 +66,20 @@ def test_graph_eligibility_of_a_step():
     assert not g.usable_general([StepEntry("a", [1, 2, 3], 158, [2])])        # 161 tokens: 11 pages
     unlimited = DecodeGraphs(runner, None, max_size=8, step=4, max_tokens=0)
     assert unlimited.usable([one("b", 10 ** 6)]) and not unlimited.usable_general([StepEntry("a", [1, 2], 0, [1])])
+
+
+def test_uniform_of_random_bits_stays_inside_the_open_interval():
+    """The plain statement of the sampler's uniform number, in float32 as the kernel computes it: all bits set
+    gives a number below 1 and a finite Gumbel value, no bit set a number above 0."""
+    import numpy as np
+
+    import kernel_refs as ref
+
+    bits = np.array([0xFFFFFFFF, 0, 0xFFFFFE00, 0x1FF], dtype=np.uint32)
+    u = ref.uniform_open(bits)
+    assert u.dtype == np.float32 and (u > 0).all() and (u < 1).all()
+    assert u[0] == np.float32(8388607.5 / 8388608.0) and u[1] == np.float32(0.5 / 8388608.0)
+    g = -np.log(-np.log(u.astype(np.float64)))
+    assert np.isfinite(g).all()
+    # the form with 24 random bits, which the kernel must not use: it rounds up to exactly 1
+    assert (np.float32(0xFFFFFF) + np.float32(0.5)) * np.float32(1.0 / 16777216.0) == np.float32(1.0)

@@ -29,9 +29,12 @@ struct Philox {
 };
 
 __device__ __forceinline__ float uniform_open(uint32_t x) {
-  // (0, 1), exactly representable: 24 random bits plus one half.
-  return ((float)(x >> 8) + 0.5f) * (1.0f / 16777216.0f);
+  // Inside (0, 1) and exact in float32: 23 random bits plus one half need 24 bits of significand, so the
+  // largest value is 8388607.5 / 8388608 < 1 and the smallest 0.5 / 8388608 > 0.  (With 24 random bits the
+  // sum 16777215.5 would round to 16777216, u = 1 and the Gumbel value to +inf.)
+  return ((float)(x >> 9) + 0.5f) * (1.0f / 8388608.0f);
 }
+__device__ __forceinline__ float gumbel_of(uint32_t x) { return -logf(-logf(uniform_open(x))); }
 
 struct Best {
   float v;
@@ -97,7 +100,7 @@ sample_kernel(const float* __restrict__ logits, const float* __restrict__ temper
         l += expf(z - m);
       }
       float score = z;
-      if (!greedy) score = z - logf(-logf(uniform_open(rr[u])));
+      if (!greedy) score = z + gumbel_of(rr[u]);
       Best c = {score, i};
       best = better(best, c);
     }
@@ -278,7 +281,7 @@ sample_chunk_kernel(const float* __restrict__ logits, const float* __restrict__ 
         l += expf(z - m);
       }
       float score = z;
-      if (!greedy) score = z - logf(-logf(uniform_open(rr[u])));
+      if (!greedy) score = z + gumbel_of(rr[u]);
       Best c = {score, i};
       best = better(best, c);
     }
@@ -378,6 +381,26 @@ TKB_EXPORT int tkb_sample_two_stage(const float* logits, const float* temperatur
   if (rc) return rc;
   return launch_pdl(sample_finish_kernel, dim3(R), dim3(32), 0, (cudaStream_t)st, logits, temperature,
                     (const float4*)part, row_slot, out_ids, out_logprob, last_token, V, nch);
+}
+
+namespace {
+__global__ void noise_of_bits_kernel(const uint32_t* __restrict__ bits, float* __restrict__ uniform,
+                                     float* __restrict__ gumbel, int n) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) {
+    uniform[i] = uniform_open(bits[i]);
+    gumbel[i] = gumbel_of(bits[i]);
+  }
+}
+
+}  // namespace
+
+// The uniform number and the Gumbel value that the sampling kernels make of 32 random bits, for tests of the
+// extremes (all bits set, no bit set), which a Philox draw reaches once in 2^32.
+TKB_EXPORT int tkb_noise_of_bits(const uint32_t* bits, float* uniform, float* gumbel, int n, cudaStream_t st) {
+  if (n <= 0) return 0;
+  noise_of_bits_kernel<<<(n + 255) / 256, 256, 0, st>>>(bits, uniform, gumbel, n);
+  return launch_status();
 }
 
 TKB_EXPORT int tkb_topk_logprobs(const float* logits, const float* temperature, int* out_idx, float* out_lp, int R,

@@ -549,6 +549,18 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor | None, stream_key: t
              _ptr(out_logprob), _ptr(last_token), c_int(R), c_int(V), _stream()), "sample")
 
 
+def noise_of_bits(bits: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+    """The uniform number in (0, 1) and the Gumbel value the sampling kernels make of 32 random bits each
+    (``bits``: int32 holding the bit patterns).  For tests of the extremes."""
+    _need_cuda(bits)
+    _need(bits.dtype == torch.int32 and bits.is_contiguous(), "noise_of_bits: bits must be contiguous int32")
+    u = torch.empty(bits.numel(), dtype=torch.float32, device=bits.device)
+    g = torch.empty_like(u)
+    _check(_fn(_libs.get("sampling.cu"), "tkb_noise_of_bits")(_ptr(bits), _ptr(u), _ptr(g), c_int(bits.numel()), _stream()),
+           "noise_of_bits")
+    return u, g
+
+
 def topk_logprobs(logits: torch.Tensor, temperature: torch.Tensor | None, k: int, out_idx: torch.Tensor,
                   out_lp: torch.Tensor) -> None:
     _need_cuda(logits, temperature, out_idx, out_lp)
