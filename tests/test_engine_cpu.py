@@ -124,3 +124,30 @@ def test_steps_ahead_and_paced_prefill_options_reach_the_engine(cpu_kernels, tin
     eng = make_engine(d, greedy_prefill=False, prefill_round_up_multiple=4, max_seqs_per_forward=2, max_tokens_per_forward=32)
     outs = eng.generate(prompts, max_num_tokens=6, ignore_eos=True)
     assert [o.completion_ids for o in outs] == [plain.greedy(p, 6) for p in prompts]
+
+
+def test_windowed_attention_through_scheduler_and_cache(cpu_kernels, tmp_path):
+    """A toy model whose attention sees a window of 21 keys (pages of 8): prompts longer than the window, decoding
+    across several page releases, first with room for everything, then in a pool so small that requests are pushed
+    out and fed again through the windowed group.  The tokens equal a plain windowed implementation's."""
+    import test_window_gpu as tw
+    from tokasaurus_b200.config import unregister_architecture
+    from tokasaurus_b200.weights import write_model_folder
+
+    tw.define_toy()
+    try:
+        c = tw.SMALL
+        folder = write_model_folder(tmp_path / "toy", c, seed=11, std=0.08, norm_init="uniform")
+        p64 = tw.PlainWindowed(folder, c)
+        prompts = [cuttings.random_tokens(n, c["vocab_size"], 300 + n) for n in (45, 9, 30, 26, 52)]
+        want = [p64.greedy(p, 24) for p in prompts]
+        for pool, opts in ((1024, {}), (104, dict(bump_city_population_me=True))):
+            eng = make_engine(folder, page_size=8, kv_cache_num_tokens=pool, max_tokens_per_forward=24,
+                              max_seqs_per_forward=4, **opts)
+            outs = eng.generate(prompts, max_num_tokens=24, ignore_eos=True)
+            assert [o.completion_ids for o in outs] == want
+            assert not eng.runner.cache.requests and eng.runner.cache.num_free_pages() == [pool // 8]
+            if opts:
+                assert eng.scheduler.stats["bumps"] > 0
+    finally:
+        unregister_architecture(tw.NAME)

@@ -234,3 +234,55 @@ def test_paced_prefill_under_random_load_always_ends(seed):
         assert not cache.requests
         outs[greedy] = {o.id: o.completion_ids for o in finished}
     assert outs[True] == outs[False]
+
+
+def test_a_request_id_in_use_is_refused():
+    s, _ = make()
+    s.add_request(req(0, 5, 3))
+    with pytest.raises(ValueError, match="already queued or running"):
+        s.add_request(req(0, 7, 3))
+    s.complete(s.schedule(), [7])
+    with pytest.raises(ValueError, match="already queued or running"):
+        s.add_request(req(0, 7, 3))
+    run(s)
+    s.add_request(req(0, 7, 3))  # the first owner has ended: the id is free again
+
+
+def test_reserve_is_kept_per_cache_group():
+    """Two cache groups, the FIRST with a window: a sequence of a windowed group never holds more pages than the
+    window and one step's tokens take, so the full group is what limits admission, and nothing is ever pushed
+    out under the worst-case reserve."""
+    needs = {0: PagedCacheNeed(1, 16, window=6), 1: PagedCacheNeed(1, 16)}
+    cache = CacheManager(needs, page_size=4, num_pages=12, max_requests=8)
+    assert [g.need.window for g in cache.groups] == [6, None]
+    s = Scheduler(cache, 8, 8, sanity_checks=True)
+    for i in range(5):
+        s.add_request(req(i, 8, 9))  # each comes to hold 4 pages of the full group: 3 fit at a time
+    plan = s.schedule()
+    assert len(s.prefilling) == 3 and len(s.queued) == 2
+    # the windowed group: at most pages_for(6 + 8) + 1 = 5 live pages a sequence, so it sets aside less than the
+    # 4 - 2 a sequence of the full group still needs only when the cap bites; here both groups ask for 2 more each
+    assert s._headroom() == [12 - 6 - 6, 12 - 6 - 6]
+    fin, plans = run(s)
+    assert len(fin) == 5 and s.stats["bumps"] == 0
+    assert cache.num_free_pages() == [12, 12]
+    # pages of the windowed group came back while their sequences ran: its tables hold -1 at the front
+    s.add_request(req(9, 20, 12))
+    for _ in range(6):
+        plan = s.schedule()
+        s.complete(plan, [7] * sum(p.samples for p in plan.portions))
+    rc = cache.requests["r9"]
+    assert rc.tables[0][0] == -1 and rc.tables[1][0] >= 0
+    assert s._still_needed(s.running()[0], 0) <= s._still_needed(s.running()[0], 1)
+
+
+def test_long_requests_in_a_windowed_pool_smaller_than_their_length():
+    """With a window in every group, the reserve per sequence is capped by what a window and a step's tokens take,
+    so requests far longer than the pool run side by side without being pushed out."""
+    cache = CacheManager({0: PagedCacheNeed(1, 16, window=8)}, page_size=4, num_pages=16, max_requests=8)
+    s = Scheduler(cache, 4, 8, sanity_checks=True)
+    for i in range(2):
+        s.add_request(req(i, 4, 60))  # 63 positions = 16 pages each without the window
+    fin, plans = run(s)
+    assert len(fin) == 2 and s.stats["bumps"] == 0
+    assert max(len(p.portions) for p in plans) == 2  # they did run together

@@ -122,6 +122,8 @@ class Scheduler:
             raise RequestTooLongError(
                 f"request {request.id!r} can need {self.cache.pages_for(total - 1)} pages, the pool has "
                 f"{self.cache.num_pages}")
+        if any(s.id == request.id for s in self.queued) or any(s.id == request.id for s in self.running()):
+            raise ValueError(f"request id {request.id!r} is already queued or running (the cache is keyed by it)")
         seq = Sequence(request, self._counter, RequestOutput(request.id))
         self._counter += 1
         self.queued.append(seq)
@@ -134,16 +136,42 @@ class Scheduler:
         return self.decoding + self.prefilling
 
     # ------------------------------------------------------------------ pages
-    def _reserved_for_running(self) -> int:
-        """Pages that running sequences may still ask for, scaled by the reserve fraction."""
-        if self.reserve_fraction <= 0:
-            return 0
-        ps = self.cache.pages_for
-        need = 0
-        for s in self.running():
-            held = len(self.cache.requests[s.id].tables[0]) if self.cache.groups else 0
-            need += max(0, ps(s.max_total()) - held)
-        return int(need * self.reserve_fraction + 0.999999)
+    def _still_needed(self, seq: Sequence, g: int, held: int | None = None) -> int:
+        """Pages of cache group ``g`` that the sequence can still ask for on top of the ``held`` it holds (None:
+        what its table holds now; 0 for a sequence that is not admitted yet).  Every group's table grows with the
+        sequence's length; in a group with a window, pages behind the window come back, so a sequence never holds
+        more than the window and one step's tokens take."""
+        group = self.cache.groups[g]
+        total = self.cache.pages_for(seq.max_total())
+        if held is None:
+            rc = self.cache.requests[seq.id]
+            allocated, held = len(rc.tables[g]), len(rc.tables[g]) - rc.released[g]
+        else:
+            allocated = held
+        need = max(0, total - allocated)
+        if group.need.window:
+            most_live = self.cache.pages_for(group.need.window + self.max_tokens) + 1
+            need = min(need, max(0, most_live - held))
+        return need
+
+    def _headroom(self) -> list[int]:
+        """Per cache group: free pages less what running sequences may still ask for, scaled by the reserve fraction."""
+        f = self.reserve_fraction
+        out = []
+        for g, group in enumerate(self.cache.groups):
+            reserved = 0
+            if f > 0:
+                reserved = int(sum(self._still_needed(s, g) for s in self.running()) * f + 0.999999)
+            out.append(group.allocator.num_free - reserved)
+        return out
+
+    def _admission_need(self, seq: Sequence) -> list[int]:
+        """Per cache group: pages a queued sequence takes at admission (its whole prompt, as the reference's
+        ``allocate_with_prefix_match`` does) plus its share of the reserve."""
+        first_need = self.cache.pages_for(seq.n_known)
+        f = self.reserve_fraction
+        return [first_need + (int(max(0, self._still_needed(seq, g, first_need)) * f + 0.999999) if f > 0 else 0)
+                for g in range(len(self.cache.groups))]
 
     def _min_free(self) -> int:
         free = self.cache.num_free_pages()
@@ -153,11 +181,7 @@ class Scheduler:
         while self.queued and len(self.prefilling) + len(self.decoding) < self.max_seqs \
                 and self.cache.slots.num_free > 0:
             seq = self.queued[0]
-            first_need = self.cache.pages_for(seq.n_known)
-            reserve_own = 0
-            if self.reserve_fraction > 0:
-                reserve_own = int((self.cache.pages_for(seq.max_total()) - first_need) * self.reserve_fraction + 0.999999)
-            if self._min_free() - self._reserved_for_running() < first_need + max(0, reserve_own):
+            if any(room < need for room, need in zip(self._headroom(), self._admission_need(seq))):
                 break
             self.queued.popleft()
             self.cache.admit(seq.id)
@@ -251,9 +275,9 @@ class Scheduler:
         outstanding by then, spread over the steps until then, are one candidate, and the smallest candidate
         wins.  Once the whole queue fits, later ends ask for nothing slower."""
         cache, f = self.cache, self.reserve_fraction
-        pages_for = cache.pages_for
+        groups = range(len(cache.groups))
         outstanding = sum(s.n_known - s.fed for s in self.prefilling)
-        available = self._min_free() - self._reserved_for_running()
+        available = self._headroom()
         running = len(self.prefilling) + len(self.decoding)
         slots = min(self.max_seqs, running + cache.slots.num_free)
         queue = list(self.queued)
@@ -262,18 +286,18 @@ class Scheduler:
         pace = float("inf")
         for seq in sorted(self.decoding, key=lambda s: s.max_total() - s.fed):
             steps = max(1, seq.max_total() - seq.fed)  # steps from now after which this sequence has ended
-            held = len(cache.requests[seq.id].tables[0]) if cache.groups else 0
-            growth = max(0, pages_for(seq.max_total()) - held)
-            available += held + int(f * growth)
+            rc = cache.requests[seq.id]
+            for g in groups:
+                # what it holds comes back, and its share of the reserve is no longer set aside
+                available[g] += len(rc.tables[g]) - rc.released[g] + int(f * self._still_needed(seq, g))
             running -= 1
             while at < len(queue) and running < slots:
-                q = queue[at]
-                first_need = pages_for(q.n_known)
-                need = first_need + max(0, int((pages_for(q.max_total()) - first_need) * f + 0.999999))
-                if need > available:
+                need = self._admission_need(queue[at])
+                if any(n > a for n, a in zip(need, available)):
                     break
-                available -= need
-                onboarded += q.n_known
+                for g in groups:
+                    available[g] -= need[g]
+                onboarded += queue[at].n_known
                 running += 1
                 at += 1
             if at == len(queue):
