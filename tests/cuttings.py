@@ -93,6 +93,28 @@ def mixed(reqs: dict[str, list[int]], max_live: int = 4, prompt_frac: float = 0.
     return steps
 
 
+def waves_of_decoding(reqs: dict[str, list[int]], wave: int, tail: int = 6, prefill_group: int = 8):
+    """Decode steps of many requests: the requests run in waves of ``wave``; within a wave, each request's tokens
+    but the last ``tail`` go in as whole prompts, ``prefill_group`` requests a step, then ``tail`` steps follow in
+    which EVERY request of the wave brings one token; then the wave ends and the next one takes over its pages."""
+    steps = []
+    items = list(reqs.items())
+    for w in range(0, len(items), wave):
+        group = items[w:w + wave]
+        for g in range(0, len(group), prefill_group):
+            entries = []
+            for rid, toks in group[g:g + prefill_group]:
+                cut = max(1, len(toks) - tail)
+                entries.append(dict(id=rid, tokens=toks[:cut], want=list(range(cut))))
+            steps.append(dict(step=len(steps), entries=entries, end=[]))
+        for t in range(tail, 0, -1):
+            entries = [dict(id=rid, tokens=[toks[len(toks) - t]], want=[0]) for rid, toks in group if len(toks) > t]
+            if entries:
+                steps.append(dict(step=len(steps), entries=entries, end=[]))
+        steps[-1]["end"] = [rid for rid, _ in group]
+    return steps
+
+
 def max_live_tokens(steps, round_to: int = 64) -> int:
     """The --max-tokens a trace needs: the most tokens live requests hold at any time, each
     request's count rounded up to a multiple of ``round_to``."""

@@ -12,8 +12,10 @@ call (the float32 logits are captured instead).  Packages the reference imports 
 lacks (pydra, accelerate, art, statsd) are stubbed.  The attention inner product and the sampling
 therefore rest on the formulas, not on the reference's code.
 
-Outputs (committed): tests/golden/reference_cfg1_logits.npy (float32 [12, 509]: 11 prompt rows from
-a whole-prompt step and 1 row from a decode step) and reference_cfg1_meta.json.
+Outputs (committed), for each of the two tiny test configurations i = 0 (tied head, plain rotary, two kv heads, pages
+of 16) and 1 (own head, llama3 rotary scaling, one kv head, pages of 8): tests/golden/reference_cfg<i>_logits.npy
+(float32 [tokens, vocab]: the prompt rows from a whole-prompt step and 1 row from a decode step) and
+reference_cfg<i>_meta.json.
 """
 
 import contextlib
@@ -83,9 +85,20 @@ def main():
     from tokasaurus_b200.weights import write_model_folder
     from safetensors import safe_open
 
-    cfgd = tiny_configs()[1]
+    from plain_llama import TINY_WEIGHTS
+
+    for index in (0, 1):
+        golden_for(index, L, LayerKVCache, AttentionInfoBuilder, BatchSamplingParams, BatchState, ExtraModelConfig,
+                   ModelOutputTensors, PageInformationBuilder, LlamaConfig, PlainLlama, tiny_configs()[index],
+                   TINY_WEIGHTS[index], rope_inv_freq, rope_tables, write_model_folder, safe_open)
+
+
+def golden_for(index, L, LayerKVCache, AttentionInfoBuilder, BatchSamplingParams, BatchState, ExtraModelConfig,
+               ModelOutputTensors, PageInformationBuilder, LlamaConfig, PlainLlama, cfgd, wopt, rope_inv_freq,
+               rope_tables, write_model_folder, safe_open):
     tmp = Path(tempfile.mkdtemp())
-    folder = write_model_folder(tmp / "cfg1", cfgd, seed=1, std=0.05, norm_init="uniform", store_dtype="float32")
+    folder = write_model_folder(tmp / f"cfg{index}", cfgd, seed=wopt["seed"], std=wopt["std"],
+                                norm_init=wopt["norm_init"], store_dtype="float32")
 
     hf_cfg = LlamaConfig(**{k: v for k, v in cfgd.items() if k not in ("architectures", "model_type")})
     torch.set_default_dtype(torch.float32)
@@ -106,7 +119,7 @@ def main():
     rope_diff = max((cos - model.model.rope_cos).abs().max().item(), (sin - model.model.rope_sin).abs().max().item())
 
     # 2. forward on the CPU with the attention and sampling library calls replaced
-    ps = 8
+    ps = wopt["page_size"]
 
     def cpu_attention(ragged_q, ragged_k, ragged_v, k_cache, v_cache, attn_info, wrappers):
         from tokasaurus.model.attention_utils import append_to_kv_cache
@@ -167,10 +180,11 @@ def main():
             return model(bs)
 
     g = torch.Generator().manual_seed(3)
-    ids = torch.randint(0, cfgd["vocab_size"], (12,), generator=g)
-    step(ids[:11], 0, [3, 5], list(range(11)))
+    n_ids = 12 if index == 1 else 21  # the prompt crosses a page edge in both
+    ids = torch.randint(0, cfgd["vocab_size"], (n_ids,), generator=g)
+    step(ids[:n_ids - 1], 0, [3, 5], list(range(n_ids - 1)))
     whole = captured[-1]
-    step(ids[11:12], 11, [3, 5], [0], decode=True)
+    step(ids[n_ids - 1:], n_ids - 1, [3, 5], [0], decode=True)
     dec = captured[-1]
     ref_logits = torch.cat([whole, dec], 0).float().numpy()
 
@@ -178,12 +192,12 @@ def main():
     plain64 = PlainLlama(folder, torch.float64).logits(ids.tolist()).double().numpy()
     d32 = float(np.abs(plain32 - ref_logits).max())
     d64 = float(np.abs(plain64 - ref_logits).max())
-    np.save(HERE / "reference_cfg1_logits.npy", ref_logits.astype(np.float32))
-    meta = dict(config=cfgd, seed=1, std=0.05, norm_init="uniform", store_dtype="float32", token_ids=ids.tolist(),
+    np.save(HERE / f"reference_cfg{index}_logits.npy", ref_logits.astype(np.float32))
+    meta = dict(config=cfgd, seed=wopt["seed"], std=wopt["std"], norm_init=wopt["norm_init"], store_dtype="float32", token_ids=ids.tolist(),
                 rope_table_max_abs_diff=rope_diff, plain32_vs_reference_max_abs=d32, plain64_vs_reference_max_abs=d64,
                 logits_abs_max=float(np.abs(ref_logits).max()), torch=torch.__version__,
                 weights_checksum=float(sum(t.double().sum().item() for t in tensors.values())))
-    with open(HERE / "reference_cfg1_meta.json", "w") as f:
+    with open(HERE / f"reference_cfg{index}_meta.json", "w") as f:
         json.dump(meta, f, indent=1)
     print(json.dumps({k: v for k, v in meta.items() if k != "config"}, indent=1))
 

@@ -75,8 +75,8 @@ def causal_gqa_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, wind
     k = k.repeat_interleave(group, dim=1)
     v = v.repeat_interleave(group, dim=1)
     scores = torch.einsum("qhd,khd->hqk", q, k) / math.sqrt(hd)
-    i = torch.arange(T).view(-1, 1)
-    j = torch.arange(T).view(1, -1)
+    i = torch.arange(T, device=q.device).view(-1, 1)
+    j = torch.arange(T, device=q.device).view(1, -1)
     hidden = j > i
     if window:
         hidden = hidden | (j <= i - window)
@@ -121,8 +121,11 @@ def lm_head(x, w, cfg):
 
 
 class PlainLlama:
-    def __init__(self, folder: str | Path, dtype: torch.dtype = torch.float64):
+    def __init__(self, folder: str | Path, dtype: torch.dtype = torch.float64, device: str = "cpu"):
+        """``device``: where the arithmetic runs (the CPU by default; a model of real layer sizes in float64 is
+        quicker with torch on the GPU, and is still this same plain arithmetic)."""
         folder = Path(folder)
+        self.device = device
         with open(folder / "config.json") as f:
             self.cfg = json.load(f)
         self.cfg.setdefault("rms_norm_eps", 1e-6)
@@ -130,14 +133,14 @@ class PlainLlama:
         self.w: dict[str, torch.Tensor] = {}
         with safe_open(str(folder / "model.safetensors"), framework="pt") as f:
             for k in f.keys():
-                self.w[k] = f.get_tensor(k).to(dtype)
+                self.w[k] = f.get_tensor(k).to(device=device, dtype=dtype)
         hd = self.cfg["hidden_size"] // self.cfg["num_attention_heads"]
-        self.inv_freq = rope_inv_freq(hd, self.cfg.get("rope_theta", 10000.0), self.cfg.get("rope_scaling"))
+        self.inv_freq = rope_inv_freq(hd, self.cfg.get("rope_theta", 10000.0), self.cfg.get("rope_scaling")).to(device)
 
     def logits(self, token_ids: list[int]) -> torch.Tensor:
         """Logits [T, vocab] at every position of one whole sequence."""
-        ids = torch.tensor(token_ids, dtype=torch.long)
-        positions = torch.arange(len(token_ids))
+        ids = torch.tensor(token_ids, dtype=torch.long, device=self.device)
+        positions = torch.arange(len(token_ids), device=self.device)
         x = self.w["model.embed_tokens.weight"][ids]  # tokasaurus/model/llama.py:514-518
         for i in range(self.cfg["num_hidden_layers"]):  # llama.py:580-581
             p = f"model.layers.{i}"

@@ -5,6 +5,7 @@ import json
 from pathlib import Path
 
 import numpy as np
+import pytest
 import torch
 
 from plain_llama import PlainLlama
@@ -12,11 +13,15 @@ from plain_llama import PlainLlama
 GOLDEN = Path(__file__).resolve().parent / "golden"
 
 
-def test_plain_matches_reference_golden(tmp_path):
+@pytest.mark.parametrize("index", [0, 1])
+def test_plain_matches_reference_golden(tmp_path, index):
+    """index 0: tied head (the reference reads the embedding for the head, tokasaurus/model/llama.py:842-845),
+    plain rotary, two kv heads; index 1: a head of its own, llama3 rotary scaling, one kv head."""
     from tokasaurus_b200.weights import write_model_folder
 
-    meta = json.load(open(GOLDEN / "reference_cfg1_meta.json"))
-    ref = np.load(GOLDEN / "reference_cfg1_logits.npy")
+    meta = json.load(open(GOLDEN / f"reference_cfg{index}_meta.json"))
+    ref = np.load(GOLDEN / f"reference_cfg{index}_logits.npy")
+    assert meta["config"]["tie_word_embeddings"] == (index == 0)
     folder = write_model_folder(tmp_path / "m", meta["config"], seed=meta["seed"], std=meta["std"],
                                 norm_init=meta["norm_init"], store_dtype=meta["store_dtype"])
     plain = PlainLlama(folder, torch.float64)

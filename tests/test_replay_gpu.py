@@ -26,12 +26,12 @@ def requests_for(cfg_index: int) -> dict[str, list[int]]:
             for i, n in enumerate(lengths)}
 
 
-def replay(model_dir, dtype, steps, page_size, max_tokens=None):
+def replay(model_dir, dtype, steps, page_size, max_tokens=None, max_requests=64):
     from tokasaurus_b200.engine.trace import TraceReplayer
 
     if max_tokens is None:
         max_tokens = cuttings.max_live_tokens(steps)
-    rp = TraceReplayer(str(model_dir), dtype, max_tokens, page_size=page_size)
+    rp = TraceReplayer(str(model_dir), dtype, max_tokens, page_size=page_size, max_requests=max_requests)
     outs = []
     for st in steps:
         outs.append(rp.run_step(st))
@@ -148,7 +148,7 @@ def test_trace_run_program(tiny_model_dirs, tmp_path):
     compare(got, p64, p32, "float32")
 
 
-def replay_through_graphs(model_dir, dtype, steps, page_size):
+def replay_through_graphs(model_dir, dtype, steps, page_size, max_seqs=8, graph_max=8, graph_step=4):
     """The steps of a cutting, each entry wanting the logits of its last token only (what generation asks of a
     step), run through the engine's CUDA graphs: decode graphs for steps of single tokens, graphs of the padded
     shape for steps with portions.  Returns {request: {position: logits}} and how many steps ran as graphs."""
@@ -156,7 +156,8 @@ def replay_through_graphs(model_dir, dtype, steps, page_size):
     from tokasaurus_b200.engine.engine import Engine
 
     eng = Engine(model=str(model_dir), dtype=dtype, page_size=page_size, kv_cache_num_tokens=cuttings.max_live_tokens(steps),
-                 max_seqs_per_forward=8, cudagraph_max_size=8, cudagraph_step=4, graph_max_tokens=4096)
+                 max_seqs_per_forward=max_seqs, cudagraph_max_size=graph_max, cudagraph_step=graph_step,
+                 graph_max_tokens=4096)
     cache, graphs = eng.runner.cache, eng.graphs
     lengths, got, n_graph = {}, {}, 0
     for st in steps:
@@ -236,3 +237,59 @@ def test_wide_heads_and_long_requests_match_plain(tmp_path, monkeypatch, hd):
         for pos, row in got[rid].items():
             err = float(np.abs(row - ref[pos]).max())
             assert err <= tol, f"request {rid} position {pos}: error {err:.3g}, tolerance {tol:.3g}"
+
+
+def many_requests(n: int, vocab: int, longest: int, seed: int) -> dict[str, list[int]]:
+    """2 * n requests (two waves of n) whose lengths cross page edges and the 64-key tiles of the attention kernels
+    while their last six tokens are decoded."""
+    rng = np.random.default_rng(seed)
+    edges = [7, 8, 9, 15, 17, 62, 64, 66, 68, 70, 126, 128, 131, 133, 190, 193, 255, 256]
+    lengths = [e for e in edges if e <= longest] + [int(x) for x in rng.integers(7, longest + 1, size=2 * n)]
+    rng.shuffle(lengths)
+    return {f"m{i}": cuttings.random_tokens(lengths[i], vocab, seed * 1000 + i) for i in range(2 * n)}
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("n", [20, 33, 64, 65, 128])
+def test_decode_steps_of_many_requests_match_plain(tiny_model_dirs, n, dtype):
+    """Decode steps of 20, 33, 64, 65 and 128 single-token requests (in bfloat16: the tcgen05 small-batch products
+    whose slices the attention kernel adds from 17 rows on, the library products with the separate rotary kernel from
+    65 on, graphs padded from 20 to 32, 33 to 48, 65 to 80 rows), eagerly and through the step graphs with the
+    reference's default graph sizes (step 16 up to 128), two waves in a pool that holds one."""
+    d, cfg = tiny_model_dirs[1], tiny_configs()[1]
+    reqs = many_requests(n, cfg["vocab_size"], 250, n)
+    p64 = cuttings.plain_logits(d, reqs, torch.float64)
+    p32 = cuttings.plain_logits(d, reqs, torch.float32) if dtype == "float32" else None
+    steps = cuttings.waves_of_decoding(reqs, n)
+    assert max(len(st["entries"]) for st in steps) == n
+    compare(replay(d, dtype, steps, 8, max_requests=128), p64, p32, dtype)
+    got, n_graph = replay_through_graphs(d, dtype, steps, 8, max_seqs=128, graph_max=128, graph_step=16)
+    assert n_graph >= 12  # every decode step of both waves
+    for rid, ref in p64.items():
+        tol = cuttings.tolerance(dtype, ref, p32[rid] if p32 else None)
+        for pos, row in got[rid].items():
+            err = float(np.abs(row - ref[pos]).max())
+            assert err <= tol, f"{dtype} n={n}: request {rid} position {pos}: error {err:.3g}, tolerance {tol:.3g}"
+
+
+@pytest.mark.parametrize("n", [20, 64, 65, 128])
+@pytest.mark.parametrize("hd", [64, 128])
+def test_decode_steps_of_many_requests_wide_heads(tmp_path, n, hd):
+    """The same with heads of 64 and 128 in bfloat16: whole tiles of keys by TMA, four query heads a kv head."""
+    from tokasaurus_b200.weights import write_model_folder
+
+    cfg = dict(architectures=["LlamaForCausalLM"], model_type="llama", num_hidden_layers=2, hidden_size=4 * hd,
+               num_attention_heads=4, num_key_value_heads=1, intermediate_size=96, vocab_size=300, rope_theta=10000.0,
+               rope_scaling=None, rms_norm_eps=1e-5, tie_word_embeddings=True, max_position_embeddings=1024)
+    d = write_model_folder(tmp_path / "wide", cfg, seed=4, std=0.04, norm_init="uniform")
+    reqs = many_requests(n, 300, 420, 7 * n + hd)
+    p64 = cuttings.plain_logits(d, reqs, torch.float64)
+    steps = cuttings.waves_of_decoding(reqs, n)
+    compare(replay(d, "bfloat16", steps, 16, max_requests=128), p64, None, "bfloat16")
+    got, n_graph = replay_through_graphs(d, "bfloat16", steps, 16, max_seqs=128, graph_max=128, graph_step=16)
+    assert n_graph >= 12
+    for rid, ref in p64.items():
+        tol = cuttings.tolerance("bfloat16", ref, None)
+        for pos, row in got[rid].items():
+            err = float(np.abs(row - ref[pos]).max())
+            assert err <= tol, f"hd={hd} n={n}: request {rid} position {pos}: error {err:.3g}, tolerance {tol:.3g}"
