@@ -119,6 +119,33 @@ def test_weight_errors_are_listed_together(tmp_path):
         assert word in msg
 
 
+def test_tensors_that_llama_checkpoints_may_carry_are_passed_over(tmp_path):
+    """The reference reads only the names it wants (tokasaurus/model/safetensors_utils.py:72-95): an older export
+    with rotary inverse frequencies, or a tied model that also stores its head, loads there.  Here such names are
+    declared by the architecture and passed over with a warning; any other extra tensor is still an error."""
+    from tokasaurus_b200.config import lookup_architecture
+
+    d = tiny_configs()[0]  # tied embeddings
+    folder = write_model_folder(tmp_path / "m", d, seed=0)
+    t = load_file(str(folder / "model.safetensors"))
+    t["model.layers.0.self_attn.rotary_emb.inv_freq"] = torch.zeros(8)
+    t["lm_head.weight"] = t["model.embed_tokens.weight"].clone()
+    save_file(t, str(folder / "model.safetensors"))
+    arch = lookup_architecture(d)
+    model = arch.build_model(arch.parse_config(d))
+    assert set(model.ignored_weight_patterns) == {"*.rotary_emb.inv_freq", "lm_head.weight"}
+    with pytest.warns(UserWarning, match="are not used"):
+        w = load_weights(folder, model.weight_specs(), torch.bfloat16, "cpu", ignore=model.ignored_weight_patterns)
+    assert "lm_head.weight" not in w and "model.embed_tokens.weight" in w
+    with pytest.raises(WeightLoadError) as e:
+        load_weights(folder, model.weight_specs(), torch.bfloat16, "cpu")
+    assert e.value.unexpected == ["lm_head.weight", "model.layers.0.self_attn.rotary_emb.inv_freq"]
+    # an untied model does read lm_head.weight, so it is not on its list
+    d1 = tiny_configs()[1]
+    arch1 = lookup_architecture(d1)
+    assert set(arch1.build_model(arch1.parse_config(d1)).ignored_weight_patterns) == {"*.rotary_emb.inv_freq"}
+
+
 def test_no_weight_files(tmp_path):
     (tmp_path / "config.json").write_text(json.dumps(tiny_configs()[0]))
     with pytest.raises(FileNotFoundError, match="safetensors"):

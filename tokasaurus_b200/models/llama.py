@@ -50,10 +50,15 @@ def build_llama(cfg: LlamaConfig) -> DecoderModel:
         )
     embed_name = "model.embed_tokens.weight"
     head_name = embed_name if cfg.tie_word_embeddings else "lm_head.weight"
+    # Tensors that Llama checkpoints may carry and that the reference, which reads only the names it wants
+    # (tokasaurus/model/safetensors_utils.py:72-95, load_state_dict(strict=False) at llama.py:940), passes over: the
+    # rotary tables' inverse frequencies of older exports, and a stored head beside tied embeddings.
+    ignored = ["*.rotary_emb.inv_freq"] + (["lm_head.weight"] if cfg.tie_word_embeddings else [])
     return DecoderModel(
         embedding=TokenEmbedding(cfg.vocab_size, H, embed_name),
         blocks=blocks,
         head=OutputHead(cfg.vocab_size, H, RMSNorm(H, cfg.rms_norm_eps, "model.norm.weight"), head_name),
+        ignored_weight_patterns=ignored,
     )
 
 

@@ -24,7 +24,12 @@ class LayerCall:
 
 
 class DecoderModel(Part):
-    def __init__(self, embedding, blocks: Sequence, head, run_order: Sequence[LayerCall] | None = None):
+    def __init__(self, embedding, blocks: Sequence, head, run_order: Sequence[LayerCall] | None = None,
+                 ignored_weight_patterns: Sequence[str] = ()):
+        """``ignored_weight_patterns``: names (shell patterns) of tensors that checkpoints of this architecture may
+        carry although no part reads them; the loader passes over them with a warning instead of refusing the
+        folder, as it does for any other tensor nobody asked for."""
+        self.ignored_weight_patterns = tuple(ignored_weight_patterns)
         self.embedding = embedding
         self.blocks = list(blocks)
         self.head = head

@@ -14,6 +14,7 @@ that a tensor marked ``keep_32bit`` stays float32 if the file stores it so; "vec
 from __future__ import annotations
 
 import fnmatch
+import warnings
 import json
 from pathlib import Path
 from typing import Iterable, Sequence
@@ -84,7 +85,12 @@ def load_weights(folder: str | Path, specs: Iterable[WeightSpec], engine_dtype: 
     where = _files_by_name(folder)
     wanted = {s.name: s for s in specs}
     missing = [n for n in wanted if n not in where]
-    unexpected = sorted(n for n in where if n not in wanted and not any(fnmatch.fnmatch(n, p) for p in ignore))
+    extra = sorted(n for n in where if n not in wanted)
+    unexpected = [n for n in extra if not any(fnmatch.fnmatch(n, p) for p in ignore)]
+    passed_over = [n for n in extra if n not in unexpected]
+    if passed_over:
+        warnings.warn(f"{folder}: {len(passed_over)} tensors that this architecture's checkpoints may carry are not "
+                      f"used: {', '.join(passed_over[:4])}{', ...' if len(passed_over) > 4 else ''}", stacklevel=2)
     wrong: list[tuple[str, tuple, tuple]] = []
     other: list[str] = []
     by_file: dict[Path, list[str]] = {}
