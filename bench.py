@@ -6,13 +6,16 @@ random weights (the metric and configuration of BASELINE.json's configs[2]).
 Prints ONE JSON line.  ``value``: decoded tokens a second at batch 8, each request holding a
 2,048-token prompt in the cache, timed on the device with CUDA events around K decode steps
 (each step: the host builds the batch, one pinned copy to the device, the model, the sampler; the
-sampled tokens stay on the device).  ``e2e``: the same through the Python entry point
+sampled tokens stay on the device); the block of K steps is repeated (at least five blocks and
+150 ms in all, ``block_ms``) and the median block is reported.  ``e2e``: the same through the Python entry point
 (``Engine.step``: scheduler, pinned host-to-device copy of the step's inputs, model, sampler,
 device-to-host read of the sampled tokens; the engine launches step t+1 before it reads step t, so
 each call reads the step before the one it launches), by the wall clock.  ``prefill``: one 2,048-token
 prompt in one step.  ``roofline``: bytes a decode step has to read (every weight it uses once, and
 the cache of the live requests) over its time, against the measured copy bandwidth.  ``points``:
-decode at batch 1 and 64.  The weights (2.5 GB) are larger than the L2 cache (126 MB), so every
+decode at batch 1, 8 and 64 over the 256 generated tokens that the metric names (with each point's
+fraction of the HBM roofline), batch 8 without CUDA graphs, and the prompt in four portions of 512.
+``breakdown``: CUDA-event time of each kind of kernel in one decode step.  The weights (2.5 GB) are larger than the L2 cache (126 MB), so every
 step reads them from HBM; nothing is flushed between steps.
 """
 
@@ -149,6 +152,61 @@ def prefill_flops(m: dict, T: int, rows: int = 1) -> float:
     return linear + attention
 
 
+TIMED_OPS = ("embed_gather", "add_rmsnorm", "rope_kv_write", "rope_kv_write_partials", "linear_decode", "linear_smallm",
+             "linear_smallm_gated", "silu_mul", "gather_rows", "attn_decode_mma", "attn_decode_rope_mma", "attn_prefill_mma",
+             "attn_prefill_tc", "sample", "gemm_tcgen05", "linear_tc_decode", "linear")
+
+
+def kernel_breakdown(ops, torch, run_step, reps: int = 5) -> dict:
+    """CUDA-event time of each kind of kernel in one eager step (microseconds, summed over the step's calls of that
+    kind, median of ``reps`` steps).  Products are told apart by their weight's shape.  The whole step is put into the
+    stream behind a kernel that keeps the GPU busy for a few milliseconds, so that no event waits for the host;
+    the events between the kernels keep a kernel from starting under the one before it, so the sum is a little above
+    a step's time as a graph replays it: read the shares."""
+    records: list[tuple[str, object, object]] = []
+    saved = {}
+
+    def wrap(name, fn):
+        def timed(*a, **k):
+            label = name
+            if name.startswith(("linear", "gemm_")) and len(a) >= 2 and hasattr(a[1], "shape"):
+                label = f"{name}[{a[1].shape[0]}x{a[1].shape[1]}]"
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            out = fn(*a, **k)
+            e1.record()
+            records.append((label, e0, e1))
+            return out
+        return timed
+
+    for name in TIMED_OPS:
+        if hasattr(ops, name):
+            saved[name] = getattr(ops, name)
+    runs = []
+    try:
+        for name, fn in saved.items():
+            # the inner calls of ops.linear_few_rows / ops.linear go through the module's globals: wrap only what
+            # the parts call, and let a wrapped function's own calls of other wrapped functions count once
+            setattr(ops, name, wrap(name, fn))
+        for _ in range(reps):
+            records.clear()
+            torch.cuda.synchronize()
+            torch.cuda._sleep(int(6e6))  # a few milliseconds of spinning: the step's launches queue up behind it
+            run_step()
+            torch.cuda.synchronize()
+            per = {}
+            for label, e0, e1 in records:
+                per[label] = per.get(label, 0.0) + e0.elapsed_time(e1) * 1e3
+            runs.append(per)
+    finally:
+        for name, fn in saved.items():
+            setattr(ops, name, fn)
+    labels = sorted({k for r in runs for k in r})
+    out = {k: round(statistics.median(r.get(k, 0.0) for r in runs), 1) for k in labels}
+    out["sum_us"] = round(sum(v for k, v in out.items()), 1)
+    return out
+
+
 def run_ours(args) -> dict:
     import numpy as np
     import torch
@@ -163,7 +221,7 @@ def run_ours(args) -> dict:
     layers = args.layers or full_layers
     cfg["num_hidden_layers"] = layers
     peaks, peak_src = load_peaks()
-    prompt_len, context_len, page_size = 2048, 4096, 16
+    prompt_len, context_len, page_size, generated = 2048, 4096, 16, 256
     max_batch = max(args.batch, 64 if not args.skip_points else args.batch)
     pool_tokens = max_batch * context_len
     eng = Engine(config_dict=cfg, random_weights=0, dtype="bfloat16", page_size=page_size,
@@ -187,22 +245,30 @@ def run_ours(args) -> dict:
         torch.cuda.synchronize()
         return a.elapsed_time(b) / reps
 
-    # ---------------------------------------------------------------- prefill: 2,048 tokens in one step
-    def prefill_once():
+    # ---------------------------------------------------------------- prefill: 2,048 tokens in one step, and in 4 of 512
+    pf_tokens = tokens(prompt_len)
+
+    def prefill_once(chunk=prompt_len):
         cache.admit("pf")
         cache.ensure_capacity("pf", prompt_len)
-        out = runner.step([StepEntry("pf", pf_tokens, 0, [prompt_len - 1])])
+        for at in range(0, prompt_len, chunk):
+            last = at + chunk >= prompt_len
+            runner.step([StepEntry("pf", pf_tokens[at:at + chunk], at, [chunk - 1] if last else [])])
         cache.free("pf")
-        return out
 
-    pf_tokens = tokens(prompt_len)
     for _ in range(max(3, args.warmup // 2)):
         prefill_once()
-    pf_reps = 5
-    pf_ms = event_ms(prefill_once, pf_reps)
+    pf_ms = statistics.median(event_ms(prefill_once, 3) for _ in range(5))
     pf_flops = prefill_flops(m, prompt_len)
     prefill = dict(value=round(prompt_len / (pf_ms / 1e3), 1), tokens=prompt_len, ms=round(pf_ms, 3),
-                   frac=round(pf_flops / (pf_ms / 1e3) / (peaks["bf16_tflops"] * 1e12), 4))
+                   frac=round(pf_flops / (pf_ms / 1e3) / (peaks["bf16_tflops"] * 1e12), 4),
+                   frac_of_sustained=round(pf_flops / (pf_ms / 1e3) / (peaks["bf16_tflops_sustained"] * 1e12), 4), of=peak_src)
+    points = {}
+    if not args.skip_points:
+        for _ in range(3):
+            prefill_once(512)
+        ch_ms = statistics.median(event_ms(lambda: prefill_once(512), 3) for _ in range(5))
+        points["prefill_chunked_4x512"] = round(prompt_len / (ch_ms / 1e3), 1)
 
     # ---------------------------------------------------------------- decode at a batch size, on the device
     def fill(batch, tag):
@@ -220,77 +286,112 @@ def run_ours(args) -> dict:
         torch.cuda.synchronize()
         return ids
 
-    def decode_run(batch, steps, warmup, tag):
-        ids = fill(batch, tag)
-        length = {rid: prompt_len for rid in ids}
-        zeros = np.zeros(batch, dtype=np.float32)
-        keys = np.zeros(batch, dtype=np.int64)
+    class Decoder:
+        """A batch of requests with their prompts in the cache; ``one`` runs one decode step (host batch building,
+        one pinned copy, model, sampler; the sampled ids stay on the device)."""
 
-        def one():
+        def __init__(self, batch, tag, graphs=True):
+            self.ids = fill(batch, tag)
+            self.length = {rid: prompt_len for rid in self.ids}
+            self.zeros = np.zeros(batch, dtype=np.float32)
+            self.keys = np.zeros(batch, dtype=np.int64)
+            self.graphs = graphs
+
+        def one(self):
             entries = []
-            for rid in ids:
-                cache.ensure_capacity(rid, length[rid] + 1)
-                entries.append(StepEntry(rid, None, length[rid], [0]))
-                length[rid] += 1
-            pos = np.asarray([length[r] for r in ids], dtype=np.int32)
-            slot = np.asarray([cache.slot(r) for r in ids], dtype=np.int32)
-            extra = dict(temperature=zeros, stream_key=keys, sample_pos=pos, row_slot=slot)
-            if eng.graphs is not None and eng.graphs.usable(entries):
+            for rid in self.ids:
+                cache.ensure_capacity(rid, self.length[rid] + 1)
+                entries.append(StepEntry(rid, None, self.length[rid], [0]))
+                self.length[rid] += 1
+            pos = np.asarray([self.length[r] for r in self.ids], dtype=np.int32)
+            slot = np.asarray([cache.slot(r) for r in self.ids], dtype=np.int32)
+            extra = dict(temperature=self.zeros, stream_key=self.keys, sample_pos=pos, row_slot=slot)
+            if self.graphs and eng.graphs is not None and eng.graphs.usable(entries):
                 eng.graphs.run(entries, extra)
                 return
             logits = runner.step(entries, extra)
             ex = runner.last_context.extra
             sampler.sample(logits, ex["temperature"], ex["stream_key"], ex["sample_pos"], ex["row_slot"], cache.last_token)
 
-        for _ in range(warmup):
-            one()
-        ops.LAUNCHES = 0
-        ms = event_ms(one, steps)
-        launches = ops.LAUNCHES
-        mean_ctx = prompt_len + warmup + steps / 2
-        runner.check_status()
-        for rid in ids:
-            cache.free(rid)
-        return ms, launches, mean_ctx
+        def context(self):
+            return next(iter(self.length.values()))
 
+        def close(self):
+            runner.check_status()
+            for rid in self.ids:
+                cache.free(rid)
+
+    def decode_point(batch, steps, warmup, tag, graphs=True):
+        d = Decoder(batch, tag, graphs)
+        for _ in range(warmup):
+            d.one()
+        ms = event_ms(d.one, steps)
+        d.close()
+        return ms
+
+    # the headline: blocks of --steps steps, the median block; at least five blocks and 150 ms in all
+    d = Decoder(args.batch, "d")
+    for _ in range(args.warmup):
+        d.one()
     clocks = ClockSampler()
     clocks.start()
-    ms, launches, mean_ctx = decode_run(args.batch, args.steps, args.warmup, "d")
+    ops.LAUNCHES = 0
+    first_ctx = d.context()
+    blocks = [event_ms(d.one, args.steps)]
+    launches = ops.LAUNCHES
+    room = context_len - d.context() - args.steps - 8
+    while (len(blocks) < 5 or sum(blocks) * args.steps < 150.0) and room >= args.steps and len(blocks) < 40:
+        blocks.append(event_ms(d.one, args.steps))
+        room -= args.steps
     clock_info = clocks.stop()
+    mean_ctx = (first_ctx + d.context()) / 2
+    ms = statistics.median(blocks)
+    # where the step's time goes: each kind of kernel, timed with events in an eager step of the same requests
+    breakdown = None if args.skip_points else kernel_breakdown(ops, torch, lambda: (setattr(d, "graphs", False), d.one(),
+                                                                                      setattr(d, "graphs", True)))
+    d.close()
     value = args.batch * 1e3 / ms
     nbytes = decode_bytes(m, args.batch, mean_ctx)
     achieved = nbytes / (ms / 1e3) / 1e9
     roofline = dict(bound="hbm", achieved=round(achieved, 1), peak=peaks["hbm_gbs"], unit="GB/s",
                     frac=round(achieved / peaks["hbm_gbs"], 4), of=peak_src)
 
-    points = {}
     if not args.skip_points:
-        for b in (1, 64):
-            pms, _, _ = decode_run(b, max(10, args.steps // 2), max(3, args.warmup // 2), f"p{b}_")
-            points[f"decode_b{b}"] = round(b * 1e3 / pms, 1)
+        # the metric's own shape: 2,048 prompt tokens, then 256 generated tokens, at batch 1, 8 and 64
+        for b in (1, args.batch, 64):
+            pms = decode_point(b, generated, max(3, args.warmup // 2), f"p{b}_")
+            points[f"decode_b{b}" if b != args.batch else f"decode_b{b}_256"] = round(b * 1e3 / pms, 1)
+            bytes_b = decode_bytes(m, b, prompt_len + generated / 2)
+            points[f"hbm_frac_b{b}"] = round(bytes_b / (pms / 1e3) / 1e9 / peaks["hbm_gbs"], 4)
+        pms = decode_point(args.batch, 32, 3, "ng", graphs=False)
+        points[f"decode_b{args.batch}_no_graphs"] = round(args.batch * 1e3 / pms, 1)
 
     # ---------------------------------------------------------------- end to end through the entry point
+    e2e_steps = args.steps * len(blocks)
     prompts = [tokens(prompt_len) for _ in range(args.batch)]
     for p in prompts:
-        eng.add_request(p, SamplingParams(temperature=0.0), max_num_tokens=args.warmup + args.steps + 8, ignore_eos=True)
+        eng.add_request(p, SamplingParams(temperature=0.0), max_num_tokens=args.warmup + e2e_steps + 8, ignore_eos=True)
     while eng.scheduler.prefilling or eng.scheduler.queued:
         eng.step()
     for _ in range(args.warmup):
         eng.step()
     torch.cuda.synchronize()
     h2d = d2h = 0
-    t0 = time.perf_counter()
-    for _ in range(args.steps):
-        eng.step()
-        h2d += eng.last_step_bytes["h2d"]
-        d2h += eng.last_step_bytes["d2h"]
-    torch.cuda.synchronize()
-    e2e_s = time.perf_counter() - t0
-    e2e = dict(value=round(args.batch * args.steps / e2e_s, 1), unit="tokens/s",
-               h2d_bytes_per_step=h2d // args.steps, d2h_bytes_per_step=d2h // args.steps,
-               ms_per_step=round(e2e_s * 1e3 / args.steps, 4))
+    e2e_blocks = []
+    for _ in range(len(blocks)):
+        t0 = time.perf_counter()
+        for _ in range(args.steps):
+            eng.step()
+            h2d += eng.last_step_bytes["h2d"]
+            d2h += eng.last_step_bytes["d2h"]
+        torch.cuda.synchronize()
+        e2e_blocks.append((time.perf_counter() - t0) * 1e3 / args.steps)
+    e2e_ms = statistics.median(e2e_blocks)
+    e2e = dict(value=round(args.batch * 1e3 / e2e_ms, 1), unit="tokens/s",
+               h2d_bytes_per_step=h2d // e2e_steps, d2h_bytes_per_step=d2h // e2e_steps,
+               ms_per_step=round(e2e_ms, 4))
 
-    return {
+    out = {
         "metric": "decode tokens/s (Llama-3.2-1B sizes, batch 8, 2,048-token prompts)",
         "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
@@ -301,19 +402,22 @@ def run_ours(args) -> dict:
             "parallelism": "1 GPU", "layers": layers, "layers_full": full_layers, "hidden": m["H"], "heads": m["nh"],
             "kv_heads": m["nkv"], "head_dim": m["hd"], "intermediate": m["I"], "vocab": m["V"], "page_size": page_size,
             "tied_embeddings": True, "rope": "llama3 factor 32", "l2": "inputs (2.5 GB of weights) larger than L2; no flush",
-            "cuda_graphs": eng.graphs is not None,
+            "cuda_graphs": eng.graphs is not None, "timed_blocks": len(blocks),
         },
         "e2e": e2e, "gpu_launches": launches, "clocks": clock_info, "prefill": prefill, "roofline": roofline,
-        "points": points,
+        "points": points, "block_ms": [round(b, 4) for b in blocks],
     }
+    if breakdown is not None:
+        out["breakdown"] = breakdown
+    return out
 
 
 def run_further(args) -> dict:
     """The further workloads BASELINE.json names, with the same kind of line: configs[3], one mixed step at
     Llama-3.2-3B sizes (32 requests that decode at contexts of 1,024 to 4,096 beside the second 2,048-token
     portion of a 4,096-token prompt), and configs[4], decode at batch 64 with every request at context 8,192 at
-    Llama-3.1-8B sizes.  Fewer layers than the models have by default (the random weights are drawn on the host);
-    ``config`` names both numbers."""
+    Llama-3.1-8B sizes (64 x 8,192 tokens of keys and values: 68.7 GB beside 16 GB of weights).  All layers by
+    default (the random weights are drawn on the device); ``--layers`` runs fewer, and ``config`` names both numbers."""
     import numpy as np
     import torch
 
@@ -323,7 +427,7 @@ def run_further(args) -> dict:
 
     cfg = load_other_config(args.config)
     full_layers = cfg["num_hidden_layers"]
-    layers = args.layers or (14 if args.config == 3 else 8)
+    layers = args.layers or full_layers
     cfg["num_hidden_layers"] = layers
     peaks, peak_src = load_peaks()
     page_size = 16

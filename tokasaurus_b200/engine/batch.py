@@ -76,21 +76,29 @@ class StepContext:
         )
         arrays = [host.token_ids, host.positions, host.token_seq, host.seq_slot, host.seq_q_start, host.seq_q_len,
                   host.seq_kv_len, host.logit_rows]
-        for ip, pg in zip(host.table_indptr, host.table_pages):
-            arrays += [ip, pg]
+        n_groups = len(host.table_indptr)
         extra = extra or {}
         plans = plans or {}
         flat = [(key, name, arr) for key, d in plans.items() for name, arr in d.items()]
-        views = stager.upload(arrays + list(extra.values()) + [a for _, _, a in flat])
-        self.extra = dict(zip(extra.keys(), views[len(arrays):]))
+        # The page ids go last: a step graph stages them at the capacity of the page pool, and only the part in
+        # use (the last entry of the row pointers) is copied.
+        everything = arrays + list(host.table_indptr) + list(extra.values()) + [a for _, _, a in flat] + list(host.table_pages)
+        used_of_last = int(host.table_indptr[-1][-1]) if n_groups else None
+        views = stager.upload(everything, used_of_last)
+        at = len(arrays)
+        indptrs = views[at:at + n_groups]
+        at += n_groups
+        self.extra = dict(zip(extra.keys(), views[at:at + len(extra)]))
+        at += len(extra)
         self.plans: dict = {}
         self.plan_caps: dict | None = None
         self.host_plans = plans
-        for (key, name, _), v in zip(flat, views[len(arrays) + len(extra):]):
+        for (key, name, _), v in zip(flat, views[at:at + len(flat)]):
             self.plans.setdefault(key, {})[name] = v
+        at += len(flat)
         (self.token_ids, self.positions, self.token_seq, self.seq_slot, self.seq_q_start, self.seq_q_len,
          self.seq_kv_len, self.logit_rows) = views[:8]
-        self.tables = [GroupTables(views[8 + 2 * g], views[9 + 2 * g]) for g in range(len(host.table_indptr))]
+        self.tables = [GroupTables(indptrs[g], views[at + g]) for g in range(n_groups)]
         self.last_token = cache_manager.last_token
         self.status = stager.status
 
@@ -117,7 +125,10 @@ class Stager:
         self._copied = torch.cuda.Event() if pin else None
         self._pending = False
 
-    def upload(self, arrays: Sequence[np.ndarray]) -> list[torch.Tensor]:
+    def upload(self, arrays: Sequence[np.ndarray], used_of_last: int | None = None) -> list[torch.Tensor]:
+        """Pack the arrays and copy them to the device in one copy; returns their device views.  ``used_of_last``:
+        only this many leading elements of the LAST array hold anything (the rest is padding that nothing reads),
+        so the copy ends there."""
         offs = []
         total = 0
         kinds = [a.dtype for a in arrays]
@@ -136,13 +147,19 @@ class Stager:
         if self._pending:
             self._copied.synchronize()  # the last copy out of the pinned buffer must be over before it is rewritten
             self._pending = False
+        n_copy = total
+        if used_of_last is not None and arrays:
+            n_copy = max(4, offs[-1] + min(int(used_of_last), arrays[-1].shape[0]))
         for a, o in zip(arrays, offs):
-            self.host_np[o:o + a.shape[0]] = a
-        self.dev[:total].copy_(self.host[:total], non_blocking=True)
+            n = min(a.shape[0], n_copy - o)
+            if n > 0:
+                self.host_np[o:o + n] = a[:n]
+        total_bytes = n_copy
+        self.dev[:n_copy].copy_(self.host[:n_copy], non_blocking=True)
         if self._copied is not None:
             self._copied.record()
             self._pending = True
-        self.bytes_last_upload = total * 4
+        self.bytes_last_upload = total_bytes * 4
         out = []
         for a, o, k in zip(arrays, offs, kinds):
             v = self.dev[o:o + a.shape[0]]

@@ -71,7 +71,7 @@ class ModelRunner:
 
         specs = self.model.weight_specs()
         if config.random_weights is not None:
-            host = random_tensors(specs, config.random_weights)
+            host = random_tensors(specs, config.random_weights, device=self.rt.device)
             by_name = {s.name: s for s in specs}
             weights = {
                 n: t.to(device=self.rt.device, dtype=target_dtype(by_name[n], t.dtype, self.rt.dtype)).contiguous()

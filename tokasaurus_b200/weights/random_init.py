@@ -22,24 +22,29 @@ _STORE = {"bfloat16": torch.bfloat16, "float32": torch.float32}
 
 
 def random_tensors(specs: Iterable[WeightSpec], seed: int, std: float = 0.02, norm_init: str = "ones",
-                   store_dtype: str = "bfloat16") -> dict[str, torch.Tensor]:
+                   store_dtype: str = "bfloat16", device: torch.device | str = "cpu") -> dict[str, torch.Tensor]:
+    """``device``: where the values are drawn and left.  The CPU's generator and a GPU's give different numbers for
+    the same seed: a model folder is always written from the CPU's (what reads the folder sees the same numbers on
+    any machine), while an engine that only needs some model of the given sizes (the benchmark's billions of
+    values) draws them where it will use them."""
     if norm_init not in ("ones", "uniform"):
         raise ValueError("norm_init is 'ones' or 'uniform'")
     dt = _STORE[store_dtype]
-    g = torch.Generator(device="cpu")
+    device = torch.device(device)
+    g = torch.Generator(device=device)
     g.manual_seed(int(seed))
     out: dict[str, torch.Tensor] = {}
     for s in specs:
         if s.role == "table":
-            out[s.name] = torch.randint(0, 2**15, s.shape, generator=g, dtype=torch.int32)
+            out[s.name] = torch.randint(0, 2**15, s.shape, generator=g, dtype=torch.int32, device=device)
         elif s.role == "vector":
             if norm_init == "ones":
-                t = torch.ones(s.shape, dtype=torch.float32)
+                t = torch.ones(s.shape, dtype=torch.float32, device=device)
             else:
-                t = torch.rand(s.shape, generator=g, dtype=torch.float32) + 0.5
+                t = torch.rand(s.shape, generator=g, dtype=torch.float32, device=device) + 0.5
             out[s.name] = t.to(dt)
         else:
-            out[s.name] = (torch.randn(s.shape, generator=g, dtype=torch.float32) * std).to(dt)
+            out[s.name] = torch.randn(s.shape, generator=g, dtype=torch.float32, device=device).mul_(std).to(dt)
     return out
 
 
