@@ -53,7 +53,12 @@ constexpr int SMEM_B = 2 * STAGE_B + SMEM_ALIGN;  // two stages (tiled kernel fo
 // to 80, two to 128), else two.  Four stages at head size 64 were measured slower, with padded rows (the
 // blocks of a step then no longer fit the SMs all at once) and again with the swizzled layout, where three
 // blocks of 65 KiB should fit an SM (batch 64: 38 k -> 30 k tok/s; batch 8 unchanged).
+#ifdef TKB_DSTAGES
+constexpr int DSTAGES = TKB_DSTAGES;  // a deeper ring for one block an SM (see the planner's "deep" steps)
+#else
 constexpr int DSTAGES = 3 * STAGE_B <= 110 * 1024 ? 3 : 2;
+#endif
+static_assert(DSTAGES >= 2 && DSTAGES * STAGE_B <= 200 * 1024, "the ring must fit an SM's shared memory");
 constexpr int DEC_SMEM_B = DSTAGES * STAGE_B + SMEM_ALIGN;
 // byte offset of 16-byte chunk `chunk` of row `row` within a tile
 __device__ __forceinline__ int tile_off(int row, int chunk) {
@@ -379,6 +384,8 @@ attn_decode_mma_kernel(const __grid_constant__ KvMapsParam<TMA> maps, int tma_ro
   // this split holds position p, and this layer call keeps its own keys (a call that reads another call's cache
   // finds the key at p already there)
   const bool owns_new = FUSED && write_cache && k_end == kv_len;
+  // the page of the token's own position: looked up here, before the wait, so that the write below waits for nothing
+  const int own_page = owns_new ? table[p / ps] : 0;
   __shared__ __align__(16) float srow[FUSED ? 18 * HD : 4];  // the token's q rows of this head tile, then its k and v row
   if (FUSED) {
     const int half = rot >> 1;
@@ -440,7 +447,7 @@ attn_decode_mma_kernel(const __grid_constant__ KvMapsParam<TMA> maps, int tma_ro
       // same kv head store the same bytes)
       const float* krow = srow + 16 * HD;
       const float* vrow = srow + 17 * HD;
-      const int page = table[p / ps];
+      const int page = own_page;
       const bool page_ok = page >= 0 && page < num_pages;
       if (!page_ok && tid == 0) atomicOr(status, TKB_STATUS_BAD_PAGE);
       const size_t dst = (((size_t)(page_ok ? page : 0) * nkv + kvh) * ps + (p % ps)) * HD;

@@ -33,6 +33,9 @@ __device__ __forceinline__ void ldmatrix_x4(uint32_t& r0, uint32_t& r1, uint32_t
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
                : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
 }
+__device__ __forceinline__ void ldmatrix_x2(uint32_t& r0, uint32_t& r1, uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];\n" : "=r"(r0), "=r"(r1) : "r"(addr));
+}
 __device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
   asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
                : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
@@ -44,11 +47,17 @@ __device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], 
 // on 148 SMs, so most SMs stream twice what the others do, and an SM streams at a fixed rate) runs as one
 // block of up to eight warps an SM instead.
 template <int NT, int WARPS = 4> struct Tile {
-  static constexpr int A_ROWS = NT * 8 < 16 ? 16 : NT * 8;  // token rows kept in shared memory (>= 16 for ldmatrix.x4)
+  static constexpr int A_ROWS = NT * 8;                      // token rows kept in shared memory (8 rows: ldmatrix.x2)
   static constexpr int ROWS = WARPS * 16;                    // weight rows (output features) per block
   static constexpr int STAGE_B = (ROWS + A_ROWS) * ROWB;
   // deep for few tokens: the weight tiles in flight are what is prefetched; one block an SM takes what fits
-  static constexpr int STAGES = WARPS > 4 ? (200 * 1024) / STAGE_B : (NT <= 2 ? 5 : 4);
+#ifndef TKB_WIDE_STAGES_KIB
+#define TKB_WIDE_STAGES_KIB 200
+#endif
+#ifndef TKB_FEW_ROWS_STAGES
+#define TKB_FEW_ROWS_STAGES 5
+#endif
+  static constexpr int STAGES = WARPS > 4 ? (TKB_WIDE_STAGES_KIB * 1024) / STAGE_B : (NT <= 2 ? TKB_FEW_ROWS_STAGES : 4);
   static constexpr int SMEM_B = STAGES * STAGE_B;
 };
 
@@ -120,7 +129,9 @@ linear_smallm_kernel(const bf16* __restrict__ A, int lda, const bf16* __restrict
   }
   const int w_row = warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
   const int w_chunk = lane >> 4;
-  const int a_row = (lane & 7) + (lane >> 4) * 8;
+  // eight token rows (NT == 1) are read with ldmatrix.x2, whose addresses come from lanes 0..15; the other lanes
+  // repeat them, so that every address stays inside the eight rows
+  const int a_row = (lane & 7) + (NT > 1 ? (lane >> 4) * 8 : 0);
   const int a_chunk = (lane >> 3) & 1;
   for (int kb = 0; kb < nkb; kb++) {
     cp_async_wait<STAGES - 2>();
@@ -140,12 +151,18 @@ linear_smallm_kernel(const bf16* __restrict__ A, int lda, const bf16* __restrict
     for (int ks = 0; ks < BK / 16; ks++) {
       uint32_t wf[4];
       ldmatrix_x4(wf[0], wf[1], wf[2], wf[3], sw + w_row * ROWB + (ks * 2 + w_chunk) * 16);
+      if constexpr (NT == 1) {
+        uint32_t b0, b1;
+        ldmatrix_x2(b0, b1, sa + a_row * ROWB + (ks * 2 + a_chunk) * 16);
+        mma_bf16(acc[0], wf, b0, b1);
+      } else {
 #pragma unroll
-      for (int j = 0; j < NT; j += 2) {
-        uint32_t b0, b1, b2, b3;
-        ldmatrix_x4(b0, b1, b2, b3, sa + (j * 8 + a_row) * ROWB + (ks * 2 + a_chunk) * 16);
-        mma_bf16(acc[j], wf, b0, b1);
-        if (j + 1 < NT) mma_bf16(acc[j + 1], wf, b2, b3);
+        for (int j = 0; j < NT; j += 2) {
+          uint32_t b0, b1, b2, b3;
+          ldmatrix_x4(b0, b1, b2, b3, sa + (j * 8 + a_row) * ROWB + (ks * 2 + a_chunk) * 16);
+          mma_bf16(acc[j], wf, b0, b1);
+          if (j + 1 < NT) mma_bf16(acc[j + 1], wf, b2, b3);
+        }
       }
     }
   }
@@ -196,8 +213,12 @@ int launch(const void* A, int lda, const void* W, int ldw, void* out, int M, int
     attr_done = true;
   }
   dim3 grid((N + T::ROWS - 1) / T::ROWS, slices);
-  return launch_pdl(linear_smallm_kernel<NT, GATED, WARPS>, grid, dim3(WARPS * 32), (size_t)T::SMEM_B, st, (const bf16*)A,
-                    lda, (const bf16*)W, ldw, out, M, N, K, kblocks_per_slice);
+  // A slice of fewer k-blocks than the ring has stages never touches the stages beyond them: ask only for the
+  // shared memory that is used, so that blocks of the kernels before and after this one fit on the SM beside
+  // these (they fetch their weights or keys while this kernel runs).
+  const int stages_used = kblocks_per_slice < T::STAGES ? (kblocks_per_slice < 1 ? 1 : kblocks_per_slice) : T::STAGES;
+  return launch_pdl(linear_smallm_kernel<NT, GATED, WARPS>, grid, dim3(WARPS * 32), (size_t)stages_used * T::STAGE_B, st,
+                    (const bf16*)A, lda, (const bf16*)W, ldw, out, M, N, K, kblocks_per_slice);
 }
 
 template <bool GATED>
