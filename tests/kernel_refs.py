@@ -40,7 +40,9 @@ def add_rmsnorm(x, delta, weight, eps, out):
 
 
 def rope_kv_write(qkv, positions, token_seq, page_indptr, page_ids, inv_freq, kcache, vcache, n_heads, n_kv_heads,
-                  head_dim, rotary_dim, page_size, write_cache, status):
+                  head_dim, rotary_dim, page_size, write_cache, status, bias=None, qk_norm=None, norm_eps=0.0):
+    """The element-wise stage before the rotation: ``bias`` [C] is added to the row and the sum rounded to the
+    row's type; ``qk_norm`` [2, head_dim] RMS-normalises every q head and every k head (rounded to the row's type)."""
     T = qkv.shape[0]
     nh, nkv, hd = n_heads, n_kv_heads, head_dim
     half = rotary_dim // 2
@@ -50,9 +52,15 @@ def rope_kv_write(qkv, positions, token_seq, page_indptr, page_ids, inv_freq, kc
             continue
         p = int(positions[t])
         row = qkv[t].float()
+        if bias is not None:
+            row = (row + bias.float().to(row.device)).to(qkv.dtype).float()
         q = row[: nh * hd].view(nh, hd).clone()
         k = row[nh * hd:(nh + nkv) * hd].view(nkv, hd).clone()
-        v = qkv[t, (nh + nkv) * hd:].view(nkv, hd)
+        v = row[(nh + nkv) * hd:].view(nkv, hd).to(qkv.dtype)
+        if qk_norm is not None:
+            w = qk_norm.float().to(row.device)
+            q = (q * torch.rsqrt(q.pow(2).mean(-1, keepdim=True) + norm_eps) * w[0]).to(qkv.dtype).float()
+            k = (k * torch.rsqrt(k.pow(2).mean(-1, keepdim=True) + norm_eps) * w[1]).to(qkv.dtype).float()
         if rotary_dim:
             ang = torch.tensor(float(p), dtype=torch.float32) * inv_freq.float().cpu()
             c, sn = ang.cos().to(row.device), ang.sin().to(row.device)
@@ -93,7 +101,7 @@ def sgemm_tn(a, w, out):
 
 
 def attn_paged(q, q_stride, out, kcache, vcache, token_seq, positions, page_indptr, page_ids, rows, n_rows, n_heads,
-               n_kv_heads, head_dim, page_size, scale, window):
+               n_kv_heads, head_dim, page_size, scale, window, status=None):
     group = n_heads // n_kv_heads
     for r in range(n_rows):
         t = int(rows[r]) if rows is not None else r

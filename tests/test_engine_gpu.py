@@ -416,3 +416,26 @@ def test_llama_layer_sizes_bfloat16_against_float32(sizes):
         err = (g - w).abs().max(dim=1).values
         print(f"step {t}: largest error {err.max().item():.3g} of max |logit| {w.abs().max().item():.3g} (tolerance {tol:.3g})")
         assert (err <= tol).all(), f"step {t}: largest error {err.max().item():.3g}, tolerance {tol:.3g}, rows {err.tolist()}"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_page_id_beyond_the_pool_is_refused_not_read(tiny_model_dirs, dtype):
+    """A block table that names a page beyond the pool (a fault of the host's books): the kernels that read keys
+    through it, not only those that write, skip the access, zeros stand in, and the step's status check raises."""
+    from tokasaurus_b200.engine.runner import DeviceStatusError
+    from tokasaurus_b200.engine.trace import TraceReplayer
+
+    toks = cuttings.random_tokens(40, 256, 5)
+    rp = TraceReplayer(str(tiny_model_dirs[0]), dtype, 256, page_size=16)
+    rp.run_step(dict(step=0, entries=[dict(id="a", tokens=toks[:20], want=[19])], end=[]))
+    rc = rp.runner.cache.requests["a"]
+    good = rc.tables[0][0]
+    rc.tables[0][0] = rp.runner.cache.num_pages + 5  # the page that holds keys 0..15, which every later query reads
+    rc.arrays.clear()
+    for step, chunk in ((1, toks[20:33]), (2, toks[33:34])):  # a portion, then a single token
+        with pytest.raises(DeviceStatusError, match="page id outside the pool"):
+            rp.run_step(dict(step=step, entries=[dict(id="a", tokens=chunk, want=[len(chunk) - 1])], end=[]))
+    rc.tables[0][0] = good
+    rc.arrays.clear()
+    out = rp.run_step(dict(step=3, entries=[dict(id="a", tokens=toks[34:36], want=[1])], end=["a"]))
+    assert np.isfinite(out).all()

@@ -262,6 +262,41 @@ def test_rope_kv_write(ops, dtype, hd, rot, nh, nkv, ps):
     assert int(status) & 2 and not kc3.any()
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("hd,rot,nh,nkv,ps", [(16, 16, 4, 2, 16), (64, 64, 6, 2, 16), (128, 64, 2, 1, 8), (48, 32, 3, 3, 4)])
+def test_rope_kv_write_with_the_elementwise_stage(ops, dtype, hd, rot, nh, nkv, ps):
+    """Biases on q|k|v and an RMS norm of every q and k head before the rotation, alone and together, many tokens a
+    block (more tokens than blocks the GPU holds would take too long here: the walk over tokens is the same)."""
+    from tokasaurus_b200.parts.rope import RotaryEncoding
+
+    T, n_pages = 300, 64
+    g = torch.Generator().manual_seed(hd + nh)
+    C = (nh + 2 * nkv) * hd
+    qkv = torch.randn(T, C, generator=g).to(dtype).to(DEV)
+    bias = (torch.randn(C, generator=g) * 0.5).to(DEV)
+    qk_norm = (torch.rand(2, hd, generator=g) + 0.5).to(DEV)
+    positions = i32(list(range(T)))
+    token_seq = i32([0 if t % 7 else -1 for t in range(T)])  # every seventh row is padding
+    pages = torch.randperm(n_pages, generator=g).tolist()[: -(-T // ps)]
+    inv = RotaryEncoding(rot, 10000.0).inv_freq().to(DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    for b, n in ((bias, None), (None, qk_norm), (bias, qk_norm)):
+        kc = torch.zeros(n_pages, nkv, ps, hd, dtype=dtype, device=DEV)
+        vc, kc2 = torch.zeros_like(kc), torch.zeros_like(kc)
+        vc2 = torch.zeros_like(kc)
+        a, want = qkv.clone(), qkv.clone()
+        ops.rope_kv_write(a, positions, token_seq, i32([0, len(pages)]), i32(pages), inv, kc, vc, nh, nkv, hd, rot, ps, True,
+                          status, bias=b, qk_norm=n, norm_eps=1e-6)
+        ref.rope_kv_write(want, positions, token_seq, i32([0, len(pages)]), i32(pages), inv, kc2, vc2, nh, nkv, hd, rot, ps,
+                          True, torch.zeros(1, dtype=torch.int32), bias=b, qk_norm=n, norm_eps=1e-6)
+        assert int(status) == 0
+        t = dict(rtol=1e-5, atol=2e-5) if dtype == torch.float32 else dict(rtol=1.6e-2, atol=1.6e-2)
+        torch.testing.assert_close(a[:, : nh * hd].float(), want[:, : nh * hd].float(), **t)
+        torch.testing.assert_close(kc.float(), kc2.float(), **t)
+        torch.testing.assert_close(vc.float(), vc2.float(), **t)
+        assert torch.equal(a[0], qkv[0])  # a padding row is untouched
+
+
 def test_sampling_greedy_and_logprob(ops):
     for V in (509, 128256, 3):
         g = torch.Generator().manual_seed(V)
@@ -722,6 +757,26 @@ def test_fused_rope_decode_attention_equals_the_separate_kernels(ops, hd, nh, nk
                              window, inv, rot, False, status)
     assert torch.equal(kc4.nan_to_num(7.0), kc1.nan_to_num(7.0)) and torch.equal(vc4, vc1)
     torch.testing.assert_close(got4.float(), want.float(), rtol=1.6e-2, atol=1e-2)
+    # the element-wise stage before the rotation (biases, RMS norm of the q and k heads): the fused kernel against the
+    # separate kernels given the same stage, from rows and from slices
+    bias = (torch.randn(qkv.shape[1], generator=g) * 0.5).to(DEV)
+    qk_norm = (torch.rand(2, hd, generator=g) + 0.5).to(DEV)
+    stage = dict(bias=bias, qk_norm=qk_norm, norm_eps=1e-6)
+    kc5, vc5, q5 = kc.clone(), vc.clone(), qkv.clone()
+    ops.rope_kv_write(q5, positions, token_seq, indptr, pages, inv, kc5, vc5, nh, nkv, hd, rot, ps, True, status, **stage)
+    want5 = torch.zeros_like(want)
+    ops.attn_decode_mma(q5, kc5, vc5, q_start, kv_len, indptr, pages, i32(plan["items"]), c[0:1], n_items, i32(plan["dec_seqs"]),
+                        i32(plan["dec_item_start"]), c[1:2], n_dec, want5, nh, nkv, hd, ps, scale, window)
+    assert (want5.float() - want.float()).abs().max() > 0.05  # the stage changes the result
+    for rows in (qkv, parts):
+        kc6, vc6 = kc.clone(), vc.clone()
+        got6 = torch.zeros_like(want)
+        ops.attn_decode_rope_mma(rows, kc6, vc6, q_start, kv_len, indptr, pages, i32(plan["items"]), c[0:1], n_items,
+                                 i32(plan["dec_seqs"]), i32(plan["dec_item_start"]), c[1:2], n_dec, got6, nh, nkv, hd, ps,
+                                 scale, window, inv, rot, True, status, item_entry=i32(plan["item_entry"]), **stage)
+        assert int(status) == 0
+        torch.testing.assert_close(kc6.float().nan_to_num(7.0), kc5.float().nan_to_num(7.0), rtol=2e-2, atol=2e-2)
+        torch.testing.assert_close(got6.float(), want5.float(), rtol=3e-2, atol=3e-2)
 
 
 # ------------------------------------------------------------------------------------------------

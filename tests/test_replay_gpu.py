@@ -219,7 +219,7 @@ def test_wide_heads_and_long_requests_match_plain(tmp_path, monkeypatch, hd):
     import tokasaurus_b200.parts.attention as attention
     from tokasaurus_b200.weights import write_model_folder
 
-    monkeypatch.setattr(attention, "decode_block_slots", lambda head_dim: 1)
+    monkeypatch.setattr(attention, "decode_block_slots", lambda head_dim, limits=None: 1)
     cfg = dict(architectures=["LlamaForCausalLM"], model_type="llama", num_hidden_layers=2, hidden_size=2 * hd,
                num_attention_heads=2, num_key_value_heads=1, intermediate_size=96, vocab_size=300, rope_theta=10000.0,
                rope_scaling=None, rms_norm_eps=1e-5, tie_word_embeddings=True, max_position_embeddings=1024)

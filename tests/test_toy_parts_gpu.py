@@ -161,3 +161,103 @@ def test_routed_feed_forward_and_learned_positions(tmp_path, dtype):
         assert compared > 0.85 * total
     finally:
         unregister_architecture("ToyRoutedLM")
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+# An attention whose projections carry biases and whose q and k heads are RMS-normalised before the rotation: the
+# element-wise stage the framework's attention offers (``QkvStage``).  Such a mixer is "new parts and a registry
+# entry", and it keeps every fast path: the decode steps below still run the fused rotary + cache write +
+# split-key attention kernel, and the portions the tcgen05 kernel (heads of 64).
+
+QKN = dict(architectures=["ToyQkNormLM"], width=128, vocab_size=113, inner=96, heads=4, kv_heads=2, layers=2, eps=1e-5,
+           qk_eps=1e-6, theta=10000.0)
+
+
+def define_qk_norm_toy():
+    from tokasaurus_b200.config import register_architecture
+    from tokasaurus_b200.parts import (DecoderModel, GatedMLP, OutputHead, PagedAttention, PreNormBlock, QkvStage, RMSNorm,
+                                       RotaryEncoding, TokenEmbedding)
+
+    def build(c):
+        W, V, hd = c["width"], c["vocab_size"], c["width"] // c["heads"]
+        blocks = []
+        for i in range(c["layers"]):
+            stage = QkvStage(bias_names=(f"b{i}.qb", f"b{i}.kb", f"b{i}.vb"), qk_norm_names=(f"b{i}.qn", f"b{i}.kn"),
+                             norm_eps=c["qk_eps"])
+            blocks.append(PreNormBlock(
+                RMSNorm(W, c["eps"], f"b{i}.n1"),
+                PagedAttention(W, c["heads"], c["kv_heads"], hd, RotaryEncoding(hd, c["theta"]), f"b{i}.q", f"b{i}.k",
+                               f"b{i}.v", f"b{i}.o", qkv_stage=stage),
+                RMSNorm(W, c["eps"], f"b{i}.n2"), GatedMLP(W, c["inner"], f"b{i}.g", f"b{i}.u", f"b{i}.d")))
+        return DecoderModel(TokenEmbedding(V, W, "emb"), blocks, OutputHead(V, W, RMSNorm(W, c["eps"], "nf"), "head"))
+
+    register_architecture("ToyQkNormLM", dict, build, replace=True)
+
+
+def plain_qk_norm_toy(folder, ids, dtype=torch.float64):
+    from safetensors import safe_open
+    c, w = QKN, {}
+    with safe_open(str(folder / "model.safetensors"), framework="pt") as f:
+        for k in f.keys():
+            w[k] = f.get_tensor(k).to(dtype)
+    T, nh, nkv, hd = len(ids), c["heads"], c["kv_heads"], c["width"] // c["heads"]
+    x = w["emb"][torch.tensor(ids)]
+    cos, sin = plain.rope_tables(torch.arange(T), plain.rope_inv_freq(hd, c["theta"], None))
+    for i in range(c["layers"]):
+        h = plain.rms_norm(x, w[f"b{i}.n1"], c["eps"])
+        q = (h @ w[f"b{i}.q"].T + w[f"b{i}.qb"]).view(T, nh, hd)
+        k = (h @ w[f"b{i}.k"].T + w[f"b{i}.kb"]).view(T, nkv, hd)
+        v = (h @ w[f"b{i}.v"].T + w[f"b{i}.vb"]).view(T, nkv, hd)
+        q = plain.rms_norm(q, w[f"b{i}.qn"], c["qk_eps"])  # over the head size
+        k = plain.rms_norm(k, w[f"b{i}.kn"], c["qk_eps"])
+        a = plain.causal_gqa_attention(plain.apply_rope(q, cos, sin), plain.apply_rope(k, cos, sin), v).reshape(T, -1)
+        x = x + a @ w[f"b{i}.o"].T
+        h = plain.rms_norm(x, w[f"b{i}.n2"], c["eps"])
+        x = x + (torch.nn.functional.silu(h @ w[f"b{i}.g"].T) * (h @ w[f"b{i}.u"].T)) @ w[f"b{i}.d"].T
+    return (plain.rms_norm(x, w["nf"], c["eps"]) @ w["head"].T).double().numpy()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_attention_with_biases_and_head_norms_keeps_the_fused_paths(tmp_path, monkeypatch, dtype):
+    import test_replay_gpu as rp
+    from tokasaurus_b200.config import unregister_architecture
+    from tokasaurus_b200.kernels import ops
+    from tokasaurus_b200.weights import write_model_folder
+
+    define_qk_norm_toy()
+    calls = dict(fused=0, tc=0)
+    fused, tc = ops.attn_decode_rope_mma, ops.attn_prefill_tc
+
+    def count_fused(*a, **k):
+        calls["fused"] += 1
+        assert k.get("bias") is not None and k.get("qk_norm") is not None
+        return fused(*a, **k)
+
+    def count_tc(*a, **k):
+        calls["tc"] += 1
+        return tc(*a, **k)
+
+    monkeypatch.setattr(ops, "attn_decode_rope_mma", count_fused)
+    monkeypatch.setattr(ops, "attn_prefill_tc", count_tc)
+    try:
+        folder = write_model_folder(tmp_path / "toy", QKN, seed=21, std=0.08, norm_init="uniform")
+        reqs = {f"q{i}": cuttings.random_tokens(n, QKN["vocab_size"], 50 + i) for i, n in enumerate([150, 37, 64, 9, 201])}
+        want = {rid: plain_qk_norm_toy(folder, toks) for rid, toks in reqs.items()}
+        want32 = {rid: plain_qk_norm_toy(folder, toks, torch.float32) for rid, toks in reqs.items()} if dtype == "float32" else None
+        # the stage is not a no-op for these weights: without the head norm the logits are far away
+        for cut in ("whole", "prefix_then_single", "changing_portions", "mixed"):
+            steps = rp.CUTS[cut](reqs)
+            rp.compare(rp.replay(folder, dtype, steps, 16), want, want32, dtype)
+        steps = cuttings.prefix_then_single(reqs)
+        got, n_graph = rp.replay_through_graphs(folder, dtype, steps, 16)
+        assert n_graph > len(steps) // 2
+        for rid, ref in want.items():
+            tol = cuttings.tolerance(dtype, ref, want32[rid] if want32 else None)
+            for pos, row in got[rid].items():
+                err = float(np.abs(row - ref[pos]).max())
+                assert err <= tol, f"{dtype}: request {rid} position {pos}: error {err:.3g}, tolerance {tol:.3g}"
+        if dtype == "bfloat16":
+            assert calls["fused"] > 0, "decode steps left the fused rotary + attention kernel"
+            assert calls["tc"] > 0, "portions left the tcgen05 kernel"
+    finally:
+        unregister_architecture("ToyQkNormLM")

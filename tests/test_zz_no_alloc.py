@@ -54,6 +54,8 @@ def test_static_scratch_entry_point_matches_the_usual_one():
     def ptr(t):
         return c_void_p(t.data_ptr())
 
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+
     for call, lens_kv in enumerate(([1, 300, 2049, 77, 1024], [513, 5, 1500])):
         kc, vc, indptr, pages, qkv = make_case(call, lens_kv, nh, nkv, hd, ps)
         B = len(lens_kv)
@@ -73,7 +75,7 @@ def test_static_scratch_entry_point_matches_the_usual_one():
         rc = fn(ptr(qkv), c_int(qkv.shape[1]), ptr(kc), ptr(vc), ptr(q_start), ptr(kv_len), ptr(indptr), ptr(pages),
                 ptr(items), ptr(counts[0:1]), c_int(n_items), ptr(dec_seqs), ptr(dec_start), ptr(counts[1:2]),
                 c_int(n_dec), ptr(got), c_int(got.shape[1]), c_int(nh), c_int(nkv), c_int(ps), c_float(scale), c_int(0),
-                stream)
+                c_int(kc.shape[0]), ptr(status), stream)
         assert rc == 0
         torch.cuda.synchronize()
         assert torch.cuda.memory_allocated() == before
@@ -85,6 +87,18 @@ def test_static_scratch_entry_point_matches_the_usual_one():
     rc = fn(ptr(qkv), c_int(qkv.shape[1]), ptr(kc), ptr(vc), ptr(q_start), ptr(kv_len), ptr(indptr), ptr(pages),
             ptr(items), ptr(counts[0:1]), c_int(too_many), ptr(dec_seqs), ptr(dec_start), ptr(counts[1:2]), c_int(n_dec),
             ptr(got), c_int(got.shape[1]), c_int(nh), c_int(nkv), c_int(ps), c_float(scale), c_int(0),
-            stream)
+            c_int(kc.shape[0]), ptr(status), stream)
     assert rc == -4
     torch.cuda.synchronize()
+    assert int(status) == 0
+    # a block table that names a page beyond the caller's cache: the status bit is set, zeros stand in for the page,
+    # nothing outside the cache is read
+    bad = pages.clone()
+    bad[0] = kc.shape[0] + 7
+    rc = fn(ptr(qkv), c_int(qkv.shape[1]), ptr(kc), ptr(vc), ptr(q_start), ptr(kv_len), ptr(indptr), ptr(bad),
+            ptr(items), ptr(counts[0:1]), c_int(n_items), ptr(dec_seqs), ptr(dec_start), ptr(counts[1:2]), c_int(n_dec),
+            ptr(got), c_int(got.shape[1]), c_int(nh), c_int(nkv), c_int(ps), c_float(scale), c_int(0),
+            c_int(kc.shape[0]), ptr(status), stream)
+    assert rc == 0
+    torch.cuda.synchronize()
+    assert int(status) & 2

@@ -38,7 +38,7 @@ TKB_EXPORT int tkb_attn_decode_static_scratch_bf16(const void* q, int q_stride, 
                                                    const int* n_items_ptr, int items_cap, const int* dec_seqs,
                                                    const int* dec_item_start, const int* n_dec_ptr, int dec_cap,
                                                    void* out, int out_stride, int nh, int nkv, int ps, float scale,
-                                                   int window, void* stream) {
+                                                   int window, int num_pages, int* status, void* stream) {
   if (items_cap <= 0 || dec_cap <= 0) return 0;
   if (nh <= 0) return -2;
   const long long need = tkb_attn_decode_scratch_floats(items_cap, nh);
@@ -49,7 +49,8 @@ TKB_EXPORT int tkb_attn_decode_static_scratch_bf16(const void* q, int q_stride, 
   float* part_o = scratch;                                   // [items_cap, nh, HD]
   float* part_ml = scratch + (size_t)items_cap * nh * HD;    // [items_cap, nh, 2]
   rc = tkb_attn_decode_mma_bf16(q, q_stride, kcache, vcache, seq_q_start, seq_kv_len, page_indptr, page_ids, items,
-                                n_items_ptr, items_cap, part_o, part_ml, nh, nkv, ps, scale, window, stream);
+                                n_items_ptr, items_cap, part_o, part_ml, nh, nkv, ps, scale, window, num_pages, status,
+                                stream);
   if (rc) return rc;
   return tkb_attn_decode_merge_bf16(part_o, part_ml, dec_seqs, dec_item_start, n_dec_ptr, dec_cap, seq_q_start, out,
                                     out_stride, nh, stream);

@@ -27,7 +27,9 @@
 //   * No cudaMalloc, cudaFree or other allocating routine is called, on the first call or later.
 //
 // Arguments are those of tkb_attn_decode_mma_bf16 followed by those of tkb_attn_decode_merge_bf16
-// (see attention_mma.cu), without the two scratch pointers.  Returns 0, a CUDA error code (> 0),
+// (see attention_mma.cu), without the two scratch pointers.  num_pages is the number of pages of the caller's
+// cache and status a device int (or null): a page id of the block tables beyond the pool sets bit 2 of *status and
+// reads as zeros instead of reaching memory outside the cache (num_pages <= 0 switches the check off).  Returns 0, a CUDA error code (> 0),
 // or a refusal (< 0: -2 sizes not supported, -3 grid too large, -4 beyond the built-in scratch).
 #pragma once
 
@@ -42,7 +44,7 @@ int tkb_attn_decode_static_scratch_bf16(const void* q, int q_stride, const void*
                                         const int* page_ids, const int* items, const int* n_items_ptr, int items_cap,
                                         const int* dec_seqs, const int* dec_item_start, const int* n_dec_ptr,
                                         int dec_cap, void* out, int out_stride, int nh, int nkv, int ps, float scale,
-                                        int window, void* stream);
+                                        int window, int num_pages, int* status, void* stream);
 
 #ifdef __cplusplus
 }

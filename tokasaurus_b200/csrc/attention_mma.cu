@@ -114,14 +114,15 @@ struct KvTileLoad {
   int page[ITERS];  // page of each row this thread copies; -1: the row is outside the keys wanted
 
   __device__ __forceinline__ void lookup(const int* __restrict__ table, int ps, int key_base, int key_lo, int key_hi,
-                                         int tid) {
+                                         int tid, int num_pages, int* status) {
     const int ps_shift = (ps & (ps - 1)) == 0 ? 31 - __clz(ps) : -1;  // page sizes that are powers of two: shifts
 #pragma unroll
     for (int i = 0; i < ITERS; i++) {
       const int idx = tid + i * NTHREADS;
       const int key = key_base + idx / CPR;
       page[i] = -1;
-      if (idx < KT * CPR && key >= key_lo && key < key_hi) page[i] = table[ps_shift >= 0 ? key >> ps_shift : key / ps];
+      if (idx < KT * CPR && key >= key_lo && key < key_hi)
+        page[i] = checked_page(table[ps_shift >= 0 ? key >> ps_shift : key / ps], num_pages, status);
     }
   }
   __device__ __forceinline__ void issue(unsigned char* stage, const bf16* __restrict__ kcache,
@@ -149,9 +150,10 @@ struct KvTileLoad {
 template <int NTHREADS>
 __device__ __forceinline__ void load_kv_tile(unsigned char* stage, const bf16* __restrict__ kcache,
                                              const bf16* __restrict__ vcache, const int* __restrict__ table, int kvh,
-                                             int nkv, int ps, int key_base, int key_lo, int key_hi, int tid) {
+                                             int nkv, int ps, int key_base, int key_lo, int key_hi, int tid,
+                                             int num_pages, int* status) {
   KvTileLoad<NTHREADS> t;
-  t.lookup(table, ps, key_base, key_lo, key_hi, tid);
+  t.lookup(table, ps, key_base, key_lo, key_hi, tid, num_pages, status);
   t.issue(stage, kcache, vcache, kvh, nkv, ps, key_base, tid);
 }
 
@@ -297,7 +299,8 @@ attn_decode_mma_kernel(const __grid_constant__ KvMapsParam<TMA> maps, int tma_ro
                        int* __restrict__ status, const float* __restrict__ qkv_parts, int n_parts,
                        long long part_stride, int* __restrict__ counters, const int* __restrict__ item_entry,
                        const int* __restrict__ dec_item_start, const int* __restrict__ out_row_of,
-                       bf16* __restrict__ out, int out_stride) {
+                       bf16* __restrict__ out, int out_stride, const float* __restrict__ qkv_bias,
+                       const float* __restrict__ qk_norm_w, float norm_eps) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
   unsigned char* smem = align_smem(smem_raw);
   trigger_dependents();
@@ -340,7 +343,7 @@ attn_decode_mma_kernel(const __grid_constant__ KvMapsParam<TMA> maps, int tma_ro
   const int tma_atom = lane / tma_boxes, tma_box = lane - tma_atom * tma_boxes;
   const bool tma_lane = use_tma && warp == 0 && tma_atom < HD / 64;
   auto tma_lookup = [&](int tile) {
-    return tma_lane ? table[(k_begin + tile * KT + tma_box * tma_rows) >> ps_shift] : 0;
+    return tma_lane ? checked_page(table[(k_begin + tile * KT + tma_box * tma_rows) >> ps_shift], num_pages, status) : 0;
   };
   auto tma_issue = [&](int tile, int page) {  // warp 0, all lanes
     unsigned char* stage = smem + (tile % DSTAGES) * STAGE_B;
@@ -372,7 +375,8 @@ attn_decode_mma_kernel(const __grid_constant__ KvMapsParam<TMA> maps, int tma_ro
       if (by_tma(st)) {
         if (warp == 0) tma_issue(st, tma_lookup(st));
       } else {
-        load_kv_tile<128>(smem + st * STAGE_B, kcache, vcache, table, kvh, nkv, ps, k_begin + st * KT, k_begin, k_end, tid);
+        load_kv_tile<128>(smem + st * STAGE_B, kcache, vcache, table, kvh, nkv, ps, k_begin + st * KT, k_begin, k_end, tid,
+                          num_pages, status);
       }
     }
     cp_async_commit();
@@ -427,6 +431,13 @@ attn_decode_mma_kernel(const __grid_constant__ KvMapsParam<TMA> maps, int tma_ro
           v.z += e.z;
           v.w += e.w;
         }
+        if (qkv_bias != nullptr) {
+          const float4 b = *reinterpret_cast<const float4*>(qkv_bias + col);
+          v.x += b.x;
+          v.y += b.y;
+          v.z += b.z;
+          v.w += b.w;
+        }
         v.x = __bfloat162float(__float2bfloat16_rn(v.x));
         v.y = __bfloat162float(__float2bfloat16_rn(v.y));
         v.z = __bfloat162float(__float2bfloat16_rn(v.z));
@@ -437,10 +448,25 @@ attn_decode_mma_kernel(const __grid_constant__ KvMapsParam<TMA> maps, int tma_ro
       for (int idx = tid; idx < (gn + 2) * HD; idx += 128) {
         const int r = idx / HD, d = idx - r * HD;
         const int col = r < gn ? (kvh * group + g0 + r) * HD + d : (r == gn ? (nh + kvh) * HD + d : (nh + nkv + kvh) * HD + d);
-        srow[(r < gn ? r : 16 + (r - gn)) * HD + d] = __bfloat162float(q[(size_t)t * q_stride + col]);
+        float v = __bfloat162float(q[(size_t)t * q_stride + col]);
+        if (qkv_bias != nullptr) v = __bfloat162float(__float2bfloat16_rn(v + qkv_bias[col]));
+        srow[(r < gn ? r : 16 + (r - gn)) * HD + d] = v;
       }
     }
     __syncthreads();
+    if (qk_norm_w != nullptr) {
+      // the element-wise stage a mixer may ask for: every q head and the k head RMS-normalised over the head size
+      for (int r = warp; r < gn + 1; r += 4) {
+        float* x = srow + (r < gn ? r : 16) * HD;
+        const float* w = qk_norm_w + (r < gn ? 0 : HD);
+        float ss = 0.f;
+        for (int d = lane; d < HD; d += 32) ss += x[d] * x[d];
+        ss = warp_sum(ss);
+        const float sc = rsqrtf(ss / (float)HD + norm_eps);
+        for (int d = lane; d < HD; d += 32) x[d] = __bfloat162float(__float2bfloat16_rn(x[d] * sc * w[d]));
+      }
+      __syncthreads();
+    }
     if (owns_new) {
       // this block's split holds position p: rotate the token's own key, keep it and the value for the patch
       // of the tile, and store them in the cache page for later steps (blocks of other head tiles of the
@@ -510,7 +536,7 @@ attn_decode_mma_kernel(const __grid_constant__ KvMapsParam<TMA> maps, int tma_ro
   auto look_ahead = [&](int tile) {
     if (tile >= n_tiles) return;
     if (by_tma(tile)) ahead_page = tma_lookup(tile);
-    else ahead.lookup(table, ps, k_begin + tile * KT, k_begin, k_end, tid);
+    else ahead.lookup(table, ps, k_begin + tile * KT, k_begin, k_end, tid, num_pages, status);
   };
   look_ahead(DSTAGES - 1);
   bool timed_out = false;
@@ -669,7 +695,8 @@ attn_prefill_mma_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restri
                         const int* __restrict__ seq_q_start, const int* __restrict__ seq_q_len,
                         const int* __restrict__ seq_kv_len, const int* __restrict__ page_indptr,
                         const int* __restrict__ page_ids, const int* __restrict__ tiles,
-                        const int* __restrict__ n_tiles_ptr, int nh, int nkv, int ps, float scale_log2, int window) {
+                        const int* __restrict__ n_tiles_ptr, int nh, int nkv, int ps, float scale_log2, int window,
+                        int num_pages, int* __restrict__ status) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
   unsigned char* smem = align_smem(smem_raw);
   trigger_dependents();
@@ -719,13 +746,13 @@ attn_prefill_mma_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restri
   const int warp_lo = window > 0 ? pos0 + warp * 16 - window + 1 : 0;
 
   const int n_tiles = (k_end - k_begin + KT - 1) / KT;
-  load_kv_tile<128>(smem, kcache, vcache, table, kvh, nkv, ps, k_begin, k_begin, k_end, tid);
+  load_kv_tile<128>(smem, kcache, vcache, table, kvh, nkv, ps, k_begin, k_begin, k_end, tid, num_pages, status);
   cp_async_commit();
   for (int it = 0; it < n_tiles; it++) {
     unsigned char* cur = smem + (it & 1) * STAGE_B;
     if (it + 1 < n_tiles)
       load_kv_tile<128>(smem + ((it + 1) & 1) * STAGE_B, kcache, vcache, table, kvh, nkv, ps, k_begin + (it + 1) * KT,
-                        k_begin, k_end, tid);
+                        k_begin, k_end, tid, num_pages, status);
     cp_async_commit();
     cp_async_wait<1>();
     __syncthreads();
@@ -904,13 +931,15 @@ TKB_EXPORT long long tkb_attn_decode_scratch_floats(int items_cap, int nh) {
   return (long long)items_cap * nh * (HD + 2);
 }
 
+// num_pages, status: page ids of the block tables are checked against the pool's size; an id beyond it sets the
+// status flag and reads as zeros (num_pages <= 0: unknown, nothing is checked; status may be null).
 // items: int32 [n_items_cap * 3] (request row, first key counted from the first visible one, number of keys); n_items_ptr: device int32 with the live count.
 // The grid is sized by items_cap, so a captured graph serves any count up to it.
 TKB_EXPORT int tkb_attn_decode_mma_bf16(const void* q, int q_stride, const void* kcache, const void* vcache,
                                         const int* seq_q_start, const int* seq_kv_len, const int* page_indptr,
                                         const int* page_ids, const int* items, const int* n_items_ptr, int items_cap,
                                         float* part_o, float* part_ml, int nh, int nkv, int ps, float scale, int window,
-                                        void* st) {
+                                        int num_pages, int* status, void* st) {
   if (items_cap <= 0) return 0;
   if (nkv <= 0 || nh % nkv != 0 || ps <= 0) return -2;
   int rc = ensure_smem_attr();
@@ -920,12 +949,13 @@ TKB_EXPORT int tkb_attn_decode_mma_bf16(const void* q, int q_stride, const void*
   if ((long long)nkv * head_tiles > 65535) return -3;
   dim3 grid(items_cap, nkv * head_tiles);
   KvMaps maps;
-  memset(&maps, 0, sizeof(maps));  // this entry point does not know the size of the pool: every tile is gathered
+  memset(&maps, 0, sizeof(maps));  // every tile is gathered (num_pages <= 0: the caller does not know the pool's size)
   return launch_decode<false>(false, grid, st, maps, (const bf16*)q, q_stride, (bf16*)kcache, (bf16*)vcache, seq_q_start,
                               seq_kv_len, page_indptr, page_ids, items, n_items_ptr, part_o, part_ml, nh, nkv, ps,
-                              scale * 1.4426950408889634f, window, head_tiles, (const float*)nullptr, 0, 0, 0,
-                              (int*)nullptr, (const float*)nullptr, 0, 0LL, (int*)nullptr, (const int*)nullptr,
-                              (const int*)nullptr, (const int*)nullptr, (bf16*)nullptr, 0);
+                              scale * 1.4426950408889634f, window, head_tiles, (const float*)nullptr, 0, 0, num_pages,
+                              status, (const float*)nullptr, 0, 0LL, (int*)nullptr, (const int*)nullptr,
+                              (const int*)nullptr, (const int*)nullptr, (bf16*)nullptr, 0, (const float*)nullptr,
+                              (const float*)nullptr, 0.f);
 }
 
 // The same with rotary encoding and the cache write folded in: qkv holds the step's un-rotated q|k|v rows
@@ -942,7 +972,8 @@ TKB_EXPORT int tkb_attn_decode_rope_mma_bf16(const void* qkv, int q_stride, cons
                                              const int* page_ids, const int* items, const int* n_items_ptr,
                                              int items_cap, float* part_o, float* part_ml, int nh, int nkv, int ps,
                                              float scale, int window, const float* inv_freq, int rot,
-                                             int write_cache, int num_pages, int tma, int* status, void* st) {
+                                             int write_cache, int num_pages, int tma, int* status,
+                                             const float* qkv_bias, const float* qk_norm_w, float norm_eps, void* st) {
   if (items_cap <= 0) return 0;
   if (nkv <= 0 || nh % nkv != 0 || ps <= 0 || rot < 0 || rot > HD || (rot & 3)) return -2;
   int rc = ensure_smem_attr();
@@ -958,7 +989,7 @@ TKB_EXPORT int tkb_attn_decode_rope_mma_bf16(const void* qkv, int q_stride, cons
                              seq_kv_len, page_indptr, page_ids, items, n_items_ptr, part_o, part_ml, nh, nkv, ps,
                              scale * 1.4426950408889634f, window, head_tiles, inv_freq, rot, write_cache, num_pages,
                              status, qkv_parts, n_parts, part_stride, (int*)nullptr, (const int*)nullptr,
-                             (const int*)nullptr, (const int*)nullptr, (bf16*)nullptr, 0);
+                             (const int*)nullptr, (const int*)nullptr, (bf16*)nullptr, 0, qkv_bias, qk_norm_w, norm_eps);
 }
 
 // Split-key attention with the merge of the splits inside the same kernel (the last block to finish a request's
@@ -974,7 +1005,7 @@ TKB_EXPORT int tkb_attn_decode_merged_bf16(const void* qkv, int q_stride, const 
                                            int fused, const float* inv_freq, int rot, int write_cache,
                                            int num_pages, int tma, int* status, int* counters, const int* item_entry,
                                            const int* dec_item_start, const int* out_row_of, void* out, int out_stride,
-                                           void* st) {
+                                           const float* qkv_bias, const float* qk_norm_w, float norm_eps, void* st) {
   if (items_cap <= 0) return 0;
   if (nkv <= 0 || nh % nkv != 0 || ps <= 0 || counters == nullptr) return -2;
   if (fused && (rot < 0 || rot > HD || (rot & 3))) return -2;
@@ -993,12 +1024,12 @@ TKB_EXPORT int tkb_attn_decode_merged_bf16(const void* qkv, int q_stride, const 
                                seq_q_start, seq_kv_len, page_indptr, page_ids, items, n_items_ptr, part_o, part_ml, nh, nkv,
                                ps, sl2, window, head_tiles, inv_freq, rot, write_cache, num_pages, status, qkv_parts,
                                n_parts, part_stride, counters, item_entry, dec_item_start, out_row_of, (bf16*)out,
-                               out_stride);
+                               out_stride, qkv_bias, qk_norm_w, norm_eps);
   return launch_decode<false>(tma != 0, grid, st, maps, (const bf16*)qkv, q_stride, (bf16*)kcache, (bf16*)vcache,
                               seq_q_start, seq_kv_len, page_indptr, page_ids, items, n_items_ptr, part_o, part_ml, nh, nkv,
                               ps, sl2, window, head_tiles, (const float*)nullptr, 0, 0, num_pages, status,
                               (const float*)nullptr, 0, 0LL, counters, item_entry, dec_item_start, out_row_of, (bf16*)out,
-                              out_stride);
+                              out_stride, (const float*)nullptr, (const float*)nullptr, 0.f);
 }
 
 TKB_EXPORT int tkb_attn_decode_merge_bf16(const float* part_o, const float* part_ml, const int* dec_seqs,
@@ -1016,7 +1047,7 @@ TKB_EXPORT int tkb_attn_prefill_mma_bf16(const void* q, int q_stride, void* out,
                                          const void* vcache, const int* seq_q_start, const int* seq_q_len,
                                          const int* seq_kv_len, const int* page_indptr, const int* page_ids,
                                          const int* tiles, const int* n_tiles_ptr, int tiles_cap, int nh, int nkv, int ps,
-                                         float scale, int window, void* st) {
+                                         float scale, int window, int num_pages, int* status, void* st) {
   if (tiles_cap <= 0) return 0;
   if (nkv <= 0 || nh % nkv != 0 || ps <= 0) return -2;
   if (nh > 65535) return -3;
@@ -1025,6 +1056,7 @@ TKB_EXPORT int tkb_attn_prefill_mma_bf16(const void* q, int q_stride, void* out,
   dim3 grid(tiles_cap, nh);
   return launch_pdl(attn_prefill_mma_kernel, grid, dim3(128), (size_t)SMEM_B, (cudaStream_t)st, (const bf16*)q, q_stride,
                     (bf16*)out, out_stride, (const bf16*)kcache, (const bf16*)vcache, seq_q_start, seq_q_len, seq_kv_len,
-                    page_indptr, page_ids, tiles, n_tiles_ptr, nh, nkv, ps, scale * 1.4426950408889634f, window);
+                    page_indptr, page_ids, tiles, n_tiles_ptr, nh, nkv, ps, scale * 1.4426950408889634f, window, num_pages,
+                    status);
 }
 TKB_EXPORT int tkb_attn_mma_head_dim() { return HD; }

@@ -69,7 +69,8 @@ attn_paged_simt_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ ou
                        const T* __restrict__ kcache, const T* __restrict__ vcache,
                        const int* __restrict__ token_seq, const int* __restrict__ positions,
                        const int* __restrict__ page_indptr, const int* __restrict__ page_ids,
-                       const int* __restrict__ rows, int nh, int nkv, int page_size, float scale_log2, int window) {
+                       const int* __restrict__ rows, int nh, int nkv, int page_size, float scale_log2, int window,
+                       int num_pages, int* __restrict__ status) {
   __shared__ float qs[WARPS][HD];
   trigger_dependents();
   grid_dependency_wait();
@@ -101,9 +102,11 @@ attn_paged_simt_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ ou
       long long rowoff = 0;
       float sc = -FLT_MAX;
       if (live) {
-        const int page = table[j / page_size];
-        rowoff = (((long long)page * nkv + kvh) * page_size + (j % page_size)) * HD;
-        sc = dot_row<T>(kcache + rowoff, qs[warp]);
+        const int page = checked_page(table[j / page_size], num_pages, status);
+        if (page >= 0) {  // else: an id beyond the pool (the status flag is set); the key counts for nothing
+          rowoff = (((long long)page * nkv + kvh) * page_size + (j % page_size)) * HD;
+          sc = dot_row<T>(kcache + rowoff, qs[warp]);
+        }
       }
       const float bm = warp_max(sc);
       const float m_new = fmaxf(m, bm);
@@ -139,8 +142,8 @@ attn_paged_simt_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ ou
 template <typename T>
 int attn_launch(const void* q, int q_stride, void* out, int out_stride, const void* kcache, const void* vcache,
                 const int* token_seq, const int* positions, const int* page_indptr, const int* page_ids,
-                const int* rows, int n_rows, int nh, int nkv, int page_size, float scale, int window,
-                cudaStream_t st) {
+                const int* rows, int n_rows, int nh, int nkv, int page_size, float scale, int window, int num_pages,
+                int* status, cudaStream_t st) {
   if (n_rows <= 0) return 0;
   if (nkv <= 0 || nh % nkv != 0 || page_size <= 0) return -2;
   if (nkv > 65535) return -3;
@@ -148,25 +151,29 @@ int attn_launch(const void* q, int q_stride, void* out, int out_stride, const vo
   const float scale_log2 = scale * 1.4426950408889634f;
   return launch_pdl(attn_paged_simt_kernel<T>, grid, dim3(WARPS * 32), 0, st, (const T*)q, q_stride, (T*)out, out_stride,
                     (const T*)kcache, (const T*)vcache, token_seq, positions, page_indptr, page_ids, rows, nh, nkv,
-                    page_size, scale_log2, window);
+                    page_size, scale_log2, window, num_pages, status);
 }
 
 }  // namespace
 
 // q: [tokens, q_stride] with head h at column h*HD; out: [n_rows, out_stride].  `rows` (nullable)
-// names the tokens whose output is wanted; row r of `out` belongs to token rows[r].
+// names the tokens whose output is wanted; row r of `out` belongs to token rows[r].  num_pages, status: a page id
+// beyond the pool sets the status flag and its keys count for nothing (num_pages <= 0: not checked).
 TKB_EXPORT int tkb_attn_paged_simt_f32(const void* q, int q_stride, void* out, int out_stride, const void* kcache,
                                        const void* vcache, const int* token_seq, const int* positions,
                                        const int* page_indptr, const int* page_ids, const int* rows, int n_rows,
-                                       int nh, int nkv, int page_size, float scale, int window, void* st) {
+                                       int nh, int nkv, int page_size, float scale, int window, int num_pages,
+                                       int* status, void* st) {
   return attn_launch<float>(q, q_stride, out, out_stride, kcache, vcache, token_seq, positions, page_indptr, page_ids,
-                            rows, n_rows, nh, nkv, page_size, scale, window, (cudaStream_t)st);
+                            rows, n_rows, nh, nkv, page_size, scale, window, num_pages, status, (cudaStream_t)st);
 }
 TKB_EXPORT int tkb_attn_paged_simt_bf16(const void* q, int q_stride, void* out, int out_stride, const void* kcache,
                                         const void* vcache, const int* token_seq, const int* positions,
                                         const int* page_indptr, const int* page_ids, const int* rows, int n_rows,
-                                        int nh, int nkv, int page_size, float scale, int window, void* st) {
+                                        int nh, int nkv, int page_size, float scale, int window, int num_pages,
+                                        int* status, void* st) {
   return attn_launch<__nv_bfloat16>(q, q_stride, out, out_stride, kcache, vcache, token_seq, positions, page_indptr,
-                                    page_ids, rows, n_rows, nh, nkv, page_size, scale, window, (cudaStream_t)st);
+                                    page_ids, rows, n_rows, nh, nkv, page_size, scale, window, num_pages, status,
+                                    (cudaStream_t)st);
 }
 TKB_EXPORT int tkb_attn_head_dim() { return HD; }

@@ -96,7 +96,7 @@ __device__ __forceinline__ uint64_t make_desc_mn(uint32_t smem_addr) {
 // are zero.  A warp's lane takes rows lane and lane + 32: their page lookups go out together.
 __device__ __forceinline__ void gather_tile(uint32_t dst, const bf16* __restrict__ cache, const int* __restrict__ table,
                                             int kvh, int nkv, int ps, int ps_shift, int key_base, int key_lo, int key_hi,
-                                            int lane) {
+                                            int lane, int num_pages, int* status) {
   size_t off[2];
   bool valid[2];
 #pragma unroll
@@ -107,7 +107,9 @@ __device__ __forceinline__ void gather_tile(uint32_t dst, const bf16* __restrict
     if (valid[i]) {
       const int pi = ps_shift >= 0 ? key >> ps_shift : key / ps;
       const int slot = ps_shift >= 0 ? key & (ps - 1) : key - pi * ps;
-      off[i] = (((size_t)__ldg(table + pi) * nkv + kvh) * ps + slot) * HD;
+      const int page = checked_page(__ldg(table + pi), num_pages, status);
+      valid[i] = page >= 0;  // a page given back behind a window, or an id beyond the pool: zeros
+      off[i] = valid[i] ? (((size_t)page * nkv + kvh) * ps + slot) * HD : 0;
     }
   }
 #pragma unroll
@@ -188,7 +190,7 @@ attn_prefill_acc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
                         const int* __restrict__ seq_kv_len, const int* __restrict__ page_indptr,
                         const int* __restrict__ page_ids, const int* __restrict__ tiles,
                         const int* __restrict__ n_tiles_ptr, int nh, int nkv, int ps, float scale_log2, int window,
-                        int* __restrict__ status) {
+                        int* __restrict__ status, int num_pages) {
   extern __shared__ unsigned char smem_raw[];
   __shared__ __align__(8) uint64_t k_full[KV_STAGES], k_empty[KV_STAGES], v_full[KV_STAGES], v_empty[KV_STAGES],
       s_full[2][2], p_full[2], pv_done[2][2];
@@ -281,11 +283,12 @@ attn_prefill_acc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
         if (lane < boxes * ATOMS) {
           const int atom = lane / boxes, bx = lane - atom * boxes;
           const int key = key_base + bx * tma_rows;
-          const int row = (__ldg(table + (key >> ps_shift)) * nkv + kvh) * ps + (key & (ps - 1));
+          // an id beyond the pool becomes -1: a negative row is outside the tensor map and reads as zeros
+          const int row = (checked_page(__ldg(table + (key >> ps_shift)), num_pages, status) * nkv + kvh) * ps + (key & (ps - 1));
           tma_load_2d(ring + b * KV_BYTES + atom * (BKV * 128) + bx * tma_rows * 128, map, &full[b], atom * 64, row);
         }
       } else {
-        gather_tile(smem_u32(ring + b * KV_BYTES), cache, table, kvh, nkv, ps, ps_shift, key_base, 0, kv_len, lane);
+        gather_tile(smem_u32(ring + b * KV_BYTES), cache, table, kvh, nkv, ps, ps_shift, key_base, 0, kv_len, lane, num_pages, status);
         cp_async_wait_all();
         fence_proxy_async();
         __syncwarp();
@@ -456,7 +459,7 @@ TKB_EXPORT int tkb_attn_prefill_acc_bf16(const void* q, int q_stride, void* out,
   return launch_pdl(attn_prefill_acc_kernel, grid, dim3(THREADS), (size_t)SMEM_BYTES, (cudaStream_t)st, map_k, map_v,
                     tma_rows, (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)kcache, (const bf16*)vcache,
                     seq_q_start, seq_q_len, seq_kv_len, page_indptr, page_ids, tiles, n_tiles_ptr, nh, nkv, ps,
-                    scale * 1.4426950408889634f, window, status);
+                    scale * 1.4426950408889634f, window, status, n_pages);
 }
 
 TKB_EXPORT int tkb_attn_prefill_acc_head_dim() { return HD; }

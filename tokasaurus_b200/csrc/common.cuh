@@ -50,6 +50,18 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
   return scratch[32];
 }
 
+// A page id read from a block table, checked against the pool before it becomes an address: an id beyond the pool
+// sets the status flag and is treated like -1 (the loaders then fill zeros; nothing is read out of range).
+// Negative ids are legitimate: a page that was given back behind an attention window.  num_pages <= 0: the caller
+// does not know the pool's size, nothing is checked.
+__device__ __forceinline__ int checked_page(int page, int num_pages, int* status) {
+  if (num_pages > 0 && page >= num_pages) {
+    if (status != nullptr) atomicOr(status, TKB_STATUS_BAD_PAGE);
+    return -1;
+  }
+  return page;
+}
+
 // Programmatic dependent launch: a kernel launched with `launch_pdl` may start while the kernel
 // before it in the stream is still running.  It must call grid_dependency_wait() before it reads
 // anything an earlier kernel wrote and before it writes anything at all; what it does before that
@@ -73,6 +85,21 @@ inline int launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t sm
   cfg.numAttrs = 1;
   cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
   return static_cast<int>(e);
+}
+
+// Number of SMs of the current device, asked once per process (the grids and work splits of the kernels are sized
+// by it; no file holds the count of a particular GPU).  1 if the query fails: every split is then still right,
+// only too coarse.
+inline int sm_count() {
+  static int cached = -1;
+  if (cached < 0) {
+    int dev = 0, n = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess ||
+        cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)
+      n = 1;
+    cached = n;
+  }
+  return cached;
 }
 
 inline int launch_status() {

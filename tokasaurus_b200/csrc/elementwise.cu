@@ -326,220 +326,238 @@ TKB_EXPORT int tkb_add_rmsnorm_bf16(float* x, const void* delta, const float* pa
 }
 
 // ------------------------------------------------------------------------------------------------
-// Rotary position encoding of q and k (half-split pairing: element j pairs with j + rot/2), in
-// place on q, and the write of the rotated k and of v into the cache pages of the token's
-// request.  qkv row layout: [nh*hd | nkv*hd | nkv*hd].  Cache layout per layer: [page, kv head,
-// slot in page, hd].  The angle is the float32 product position * inv_freq[j]; cos and sin use
-// the accurate float routines (full range reduction), once per token and pair, shared by heads.
-// rot == 0 means no position encoding.  Tokens with token_seq < 0 are padding and are skipped.
-template <typename T>
-__global__ void rope_kv_write_kernel(T* __restrict__ qkv, const int* __restrict__ positions,
-                                     const int* __restrict__ token_seq, const int* __restrict__ page_indptr,
-                                     const int* __restrict__ page_ids, const float* __restrict__ inv_freq,
-                                     T* __restrict__ kcache, T* __restrict__ vcache, int nh, int nkv, int hd, int rot,
-                                     int page_size, int num_pages, int write_cache, int* __restrict__ status) {
+// From a step's q|k|v rows to rotated q and to the cache: rotary position encoding of q and k (half-split
+// pairing: element j pairs with j + rot/2), the rotated q written out (in place or to a tensor of its own), the
+// rotated k and v written into the cache pages of the token's request.  q|k|v row layout: [nh*hd | nkv*hd |
+// nkv*hd], as rows of the activation type or as float32 slices of a K-split product, [n_partials][tokens, C],
+// which are added in order and rounded to the activation type first.  Cache layout per layer: [page, kv head,
+// slot in page, hd].  The angle is the float32 product position * inv_freq[j]; cos and sin use the accurate
+// float routines (full range reduction), once per token and pair, shared by heads.  rot == 0: no position
+// encoding.  Tokens with token_seq < 0 are padding and are skipped.
+//
+// Between "q|k|v ready" and "rotate" sits an element-wise stage that a mixer may ask for:
+//   bias       float32 [C] or null: added to the row (and the sum rounded to the activation type);
+//   qk_norm_w  float32 [2][hd] or null: every q head and every k head is RMS-normalised over its hd elements
+//              (statistics in float32, eps = norm_eps) and scaled by the first (q) or second (k) weight row.
+//
+// A block takes tokens t = blockIdx.x, blockIdx.x + gridDim.x, ...; the token's row is staged in shared memory
+// as float32 with 16-byte loads, everything after reads it from there and leaves in 16-byte stores.  What the
+// host wrote for the step (positions, request rows, block tables) is there before any kernel of the step runs:
+// the first token's page and angles are worked out before the wait for the kernel that makes q|k|v.
+template <typename T> struct Vec16;
+template <> struct Vec16<float> {
+  static constexpr int N = 4;
+  static __device__ __forceinline__ void load(const float* p, float (&v)[4]) {
+    const float4 x = *reinterpret_cast<const float4*>(p);
+    v[0] = x.x; v[1] = x.y; v[2] = x.z; v[3] = x.w;
+  }
+  static __device__ __forceinline__ void store(float* p, const float (&v)[4]) {
+    *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+  }
+};
+template <> struct Vec16<__nv_bfloat16> {
+  static constexpr int N = 8;
+  static __device__ __forceinline__ void load(const __nv_bfloat16* p, float (&v)[8]) {
+    const uint4 x = *reinterpret_cast<const uint4*>(p);
+    const uint32_t w[4] = {x.x, x.y, x.z, x.w};
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+      v[2 * i] = __uint_as_float(w[i] << 16);
+      v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+    }
+  }
+  static __device__ __forceinline__ void store(__nv_bfloat16* p, const float (&v)[8]) {
+    uint32_t w[4];
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+      __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+      w[i] = *reinterpret_cast<uint32_t*>(&h);
+    }
+    *reinterpret_cast<uint4*>(p) = make_uint4(w[0], w[1], w[2], w[3]);
+  }
+};
+
+// element `d` of a head after the rotation; `x` points at the head's first element in shared memory
+__device__ __forceinline__ float rotated(const float* x, const float* cs, int d, int half, int rot) {
+  if (d < half) return x[d] * cs[d] - x[d + half] * cs[half + d];
+  if (d < rot) return x[d] * cs[d - half] + x[d - half] * cs[d];
+  return x[d];
+}
+
+template <typename T, bool PARTS>
+__global__ void __launch_bounds__(256)
+rope_kv_write_kernel(const T* __restrict__ rows, const float* __restrict__ partials, int n_partials,
+                     long long partial_stride, T* __restrict__ q_out, long long q_out_stride,
+                     const int* __restrict__ positions, const int* __restrict__ token_seq,
+                     const int* __restrict__ page_indptr, const int* __restrict__ page_ids,
+                     const float* __restrict__ inv_freq, T* __restrict__ kcache, T* __restrict__ vcache, int n_tokens,
+                     int nh, int nkv, int hd, int rot, int page_size, int num_pages, int write_cache,
+                     int* __restrict__ status, const float* __restrict__ bias, const float* __restrict__ qk_norm_w,
+                     float norm_eps) {
   trigger_dependents();
-  // What the host wrote for the step (positions, request rows, block tables) is there before any kernel of the
-  // step runs: the token's page and its angles are worked out before the wait for the kernel that makes q|k|v.
-  extern __shared__ float cs[];  // cos[rot/2], sin[rot/2]
-  const int t = blockIdx.x;
-  const int s = token_seq[t];
-  if (s < 0) return;
-  const int pos = positions[t];
-  const int page = write_cache ? page_ids[page_indptr[s] + pos / page_size] : 0;  // on its way during the sin/cos
+  extern __shared__ __align__(16) float sm[];  // row[C], cos[rot/2], sin[rot/2]
+  constexpr int N = Vec16<T>::N;
+  const int C = (nh + 2 * nkv) * hd;
+  float* row = sm;
+  float* cs = sm + C;
   const int half = rot >> 1;
-  for (int j = threadIdx.x; j < half; j += blockDim.x) {
-    float ang = (float)pos * inv_freq[j];
-    float sn, c;
-    sincosf(ang, &sn, &c);
-    cs[j] = c;
-    cs[half + j] = sn;
-  }
-  __syncthreads();
-  grid_dependency_wait();
-
-  T* row = qkv + (size_t)t * (size_t)(nh + 2 * nkv) * hd;
-  const bool vec = (half & 3) == 0 && (hd & 3) == 0;  // four elements a thread and step
-  // q heads: rotate in place.
-  if (vec) {
-    const int h4 = half >> 2;
-    for (int idx = threadIdx.x; idx < nh * h4; idx += blockDim.x) {
-      const int h = idx / h4, j = (idx - h * h4) * 4;
-      T* p = row + h * hd;
-      const float4 x1 = load4(p + j), x2 = load4(p + j + half);
-      const float4 c = *reinterpret_cast<const float4*>(cs + j), sn = *reinterpret_cast<const float4*>(cs + half + j);
-      store4(p + j, make_float4(x1.x * c.x - x2.x * sn.x, x1.y * c.y - x2.y * sn.y, x1.z * c.z - x2.z * sn.z,
-                                x1.w * c.w - x2.w * sn.w));
-      store4(p + j + half, make_float4(x2.x * c.x + x1.x * sn.x, x2.y * c.y + x1.y * sn.y, x2.z * c.z + x1.z * sn.z,
-                                       x2.w * c.w + x1.w * sn.w));
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
+  bool waited = false;
+  for (int t = blockIdx.x; t < n_tokens; t += gridDim.x) {
+    const int s = token_seq[t];
+    if (s < 0) continue;  // padding (the same for every thread of the block)
+    const int pos = positions[t];
+    const int page = write_cache ? page_ids[page_indptr[s] + pos / page_size] : 0;  // on its way during the sin/cos
+    for (int j = tid; j < half; j += blockDim.x) {
+      float sn, c;
+      sincosf((float)pos * inv_freq[j], &sn, &c);
+      cs[j] = c;
+      cs[half + j] = sn;
     }
-  } else {
-    for (int idx = threadIdx.x; idx < nh * half; idx += blockDim.x) {
-      const int h = idx / half, j = idx - h * half;
-      T* p = row + h * hd;
-      const float x1 = to_float(p[j]), x2 = to_float(p[j + half]);
-      const float c = cs[j], sn = cs[half + j];
-      p[j] = from_float<T>(x1 * c - x2 * sn);
-      p[j + half] = from_float<T>(x2 * c + x1 * sn);
+    if (!waited) {
+      grid_dependency_wait();
+      waited = true;
     }
-  }
-  if (!write_cache) return;  // a layer call that reads another call's cache writes none of its own
-  if (page < 0 || page >= num_pages) {
-    if (threadIdx.x == 0) atomicOr(status, TKB_STATUS_BAD_PAGE);
-    return;
-  }
-  const int slot = pos % page_size;
-  const T* krow = row + nh * hd;
-  const T* vrow = krow + nkv * hd;
-  if (vec) {
-    const int d4n = hd >> 2;
-    for (int idx = threadIdx.x; idx < nkv * d4n; idx += blockDim.x) {
-      const int h = idx / d4n, d = (idx - h * d4n) * 4;
-      const size_t dst = (((size_t)page * nkv + h) * page_size + slot) * hd + d;
-      const T* kh = krow + h * hd;
-      float4 kv = load4(kh + d);
-      if (d < half) {
-        const float4 y = load4(kh + d + half);
-        const float4 c = *reinterpret_cast<const float4*>(cs + d), sn = *reinterpret_cast<const float4*>(cs + half + d);
-        kv = make_float4(kv.x * c.x - y.x * sn.x, kv.y * c.y - y.y * sn.y, kv.z * c.z - y.z * sn.z, kv.w * c.w - y.w * sn.w);
-      } else if (d < rot) {
-        const int j = d - half;
-        const float4 y = load4(kh + j);
-        const float4 c = *reinterpret_cast<const float4*>(cs + j), sn = *reinterpret_cast<const float4*>(cs + half + j);
-        kv = make_float4(kv.x * c.x + y.x * sn.x, kv.y * c.y + y.y * sn.y, kv.z * c.z + y.z * sn.z, kv.w * c.w + y.w * sn.w);
+    // the row, as float32 values that the activation type can hold
+    if (PARTS) {
+      for (int i = tid * 4; i < C; i += blockDim.x * 4) {
+        const float* src = partials + (size_t)t * C + i;
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int p = 0; p < n_partials; p++) {
+          const float4 e = *reinterpret_cast<const float4*>(src + (size_t)p * partial_stride);
+          v.x += e.x; v.y += e.y; v.z += e.z; v.w += e.w;
+        }
+        if (bias != nullptr) {
+          const float4 b = *reinterpret_cast<const float4*>(bias + i);
+          v.x += b.x; v.y += b.y; v.z += b.z; v.w += b.w;
+        }
+        *reinterpret_cast<float4*>(row + i) = make_float4(to_float(from_float<T>(v.x)), to_float(from_float<T>(v.y)),
+                                                          to_float(from_float<T>(v.z)), to_float(from_float<T>(v.w)));
       }
-      store4(kcache + dst, kv);
-      store4(vcache + dst, load4(vrow + h * hd + d));
-    }
-    return;
-  }
-  for (int idx = threadIdx.x; idx < nkv * hd; idx += blockDim.x) {
-    const int h = idx / hd, d = idx - h * hd;
-    const size_t dst = (((size_t)page * nkv + h) * page_size + slot) * hd + d;
-    float kv;
-    if (d < half) {
-      kv = to_float(krow[idx]) * cs[d] - to_float(krow[idx + half]) * cs[half + d];
-    } else if (d < rot) {
-      const int j = d - half;
-      kv = to_float(krow[idx]) * cs[j] + to_float(krow[idx - half]) * cs[half + j];
     } else {
-      kv = to_float(krow[idx]);
+      const T* src = rows + (size_t)t * C;
+      for (int i = tid * N; i < C; i += blockDim.x * N) {
+        float v[N];
+        Vec16<T>::load(src + i, v);
+        if (bias != nullptr) {
+#pragma unroll
+          for (int e = 0; e < N; e++) v[e] = to_float(from_float<T>(v[e] + bias[i + e]));
+        }
+#pragma unroll
+        for (int e = 0; e < N; e += 4) *reinterpret_cast<float4*>(row + i + e) = make_float4(v[e], v[e + 1], v[e + 2], v[e + 3]);
+      }
     }
-    kcache[dst] = from_float<T>(kv);
-    vcache[dst] = vrow[idx];
+    __syncthreads();
+    if (qk_norm_w != nullptr) {
+      // RMS norm of every q head and every k head over its hd elements; one warp a head
+      for (int h = warp; h < nh + nkv; h += nwarps) {
+        float* x = row + (size_t)h * hd;
+        const float* w = qk_norm_w + (h < nh ? 0 : hd);
+        float ss = 0.f;
+        for (int d = lane; d < hd; d += 32) ss += x[d] * x[d];
+        ss = warp_sum(ss);
+        const float scale = rsqrtf(ss / (float)hd + norm_eps);
+        for (int d = lane; d < hd; d += 32) x[d] = to_float(from_float<T>(x[d] * scale * w[d]));
+      }
+      __syncthreads();
+    }
+    // q: rotate and write out
+    T* qo = q_out + (size_t)t * q_out_stride;
+    for (int i = tid * N; i < nh * hd; i += blockDim.x * N) {
+      const int h = i / hd, d0 = i - h * hd;
+      float v[N];
+#pragma unroll
+      for (int e = 0; e < N; e++) v[e] = rotated(row + h * hd, cs, d0 + e, half, rot);
+      Vec16<T>::store(qo + i, v);
+    }
+    if (write_cache) {  // a layer call that reads another call's cache writes none of its own
+      if (page < 0 || page >= num_pages) {
+        if (tid == 0) atomicOr(status, TKB_STATUS_BAD_PAGE);
+      } else {
+        const int slot = pos % page_size;
+        const float* krow = row + nh * hd;
+        const float* vrow = krow + nkv * hd;
+        for (int i = tid * N; i < nkv * hd; i += blockDim.x * N) {
+          const int h = i / hd, d0 = i - h * hd;
+          const size_t dst = (((size_t)page * nkv + h) * page_size + slot) * hd + d0;
+          float kv[N], vv[N];
+#pragma unroll
+          for (int e = 0; e < N; e++) {
+            kv[e] = rotated(krow + h * hd, cs, d0 + e, half, rot);
+            vv[e] = vrow[i + e];
+          }
+          Vec16<T>::store(kcache + dst, kv);
+          Vec16<T>::store(vcache + dst, vv);
+        }
+      }
+    }
+    __syncthreads();  // the row and the angles are reused by the block's next token
   }
 }
 
-template <typename T>
-static int rope_kv_write_launch(void* qkv, const int* positions, const int* token_seq, const int* page_indptr,
-                                const int* page_ids, const float* inv_freq, void* kcache, void* vcache,
-                                int n_tokens, int nh, int nkv, int hd, int rot, int page_size, int num_pages,
-                                int write_cache, int* status, cudaStream_t st) {
+template <typename T, bool PARTS>
+static int rope_kv_write_launch(const void* rows, const float* partials, int n_partials, long long partial_stride,
+                                void* q_out, long long q_out_stride, const int* positions, const int* token_seq,
+                                const int* page_indptr, const int* page_ids, const float* inv_freq, void* kcache,
+                                void* vcache, int n_tokens, int nh, int nkv, int hd, int rot, int page_size,
+                                int num_pages, int write_cache, int* status, const float* bias,
+                                const float* qk_norm_w, float norm_eps, cudaStream_t st) {
   if (n_tokens <= 0) return 0;
-  if (rot < 0 || rot > hd || (rot & 1)) return -2;
-  int work = nh * (rot / 2) > nkv * hd ? nh * (rot / 2) : nkv * hd;
-  int threads = work >= 512 ? 256 : (work >= 128 ? 128 : 64);
-  size_t smem = (size_t)(rot > 0 ? rot : 2) * sizeof(float);
-  return launch_pdl(rope_kv_write_kernel<T>, dim3(n_tokens), dim3(threads), smem, st, (T*)qkv, positions, token_seq,
-                    page_indptr, page_ids, inv_freq, (T*)kcache, (T*)vcache, nh, nkv, hd, rot, page_size, num_pages,
-                    write_cache, status);
+  if (rot < 0 || rot > hd || (rot & 1) || (hd & 15) || nh <= 0 || nkv <= 0 || (PARTS && n_partials < 1)) return -2;
+  const size_t smem = ((size_t)(nh + 2 * nkv) * hd + (rot > 0 ? rot : 2)) * sizeof(float);
+  if (smem > 160 * 1024) return -2;  // a row wider than an SM's shared memory holds
+  static bool attr_done = false;
+  if (!attr_done) {
+    cudaError_t e = cudaFuncSetAttribute(rope_kv_write_kernel<T, PARTS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         160 * 1024);
+    if (e != cudaSuccess) return (int)e;
+    attr_done = true;
+  }
+  // as many blocks as the GPU holds at once; each walks over its share of the tokens
+  const int per_sm = smem > 0 ? (int)((200 * 1024) / (smem + 1024)) : 8;
+  int blocks = sm_count() * (per_sm < 1 ? 1 : (per_sm > 8 ? 8 : per_sm));
+  if (blocks > n_tokens) blocks = n_tokens;
+  return launch_pdl(rope_kv_write_kernel<T, PARTS>, dim3(blocks), dim3(256), smem, st, (const T*)rows, partials,
+                    n_partials, partial_stride, (T*)q_out, q_out_stride, positions, token_seq, page_indptr, page_ids,
+                    inv_freq, (T*)kcache, (T*)vcache, n_tokens, nh, nkv, hd, rot, page_size, num_pages, write_cache,
+                    status, bias, qk_norm_w, norm_eps);
 }
+
+// qkv: rows [n_tokens, C] of float32 / bfloat16; q is rotated in place.  bias, qk_norm_w: see above (null: none).
 TKB_EXPORT int tkb_rope_kv_write_f32(void* qkv, const int* positions, const int* token_seq, const int* page_indptr,
                                      const int* page_ids, const float* inv_freq, void* kcache, void* vcache,
                                      int n_tokens, int nh, int nkv, int hd, int rot, int page_size, int num_pages,
-                                     int write_cache, int* status, void* st) {
-  return rope_kv_write_launch<float>(qkv, positions, token_seq, page_indptr, page_ids, inv_freq, kcache, vcache,
-                                     n_tokens, nh, nkv, hd, rot, page_size, num_pages, write_cache, status,
-                                     (cudaStream_t)st);
+                                     int write_cache, int* status, const float* bias, const float* qk_norm_w,
+                                     float norm_eps, void* st) {
+  return rope_kv_write_launch<float, false>(qkv, nullptr, 0, 0, qkv, (long long)(nh + 2 * nkv) * hd, positions,
+                                            token_seq, page_indptr, page_ids, inv_freq, kcache, vcache, n_tokens, nh,
+                                            nkv, hd, rot, page_size, num_pages, write_cache, status, bias, qk_norm_w,
+                                            norm_eps, (cudaStream_t)st);
 }
 TKB_EXPORT int tkb_rope_kv_write_bf16(void* qkv, const int* positions, const int* token_seq, const int* page_indptr,
                                       const int* page_ids, const float* inv_freq, void* kcache, void* vcache,
                                       int n_tokens, int nh, int nkv, int hd, int rot, int page_size, int num_pages,
-                                      int write_cache, int* status, void* st) {
-  return rope_kv_write_launch<__nv_bfloat16>(qkv, positions, token_seq, page_indptr, page_ids, inv_freq, kcache,
-                                             vcache, n_tokens, nh, nkv, hd, rot, page_size, num_pages, write_cache,
-                                             status, (cudaStream_t)st);
+                                      int write_cache, int* status, const float* bias, const float* qk_norm_w,
+                                      float norm_eps, void* st) {
+  return rope_kv_write_launch<__nv_bfloat16, false>(qkv, nullptr, 0, 0, qkv, (long long)(nh + 2 * nkv) * hd, positions,
+                                                    token_seq, page_indptr, page_ids, inv_freq, kcache, vcache,
+                                                    n_tokens, nh, nkv, hd, rot, page_size, num_pages, write_cache,
+                                                    status, bias, qk_norm_w, norm_eps, (cudaStream_t)st);
 }
 
-// The same for q|k|v that arrive as float32 slices of a split matrix product, [n_partials][tokens, C]:
-// the slices are added in order into shared memory, q is rotated and written to q_out
-// [tokens, nh*hd] in the activation type, rotated k and v go to the cache.
-template <typename T>
-__global__ void rope_kv_write_partials_kernel(const float* __restrict__ partials, int n_partials,
-                                              long long partial_stride, T* __restrict__ q_out,
-                                              const int* __restrict__ positions, const int* __restrict__ token_seq,
-                                              const int* __restrict__ page_indptr, const int* __restrict__ page_ids,
-                                              const float* __restrict__ inv_freq, T* __restrict__ kcache,
-                                              T* __restrict__ vcache, int nh, int nkv, int hd, int rot, int page_size,
-                                              int num_pages, int write_cache, int* __restrict__ status) {
-  trigger_dependents();
-  grid_dependency_wait();
-  extern __shared__ float sm[];  // row[C], cos[rot/2], sin[rot/2]
-  const int C = (nh + 2 * nkv) * hd;
-  float* row = sm;
-  float* cs = sm + C;
-  const int t = blockIdx.x;
-  const int s = token_seq[t];
-  if (s < 0) return;
-  const int pos = positions[t];
-  const int half = rot >> 1;
-  for (int i = threadIdx.x; i < C; i += blockDim.x) {
-    float v = 0.f;
-    for (int p = 0; p < n_partials; p++) v += partials[(size_t)p * partial_stride + (size_t)t * C + i];
-    // the product's result in the activation type, as the unsplit path would have stored it
-    row[i] = to_float(from_float<T>(v));
-  }
-  for (int j = threadIdx.x; j < half; j += blockDim.x) {
-    float sn, c;
-    sincosf((float)pos * inv_freq[j], &sn, &c);
-    cs[j] = c;
-    cs[half + j] = sn;
-  }
-  __syncthreads();
-  T* qo = q_out + (size_t)t * nh * hd;
-  for (int idx = threadIdx.x; idx < nh * hd; idx += blockDim.x) {
-    const int d = idx % hd;
-    float v;
-    if (d < half) v = row[idx] * cs[d] - row[idx + half] * cs[half + d];
-    else if (d < rot) v = row[idx] * cs[d - half] + row[idx - half] * cs[d];
-    else v = row[idx];
-    qo[idx] = from_float<T>(v);
-  }
-  if (!write_cache) return;
-  const int page = page_ids[page_indptr[s] + pos / page_size];
-  if (page < 0 || page >= num_pages) {
-    if (threadIdx.x == 0) atomicOr(status, TKB_STATUS_BAD_PAGE);
-    return;
-  }
-  const int slot = pos % page_size;
-  const float* krow = row + nh * hd;
-  const float* vrow = krow + nkv * hd;
-  for (int idx = threadIdx.x; idx < nkv * hd; idx += blockDim.x) {
-    const int h = idx / hd, d = idx - h * hd;
-    const size_t dst = (((size_t)page * nkv + h) * page_size + slot) * hd + d;
-    float kv;
-    if (d < half) kv = krow[idx] * cs[d] - krow[idx + half] * cs[half + d];
-    else if (d < rot) kv = krow[idx] * cs[d - half] + krow[idx - half] * cs[d];
-    else kv = krow[idx];
-    kcache[dst] = from_float<T>(kv);
-    vcache[dst] = from_float<T>(vrow[idx]);
-  }
-}
-
+// The same for q|k|v that arrive as float32 slices of a split matrix product, [n_partials][tokens, C]; the rotated
+// q goes to q_out [tokens, nh*hd] in bfloat16.
 TKB_EXPORT int tkb_rope_kv_write_partials_bf16(const float* partials, int n_partials, long long partial_stride,
                                                void* q_out, const int* positions, const int* token_seq,
                                                const int* page_indptr, const int* page_ids, const float* inv_freq,
                                                void* kcache, void* vcache, int n_tokens, int nh, int nkv, int hd,
                                                int rot, int page_size, int num_pages, int write_cache, int* status,
-                                               void* st) {
-  typedef __nv_bfloat16 T;
-  if (n_tokens <= 0) return 0;
-  if (rot < 0 || rot > hd || (rot & 1) || n_partials < 1) return -2;
-  const size_t smem = ((size_t)(nh + 2 * nkv) * hd + (rot > 0 ? rot : 2)) * sizeof(float);
-  if (smem > 48 * 1024) return -2;
-  return launch_pdl(rope_kv_write_partials_kernel<T>, dim3(n_tokens), dim3(256), smem, (cudaStream_t)st, partials,
-                    n_partials, partial_stride, (T*)q_out, positions, token_seq, page_indptr, page_ids, inv_freq,
-                    (T*)kcache, (T*)vcache, nh, nkv, hd, rot, page_size, num_pages, write_cache, status);
+                                               const float* bias, const float* qk_norm_w, float norm_eps, void* st) {
+  return rope_kv_write_launch<__nv_bfloat16, true>(nullptr, partials, n_partials, partial_stride, q_out,
+                                                   (long long)nh * hd, positions, token_seq, page_indptr, page_ids,
+                                                   inv_freq, kcache, vcache, n_tokens, nh, nkv, hd, rot, page_size,
+                                                   num_pages, write_cache, status, bias, qk_norm_w, norm_eps,
+                                                   (cudaStream_t)st);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -593,7 +611,7 @@ static int silu_mul_launch(const void* gu, void* out, int rows, int I, int inter
   long long total = (long long)rows * I;
   if (total <= 0) return 0;
   long long blocks = (((I & 7) == 0 ? total / 8 : total) + 255) / 256;
-  if (blocks > 148 * 16) blocks = 148 * 16;
+  if (blocks > sm_count() * 16) blocks = sm_count() * 16;
   if (blocks < 1) blocks = 1;
   return launch_pdl(silu_mul_kernel<T>, dim3((int)blocks), dim3(256), 0, st, (const T*)gu, (T*)out, total, I, interleave);
 }

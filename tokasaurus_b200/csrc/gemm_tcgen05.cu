@@ -208,12 +208,7 @@ int launch(const void* A, int lda, const void* W, int ldw, void* out, int ldo, i
   if (rc) return rc;
   rc = make_map(&map_w, W, N, K, ldw, BN);
   if (rc) return rc;
-  static int n_sms = 0;
-  if (n_sms == 0) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (cudaDeviceGetAttribute(&n_sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n_sms <= 0) n_sms = 148;
-  }
+  const int n_sms = tkb::sm_count();
   const int tiles = ((N + BN - 1) / BN) * ((M + BM - 1) / BM);
   dim3 grid(tiles < n_sms ? tiles : n_sms);
   gemm_tcgen05_kernel<BN, GATED><<<grid, THREADS, Cfg<BN>::SMEM_BYTES, st>>>(map_a, map_w, (bf16*)out, ldo, M, N, K, status);

@@ -198,7 +198,7 @@ int launch(const void* A, int lda, const void* W, int ldw, void* out, int M, int
 TKB_EXPORT int tkb_linear_tcgen05_decode_slices(int N, int K, int max_slices) {
   const int tiles = (N + BMW - 1) / BMW;
   const int kblocks = (K + BK - 1) / BK;
-  int s = 148 / tiles;
+  int s = tkb::sm_count() / tiles;
   if (s > max_slices) s = max_slices;
   if (s > kblocks / 2) s = kblocks / 2;
   if (s < 1) s = 1;

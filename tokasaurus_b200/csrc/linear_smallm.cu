@@ -44,7 +44,7 @@ __device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], 
 
 // WARPS warps a block, 16 output features a warp.  Four warps and two blocks an SM is the general shape; a wide
 // product whose feature tiles do not divide evenly over the SMs that way (gate/up of 16,384 rows: 256 blocks
-// on 148 SMs, so most SMs stream twice what the others do, and an SM streams at a fixed rate) runs as one
+// on a B200's 148 SMs, so most SMs stream twice what the others do, and an SM streams at a fixed rate) runs as one
 // block of up to eight warps an SM instead.
 template <int NT, int WARPS = 4> struct Tile {
   static constexpr int A_ROWS = NT * 8;                      // token rows kept in shared memory (8 rows: ldmatrix.x2)
@@ -226,7 +226,8 @@ int dispatch(const void* A, int lda, const void* W, int ldw, void* out, int M, i
              int kblocks_per_slice, cudaStream_t st) {
   if (GATED && M <= 8 && slices == 1) {
     // one block an SM when that gives every SM the same share of the weights (see Tile)
-    const int per_sm = ((N + 15) / 16 + 147) / 148;  // 16-row tiles an SM
+    const int sms = sm_count();
+    const int per_sm = ((N + 15) / 16 + sms - 1) / sms;  // 16-row tiles an SM
     if (per_sm == 5) return launch<1, GATED, 5>(A, lda, W, ldw, out, M, N, K, slices, kblocks_per_slice, st);
     if (per_sm == 6) return launch<1, GATED, 6>(A, lda, W, ldw, out, M, N, K, slices, kblocks_per_slice, st);
     if (per_sm == 7) return launch<1, GATED, 7>(A, lda, W, ldw, out, M, N, K, slices, kblocks_per_slice, st);
@@ -245,7 +246,7 @@ int dispatch(const void* A, int lda, const void* W, int ldw, void* out, int M, i
 TKB_EXPORT int tkb_linear_smallm_slices(int N, int K, int max_slices) {
   const int tiles = (N + BN - 1) / BN;
   const int kblocks = (K + BK - 1) / BK;
-  int s = (2 * 148 + tiles - 1) / tiles;
+  int s = (2 * sm_count() + tiles - 1) / tiles;
   if (s > max_slices) s = max_slices;
   if (s > kblocks / 2) s = kblocks / 2;  // at least two k-blocks (256 k) a slice
   if (s < 1) s = 1;

@@ -362,7 +362,7 @@ TKB_EXPORT int tkb_sample(const float* logits, const float* temperature, const u
 // are too few to fill the GPU with one block each.  nch = tkb_sample_chunks(R, V).
 TKB_EXPORT int tkb_sample_chunks(int R, int V) {
   if (R <= 0 || V < 32768) return 1;
-  int nch = (2 * 148 + R - 1) / R;
+  int nch = (2 * sm_count() + R - 1) / R;
   if (nch > 64) nch = 64;
   const int ngroups = (V + 3) / 4;
   if (nch > ngroups / 256) nch = ngroups / 256;

@@ -160,11 +160,15 @@ def add_rmsnorm(x: torch.Tensor, delta: torch.Tensor | None, weight: torch.Tenso
 def rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, token_seq: torch.Tensor, page_indptr: torch.Tensor,
                   page_ids: torch.Tensor, inv_freq: torch.Tensor | None, kcache: torch.Tensor, vcache: torch.Tensor,
                   n_heads: int, n_kv_heads: int, head_dim: int, rotary_dim: int, page_size: int,
-                  write_cache: bool, status: torch.Tensor) -> None:
+                  write_cache: bool, status: torch.Tensor, bias: torch.Tensor | None = None,
+                  qk_norm: torch.Tensor | None = None, norm_eps: float = 0.0) -> None:
     """Rotate q (in place) and k by position, write rotated k and v into the request's pages.
 
-    kcache/vcache: [pages, n_kv_heads, page_size, head_dim]."""
-    _need_cuda(qkv, positions, token_seq, page_indptr, page_ids, inv_freq, kcache, vcache, status)
+    kcache/vcache: [pages, n_kv_heads, page_size, head_dim].  The element-wise stage before the rotation:
+    ``bias`` float32 [C] is added to the row; ``qk_norm`` float32 [2, head_dim] RMS-normalises every q head (first
+    row of weights) and every k head (second row) over the head size, with ``norm_eps``."""
+    _need_cuda(qkv, positions, token_seq, page_indptr, page_ids, inv_freq, kcache, vcache, status, bias, qk_norm)
+    _check_qkv_stage(bias, qk_norm, (n_heads + 2 * n_kv_heads) * head_dim, head_dim)
     n = qkv.shape[0]
     _need(qkv.is_contiguous() and qkv.shape[1] == (n_heads + 2 * n_kv_heads) * head_dim, "rope_kv_write: qkv shape")
     _need(kcache.is_contiguous() and vcache.is_contiguous() and kcache.dtype == qkv.dtype, "rope_kv_write: cache")
@@ -177,13 +181,20 @@ def rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, token_seq: torch.T
     _check(f(_ptr(qkv), _ptr(positions), _ptr(token_seq), _ptr(page_indptr), _ptr(page_ids), _ptr(inv_freq),
              _ptr(kcache), _ptr(vcache), c_int(n), c_int(n_heads), c_int(n_kv_heads), c_int(head_dim),
              c_int(rotary_dim), c_int(page_size), c_int(kcache.shape[0]), c_int(1 if write_cache else 0),
-             _ptr(status), _stream()), "rope_kv_write")
+             _ptr(status), _ptr(bias), _ptr(qk_norm), c_float(norm_eps), _stream()), "rope_kv_write")
+
+
+def _check_qkv_stage(bias: torch.Tensor | None, qk_norm: torch.Tensor | None, C: int, head_dim: int) -> None:
+    if bias is not None:
+        _need(bias.dtype == torch.float32 and bias.is_contiguous() and bias.numel() == C, "q|k|v bias: float32 [C]")
+    if qk_norm is not None:
+        _need(qk_norm.dtype == torch.float32 and qk_norm.is_contiguous() and tuple(qk_norm.shape) == (2, head_dim),
+              "q/k norm weights: float32 [2, head_dim]")
 
 
 SMALL_M_MAX = 16   # above this many rows the library product is as fast or faster (measured on B200)
 GATED_M_MAX = 8    # the gated small-batch product wins only up to this many rows
 DECODE_M_MAX = 16
-LAZY_NORM_M_MAX = 0  # up to this many rows the norm is folded into the consumer's matrix product
 _EPILOGUES = {"bf16": 0, "add": 1, "gated": 2, "f32": 3}
 
 
@@ -269,23 +280,27 @@ def rope_kv_write_partials(partials: torch.Tensor, q_out: torch.Tensor, position
                            token_seq: torch.Tensor, page_indptr: torch.Tensor, page_ids: torch.Tensor,
                            inv_freq: torch.Tensor | None, kcache: torch.Tensor, vcache: torch.Tensor, n_heads: int,
                            n_kv_heads: int, head_dim: int, rotary_dim: int, page_size: int, write_cache: bool,
-                           status: torch.Tensor) -> None:
+                           status: torch.Tensor, bias: torch.Tensor | None = None,
+                           qk_norm: torch.Tensor | None = None, norm_eps: float = 0.0) -> None:
     """``rope_kv_write`` for q|k|v that arrive as float32 slices [slices, T, C] of a split product: the
     slices are added, q is rotated into ``q_out`` [T, n_heads*head_dim] (bfloat16), k and v go to the cache."""
-    _need_cuda(partials, q_out, positions, token_seq, page_indptr, page_ids, inv_freq, kcache, vcache, status)
+    _need_cuda(partials, q_out, positions, token_seq, page_indptr, page_ids, inv_freq, kcache, vcache, status, bias,
+               qk_norm)
     S, T, C = partials.shape
+    _check_qkv_stage(bias, qk_norm, C, head_dim)
     _need(partials.dtype == torch.float32 and partials.is_contiguous() and C == (n_heads + 2 * n_kv_heads) * head_dim,
           "rope_kv_write_partials: partials")
     _need(q_out.dtype == torch.bfloat16 and q_out.is_contiguous() and tuple(q_out.shape) == (T, n_heads * head_dim),
           "rope_kv_write_partials: q_out")
     _need(kcache.dtype == torch.bfloat16 and tuple(kcache.shape[1:]) == (n_kv_heads, page_size, head_dim),
           "rope_kv_write_partials: cache layout")
-    _need((C + max(rotary_dim, 2)) * 4 <= 48 * 1024, "rope_kv_write_partials: row too wide for shared memory")
+    _need((C + max(rotary_dim, 2)) * 4 <= 160 * 1024, "rope_kv_write_partials: row too wide for shared memory")
     f = _fn(_libs.get("elementwise.cu"), "tkb_rope_kv_write_partials_bf16")
     _check(f(_ptr(partials), c_int(S), ctypes.c_longlong(T * C), _ptr(q_out), _ptr(positions), _ptr(token_seq),
              _ptr(page_indptr), _ptr(page_ids), _ptr(inv_freq), _ptr(kcache), _ptr(vcache), c_int(T), c_int(n_heads),
              c_int(n_kv_heads), c_int(head_dim), c_int(rotary_dim), c_int(page_size), c_int(kcache.shape[0]),
-             c_int(1 if write_cache else 0), _ptr(status), _stream()), "rope_kv_write_partials")
+             c_int(1 if write_cache else 0), _ptr(status), _ptr(bias), _ptr(qk_norm), c_float(norm_eps), _stream()),
+           "rope_kv_write_partials")
 
 
 def silu_mul(gate_up: torch.Tensor, out: torch.Tensor, interleave: int = 0) -> None:
@@ -326,11 +341,12 @@ def sgemm_tn(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
 def attn_paged(q: torch.Tensor, q_stride: int, out: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor,
                token_seq: torch.Tensor, positions: torch.Tensor, page_indptr: torch.Tensor, page_ids: torch.Tensor,
                rows: torch.Tensor | None, n_rows: int, n_heads: int, n_kv_heads: int, head_dim: int,
-               page_size: int, scale: float, window: int | None) -> None:
+               page_size: int, scale: float, window: int | None, status: torch.Tensor | None = None) -> None:
     """Causal GQA attention over the paged cache on the FP32 pipes (any mix of portions and single tokens).
 
-    q: first n_heads*head_dim columns of each row of a [T, q_stride] buffer; out: [n_rows, n_heads*head_dim]."""
-    _need_cuda(q, out, kcache, vcache, token_seq, positions, page_indptr, page_ids, rows)
+    q: first n_heads*head_dim columns of each row of a [T, q_stride] buffer; out: [n_rows, n_heads*head_dim].
+    ``status``: the device status word; a page id beyond the pool sets its bit 2 and its keys count for nothing."""
+    _need_cuda(q, out, kcache, vcache, token_seq, positions, page_indptr, page_ids, rows, status)
     check_head_dim(head_dim)
     _need(out.is_contiguous() and out.shape[1] == n_heads * head_dim and out.shape[0] >= n_rows, "attn_paged: out")
     _need(kcache.dtype == q.dtype == out.dtype, "attn_paged: dtypes")
@@ -338,7 +354,8 @@ def attn_paged(q: torch.Tensor, q_stride: int, out: torch.Tensor, kcache: torch.
     f = _fn(_libs.get("attention_simt.cu", TKB_HD=head_dim), f"tkb_attn_paged_simt_{_suffix(q.dtype)}")
     _check(f(_ptr(q), c_int(q_stride), _ptr(out), c_int(out.shape[1]), _ptr(kcache), _ptr(vcache), _ptr(token_seq),
              _ptr(positions), _ptr(page_indptr), _ptr(page_ids), _ptr(rows), c_int(n_rows), c_int(n_heads),
-             c_int(n_kv_heads), c_int(page_size), c_float(scale), c_int(window or 0), _stream()), "attn_paged")
+             c_int(n_kv_heads), c_int(page_size), c_float(scale), c_int(window or 0), c_int(kcache.shape[0]), _ptr(status),
+             _stream()), "attn_paged")
 
 
 _COUNTERS: dict = {}
@@ -366,14 +383,14 @@ def attn_decode_mma(qkv: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tenso
                     n_dec: torch.Tensor, dec_cap: int, out: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int,
                     page_size: int, scale: float, window: int | None,
                     out_row_of: torch.Tensor | None = None, item_entry: torch.Tensor | None = None,
-                    tma: bool = True) -> None:
+                    tma: bool = True, status: torch.Tensor | None = None) -> None:
     """bfloat16 split-key attention for requests that bring one token: ``items`` are (request row,
     first key, number of keys) triples, computed into float32 partial results and merged into
     ``out`` [T, n_heads*head_dim] at each request's token row (or at row ``out_row_of[request]``).
     ``n_items``/``n_dec`` are device counters; the launch grids are sized by ``items_cap``/``dec_cap``.
     ``tma``: some work item is longer than three tiles (the kernel variant that fetches tiles by TMA pays)."""
     _need_cuda(qkv, kcache, vcache, seq_q_start, seq_kv_len, page_indptr, page_ids, items, n_items, dec_seqs,
-               dec_item_start, n_dec, out)
+               dec_item_start, n_dec, out, status)
     check_head_dim(head_dim)
     _need(qkv.dtype == torch.bfloat16 and kcache.dtype == torch.bfloat16 and out.dtype == torch.bfloat16,
           "attn_decode_mma: bfloat16 only")
@@ -391,15 +408,15 @@ def attn_decode_mma(qkv: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tenso
             _ptr(seq_q_start), _ptr(seq_kv_len), _ptr(page_indptr), _ptr(page_ids), _ptr(items), _ptr(n_items),
             c_int(items_cap), _ptr(part_o), _ptr(part_ml), c_int(n_heads), c_int(n_kv_heads), c_int(page_size),
             c_float(scale), c_int(window or 0), c_int(0), _ptr(None), c_int(0), c_int(0), c_int(kcache.shape[0]),
-            c_int(1 if tma else 0), _ptr(None), _ptr(counters), _ptr(item_entry), _ptr(dec_item_start),
-            _ptr(out_row_of if out_row_of is not None else seq_q_start), _ptr(out), c_int(out.shape[1]), _stream()),
-            "attn_decode_merged")
+            c_int(1 if tma else 0), _ptr(status), _ptr(counters), _ptr(item_entry), _ptr(dec_item_start),
+            _ptr(out_row_of if out_row_of is not None else seq_q_start), _ptr(out), c_int(out.shape[1]), _ptr(None),
+            _ptr(None), c_float(0.0), _stream()), "attn_decode_merged")
         return
     _check(_fn(lib, "tkb_attn_decode_mma_bf16")(
         _ptr(qkv), c_int(qkv.shape[1]), _ptr(kcache), _ptr(vcache), _ptr(seq_q_start), _ptr(seq_kv_len),
         _ptr(page_indptr), _ptr(page_ids), _ptr(items), _ptr(n_items), c_int(items_cap), _ptr(part_o), _ptr(part_ml),
         c_int(n_heads), c_int(n_kv_heads), c_int(page_size), c_float(scale), c_int(window or 0),
-        _stream()), "attn_decode_mma")
+        c_int(kcache.shape[0]), _ptr(status), _stream()), "attn_decode_mma")
     _check(_fn(lib, "tkb_attn_decode_merge_bf16")(
         _ptr(part_o), _ptr(part_ml), _ptr(dec_seqs), _ptr(dec_item_start), _ptr(n_dec), c_int(dec_cap),
         _ptr(out_row_of if out_row_of is not None else seq_q_start), _ptr(out), c_int(out.shape[1]), c_int(n_heads),
@@ -413,14 +430,16 @@ def attn_decode_rope_mma(qkv: torch.Tensor, kcache: torch.Tensor, vcache: torch.
                          n_heads: int, n_kv_heads: int, head_dim: int, page_size: int, scale: float,
                          window: int | None, inv_freq: torch.Tensor | None, rotary_dim: int,
                          write_cache: bool, status: torch.Tensor, item_entry: torch.Tensor | None = None,
-                         tma: bool = True) -> None:
+                         tma: bool = True, bias: torch.Tensor | None = None, qk_norm: torch.Tensor | None = None,
+                         norm_eps: float = 0.0) -> None:
     """``attn_decode_mma`` with rotary encoding and the cache write folded in: ``qkv`` holds the step's
     un-rotated q|k|v rows of requests that bring one token each, as bfloat16 [T, C] or as the float32 slices
     [slices, T, C] of a K-split product (``linear_smallm``); C = (n_heads + 2 n_kv_heads) * head_dim."""
     _need_cuda(qkv, kcache, vcache, seq_q_start, seq_kv_len, page_indptr, page_ids, items, n_items, dec_seqs,
-               dec_item_start, n_dec, out, inv_freq, status)
+               dec_item_start, n_dec, out, inv_freq, status, bias, qk_norm)
     check_head_dim(head_dim)
     C = (n_heads + 2 * n_kv_heads) * head_dim
+    _check_qkv_stage(bias, qk_norm, C, head_dim)
     _need(kcache.dtype == torch.bfloat16 and out.dtype == torch.bfloat16, "attn_decode_rope_mma: bfloat16 only")
     _need(qkv.is_contiguous() and qkv.shape[-1] == C, "attn_decode_rope_mma: qkv")
     if qkv.dim() == 3:
@@ -447,8 +466,8 @@ def attn_decode_rope_mma(qkv: torch.Tensor, kcache: torch.Tensor, vcache: torch.
             c_int(page_size), c_float(scale), c_int(window or 0), c_int(1), _ptr(inv_freq),
             c_int(rotary_dim), c_int(1 if write_cache else 0), c_int(kcache.shape[0]), c_int(1 if tma else 0),
             _ptr(status), _ptr(counters),
-            _ptr(item_entry), _ptr(dec_item_start), _ptr(seq_q_start), _ptr(out), c_int(out.shape[1]), _stream()),
-            "attn_decode_merged")
+            _ptr(item_entry), _ptr(dec_item_start), _ptr(seq_q_start), _ptr(out), c_int(out.shape[1]), _ptr(bias),
+            _ptr(qk_norm), c_float(norm_eps), _stream()), "attn_decode_merged")
         return
     _check(_fn(lib, "tkb_attn_decode_rope_mma_bf16")(
         _ptr(qkv_ptr), c_int(C), _ptr(parts), c_int(n_parts), ctypes.c_longlong(part_stride), _ptr(kcache),
@@ -456,7 +475,8 @@ def attn_decode_rope_mma(qkv: torch.Tensor, kcache: torch.Tensor, vcache: torch.
         _ptr(page_indptr), _ptr(page_ids), _ptr(items), _ptr(n_items), c_int(items_cap), _ptr(part_o), _ptr(part_ml),
         c_int(n_heads), c_int(n_kv_heads), c_int(page_size), c_float(scale), c_int(window or 0),
         _ptr(inv_freq), c_int(rotary_dim), c_int(1 if write_cache else 0), c_int(kcache.shape[0]),
-        c_int(1 if tma else 0), _ptr(status), _stream()), "attn_decode_rope_mma")
+        c_int(1 if tma else 0), _ptr(status), _ptr(bias), _ptr(qk_norm), c_float(norm_eps), _stream()),
+        "attn_decode_rope_mma")
     _check(_fn(lib, "tkb_attn_decode_merge_bf16")(
         _ptr(part_o), _ptr(part_ml), _ptr(dec_seqs), _ptr(dec_item_start), _ptr(n_dec), c_int(dec_cap),
         _ptr(seq_q_start), _ptr(out), c_int(out.shape[1]), c_int(n_heads), _stream()), "attn_decode_merge")
@@ -466,7 +486,7 @@ def attn_prefill_mma(qkv: torch.Tensor, out: torch.Tensor, kcache: torch.Tensor,
                      seq_q_start: torch.Tensor, seq_q_len: torch.Tensor, seq_kv_len: torch.Tensor,
                      page_indptr: torch.Tensor, page_ids: torch.Tensor, tiles: torch.Tensor, n_tiles: torch.Tensor,
                      tiles_cap: int, n_heads: int, n_kv_heads: int, head_dim: int, page_size: int, scale: float,
-                     window: int | None) -> None:
+                     window: int | None, status: torch.Tensor | None = None) -> None:
     """bfloat16 causal attention for prompt portions: ``tiles`` are (request row, first query of a
     64-query tile within the portion) pairs; results go to ``out`` [T, n_heads*head_dim] at the token rows."""
     _need_cuda(qkv, out, kcache, vcache, seq_q_start, seq_q_len, seq_kv_len, page_indptr, page_ids, tiles, n_tiles)
@@ -481,7 +501,7 @@ def attn_prefill_mma(qkv: torch.Tensor, out: torch.Tensor, kcache: torch.Tensor,
         _ptr(qkv), c_int(qkv.shape[1]), _ptr(out), c_int(out.shape[1]), _ptr(kcache), _ptr(vcache), _ptr(seq_q_start),
         _ptr(seq_q_len), _ptr(seq_kv_len), _ptr(page_indptr), _ptr(page_ids), _ptr(tiles), _ptr(n_tiles),
         c_int(tiles_cap), c_int(n_heads), c_int(n_kv_heads), c_int(page_size), c_float(scale), c_int(window or 0),
-        _stream()), "attn_prefill_mma")
+        c_int(kcache.shape[0]), _ptr(status), _stream()), "attn_prefill_mma")
 
 
 ATTN_PREFILL_TC = True  # portions of prompts on the tcgen05 kernels where one takes the head size

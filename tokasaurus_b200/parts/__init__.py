@@ -1,11 +1,11 @@
 from tokasaurus_b200.parts.base import (  # noqa: F401
     FeedForward,
-    LazyNorm,
     Mixer,
     Norm,
     PagedCacheNeed,
     Part,
     PositionEncoding,
+    QkvStage,
     ResidualStream,
     StateNeed,
     WeightSpec,

@@ -23,21 +23,24 @@ import numpy as np
 import torch
 
 from tokasaurus_b200.kernels import ops
-from tokasaurus_b200.parts.base import LazyNorm, Mixer, PagedCacheNeed, PositionEncoding, WeightSpec
+from tokasaurus_b200.parts.base import Mixer, PagedCacheNeed, PositionEncoding, QkvStage, WeightSpec
 
 MIN_SPLIT_KEYS = 128  # no work item of the split-key kernel is cut finer than this
 QUERY_TILE = 64  # queries per block of the tiled mma.sync kernel
 QUERY_TILE_TC = 128  # queries per block of the tcgen05 kernel
-DECODE_BLOCK_SLOTS = 148 * 3  # blocks of the split-key kernel that a B200 holds at once (head sizes up to 64)
-
-
-def decode_block_slots(head_dim: int) -> int:
-    """Blocks of the split-key kernel that the GPU holds at once: what of an SM's 227 KiB of shared memory the
-    kernel's stages take (two tiles of 64 rows a stage, rows of head_dim * 2 bytes, padded by 16 where the head
-    size is no multiple of 64; three stages, two when three pass 110 KiB), at most three blocks an SM."""
+def decode_block_slots(head_dim: int, limits=None) -> int:
+    """Blocks of the split-key kernel that the GPU holds at once: what of an SM's shared memory the kernel's
+    stages take (two tiles of 64 rows a stage, rows of head_dim * 2 bytes, padded by 16 where the head size is
+    no multiple of 64; three stages, two when three pass 110 KiB), at most three blocks an SM.  ``limits``: the
+    device's SM count and shared memory (``kernels.device.DeviceLimits``; None: planning without a device)."""
+    if limits is None:
+        from tokasaurus_b200.kernels.device import NO_DEVICE as limits
     stage = 2 * 64 * (head_dim * 2 + (0 if head_dim % 64 == 0 else 16))
     stages = 3 if 3 * stage <= 110 * 1024 else 2
-    return 148 * max(1, min(3, (227 * 1024) // (stages * stage + 2048)))
+    return limits.sm_count * max(1, min(3, limits.shared_memory_per_sm // (stages * stage + 2048)))
+
+
+DECODE_BLOCK_SLOTS = decode_block_slots(64)  # the default of the planning functions below
 
 
 def split_keys_evenly(span: np.ndarray, blocks_per_item: int, slots: int = DECODE_BLOCK_SLOTS
@@ -139,12 +142,12 @@ def plan_attention(host, window: int | None, capacity: dict | None = None, block
 
 class PagedAttention(Mixer):
     graph_safe = True
-    takes_lazy_norm = True
-    adds_residual = True
 
     def __init__(self, width: int, n_heads: int, n_kv_heads: int, head_dim: int, position: PositionEncoding,
                  q_name: str, k_name: str, v_name: str, o_name: str, window: int | None = None,
-                 softmax_scale: float | None = None):
+                 softmax_scale: float | None = None, qkv_stage: QkvStage | None = None):
+        """``qkv_stage``: an element-wise stage between the projections and the position encoding (biases, per-head
+        norms; ``parts.base.QkvStage``).  Llama has none."""
         if n_heads % n_kv_heads:
             raise ValueError(f"n_heads={n_heads} is not a multiple of n_kv_heads={n_kv_heads}")
         ops.check_head_dim(head_dim)
@@ -156,21 +159,33 @@ class PagedAttention(Mixer):
         self.window = window
         self.scale = float(softmax_scale) if softmax_scale is not None else ops.softmax_scale(head_dim)
         self.names = (q_name, k_name, v_name, o_name)
+        self.qkv_stage = qkv_stage
+        self.qkv_bias: torch.Tensor | None = None   # float32 [(heads + 2 kv heads) * head_dim]
+        self.qk_norm: torch.Tensor | None = None    # float32 [2, head_dim]
+        self.norm_eps = float(qkv_stage.norm_eps) if qkv_stage is not None else 0.0
         self.w_qkv: torch.Tensor | None = None
         self.w_o: torch.Tensor | None = None
         self.inv_freq: torch.Tensor | None = None
         self.dtype: torch.dtype | None = None
+        self.block_slots = decode_block_slots(head_dim)  # bind() asks the device
 
     # --- declarations ---
     def weight_specs(self):
         q, k, v, o = self.names
         hd = self.head_dim
-        return (
+        specs = [
             WeightSpec(q, (self.n_heads * hd, self.width)),
             WeightSpec(k, (self.n_kv_heads * hd, self.width)),
             WeightSpec(v, (self.n_kv_heads * hd, self.width)),
             WeightSpec(o, (self.width, self.n_heads * hd)),
-        )
+        ]
+        st = self.qkv_stage
+        if st is not None and st.bias_names is not None:
+            for name, heads in zip(st.bias_names, (self.n_heads, self.n_kv_heads, self.n_kv_heads)):
+                specs.append(WeightSpec(name, (heads * hd,), role="vector"))
+        if st is not None and st.qk_norm_names is not None:
+            specs += [WeightSpec(name, (hd,), role="vector") for name in st.qk_norm_names]
+        return tuple(specs)
 
     def cache_need(self):
         return PagedCacheNeed(self.n_kv_heads, self.head_dim, self.window)
@@ -179,9 +194,15 @@ class PagedAttention(Mixer):
         q, k, v, o = self.names
         self.w_qkv = torch.cat([weights[q], weights[k], weights[v]], dim=0).contiguous()
         self.w_o = weights[o].contiguous()
+        st = self.qkv_stage
+        if st is not None and st.bias_names is not None:
+            self.qkv_bias = torch.cat([weights[n].float() for n in st.bias_names]).contiguous()
+        if st is not None and st.qk_norm_names is not None:
+            self.qk_norm = torch.stack([weights[n].float() for n in st.qk_norm_names]).contiguous()
         inv = self.position.inv_freq() if self.position.kind == "rotary" else None
         self.inv_freq = inv.to(rt.device) if inv is not None else None
         self.dtype = rt.dtype
+        self.block_slots = decode_block_slots(self.head_dim, getattr(rt, "limits", None))
 
     def plan_key(self):
         if self.dtype != torch.bfloat16:
@@ -196,19 +217,19 @@ class PagedAttention(Mixer):
 
     def plan(self, host, capacity=None):
         return plan_attention(host, self.window, capacity, self._blocks_per_item(), self._query_tile(),
-                              decode_block_slots(self.head_dim))
+                              self.block_slots)
 
     def plan_capacity(self, n_requests: int) -> dict:
         """The most work items ``plan`` can make for a step of ``n_requests`` single-token requests, whatever
         their contexts: each request gets at most (its keys // the item size) items, at least one."""
-        wave = max(1, decode_block_slots(self.head_dim) // max(1, self._blocks_per_item()))
+        wave = max(1, self.block_slots // max(1, self._blocks_per_item()))
         return dict(items=n_requests + wave + wave // 4 + 1, dec=n_requests, tiles=0)
 
     def plan_capacity_general(self, n_tokens: int, n_requests: int, n_rows: int, counts) -> dict:
         """Capacities of every work list for a step of up to ``n_tokens`` tokens in ``n_requests`` requests with
         ``n_rows`` wanted rows; a list the step does not use at all (``counts`` are the plan's own) gets 0, so that
         its kernel is not launched."""
-        wave = max(1, decode_block_slots(self.head_dim) // max(1, self._blocks_per_item()))
+        wave = max(1, self.block_slots // max(1, self._blocks_per_item()))
         spare = wave + wave // 4 + 1
         has_dec, has_tiles, has_rows = int(counts[1]) > 0, int(counts[2]) > 0, int(counts[4]) > 0
         return dict(items=(n_requests + spare) if has_dec else 0, dec=n_requests if has_dec else 0,
@@ -238,35 +259,13 @@ class PagedAttention(Mixer):
         return out
 
     # --- one step ---
-    def forward(self, ctx, h, cache, out_rows=None, residual: torch.Tensor | None = None):
+    def forward(self, ctx, h, cache, out_rows=None):
         T = h.shape[0]
         hd, nh, nkv = self.head_dim, self.n_heads, self.n_kv_heads
         tables = ctx.tables[cache.group]
         rot = self.position.rotary_dim if self.position.kind == "rotary" else 0
-        if isinstance(h, LazyNorm):
-            plan = ctx.plans.get(self.plan_key())
-            counts = ctx.host_plans[self.plan_key()]["counts"] if plan is not None else None
-            if (plan is not None and out_rows is None and int(counts[2]) == 0 and int(counts[1]) > 0 and rot % 4 == 0
-                    and ops.can_use_linear_decode(h.x, self.w_qkv) and (nh * hd) % 8 == 0):
-                # every request brings one token: norm + q|k|v product, then rotary + cache write +
-                # split-key attention, merge, output product + residual add: four kernels
-                qkv = ops.linear_decode(h.x, self.w_qkv, "bf16", h.weight, h.eps)
-                attn = torch.empty((T, nh * hd), dtype=qkv.dtype, device=qkv.device)
-                caps = ctx.plan_caps.get(self.plan_key()) if ctx.plan_caps else None
-                c = plan["counts"]
-                ops.attn_decode_rope_mma(qkv, cache.k, cache.v, ctx.seq_q_start, ctx.seq_kv_len, tables.indptr,
-                                         tables.page_ids, plan["items"], c[0:1], caps["items"] if caps else int(counts[0]),
-                                         plan["dec_seqs"], plan["dec_item_start"], c[1:2],
-                                         caps["dec"] if caps else int(counts[1]), attn, nh, nkv, hd, cache.page_size,
-                                         self.scale, self.window, self.inv_freq, rot, cache.writable,
-                                         ctx.status, item_entry=plan["item_entry"], tma=bool(counts[5]))
-                if residual is not None:
-                    ops.linear_decode(attn, self.w_o, "add", out=residual)
-                    return None
-                return ops.linear_decode(attn, self.w_o, "bf16")
-            h = h.materialize()
         small = (ops.can_use_few_rows(h, self.w_qkv, ops.ATTN_FEW_ROWS_MAX) and (nh * hd) % 8 == 0
-                 and (self.w_qkv.shape[0] + max(rot, 2)) * 4 <= 48 * 1024)
+                 and (self.w_qkv.shape[0] + max(rot, 2)) * 4 <= 160 * 1024)
         few = lambda a, w: ops.linear_few_rows(a, w, ctx.status)  # noqa: E731
         if small:
             # few rows: K-split products whose float32 slices the next kernel adds
@@ -283,17 +282,19 @@ class PagedAttention(Mixer):
                                          plan["dec_seqs"], plan["dec_item_start"], c[1:2],
                                          caps["dec"] if caps else int(counts[1]), attn, nh, nkv, hd, cache.page_size,
                                          self.scale, self.window, self.inv_freq, rot, cache.writable,
-                                         ctx.status, item_entry=plan["item_entry"], tma=bool(counts[5]))
+                                         ctx.status, item_entry=plan["item_entry"], tma=bool(counts[5]),
+                                         bias=self.qkv_bias, qk_norm=self.qk_norm, norm_eps=self.norm_eps)
                 return few(attn, self.w_o)
             qkv = torch.empty((T, nh * hd), dtype=h.dtype, device=h.device)  # q only; k and v go straight to the cache
             ops.rope_kv_write_partials(parts, qkv, ctx.positions, ctx.token_seq, tables.indptr, tables.page_ids,
                                        self.inv_freq, cache.k, cache.v, nh, nkv, hd, rot, cache.page_size,
-                                       cache.writable, ctx.status)
+                                       cache.writable, ctx.status, bias=self.qkv_bias, qk_norm=self.qk_norm, norm_eps=self.norm_eps)
             project = few
         else:
             qkv = ops.linear(h, self.w_qkv)
             ops.rope_kv_write(qkv, ctx.positions, ctx.token_seq, tables.indptr, tables.page_ids, self.inv_freq,
-                              cache.k, cache.v, nh, nkv, hd, rot, cache.page_size, cache.writable, ctx.status)
+                              cache.k, cache.v, nh, nkv, hd, rot, cache.page_size, cache.writable, ctx.status,
+                              bias=self.qkv_bias, qk_norm=self.qk_norm, norm_eps=self.norm_eps)
             project = ops.linear
         plan = ctx.plans.get(self.plan_key()) if h.dtype == torch.bfloat16 else None
         if plan is not None and out_rows is not None and out_rows is ctx.logit_rows and "row_items" in plan:
@@ -309,14 +310,15 @@ class PagedAttention(Mixer):
                                 tables.page_ids, plan["row_items"], c[3:4], n_items, plan["row_index"],
                                 plan["row_item_start"], c[4:5], n_rows, attn, nh, nkv, hd, cache.page_size,
                                 self.scale, self.window, out_row_of=plan["row_index"],
-                                item_entry=plan["row_item_entry"], tma=bool(counts[6]))
+                                item_entry=plan["row_item_entry"], tma=bool(counts[6]), status=ctx.status)
             return project(attn, self.w_o)
         if plan is None or out_rows is not None:
             # float32, or only some rows are wanted: the FP32-pipe kernel, one warp per (row, head)
             n_rows = T if out_rows is None else out_rows.numel()
             attn = torch.empty((n_rows, nh * hd), dtype=h.dtype, device=h.device)
             ops.attn_paged(qkv, qkv.shape[1], attn, cache.k, cache.v, ctx.token_seq, ctx.positions, tables.indptr,
-                           tables.page_ids, out_rows, n_rows, nh, nkv, hd, cache.page_size, self.scale, self.window)
+                           tables.page_ids, out_rows, n_rows, nh, nkv, hd, cache.page_size, self.scale, self.window,
+                           ctx.status)
             return project(attn, self.w_o)
         attn = torch.empty((T, nh * hd), dtype=h.dtype, device=h.device)
         caps = ctx.plan_caps.get(self.plan_key()) if ctx.plan_caps else None
@@ -329,7 +331,7 @@ class PagedAttention(Mixer):
             ops.attn_decode_mma(qkv, cache.k, cache.v, ctx.seq_q_start, ctx.seq_kv_len, tables.indptr, tables.page_ids,
                                 plan["items"], c[0:1], items_cap, plan["dec_seqs"], plan["dec_item_start"], c[1:2],
                                 dec_cap, attn, nh, nkv, hd, cache.page_size, self.scale, self.window,
-                                item_entry=plan["item_entry"], tma=bool(counts[5]))
+                                item_entry=plan["item_entry"], tma=bool(counts[5]), status=ctx.status)
         if tiles_cap and self._query_tile() == QUERY_TILE_TC:
             ops.attn_prefill_tc(qkv, attn, cache.k, cache.v, ctx.seq_q_start, ctx.seq_q_len, ctx.seq_kv_len,
                                 tables.indptr, tables.page_ids, plan["tiles"], c[2:3], tiles_cap, nh, nkv, hd,
@@ -337,5 +339,5 @@ class PagedAttention(Mixer):
         elif tiles_cap:
             ops.attn_prefill_mma(qkv, attn, cache.k, cache.v, ctx.seq_q_start, ctx.seq_q_len, ctx.seq_kv_len,
                                  tables.indptr, tables.page_ids, plan["tiles"], c[2:3], tiles_cap, nh, nkv, hd,
-                                 cache.page_size, self.scale, self.window)
+                                 cache.page_size, self.scale, self.window, ctx.status)
         return project(attn, self.w_o)

@@ -59,6 +59,21 @@ class StateNeed:
     dtype: str = "float32"
 
 
+@dataclass(frozen=True)
+class QkvStage:
+    """An element-wise stage between "q|k|v ready" and the position encoding of an attention mixer, for
+    architectures whose projections carry a bias or whose heads are normalised.  The attention kernels honour it
+    on every path, the fused decode path included: a mixer that needs one of these gives up no fast path.
+
+    ``bias_names``: tensors (q bias [heads*head_dim], k bias and v bias [kv heads*head_dim]) added to the
+    projections.  ``qk_norm_names``: tensors [head_dim] by which every q head / every k head is scaled after an
+    RMS norm over the head size (statistics in 32-bit, ``norm_eps``)."""
+
+    bias_names: tuple[str, str, str] | None = None
+    qk_norm_names: tuple[str, str] | None = None
+    norm_eps: float = 1e-6
+
+
 class Part:
     def weight_specs(self) -> Sequence[WeightSpec]:
         return ()
@@ -68,24 +83,10 @@ class Part:
         device and in the dtype their role asks for."""
 
 
-class LazyNorm:
-    """A norm that has not run yet: the float32 rows ``x``, the norm's ``weight`` and ``eps``.  A part
-    that can fold the norm into its first matrix product (``takes_lazy_norm = True``) reads these; any
-    other part is given ``materialize()``, the normalised rows in the engine's dtype."""
-
-    def __init__(self, x: "torch.Tensor", weight: "torch.Tensor", eps: float, out_dtype: "torch.dtype", run):
-        self.x, self.weight, self.eps, self.dtype, self._run = x, weight, eps, out_dtype, run
-        self.shape = x.shape
-        self.device = x.device
-
-    def materialize(self) -> "torch.Tensor":
-        return self._run(self.x)
-
-
 class Norm(Part):
-    def forward(self, ctx: "StepContext", stream: "ResidualStream", lazy_ok: bool = False):
+    def forward(self, ctx: "StepContext", stream: "ResidualStream"):
         """Fold the stream's pending update into it and return the normalised rows [T, width]
-        in the engine's dtype; with ``lazy_ok`` the norm may hand back a ``LazyNorm`` instead."""
+        in the engine's dtype."""
         raise NotImplementedError
 
 
@@ -95,25 +96,11 @@ class PositionEncoding:
     kind: str = "none"
 
 
-def run_norm(norm: "Norm", ctx, stream: "ResidualStream", lazy_ok: bool):
-    """Run a norm for a consumer; a LazyNorm may come back only if ``lazy_ok`` and the norm offers it."""
-    if lazy_ok:
-        try:
-            return norm.forward(ctx, stream, lazy_ok=True)
-        except TypeError:  # a norm written without the lazy_ok argument
-            pass
-    return norm.forward(ctx, stream)
-
-
 class Mixer(Part):
     # True if ``forward`` only launches work on the current stream and reads nothing of the step on
     # the host that could change between two steps of the same shape: such a step can be replayed
     # from a CUDA graph.
     graph_safe = False
-    # The block may pass a LazyNorm as ``h`` / pass ``residual=`` (the float32 rows to add the result to;
-    # the part then returns None) to parts that declare so.
-    takes_lazy_norm = False
-    adds_residual = False
 
     def cache_need(self) -> PagedCacheNeed | StateNeed | None:
         return None
@@ -144,9 +131,6 @@ class Mixer(Part):
 
 
 class FeedForward(Part):
-    takes_lazy_norm = False
-    adds_residual = False
-
     def forward(self, ctx: "StepContext", h: "torch.Tensor") -> "torch.Tensor":
         raise NotImplementedError
 

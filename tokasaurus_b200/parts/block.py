@@ -8,7 +8,7 @@ from __future__ import annotations
 import torch
 
 from tokasaurus_b200.kernels import ops
-from tokasaurus_b200.parts.base import FeedForward, Mixer, Norm, Part, ResidualStream, run_norm
+from tokasaurus_b200.parts.base import FeedForward, Mixer, Norm, Part, ResidualStream
 
 
 class PreNormBlock(Part):
@@ -32,23 +32,12 @@ class PreNormBlock(Part):
         """``out_rows`` (int32 device tensor or None): only these rows are needed after the mixer
         (the last block of a step: tokasaurus/model/llama.py:273-278); the stream that comes back
         then has len(out_rows) rows."""
-        h = self._normed(self.mixer_norm, ctx, stream, self.mixer)
+        h = self.mixer_norm.forward(ctx, stream)
         if out_rows is not None:
             x = torch.empty((out_rows.numel(), stream.x.shape[1]), dtype=stream.x.dtype, device=stream.x.device)
             ops.gather_rows(stream.x, out_rows, x)
             stream = ResidualStream(x)
-        if getattr(self.mixer, "adds_residual", False):
-            stream.delta = self.mixer.forward(ctx, h, cache, out_rows, residual=stream.x)
-        else:
-            stream.delta = self.mixer.forward(ctx, h, cache, out_rows)
-        h = self._normed(self.ffn_norm, ctx, stream, self.ffn)
-        if getattr(self.ffn, "adds_residual", False):
-            stream.delta = self.ffn.forward(ctx, h, residual=stream.x)
-        else:
-            stream.delta = self.ffn.forward(ctx, h)
+        stream.delta = self.mixer.forward(ctx, h, cache, out_rows)
+        h = self.ffn_norm.forward(ctx, stream)
+        stream.delta = self.ffn.forward(ctx, h)
         return stream
-
-    @staticmethod
-    def _normed(norm, ctx, stream, consumer):
-        """The consumer's input: a LazyNorm only for consumers that say they take one."""
-        return run_norm(norm, ctx, stream, getattr(consumer, "takes_lazy_norm", False))

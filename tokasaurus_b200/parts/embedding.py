@@ -6,7 +6,7 @@ from __future__ import annotations
 import torch
 
 from tokasaurus_b200.kernels import ops
-from tokasaurus_b200.parts.base import LazyNorm, Norm, Part, ResidualStream, WeightSpec, run_norm
+from tokasaurus_b200.parts.base import Norm, Part, ResidualStream, WeightSpec
 
 
 class TokenEmbedding(Part):
@@ -47,9 +47,5 @@ class OutputHead(Part):
         self.weight = weights[self.weight_name]
 
     def forward(self, ctx, stream: ResidualStream) -> torch.Tensor:
-        h = run_norm(self.norm, ctx, stream, True)
-        if isinstance(h, LazyNorm):
-            if ops.can_use_linear_decode(h.x, self.weight):
-                return ops.linear_decode(h.x, self.weight, "f32", h.weight, h.eps)
-            h = h.materialize()
+        h = self.norm.forward(ctx, stream)
         return ops.linear(h, self.weight, out_dtype=torch.float32)

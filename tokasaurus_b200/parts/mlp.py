@@ -7,13 +7,10 @@ from __future__ import annotations
 import torch
 
 from tokasaurus_b200.kernels import ops
-from tokasaurus_b200.parts.base import FeedForward, LazyNorm, WeightSpec
+from tokasaurus_b200.parts.base import FeedForward, WeightSpec
 
 
 class GatedMLP(FeedForward):
-    takes_lazy_norm = True
-    adds_residual = True
-
     def __init__(self, width: int, inner: int, gate_name: str, up_name: str, down_name: str):
         self.width = width
         self.inner = inner
@@ -41,18 +38,9 @@ class GatedMLP(FeedForward):
             self.w_gate_up = torch.cat([weights[g], weights[u]], dim=0).contiguous()
         self.w_down = weights[d].contiguous()
 
-    def forward(self, ctx, h, residual: torch.Tensor | None = None):
+    def forward(self, ctx, h):
         """Returns the update [rows, width] in h's dtype, or as float32 slices [slices, rows, width]
-        that the next norm adds (few rows, bfloat16); or None after adding the update to ``residual``
-        (at most 16 rows, bfloat16: norm, both products, gate and residual add in two kernels)."""
-        if isinstance(h, LazyNorm):
-            if self.interleave and ops.can_use_linear_decode(h.x, self.w_gate_up):
-                act = ops.linear_decode(h.x, self.w_gate_up, "gated", h.weight, h.eps)
-                if residual is not None:
-                    ops.linear_decode(act, self.w_down, "add", out=residual)
-                    return None
-                return ops.linear_decode(act, self.w_down, "bf16")
-            h = h.materialize()
+        that the next norm adds (few rows, bfloat16)."""
         status = ctx.status if ctx is not None else None
         if self.interleave and ops.can_use_few_rows(h, self.w_gate_up) and self.w_gate_up.shape[0] % 16 == 0:
             act = ops.linear_few_rows_gated(h, self.w_gate_up, status)

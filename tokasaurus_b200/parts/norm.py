@@ -7,7 +7,7 @@ from __future__ import annotations
 import torch
 
 from tokasaurus_b200.kernels import ops
-from tokasaurus_b200.parts.base import LazyNorm, Norm, ResidualStream, WeightSpec
+from tokasaurus_b200.parts.base import Norm, ResidualStream, WeightSpec
 
 
 class RMSNorm(Norm):
@@ -30,11 +30,7 @@ class RMSNorm(Norm):
         ops.add_rmsnorm(x, delta, self.weight, self.eps, out)
         return out
 
-    def forward(self, ctx, stream: ResidualStream, lazy_ok: bool = False):
-        if (lazy_ok and stream.delta is None and self.out_dtype == torch.bfloat16
-                and 0 < stream.x.shape[0] <= ops.LAZY_NORM_M_MAX and self.width % 8 == 0):
-            # few rows and nothing to add: let the consumer fold the norm into its matrix product
-            return LazyNorm(stream.x, self.weight, self.eps, self.out_dtype, self._run)
+    def forward(self, ctx, stream: ResidualStream):
         out = self._run(stream.x, stream.delta)
         stream.delta = None
         return out
