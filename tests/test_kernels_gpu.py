@@ -269,7 +269,7 @@ def test_rope_kv_write_with_the_elementwise_stage(ops, dtype, hd, rot, nh, nkv, 
     block (more tokens than blocks the GPU holds would take too long here: the walk over tokens is the same)."""
     from tokasaurus_b200.parts.rope import RotaryEncoding
 
-    T, n_pages = 300, 64
+    T, n_pages = 300, 128
     g = torch.Generator().manual_seed(hd + nh)
     C = (nh + 2 * nkv) * hd
     qkv = torch.randn(T, C, generator=g).to(dtype).to(DEV)

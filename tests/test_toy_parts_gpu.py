@@ -169,7 +169,7 @@ def test_routed_feed_forward_and_learned_positions(tmp_path, dtype):
 # entry", and it keeps every fast path: the decode steps below still run the fused rotary + cache write +
 # split-key attention kernel, and the portions the tcgen05 kernel (heads of 64).
 
-QKN = dict(architectures=["ToyQkNormLM"], width=128, vocab_size=113, inner=96, heads=4, kv_heads=2, layers=2, eps=1e-5,
+QKN = dict(architectures=["ToyQkNormLM"], width=256, vocab_size=113, inner=96, heads=4, kv_heads=2, layers=2, eps=1e-5,
            qk_eps=1e-6, theta=10000.0)
 
 
