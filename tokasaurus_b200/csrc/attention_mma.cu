@@ -114,20 +114,20 @@ struct KvTileLoad {
   int page[ITERS];  // page of each row this thread copies; -1: the row is outside the keys wanted
 
   __device__ __forceinline__ void lookup(const int* __restrict__ table, int ps, int key_base, int key_lo, int key_hi,
-                                         int tid, int num_pages, int* status) {
+                                         int tid) {
     const int ps_shift = (ps & (ps - 1)) == 0 ? 31 - __clz(ps) : -1;  // page sizes that are powers of two: shifts
 #pragma unroll
     for (int i = 0; i < ITERS; i++) {
       const int idx = tid + i * NTHREADS;
       const int key = key_base + idx / CPR;
       page[i] = -1;
-      if (idx < KT * CPR && key >= key_lo && key < key_hi)
-        page[i] = checked_page(table[ps_shift >= 0 ? key >> ps_shift : key / ps], num_pages, status);
+      // (checked against the pool in issue(), when the value is needed: a check here would wait for the load)
+      if (idx < KT * CPR && key >= key_lo && key < key_hi) page[i] = table[ps_shift >= 0 ? key >> ps_shift : key / ps];
     }
   }
   __device__ __forceinline__ void issue(unsigned char* stage, const bf16* __restrict__ kcache,
                                         const bf16* __restrict__ vcache, int kvh, int nkv, int ps, int key_base,
-                                        int tid) const {
+                                        int tid, int num_pages, bool& bad_page) const {
     const uint32_t sk = smem_u32(stage), sv = sk + TILE_B;
     const int ps_shift = (ps & (ps - 1)) == 0 ? 31 - __clz(ps) : -1;
 #pragma unroll
@@ -137,8 +137,9 @@ struct KvTileLoad {
         const int r = idx / CPR, c = idx - r * CPR;
         const int key = key_base + r;
         const int slot = ps_shift >= 0 ? key & (ps - 1) : key % ps;
-        const bool valid = page[i] >= 0;
-        const size_t off = valid ? (((size_t)page[i] * nkv + kvh) * ps + slot) * HD + c * 8 : 0;
+        const int pg = checked_page(page[i], num_pages, bad_page);
+        const bool valid = pg >= 0;
+        const size_t off = valid ? (((size_t)pg * nkv + kvh) * ps + slot) * HD + c * 8 : 0;
         const uint32_t d = tile_off(r, c);
         cp_async16(sk + d, kcache + off, valid);
         cp_async16(sv + d, vcache + off, valid);
@@ -151,10 +152,10 @@ template <int NTHREADS>
 __device__ __forceinline__ void load_kv_tile(unsigned char* stage, const bf16* __restrict__ kcache,
                                              const bf16* __restrict__ vcache, const int* __restrict__ table, int kvh,
                                              int nkv, int ps, int key_base, int key_lo, int key_hi, int tid,
-                                             int num_pages, int* status) {
+                                             int num_pages, bool& bad_page) {
   KvTileLoad<NTHREADS> t;
-  t.lookup(table, ps, key_base, key_lo, key_hi, tid, num_pages, status);
-  t.issue(stage, kcache, vcache, kvh, nkv, ps, key_base, tid);
+  t.lookup(table, ps, key_base, key_lo, key_hi, tid);
+  t.issue(stage, kcache, vcache, kvh, nkv, ps, key_base, tid, num_pages, bad_page);
 }
 
 // S[16 x 16 keys] = Q . K^T for the 16 key rows starting at key_row of the K tile.  s[nt][4], nt = 0, 1.
@@ -337,13 +338,14 @@ attn_decode_mma_kernel(const __grid_constant__ KvMapsParam<TMA> maps, int tma_ro
   __shared__ __align__(8) uint64_t kv_full[DSTAGES];
   const bool use_tma = TMA && SWZ && tma_rows > 0 && (k_begin & (KT - 1)) == 0 && n_tiles > DSTAGES;  // short items gain nothing
   const int ps_shift = 31 - __clz(ps);  // used with TMA only (page sizes that are powers of two)
+  bool bad_page = false;  // a page id beyond the pool was met (its keys read as zeros); reported once, at the end
   auto by_tma = [&](int tile) { return use_tma && k_begin + (tile + 1) * KT <= kv_len; };
   // warp 0: the page of the box that this lane asks for (lanes beyond the tile's boxes ask for nothing)
   const int tma_boxes = use_tma ? KT / tma_rows : 1;
   const int tma_atom = lane / tma_boxes, tma_box = lane - tma_atom * tma_boxes;
   const bool tma_lane = use_tma && warp == 0 && tma_atom < HD / 64;
   auto tma_lookup = [&](int tile) {
-    return tma_lane ? checked_page(table[(k_begin + tile * KT + tma_box * tma_rows) >> ps_shift], num_pages, status) : 0;
+    return tma_lane ? table[(k_begin + tile * KT + tma_box * tma_rows) >> ps_shift] : 0;
   };
   auto tma_issue = [&](int tile, int page) {  // warp 0, all lanes
     unsigned char* stage = smem + (tile % DSTAGES) * STAGE_B;
@@ -352,7 +354,8 @@ attn_decode_mma_kernel(const __grid_constant__ KvMapsParam<TMA> maps, int tma_ro
     __syncwarp();
     if (tma_lane) {
       const int key = k_begin + tile * KT + tma_box * tma_rows;
-      const int row = (page * nkv + kvh) * ps + (key & (ps - 1));
+      // an id beyond the pool becomes -1: a negative row lies outside the tensor map and reads as zeros
+      const int row = (checked_page(page, num_pages, bad_page) * nkv + kvh) * ps + (key & (ps - 1));
       unsigned char* dst = stage + tma_atom * ATOM_B + tma_box * tma_rows * 128;
       if constexpr (TMA) {
         tkb5::tma_load_2d(dst, &maps.k, bar, tma_atom * 64, row);
@@ -376,7 +379,7 @@ attn_decode_mma_kernel(const __grid_constant__ KvMapsParam<TMA> maps, int tma_ro
         if (warp == 0) tma_issue(st, tma_lookup(st));
       } else {
         load_kv_tile<128>(smem + st * STAGE_B, kcache, vcache, table, kvh, nkv, ps, k_begin + st * KT, k_begin, k_end, tid,
-                          num_pages, status);
+                          num_pages, bad_page);
       }
     }
     cp_async_commit();
@@ -536,7 +539,7 @@ attn_decode_mma_kernel(const __grid_constant__ KvMapsParam<TMA> maps, int tma_ro
   auto look_ahead = [&](int tile) {
     if (tile >= n_tiles) return;
     if (by_tma(tile)) ahead_page = tma_lookup(tile);
-    else ahead.lookup(table, ps, k_begin + tile * KT, k_begin, k_end, tid, num_pages, status);
+    else ahead.lookup(table, ps, k_begin + tile * KT, k_begin, k_end, tid);
   };
   look_ahead(DSTAGES - 1);
   bool timed_out = false;
@@ -551,7 +554,8 @@ attn_decode_mma_kernel(const __grid_constant__ KvMapsParam<TMA> maps, int tma_ro
         if (by_tma(nxt)) {
           if (warp == 0) tma_issue(nxt, ahead_page);
         } else {
-          ahead.issue(smem + (nxt % DSTAGES) * STAGE_B, kcache, vcache, kvh, nkv, ps, k_begin + nxt * KT, tid);
+          ahead.issue(smem + (nxt % DSTAGES) * STAGE_B, kcache, vcache, kvh, nkv, ps, k_begin + nxt * KT, tid, num_pages,
+                      bad_page);
         }
       }
       cp_async_commit();
@@ -585,6 +589,7 @@ attn_decode_mma_kernel(const __grid_constant__ KvMapsParam<TMA> maps, int tma_ro
   }
   cp_async_wait<0>();
   if (timed_out && status != nullptr) atomicOr(status, TKB_STATUS_WAIT_TIMEOUT);
+  report_bad_page(bad_page, status);
   __syncthreads();
   // row sums over the four threads of a row
 #pragma unroll
@@ -746,13 +751,14 @@ attn_prefill_mma_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restri
   const int warp_lo = window > 0 ? pos0 + warp * 16 - window + 1 : 0;
 
   const int n_tiles = (k_end - k_begin + KT - 1) / KT;
-  load_kv_tile<128>(smem, kcache, vcache, table, kvh, nkv, ps, k_begin, k_begin, k_end, tid, num_pages, status);
+  bool bad_page = false;
+  load_kv_tile<128>(smem, kcache, vcache, table, kvh, nkv, ps, k_begin, k_begin, k_end, tid, num_pages, bad_page);
   cp_async_commit();
   for (int it = 0; it < n_tiles; it++) {
     unsigned char* cur = smem + (it & 1) * STAGE_B;
     if (it + 1 < n_tiles)
       load_kv_tile<128>(smem + ((it + 1) & 1) * STAGE_B, kcache, vcache, table, kvh, nkv, ps, k_begin + (it + 1) * KT,
-                        k_begin, k_end, tid, num_pages, status);
+                        k_begin, k_end, tid, num_pages, bad_page);
     cp_async_commit();
     cp_async_wait<1>();
     __syncthreads();
@@ -843,6 +849,7 @@ attn_prefill_mma_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restri
       *reinterpret_cast<uint32_t*>(out + (size_t)(t0 + row_b) * out_stride + (size_t)head * HD + col) =
           pack_bf16(o[dt][2] * inv_b, o[dt][3] * inv_b);
   }
+  report_bad_page(bad_page, status);
 }
 
 static bool g_attr_set = false;

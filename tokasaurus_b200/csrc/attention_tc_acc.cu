@@ -96,7 +96,7 @@ __device__ __forceinline__ uint64_t make_desc_mn(uint32_t smem_addr) {
 // are zero.  A warp's lane takes rows lane and lane + 32: their page lookups go out together.
 __device__ __forceinline__ void gather_tile(uint32_t dst, const bf16* __restrict__ cache, const int* __restrict__ table,
                                             int kvh, int nkv, int ps, int ps_shift, int key_base, int key_lo, int key_hi,
-                                            int lane, int num_pages, int* status) {
+                                            int lane, int num_pages, bool& bad_page) {
   size_t off[2];
   bool valid[2];
 #pragma unroll
@@ -107,7 +107,7 @@ __device__ __forceinline__ void gather_tile(uint32_t dst, const bf16* __restrict
     if (valid[i]) {
       const int pi = ps_shift >= 0 ? key >> ps_shift : key / ps;
       const int slot = ps_shift >= 0 ? key & (ps - 1) : key - pi * ps;
-      const int page = checked_page(__ldg(table + pi), num_pages, status);
+      const int page = checked_page(__ldg(table + pi), num_pages, bad_page);
       valid[i] = page >= 0;  // a page given back behind a window, or an id beyond the pool: zeros
       off[i] = valid[i] ? (((size_t)page * nkv + kvh) * ps + slot) * HD : 0;
     }
@@ -270,7 +270,7 @@ attn_prefill_acc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
     unsigned char* ring = is_v ? sV : sK;
     uint64_t* full = is_v ? v_full : k_full;
     uint64_t* empty = is_v ? v_empty : k_empty;
-    bool ok = true;
+    bool ok = true, bad_page = false;
     for (int j = 0; j < n_kv_tiles; j++) {
       const int b = j % KV_STAGES;
       const int key_base = k_begin + j * BKV;
@@ -284,11 +284,11 @@ attn_prefill_acc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
           const int atom = lane / boxes, bx = lane - atom * boxes;
           const int key = key_base + bx * tma_rows;
           // an id beyond the pool becomes -1: a negative row is outside the tensor map and reads as zeros
-          const int row = (checked_page(__ldg(table + (key >> ps_shift)), num_pages, status) * nkv + kvh) * ps + (key & (ps - 1));
+          const int row = (checked_page(__ldg(table + (key >> ps_shift)), num_pages, bad_page) * nkv + kvh) * ps + (key & (ps - 1));
           tma_load_2d(ring + b * KV_BYTES + atom * (BKV * 128) + bx * tma_rows * 128, map, &full[b], atom * 64, row);
         }
       } else {
-        gather_tile(smem_u32(ring + b * KV_BYTES), cache, table, kvh, nkv, ps, ps_shift, key_base, 0, kv_len, lane, num_pages, status);
+        gather_tile(smem_u32(ring + b * KV_BYTES), cache, table, kvh, nkv, ps, ps_shift, key_base, 0, kv_len, lane, num_pages, bad_page);
         cp_async_wait_all();
         fence_proxy_async();
         __syncwarp();
@@ -296,6 +296,7 @@ attn_prefill_acc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
       }
     }
     if (!ok) failed = 1;
+    report_bad_page(bad_page, status);
   } else if (warp >= 10) {
     const int hh = warp - 10;
     if (lane == 0 && hh < n_heads_here) {

@@ -61,6 +61,16 @@ __device__ __forceinline__ int checked_page(int page, int num_pages, int* status
   }
   return page;
 }
+// The same for inner loops: no branch and no atomic there, the caller keeps `bad` in a register and reports it
+// once, at its end, with report_bad_page().
+__device__ __forceinline__ int checked_page(int page, int num_pages, bool& bad) {
+  const bool b = num_pages > 0 && page >= num_pages;
+  bad |= b;
+  return b ? -1 : page;
+}
+__device__ __forceinline__ void report_bad_page(bool bad, int* status) {
+  if (bad && status != nullptr) atomicOr(status, TKB_STATUS_BAD_PAGE);
+}
 
 // Programmatic dependent launch: a kernel launched with `launch_pdl` may start while the kernel
 // before it in the stream is still running.  It must call grid_dependency_wait() before it reads
