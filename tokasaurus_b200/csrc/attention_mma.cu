@@ -386,7 +386,7 @@ attn_decode_mma_kernel(const __grid_constant__ KvMapsParam<TMA> maps, int tma_ro
   }
   // Q fragments: row r of the tile is query head g0 + r; rows >= gn are zero.
   uint32_t qf[KSTEPS][4];
-  __shared__ float cs[FUSED ? HD : 2];               // cos[rot/2], sin[rot/2] of this token's position
+  __shared__ __align__(16) float cs[FUSED ? HD : 2];  // cos[rot/2], sin[rot/2] of this token's position
   __shared__ bf16 knew[FUSED ? HD : 2], vnew[FUSED ? HD : 2];  // the token's own rotated key and its value
   // this split holds position p, and this layer call keeps its own keys (a call that reads another call's cache
   // finds the key at p already there)
@@ -494,32 +494,41 @@ attn_decode_mma_kernel(const __grid_constant__ KvMapsParam<TMA> maps, int tma_ro
       }
     }
   }
+  // Fused: the q rows are rotated ONCE, by all threads together, into a bfloat16 tile in shared memory whose rows
+  // are 4 words longer than the head, so that the fragment loads below (eight rows a warp instruction) fall into
+  // 32 different banks.  (Each thread rotating the fragments it needs straight from the float32 rows cost 1.5 us
+  // of a 17 us kernel: sixteen times the arithmetic, and every load an eight-way bank conflict.)
+  constexpr int SQ_STRIDE = HD / 2 + 4;  // words (two bfloat16 each) from one row to the next
+  __shared__ uint32_t sq[FUSED ? 16 * SQ_STRIDE : 1];
+  if (FUSED) {
+    const int half = rot >> 1;
+    for (int idx = tid; idx < gn * (HD / 2); idx += 128) {
+      const int row = idx / (HD / 2), col = (idx - row * (HD / 2)) * 2;
+      const float* src = srow + row * HD;
+      float2 x = *reinterpret_cast<const float2*>(src + col);
+      if (col < rot) {
+        const bool low = col < half;
+        const int pc = low ? col + half : col - half;   // partner column
+        const int j = low ? col : col - half;           // angle index
+        const float2 y = *reinterpret_cast<const float2*>(src + pc);
+        const float2 c = *reinterpret_cast<const float2*>(cs + j), sn = *reinterpret_cast<const float2*>(cs + half + j);
+        x = low ? make_float2(x.x * c.x - y.x * sn.x, x.y * c.y - y.y * sn.y)
+                : make_float2(x.x * c.x + y.x * sn.x, x.y * c.y + y.y * sn.y);
+      }
+      sq[row * SQ_STRIDE + (col >> 1)] = pack_bf16(x.x, x.y);
+    }
+    __syncthreads();
+  }
   {
     const int r = lane >> 2, cq = (lane & 3) * 2;
-    const int half = rot >> 1;
 #pragma unroll
     for (int ks = 0; ks < KSTEPS; ks++) {
 #pragma unroll
       for (int i = 0; i < 4; i++) {
         const int row = r + (i & 1) * 8, col = ks * 16 + cq + (i >> 1) * 8;
         uint32_t v = 0u;
-        if (row < gn) {
-          if (!FUSED) {
-            v = *reinterpret_cast<const uint32_t*>(qrow + (size_t)row * HD + col);
-          } else {
-            const float* src = srow + row * HD;
-            float r0 = src[col], r1 = src[col + 1];
-            if (col < rot) {
-              const bool low = col < half;
-              const int pc = low ? col + half : col - half;   // partner column
-              const int j = low ? col : col - half;           // angle index
-              const float y0 = src[pc], y1 = src[pc + 1];
-              r0 = low ? r0 * cs[j] - y0 * cs[half + j] : r0 * cs[j] + y0 * cs[half + j];
-              r1 = low ? r1 * cs[j + 1] - y1 * cs[half + j + 1] : r1 * cs[j + 1] + y1 * cs[half + j + 1];
-            }
-            v = pack_bf16(r0, r1);
-          }
-        }
+        if (row < gn)
+          v = FUSED ? sq[row * SQ_STRIDE + (col >> 1)] : *reinterpret_cast<const uint32_t*>(qrow + (size_t)row * HD + col);
         qf[ks][i] = v;
       }
     }
