@@ -60,6 +60,7 @@ constexpr int DSTAGES = 3 * STAGE_B <= 110 * 1024 ? 3 : 2;
 #endif
 static_assert(DSTAGES >= 2 && DSTAGES * STAGE_B <= 200 * 1024, "the ring must fit an SM's shared memory");
 constexpr int DEC_SMEM_B = DSTAGES * STAGE_B + SMEM_ALIGN;
+static_assert(4 * 16 * (HD + 8 + 2) * 4 <= DSTAGES * STAGE_B, "the warps' partial results are combined in the ring's memory");
 // byte offset of 16-byte chunk `chunk` of row `row` within a tile
 __device__ __forceinline__ int tile_off(int row, int chunk) {
   return SWZ ? (chunk >> 3) * ATOM_B + row * 128 + (((chunk & 7) ^ (row & 7)) << 4) : row * ROWB + chunk * 16;
@@ -606,18 +607,18 @@ attn_decode_mma_kernel(const __grid_constant__ KvMapsParam<TMA> maps, int tma_ro
     l[h] += __shfl_xor_sync(0xffffffffu, l[h], 1);
     l[h] += __shfl_xor_sync(0xffffffffu, l[h], 2);
   }
-  // combine the four warps through shared memory: so[warp][row][HD], sml[warp][row][2]
+  // combine the four warps through shared memory: so[warp][row][HD + 8], sml[warp][row][2]; the rows are 8 words
+  // longer than the head so that the 8-byte stores of a half-warp (four rows, four column pairs) hit 32 banks
+  constexpr int SO = HD + 8;
   float* so = reinterpret_cast<float*>(smem);
-  float* sml = so + 4 * 16 * HD;
+  float* sml = so + 4 * 16 * SO;
   {
     const int r = lane >> 2, cq = (lane & 3) * 2;
 #pragma unroll
     for (int dt = 0; dt < DTILES; dt++) {
-      float* b = so + ((warp * 16 + r) * HD) + dt * 8 + cq;
-      b[0] = o[dt][0];
-      b[1] = o[dt][1];
-      b[8 * HD] = o[dt][2];
-      b[8 * HD + 1] = o[dt][3];
+      float* b = so + ((warp * 16 + r) * SO) + dt * 8 + cq;
+      *reinterpret_cast<float2*>(b) = make_float2(o[dt][0], o[dt][1]);
+      *reinterpret_cast<float2*>(b + 8 * SO) = make_float2(o[dt][2], o[dt][3]);
     }
     if ((lane & 3) == 0) {
       sml[(warp * 16 + r) * 2] = m[0];
@@ -646,7 +647,7 @@ attn_decode_mma_kernel(const __grid_constant__ KvMapsParam<TMA> maps, int tma_ro
 #pragma unroll
     for (int w = 0; w < 4; w++) {
       const float f = exp2f(sml[(w * 16 + r) * 2] - mm);
-      acc += f * so[(w * 16 + r) * HD + d];
+      acc += f * so[(w * 16 + r) * SO + d];
       ll += f * sml[(w * 16 + r) * 2 + 1];
     }
     const int head = kvh * group + g0 + r;
