@@ -27,7 +27,7 @@ def test_split_covers_every_key_once(spans, blocks_per_item):
 
 
 def test_one_wave_where_the_batch_allows():
-    for batch, want_items in ((8, 48), (16, 48), (32, 64), (64, 64)):
+    for batch, want_items in ((8, 72), (16, 64), (32, 64), (64, 64)):  # a wave of 148 SMs x 4 blocks, 8 blocks an item
         n, _ = split_keys_evenly(np.full((batch,), 2053, dtype=np.int64), 8)
         assert int(n.sum()) == want_items, batch
 

@@ -387,14 +387,23 @@ attn_decode_mma_kernel(const __grid_constant__ KvMapsParam<TMA> maps, int tma_ro
   }
   // Q fragments: row r of the tile is query head g0 + r; rows >= gn are zero.
   uint32_t qf[KSTEPS][4];
-  __shared__ __align__(16) float cs[FUSED ? HD : 2];  // cos[rot/2], sin[rot/2] of this token's position
+  // What the fused form needs only until the key loop starts lives in the ring's LAST stage, which no tile enters
+  // before the loop's first iteration: the token's q rows of this head tile, then its k and v row (float32,
+  // srow[18][HD]); the rotated q as bfloat16 pairs (sq, rows 4 words longer than the head); cos and sin of the
+  // token's position (cs).  As static shared memory these 7 KiB cost the fourth block an SM, and with it a quarter
+  // of the speed of steps whose work items outnumber three blocks an SM (batch 64: 38 k -> 30 k tok/s).
+  constexpr int SQ_STRIDE = HD / 2 + 4;  // words (two bfloat16 each) from one row of sq to the next
+  static_assert(!FUSED || (18 * HD + 16 * SQ_STRIDE + HD) * 4 <= STAGE_B, "the fused prologue's scratch must fit one stage");
+  unsigned char* pro = smem + (DSTAGES - 1) * STAGE_B;
+  float* srow = reinterpret_cast<float*>(pro);
+  uint32_t* sq = reinterpret_cast<uint32_t*>(pro + 18 * HD * 4);
+  float* cs = reinterpret_cast<float*>(pro + 18 * HD * 4 + 16 * SQ_STRIDE * 4);
   __shared__ bf16 knew[FUSED ? HD : 2], vnew[FUSED ? HD : 2];  // the token's own rotated key and its value
   // this split holds position p, and this layer call keeps its own keys (a call that reads another call's cache
   // finds the key at p already there)
   const bool owns_new = FUSED && write_cache && k_end == kv_len;
   // the page of the token's own position: looked up here, before the wait, so that the write below waits for nothing
   const int own_page = owns_new ? table[p / ps] : 0;
-  __shared__ __align__(16) float srow[FUSED ? 18 * HD : 4];  // the token's q rows of this head tile, then its k and v row
   if (FUSED) {
     const int half = rot >> 1;
     for (int j = tid; j < half; j += 128) {
@@ -499,8 +508,6 @@ attn_decode_mma_kernel(const __grid_constant__ KvMapsParam<TMA> maps, int tma_ro
   // are 4 words longer than the head, so that the fragment loads below (eight rows a warp instruction) fall into
   // 32 different banks.  (Each thread rotating the fragments it needs straight from the float32 rows cost 1.5 us
   // of a 17 us kernel: sixteen times the arithmetic, and every load an eight-way bank conflict.)
-  constexpr int SQ_STRIDE = HD / 2 + 4;  // words (two bfloat16 each) from one row to the next
-  __shared__ uint32_t sq[FUSED ? 16 * SQ_STRIDE : 1];
   if (FUSED) {
     const int half = rot >> 1;
     for (int idx = tid; idx < gn * (HD / 2); idx += 128) {

@@ -31,13 +31,14 @@ QUERY_TILE_TC = 128  # queries per block of the tcgen05 kernel
 def decode_block_slots(head_dim: int, limits=None) -> int:
     """Blocks of the split-key kernel that the GPU holds at once: what of an SM's shared memory the kernel's
     stages take (two tiles of 64 rows a stage, rows of head_dim * 2 bytes, padded by 16 where the head size is
-    no multiple of 64; three stages, two when three pass 110 KiB), at most three blocks an SM.  ``limits``: the
+    no multiple of 64; three stages, two when three pass 110 KiB), at most four blocks an SM (128 threads of up to
+    124 registers each).  ``limits``: the
     device's SM count and shared memory (``kernels.device.DeviceLimits``; None: planning without a device)."""
     if limits is None:
         from tokasaurus_b200.kernels.device import NO_DEVICE as limits
     stage = 2 * 64 * (head_dim * 2 + (0 if head_dim % 64 == 0 else 16))
     stages = 3 if 3 * stage <= 110 * 1024 else 2
-    return limits.sm_count * max(1, min(3, limits.shared_memory_per_sm // (stages * stage + 2048)))
+    return limits.sm_count * max(1, min(4, limits.shared_memory_per_sm // (stages * stage + 2048)))
 
 
 DECODE_BLOCK_SLOTS = decode_block_slots(64)  # the default of the planning functions below
