@@ -268,7 +268,18 @@ def run(args) -> dict:
         samples = [event_ms(lambda: decode_step(seqs), steps) for _ in range(repeats)]
         return seqs, statistics.median(samples), samples
 
-    seqs, ms, samples = decode_run(args.batch, args.steps, args.warmup, "d", repeats=args.repeats)
+    sys.path.insert(0, os.path.dirname(HERE))
+    from bench import ClockSampler  # nvidia-smi in a thread; bench.py imports nothing of this repository's package
+
+    clocks = ClockSampler()
+    clocks.start()
+    seqs = fill(args.batch, "d")
+    for _ in range(args.warmup):
+        decode_step(seqs)
+    clocks.mark()
+    samples = [event_ms(lambda: decode_step(seqs), args.steps) for _ in range(args.repeats)]
+    ms = statistics.median(samples)
+    clock_info = clocks.stop()
 
     # -- the device's share alone: one planned decode step replayed from its CUDA graph, no host work between
     #    (what bench_model.py graph=True plan_before=True times, utils.py:254-309) ------------------------------
@@ -352,7 +363,7 @@ def run(args) -> dict:
         "e2e": dict(value=round(args.batch * args.steps / e2e_s, 1), unit="tokens/s", h2d_bytes_per_step=h2d,
                     d2h_bytes_per_step=d2h[0] // max(1, args.steps), ms_per_step=round(e2e_s * 1e3 / args.steps, 4)),
         "prefill": dict(value=round(prompt_len / (pf_ms / 1e3), 1), tokens=prompt_len, ms=round(pf_ms, 3)),
-        "points": points, "graph_replay_ms": None if replay_ms is None else round(replay_ms, 4), "block_ms": [round(s, 4) for s in samples], "setup_s": round(setup_s, 1),
+        "clocks": clock_info, "points": points, "graph_replay_ms": None if replay_ms is None else round(replay_ms, 4), "block_ms": [round(s, 4) for s in samples], "setup_s": round(setup_s, 1),
         "path": "make_model -> ModelRunner (CUDA graphs) -> seqs_to_input / plan / run, FlashInfer "
                 + __import__("flashinfer").__version__,
         "native_so_loaded": native_libraries(),

@@ -348,7 +348,8 @@ def run_ours(args) -> dict:
     blocks = [event_ms(d.one, args.steps)]
     launches = ops.LAUNCHES
     room = context_len - d.context() - args.steps - 8
-    while (len(blocks) < 5 or sum(blocks) * args.steps < 500.0) and room >= args.steps and len(blocks) < 60:
+    while ((len(blocks) < 5 or sum(blocks) * args.steps < 500.0) and room >= args.steps
+           and len(blocks) < (args.max_blocks or 60)):
         blocks.append(event_ms(d.one, args.steps))
         room -= args.steps
     clock_info = clocks.stop()
@@ -609,7 +610,7 @@ def run_reference(args) -> dict:
         tail = " | ".join((proc.stderr or proc.stdout).strip().splitlines()[-3:])[-400:]
         return {"impl": "reference", "unavailable": f"the reference arm exited with {proc.returncode}: {tail}"}
     out = json.loads(line)
-    out["clocks"] = clock_info
+    out.setdefault("clocks", clock_info)  # the arm samples its own timed region; this one covers the whole process
     return out
 
 
@@ -622,6 +623,9 @@ def main() -> int:
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration (0: all)")
     ap.add_argument("--skip-points", action="store_true", help="leave out the batch-1 and batch-64 points")
+    ap.add_argument("--max-blocks", type=int, default=0,
+                    help="at most this many timed blocks of --steps steps (0: at least five and half a second's worth); "
+                         "1 keeps a profiler's capture short")
     ap.add_argument("--reference-timeout", type=int, default=1500, help="seconds the reference arm may take")
     ap.add_argument("--config", type=int, default=2, choices=[2, 3, 4],
                     help="2: the headline metric (default); 3 and 4: the further workloads, see run_further")
