@@ -115,7 +115,8 @@ def prepare(head_dims=(), dtype: torch.dtype = torch.bfloat16) -> None:
 
     for hd in head_dims:
         check_head_dim(hd)
-    for source, defines in all_modules(head_dims):
+    name = {torch.float32: "float32", torch.bfloat16: "bfloat16"}.get(dtype)
+    for source, defines in all_modules(head_dims, name):
         _libs.get(source, **(defines or {}))
 
 
