@@ -362,7 +362,7 @@ def test_llama_layer_sizes_bfloat16_against_float32(sizes):
     14,336; vocabulary 32,000, untied), random weights: the bfloat16 path (tcgen05 attention and gate/up product for the
     prompts, K-split products, fused rotary + split-key attention with TMA tiles and the step graph for the
     decoded tokens) against the float32 path of the same engine, which the tiny models tie to the plain
-    implementation.  Eight prompts of about 1,400 tokens, so that the split-key kernel gets work items of four
+    implementation.  Eight prompts of about 1,800 tokens, so that the split-key kernel gets work items of four
     tiles; then five decoded tokens each (the float32 path's greedy choice is fed to both)."""
     from tokasaurus_b200.engine.batch import StepEntry
     from tokasaurus_b200.engine.engine import Engine
@@ -375,12 +375,12 @@ def test_llama_layer_sizes_bfloat16_against_float32(sizes):
     if sizes == "8b":
         cfg.update(num_hidden_layers=1, hidden_size=4096, intermediate_size=14336, vocab_size=32000,
                    tie_word_embeddings=False)
-    lengths = [1400, 1337, 1290, 1411, 1376, 1302, 1455, 1360]
+    lengths = [1850, 1787, 1740, 1861, 1826, 1752, 1905, 1810]
     prompts = [cuttings.random_tokens(n, cfg["vocab_size"], 900 + i) for i, n in enumerate(lengths)]
     ids = [f"p{i}" for i in range(len(prompts))]
 
     def run(dtype, feed=None):
-        eng = Engine(config_dict=cfg, random_weights=0, dtype=dtype, page_size=16, kv_cache_num_tokens=8 * 1536,
+        eng = Engine(config_dict=cfg, random_weights=0, dtype=dtype, page_size=16, kv_cache_num_tokens=8 * 2048,
                      max_tokens_per_forward=8192, max_seqs_per_forward=8)
         runner, cache = eng.runner, eng.runner.cache
         rows = []  # [step][request] -> logits

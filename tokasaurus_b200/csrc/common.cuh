@@ -64,9 +64,6 @@ __device__ __forceinline__ int checked_page(int page, int num_pages, int* status
 // The same for inner loops: no branch and no atomic there, the caller keeps `bad` in a register and reports it
 // once, at its end, with report_bad_page().
 __device__ __forceinline__ int checked_page(int page, int num_pages, bool& bad) {
-#ifdef TKB_EXP_NO_PAGE_CHECK
-  return page;
-#endif
   const bool b = num_pages > 0 && page >= num_pages;
   bad |= b;
   return b ? -1 : page;

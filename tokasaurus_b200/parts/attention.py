@@ -121,8 +121,12 @@ def plan_attention(host, window: int | None, capacity: dict | None = None, block
         i32 = lambda a: np.ascontiguousarray(a, dtype=np.int32)  # noqa: E731
         extra = dict(row_items=i32(np.stack([r_item, r_first, r_isize], axis=1).reshape(-1)), row_item_start=i32(r_start),
                      row_item_entry=i32(r_item),
-                     row_token=i32(rows), row_kv_len=i32(r_kv), row_seq=i32(np.asarray(host.token_seq)[rows]),
+                     row_token=i32(rows), row_kv_len=i32(r_kv),
                      row_index=i32(np.arange(n_rows)))
+        # where each row's request starts in the page-id list of each cache group (a windowed group's tables can be
+        # shorter than those of a group that sees all keys while a prompt is on its way)
+        for g, indptr in enumerate(host.table_indptr):
+            extra[f"row_indptr_g{g}"] = i32(np.asarray(indptr)[np.asarray(host.token_seq)[rows]])
     # counts[5], counts[6]: some work item of the requests that decode (of the wanted rows) is longer than three
     # tiles of 64 keys; the split-key kernel then runs in the variant that fetches whole tiles by TMA
     long_items = int(n_items > 0 and int(item_size.max()) > 3 * 64)
@@ -255,8 +259,9 @@ class PagedAttention(Mixer):
             out["row_items"] = padded(plan["row_items"], 3 * ri)
             out["row_item_entry"] = padded(plan["row_item_entry"], ri)
             out["row_item_start"] = padded(plan["row_item_start"], rows + 1)
-            for name in ("row_token", "row_kv_len", "row_seq", "row_index"):
-                out[name] = padded(plan[name], rows)
+            for name in plan:
+                if name in ("row_token", "row_kv_len", "row_index") or name.startswith("row_indptr_g"):
+                    out[name] = padded(plan[name], rows)
         return out
 
     # --- one step ---
@@ -305,9 +310,9 @@ class PagedAttention(Mixer):
             n_items = caps["row_items"] if caps else int(counts[3])
             n_rows = caps["rows"] if caps else int(counts[4])
             attn = torch.empty((n_rows, nh * hd), dtype=h.dtype, device=h.device)
-            row_indptr = tables.indptr.index_select(0, plan["row_seq"])
             c = plan["counts"]
-            ops.attn_decode_mma(qkv, cache.k, cache.v, plan["row_token"], plan["row_kv_len"], row_indptr,
+            ops.attn_decode_mma(qkv, cache.k, cache.v, plan["row_token"], plan["row_kv_len"],
+                                plan[f"row_indptr_g{cache.group}"],
                                 tables.page_ids, plan["row_items"], c[3:4], n_items, plan["row_index"],
                                 plan["row_item_start"], c[4:5], n_rows, attn, nh, nkv, hd, cache.page_size,
                                 self.scale, self.window, out_row_of=plan["row_index"],
