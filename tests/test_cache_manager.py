@@ -87,6 +87,30 @@ def test_window_gives_pages_back_and_they_are_reused():
     m.check()
 
 
+def test_windowed_groups_fill_portion_by_portion_in_a_pool_of_their_own():
+    """With the step's token limit known, a windowed group's pool holds what the request slots can hold at once
+    (window 20 + 16 tokens a step + 1 ahead = 37 tokens -> 5 pages, + 1: 6 a request), and a prompt that is
+    longer than that pool passes through it while the full group holds all of it from the start."""
+    m = CacheManager({0: FULL, 1: WIN}, page_size=8, num_pages=64, max_requests=2, max_step_tokens=16)
+    assert [g.allocator.num_pages for g in m.groups] == [64, 12]
+    m.admit("a")
+    with pytest.raises(NoSpaceError):
+        m.ensure_capacity("a", 200)  # all of it at once does not fit the windowed pool, and nothing is taken
+    assert m.num_free_pages() == [64, 12]
+    done = 0
+    while done < 200:
+        n = min(16, 200 - done)
+        assert m.can_hold("a", 200, windowed_tokens=done + n)
+        m.ensure_capacity("a", 200, windowed_tokens=done + n)
+        assert len(m.table("a", 0)) == 25 and len(m.table("a", 1)) == -(-(done + n) // 8)
+        done += n
+        m.release_behind_window("a", done)
+        assert sum(p >= 0 for p in m.table("a", 1)) <= 6
+        m.check()
+    m.free("a")
+    assert m.num_free_pages() == [64, 12]
+
+
 @pytest.mark.parametrize("seed", range(8))
 def test_random_orders_keep_the_books(seed):
     rng = random.Random(seed)

@@ -286,3 +286,41 @@ def test_long_requests_in_a_windowed_pool_smaller_than_their_length():
     fin, plans = run(s)
     assert len(fin) == 2 and s.stats["bumps"] == 0
     assert max(len(p.portions) for p in plans) == 2  # they did run together
+
+
+def test_a_windowed_group_has_a_pool_of_its_own_size_and_long_prompts_pass_through_it():
+    """The pool of a group with a window is sized by what the request slots can hold at once, not by the token
+    count that sizes the groups that see all keys; a prompt longer than that pool takes its pages there portion by
+    portion while the pages behind the window come back."""
+    needs = {0: PagedCacheNeed(1, 16), 1: PagedCacheNeed(1, 16, window=8)}
+    cache = CacheManager(needs, page_size=4, num_pages=128, max_requests=2, max_step_tokens=8)
+    # window 8 + step 8 + 1 token ahead = 17 tokens -> 5 pages, + 1 for where the window starts: 6 a request
+    assert [g.allocator.num_pages for g in cache.groups] == [128, 12]
+    s = Scheduler(cache, 8, 2, sanity_checks=True)
+    for i in range(3):
+        s.add_request(req(i, 150 + i, 20))  # 38 pages of prompt each: three times the windowed pool
+    fin, plans = run(s)
+    assert len(fin) == 3 and s.stats["bumps"] == 0
+    assert all(sum(p.n_tokens for p in plan.portions) <= 8 for plan in plans)
+    assert max(len(plan.portions) for plan in plans) == 2
+    assert cache.num_free_pages() == [128, 12]
+
+
+def test_prompt_portions_shrink_when_a_windowed_pool_is_short():
+    """A windowed pool too small for two requests at full pace: portions are cut to the pages that are free, a
+    request that cannot go on at all waits for the other or pushes it out, and every request ends."""
+    cache = CacheManager({0: PagedCacheNeed(1, 16, window=8)}, page_size=4, num_pages=7, max_requests=4,
+                         max_step_tokens=12)
+    assert cache.groups[0].allocator.num_pages == 7
+    s = Scheduler(cache, 12, 4, sanity_checks=True)
+    for i in range(3):
+        s.add_request(req(i, 40 + 3 * i, 10))
+    fin, plans = run(s)
+    assert sorted(o.id for o in fin) == ["r0", "r1", "r2"]
+    assert all(len(o.completion_ids) == 10 for o in fin)
+    sizes = {p.n_tokens for plan in plans for p in plan.portions if not p.from_device}
+    assert min(sizes) < 12  # some portion was cut short of the budget by the pages
+    assert cache.num_free_pages() == [7]
+    with pytest.raises(RequestTooLongError, match="cache group 0"):
+        small = CacheManager({0: PagedCacheNeed(1, 16, window=8)}, page_size=4, num_pages=3, max_requests=4)
+        Scheduler(small, 12, 4).add_request(req(0, 40, 10))  # a window of 8 and the next token can span 4 pages

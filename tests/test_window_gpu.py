@@ -249,6 +249,6 @@ def test_windowed_generation_through_the_entry_point(toys, run_ahead):
                      run_ahead=run_ahead, **opts)
         outs = eng.generate(prompts, max_num_tokens=n_new, ignore_eos=True)
         assert [o.completion_ids for o in outs] == want
-        assert not eng.runner.cache.requests and eng.runner.cache.num_free_pages() == [eng.runner.cache.num_pages]
+        assert not eng.runner.cache.requests and eng.runner.cache.num_free_pages() == [g.allocator.num_pages for g in eng.runner.cache.groups]
         if opts:
             assert eng.scheduler.stats["bumps"] > 0

@@ -79,13 +79,22 @@ class RequestCache:
 
 class CacheManager:
     def __init__(self, needs: Mapping[int, PagedCacheNeed | StateNeed | None], page_size: int, num_pages: int,
-                 max_requests: int, dtype: torch.dtype = torch.bfloat16, device: torch.device | str | None = None):
+                 max_requests: int, dtype: torch.dtype = torch.bfloat16, device: torch.device | str | None = None,
+                 max_step_tokens: int | None = None):
         """``needs``: {cache entry: need of the mixer using it} (``DecoderModel.cache_entries``).
-        ``device=None`` keeps the books only (no device memory), for tests of the accounting."""
+        ``device=None`` keeps the books only (no device memory), for tests of the accounting.
+
+        ``num_pages`` is a count of tokens a request may hold, in pages: every group whose mixers see all keys
+        gets a pool of that many pages (a token needs an entry in each of them), so the memory is the sum over the
+        groups of ``num_pages`` times the group's bytes a page (``device_bytes_by_group``).  A windowed group needs
+        less: with ``max_step_tokens`` given (the most tokens one request brings in a step) its pool is capped at
+        what ``max_requests`` requests can hold at once: a window, a step's tokens and the one token of a step
+        launched ahead each, and a page for where the window starts inside a page."""
         if page_size <= 0:
             raise ValueError("page_size must be positive")
         self.page_size = page_size
         self.num_pages = num_pages
+        self.max_step_tokens = max_step_tokens
         self.dtype = dtype
         self.device = torch.device(device) if device is not None else None
         self.groups: list[CacheGroup] = []
@@ -98,7 +107,10 @@ class CacheManager:
             if isinstance(need, PagedCacheNeed):
                 g = by_need.get(need)
                 if g is None:
-                    g = CacheGroup(len(self.groups), need, [], PageAllocator(num_pages))
+                    pool = num_pages
+                    if need.window and max_step_tokens is not None:
+                        pool = min(num_pages, max_requests * (self.pages_for(need.window + max_step_tokens + 1) + 1))
+                    g = CacheGroup(len(self.groups), need, [], PageAllocator(pool))
                     by_need[need] = g
                     self.groups.append(g)
                 self._entry_group[entry] = (g.index, len(g.entries))
@@ -113,7 +125,7 @@ class CacheManager:
         if self.device is not None:
             for g in self.groups:
                 n = g.need
-                g.storage = torch.zeros((len(g.entries), 2, num_pages, n.n_kv_heads, page_size, n.head_dim),
+                g.storage = torch.zeros((len(g.entries), 2, g.allocator.num_pages, n.n_kv_heads, page_size, n.head_dim),
                                         dtype=dtype, device=self.device)
             for entry, need in self._state_need.items():
                 self._state[entry] = torch.zeros((max_requests, *need.shape), dtype=_DTYPES[need.dtype],
@@ -125,7 +137,11 @@ class CacheManager:
         return (n_tokens + self.page_size - 1) // self.page_size
 
     def device_bytes(self) -> int:
-        return sum(g.storage.numel() * g.storage.element_size() for g in self.groups if g.storage is not None)
+        return sum(self.device_bytes_by_group())
+
+    def device_bytes_by_group(self) -> list[int]:
+        """Bytes of key/value storage of each cache group (0 where the manager keeps books only)."""
+        return [g.storage.numel() * g.storage.element_size() if g.storage is not None else 0 for g in self.groups]
 
     def num_free_pages(self) -> list[int]:
         return [g.allocator.num_free for g in self.groups]
@@ -142,20 +158,25 @@ class CacheManager:
                 st[slot].zero_()
         return rc
 
-    def pages_missing(self, request: object, n_tokens: int) -> list[int]:
-        """Per group: pages to add so that positions [0, n_tokens) have a page."""
+    def pages_missing(self, request: object, n_tokens: int, windowed_tokens: int | None = None) -> list[int]:
+        """Per group: pages to add so that positions [0, n_tokens) have a page; in groups with a window,
+        positions [0, min(n_tokens, windowed_tokens)) if ``windowed_tokens`` is given."""
         rc = self.requests[request]
         need = self.pages_for(n_tokens)
-        return [max(0, need - len(rc.tables[g.index])) for g in self.groups]
+        need_w = need if windowed_tokens is None else self.pages_for(min(n_tokens, windowed_tokens))
+        return [max(0, (need_w if g.need.window else need) - len(rc.tables[g.index])) for g in self.groups]
 
-    def can_hold(self, request: object, n_tokens: int) -> bool:
-        return all(m <= g.allocator.num_free for m, g in zip(self.pages_missing(request, n_tokens), self.groups))
+    def can_hold(self, request: object, n_tokens: int, windowed_tokens: int | None = None) -> bool:
+        return all(m <= g.allocator.num_free
+                   for m, g in zip(self.pages_missing(request, n_tokens, windowed_tokens), self.groups))
 
-    def ensure_capacity(self, request: object, n_tokens: int) -> None:
-        """Give the request pages for positions [0, n_tokens) in every group, or raise
-        ``NoSpaceError`` and change nothing."""
+    def ensure_capacity(self, request: object, n_tokens: int, windowed_tokens: int | None = None) -> None:
+        """Give the request pages for positions [0, n_tokens) in every group, or raise ``NoSpaceError`` and change
+        nothing.  A group with a window only needs pages for the tokens that have gone, or are about to go,
+        through the model: ``windowed_tokens`` (at most ``n_tokens``) says how far such groups are filled, so that
+        a long prompt takes pages there portion by portion while the pages behind the window come back."""
         rc = self.requests[request]
-        missing = self.pages_missing(request, n_tokens)
+        missing = self.pages_missing(request, n_tokens, windowed_tokens)
         for m, g in zip(missing, self.groups):
             if m > g.allocator.num_free:
                 raise NoSpaceError(

@@ -61,6 +61,17 @@ class DecodeGraphs:
         pages_for = self.runner.cache.pages_for
         return all(pages_for(e.start + e.n_tokens) <= limit for e in entries)
 
+    def _page_caps(self, host: HostBatch) -> list[int]:
+        """Length to which each cache group's block tables are padded (part of a graph's key).  The capacity of
+        the pool, which the tables of a group that sees all keys never outgrow; a windowed group's tables also
+        list the pages given back (as -1) and can grow past its pool: then the next power of two, so that a graph
+        is recorded anew at doublings only."""
+        caps = []
+        for g, pg in zip(self.runner.cache.groups, host.table_pages):
+            pool = max(g.allocator.num_pages, 1)
+            caps.append(pool if pg.shape[0] <= pool else _pow2_at_least(pg.shape[0], pool))
+        return caps
+
     def usable(self, entries) -> bool:
         return (bool(self.sizes) and len(entries) <= self.sizes[-1] and self.runner.model.graph_safe
                 and all(e.n_tokens == 1 and list(e.want) == [0] for e in entries) and self._tables_fit(entries))
@@ -82,7 +93,7 @@ class DecodeGraphs:
         T, S, R = host.token_ids.shape[0], len(entries), host.logit_rows.shape[0]
         tp = next(b for b in TOKEN_BUCKETS if b >= T)
         sp = next(s for s in self.sizes if s >= S)
-        page_caps = [max(g.allocator.num_pages, pg.shape[0], 1) for g, pg in zip(runner.cache.groups, host.table_pages)]
+        page_caps = self._page_caps(host)
         planners = runner.model.planners()
         raw = {key: m.plan(host) for key, m in planners.items()}
         caps = {}
@@ -127,8 +138,7 @@ class DecodeGraphs:
         B = len(entries)
         bp = next(s for s in self.sizes if s >= B)
         host = build_host_batch(entries, runner.cache)
-        # block tables at the capacity of the pool: a request's table never outgrows it
-        page_caps = [max(g.allocator.num_pages, pg.shape[0], 1) for g, pg in zip(runner.cache.groups, host.table_pages)]
+        page_caps = self._page_caps(host)
         planners = runner.model.planners()
         raw = {key: m.plan(host) for key, m in planners.items()}
         caps = {}

@@ -85,7 +85,7 @@ class ModelRunner:
 
         self.cache = CacheManager(needs, config.page_size, config.kv_cache_num_blocks(),
                                   max_requests=config.max_seqs_per_forward, dtype=self.rt.dtype,
-                                  device=self.rt.device)
+                                  device=self.rt.device, max_step_tokens=config.max_tokens_per_forward)
         self.stager = Stager(self.rt.device)
         self.vocab = self.model.vocab
         self.last_upload_bytes = 0

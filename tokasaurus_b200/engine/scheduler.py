@@ -118,10 +118,14 @@ class Scheduler:
             raise RequestTooLongError(
                 f"request {request.id!r}: prompt {n} + max_num_tokens {request.max_num_tokens} exceeds "
                 f"max_num_tokens_per_request={self.max_request_tokens}")
-        if self.cache.pages_for(total - 1) > self.cache.num_pages:
-            raise RequestTooLongError(
-                f"request {request.id!r} can need {self.cache.pages_for(total - 1)} pages, the pool has "
-                f"{self.cache.num_pages}")
+        for g, group in enumerate(self.cache.groups):
+            need = self.cache.pages_for(total - 1)
+            if group.need.window:  # the least with which a token still sees its whole window
+                need = min(need, self.cache.pages_for(group.need.window + 1) + 1)
+            if need > group.allocator.num_pages:
+                raise RequestTooLongError(
+                    f"request {request.id!r} can need {need} pages of cache group {g}, its pool has "
+                    f"{group.allocator.num_pages}")
         if any(s.id == request.id for s in self.queued) or any(s.id == request.id for s in self.running()):
             raise ValueError(f"request id {request.id!r} is already queued or running (the cache is keyed by it)")
         seq = Sequence(request, self._counter, RequestOutput(request.id))
@@ -150,9 +154,18 @@ class Scheduler:
             allocated = held
         need = max(0, total - allocated)
         if group.need.window:
-            most_live = self.cache.pages_for(group.need.window + self.max_tokens) + 1
-            need = min(need, max(0, most_live - held))
+            need = min(need, max(0, self._most_live(g) - held))
         return need
+
+    def _most_live(self, g: int) -> int:
+        """Most pages a sequence holds at a time in the windowed group ``g``: the window, a step's tokens (and the
+        one token of a step launched ahead) and a page for where the window starts inside a page."""
+        return self.cache.pages_for(self.cache.groups[g].need.window + self.max_tokens + 1) + 1
+
+    def _first_windowed_tokens(self, seq: Sequence) -> int:
+        """How far windowed groups are filled at admission: the first step's tokens at most; the rest of a prompt
+        takes its pages there portion by portion (``_fit_portion``)."""
+        return min(seq.n_known, self.max_tokens)
 
     def _headroom(self) -> list[int]:
         """Per cache group: free pages less what running sequences may still ask for, scaled by the reserve fraction."""
@@ -168,10 +181,14 @@ class Scheduler:
     def _admission_need(self, seq: Sequence) -> list[int]:
         """Per cache group: pages a queued sequence takes at admission (its whole prompt, as the reference's
         ``allocate_with_prefix_match`` does) plus its share of the reserve."""
-        first_need = self.cache.pages_for(seq.n_known)
+        full = self.cache.pages_for(seq.n_known)
+        windowed = self.cache.pages_for(self._first_windowed_tokens(seq))
         f = self.reserve_fraction
-        return [first_need + (int(max(0, self._still_needed(seq, g, first_need)) * f + 0.999999) if f > 0 else 0)
-                for g in range(len(self.cache.groups))]
+        out = []
+        for g, group in enumerate(self.cache.groups):
+            first_need = windowed if group.need.window else full
+            out.append(first_need + (int(max(0, self._still_needed(seq, g, first_need)) * f + 0.999999) if f > 0 else 0))
+        return out
 
     def _min_free(self) -> int:
         free = self.cache.num_free_pages()
@@ -185,7 +202,7 @@ class Scheduler:
                 break
             self.queued.popleft()
             self.cache.admit(seq.id)
-            self.cache.ensure_capacity(seq.id, seq.n_known)
+            self.cache.ensure_capacity(seq.id, seq.n_known, windowed_tokens=self._first_windowed_tokens(seq))
             seq.fed = 0
             seq.admitted_at = self._admissions
             self._admissions += 1
@@ -238,13 +255,40 @@ class Scheduler:
         for seq in self.decoding:
             plan.portions.append(ScheduledPortion(seq, seq.fed, 1, True, from_device=True))
         budget = self._prefill_budget(self.max_tokens - len(plan.portions))
-        for seq in self.prefilling:
+        for seq in list(self.prefilling):
             if budget <= 0:
                 break
-            n = min(budget, seq.n_known - seq.fed)
+            if seq not in self.prefilling:
+                continue  # was pushed out a moment ago
+            n = self._fit_portion(seq, min(budget, seq.n_known - seq.fed))
+            while n == 0 and not plan.portions:
+                # nothing else runs in this step and this prompt cannot go on: push out a later sequence for it
+                victim = self._bump_one(protect=seq)
+                if victim is None:
+                    raise NoSpaceError(
+                        f"request {seq.id!r} cannot go on at token {seq.fed}: a windowed cache group has "
+                        f"{self._min_free()} free pages with nothing else running")
+                plan.bumped.append(victim.id)
+                n = self._fit_portion(seq, min(budget, seq.n_known - seq.fed))
+            if n == 0:
+                continue
             plan.portions.append(ScheduledPortion(seq, seq.fed, n, seq.fed + n == seq.n_known, from_device=False))
             budget -= n
         return plan
+
+    def _fit_portion(self, seq: Sequence, n: int) -> int:
+        """Pages of the windowed groups for the next ``n`` prompt tokens of ``seq``; fewer tokens if their pools
+        have no more, 0 if not one token fits.  (The groups that see all keys hold the whole prompt since
+        admission.)"""
+        rc = self.cache.requests[seq.id]
+        for g, group in enumerate(self.cache.groups):
+            if group.need.window:
+                reach = (len(rc.tables[g]) + group.allocator.num_free) * self.cache.page_size
+                n = min(n, reach - seq.fed)
+        if n <= 0:
+            return 0
+        self.cache.ensure_capacity(seq.id, seq.n_known, windowed_tokens=seq.fed + n)
+        return n
 
     # ------------------------------------------------------------------ how much of the prompts goes into a step
     def _prefill_budget(self, room: int) -> int:
