@@ -256,11 +256,24 @@ def run_ours(args) -> dict:
     pf_tokens = tokens(prompt_len)
 
     def prefill_once(chunk=prompt_len):
+        """The prompt in portions of ``chunk`` tokens, each run as the engine runs such a step: as a step graph
+        where it keeps graphs for steps of that size, else kernel by kernel."""
         cache.admit("pf")
         cache.ensure_capacity("pf", prompt_len)
         for at in range(0, prompt_len, chunk):
             last = at + chunk >= prompt_len
-            runner.step([StepEntry("pf", pf_tokens[at:at + chunk], at, [chunk - 1] if last else [])])
+            entries = [StepEntry("pf", pf_tokens[at:at + chunk], at, [chunk - 1] if last else [])]
+            rows = 1 if last else 0
+            extra = dict(temperature=np.zeros(rows, dtype=np.float32), stream_key=np.zeros(rows, dtype=np.int64),
+                         sample_pos=np.full(rows, at + chunk, dtype=np.int32),
+                         row_slot=np.full(rows, cache.slot("pf"), dtype=np.int32))
+            prep = None
+            if eng.graphs is not None and eng.graphs.usable_general(entries):
+                prep = eng.graphs.prepare_general(entries, extra)
+            if prep is not None:
+                eng.graphs.launch(prep)
+            else:
+                runner.step(entries, extra)
         cache.free("pf")
 
     for _ in range(max(3, args.warmup // 2)):

@@ -117,7 +117,8 @@ def test_steps_ahead_and_paced_prefill_options_reach_the_engine(cpu_kernels, tin
     eng = make_engine(d, scheduling_steps_ahead=0, greedy_prefill=False, prefill_round_up_multiple=4)
     assert eng.run_ahead is False and eng.scheduler.greedy_prefill is False and eng.scheduler.prefill_multiple == 4
     eng = make_engine(d, scheduling_steps_ahead=8)
-    assert eng.run_ahead is True and eng.scheduler.greedy_prefill is True
+    assert eng.run_ahead is True and eng.steps_ahead == 8 and eng.scheduler.greedy_prefill is True
+    assert len(eng.sampler.host) == 10  # a landing place for every step in flight and the one being read, and one spare
     # paced prefill changes when tokens run, not which tokens come out
     prompts = [cuttings.random_tokens(n, 256, 5 * n) for n in (30, 3, 40, 25)]
     plain = PlainLlama(d, torch.float64)

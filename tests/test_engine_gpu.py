@@ -189,8 +189,8 @@ def test_cuda_graph_decode_equals_eager(tiny_model_dirs, dtype):
 
 def test_cuda_graph_decode_with_requests_ending_at_different_times(tiny_model_dirs):
     """Requests that end by length at different steps and on stop tokens, and late arrivals: the engine launches
-    the next step before it has read the current one, on a guess that is wrong again and again; the rows of
-    requests that had ended after all must be dropped, with and without that run-ahead."""
+    the next steps (one, two, five of them) before it has read the current one, on a guess that is wrong again and
+    again; the rows of requests that had ended after all must be dropped, with and without that run-ahead."""
     from tokasaurus_b200 import SamplingParams
 
     d = tiny_model_dirs[0]
@@ -201,8 +201,9 @@ def test_cuda_graph_decode_with_requests_ending_at_different_times(tiny_model_di
     stop_at = full[2][9]  # request 2 stops when it first produces this token
     want = [list(f) for f in full]
     want[2] = full[2][: full[2].index(stop_at) + 1]
-    for graphs, ahead in ((False, True), (True, False), (True, True)):
-        eng = make_engine(d, use_cudagraphs=graphs, cudagraph_step=4, cudagraph_max_size=8, run_ahead=ahead)
+    for graphs, ahead in ((False, 1), (True, 0), (True, 1), (True, 2), (True, 5)):
+        eng = make_engine(d, use_cudagraphs=graphs, cudagraph_step=4, cudagraph_max_size=8, scheduling_steps_ahead=ahead)
+        assert eng.steps_ahead == ahead
         ids = []
         for i, (p, m) in enumerate(zip(prompts[:4], limits[:4])):
             ids.append(eng.add_request(p, SamplingParams(), max_num_tokens=m, ignore_eos=True,
@@ -214,7 +215,7 @@ def test_cuda_graph_decode_with_requests_ending_at_different_times(tiny_model_di
             ids.append(eng.add_request(p, SamplingParams(), max_num_tokens=m, ignore_eos=True))
         done += eng.run_until_done()
         by_id = {o.id: o for o in done}
-        assert [by_id[i].completion_ids for i in ids] == want, f"graphs={graphs} run_ahead={ahead}"
+        assert [by_id[i].completion_ids for i in ids] == want, f"graphs={graphs} steps ahead={ahead}"
         assert by_id[ids[2]].finish_reason == "stop"
         assert not eng.runner.cache.requests and not eng.has_work()
 
@@ -230,15 +231,22 @@ def test_run_ahead_with_stop_tokens_under_sampling(tiny_model_dirs):
     ref = make_engine(d, dtype="bfloat16", page_size=8, run_ahead=False).generate(prompts, sp, max_num_tokens=30, ignore_eos=True)
     stops = [[o.completion_ids[4 + 3 * i]] for i, o in enumerate(ref)]
     outs = {}
-    for ahead in (False, True):
-        eng = make_engine(d, dtype="bfloat16", page_size=8, run_ahead=ahead)
+    deepest = 0
+    for ahead in (0, 1, 3):
+        eng = make_engine(d, dtype="bfloat16", page_size=8, scheduling_steps_ahead=ahead)
         ids = [eng.add_request(p, s, max_num_tokens=30, ignore_eos=True, stop_token_ids=st)
                for p, s, st in zip(prompts, sp, stops)]
-        by_id = {o.id: o for o in eng.run_until_done()}
+        done = []
+        while eng.has_work():
+            done += eng.step()
+            deepest = max(deepest, len(eng._inflight)) if ahead == 3 else deepest
+        by_id = {o.id: o for o in done}
         outs[ahead] = [by_id[i] for i in ids]
         assert not eng.runner.cache.requests and not eng.has_work()
-    for a, b, r, st in zip(outs[False], outs[True], ref, stops):
-        assert a.completion_ids == b.completion_ids and a.finish_reason == b.finish_reason == "stop"
+    assert deepest == 3  # three steps were in flight beyond the one being read
+    for a, b, c, r, st in zip(outs[0], outs[1], outs[3], ref, stops):
+        assert a.completion_ids == b.completion_ids == c.completion_ids
+        assert a.finish_reason == b.finish_reason == c.finish_reason == "stop"
         assert a.completion_ids == r.completion_ids[: r.completion_ids.index(st[0]) + 1]
 
 

@@ -35,7 +35,7 @@ class EngineConfig:
     max_tokens_per_forward: int = 8192
     max_seqs_per_forward: int = 1024
     prefill_round_up_multiple: int = 16  # of the paced prompt tokens a step (greedy_prefill=F)
-    scheduling_steps_ahead: int = 1  # 0: no run-ahead; this engine looks one step ahead, never more (reference: 8)
+    scheduling_steps_ahead: int = 2  # decode steps launched before the current one's results are read (0: none; reference: 8)
     max_num_tokens_per_request: int | None = None
     greedy_prefill: bool = True
     use_cudagraphs: bool = True

@@ -107,23 +107,27 @@ class StepContext:
 
 
 class Stager:
-    """A pinned host buffer and its device twin; ``upload`` packs int32 arrays into the first and
-    copies once.  Segments start on 16-byte boundaries."""
+    """Pinned host buffers and their device twin; ``upload`` packs int32 arrays into a host buffer and
+    copies once.  Segments start on 16-byte boundaries.  ``host_buffers``: how many pinned buffers take turns, so
+    that as many uploads can be in the stream at a time without the host waiting for the oldest to be over (the
+    device twin is one: copies into it are ordered by the stream behind the kernels that read it)."""
 
-    def __init__(self, device: torch.device, capacity_ints: int = 1 << 16):
+    def __init__(self, device: torch.device, capacity_ints: int = 1 << 16, host_buffers: int = 1):
         self.device = device
         self.status = torch.zeros((1,), dtype=torch.int32, device=device)
+        self.host_buffers = max(1, int(host_buffers))
         self._alloc(capacity_ints)
 
     def _alloc(self, n: int) -> None:
         self.capacity = n
         pin = self.device.type == "cuda"
-        self.host = torch.empty((n,), dtype=torch.int32, pin_memory=pin)
-        self.host_np = self.host.numpy()
+        self._hosts = [torch.empty((n,), dtype=torch.int32, pin_memory=pin) for _ in range(self.host_buffers)]
+        self._hosts_np = [h.numpy() for h in self._hosts]
         self.dev = torch.empty((n,), dtype=torch.int32, device=self.device)
         self.bytes_last_upload = 0
-        self._copied = torch.cuda.Event() if pin else None
-        self._pending = False
+        self._copied = [torch.cuda.Event() if pin else None for _ in range(self.host_buffers)]
+        self._pending = [False] * self.host_buffers
+        self._turn = 0
 
     def upload(self, arrays: Sequence[np.ndarray], used_of_last: int | None = None) -> list[torch.Tensor]:
         """Pack the arrays and copy them to the device in one copy; returns their device views.  ``used_of_last``:
@@ -144,21 +148,24 @@ class Stager:
             if self.device.type == "cuda":
                 torch.cuda.current_stream(self.device).synchronize()
             self._alloc(max(total, 2 * self.capacity))
-        if self._pending:
-            self._copied.synchronize()  # the last copy out of the pinned buffer must be over before it is rewritten
-            self._pending = False
+        turn = self._turn
+        self._turn = (turn + 1) % self.host_buffers
+        host, host_np = self._hosts[turn], self._hosts_np[turn]
+        if self._pending[turn]:
+            self._copied[turn].synchronize()  # the last copy out of this pinned buffer must be over before it is rewritten
+            self._pending[turn] = False
         n_copy = total
         if used_of_last is not None and arrays:
             n_copy = max(4, offs[-1] + min(int(used_of_last), arrays[-1].shape[0]))
         for a, o in zip(arrays, offs):
             n = min(a.shape[0], n_copy - o)
             if n > 0:
-                self.host_np[o:o + n] = a[:n]
+                host_np[o:o + n] = a[:n]
         total_bytes = n_copy
-        self.dev[:n_copy].copy_(self.host[:n_copy], non_blocking=True)
-        if self._copied is not None:
-            self._copied.record()
-            self._pending = True
+        self.dev[:n_copy].copy_(host[:n_copy], non_blocking=True)
+        if self._copied[turn] is not None:
+            self._copied[turn].record()
+            self._pending[turn] = True
         self.bytes_last_upload = total_bytes * 4
         out = []
         for a, o, k in zip(arrays, offs, kinds):

@@ -14,7 +14,8 @@ from __future__ import annotations
 
 import logging
 import time
-from dataclasses import dataclass
+from collections import deque
+from dataclasses import dataclass, field
 from typing import Any, Sequence
 
 import numpy as np
@@ -36,6 +37,7 @@ class _InFlight:
     rows: int    # rows of the plan
     slot: int    # the sampler's landing place on the host
     h2d: int
+    produced: dict = field(default_factory=dict)  # id(sequence) -> completion tokens it has once this step is read
 
 
 class Engine:
@@ -45,7 +47,8 @@ class Engine:
         """``model``: folder with config.json and model.safetensors.  ``options``: fields of
         ``EngineConfig`` (the reference's option names).  ``config_dict`` with
         ``random_weights=<seed>`` builds a model without a folder.  ``run_ahead``: launch the next decode step
-        before the results of the current one have been read (see ``step``).  ``graph_max_tokens``: steps with prompt
+        before the results of the current one have been read, up to ``scheduling_steps_ahead`` steps deep (see
+        ``step``).  ``graph_max_tokens``: steps with prompt
         portions of up to this many tokens are replayed from CUDA graphs of their padded shape, like decode steps
         (0: only decode steps are)."""
         cfg = config or EngineConfig()
@@ -65,19 +68,21 @@ class Engine:
             cfg.max_num_tokens_per_request, self.runner.eos_token_ids, kv_reserve_fraction,
             cfg.bump_city_population_me, cfg.allocator_sanity_checks, cfg.greedy_prefill,
             cfg.prefill_round_up_multiple)
+        # steps launched beyond the one whose results are being read (tokasaurus/common_types.py:89, where the
+        # default is 8; here every step ahead is a row wasted for a request that ends on a stop token)
+        self.steps_ahead = max(0, int(cfg.scheduling_steps_ahead)) if run_ahead else 0
         self.sampler = Sampler(self.runner.rt.device, max(64, cfg.max_seqs_per_forward, cfg.cudagraph_max_size),
-                               cfg.enable_chosen_logprobs)
+                               cfg.enable_chosen_logprobs, landing_places=self.steps_ahead + 2)
         self.graphs = None
         if cfg.use_cudagraphs and self.runner.rt.device.type == "cuda":
             from tokasaurus_b200.engine.graphs import DecodeGraphs
 
             self.graphs = DecodeGraphs(self.runner, self.sampler, cfg.cudagraph_max_size, cfg.cudagraph_step,
-                                       graph_max_tokens, cfg.cudagraph_max_kv_indices_per_seq)
+                                       graph_max_tokens, cfg.cudagraph_max_kv_indices_per_seq,
+                                       host_buffers=self.steps_ahead + 1)
         self._auto_id = 0
-        # the reference schedules up to ``scheduling_steps_ahead`` steps before it has seen their results; this
-        # engine looks one step ahead (0 switches that off, larger values mean one)
-        self.run_ahead = run_ahead and cfg.scheduling_steps_ahead >= 1
-        self._inflight: _InFlight | None = None
+        self.run_ahead = self.steps_ahead >= 1
+        self._inflight: deque[_InFlight] = deque()  # launched steps, oldest first
         self._next_slot = 0
         self.last_step_bytes = dict(h2d=0, d2h=0)
         # a line of statistics every ``stats_report_seconds`` at level INFO, as the reference's manager reports
@@ -112,7 +117,7 @@ class Engine:
         return request_id
 
     def has_work(self) -> bool:
-        return self.scheduler.has_work() or self._inflight is not None
+        return self.scheduler.has_work() or bool(self._inflight)
 
     # ------------------------------------------------------------------ one step
     def _sampling_arrays(self, plan: StepPlan) -> dict[str, np.ndarray]:
@@ -137,23 +142,29 @@ class Engine:
 
         Decode steps that run as CUDA graphs are pipelined, as the reference overlaps its manager with its
         model worker (tokasaurus/manager/manager.py:981-1023 keeps steps queued ahead of the model): before the
-        results of step t are read, step t+1 is launched on the guess that every request of step t goes on (the
-        token it feeds is still on the device, in the last-token table).  If a request of step t ends on an
-        end-of-sequence or stop token after all, its row of step t+1 is thrown away: one wasted row, no wrong
-        result, and its pages, freed meanwhile, are not written again by anything that follows in the stream
-        before their next owner's own writes.  Ends by length are known beforehand and never guessed."""
+        results of step t are read, steps t+1 .. t+``scheduling_steps_ahead`` are launched on the guess that every
+        request of step t goes on (the token each feeds is still on the device, in the last-token table).  If a
+        request of step t ends on an end-of-sequence or stop token after all, its rows of the steps in flight are
+        thrown away: wasted rows, no wrong result, and its pages, freed meanwhile, are not written again by
+        anything that follows in the stream before their next owner's own writes.  Ends by length are known
+        beforehand and never guessed.  Steps are launched ahead only while the scheduler has nothing to decide
+        (nothing queued or mid-prompt, a page for every request); a request that arrives waits until the steps
+        in flight have been read."""
         done = self._step()
         self._report_stats()
         return done
 
     def _step(self) -> list[RequestOutput]:
-        if self._inflight is None:
+        if not self._inflight:
             done = self._start()
             if done is not None:
                 return done
-        cur = self._inflight
-        self._inflight = self._launch_following(cur) if self.run_ahead else None
-        return self._finish(cur)
+        while len(self._inflight) <= self.steps_ahead:
+            following = self._launch_following(self._inflight[-1])
+            if following is None:
+                break
+            self._inflight.append(following)
+        return self._finish(self._inflight.popleft())
 
     def _report_stats(self) -> None:
         now = time.monotonic()
@@ -176,7 +187,7 @@ class Engine:
                 prep: dict | None = None) -> _InFlight:
         padded = self.graphs.launch(prep if prep is not None else self.graphs.prepare(entries, extra))
         slot = self._next_slot
-        self._next_slot ^= 1
+        self._next_slot = (slot + 1) % len(self.sampler.host)
         self.sampler.start_read(padded, slot, self.runner.stager.status)
         return _InFlight(plan, padded, slot, self.runner.last_upload_bytes)
 
@@ -193,14 +204,17 @@ class Engine:
         extra = self._sampling_arrays(plan)
         wants_topk = any(p.seq.request.topk_logprobs for p in plan.portions if p.samples)
         if self.graphs is not None and not wants_topk:
+            prep = None
             if self.graphs.usable(entries):
-                self._inflight = self._launch(plan, entries, extra)
+                flight = self._launch(plan, entries, extra)
+            elif self.graphs.usable_general(entries) and (prep := self.graphs.prepare_general(entries, extra)) is not None:
+                flight = self._launch(plan, entries, extra, prep)
+            else:
+                flight = None
+            if flight is not None:
+                flight.produced = {id(p.seq): len(p.seq.output.completion_ids) + 1 for p in plan.portions if p.samples}
+                self._inflight.append(flight)
                 return None
-            if self.graphs.usable_general(entries):
-                prep = self.graphs.prepare_general(entries, extra)
-                if prep is not None:
-                    self._inflight = self._launch(plan, entries, extra, prep)
-                    return None
         logits = self.runner.step(entries, extra)
         R = logits.shape[0]
         ids: list[int] = []
@@ -242,21 +256,26 @@ class Engine:
         return self.scheduler.complete(plan, kept_ids, kept_lps if self.config.enable_chosen_logprobs else None, None)
 
     def _launch_following(self, cur: _InFlight) -> _InFlight | None:
-        """Launch the decode step after ``cur`` before ``cur``'s results are known: every request of ``cur`` that
-        is still running and does not end by length in ``cur`` brings the token ``cur`` samples for it.  None if
-        the scheduler has decisions to make first (something is queued or mid-prompt, a page is missing)."""
+        """Launch the decode step after ``cur`` (the newest step in flight) before ``cur``'s results are known:
+        every request of ``cur`` that is still running and does not end by length in ``cur`` brings the token
+        ``cur`` samples for it.  None if the scheduler has decisions to make first (something is queued or
+        mid-prompt, a page is missing)."""
         sched = self.scheduler
         if sched.queued or sched.prefilling:
             return None
         running = set(map(id, sched.decoding))
-        portions, entries = [], []
+        portions, entries, produced = [], [], {}
         try:
             for p in cur.plan.portions:
                 seq = p.seq
                 if id(seq) not in running:
-                    continue  # ended in the step before ``cur``
-                if len(seq.output.completion_ids) + 1 >= seq.request.max_num_tokens:
+                    continue  # ended in a step that has been read since ``cur`` was launched
+                if not p.samples:
+                    return None  # a prompt portion that goes on: the scheduler cuts the next one
+                made = cur.produced[id(seq)]
+                if made >= seq.request.max_num_tokens:
                     continue  # ends by length in ``cur``
+                produced[id(seq)] = made + 1
                 start = p.start + p.n_tokens
                 self.runner.cache.ensure_capacity(seq.id, start + 1)
                 portions.append(ScheduledPortion(seq, start, 1, True, from_device=True))
@@ -266,7 +285,9 @@ class Engine:
         if not entries or not self.graphs.usable(entries):
             return None
         plan = StepPlan(portions)
-        return self._launch(plan, entries, self._sampling_arrays(plan))
+        flight = self._launch(plan, entries, self._sampling_arrays(plan))
+        flight.produced = produced
+        return flight
 
     def warm_up(self, batch_sizes: Sequence[int] | None = None) -> int:
         """Record the CUDA graphs of decode steps before the first request needs them, as the reference records

@@ -40,10 +40,13 @@ def _pad(a: np.ndarray, n: int, fill: int = 0) -> np.ndarray:
 
 class DecodeGraphs:
     def __init__(self, runner, sampler, max_size: int, step: int, max_tokens: int = 0,
-                 max_pages_per_request: int | None = None):
+                 max_pages_per_request: int | None = None, host_buffers: int = 2):
         """``max_pages_per_request``: the reference's ``cudagraph_max_kv_indices_per_seq`` (common_types.py:117):
         a step with a request that holds more pages than this runs without a graph.  (The reference sizes its
-        graphs' block tables by it; here they are sized by the pool, so the option only keeps its meaning.)"""
+        graphs' block tables by it; here they are sized by the pool, so the option only keeps its meaning.)
+        ``host_buffers``: pinned buffers a graph's inputs take turns in, one for each step that can be in the stream
+        at a time."""
+        self.host_buffers = host_buffers
         self.max_pages_per_request = max_pages_per_request
         self.runner = runner
         self.sampler = sampler
@@ -164,7 +167,7 @@ class DecodeGraphs:
         runner = self.runner
         slot = self.graphs.get(prep["key"])
         if slot is None:
-            slot = dict(stager=Stager(runner.rt.device, 1 << 12), graph=None)
+            slot = dict(stager=Stager(runner.rt.device, 1 << 12, self.host_buffers), graph=None)
             slot["stager"].status = runner.stager.status
             self.graphs[prep["key"]] = slot
         ctx = StepContext(prep["padded"], runner.cache, runner.rt.device, slot["stager"], prep["ex"], prep["plans"])

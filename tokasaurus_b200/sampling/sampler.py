@@ -16,8 +16,9 @@ from tokasaurus_b200.kernels import ops
 
 
 class Sampler:
-    def __init__(self, device: torch.device, max_rows: int, want_logprobs: bool = True):
+    def __init__(self, device: torch.device, max_rows: int, want_logprobs: bool = True, landing_places: int = 2):
         self.device = device
+        self.landing_places = max(2, int(landing_places))
         self.want_logprobs = want_logprobs
         self.bytes_last_read = 0
         self._alloc(max_rows)
@@ -26,10 +27,10 @@ class Sampler:
         self.max_rows = n
         self.out = torch.zeros((2 * n,), dtype=torch.int32, device=self.device)
         cuda = self.device.type == "cuda"
-        # two landing places on the host, so that the results of a step can be on their way while the
-        # step before it is still being read; the last word of each holds the device's status flag
-        self.host = [torch.zeros((2 * n + 1,), dtype=torch.int32, pin_memory=cuda) for _ in range(2)]
-        self.events = [torch.cuda.Event() if cuda else None for _ in range(2)]
+        # several landing places on the host, so that the results of the steps in flight can be on their way while
+        # the step before them is still being read; the last word of each holds the device's status flag
+        self.host = [torch.zeros((2 * n + 1,), dtype=torch.int32, pin_memory=cuda) for _ in range(self.landing_places)]
+        self.events = [torch.cuda.Event() if cuda else None for _ in range(self.landing_places)]
 
     def sample(self, logits: torch.Tensor, temperature: torch.Tensor, stream_key: torch.Tensor,
                sample_pos: torch.Tensor, row_slot: torch.Tensor, last_token: torch.Tensor) -> None:
