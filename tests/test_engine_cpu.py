@@ -127,6 +127,31 @@ def test_steps_ahead_and_paced_prefill_options_reach_the_engine(cpu_kernels, tin
     assert [o.completion_ids for o in outs] == [plain.greedy(p, 6) for p in prompts]
 
 
+def test_admission_by_simulated_cache_use_through_the_entry_point(cpu_kernels, tiny_model_dirs):
+    """A pool that cannot hold every request at its longest: admitted by the simulation of future page use, the
+    requests run side by side where a worst-case reserve would take them in turn, nothing is pushed out, and the
+    tokens are the plain implementation's."""
+    d = tiny_model_dirs[0]
+    prompts = [cuttings.random_tokens(n, 256, 7 * n) for n in (20, 9, 14, 30, 5)]
+    limits = [40, 6, 8, 5, 10]
+    plain = PlainLlama(d, torch.float64)
+    want = [plain.greedy(p, m) for p, m in zip(prompts, limits)]
+    most = {}
+    for admission in ("reserve", "simulate"):
+        eng = make_engine(d, page_size=16, kv_cache_num_tokens=8 * 16, max_seqs_per_forward=8, admission=admission)
+        ids = [eng.add_request(p, max_num_tokens=m, ignore_eos=True) for p, m in zip(prompts, limits)]
+        done, most[admission] = [], 0
+        while eng.has_work():
+            done += eng.step()
+            most[admission] = max(most[admission], len(eng.scheduler.running()))
+        by_id = {o.id: o for o in done}
+        assert [by_id[i].completion_ids for i in ids] == want
+        assert eng.scheduler.stats["bumps"] == 0 and not eng.runner.cache.requests
+    assert most["simulate"] > most["reserve"]
+    with pytest.raises(ValueError, match="admission"):
+        make_engine(d, admission="optimistic")
+
+
 def test_windowed_attention_through_scheduler_and_cache(cpu_kernels, tmp_path):
     """A toy model whose attention sees a window of 21 keys (pages of 8): prompts longer than the window, decoding
     across several page releases, first with room for everything, then in a pool so small that requests are pushed

@@ -324,3 +324,82 @@ def test_prompt_portions_shrink_when_a_windowed_pool_is_short():
     with pytest.raises(RequestTooLongError, match="cache group 0"):
         small = CacheManager({0: PagedCacheNeed(1, 16, window=8)}, page_size=4, num_pages=3, max_requests=4)
         Scheduler(small, 12, 4).add_request(req(0, 40, 10))  # a window of 8 and the next token can span 4 pages
+
+
+def make_sim(num_pages, max_tokens=16, max_seqs=8, page_size=4, **kw):
+    cache = CacheManager({0: PagedCacheNeed(1, 16)}, page_size=page_size, num_pages=num_pages, max_requests=max_seqs)
+    return Scheduler(cache, max_tokens, max_seqs, sanity_checks=True, admission="simulate", **kw), cache
+
+
+def test_simulated_peak_is_the_highest_use_before_some_end():
+    """Two decoding sequences that end at different times: the peak is the larger of (both, when the first ends)
+    and (the second alone at its longest), worked out by hand."""
+    s, cache = make_sim(64)
+    s.add_request(req(0, 8, 5))    # 12 positions at most: 3 pages
+    s.add_request(req(1, 8, 21))   # 28 positions at most: 7 pages
+    s.complete(s.schedule(), [7, 7])
+    assert [q.fed for q in s.decoding] == [8, 8]
+    # r0 ends after 4 more steps with 12 tokens (3 pages) while r1 has 12 too (3 pages): 6; r1 alone at its end: 7
+    assert s._simulated_peak() == [7]
+    # a third that is as long as r0 adds 3 pages at the first end and nothing at the second
+    s.add_request(req(2, 8, 5))
+    assert s._simulated_peak([s.queued[0]]) == [9]
+    # one as long as r1, admitted now, is fed in the next step and ends one step after r1: 7 + 7 just before r1 ends
+    s.queued.clear()
+    s.add_request(req(3, 8, 21))
+    assert s._simulated_peak([s.queued[0]]) == [14]
+
+
+def test_simulated_admission_lets_in_what_a_worst_case_reserve_keeps_out():
+    """Sequences of very different lengths in a pool that cannot hold all of them at their longest at once: the
+    reserve admits them one after the other, the simulation sees that the short ones are gone before the long one
+    grows, admits them together, and still nothing is pushed out."""
+    def requests(s):
+        s.add_request(req(0, 8, 41))  # 48 positions: 12 pages at its end
+        for i in range(1, 5):
+            s.add_request(req(i, 8, 5))  # 12 positions: 3 pages each
+    cache = CacheManager({0: PagedCacheNeed(1, 16)}, page_size=4, num_pages=16, max_requests=8)
+    reserve = Scheduler(cache, 64, 8, sanity_checks=True)
+    requests(reserve)
+    reserve.schedule()
+    assert len(reserve.prefilling) == 2  # 12 + 3 of 16 pages spoken for
+    sim, cache = make_sim(16, max_tokens=64)
+    requests(sim)
+    sim.schedule()
+    assert len(sim.prefilling) == 5  # when the short ones end they hold 4 * 3 pages and the long one 3: 15
+    fin, plans = run(sim)
+    assert len(fin) == 5 and sim.stats["bumps"] == 0
+    assert cache.num_free_pages() == [16]
+
+
+def test_simulated_admission_keeps_out_what_would_not_fit():
+    sim, cache = make_sim(16, max_tokens=64)
+    sim.add_request(req(0, 8, 41))  # 12 pages at its end
+    sim.add_request(req(1, 8, 37))  # 11 pages at its end, one step before the other ends: 11 + 12 > 16
+    sim.schedule()
+    assert len(sim.prefilling) == 1 and len(sim.queued) == 1
+    fin, _ = run(sim)
+    assert [o.id for o in fin] == ["r0", "r1"] and sim.stats["bumps"] == 0
+
+
+@pytest.mark.parametrize("seed", range(4))
+def test_simulated_admission_random_workloads_never_push_out(seed):
+    """With prompts fed at the full token budget (greedy prefill) the simulation's assumptions hold, so requests
+    of random lengths arriving at random steps all end without anyone being pushed out, in pools of two sizes."""
+    import random
+    rng = random.Random(seed)
+    for pages in (24, 60):
+        sim, cache = make_sim(pages, max_tokens=32, max_seqs=6)
+        pending = [req(i, rng.randint(1, 30), rng.randint(1, 40)) for i in range(25)]
+        finished = []
+        while pending or sim.has_work():
+            for _ in range(rng.randint(0, 2)):
+                if pending:
+                    sim.add_request(pending.pop())
+            if not sim.has_work():
+                continue
+            plan = sim.schedule()
+            finished += sim.complete(plan, [7] * sum(p.samples for p in plan.portions))
+            assert all(pk <= g.allocator.num_pages for pk, g in zip(sim._simulated_peak(), cache.groups))
+        assert len(finished) == 25 and sim.stats["bumps"] == 0
+        assert cache.num_free_pages() == [pages]

@@ -43,14 +43,16 @@ class _InFlight:
 class Engine:
     def __init__(self, model: str | None = None, config: EngineConfig | None = None,
                  config_dict: dict[str, Any] | None = None, seed: int = 0, kv_reserve_fraction: float = 1.0,
-                 run_ahead: bool = True, graph_max_tokens: int = 1024, **options: Any):
+                 run_ahead: bool = True, graph_max_tokens: int = 1024, admission: str = "reserve",
+                 **options: Any):
         """``model``: folder with config.json and model.safetensors.  ``options``: fields of
         ``EngineConfig`` (the reference's option names).  ``config_dict`` with
         ``random_weights=<seed>`` builds a model without a folder.  ``run_ahead``: launch the next decode step
         before the results of the current one have been read, up to ``scheduling_steps_ahead`` steps deep (see
         ``step``).  ``graph_max_tokens``: steps with prompt
         portions of up to this many tokens are replayed from CUDA graphs of their padded shape, like decode steps
-        (0: only decode steps are)."""
+        (0: only decode steps are).  ``kv_reserve_fraction``, ``admission``: how queued requests get in
+        (``Scheduler``)."""
         cfg = config or EngineConfig()
         if model is not None:
             cfg.model = model
@@ -67,7 +69,7 @@ class Engine:
             self.runner.cache, cfg.max_tokens_per_forward, cfg.max_seqs_per_forward,
             cfg.max_num_tokens_per_request, self.runner.eos_token_ids, kv_reserve_fraction,
             cfg.bump_city_population_me, cfg.allocator_sanity_checks, cfg.greedy_prefill,
-            cfg.prefill_round_up_multiple)
+            cfg.prefill_round_up_multiple, admission)
         # steps launched beyond the one whose results are being read (tokasaurus/common_types.py:89, where the
         # default is 8; here every step ahead is a row wasted for a request that ends on a stop token)
         self.steps_ahead = max(0, int(cfg.scheduling_steps_ahead)) if run_ahead else 0

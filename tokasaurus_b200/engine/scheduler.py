@@ -30,6 +30,8 @@ from __future__ import annotations
 from collections import deque
 from dataclasses import dataclass, field
 
+import numpy as np
+
 from tokasaurus_b200.cache.manager import CacheManager
 from tokasaurus_b200.cache.pages import NoSpaceError
 from tokasaurus_b200.sampling.params import Request, RequestOutput
@@ -88,7 +90,18 @@ class Scheduler:
     def __init__(self, cache: CacheManager, max_tokens_per_forward: int, max_seqs_per_forward: int,
                  max_num_tokens_per_request: int | None = None, eos_token_ids: tuple[int, ...] = (),
                  kv_reserve_fraction: float = 1.0, bump_city_population_me: bool = False,
-                 sanity_checks: bool = False, greedy_prefill: bool = True, prefill_round_up_multiple: int = 16):
+                 sanity_checks: bool = False, greedy_prefill: bool = True, prefill_round_up_multiple: int = 16,
+                 admission: str = "reserve"):
+        """``admission``: how a queued sequence gets in.  ``"reserve"``: its prompt's pages must be free after
+        ``kv_reserve_fraction`` of what the running sequences can still ask for is set aside (1.0: the worst case,
+        nothing is ever pushed out; 0, or ``bump_city_population_me``: nothing is set aside).  ``"simulate"``: the
+        pages in use at every future step are worked out as if each sequence ran to its longest and then gave its
+        pages back, and the sequence gets in if the highest of these, with it, fits the pool
+        (``_simulated_peak``; the reference decides so, tokasaurus/manager/scheduler.py:46-216): sequences that
+        end at different times share room that a worst-case reserve counts for each of them."""
+        if admission not in ("reserve", "simulate"):
+            raise ValueError(f"admission={admission!r}: 'reserve' or 'simulate'")
+        self.admission = admission
         self.cache = cache
         self.greedy_prefill = greedy_prefill
         self.prefill_multiple = max(1, int(prefill_round_up_multiple))
@@ -190,6 +203,51 @@ class Scheduler:
             out.append(first_need + (int(max(0, self._still_needed(seq, g, first_need)) * f + 0.999999) if f > 0 else 0))
         return out
 
+    def _simulated_peak(self, candidates: list[Sequence] = ()) -> list[int]:
+        """Per cache group: the most pages in use at any step from now on, if every running sequence, and then
+        ``candidates`` (admitted now, fed after the prompts that are already on their way), decodes a token a step
+        up to its longest and gives its pages back when it ends, and no one else comes.  Between two ends the use only
+        grows, so the highest use is just before some sequence ends: these moments are looked at (all of them up to
+        256 sequences; beyond that 256 of them, each standing for the interval since the one before it with
+        everything alive in it at its length of the interval's end, which can only overstate).
+
+        What this rests on, as in the reference (``calc_block_usage_over_time``,
+        tokasaurus/manager/scheduler.py:46-216, where an early-stop predictor may shorten the lengths; here they are
+        the requests' limits, so ends on a stop token only free pages sooner): prompts go through at the step's
+        token budget in the order of admission.  If they go slower than that (a paced prefill), a sequence lives
+        longer than assumed and pushing out remains the last resort."""
+        cache = self.cache
+        seqs = self.decoding + self.prefilling + list(candidates)
+        if not seqs:
+            return [0] * len(cache.groups)
+        n_dec = len(self.decoding)
+        budget = max(1, self.max_tokens - n_dec)
+        start = np.zeros(len(seqs), dtype=np.int64)   # step at which the sequence decodes its first token
+        base = np.zeros(len(seqs), dtype=np.int64)    # tokens it has in the cache then
+        prompt_tokens = 0
+        for i, s in enumerate(seqs):
+            if i < n_dec:
+                base[i] = s.fed
+            else:
+                prompt_tokens += s.n_known - (s.fed if s in self.prefilling else 0)
+                start[i] = -(-prompt_tokens // budget)
+                base[i] = s.n_known
+        end = start + np.asarray([s.max_total() for s in seqs], dtype=np.int64) - base  # its last step
+        end = np.maximum(end, start)
+        moments = np.unique(end)
+        if moments.shape[0] > 256:
+            moments = moments[np.unique(np.linspace(0, moments.shape[0] - 1, 256).astype(np.int64))]
+        before = np.concatenate([[-1], moments[:-1]])
+        alive = end[None, :] > before[:, None]                                    # [moments, sequences]
+        at = np.minimum(moments[:, None], end[None, :])
+        tokens = base[None, :] + np.maximum(0, at - start[None, :])
+        pages = -(-tokens // cache.page_size)
+        peaks = []
+        for g, group in enumerate(cache.groups):
+            p = np.minimum(pages, self._most_live(g)) if group.need.window else pages
+            peaks.append(int((p * alive).sum(axis=1).max()))
+        return peaks
+
     def _min_free(self) -> int:
         free = self.cache.num_free_pages()
         return min(free) if free else 1 << 30
@@ -198,7 +256,14 @@ class Scheduler:
         while self.queued and len(self.prefilling) + len(self.decoding) < self.max_seqs \
                 and self.cache.slots.num_free > 0:
             seq = self.queued[0]
-            if any(room < need for room, need in zip(self._headroom(), self._admission_need(seq))):
+            if self.admission == "simulate":
+                first = [self.cache.pages_for(self._first_windowed_tokens(seq) if g.need.window else seq.n_known)
+                         for g in self.cache.groups]
+                if any(n > g.allocator.num_free for n, g in zip(first, self.cache.groups)) or \
+                        any(peak > g.allocator.num_pages
+                            for peak, g in zip(self._simulated_peak([seq]), self.cache.groups)):
+                    break
+            elif any(room < need for room, need in zip(self._headroom(), self._admission_need(seq))):
                 break
             self.queued.popleft()
             self.cache.admit(seq.id)
