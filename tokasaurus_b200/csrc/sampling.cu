@@ -256,35 +256,55 @@ sample_chunk_kernel(const float* __restrict__ logits, const float* __restrict__ 
   const int g_end = min(ngroups, g_begin + groups_per_chunk);
   Best best = {-FLT_MAX, 0x7fffffff};
   float m = -FLT_MAX, l = 0.f;
-  for (int g = g_begin + threadIdx.x; g < g_end; g += CH_THREADS) {
-    uint4 rnd = make_uint4(0, 0, 0, 0);
-    if (!greedy) rnd = Philox::run(make_uint4((uint32_t)g, pos, 0u, 0u), k2);
-    const uint32_t rr[4] = {rnd.x, rnd.y, rnd.z, rnd.w};
-    float z4[4];
-    if (g * 4 + 3 < V && ((((uintptr_t)lg) & 15) == 0)) {
-      const float4 v = *reinterpret_cast<const float4*>(lg + g * 4);
-      z4[0] = v.x; z4[1] = v.y; z4[2] = v.z; z4[3] = v.w;
-    } else {
+  const bool vec = (((uintptr_t)lg) & 15) == 0;
+  // Sixteen values a thread and pass: their loads are in flight together, and the running maximum and sum, on
+  // which every value of a one-by-one update waits, move once a pass (values that are not numbers count as -inf).
+  constexpr int PASS = 4;
+  for (int g0 = g_begin + threadIdx.x; g0 < g_end; g0 += PASS * CH_THREADS) {
+    float z[PASS][4];
 #pragma unroll
-      for (int u = 0; u < 4; u++) z4[u] = g * 4 + u < V ? lg[g * 4 + u] : -INFINITY;
-    }
-#pragma unroll
-    for (int u = 0; u < 4; u++) {
-      const int i = g * 4 + u;
-      if (i >= V) break;
-      const float z = z4[u] * inv_t;
-      if (!(z == z)) continue;
-      if (z > m) {
-        l = l * expf(m - z) + 1.f;
-        m = z;
+    for (int u = 0; u < PASS; u++) {
+      const int g = g0 + u * CH_THREADS;
+      if (g < g_end && g * 4 + 3 < V && vec) {
+        const float4 v = *reinterpret_cast<const float4*>(lg + g * 4);
+        z[u][0] = v.x; z[u][1] = v.y; z[u][2] = v.z; z[u][3] = v.w;
       } else {
-        l += expf(z - m);
+#pragma unroll
+        for (int e = 0; e < 4; e++) z[u][e] = (g < g_end && g * 4 + e < V) ? lg[g * 4 + e] : -INFINITY;
       }
-      float score = z;
-      if (!greedy) score = z + gumbel_of(rr[u]);
-      Best c = {score, i};
-      best = better(best, c);
     }
+    float top = -INFINITY;
+#pragma unroll
+    for (int u = 0; u < PASS; u++)
+#pragma unroll
+      for (int e = 0; e < 4; e++) {
+        float x = z[u][e] * inv_t;
+        x = (x == x) ? x : -INFINITY;
+        z[u][e] = x;
+        top = fmaxf(top, x);
+      }
+    if (top > m) {
+      l *= expf(m - top);
+      m = top;
+    }
+    float add = 0.f;
+#pragma unroll
+    for (int u = 0; u < PASS; u++) {
+      const int g = g0 + u * CH_THREADS;
+      uint4 rnd = make_uint4(0, 0, 0, 0);
+      if (!greedy && g < g_end) rnd = Philox::run(make_uint4((uint32_t)g, pos, 0u, 0u), k2);
+      const uint32_t rr[4] = {rnd.x, rnd.y, rnd.z, rnd.w};
+#pragma unroll
+      for (int e = 0; e < 4; e++) {
+        const float x = z[u][e];
+        add += expf(x - m);
+        if (x > -INFINITY) {
+          Best c = {greedy ? x : x + gumbel_of(rr[e]), g * 4 + e};
+          best = better(best, c);
+        }
+      }
+    }
+    l += add;
   }
   best = warp_best(best);
   const float wm = warp_max(m);
@@ -362,7 +382,7 @@ TKB_EXPORT int tkb_sample(const float* logits, const float* temperature, const u
 // are too few to fill the GPU with one block each.  nch = tkb_sample_chunks(R, V).
 TKB_EXPORT int tkb_sample_chunks(int R, int V) {
   if (R <= 0 || V < 32768) return 1;
-  int nch = (2 * sm_count() + R - 1) / R;
+  int nch = (6 * sm_count() + R - 1) / R;  // six blocks of 256 threads an SM
   if (nch > 64) nch = 64;
   const int ngroups = (V + 3) / 4;
   if (nch > ngroups / 256) nch = ngroups / 256;
