@@ -91,3 +91,17 @@ def test_plan_says_whether_some_item_is_longer_than_three_tiles():
     assert flag([100, 7]) == 0
     assert flag([2048] * 8) == 1       # items of 384 keys
     assert flag([50, 40000]) == 1
+
+
+def test_few_query_tiles_ask_for_one_head_a_block():
+    """counts[7]: a step whose portions make so few 128-query tiles that blocks of two heads would leave SMs without
+    work (one 512-token portion: 4 tiles x 16 pairs on 148 SMs) asks the portions' kernel for a block a head."""
+    def counts(q_lens, head_blocks):
+        host = SimpleNamespace(seq_q_len=np.asarray(q_lens, dtype=np.int32),
+                               seq_kv_len=np.asarray([q + 1000 for q in q_lens], dtype=np.int32))
+        return plan_attention(host, None, query_tile=128, head_blocks=head_blocks)["counts"]
+    assert counts([512], 148 // 32)[2] == 4 and counts([512], 148 // 32)[7] == 1
+    assert counts([513], 148 // 32)[7] == 0       # five tiles of 32 heads are more than the SMs
+    assert counts([1, 1, 300], 148 // 32)[7] == 1  # decoding requests make no tiles
+    assert counts([1, 1], 148 // 32)[7] == 0       # no tiles at all
+    assert counts([512], 0)[7] == 0                # a planner that was given no device

@@ -215,7 +215,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
                        const int* __restrict__ seq_kv_len, const int* __restrict__ page_indptr,
                        const int* __restrict__ page_ids, const int* __restrict__ tiles,
                        const int* __restrict__ n_tiles_ptr, int nh, int nkv, int ps, float scale_log2, int window,
-                       int* __restrict__ status, int num_pages) {
+                       int* __restrict__ status, int num_pages, int single) {
   extern __shared__ unsigned char smem_raw[];
   __shared__ __align__(8) uint64_t k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], p_full[2], pv_done[2][2], skew;
   __shared__ uint32_t tmem_slot;
@@ -232,11 +232,12 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
 
   const int s = tiles[2 * blockIdx.y], qt0 = tiles[2 * blockIdx.y + 1];
   const int group = nh / nkv;
-  const int pairs = (group + 1) >> 1;
+  // `single`: one head a block (the host asks for it when pairs would leave SMs without a block)
+  const int pairs = single ? group : (group + 1) >> 1;
   const int kvh = blockIdx.x / pairs;
   const int pair = blockIdx.x - kvh * pairs;
-  const int head0 = kvh * group + 2 * pair;
-  const int n_heads_here = 2 * pair + 1 < group ? 2 : 1;
+  const int head0 = kvh * group + (single ? pair : 2 * pair);
+  const int n_heads_here = (!single && 2 * pair + 1 < group) ? 2 : 1;
   const int q_len = seq_q_len[s], kv_len = seq_kv_len[s];
   const int rows_live = min(BQ, q_len - qt0);
   const int pos0 = kv_len - q_len + qt0;
@@ -449,7 +450,7 @@ TKB_EXPORT int tkb_attn_prefill_tc_bf16(const void* q, int q_stride, void* out, 
                                         const void* vcache, int n_pages, const int* seq_q_start, const int* seq_q_len,
                                         const int* seq_kv_len, const int* page_indptr, const int* page_ids,
                                         const int* tiles, const int* n_tiles_ptr, int tiles_cap, int nh, int nkv, int ps,
-                                        float scale, int window, int* status, void* st) {
+                                        float scale, int window, int single, int* status, void* st) {
   if (tiles_cap <= 0) return 0;
   if (nkv <= 0 || nh % nkv != 0 || ps <= 0 || (q_stride & 7) || (out_stride & 7)) return -2;
   if (tiles_cap > 65535) return -3;
@@ -472,10 +473,10 @@ TKB_EXPORT int tkb_attn_prefill_tc_bf16(const void* q, int q_stride, void* out, 
     if (rc == 0) rc = make_map(&map_v, vcache, (int)rows, HD, HD, tma_rows);
     if (rc != 0) return rc;
   }
-  const int pairs = (nh / nkv + 1) / 2;
+  const int pairs = single ? nh / nkv : (nh / nkv + 1) / 2;
   dim3 grid(nkv * pairs, tiles_cap);  // the head pairs of one query tile are neighbours: long tiles start first
   return launch_pdl(attn_prefill_tc_kernel, grid, dim3(THREADS), (size_t)SMEM_BYTES, (cudaStream_t)st, map_k, map_v,
                     tma_rows, (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)kcache, (const bf16*)vcache,
                     seq_q_start, seq_q_len, seq_kv_len, page_indptr, page_ids, tiles, n_tiles_ptr, nh, nkv, ps,
-                    scale * 1.4426950408889634f, window, status, n_pages);
+                    scale * 1.4426950408889634f, window, status, n_pages, single ? 1 : 0);
 }

@@ -110,7 +110,8 @@ class DecodeGraphs:
                 return None
             caps[key] = c
         key = ("general", tp, sp, tuple(page_caps),
-               tuple(sorted((str(k), tuple(sorted(c.items())), int(raw[k]["counts"][5]), int(raw[k]["counts"][6]))
+               tuple(sorted((str(k), tuple(sorted(c.items())), int(raw[k]["counts"][5]), int(raw[k]["counts"][6]),
+                             int(raw[k]["counts"][7]))
                             for k, c in caps.items())))
         plans = {k: planners[k].pad_plan(p, caps[k]) for k, p in raw.items()}
         last = [int(ip[-1]) for ip in host.table_indptr]

@@ -522,10 +522,12 @@ def attn_prefill_tc(qkv: torch.Tensor, out: torch.Tensor, kcache: torch.Tensor, 
                     seq_q_start: torch.Tensor, seq_q_len: torch.Tensor, seq_kv_len: torch.Tensor,
                     page_indptr: torch.Tensor, page_ids: torch.Tensor, tiles: torch.Tensor, n_tiles: torch.Tensor,
                     tiles_cap: int, n_heads: int, n_kv_heads: int, head_dim: int, page_size: int, scale: float,
-                    window: int | None, status: torch.Tensor) -> None:
+                    window: int | None, status: torch.Tensor, single_heads: bool = False) -> None:
     """bfloat16 causal attention for prompt portions on tcgen05 tensor cores (head sizes 64 and 128): ``tiles`` are
     (request row, first query of a 128-query tile within the portion) pairs; results go to ``out``
-    [T, n_heads*head_dim] at the token rows.  ``status`` collects a wait that ran out."""
+    [T, n_heads*head_dim] at the token rows.  ``status`` collects a wait that ran out.  A block takes two query
+    heads of a kv head; ``single_heads``: one (twice the blocks, for steps whose tiles are too few to give every
+    SM a pair)."""
     _need_cuda(qkv, out, kcache, vcache, seq_q_start, seq_q_len, seq_kv_len, page_indptr, page_ids, tiles, n_tiles,
                status)
     _need(head_dim in ATTN_PREFILL_TC_KERNELS,
@@ -543,7 +545,7 @@ def attn_prefill_tc(qkv: torch.Tensor, out: torch.Tensor, kcache: torch.Tensor, 
         _ptr(qkv), c_int(qkv.stride(0)), _ptr(out), c_int(out.shape[1]), _ptr(kcache), _ptr(vcache),
         c_int(kcache.shape[0]), _ptr(seq_q_start), _ptr(seq_q_len), _ptr(seq_kv_len), _ptr(page_indptr), _ptr(page_ids),
         _ptr(tiles), _ptr(n_tiles), c_int(tiles_cap), c_int(n_heads), c_int(n_kv_heads), c_int(page_size), c_float(scale),
-        c_int(window or 0), _ptr(status), _stream()), "attn_prefill_tc")
+        c_int(window or 0), c_int(1 if single_heads else 0), _ptr(status), _stream()), "attn_prefill_tc")
 
 
 def sample(logits: torch.Tensor, temperature: torch.Tensor | None, stream_key: torch.Tensor | None,

@@ -73,10 +73,12 @@ def split_keys_evenly(span: np.ndarray, blocks_per_item: int, slots: int = DECOD
 
 
 def plan_attention(host, window: int | None, capacity: dict | None = None, blocks_per_item: int = 8,
-                   query_tile: int = QUERY_TILE, slots: int = DECODE_BLOCK_SLOTS) -> dict[str, np.ndarray]:
+                   query_tile: int = QUERY_TILE, slots: int = DECODE_BLOCK_SLOTS,
+                   head_blocks: int = 0) -> dict[str, np.ndarray]:
     """Work items for one step: (request row, first key, keys) triples for requests with one token,
     (request row, first query) pairs for ``query_tile``-query tiles of longer portions.  ``blocks_per_item``:
-    blocks the split-key kernel launches per item (kv heads x head tiles)."""
+    blocks the split-key kernel launches per item (kv heads x head tiles).  ``head_blocks``: how many query tiles
+    a step may have for the portions' kernel to give every query head a block of its own (0: never)."""
     q_len = np.asarray(host.seq_q_len, dtype=np.int64)
     kv_len = np.asarray(host.seq_kv_len, dtype=np.int64)
     dec_seqs = np.nonzero(q_len == 1)[0]
@@ -131,8 +133,10 @@ def plan_attention(host, window: int | None, capacity: dict | None = None, block
     # tiles of 64 keys; the split-key kernel then runs in the variant that fetches whole tiles by TMA
     long_items = int(n_items > 0 and int(item_size.max()) > 3 * 64)
     long_row_items = int(n_row_items > 0 and int(r_isize.max()) > 3 * 64)
-    counts = np.asarray([n_items, dec_seqs.shape[0], n_tiles, n_row_items, n_rows, long_items, long_row_items, 0],
-                        dtype=np.int32)
+    # counts[7]: so few query tiles that blocks of two heads would leave SMs idle: one head a block
+    few_tiles = int(0 < n_tiles <= head_blocks)
+    counts = np.asarray([n_items, dec_seqs.shape[0], n_tiles, n_row_items, n_rows, long_items, long_row_items,
+                         few_tiles], dtype=np.int32)
 
     def padded(x, n):
         a = np.zeros(max(n, x.shape[0], 1), dtype=np.int32)
@@ -173,6 +177,7 @@ class PagedAttention(Mixer):
         self.inv_freq: torch.Tensor | None = None
         self.dtype: torch.dtype | None = None
         self.block_slots = decode_block_slots(head_dim)  # bind() asks the device
+        self.sm_count = 0
 
     # --- declarations ---
     def weight_specs(self):
@@ -208,6 +213,9 @@ class PagedAttention(Mixer):
         self.inv_freq = inv.to(rt.device) if inv is not None else None
         self.dtype = rt.dtype
         self.block_slots = decode_block_slots(self.head_dim, getattr(rt, "limits", None))
+        from tokasaurus_b200.kernels.device import NO_DEVICE
+
+        self.sm_count = (getattr(rt, "limits", None) or NO_DEVICE).sm_count
 
     def plan_key(self):
         if self.dtype != torch.bfloat16:
@@ -222,7 +230,7 @@ class PagedAttention(Mixer):
 
     def plan(self, host, capacity=None):
         return plan_attention(host, self.window, capacity, self._blocks_per_item(), self._query_tile(),
-                              self.block_slots)
+                              self.block_slots, self.sm_count // self.n_heads)
 
     def plan_capacity(self, n_requests: int) -> dict:
         """The most work items ``plan`` can make for a step of ``n_requests`` single-token requests, whatever
@@ -341,7 +349,7 @@ class PagedAttention(Mixer):
         if tiles_cap and self._query_tile() == QUERY_TILE_TC:
             ops.attn_prefill_tc(qkv, attn, cache.k, cache.v, ctx.seq_q_start, ctx.seq_q_len, ctx.seq_kv_len,
                                 tables.indptr, tables.page_ids, plan["tiles"], c[2:3], tiles_cap, nh, nkv, hd,
-                                cache.page_size, self.scale, self.window, ctx.status)
+                                cache.page_size, self.scale, self.window, ctx.status, single_heads=bool(counts[7]))
         elif tiles_cap:
             ops.attn_prefill_mma(qkv, attn, cache.k, cache.v, ctx.seq_q_start, ctx.seq_q_len, ctx.seq_kv_len,
                                  tables.indptr, tables.page_ids, plan["tiles"], c[2:3], tiles_cap, nh, nkv, hd,
