@@ -331,7 +331,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
       bool ok = true;
       auto issue_qk = [&](int j) {
         const int kb = j & 1;
-        if (!mbar_wait(&k_full[kb], (j >> 1) & 1)) return false;
+        if (!mbar_wait_idle(&k_full[kb], (j >> 1) & 1)) return false;
         tcgen05_fence_after();
         const uint64_t dk = desc_k0 + (uint64_t)(kb * (KV_BYTES / 16));
 #pragma unroll
@@ -344,9 +344,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
       ok = issue_qk(0);
       for (int j = 0; j < n_kv_tiles && ok; j++) {
         const int vb = j & 1;
-        if (!mbar_wait(&p_full[hh], j & 1)) { ok = false; break; }
+        if (!mbar_wait_idle(&p_full[hh], j & 1)) { ok = false; break; }
         if (j + 1 < n_kv_tiles && !issue_qk(j + 1)) { ok = false; break; }
-        if (!mbar_wait(&v_full[vb], (j >> 1) & 1)) { ok = false; break; }
+        if (!mbar_wait_idle(&v_full[vb], (j >> 1) & 1)) { ok = false; break; }
         tcgen05_fence_after();
         const uint64_t dp = desc_p0 + (uint64_t)(vb * (P_BYTES / 16)), dv = desc_v0 + (uint64_t)(vb * (KV_BYTES / 16));
 #pragma unroll
