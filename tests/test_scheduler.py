@@ -403,3 +403,23 @@ def test_simulated_admission_random_workloads_never_push_out(seed):
             assert all(pk <= g.allocator.num_pages for pk, g in zip(sim._simulated_peak(), cache.groups))
         assert len(finished) == 25 and sim.stats["bumps"] == 0
         assert cache.num_free_pages() == [pages]
+
+
+def test_many_sequences_are_told_apart_by_identity_and_stage():
+    """Six hundred sequences with the same prompt at once: the scheduler's membership questions are answered by a
+    sequence's stage and identity (two sequences with equal fields are different sequences), so a step's decisions
+    take time in proportion to the sequences, and every one of them ends with its own tokens."""
+    import time
+    s, cache = make(num_pages=600 * 8, page_size=4, max_tokens=4096, max_seqs=600)
+    seqs = [s.add_request(Request(f"same{i}", [1, 2, 3, 4, 5], 20, SamplingParams())) for i in range(600)]
+    assert seqs[0] != seqs[1] and seqs[0] == seqs[0]
+    assert {q.stage for q in seqs} == {"queued"}
+    t0 = time.perf_counter()
+    plan = s.schedule()
+    assert {q.stage for q in seqs} == {"prefilling"} and len(plan.portions) == 600
+    s.complete(plan, list(range(600)))
+    assert {q.stage for q in seqs} == {"decoding"}
+    fin, plans = run(s, token=lambda seq: seq.index)
+    assert len(fin) == 600 and all(o.completion_ids[1:] == [int(o.id[4:])] * 19 for o in fin)
+    assert {q.stage for q in seqs} == {"queued"} and not s._live_ids
+    assert time.perf_counter() - t0 < 20.0  # 21 steps of 600 sequences: seconds even on a slow machine, not minutes

@@ -41,13 +41,14 @@ class RequestTooLongError(ValueError):
     pass
 
 
-@dataclass
+@dataclass(eq=False)  # a sequence equals itself only: membership tests compare identities, not token lists
 class Sequence:
     request: Request
     index: int  # running number of the request within the engine (random stream, admission order)
     output: RequestOutput
     fed: int = 0  # tokens of prompt + completion that have gone through the model
     admitted_at: int = -1
+    stage: str = "queued"  # "queued", "prefilling" or "decoding": which of the scheduler's lists holds it
 
     @property
     def id(self) -> str:
@@ -114,6 +115,7 @@ class Scheduler:
         self.queued: deque[Sequence] = deque()
         self.prefilling: list[Sequence] = []
         self.decoding: list[Sequence] = []
+        self._live_ids: set[str] = set()  # ids of the requests that are queued or running
         self._counter = 0
         self._admissions = 0
         self.stats = dict(steps=0, prefill_tokens=0, decode_tokens=0, bumps=0, finished=0)
@@ -139,11 +141,12 @@ class Scheduler:
                 raise RequestTooLongError(
                     f"request {request.id!r} can need {need} pages of cache group {g}, its pool has "
                     f"{group.allocator.num_pages}")
-        if any(s.id == request.id for s in self.queued) or any(s.id == request.id for s in self.running()):
+        if request.id in self._live_ids:
             raise ValueError(f"request id {request.id!r} is already queued or running (the cache is keyed by it)")
         seq = Sequence(request, self._counter, RequestOutput(request.id))
         self._counter += 1
         self.queued.append(seq)
+        self._live_ids.add(request.id)
         return seq
 
     def has_work(self) -> bool:
@@ -229,7 +232,7 @@ class Scheduler:
             if i < n_dec:
                 base[i] = s.fed
             else:
-                prompt_tokens += s.n_known - (s.fed if s in self.prefilling else 0)
+                prompt_tokens += s.n_known - (s.fed if s.stage == "prefilling" else 0)
                 start[i] = -(-prompt_tokens // budget)
                 base[i] = s.n_known
         end = start + np.asarray([s.max_total() for s in seqs], dtype=np.int64) - base  # its last step
@@ -253,6 +256,7 @@ class Scheduler:
         return min(free) if free else 1 << 30
 
     def _admit(self) -> None:
+        room = None  # the headroom, worked out once and kept up to date while sequences get in
         while self.queued and len(self.prefilling) + len(self.decoding) < self.max_seqs \
                 and self.cache.slots.num_free > 0:
             seq = self.queued[0]
@@ -263,14 +267,20 @@ class Scheduler:
                         any(peak > g.allocator.num_pages
                             for peak, g in zip(self._simulated_peak([seq]), self.cache.groups)):
                     break
-            elif any(room < need for room, need in zip(self._headroom(), self._admission_need(seq))):
-                break
+            else:
+                if room is None:
+                    room = self._headroom()
+                need = self._admission_need(seq)
+                if any(r < n for r, n in zip(room, need)):
+                    break
+                room = [r - n for r, n in zip(room, need)]
             self.queued.popleft()
             self.cache.admit(seq.id)
             self.cache.ensure_capacity(seq.id, seq.n_known, windowed_tokens=self._first_windowed_tokens(seq))
             seq.fed = 0
             seq.admitted_at = self._admissions
             self._admissions += 1
+            seq.stage = "prefilling"
             self.prefilling.append(seq)
 
     def _bump_one(self, protect: Sequence) -> Sequence | None:
@@ -287,10 +297,11 @@ class Scheduler:
         return victim
 
     def _release(self, seq: Sequence) -> None:
-        if seq in self.decoding:
+        if seq.stage == "decoding":
             self.decoding.remove(seq)
-        if seq in self.prefilling:
+        elif seq.stage == "prefilling":
             self.prefilling.remove(seq)
+        seq.stage = "queued"
         self.cache.free(seq.id)
 
     # ------------------------------------------------------------------ one step
@@ -298,7 +309,7 @@ class Scheduler:
         plan = StepPlan()
         # 1. pages for the next token of every decoding sequence, pushing sequences out if the pool is dry
         for seq in sorted(self.decoding, key=lambda s: s.admitted_at):
-            if seq not in self.decoding:
+            if seq.stage != "decoding":
                 continue  # was pushed out a moment ago
             while True:
                 try:
@@ -323,7 +334,7 @@ class Scheduler:
         for seq in list(self.prefilling):
             if budget <= 0:
                 break
-            if seq not in self.prefilling:
+            if seq.stage != "prefilling":
                 continue  # was pushed out a moment ago
             n = self._fit_portion(seq, min(budget, seq.n_known - seq.fed))
             while n == 0 and not plan.portions:
@@ -439,9 +450,10 @@ class Scheduler:
                 seq.output.topk_ids.append(topk[k][0][: seq.request.topk_logprobs])
                 seq.output.topk_logprobs.append(topk[k][1][: seq.request.topk_logprobs])
             k += 1
-            if seq in self.prefilling:
+            if seq.stage == "prefilling":
                 self.prefilling.remove(seq)
                 self.decoding.append(seq)
+                seq.stage = "decoding"
             reason = None
             if (not seq.request.ignore_eos and tok in self.eos) or tok in seq.request.stop_token_ids:
                 reason = "stop"
@@ -450,6 +462,7 @@ class Scheduler:
             if reason:
                 seq.output.finish_reason = reason
                 self._release(seq)
+                self._live_ids.discard(seq.id)
                 finished.append(seq.output)
                 self.stats["finished"] += 1
         if k != len(sampled):
