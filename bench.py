@@ -413,6 +413,28 @@ def run_ours(args) -> dict:
                h2d_bytes_per_step=h2d // e2e_steps, d2h_bytes_per_step=d2h // e2e_steps,
                ms_per_step=round(e2e_ms, 4))
 
+    if not args.skip_points:
+        # many requests through the entry point: 256 requests of 512 + 128 tokens, all of them admitted at once
+        # (prompt portions under the token budget, then decode steps of up to 256 requests from step graphs)
+        n_req, n_prompt, n_gen = 256, 512, 128
+        del eng
+        serve = Engine(config_dict=cfg, random_weights=0, dtype="bfloat16", page_size=page_size,
+                       kv_cache_num_tokens=n_req * (n_prompt + n_gen + 64), max_tokens_per_forward=8192,
+                       max_seqs_per_forward=n_req, cudagraph_max_size=n_req)
+        many = [tokens(n_prompt) for _ in range(n_req)]
+        greedy = SamplingParams(temperature=0.0)
+        serve.warm_up()  # the decode graphs of every batch size, as a server records them when it starts
+        serve.generate(many, greedy, max_num_tokens=4, ignore_eos=True)
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        serve.generate(many, greedy, max_num_tokens=n_gen, ignore_eos=True)
+        torch.cuda.synchronize()
+        points["engine_256_requests_512p128_total"] = round(n_req * (n_prompt + n_gen) / (time.perf_counter() - t0), 1)
+        cuda_graphs = serve.graphs is not None
+        del serve
+    else:
+        cuda_graphs = eng.graphs is not None
+
     out = {
         "metric": "decode tokens/s (Llama-3.2-1B sizes, batch 8, 2,048-token prompts)",
         "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
@@ -424,7 +446,7 @@ def run_ours(args) -> dict:
             "parallelism": "1 GPU", "layers": layers, "layers_full": full_layers, "hidden": m["H"], "heads": m["nh"],
             "kv_heads": m["nkv"], "head_dim": m["hd"], "intermediate": m["I"], "vocab": m["V"], "page_size": page_size,
             "tied_embeddings": True, "rope": "llama3 factor 32", "l2": "inputs (2.5 GB of weights) larger than L2; no flush",
-            "cuda_graphs": eng.graphs is not None, "timed_blocks": len(blocks),
+            "cuda_graphs": cuda_graphs, "timed_blocks": len(blocks),
         },
         "e2e": e2e, "gpu_launches": launches, "clocks": clock_info, "prefill": prefill, "roofline": roofline,
         "points": points, "block_ms": [round(b, 4) for b in blocks],
