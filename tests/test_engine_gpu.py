@@ -75,6 +75,57 @@ def test_pushed_out_requests_give_the_same_tokens(tiny_model_dirs):
     assert [o.completion_ids for o in outs] == want
 
 
+@pytest.mark.parametrize("seed", [0, 1])
+def test_random_arrivals_in_a_small_pool_every_way_of_running(tiny_model_dirs, seed):
+    """Thirty requests of random lengths and limits, some with stop tokens, arriving at random steps into a pool
+    of 128 tokens, which holds a few of them at a time: worst-case reserve, no reserve (requests are pushed out and fed again) and
+    admission by simulation; with step graphs and three steps of run-ahead, and without either.  Greedy float32
+    tokens equal the plain implementation's every time, and every page and slot comes back."""
+    import random
+    from tokasaurus_b200 import SamplingParams
+
+    cfg_index = seed % 2
+    d = tiny_model_dirs[cfg_index]
+    vocab = PlainLlama(d).cfg["vocab_size"]
+    page = TINY_WEIGHTS[cfg_index]["page_size"]
+    rng = random.Random(100 + seed)
+    reqs = [(cuttings.random_tokens(rng.randint(1, 70), vocab, 1000 * seed + i), rng.randint(1, 25)) for i in range(30)]
+    plain = PlainLlama(d, torch.float64)
+    full = [plain.greedy(p, m) for p, m in reqs]
+    stops, want = [], []
+    for i, f in enumerate(full):
+        if i % 4 == 0 and len(f) > 3:  # stops where it first produces its fourth token
+            stops.append([f[3]])
+            want.append(f[: f.index(f[3]) + 1])
+        else:
+            stops.append([])
+            want.append(f)
+    arrive = sorted(rng.randint(0, 40) for _ in reqs)
+    ways = [dict(), dict(bump_city_population_me=True), dict(admission="simulate"),
+            dict(use_cudagraphs=False, scheduling_steps_ahead=0, bump_city_population_me=True),
+            dict(scheduling_steps_ahead=3, admission="simulate", greedy_prefill=False, prefill_round_up_multiple=4)]
+    for way in ways:
+        eng = make_engine(d, page_size=page, kv_cache_num_tokens=128, max_seqs_per_forward=6,
+                          max_tokens_per_forward=48, cudagraph_max_size=8, cudagraph_step=4,
+                          **{"scheduling_steps_ahead": 3, **way})
+        ids, done, step, nxt = [], [], 0, 0
+        while nxt < len(reqs) or eng.has_work():
+            while nxt < len(reqs) and arrive[nxt] <= step:
+                p, m = reqs[nxt]
+                ids.append(eng.add_request(p, SamplingParams(), max_num_tokens=m, ignore_eos=True,
+                                           stop_token_ids=stops[nxt]))
+                nxt += 1
+            if eng.has_work():
+                done += eng.step()
+            step += 1
+        by_id = {o.id: o for o in done}
+        assert [by_id[i].completion_ids for i in ids] == want, f"way {way}"
+        assert not eng.runner.cache.requests and not eng.has_work()
+        assert eng.runner.cache.num_free_pages() == [g.allocator.num_pages for g in eng.runner.cache.groups]
+        if way.get("bump_city_population_me"):
+            assert eng.scheduler.stats["bumps"] > 0, f"way {way}: the pool was meant to be too small"
+
+
 def test_temperature_sampling_seeded(tiny_model_dirs):
     from tokasaurus_b200 import SamplingParams
 
