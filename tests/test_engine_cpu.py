@@ -152,6 +152,36 @@ def test_admission_by_simulated_cache_use_through_the_entry_point(cpu_kernels, t
         make_engine(d, admission="optimistic")
 
 
+def test_random_arrivals_in_a_small_pool(cpu_kernels, tiny_model_dirs):
+    """Sixteen requests of random lengths and limits arriving at random steps into a pool of 96 tokens, under the
+    worst-case reserve, with no reserve (requests are pushed out and fed again), under admission by simulation and
+    with a paced prefill: the plain implementation's greedy tokens every time, and every page given back."""
+    import random
+
+    d = tiny_model_dirs[1]
+    rng = random.Random(5)
+    reqs = [(cuttings.random_tokens(rng.randint(1, 60), 509, 70 + i), rng.randint(1, 16)) for i in range(16)]
+    plain = PlainLlama(d, torch.float64)
+    want = [plain.greedy(p, m) for p, m in reqs]
+    arrive = sorted(rng.randint(0, 25) for _ in reqs)
+    for way in (dict(), dict(bump_city_population_me=True), dict(admission="simulate"),
+                dict(admission="simulate", greedy_prefill=False, prefill_round_up_multiple=4)):
+        eng = make_engine(d, page_size=8, kv_cache_num_tokens=96, max_seqs_per_forward=5, max_tokens_per_forward=40, **way)
+        ids, done, step, nxt = [], [], 0, 0
+        while nxt < len(reqs) or eng.has_work():
+            while nxt < len(reqs) and arrive[nxt] <= step:
+                ids.append(eng.add_request(reqs[nxt][0], max_num_tokens=reqs[nxt][1], ignore_eos=True))
+                nxt += 1
+            if eng.has_work():
+                done += eng.step()
+            step += 1
+        by_id = {o.id: o for o in done}
+        assert [by_id[i].completion_ids for i in ids] == want, f"way {way}"
+        assert not eng.runner.cache.requests and eng.runner.cache.num_free_pages() == [12]
+        if way.get("bump_city_population_me"):
+            assert eng.scheduler.stats["bumps"] > 0
+
+
 def test_windowed_attention_through_scheduler_and_cache(cpu_kernels, tmp_path):
     """A toy model whose attention sees a window of 21 keys (pages of 8): prompts longer than the window, decoding
     across several page releases, first with room for everything, then in a pool so small that requests are pushed
