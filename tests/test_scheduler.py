@@ -423,3 +423,31 @@ def test_many_sequences_are_told_apart_by_identity_and_stage():
     assert len(fin) == 600 and all(o.completion_ids[1:] == [int(o.id[4:])] * 19 for o in fin)
     assert {q.stage for q in seqs} == {"queued"} and not s._live_ids
     assert time.perf_counter() - t0 < 20.0  # 21 steps of 600 sequences: seconds even on a slow machine, not minutes
+
+
+@pytest.mark.parametrize("seed", range(12))
+def test_simulated_peak_is_what_really_happens(seed):
+    """Random sets of requests, all admitted, some in mid-prompt: the most pages the cache really holds from then on
+    (no one else comes, prompts fed greedily) is exactly the simulated peak."""
+    import random
+    rng = random.Random(seed)
+    cache = CacheManager({0: PagedCacheNeed(1, 16)}, page_size=4, num_pages=4000, max_requests=40)
+    s = Scheduler(cache, 24, 40, sanity_checks=True, admission="simulate")
+    for i in range(rng.randint(3, 30)):
+        s.add_request(req(i, rng.randint(1, 50), rng.randint(1, 60)))
+    for _ in range(rng.randint(1, 4)):  # a few steps in: some decode, some are in mid-prompt, some still queued
+        plan = s.schedule()
+        s.complete(plan, [7] * sum(p.samples for p in plan.portions))
+    while s.queued:  # everyone in (the pool is large); what follows is what the simulation speaks about
+        plan = s.schedule()
+        s.complete(plan, [7] * sum(p.samples for p in plan.portions))
+        if not s.has_work():
+            return
+    predicted = s._simulated_peak()[0]
+    used = lambda: cache.groups[0].allocator.num_pages - cache.groups[0].allocator.num_free  # noqa: E731
+    most = used()
+    while s.has_work():
+        plan = s.schedule()
+        most = max(most, used())
+        s.complete(plan, [7] * sum(p.samples for p in plan.portions))
+    assert most == predicted  # under a greedy prefill the simulation is what happens

@@ -27,6 +27,7 @@ tokasaurus/manager/scheduler.py:576-637 ``schedule``, :640-684 ``apply_decision`
 
 from __future__ import annotations
 
+import bisect
 from collections import deque
 from dataclasses import dataclass, field
 
@@ -216,25 +217,39 @@ class Scheduler:
 
         What this rests on, as in the reference (``calc_block_usage_over_time``,
         tokasaurus/manager/scheduler.py:46-216, where an early-stop predictor may shorten the lengths; here they are
-        the requests' limits, so ends on a stop token only free pages sooner): prompts go through at the step's
-        token budget in the order of admission.  If they go slower than that (a paced prefill), a sequence lives
-        longer than assumed and pushing out remains the last resort."""
+        the requests' limits, so ends on a stop token only free pages sooner): prompts go through as a greedy
+        prefill feeds them, in the order of admission.  If they go slower than that (a paced prefill), a sequence
+        lives longer than assumed and pushing out remains the last resort."""
         cache = self.cache
         seqs = self.decoding + self.prefilling + list(candidates)
         if not seqs:
             return [0] * len(cache.groups)
         n_dec = len(self.decoding)
-        budget = max(1, self.max_tokens - n_dec)
         start = np.zeros(len(seqs), dtype=np.int64)   # step at which the sequence decodes its first token
         base = np.zeros(len(seqs), dtype=np.int64)    # tokens it has in the cache then
-        prompt_tokens = 0
-        for i, s in enumerate(seqs):
-            if i < n_dec:
-                base[i] = s.fed
-            else:
-                prompt_tokens += s.n_known - (s.fed if s.stage == "prefilling" else 0)
-                start[i] = -(-prompt_tokens // budget)
-                base[i] = s.n_known
+        for i, s in enumerate(self.decoding):
+            base[i] = s.fed
+        # The prompts, step by step as a greedy prefill feeds them: what the decoding sequences leave of the token
+        # budget goes to the prompts in order, and a prompt that is through decodes from the next step on (and takes
+        # a token of the budget itself).
+        ends = sorted(s.max_total() - s.fed for s in self.decoding)   # a decoding sequence runs in steps 0 .. end - 1
+        through: list[tuple[int, int]] = []                           # (first, one past the last) decoding step
+        left = [s.n_known - (s.fed if s.stage == "prefilling" else 0) for s in seqs[n_dec:]]
+        at, k = 0, 0
+        while at < len(left):
+            running = len(ends) - bisect.bisect_right(ends, k) + sum(1 for a, b in through if a <= k < b)
+            budget = self.max_tokens - running
+            while budget > 0 and at < len(left):
+                take = min(budget, left[at])
+                left[at] -= take
+                budget -= take
+                if left[at] == 0:
+                    s = seqs[n_dec + at]
+                    start[n_dec + at] = k + 1
+                    base[n_dec + at] = s.n_known
+                    through.append((k + 1, k + 1 + s.max_total() - s.n_known))
+                    at += 1
+            k += 1
         end = start + np.asarray([s.max_total() for s in seqs], dtype=np.int64) - base  # its last step
         end = np.maximum(end, start)
         moments = np.unique(end)
