@@ -150,6 +150,10 @@ def test_admission_by_simulated_cache_use_through_the_entry_point(cpu_kernels, t
     assert most["simulate"] > most["reserve"]
     with pytest.raises(ValueError, match="admission"):
         make_engine(d, admission="optimistic")
+    # the simulation is what an engine admits by unless it is asked for the optimistic reserve
+    assert make_engine(d).scheduler.admission == "simulate"
+    assert make_engine(d, bump_city_population_me=True).scheduler.admission == "reserve"
+    assert make_engine(d, kv_reserve_fraction=0.5).scheduler.admission == "reserve"
 
 
 def test_random_arrivals_in_a_small_pool(cpu_kernels, tiny_model_dirs):

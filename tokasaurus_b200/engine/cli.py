@@ -83,7 +83,7 @@ def main(argv: list[str] | None = None) -> int:
     # the engine's statistics lines (level INFO, every stats_report_seconds) go to the standard error stream
     logging.basicConfig(stream=sys.stderr, format="[toka] %(message)s")
     engine = Engine(config=cfg, seed=opts.get("seed") or 0, kv_reserve_fraction=opts.get("kv_reserve_fraction", 1.0),
-                    admission=opts.get("admission") or "reserve")
+                    admission=opts.get("admission"))
     sp = SamplingParams(temperature=opts.get("temperature") or 0.0, seed=opts.get("seed"))
     t0 = time.time()
     outs = engine.generate(prompts, sp, max_num_tokens=opts.get("max_num_tokens") or 16,

@@ -43,7 +43,7 @@ class _InFlight:
 class Engine:
     def __init__(self, model: str | None = None, config: EngineConfig | None = None,
                  config_dict: dict[str, Any] | None = None, seed: int = 0, kv_reserve_fraction: float = 1.0,
-                 run_ahead: bool = True, graph_max_tokens: int = 1024, admission: str = "reserve",
+                 run_ahead: bool = True, graph_max_tokens: int = 1024, admission: str | None = None,
                  **options: Any):
         """``model``: folder with config.json and model.safetensors.  ``options``: fields of
         ``EngineConfig`` (the reference's option names).  ``config_dict`` with
@@ -52,7 +52,8 @@ class Engine:
         ``step``).  ``graph_max_tokens``: steps with prompt
         portions of up to this many tokens are replayed from CUDA graphs of their padded shape, like decode steps
         (0: only decode steps are).  ``kv_reserve_fraction``, ``admission``: how queued requests get in
-        (``Scheduler``)."""
+        (``Scheduler``); by default by a simulation of future page use, as the reference admits, unless a reserve
+        fraction below 1 or ``bump_city_population_me`` asks for the optimistic reserve."""
         cfg = config or EngineConfig()
         if model is not None:
             cfg.model = model
@@ -62,6 +63,8 @@ class Engine:
             setattr(cfg, k, v)
         if cfg.max_seqs_per_forward > cfg.max_tokens_per_forward:
             cfg.max_seqs_per_forward = cfg.max_tokens_per_forward
+        if admission is None:
+            admission = "reserve" if (kv_reserve_fraction != 1.0 or cfg.bump_city_population_me) else "simulate"
         self.config = cfg
         self.seed = seed
         self.runner = ModelRunner(cfg, config_dict)
