@@ -16,6 +16,9 @@ tokasaurus/manager/scheduler.py:576-637 ``schedule``, :640-684 ``apply_decision`
   running request can still come to need (no request is ever pushed out); smaller values admit
   more and rely on the next rule; ``bump_city_population_me`` (the reference's debugging flag,
   common_types.py:125) sets nothing aside.
+  With ``admission="simulate"`` the request enters instead when the pages in use at every future step,
+  worked out as if every running request went on to its limit, stay within the pool with it
+  (``calc_block_usage_over_time`` and the onboarding around it, scheduler.py:46-216, manager.py:486-656).
 * When a decoding sequence needs a page and none is free, the most recently admitted running
   sequence is pushed out ("bumped", manager.py:745-813): its pages and slot are given back and it
   returns to the HEAD of the queue.  Unlike the reference, which restarts it from the bare prompt
@@ -271,32 +274,68 @@ class Scheduler:
         return min(free) if free else 1 << 30
 
     def _admit(self) -> None:
+        if self.admission == "simulate":
+            for seq in self._fitting_by_simulation():
+                self._take_in(seq)
+            return
         room = None  # the headroom, worked out once and kept up to date while sequences get in
         while self.queued and len(self.prefilling) + len(self.decoding) < self.max_seqs \
                 and self.cache.slots.num_free > 0:
             seq = self.queued[0]
-            if self.admission == "simulate":
-                first = [self.cache.pages_for(self._first_windowed_tokens(seq) if g.need.window else seq.n_known)
-                         for g in self.cache.groups]
-                if any(n > g.allocator.num_free for n, g in zip(first, self.cache.groups)) or \
-                        any(peak > g.allocator.num_pages
-                            for peak, g in zip(self._simulated_peak([seq]), self.cache.groups)):
-                    break
+            if room is None:
+                room = self._headroom()
+            need = self._admission_need(seq)
+            if any(r < n for r, n in zip(room, need)):
+                break
+            room = [r - n for r, n in zip(room, need)]
+            self._take_in(seq)
+
+    def _take_in(self, seq: Sequence) -> None:
+        """Admit the head of the queue: a slot, the prompt's pages, into the list of those in prompt."""
+        assert self.queued[0] is seq
+        self.queued.popleft()
+        self.cache.admit(seq.id)
+        self.cache.ensure_capacity(seq.id, seq.n_known, windowed_tokens=self._first_windowed_tokens(seq))
+        seq.fed = 0
+        seq.admitted_at = self._admissions
+        self._admissions += 1
+        seq.stage = "prefilling"
+        self.prefilling.append(seq)
+
+    def _fitting_by_simulation(self) -> list[Sequence]:
+        """The longest head of the queue that gets in under admission by simulation: slots for all of them, their
+        prompts' pages free now, and the simulated peak with all of them within every pool.  A longer head never
+        has a lower peak, so the longest one that fits is found by halving (the reference takes its queue in
+        batches with a binary back-off too, tokasaurus/manager/manager.py:561-656): a few simulations an
+        admission round instead of one a sequence."""
+        limit = min(len(self.queued), self.max_seqs - len(self.prefilling) - len(self.decoding),
+                    self.cache.slots.num_free)
+        if limit <= 0:
+            return []
+        head = [self.queued[i] for i in range(limit)]
+        groups = self.cache.groups
+        # how many of them find their first pages free
+        free = [g.allocator.num_free for g in groups]
+        for n, seq in enumerate(head):
+            for i, g in enumerate(groups):
+                free[i] -= self.cache.pages_for(self._first_windowed_tokens(seq) if g.need.window else seq.n_known)
+            if min(free) < 0:
+                head = head[:n]
+                break
+
+        def fits(k: int) -> bool:
+            return all(peak <= g.allocator.num_pages for peak, g in zip(self._simulated_peak(head[:k]), groups))
+
+        if not head or fits(len(head)):
+            return head
+        lo, hi = 0, len(head) - 1  # fits(lo) holds (with nobody new the running ones fit); find the largest that does
+        while lo < hi:
+            mid = (lo + hi + 1) // 2
+            if fits(mid):
+                lo = mid
             else:
-                if room is None:
-                    room = self._headroom()
-                need = self._admission_need(seq)
-                if any(r < n for r, n in zip(room, need)):
-                    break
-                room = [r - n for r, n in zip(room, need)]
-            self.queued.popleft()
-            self.cache.admit(seq.id)
-            self.cache.ensure_capacity(seq.id, seq.n_known, windowed_tokens=self._first_windowed_tokens(seq))
-            seq.fed = 0
-            seq.admitted_at = self._admissions
-            self._admissions += 1
-            seq.stage = "prefilling"
-            self.prefilling.append(seq)
+                hi = mid - 1
+        return head[:lo]
 
     def _bump_one(self, protect: Sequence) -> Sequence | None:
         """Push out the most recently admitted running sequence other than ``protect``."""
