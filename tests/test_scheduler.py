@@ -451,3 +451,28 @@ def test_simulated_peak_is_what_really_happens(seed):
         most = max(most, used())
         s.complete(plan, [7] * sum(p.samples for p in plan.portions))
     assert most == predicted  # under a greedy prefill the simulation is what happens
+
+
+@pytest.mark.parametrize("seed", range(8))
+def test_the_head_taken_in_one_go_is_the_head_taken_one_by_one(seed):
+    """Admission by simulation finds the longest head of the queue that fits by halving; it is the same head that
+    asking request by request gives, and the next one in the queue would not have fitted."""
+    import random
+    rng = random.Random(seed)
+    s, cache = make_sim(rng.randint(20, 120), max_tokens=32, max_seqs=rng.randint(3, 12))
+    for i in range(20):
+        s.add_request(req(i, rng.randint(1, 40), rng.randint(1, 50)))
+    for _ in range(rng.randint(0, 5)):
+        plan = s.schedule()
+        s.complete(plan, [7] * sum(p.samples for p in plan.portions))
+    head = s._fitting_by_simulation()
+    pool = cache.groups[0].allocator.num_pages
+    slots = min(len(s.queued), s.max_seqs - len(s.running()), cache.slots.num_free)
+    one_by_one, free = 0, cache.groups[0].allocator.num_free
+    while one_by_one < slots:
+        nxt = s.queued[one_by_one]
+        free -= cache.pages_for(nxt.n_known)
+        if free < 0 or s._simulated_peak([s.queued[i] for i in range(one_by_one + 1)])[0] > pool:
+            break
+        one_by_one += 1
+    assert [q.id for q in head] == [s.queued[i].id for i in range(one_by_one)]
