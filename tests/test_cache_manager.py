@@ -3,6 +3,7 @@ requests; windows give pages back; slots."""
 
 import random
 
+import numpy as np
 import pytest
 
 from tokasaurus_b200.cache import CacheManager, NoSlotError, NoSpaceError, PageAllocator, StateSlotAllocator
@@ -152,3 +153,36 @@ def test_random_orders_keep_the_books(seed):
     assert m.slots.num_free == 6
     with pytest.raises(KeyError):
         m.free("q0")
+
+
+def test_decode_steps_are_laid_out_whole_and_equal_the_general_layout():
+    """A step of single tokens from the device is laid out by array operations; every array equals what the
+    request-by-request layout makes of the same entries (two cache groups, one windowed with pages given back)."""
+    from dataclasses import fields
+    from tokasaurus_b200.engine.batch import StepEntry, _decode_host_batch, _general_host_batch, build_host_batch
+
+    m = CacheManager({0: FULL, 1: WIN}, page_size=8, num_pages=64, max_requests=8)
+    rng = random.Random(3)
+    entries = []
+    for i in range(7):
+        rid, n = f"r{i}", rng.randint(0, 70)
+        m.admit(rid)
+        m.ensure_capacity(rid, n + 1)
+        m.release_behind_window(rid, n)
+        entries.append(StepEntry(rid, None, n, [0]))
+    fast, slow = _decode_host_batch(entries, m), _general_host_batch(entries, m)
+    for f in fields(fast):
+        a, b = getattr(fast, f.name), getattr(slow, f.name)
+        if isinstance(a, list) and a and isinstance(a[0], np.ndarray):
+            assert all(np.array_equal(x, y) and x.dtype == y.dtype for x, y in zip(a, b)), f.name
+        elif isinstance(a, np.ndarray):
+            assert np.array_equal(a, b) and a.dtype == b.dtype, f.name
+        else:
+            assert a == b, f.name
+    assert build_host_batch(entries, m).token_ids.tolist() == [-1] * 7
+    with pytest.raises(ValueError, match="twice"):
+        build_host_batch(entries + [entries[0]], m)
+    m.free("r0")
+    m.admit("short")
+    with pytest.raises(ValueError, match="holds 0 pages"):
+        build_host_batch([StepEntry("short", None, 3, [0])], m)

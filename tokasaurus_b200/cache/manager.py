@@ -176,6 +176,10 @@ class CacheManager:
         through the model: ``windowed_tokens`` (at most ``n_tokens``) says how far such groups are filled, so that
         a long prompt takes pages there portion by portion while the pages behind the window come back."""
         rc = self.requests[request]
+        if windowed_tokens is None:
+            need = (n_tokens + self.page_size - 1) // self.page_size
+            if all(len(t) >= need for t in rc.tables):
+                return  # the common case of a decode step: the token's page is there already
         missing = self.pages_missing(request, n_tokens, windowed_tokens)
         for m, g in zip(missing, self.groups):
             if m > g.allocator.num_free:

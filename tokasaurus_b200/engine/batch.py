@@ -177,6 +177,12 @@ class Stager:
 def build_host_batch(entries: Sequence[StepEntry], cache_manager) -> HostBatch:
     """Lay the entries out as one batch.  Every request must already hold pages for the positions
     it brings (``CacheManager.ensure_capacity``)."""
+    if all(e.tokens is None and len(e.want) == 1 and e.want[0] == 0 for e in entries):
+        return _decode_host_batch(entries, cache_manager)
+    return _general_host_batch(entries, cache_manager)
+
+
+def _general_host_batch(entries: Sequence[StepEntry], cache_manager) -> HostBatch:
     seen = set()
     tok: list[int] = []
     pos: list[int] = []
@@ -220,3 +226,37 @@ def build_host_batch(entries: Sequence[StepEntry], cache_manager) -> HostBatch:
                      [i32(x) for x in indptr],
                      [np.concatenate(x) if x else np.zeros((0,), dtype=np.int32) for x in pages],
                      [e.request for e in entries])
+
+
+def _decode_host_batch(entries: Sequence[StepEntry], cache_manager) -> HostBatch:
+    """``build_host_batch`` for a step in which every request brings the one token it sampled last and wants its
+    logits (a decode step): the same arrays, made whole instead of request by request, which is what the host has
+    time for when hundreds of requests decode."""
+    S = len(entries)
+    ps = cache_manager.page_size
+    requests = cache_manager.requests
+    ids = [e.request for e in entries]
+    if len(set(ids)) != S:
+        seen = set()
+        for r in ids:
+            if r in seen:
+                raise ValueError(f"request {r!r} appears twice in one step")
+            seen.add(r)
+    rcs = [requests[r] for r in ids]
+    start = np.fromiter((e.start for e in entries), dtype=np.int32, count=S)
+    ar = np.arange(S, dtype=np.int32)
+    need = (start + ps) // ps  # pages for positions [0, start + 1)
+    need_list = need.tolist()
+    indptrs, pages = [], []
+    for g in range(len(cache_manager.groups)):
+        tables = [rc.table_array(g) for rc in rcs]
+        for r, t, n in zip(ids, tables, need_list):
+            if t.shape[0] < n:
+                raise ValueError(f"request {r!r} holds {t.shape[0]} pages of group {g}, needs {n}")
+        indptr = np.zeros(S + 1, dtype=np.int32)
+        np.cumsum(need, out=indptr[1:])
+        indptrs.append(indptr)
+        pages.append(np.concatenate([t[:n] for t, n in zip(tables, need_list)]) if S else np.zeros((0,), dtype=np.int32))
+    slot = np.fromiter((rc.slot for rc in rcs), dtype=np.int32, count=S)
+    return HostBatch(np.full(S, -1, dtype=np.int32), start, ar, slot, ar.copy(), np.ones(S, dtype=np.int32), start + 1,
+                     ar.copy(), indptrs, pages, ids)
