@@ -199,6 +199,18 @@ def test_command_line(tiny_model_dirs, tmp_path):
     bad = subprocess.run([sys.executable, str(ROOT / "bin" / "toka"), f"model={d}", "nonsense=1"], capture_output=True,
                          text=True, timeout=120)
     assert bad.returncode == 2 and "unknown option" in bad.stderr
+    # the options of the command that reach the scheduler: two prompts, a reserve, a deeper run-ahead
+    q = cuttings.random_tokens(7, 256, 6)
+    proc = subprocess.run([sys.executable, str(ROOT / "bin" / "toka"), f"model={d}", "dtype=float32",
+                           "kv_cache_num_tokens=(16*64)", f"prompt_ids={json.dumps([p, q])}", "max_num_tokens=6",
+                           "ignore_eos=T", "admission=reserve", "kv_reserve_fraction=0.5", "scheduling_steps_ahead=4"],
+                          capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    recs = [json.loads(line) for line in proc.stdout.strip().split("\n")[-2:]]
+    assert recs[0]["completion_ids"] == want and recs[1]["completion_ids"] == PlainLlama(d, torch.float64).greedy(q, 6)
+    bad = subprocess.run([sys.executable, str(ROOT / "bin" / "toka"), f"model={d}", f"prompt_ids={json.dumps(p)}",
+                          "admission=hopeful"], capture_output=True, text=True, timeout=120)
+    assert bad.returncode != 0 and "admission" in bad.stderr
 
 
 def test_bad_token_id_is_refused_on_the_host(tiny_model_dirs):
